@@ -1,0 +1,230 @@
+"""Interleaved two-tower decoder: a VLM backbone and an action expert that share attention.
+
+Each layer projects q/k/v per tower, concatenates the present towers along the token axis,
+applies RoPE, optionally prepends cached (already rotated) prefix keys/values, runs ONE
+block-causal attention and sends each tower's slice back through its own output projection
+and MLP.  This covers the three reference wrappers with one implementation
+(OpenTau ``policies/pi05/paligemma_with_expert.py:549-803``,
+``policies/pi07/gemma3_with_expert.py:419-584``, ``policies/cosmos3/qwen3vl_with_expert.py:208-342``).
+
+The KV cache is a pre-allocated ``(L, B, S_max, Hkv, D)`` pair per model instead of a
+dict grown by concatenation, so the denoise loop has static shapes and can be graph captured.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor, nn
+
+from .. import ops
+from .layers import AdaRMSNorm, DecoderLayer, Tower, TowerConfig
+
+
+@dataclass
+class KVCache:
+    """Post-RoPE keys/values of the first ``length`` prefix tokens for every layer."""
+
+    k: Tensor  # (L, B, S, Hkv, D)
+    v: Tensor
+    valid: Tensor  # (B, S) bool: pad mask of the cached tokens
+    length: int
+
+    def detach(self) -> "KVCache":
+        return KVCache(self.k.detach(), self.v.detach(), self.valid, self.length)
+
+    def expand_batch(self, n: int) -> "KVCache":
+        """Widen a batch-1 cache to ``n`` candidates that share the prefix (best-of-N)."""
+        L, B, S, H, D = self.k.shape
+        return KVCache(self.k.expand(L, n, S, H, D) if B == 1 else self.k.repeat_interleave(n, 1),
+                       self.v.expand(L, n, S, H, D) if B == 1 else self.v.repeat_interleave(n, 1),
+                       self.valid.expand(n, S) if B == 1 else self.valid.repeat_interleave(n, 0), self.length)
+
+
+class DualStreamDecoder(nn.Module):
+    """Runs ``towers[i]`` over ``inputs_embeds[i]`` (``None`` = tower absent in this pass)."""
+
+    def __init__(self, towers: list[Tower], dropout: float = 0.0, same_theta_for_all: bool = True,
+                 gradient_checkpointing: bool = False):
+        super().__init__()
+        self.towers = towers  # plain list: the owning wrapper registers the modules under HF names
+        self.dropout = nn.Dropout(dropout)
+        self.gradient_checkpointing = gradient_checkpointing
+        n = {t.cfg.num_hidden_layers for t in towers}
+        if len(n) != 1:
+            raise ValueError(f"towers must have the same depth, got {n}")
+        self.num_layers = n.pop()
+
+    # -- adaptive-norm conditions: one GEMM for all layers of a tower ------------------------------
+    @staticmethod
+    def _ada_mods(tower: Tower, cond: Tensor | None) -> list | None:
+        """Pre-computes ``dense(cond)`` of every adaptive norm of ``tower`` in one GEMM.
+
+        The condition is the same for every layer, so the 2L+1 small GEMMs collapse into one
+        ``[rows, cond] x [cond, (2L+1)*3H]`` product.  Returns per-layer tuples of slices.
+        """
+        if cond is None or not tower.cfg.use_adarms:
+            return None
+        norms: list[AdaRMSNorm] = []
+        for layer in tower.layers:
+            norms += [layer.input_layernorm, layer.post_attention_layernorm]
+        norms.append(tower.norm)
+        w = torch.cat([n.dense.weight for n in norms], dim=0)
+        b = torch.cat([n.dense.bias for n in norms], dim=0)
+        out = ops.linear(cond.to(w.dtype), w, b)
+        chunks = out.split(3 * tower.cfg.hidden_size, dim=-1)
+        return list(chunks)
+
+    def _layer(self, li: int, xs: list[Tensor | None], cos_sin, q_blk, k_blk, q_valid, k_valid,
+               cache_k, cache_v, mods) -> tuple[list[Tensor | None], Tensor | None, Tensor | None]:
+        towers = self.towers
+        qs, ks, vs, gates1, lens = [], [], [], [], []
+        for ti, (tower, x) in enumerate(zip(towers, xs)):
+            if x is None:
+                continue
+            layer: DecoderLayer = tower.layers[li]
+            if mods[ti] is not None:
+                h, g1 = layer.input_layernorm(x, precomputed=mods[ti][2 * li])
+            else:
+                h, g1 = layer.input_layernorm(x)
+            q, k, v = layer.self_attn.qkv(h)
+            qs.append(q), ks.append(k), vs.append(v), gates1.append(g1), lens.append(x.shape[1])
+        q = qs[0] if len(qs) == 1 else torch.cat(qs, dim=1)
+        k = ks[0] if len(ks) == 1 else torch.cat(ks, dim=1)
+        v = vs[0] if len(vs) == 1 else torch.cat(vs, dim=1)
+        cos, sin = cos_sin
+        q = ops.rope(q, cos, sin)
+        k = ops.rope(k, cos, sin)
+        new_k, new_v = k, v
+        if cache_k is not None:
+            k = torch.cat([cache_k, k], dim=1)
+            v = torch.cat([cache_v, v], dim=1)
+        first = next(t for t, x in zip(towers, xs) if x is not None)
+        att = ops.block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, first.cfg.attn_scale)
+        outs: list[Tensor | None] = []
+        start, j = 0, 0
+        for ti, (tower, x) in enumerate(zip(towers, xs)):
+            if x is None:
+                outs.append(None)
+                continue
+            layer = tower.layers[li]
+            cfg = tower.cfg
+            a = att[:, start:start + lens[j]]
+            start += lens[j]
+            g1 = gates1[j]
+            j += 1
+            drop = self.dropout if self.training and self.dropout.p > 0 else None
+            if cfg.sandwich_norms:
+                # Gemma-3: x + post_attn_norm(o_proj(att)); x + post_ffw_norm(mlp(pre_ffw_norm(x)))
+                o = layer.self_attn.o_proj(a)
+                if drop is not None:
+                    o = drop(o)
+                y = x + layer.post_attention_layernorm(o)[0]
+                m = layer.mlp(layer.pre_feedforward_layernorm(y)[0])
+                if drop is not None:
+                    m = drop(m)
+                outs.append(y + layer.post_feedforward_layernorm(m)[0])
+                continue
+            if g1 is None and drop is None:
+                y = layer.self_attn.o_proj(a, residual=x)
+            else:
+                o = layer.self_attn.o_proj(a)
+                if drop is not None:
+                    o = drop(o)
+                y = ops.gated_residual(x, o, g1)
+            if mods[ti] is not None:
+                n, g2 = layer.post_attention_layernorm(y, precomputed=mods[ti][2 * li + 1])
+            else:
+                n, g2 = layer.post_attention_layernorm(y)
+            if g2 is None and drop is None:
+                outs.append(layer.mlp(n, residual=y))
+            else:
+                m = layer.mlp(n)
+                if drop is not None:
+                    m = drop(m)
+                outs.append(ops.gated_residual(y, m, g2))
+        return outs, new_k, new_v
+
+    def forward(self, inputs_embeds: list[Tensor | None], position_ids: Tensor, q_blk: Tensor,
+                q_valid: Tensor, *, adarms_cond: list[Tensor | None] | None = None,
+                past: KVCache | None = None, fill_cache_len: int | None = None,
+                k_blk: Tensor | None = None, k_valid: Tensor | None = None,
+                mrope: bool = False, per_layer_cache: bool = True,
+                ) -> tuple[list[Tensor | None], KVCache | None]:
+        """One pass over all layers.
+
+        ``position_ids``: ``(B, S_total)`` (or ``(3,B,S_total)`` with ``mrope``) for the
+        concatenated present towers.  ``q_blk/q_valid`` describe those tokens; when ``past`` is
+        given its tokens are prepended as keys with block id ``INT_MIN`` (visible to every
+        query, gated only by ``past.valid``).  ``fill_cache_len=n`` returns a cache holding the
+        first ``n`` tokens' post-RoPE K/V of every layer.
+        """
+        towers = self.towers
+        xs = list(inputs_embeds)
+        present = [t for t, x in zip(towers, xs) if x is not None]
+        hd = present[0].cfg.head_dim
+        adarms_cond = adarms_cond or [None] * len(towers)
+        mods = [self._ada_mods(t, c) if x is not None else None for t, c, x in zip(towers, adarms_cond, xs)]
+
+        if k_blk is None:
+            k_blk, k_valid = q_blk, q_valid
+        if past is not None:
+            B = q_blk.shape[0]
+            cross_blk = torch.full((B, past.length), ops.INT_MIN, dtype=torch.int32, device=q_blk.device)
+            k_blk = torch.cat([cross_blk, k_blk], dim=1)
+            k_valid = torch.cat([past.valid[:, :past.length], k_valid], dim=1)
+
+        # RoPE tables once per distinct base (Gemma-3 alternates two bases across layers).
+        table_cache: dict[float, tuple[Tensor, Tensor]] = {}
+
+        def tables(theta: float):
+            if theta not in table_cache:
+                if mrope:
+                    table_cache[theta] = ops.mrope_angles(position_ids, hd, theta, True,
+                                                          present[0].cfg.mrope_sections)
+                else:
+                    table_cache[theta] = ops.rope_angles(position_ids, hd, theta)
+            return table_cache[theta]
+
+        new_cache = None
+        if fill_cache_len is not None:
+            B = q_blk.shape[0]
+            hk = present[0].cfg.num_key_value_heads
+            ref_x = next(x for x in xs if x is not None)
+            new_cache = KVCache(
+                ref_x.new_empty(self.num_layers, B, fill_cache_len, hk, hd),
+                ref_x.new_empty(self.num_layers, B, fill_cache_len, hk, hd),
+                q_valid[:, :fill_cache_len], fill_cache_len)
+        keep_graph = fill_cache_len is not None and torch.is_grad_enabled()
+        ks_list, vs_list = [], []
+
+        for li in range(self.num_layers):
+            theta = towers[0].cfg.layer_theta(li)
+            ck = past.k[li, :, :past.length] if past is not None else None
+            cv = past.v[li, :, :past.length] if past is not None else None
+            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                xs, nk, nv = checkpoint(self._layer, li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid,
+                                        ck, cv, mods, use_reentrant=False)
+            else:
+                xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods)
+            if fill_cache_len is not None:
+                if keep_graph:
+                    ks_list.append(nk[:, :fill_cache_len])
+                    vs_list.append(nv[:, :fill_cache_len])
+                else:
+                    new_cache.k[li].copy_(nk[:, :fill_cache_len])
+                    new_cache.v[li].copy_(nv[:, :fill_cache_len])
+        if keep_graph:
+            new_cache = KVCache(torch.stack(ks_list), torch.stack(vs_list), new_cache.valid, fill_cache_len)
+
+        outs: list[Tensor | None] = []
+        for ti, (tower, x) in enumerate(zip(towers, xs)):
+            if x is None:
+                outs.append(None)
+            elif mods[ti] is not None:
+                outs.append(tower.norm(x, precomputed=mods[ti][2 * self.num_layers])[0])
+            else:
+                outs.append(tower.norm(x)[0])
+        return outs, new_cache

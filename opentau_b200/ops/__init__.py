@@ -1,0 +1,125 @@
+"""Public op surface of the framework.
+
+``ops.<name>`` is what model code calls.  Each differentiable op is a hand-written
+autograd function (``fused.py``) over single-launch primitives (``prims.py``); a primitive
+runs the sm_100a kernel for CUDA bf16 tensors and a plain-PyTorch body on CPU.  Setting
+``OPENTAU_B200_ORACLE=1`` routes everything to ``reference.py`` (plain autograd over library
+calls) — the comparison arm, never the product path.  On a CUDA tensor a missing native
+library raises; there is no silent fallback.
+"""
+
+from __future__ import annotations
+
+import os
+
+from torch import Tensor
+
+
+def oracle_mode() -> bool:
+    return os.environ.get("OPENTAU_B200_ORACLE", "0") == "1"
+
+
+from . import reference as ref  # noqa: E402
+from .reference import (BIG_NEG, INT_MIN, apply_rope, dense_mask_from_blocks, flow_interpolate,  # noqa: E402
+                        make_block_ids, mrope_angles, rope_angles, sinusoidal_time_embedding)
+from . import prims, fused  # noqa: E402
+
+
+def linear(x: Tensor, w: Tensor, bias: Tensor | None = None, residual: Tensor | None = None) -> Tensor:
+    if oracle_mode():
+        return ref.linear(x, w, bias, residual)
+    return fused.linear(x, w, bias, residual)
+
+
+def rms_norm(x: Tensor, weight: Tensor | None, eps: float = 1e-6, unit_offset: bool = True) -> Tensor:
+    if oracle_mode():
+        return ref.rms_norm(x, weight, eps, unit_offset)
+    return fused.rms_norm(x, weight, eps, unit_offset)
+
+
+def ada_rms_norm(x: Tensor, mod: Tensor, eps: float = 1e-6):
+    if oracle_mode():
+        return ref.ada_rms_norm(x, mod, eps)
+    return fused.ada_rms_norm(x, mod, eps)
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Tensor, eps: float = 1e-6) -> Tensor:
+    if oracle_mode():
+        return ref.layer_norm(x, weight, bias, eps)
+    return fused.layer_norm(x, weight, bias, eps)
+
+
+def gated_residual(x: Tensor, y: Tensor, gate: Tensor | None) -> Tensor:
+    return ref.gated_residual(x, y, gate)
+
+
+def rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    if oracle_mode():
+        return ref.apply_rope(x, cos, sin)
+    return fused.rope(x, cos, sin)
+
+
+def gated_mlp(x: Tensor, w_gate_up: Tensor, w_down: Tensor, act: str, residual: Tensor | None = None) -> Tensor:
+    """``down(act(gate)·up)`` with the block-interleaved fused gate/up weight (``prims.GLU_BLOCK``)."""
+    if oracle_mode():
+        gu = ref.linear(x, w_gate_up)
+        h = _ref_glu(gu, act)
+        return ref.linear(h, w_down, None, residual)
+    return fused.gated_mlp(x, w_gate_up, w_down, act, residual)
+
+
+def _ref_glu(gu: Tensor, act: str) -> Tensor:
+    g, u = prims._split_glu(gu)
+    return (ref.act_fn(g.float(), act) * u.float()).flatten(-2).to(gu.dtype)
+
+
+def act_fn(x: Tensor, act: str) -> Tensor:
+    return ref.act_fn(x, act)
+
+
+def block_attention(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor,
+                    q_valid: Tensor, k_valid: Tensor, scale: float) -> Tensor:
+    if oracle_mode():
+        return ref.block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
+    return fused.block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
+
+
+def mha(q: Tensor, k: Tensor, v: Tensor, scale: float, add_mask: Tensor | None = None) -> Tensor:
+    """Full (unmasked) multi-head attention; with ``add_mask`` it stays on the reference body."""
+    if oracle_mode() or add_mask is not None:
+        return ref.mha(q, k, v, scale, add_mask)
+    import torch
+    B, S, _, _ = q.shape
+    Sk = k.shape[1]
+    zq = torch.zeros(B, S, dtype=torch.int32, device=q.device)
+    zk = torch.zeros(B, Sk, dtype=torch.int32, device=q.device)
+    oq = torch.ones(B, S, dtype=torch.bool, device=q.device)
+    ok = torch.ones(B, Sk, dtype=torch.bool, device=q.device)
+    return fused.block_attention(q, k, v, zq, zk, oq, ok, scale)
+
+
+def flow_matching_masked_mse(u_t, v_t, prefix_mask=None, actions_is_pad=None, real_action_dim=None,
+                             return_per_sample=False):
+    return ref.flow_matching_masked_mse(u_t, v_t, prefix_mask, actions_is_pad, real_action_dim,
+                                        return_per_sample)
+
+
+def linear_cross_entropy(h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor) -> Tensor:
+    if oracle_mode():
+        return ref.linear_cross_entropy(h, w, bias, labels)
+    return fused.linear_cross_entropy(h, w, bias, labels)
+
+
+def resize_with_pad(img: Tensor, width: int, height: int, pad_value: float = -1.0) -> Tensor:
+    if img.is_cuda and not oracle_mode():
+        from . import cuda_ops
+        return cuda_ops.resize_with_pad(img, width, height, pad_value)
+    return ref.resize_with_pad(img, width, height, pad_value)
+
+
+__all__ = [
+    "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "rope",
+    "gated_mlp", "act_fn", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
+    "resize_with_pad", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
+    "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "oracle_mode", "prims", "fused", "ref",
+]

@@ -1,0 +1,241 @@
+"""Autograd functions whose forward and backward are explicit sequences of primitives.
+
+Writing the backward by hand (instead of letting autograd chain small ops) is what lets each
+step be one fused kernel on the B200 and lets the MLP keep only ``x`` and the gate/up GEMM
+output alive between forward and backward.
+
+Weight gradients: when a parameter carries a ``main_grad`` tensor (a view into the flat
+gradient buffer of ``parallel.flat.FlatParamStore``) the weight-gradient GEMM accumulates
+straight into it and autograd receives ``None``; otherwise the gradient is returned normally.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import prims
+
+
+def _flat2d(x: Tensor) -> Tensor:
+    return x.reshape(-1, x.shape[-1])
+
+
+def _sink_wgrad(wref, a: Tensor, b: Tensor):
+    """d(weight) = a.T @ b, into ``main_grad`` when present (returns None) else returned."""
+    mg = getattr(wref, "main_grad", None)
+    if mg is not None:
+        prims.mm_tn(a, b, out=mg, accumulate=True)
+        return None
+    return prims.mm_tn(a, b)
+
+
+def _sink_vec(pref, g: Tensor):
+    mg = getattr(pref, "main_grad", None)
+    if mg is not None:
+        mg.add_(g.to(mg.dtype))
+        return None
+    return g
+
+
+class LinearFn(torch.autograd.Function):
+    """``y = x @ w.T (+ bias) (+ residual)``."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        x2 = _flat2d(x)
+        r2 = _flat2d(residual) if residual is not None else None
+        y = prims.mm_nt(x2, w, bias=bias, residual=r2)
+        ctx.save_for_backward(x2, w)
+        ctx.wref, ctx.bref = w, bias
+        ctx.x_shape = x.shape
+        ctx.has_res = residual is not None
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _flat2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = prims.mm_nn(dy2, w).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = _sink_wgrad(ctx.wref, dy2, x2)
+        if ctx.bref is not None and ctx.needs_input_grad[2]:
+            db = _sink_vec(ctx.bref, prims.col_sum(dy2))
+        dres = dy if ctx.has_res else None
+        return dx, dw, db, dres
+
+
+def linear(x, w, bias=None, residual=None):
+    return LinearFn.apply(x, w, bias, residual)
+
+
+class GatedMLPFn(torch.autograd.Function):
+    """``down(act(gate(x)) * up(x)) (+ residual)`` with a fused, block-interleaved gate/up weight.
+
+    Saves ``x`` and the gate/up GEMM output only; the activation product is recomputed in the
+    backward and its gradient overwrites the saved gate/up buffer in place.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down, residual, act):
+        x2 = _flat2d(x)
+        gu = prims.mm_nt(x2, w_gu)
+        h = prims.glu_fwd(gu, act)
+        r2 = _flat2d(residual) if residual is not None else None
+        y = prims.mm_nt(h, w_down, residual=r2)
+        ctx.save_for_backward(x2, gu, w_gu, w_down)
+        ctx.wgu, ctx.wdown = w_gu, w_down
+        ctx.act, ctx.x_shape, ctx.has_res = act, x.shape, residual is not None
+        return y.view(*x.shape[:-1], w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, gu, w_gu, w_down = ctx.saved_tensors
+        dy2 = _flat2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        h = prims.glu_fwd(gu, ctx.act)
+        dwd = _sink_wgrad(ctx.wdown, dy2, h) if ctx.needs_input_grad[2] else None
+        dh = prims.mm_nn(dy2, w_down, out=h)  # h is dead after the weight gradient
+        dgu = prims.glu_bwd(gu, dh, ctx.act, inplace=True)
+        del dh, h
+        dwgu = _sink_wgrad(ctx.wgu, dgu, x2) if ctx.needs_input_grad[1] else None
+        dx = prims.mm_nn(dgu, w_gu).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        return dx, dwgu, dwd, (dy if ctx.has_res else None), None
+
+
+def gated_mlp(x, w_gu, w_down, act, residual=None):
+    return GatedMLPFn.apply(x, w_gu, w_down, residual, act)
+
+
+class RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, unit_offset):
+        y, rstd = prims.rms_fwd(x, w, eps, unit_offset)
+        ctx.save_for_backward(x, w if w is not None else x.new_empty(0), rstd)
+        ctx.has_w, ctx.unit_offset, ctx.wref = w is not None, unit_offset, w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dx, dw = prims.rms_bwd(dy.contiguous(), x, w if ctx.has_w else None, rstd, ctx.unit_offset)
+        if dw is not None:
+            dw = _sink_vec(ctx.wref, dw) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None
+
+
+def rms_norm(x, w, eps=1e-6, unit_offset=True):
+    return RMSNormFn.apply(x, w, eps, unit_offset)
+
+
+class AdaRMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mod, eps):
+        y, rstd = prims.ada_rms_fwd(x, mod, eps)
+        ctx.save_for_backward(x, mod, rstd)
+        H = x.shape[-1]
+        gate = mod[..., 2 * H:]
+        if gate.dim() == 2:
+            gate = gate[:, None, :]
+        return y, gate
+
+    @staticmethod
+    def backward(ctx, dy, dgate):
+        x, mod, rstd = ctx.saved_tensors
+        dx, dscale, dshift = prims.ada_rms_bwd(dy.contiguous(), x, mod, rstd)
+        if dgate is None:
+            dgate = torch.zeros_like(dscale)
+        elif mod.dim() == 2:
+            dgate = dgate.reshape(mod.shape[0], -1, dscale.shape[-1]).sum(1) if dgate.dim() == 3 else dgate
+        dmod = torch.cat([dscale, dshift, dgate.to(dscale.dtype)], dim=-1)
+        return dx, dmod, None
+
+
+def ada_rms_norm(x, mod, eps=1e-6):
+    return AdaRMSNormFn.apply(x, mod, eps)
+
+
+class LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        y, mean, rstd = prims.ln_fwd(x, w, b, eps)
+        ctx.save_for_backward(x, w, mean, rstd)
+        ctx.wref, ctx.bref = w, b
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, mean, rstd = ctx.saved_tensors
+        dx, dw, db = prims.ln_bwd(dy.contiguous(), x, w, mean, rstd)
+        return dx, _sink_vec(ctx.wref, dw), _sink_vec(ctx.bref, db), None
+
+
+def layer_norm(x, w, b, eps=1e-6):
+    return LayerNormFn.apply(x, w, b, eps)
+
+
+class RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return prims.rope_fwd(x, cos, sin, inverse=False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        return prims.rope_fwd(dy, cos, sin, inverse=True), None, None
+
+
+def rope(x, cos, sin):
+    return RopeFn.apply(x, cos, sin)
+
+
+class BlockAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, q_blk, k_blk, q_valid, k_valid, scale):
+        o, lse = prims.attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
+        ctx.save_for_backward(q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid = ctx.saved_tensors
+        dq, dk, dv = prims.attn_bwd(do.contiguous(), q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, ctx.scale)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, scale):
+    return BlockAttentionFn.apply(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
+
+
+class LinearCEFn(torch.autograd.Function):
+    """Per-row ``CE(h @ w.T + b, labels)`` without keeping the logits for the backward."""
+
+    @staticmethod
+    def forward(ctx, h, w, bias, labels):
+        loss, lse = prims.linear_ce_fwd(h, w, bias, labels)
+        ctx.save_for_backward(h, w, labels, lse)
+        ctx.wref, ctx.bref = w, bias
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        h, w, labels, lse = ctx.saved_tensors
+        dh, dw, db = prims.linear_ce_bwd(dloss.contiguous(), h, w, ctx.bref, labels, lse)
+        mg = getattr(ctx.wref, "main_grad", None)
+        if mg is not None:
+            mg.add_(dw.to(mg.dtype))
+            dw = None
+        if db is not None:
+            db = _sink_vec(ctx.bref, db)
+        return dh, dw, db, None
+
+
+def linear_cross_entropy(h, w, bias, labels):
+    return LinearCEFn.apply(h, w, bias, labels)

@@ -1,0 +1,147 @@
+"""Text and action tokenizers that work without network access.
+
+The reference loads the PaliGemma sentencepiece tokenizer and the FAST action processor from the
+hub (OpenTau ``policies/pi05/modeling_pi05.py:300-347``).  Here both are looked up locally first
+(``transformers`` cache); when they are not on disk, deterministic stand-ins with the same
+interface keep training, tests and benchmarks runnable:
+
+* :class:`HashTokenizer` — whitespace/punctuation pieces hashed into a fixed vocabulary;
+* :class:`DctActionTokenizer` — FAST-style discrete cosine transform + uniform quantisation of an
+  action chunk, one id per retained coefficient (no BPE merge table).
+"""
+
+from __future__ import annotations
+
+import hashlib
+import logging
+import math
+import re
+from functools import lru_cache
+
+import numpy as np
+import torch
+from torch import Tensor
+
+_PIECE = re.compile(r"\w+|[^\w\s]|\s+")
+
+
+class HashTokenizer:
+    """Deterministic offline tokenizer: ids 0=pad, 1=eos, 2=bos, pieces hashed into [3, vocab)."""
+
+    pad_token_id, eos_token_id, bos_token_id = 0, 1, 2
+
+    def __init__(self, vocab_size: int = 257152):
+        self.vocab_size = vocab_size
+
+    @lru_cache(maxsize=65536)
+    def _piece_id(self, piece: str) -> int:
+        h = int.from_bytes(hashlib.blake2b(piece.encode("utf-8"), digest_size=8).digest(), "little")
+        return 3 + h % (self.vocab_size - 3)
+
+    def encode(self, text: str, add_special_tokens: bool = True) -> list[int]:
+        ids = [self._piece_id(p) for p in _PIECE.findall(text)]
+        return ([self.bos_token_id] + ids) if add_special_tokens else ids
+
+    def __call__(self, texts, max_length: int | None = None, padding: str | bool = "max_length",
+                 truncation: bool = True, padding_side: str = "right", return_tensors: str = "pt",
+                 add_special_tokens: bool = True):
+        if isinstance(texts, str):
+            texts = [texts]
+        rows = [self.encode(t, add_special_tokens) for t in texts]
+        L = max_length or max(len(r) for r in rows)
+        ids = torch.full((len(rows), L), self.pad_token_id, dtype=torch.long)
+        mask = torch.zeros((len(rows), L), dtype=torch.long)
+        for i, r in enumerate(rows):
+            r = r[:L] if truncation else r
+            if padding_side == "right":
+                ids[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+                mask[i, :len(r)] = 1
+            else:
+                ids[i, L - len(r):] = torch.tensor(r, dtype=torch.long)
+                mask[i, L - len(r):] = 1
+        return {"input_ids": ids, "attention_mask": mask}
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        return " ".join(f"<{int(i)}>" for i in ids if not (skip_special_tokens and int(i) < 3))
+
+
+def load_text_tokenizer(name_or_path: str, vocab_size: int = 257152):
+    """Local HF tokenizer when available, else :class:`HashTokenizer`."""
+    try:
+        from transformers import AutoTokenizer
+        tok = AutoTokenizer.from_pretrained(name_or_path, local_files_only=True)
+        if len(tok) > vocab_size:
+            raise ValueError("tokenizer vocabulary exceeds the model's embedding table")
+        return tok
+    except Exception as e:  # noqa: BLE001 - any failure means "not on disk"
+        logging.getLogger(__name__).info(
+            "tokenizer %r not available locally (%s); using the offline hash tokenizer", name_or_path,
+            type(e).__name__)
+        return HashTokenizer(vocab_size)
+
+
+class DctActionTokenizer:
+    """FAST-style action tokenizer: per-dimension DCT-II over time, quantise, flatten low
+    frequencies first.  Id 0 is the pad id; coefficient value ``q`` maps to ``1 + clip(q + R)``."""
+
+    def __init__(self, vocab_size: int = 2048, scale: float = 10.0):
+        self.vocab_size = vocab_size
+        self.scale = scale
+        self.radius = (vocab_size - 2) // 2
+
+    @staticmethod
+    @lru_cache(maxsize=16)
+    def _dct_matrix(n: int) -> np.ndarray:
+        k = np.arange(n)[:, None]
+        t = np.arange(n)[None, :]
+        m = np.cos(math.pi * (t + 0.5) * k / n) * math.sqrt(2.0 / n)
+        m[0] /= math.sqrt(2.0)
+        return m
+
+    def __call__(self, actions) -> list[list[int]]:
+        a = np.asarray(actions.detach().float().cpu() if isinstance(actions, Tensor) else actions, dtype=np.float64)
+        if a.ndim == 2:
+            a = a[None]
+        B, T, D = a.shape
+        coef = np.einsum("kt,btd->bkd", self._dct_matrix(T), a)
+        q = np.clip(np.rint(coef * self.scale), -self.radius, self.radius).astype(np.int64)
+        out = []
+        for b in range(B):
+            flat = q[b].reshape(-1)               # frequency-major: low frequencies first
+            nz = np.nonzero(flat)[0]
+            end = int(nz[-1]) + 1 if len(nz) else 0
+            out.append((flat[:end] + self.radius + 1).tolist())
+        return out
+
+    def decode(self, tokens: list[list[int]], time_horizon: int, action_dim: int) -> np.ndarray:
+        out = np.zeros((len(tokens), time_horizon, action_dim))
+        m = self._dct_matrix(time_horizon)
+        for b, ids in enumerate(tokens):
+            flat = np.zeros(time_horizon * action_dim)
+            ids = [i for i in ids if i > 0][: flat.size]
+            flat[:len(ids)] = np.asarray(ids, dtype=np.float64) - self.radius - 1
+            out[b] = m.T @ (flat.reshape(time_horizon, action_dim) / self.scale)
+        return out
+
+
+def load_action_tokenizer(name_or_path: str, vocab_size: int = 2048):
+    try:
+        from transformers import AutoProcessor
+        return AutoProcessor.from_pretrained(name_or_path, trust_remote_code=True, local_files_only=True)
+    except Exception as e:  # noqa: BLE001
+        logging.getLogger(__name__).info(
+            "action tokenizer %r not available locally (%s); using the offline DCT tokenizer",
+            name_or_path, type(e).__name__)
+        return DctActionTokenizer(vocab_size)
+
+
+def pad_tokens(rows: list[list[int]], max_length: int, pad_id: int = 0) -> tuple[Tensor, Tensor]:
+    """Right-pads/truncates id lists to ``max_length``; returns ``(ids long, mask bool)``."""
+    ids = torch.full((len(rows), max_length), pad_id, dtype=torch.long)
+    mask = torch.zeros((len(rows), max_length), dtype=torch.bool)
+    for i, r in enumerate(rows):
+        r = list(r)[:max_length]
+        if r:
+            ids[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+            mask[i, :len(r)] = True
+    return ids, mask
