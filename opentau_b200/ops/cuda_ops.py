@@ -1,0 +1,411 @@
+"""Python side of the sm_100a kernels: argument checks, output allocation, ctypes launches.
+
+Every launcher validates shapes/strides/alignment on the host before the launch (the GPU pool has no
+compute-sanitizer), launches on the current torch stream, and returns torch tensors.  A nonzero
+return code from the native side raises.  ``check_status()`` reads the device status word that
+bounded waits write when they give up.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+launch_count = 0  # number of native kernel launches issued through this module (for benchmarks)
+
+EPI_BIAS, EPI_RESIDUAL, EPI_ACCUM, EPI_OUT_F32 = 1, 2, 4, 8
+EPI_GLU_GELU, EPI_GLU_SILU, EPI_BIAS_F32, EPI_NO_OUT, EPI_ACT_GELU = 16, 32, 64, 128, 256
+
+_status_ptr: dict[int, int] = {}
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Tensor | None) -> c_void_p:
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"native {what} failed with code {rc}")
+
+
+def status_pointer() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _status_ptr:
+        out = c_void_p(0)
+        _check(_lib.load("elementwise").otb_status_alloc(ctypes.byref(out)), "status_alloc")
+        _status_ptr[dev] = out.value
+    return _status_ptr[dev]
+
+
+def check_status(reset: bool = True) -> None:
+    """Raises if any kernel reported a timed-out wait since the last check (synchronises)."""
+    dev = torch.cuda.current_device()
+    if dev not in _status_ptr:
+        return
+    torch.cuda.synchronize()
+    buf = (ctypes.c_uint * 4)()
+    _check(_lib.load("elementwise").otb_status_read(c_void_p(_status_ptr[dev]), buf, int(reset)), "status_read")
+    if buf[0] != 0:
+        raise RuntimeError(f"kernel wait timed out: kernel={buf[0] >> 16} stage={buf[0] & 0xffff} "
+                           f"block={buf[1]} detail={buf[2]} reports={buf[3]}")
+
+
+# --------------------------------------------------------------------------------------------- GEMM
+def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual: Tensor | None = None,
+         out: Tensor | None = None, accumulate: bool = False, out_dtype: torch.dtype | None = None,
+         glu: str | None = None, glu_out: Tensor | None = None, store_out: bool = True, act: str | None = None,
+         bn: int = 0) -> Tensor:
+    """tcgen05 GEMM.  layout 'nt': a(M,K) b(N,K); 'nn': a(M,K) b(K,N); 'tn': a(K,M) b(K,N)."""
+    global launch_count
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm expects bf16 operands"
+    if a.stride(-1) != 1 or (a.stride(0) % 8) or (a.data_ptr() % 16):
+        a = a.contiguous()
+    if b.stride(-1) != 1 or (b.stride(0) % 8) or (b.data_ptr() % 16):
+        b = b.contiguous()
+    if layout == "nt":
+        M, K = a.shape
+        N, Kb = b.shape
+        a_mn, b_mn = 0, 0
+    elif layout == "nn":
+        M, K = a.shape
+        Kb, N = b.shape
+        a_mn, b_mn = 0, 1
+    elif layout == "tn":
+        K, M = a.shape
+        Kb, N = b.shape
+        a_mn, b_mn = 1, 1
+    else:
+        raise ValueError(layout)
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {tuple(a.shape)} x {tuple(b.shape)} ({layout})")
+    if N % 8:
+        raise ValueError(f"N={N} must be a multiple of 8")
+    flags = 0
+    odt = out_dtype or (out.dtype if out is not None else torch.bfloat16)
+    if out is None and store_out:
+        out = torch.empty(M, N, dtype=odt, device=a.device)
+    if out is not None:
+        if out.shape != (M, N) or out.stride(1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16:
+            raise ValueError("bad output tensor for gemm")
+        if out.dtype == torch.float32:
+            flags |= EPI_OUT_F32
+        elif out.dtype != torch.bfloat16:
+            raise ValueError("gemm output must be bf16 or fp32")
+    else:
+        flags |= EPI_NO_OUT
+    if accumulate:
+        flags |= EPI_ACCUM
+    if bias is not None:
+        if bias.numel() != N:
+            raise ValueError("bias size")
+        flags |= EPI_BIAS
+        if bias.dtype == torch.float32:
+            flags |= EPI_BIAS_F32
+        elif bias.dtype != torch.bfloat16:
+            raise ValueError("bias dtype")
+        bias = bias.contiguous()
+    if act == "gelu_tanh":
+        flags |= EPI_ACT_GELU
+    elif act is not None:
+        raise ValueError(act)
+    ldr = 0
+    if residual is not None:
+        if residual.shape != (M, N) or residual.dtype != torch.bfloat16 or residual.stride(1) != 1:
+            raise ValueError("bad residual for gemm")
+        flags |= EPI_RESIDUAL
+        ldr = residual.stride(0)
+    ldo2 = 0
+    if glu is not None:
+        flags |= EPI_GLU_GELU if glu == "gelu_tanh" else EPI_GLU_SILU
+        if glu_out is None:
+            glu_out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=a.device)
+        ldo2 = glu_out.stride(0)
+    rc = _lib.load("gemm_tcgen05").otb_gemm_bf16(
+        _p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
+        c_longlong(out.stride(0) if out is not None else N), c_int(a_mn), c_int(b_mn), _p(bias), _p(residual),
+        c_longlong(ldr), _p(glu_out), c_longlong(ldo2), c_int(flags), c_int(bn), c_void_p(status_pointer()),
+        _stream())
+    _check(rc, f"gemm[{layout} {M}x{N}x{K}]")
+    launch_count += 1
+    if glu is not None:
+        return glu_out if not store_out else (out, glu_out)
+    return out
+
+
+# --------------------------------------------------------------------------------------------- norms
+def _rows(x: Tensor) -> tuple[Tensor, int, int]:
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    return x2, x2.shape[0], H
+
+
+def rms_fwd(x: Tensor, w: Tensor | None, eps: float, unit_offset: bool):
+    global launch_count
+    x2, R, H = _rows(x)
+    y = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    rstd = torch.empty(R, dtype=torch.float32, device=x.device)
+    mode = 0 if w is None else (1 if unit_offset else 2)
+    wt = w.to(torch.bfloat16).contiguous() if w is not None else None
+    _check(_lib.load("elementwise").otb_rms_fwd(_p(x2), c_longlong(x2.stride(0)), _p(wt), c_void_p(0), c_longlong(0),
+                                                c_int(1), _p(y), _p(rstd), c_longlong(R), c_int(H), c_float(eps),
+                                                c_int(mode), _stream()), "rms_fwd")
+    launch_count += 1
+    return y.view(x.shape), rstd
+
+
+def _bwd_blocks(R: int) -> tuple[int, int]:
+    rpb = max(1, (R + 591) // 592)
+    return rpb, (R + rpb - 1) // rpb
+
+
+def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: bool):
+    global launch_count
+    x2, R, H = _rows(x)
+    dy2, _, _ = _rows(dy)
+    if dy2.stride(0) != H:
+        dy2 = dy2.contiguous()
+    dx = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    mode = 0 if w is None else (1 if unit_offset else 2)
+    rpb, nb = _bwd_blocks(R)
+    partial = torch.empty(nb, H, dtype=torch.float32, device=x.device) if w is not None else None
+    wt = w.to(torch.bfloat16).contiguous() if w is not None else None
+    lib = _lib.load("elementwise")
+    _check(lib.otb_rms_bwd(_p(dy2), _p(x2), c_longlong(x2.stride(0)), _p(wt), c_void_p(0), c_longlong(0), c_int(1),
+                           _p(rstd), _p(dx), _p(partial), c_void_p(0), c_void_p(0), c_longlong(R), c_int(H),
+                           c_int(mode), c_int(rpb), _stream()), "rms_bwd")
+    launch_count += 1
+    dw = None
+    if w is not None:
+        dw = torch.empty(H, dtype=torch.bfloat16, device=x.device)
+        _check(lib.otb_colsum_partials(_p(partial), c_int(nb), c_int(H), _p(dw), c_int(0), _stream()), "colsum")
+        launch_count += 1
+        dw = dw.to(w.dtype)
+    return dx.view(x.shape), dw
+
+
+def ada_rms_fwd(x: Tensor, mod: Tensor, eps: float):
+    global launch_count
+    B, S, H = x.shape
+    x2, R, _ = _rows(x)
+    mod2 = mod.reshape(-1, 3 * H)
+    if mod2.stride(1) != 1 or mod2.stride(0) % 8 or mod2.data_ptr() % 16:
+        mod2 = mod2.contiguous()
+    rows_per_mod = S if mod.dim() == 2 else 1
+    y = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    rstd = torch.empty(R, dtype=torch.float32, device=x.device)
+    _check(_lib.load("elementwise").otb_rms_fwd(_p(x2), c_longlong(x2.stride(0)), c_void_p(0), _p(mod2),
+                                                c_longlong(mod2.stride(0)), c_int(rows_per_mod), _p(y), _p(rstd),
+                                                c_longlong(R), c_int(H), c_float(eps), c_int(0), _stream()),
+           "ada_rms_fwd")
+    launch_count += 1
+    return y.view(x.shape), rstd
+
+
+def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor):
+    global launch_count
+    B, S, H = x.shape
+    x2, R, _ = _rows(x)
+    dy2 = dy.reshape(R, H).contiguous()
+    mod2 = mod.reshape(-1, 3 * H)
+    if mod2.stride(1) != 1 or mod2.stride(0) % 8 or mod2.data_ptr() % 16:
+        mod2 = mod2.contiguous()
+    rows_per_mod = S if mod.dim() == 2 else 1
+    dx = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    dscale = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    dshift = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    _check(_lib.load("elementwise").otb_rms_bwd(_p(dy2), _p(x2), c_longlong(x2.stride(0)), c_void_p(0), _p(mod2),
+                                                c_longlong(mod2.stride(0)), c_int(rows_per_mod), _p(rstd), _p(dx),
+                                                c_void_p(0), _p(dscale), _p(dshift), c_longlong(R), c_int(H), c_int(0),
+                                                c_int(1), _stream()), "ada_rms_bwd")
+    launch_count += 1
+    dscale, dshift = dscale.view(B, S, H), dshift.view(B, S, H)
+    if mod.dim() == 2:
+        dscale, dshift = dscale.float().sum(1).to(mod.dtype), dshift.float().sum(1).to(mod.dtype)
+    return dx.view(x.shape), dscale, dshift
+
+
+def ln_fwd(x: Tensor, w: Tensor, b: Tensor, eps: float):
+    global launch_count
+    x2, R, H = _rows(x)
+    if x2.stride(0) != H:
+        x2 = x2.contiguous()
+    y = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    mean = torch.empty(R, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(R, dtype=torch.float32, device=x.device)
+    _check(_lib.load("elementwise").otb_ln_fwd(_p(x2), _p(w.to(torch.bfloat16).contiguous()),
+                                               _p(b.to(torch.bfloat16).contiguous()), _p(y), _p(mean), _p(rstd),
+                                               c_longlong(R), c_int(H), c_float(eps), _stream()), "ln_fwd")
+    launch_count += 1
+    return y.view(x.shape), mean, rstd
+
+
+# --------------------------------------------------------------------------------------------- GLU / RoPE
+_ACT = {"gelu_tanh": 0, "silu": 1}
+
+
+def glu_fwd(gu: Tensor, act: str) -> Tensor:
+    global launch_count
+    gu2, M, I2 = _rows(gu)
+    if gu2.stride(0) != I2:
+        gu2 = gu2.contiguous()
+    h = torch.empty(M, I2 // 2, dtype=gu.dtype, device=gu.device)
+    _check(_lib.load("elementwise").otb_glu_fwd(_p(gu2), _p(h), c_longlong(M), c_int(I2 // 2), c_int(_ACT[act]),
+                                                _stream()), "glu_fwd")
+    launch_count += 1
+    return h.view(*gu.shape[:-1], I2 // 2)
+
+
+def glu_bwd(gu: Tensor, dh: Tensor, act: str, inplace: bool = False) -> Tensor:
+    global launch_count
+    gu2, M, I2 = _rows(gu)
+    if gu2.stride(0) != I2:
+        gu2 = gu2.contiguous()
+    dh2 = dh.reshape(M, I2 // 2).contiguous()
+    dgu = gu2 if inplace else torch.empty_like(gu2)
+    _check(_lib.load("elementwise").otb_glu_bwd(_p(gu2), _p(dh2), _p(dgu), c_longlong(M), c_int(I2 // 2),
+                                                c_int(_ACT[act]), _stream()), "glu_bwd")
+    launch_count += 1
+    return dgu.view(gu.shape)
+
+
+def rope_fwd(x: Tensor, cos: Tensor, sin: Tensor, inverse: bool = False) -> Tensor:
+    global launch_count
+    B, S, H, D = x.shape
+    if x.stride(3) != 1 or any(s % 8 for s in x.stride()[:3]) or x.data_ptr() % 16:
+        x = x.contiguous()
+    cos = cos.float().contiguous()
+    sin = sin.float().contiguous()
+    if cos.shape != (B, S, D // 2):
+        cos = cos.expand(B, S, D // 2).contiguous()
+        sin = sin.expand(B, S, D // 2).contiguous()
+    y = torch.empty(B, S, H, D, dtype=x.dtype, device=x.device)
+    _check(_lib.load("elementwise").otb_rope(_p(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)),
+                                             c_longlong(x.stride(2)), _p(cos), _p(sin), _p(y), c_int(B), c_int(S),
+                                             c_int(H), c_int(D), c_int(int(inverse)), _stream()), "rope")
+    launch_count += 1
+    return y
+
+
+# --------------------------------------------------------------------------------------------- CE
+def linear_ce_fwd(h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor):
+    global launch_count
+    R, V = h.shape[0], w.shape[0]
+    logits = gemm(h, w, "nt", bias=bias, out_dtype=torch.float32)
+    loss = torch.empty(R, dtype=torch.float32, device=h.device)
+    lse = torch.empty(R, dtype=torch.float32, device=h.device)
+    labels = labels.contiguous()
+    _check(_lib.load("elementwise").otb_ce_fwd(_p(logits), _p(labels), _p(loss), _p(lse), c_longlong(R), c_int(V),
+                                               _stream()), "ce_fwd")
+    launch_count += 1
+    return loss, lse
+
+
+def linear_ce_bwd(dloss: Tensor, h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor, lse: Tensor):
+    global launch_count
+    R, V = h.shape[0], w.shape[0]
+    logits = gemm(h, w, "nt", bias=bias, out_dtype=torch.float32)  # recomputed: logits are never kept
+    dlogits = torch.empty(R, V, dtype=torch.bfloat16, device=h.device)
+    _check(_lib.load("elementwise").otb_ce_bwd(_p(logits), _p(labels.contiguous()), _p(lse),
+                                               _p(dloss.float().contiguous()), _p(dlogits), c_longlong(R), c_int(V),
+                                               _stream()), "ce_bwd")
+    launch_count += 1
+    del logits
+    dh = gemm(dlogits, w, "nn")
+    dw = gemm(dlogits, h, "tn")
+    db = col_sum(dlogits).to(bias.dtype) if bias is not None else None
+    return dh, dw, db
+
+
+def col_sum(a: Tensor) -> Tensor:
+    global launch_count
+    a2, R, H = _rows(a)
+    rpb = max(1, (R + 255) // 256)
+    nb = (R + rpb - 1) // rpb
+    partial = torch.empty(nb, H, dtype=torch.float32, device=a.device)
+    lib = _lib.load("elementwise")
+    _check(lib.otb_colsum_bf16(_p(a2), c_longlong(R), c_int(H), c_longlong(a2.stride(0)), _p(partial), c_int(rpb),
+                               _stream()), "colsum_bf16")
+    out = torch.empty(H, dtype=torch.bfloat16, device=a.device)
+    _check(lib.otb_colsum_partials(_p(partial), c_int(nb), c_int(H), _p(out), c_int(0), _stream()), "colsum")
+    launch_count += 2
+    return out
+
+
+# --------------------------------------------------------------------------------------------- optimizer
+def sumsq_partials(g: Tensor, partial: Tensor) -> None:
+    global launch_count
+    _check(_lib.load("elementwise").otb_sumsq(_p(g), c_longlong(g.numel()), c_int(int(g.dtype == torch.bfloat16)),
+                                              _p(partial), c_int(partial.numel()), _stream()), "sumsq")
+    launch_count += 1
+
+
+def clip_coef(partial: Tensor, grad_scale: float, max_norm: float, out: Tensor) -> None:
+    global launch_count
+    _check(_lib.load("elementwise").otb_clip_coef(_p(partial), c_int(partial.numel()), c_float(grad_scale),
+                                                  c_float(max_norm), _p(out), _stream()), "clip_coef")
+    launch_count += 1
+
+
+def adamw(p32: Tensor, g: Tensor, m: Tensor, v: Tensor, p16: Tensor | None, *, lr: float, beta1: float, beta2: float,
+          eps: float, weight_decay: float, step: int, scale: Tensor | None = None) -> None:
+    global launch_count
+    n = p32.numel()
+    assert g.numel() == n and m.numel() == n and v.numel() == n
+    _check(_lib.load("elementwise").otb_adamw(_p(p32), _p(g), c_int(int(g.dtype == torch.bfloat16)), _p(m), _p(v),
+                                              _p(p16), c_longlong(n), c_float(lr), c_float(beta1), c_float(beta2),
+                                              c_float(eps), c_float(weight_decay), c_float(1.0 - beta1 ** step),
+                                              c_float(1.0 - beta2 ** step), _p(scale), _stream()), "adamw")
+    launch_count += 1
+
+
+# --------------------------------------------------------------------------------------------- images
+def resize_with_pad(img: Tensor, width: int, height: int, pad_value: float = -1.0) -> Tensor:
+    global launch_count
+    N, C, Hin, Win = img.shape
+    ratio = max(Win / width, Hin / height)
+    rh, rw = int(Hin / ratio), int(Win / ratio)
+    x = img.float().contiguous()
+    out = torch.empty(N, C, height, width, dtype=torch.float32, device=img.device)
+    _check(_lib.load("elementwise").otb_resize_pad(_p(x), _p(out), c_int(N * C), c_int(Hin), c_int(Win), c_int(height),
+                                                   c_int(width), c_int(rh), c_int(rw), c_float(pad_value), _stream()),
+           "resize_pad")
+    launch_count += 1
+    return out
+
+
+def gated_residual(x: Tensor, y: Tensor, gate: Tensor) -> Tensor:
+    global launch_count
+    B, S, H = x.shape
+    x2, y2 = x.reshape(-1, H).contiguous(), y.reshape(-1, H).contiguous()
+    g2 = gate.reshape(-1, H) if gate.stride(-1) == 1 else gate.reshape(-1, H).contiguous()
+    if g2.stride(0) % 8 or g2.data_ptr() % 16:
+        g2 = g2.contiguous()
+    rows_per_gate = (B * S) // g2.shape[0]
+    out = torch.empty_like(x2)
+    _check(_lib.load("elementwise").otb_gated_residual(_p(x2), _p(y2), _p(g2), c_longlong(g2.stride(0)),
+                                                       c_int(rows_per_gate), _p(out), c_longlong(B * S), c_int(H),
+                                                       _stream()), "gated_residual")
+    launch_count += 1
+    return out.view(x.shape)
+
+
+# --------------------------------------------------------------------------------------------- attention
+def attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale):
+    from . import attention
+    return attention.attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
+
+
+def attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale):
+    from . import attention
+    return attention.attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)

@@ -83,11 +83,12 @@ class GatedMLPFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_gu, w_down, residual, act):
         x2 = _flat2d(x)
-        gu = prims.mm_nt(x2, w_gu)
-        h = prims.glu_fwd(gu, act)
+        need_bwd = any(ctx.needs_input_grad[:3])
+        gu, h = prims.mm_nt_glu(x2, w_gu, act, keep_gu=need_bwd)
         r2 = _flat2d(residual) if residual is not None else None
         y = prims.mm_nt(h, w_down, residual=r2)
-        ctx.save_for_backward(x2, gu, w_gu, w_down)
+        if need_bwd:
+            ctx.save_for_backward(x2, gu, w_gu, w_down)
         ctx.wgu, ctx.wdown = w_gu, w_down
         ctx.act, ctx.x_shape, ctx.has_res = act, x.shape, residual is not None
         return y.view(*x.shape[:-1], w_down.shape[0])

@@ -81,7 +81,20 @@ def mm_tn(a: Tensor, b: Tensor, out: Tensor | None = None, accumulate: bool = Fa
 
 def col_sum(a: Tensor) -> Tensor:
     """Sum over rows of ``(M,N)`` in fp32 (bias gradient)."""
+    if _cuda(a):
+        from . import cuda_ops
+        return cuda_ops.col_sum(a)
     return a.float().sum(0).to(a.dtype)
+
+
+def mm_nt_glu(x: Tensor, w_gu: Tensor, act: str, keep_gu: bool = True) -> tuple[Tensor | None, Tensor]:
+    """``gu = x @ w_gu.T`` and ``h = act(gate) * up`` in one launch (activation in the GEMM epilogue)."""
+    if _cuda(x):
+        from . import cuda_ops
+        res = cuda_ops.gemm(x, w_gu, "nt", glu=act, store_out=keep_gu)
+        return res if keep_gu else (None, res)
+    gu = x @ w_gu.t()
+    return (gu if keep_gu else None), glu_fwd(gu, act)
 
 
 # ----------------------------------------------------------------------------- norms

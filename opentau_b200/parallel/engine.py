@@ -1,0 +1,258 @@
+"""Training engine: one process per GPU, flat bf16 parameters, sharded fp32 AdamW state.
+
+Replaces the reference's ``accelerate`` wrappers (DDP / DeepSpeed ZeRO-1/2/3 / FSDP; OpenTau
+``src/opentau/scripts/train.py:219-300,728-1006``) with one explicit step:
+
+    forward -> weighted loss -> backward (weight gradients accumulate into the flat gradient buffer)
+    -> gradient reduce-scatter over ranks -> global-norm clip coefficient -> fused AdamW on this rank's
+    shard of fp32 masters -> all-gather of the refreshed bf16 parameters.
+
+Numerics contract kept from the reference (``optim/master_weights.py:188-297``): bf16 live weights,
+fp32 masters for trainable parameters, L2 clip of the (rank-averaged) gradient at ``grad_clip_norm``
+with the pre-clip norm reported, decoupled weight decay, masters rounded to bf16 after the update.
+The gradient mean is taken in fp32 (the reference's DDP averages in bf16).
+
+``strategy``: ``"ddp"`` keeps full optimizer state on every rank (all-reduce); ``"zero2"`` / ``"fsdp"``
+shard the optimizer state (reduce-scatter + all-gather).  Parameters stay replicated in bf16 in both:
+with 180 GB of HBM3e a 3.4 B-parameter policy has no reason to re-gather weights every layer.
+``comm``: ``"p2p"`` runs the fused peer-memory kernels, ``"nccl"`` the library collectives (baseline).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from .. import ops
+from .flat import FlatGroup, FlatParamStore
+
+
+@dataclass
+class OptimHyper:
+    lr: float = 2.5e-5
+    betas: tuple[float, float] = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 1e-10
+    grad_clip_norm: float = 10.0
+
+
+def assemble_weighted_loss(losses: dict[str, Tensor], weights: dict[str, float]) -> Tensor:
+    """``sum_k w_k * loss_k`` over (MSE, CE) in that fixed order; zero-weight terms are dropped from
+    the graph (reference ``scripts/train.py:166-216``)."""
+    total = None
+    for key in ("MSE", "CE"):
+        w = float(weights.get(key, 1.0))
+        if key not in losses or w == 0.0:
+            continue
+        term = losses[key] * w if w != 1.0 else losses[key]
+        total = term if total is None else total + term
+    if total is None:
+        raise ValueError("every loss term has zero weight")
+    return total
+
+
+class _ShardState:
+    """fp32 master / moments for the slice ``[lo, hi)`` of one flat group."""
+
+    def __init__(self, group: FlatGroup, lo: int, hi: int):
+        self.lo, self.hi = lo, hi
+        dev = group.data.device
+        self.master = group.data[lo:hi].float().clone() if group.dtype != torch.float32 else None
+        self.m = torch.zeros(hi - lo, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(hi - lo, dtype=torch.float32, device=dev)
+
+
+class TrainEngine:
+    def __init__(self, policy: nn.Module, hyper: OptimHyper, *, device: torch.device | str,
+                 lr_lambda: Callable[[int], float] | None = None, loss_weights: dict[str, float] | None = None,
+                 strategy: str = "zero2", comm: str = "auto", process_group=None,
+                 grad_accum_steps: int = 1):
+        self.policy = policy
+        self.hyper = hyper
+        self.device = torch.device(device)
+        self.lr_lambda = lr_lambda
+        self.loss_weights = loss_weights or {"MSE": 1.0, "CE": 1.0}
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if self.world > 1 else 0
+        if strategy in ("fsdp", "zero1", "zero3", "deepspeed"):
+            strategy = "zero2"
+        if strategy not in ("ddp", "zero2"):
+            raise ValueError(f"unknown strategy {strategy!r}")
+        self.strategy = strategy if self.world > 1 else "ddp"
+        self.grad_accum_steps = grad_accum_steps
+        self.p2p = None
+        if comm == "auto":
+            comm = "p2p" if (self.world > 1 and self.device.type == "cuda") else "nccl"
+        allocator = None
+        if comm == "p2p" and self.world > 1:
+            from .comm import PeerComm
+            self.p2p = PeerComm(self.device, process_group)
+            allocator = self.p2p.alloc_symmetric
+        self.comm = comm
+        self.store = FlatParamStore(policy, self.device, pad_to=self.world, allocator=allocator)
+        if self.world > 1:
+            self._broadcast_params()
+        self.shards: list[_ShardState] = []
+        for g in self.store.groups:
+            if self.strategy == "zero2":
+                per = g.numel // self.world
+                lo, hi = self.rank * per, (self.rank + 1) * per
+            else:
+                lo, hi = 0, g.numel
+            self.shards.append(_ShardState(g, lo, hi))
+        if self.p2p is not None:
+            self.p2p.register(self.store, self.shards)
+        self.step_count = 0
+        self._micro = 0
+        n_part = 1024
+        self._partials = torch.zeros(len(self.store.groups) * n_part, dtype=torch.float32, device=self.device)
+        self._n_part = n_part
+        self._scale = torch.ones(2, dtype=torch.float32, device=self.device)
+        self.last_grad_norm: Tensor | None = None
+        self.store.zero_grad()
+
+    # -------------------------------------------------------------------------------------------
+    def _broadcast_params(self) -> None:
+        """Rank 0's initial weights win (DDP init broadcast / FSDP sync_module_states)."""
+        for g in self.store.groups:
+            dist.broadcast(g.data, src=0, group=self.pg)
+        for p in self.policy.parameters():
+            if not p.requires_grad:
+                dist.broadcast(p.data, src=0, group=self.pg)
+
+    def current_lr(self) -> float:
+        mult = self.lr_lambda(self.step_count) if self.lr_lambda is not None else 1.0
+        return self.hyper.lr * mult
+
+    # -------------------------------------------------------------------------------------------
+    def forward_backward(self, batch: dict[str, Any]) -> dict[str, Tensor]:
+        losses = self.policy(batch)
+        loss = assemble_weighted_loss(losses, self.loss_weights)
+        if self.grad_accum_steps > 1:
+            loss = loss / self.grad_accum_steps
+        loss.backward()
+        self._micro += 1
+        out = {k: v.detach() for k, v in losses.items() if isinstance(v, Tensor)}
+        out["loss"] = loss.detach() * self.grad_accum_steps
+        return out
+
+    def optimizer_step(self) -> Tensor:
+        """Gradient sync + clip + AdamW + parameter refresh.  Returns the pre-clip gradient norm."""
+        self.store.fold_autograd_grads()
+        self.step_count += 1
+        h = self.hyper
+        lr = self.hyper.lr * (self.lr_lambda(self.step_count - 1) if self.lr_lambda is not None else 1.0)
+        if self.p2p is not None:
+            norm = self.p2p.fused_step(lr=lr, hyper=h, step=self.step_count)
+        else:
+            norm = self._library_step(lr)
+        self.last_grad_norm = norm
+        self.store.zero_grad()
+        self._micro = 0
+        return norm
+
+    def _library_step(self, lr: float) -> Tensor:
+        h = self.hyper
+        world = self.world
+        grads: list[Tensor] = []
+        for g, sh in zip(self.store.groups, self.shards):
+            if world > 1:
+                if self.strategy == "zero2":
+                    if dist.get_backend(self.pg) == "nccl":
+                        shard = torch.empty(sh.hi - sh.lo, dtype=g.dtype, device=self.device)
+                        dist.reduce_scatter_tensor(shard, g.grad, op=dist.ReduceOp.SUM, group=self.pg)
+                    else:
+                        dist.all_reduce(g.grad, op=dist.ReduceOp.SUM, group=self.pg)
+                        shard = g.grad[sh.lo:sh.hi]
+                else:
+                    dist.all_reduce(g.grad, op=dist.ReduceOp.SUM, group=self.pg)
+                    shard = g.grad
+            else:
+                shard = g.grad
+            grads.append(shard)
+        # global L2 norm of the rank-averaged gradient
+        native = self.device.type == "cuda" and not ops.oracle_mode()
+        if native:
+            from ..ops import cuda_ops
+            self._partials.zero_()
+            for i, sg in enumerate(grads):
+                cuda_ops.sumsq_partials(sg, self._partials[i * self._n_part:(i + 1) * self._n_part])
+            total_sq = self._partials.sum()
+        else:
+            total_sq = sum((sg.float().pow(2).sum() for sg in grads), torch.zeros((), device=self.device))
+        if world > 1 and self.strategy == "zero2":
+            dist.all_reduce(total_sq, group=self.pg)
+        inv_world = 1.0 / world
+        norm = total_sq.sqrt() * inv_world
+        if h.grad_clip_norm and h.grad_clip_norm > 0:
+            coef = torch.clamp(h.grad_clip_norm / (norm + 1e-6), max=1.0)
+        else:
+            coef = torch.ones((), device=self.device)
+        self._scale[0] = coef * inv_world
+        self._scale[1] = norm
+        for g, sh, sg in zip(self.store.groups, self.shards, grads):
+            p_shard = g.data[sh.lo:sh.hi]
+            if native:
+                from ..ops import cuda_ops
+                if sh.master is not None:
+                    cuda_ops.adamw(sh.master, sg, sh.m, sh.v, p_shard, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
+                                   eps=h.eps, weight_decay=h.weight_decay, step=self.step_count, scale=self._scale)
+                else:
+                    cuda_ops.adamw(p_shard, sg, sh.m, sh.v, None, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
+                                   eps=h.eps, weight_decay=h.weight_decay, step=self.step_count, scale=self._scale)
+            else:
+                master = sh.master if sh.master is not None else p_shard
+                ops.ref.adamw_flat(master, sg, sh.m, sh.v, p_shard if sh.master is not None else None, lr=lr,
+                                   beta1=h.betas[0], beta2=h.betas[1], eps=h.eps, weight_decay=h.weight_decay,
+                                   step=self.step_count, grad_scale=float(self._scale[0]))
+            if world > 1 and self.strategy == "zero2":
+                if dist.get_backend(self.pg) == "nccl":
+                    dist.all_gather_into_tensor(g.data, p_shard.clone(), group=self.pg)
+                else:
+                    parts = [torch.empty_like(p_shard) for _ in range(world)]
+                    dist.all_gather(parts, p_shard.clone(), group=self.pg)
+                    g.data.copy_(torch.cat(parts))
+        return norm
+
+    def train_step(self, batch: dict[str, Any]) -> dict[str, Tensor]:
+        """One optimizer step over ``grad_accum_steps`` calls (returns metrics of this micro-batch)."""
+        out = self.forward_backward(batch)
+        if self._micro >= self.grad_accum_steps:
+            out["grad_norm"] = self.optimizer_step()
+            out["lr"] = torch.tensor(self.current_lr())
+        return out
+
+    # ------------------------------------------------------------------------------------------- state
+    def state_dict(self) -> dict[str, Any]:
+        sd: dict[str, Any] = {"step": self.step_count, "rank": self.rank, "world": self.world,
+                              "strategy": self.strategy}
+        for i, sh in enumerate(self.shards):
+            sd[f"group{i}.lo"], sd[f"group{i}.hi"] = sh.lo, sh.hi
+            sd[f"group{i}.m"], sd[f"group{i}.v"] = sh.m, sh.v
+            if sh.master is not None:
+                sd[f"group{i}.master"] = sh.master
+        return sd
+
+    def load_state_dict(self, sd: dict[str, Any], rebuild_masters_from_live: bool = False) -> None:
+        self.step_count = int(sd["step"])
+        for i, sh in enumerate(self.shards):
+            if (sd[f"group{i}.lo"], sd[f"group{i}.hi"]) != (sh.lo, sh.hi):
+                raise ValueError("optimizer shard layout differs (world size changed); use rebuild")
+            sh.m.copy_(sd[f"group{i}.m"])
+            sh.v.copy_(sd[f"group{i}.v"])
+            if sh.master is not None:
+                if rebuild_masters_from_live or f"group{i}.master" not in sd:
+                    sh.master.copy_(self.store.groups[i].data[sh.lo:sh.hi].float())
+                else:
+                    sh.master.copy_(sd[f"group{i}.master"])
+
+    def rebuild_masters_from_live(self) -> None:
+        for g, sh in zip(self.store.groups, self.shards):
+            if sh.master is not None:
+                sh.master.copy_(g.data[sh.lo:sh.hi].float())

@@ -1,0 +1,218 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op (run on a B200)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def _ref_gemm(a, b, layout):
+    a, b = a.float(), b.float()
+    if layout == "nt":
+        return a @ b.t()
+    if layout == "nn":
+        return a @ b
+    return a.t() @ b
+
+
+def _operands(layout, M, N, K, dev):
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K)
+    mk = lambda *s: (torch.randn(*s, generator=g) * 0.5).to(torch.bfloat16).to(dev)  # noqa: E731
+    if layout == "nt":
+        return mk(M, K), mk(N, K)
+    if layout == "nn":
+        return mk(M, K), mk(K, N)
+    return mk(K, M), mk(K, N)
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 264, 136), (1000, 2048, 1024),
+                                   (50, 1024, 2048), (384, 64, 512), (130, 128, 72)])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_layouts(layout, shape, bn, dev):
+    from opentau_b200.ops import cuda_ops
+    M, N, K = shape
+    if layout == "tn" and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    a, b = _operands(layout, M, N, K, dev)
+    out = cuda_ops.gemm(a, b, layout, bn=bn)
+    cuda_ops.check_status()
+    ref = _ref_gemm(a, b, layout)
+    err = (out.float() - ref).abs().max().item()
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    assert err <= tol, f"{layout} {shape} bn={bn}: max err {err} (tol {tol})"
+
+
+def test_gemm_epilogues(dev):
+    from opentau_b200.ops import cuda_ops
+    M, N, K = 300, 512, 320
+    a, b = _operands("nt", M, N, K, dev)
+    bias = torch.randn(N, device=dev).to(torch.bfloat16)
+    res = torch.randn(M, N, device=dev).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    out = cuda_ops.gemm(a, b, "nt", bias=bias, residual=res)
+    torch.testing.assert_close(out.float(), ref + bias.float() + res.float(), rtol=2e-2, atol=8e-2)
+    out32 = cuda_ops.gemm(a, b, "nt", bias=bias.float(), out_dtype=torch.float32)
+    torch.testing.assert_close(out32, ref + bias.float(), rtol=1e-3, atol=1e-2)
+    acc = torch.ones(M, N, device=dev, dtype=torch.bfloat16)
+    cuda_ops.gemm(a, b, "nt", out=acc, accumulate=True)
+    torch.testing.assert_close(acc.float(), ref + 1.0, rtol=2e-2, atol=8e-2)
+    g = cuda_ops.gemm(a, b, "nt", bias=bias, act="gelu_tanh")
+    torch.testing.assert_close(g.float(), torch.nn.functional.gelu(ref + bias.float(), approximate="tanh"),
+                               rtol=2e-2, atol=8e-2)
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_gemm_glu_epilogue(act, dev):
+    from opentau_b200.ops import cuda_ops, prims
+    M, K, I = 260, 256, 384
+    x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(dev)
+    w = (torch.randn(2 * I, K) * 0.1).to(torch.bfloat16).to(dev)
+    gu, h = cuda_ops.gemm(x, w, "nt", glu=act)
+    gu_ref = (x.float() @ w.float().t()).to(torch.bfloat16)
+    torch.testing.assert_close(gu.float(), gu_ref.float(), rtol=2e-2, atol=3e-2)
+    h_ref = prims.glu_fwd(gu_ref.cpu().float(), act).to(dev)
+    torch.testing.assert_close(h.float(), h_ref, rtol=3e-2, atol=3e-2)
+    h_only = cuda_ops.gemm(x, w, "nt", glu=act, store_out=False)
+    torch.testing.assert_close(h_only.float(), h.float())
+    h2 = cuda_ops.glu_fwd(gu, act)
+    torch.testing.assert_close(h2.float(), h.float(), rtol=2e-2, atol=2e-2)
+    dh = torch.randn(M, I, device=dev).to(torch.bfloat16)
+    dgu = cuda_ops.glu_bwd(gu, dh, act)
+    dgu_ref = prims.glu_bwd(gu.cpu().float(), dh.cpu().float(), act)
+    torch.testing.assert_close(dgu.cpu().float(), dgu_ref, rtol=3e-2, atol=3e-2)
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("H", [64, 256, 1024, 1152, 2048, 5120])
+@pytest.mark.parametrize("mode", ["plain1", "plain0", "noweight"])
+def test_rms_norm_kernels(H, mode, dev):
+    from opentau_b200.ops import cuda_ops, prims
+    R = 77
+    x = torch.randn(R, H, device=dev).to(torch.bfloat16)
+    w = (torch.randn(H, device=dev) * 0.1).to(torch.bfloat16) if mode != "noweight" else None
+    unit = mode == "plain1"
+    y, rstd = cuda_ops.rms_fwd(x, w, 1e-6, unit)
+    yr, rr = prims.rms_fwd(x.cpu().float(), None if w is None else w.cpu().float(), 1e-6, unit)
+    torch.testing.assert_close(y.cpu().float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(rstd.cpu(), rr, rtol=1e-4, atol=1e-5)
+    dy = torch.randn(R, H, device=dev).to(torch.bfloat16)
+    dx, dw = cuda_ops.rms_bwd(dy, x, w, rstd, unit)
+    dxr, dwr = prims.rms_bwd(dy.cpu().float(), x.cpu().float(), None if w is None else w.cpu().float(), rr, unit)
+    torch.testing.assert_close(dx.cpu().float(), dxr, rtol=3e-2, atol=3e-2)
+    if w is not None:
+        torch.testing.assert_close(dw.cpu().float(), dwr, rtol=3e-2, atol=1e-1)
+
+
+@pytest.mark.parametrize("per_token", [True, False])
+def test_ada_rms_kernels(per_token, dev):
+    from opentau_b200.ops import cuda_ops, prims
+    B, S, H = 3, 10, 1024
+    x = torch.randn(B, S, H, device=dev).to(torch.bfloat16)
+    mod = (torch.randn(B, S, 3 * H, device=dev) * 0.3).to(torch.bfloat16)
+    if not per_token:
+        mod = mod[:, 0].contiguous()
+    y, rstd = cuda_ops.ada_rms_fwd(x, mod, 1e-6)
+    yr, rr = prims.ada_rms_fwd(x.cpu().float(), mod.cpu().float(), 1e-6)
+    torch.testing.assert_close(y.cpu().float(), yr, rtol=2e-2, atol=3e-2)
+    dy = torch.randn(B, S, H, device=dev).to(torch.bfloat16)
+    dx, dsc, dsh = cuda_ops.ada_rms_bwd(dy, x, mod, rstd)
+    dxr, dscr, dshr = prims.ada_rms_bwd(dy.cpu().float(), x.cpu().float(), mod.cpu().float(), rr)
+    torch.testing.assert_close(dx.cpu().float(), dxr, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(dsc.cpu().float(), dscr, rtol=3e-2, atol=1e-1)
+    torch.testing.assert_close(dsh.cpu().float(), dshr, rtol=3e-2, atol=1e-1)
+
+
+def test_layer_norm_kernel(dev):
+    from opentau_b200.ops import cuda_ops, prims
+    x = torch.randn(50, 1152, device=dev).to(torch.bfloat16)
+    w = torch.randn(1152, device=dev).to(torch.bfloat16)
+    b = torch.randn(1152, device=dev).to(torch.bfloat16)
+    y, mean, rstd = cuda_ops.ln_fwd(x, w, b, 1e-6)
+    yr, mr, rr = prims.ln_fwd(x.cpu().float(), w.cpu().float(), b.cpu().float(), 1e-6)
+    torch.testing.assert_close(y.cpu().float(), yr, rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(mean.cpu(), mr, rtol=1e-3, atol=1e-4)
+
+
+def test_rope_kernel_strided(dev):
+    from opentau_b200 import ops
+    from opentau_b200.ops import cuda_ops
+    B, S, H, D = 2, 33, 4, 64
+    qkv = torch.randn(B, S, (H + 2) * D, device=dev).to(torch.bfloat16)
+    q = qkv[..., :H * D].unflatten(-1, (H, D))
+    pos = torch.arange(S, device=dev)[None].expand(B, -1)
+    cos, sin = ops.rope_angles(pos, D, 10000.0)
+    y = cuda_ops.rope_fwd(q, cos, sin)
+    yr = ops.ref.apply_rope(q.float(), cos, sin)
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    back = cuda_ops.rope_fwd(y, cos, sin, inverse=True)
+    torch.testing.assert_close(back.float(), q.float(), rtol=3e-2, atol=3e-2)
+
+
+def test_linear_ce_kernels(dev):
+    from opentau_b200.ops import cuda_ops, prims
+    R, H, V = 96, 256, 2048
+    h = torch.randn(R, H, device=dev).to(torch.bfloat16)
+    w = (torch.randn(V, H, device=dev) * 0.05).to(torch.bfloat16)
+    b = (torch.randn(V, device=dev) * 0.1).to(torch.bfloat16)
+    labels = torch.randint(0, V, (R,), device=dev)
+    loss, lse = cuda_ops.linear_ce_fwd(h, w, b, labels)
+    lr_, lser = prims.linear_ce_fwd(h.cpu().float(), w.cpu().float(), b.cpu().float(), labels.cpu())
+    torch.testing.assert_close(loss.cpu(), lr_, rtol=1e-2, atol=2e-2)
+    dloss = torch.rand(R, device=dev)
+    dh, dw, db = cuda_ops.linear_ce_bwd(dloss, h, w, b, labels, lse)
+    dhr, dwr, dbr = prims.linear_ce_bwd(dloss.cpu(), h.cpu().float(), w.cpu().float(), b.cpu().float(), labels.cpu(), lser)
+    torch.testing.assert_close(dh.cpu().float(), dhr, rtol=5e-2, atol=2e-2)
+    torch.testing.assert_close(dw.cpu().float(), dwr, rtol=5e-2, atol=3e-2)
+    torch.testing.assert_close(db.cpu().float(), dbr, rtol=5e-2, atol=3e-2)
+
+
+def test_adamw_and_clip_kernels(dev):
+    from opentau_b200.ops import cuda_ops
+    from opentau_b200.ops import reference as ref
+    n = 100_003
+    p = torch.randn(n, device=dev)
+    g = torch.randn(n, device=dev).to(torch.bfloat16)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    p16 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    pr, mr, vr = p.clone().cpu(), m.clone().cpu(), v.clone().cpu()
+    scale = torch.tensor([0.5, 0.0], device=dev)
+    for step in (1, 2, 3):
+        cuda_ops.adamw(p, g, m, v, p16, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01, step=step, scale=scale)
+        ref.adamw_flat(pr, g.cpu(), mr, vr, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01,
+                       step=step, grad_scale=0.5)
+    torch.testing.assert_close(p.cpu(), pr, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(p16.cpu().float(), pr, rtol=1e-2, atol=1e-2)
+    partial = torch.zeros(1024, device=dev)
+    cuda_ops.sumsq_partials(g, partial)
+    torch.testing.assert_close(partial.sum().cpu(), g.float().pow(2).sum().cpu(), rtol=1e-4, atol=1e-2)
+    out = torch.zeros(2, device=dev)
+    cuda_ops.clip_coef(partial, 0.25, 1.0, out)
+    norm = g.float().pow(2).sum().sqrt().item() * 0.25
+    assert abs(out[1].item() - norm) / norm < 1e-4
+    assert abs(out[0].item() - 0.25 * min(1.0, 1.0 / (norm + 1e-6))) < 1e-6
+
+
+def test_resize_pad_kernel(dev):
+    from opentau_b200 import ops
+    from opentau_b200.ops import cuda_ops
+    img = torch.rand(2, 3, 120, 200, device=dev)
+    out = cuda_ops.resize_with_pad(img, 224, 224, 0.0)
+    ref = ops.ref.resize_with_pad(img.cpu(), 224, 224, 0.0)
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_native_libraries_are_loaded(dev):
+    from opentau_b200.ops import _lib, cuda_ops
+    a = torch.randn(128, 64, device=dev).to(torch.bfloat16)
+    cuda_ops.gemm(a, a, "nt")
+    with open("/proc/self/maps") as f:
+        maps = f.read()
+    assert "libotb_gemm_tcgen05.so" in maps
+    assert any("gemm_tcgen05" in p for p in _lib.loaded_libraries())
