@@ -3,18 +3,58 @@
 from __future__ import annotations
 
 import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
+import torch
 from torch import Tensor
 
+from . import _lib
 
-def available() -> bool:
-    from . import build
-    return build.lib_path("attention_tcgen05").exists() and os.environ.get("OPENTAU_B200_DENSE_ATTN", "0") != "1"
+
+def _enabled() -> bool:
+    return os.environ.get("OPENTAU_B200_DENSE_ATTN", "0") != "1"
 
 
 def supported(q: Tensor, k: Tensor, v: Tensor) -> bool:
-    return False
+    if not _enabled() or q.dtype != torch.bfloat16:
+        return False
+    B, Sq, H, D = q.shape
+    Hkv = k.shape[2]
+    g = H // Hkv
+    return D % 8 == 0 and 16 <= D <= 256 and H % Hkv == 0 and g <= 128 and 128 % g == 0
 
 
 def supported_bwd(q: Tensor, k: Tensor, v: Tensor) -> bool:
     return False
+
+
+def _prep(t: Tensor) -> Tensor:
+    if t.stride(3) != 1 or any(s % 8 for s in t.stride()[:3]) or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor, q_valid: Tensor, k_valid: Tensor,
+             scale: float):
+    from . import cuda_ops
+    B, Sq, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    q, k, v = _prep(q), _prep(k), _prep(v)
+    o = torch.empty(B, Sq, H * D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device)
+    qb = q_blk.to(torch.int32).contiguous()
+    kb = k_blk.to(torch.int32).contiguous()
+    qv = q_valid.to(torch.uint8).contiguous()
+    kv = k_valid.to(torch.uint8).contiguous()
+    rc = _lib.load("attention_tcgen05").otb_attn_fwd(
+        c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
+        c_void_p(lse.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()), c_void_p(qv.data_ptr()),
+        c_void_p(kv.data_ptr()), c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hkv), c_int(D),
+        c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
+        c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
+        c_longlong(v.stride(0)), c_longlong(v.stride(1)), c_longlong(v.stride(2)),
+        c_float(scale), c_void_p(cuda_ops.status_pointer()), cuda_ops._stream())
+    if rc != 0:
+        raise RuntimeError(f"native attn_fwd failed with code {rc} (B={B} Sq={Sq} Sk={Sk} H={H} Hkv={Hkv} D={D})")
+    cuda_ops.launch_count += 1
+    return o, lse

@@ -1,0 +1,445 @@
+// Block-causal flash attention forward for sm_100a: TMA-fed, S = Q K^T and O += P V on tcgen05 with
+// both accumulators in tensor memory, online softmax by 128 threads that each own one TMEM lane.
+//
+// Mask rule (same as the dense reference): query i sees key j iff q_valid[i] && k_valid[j] &&
+// k_blk[j] <= q_blk[i].  Cached cross-attention keys carry k_blk = INT_MIN.  Rows that see no key
+// produce O = 0 and LSE = 0.
+//
+// Work decomposition: one CTA per (batch, kv head, tile of 128 "rows"), where a row is a
+// (query position, query head of the GQA group) pair: 128 rows = (128/g) positions x g heads, so one
+// K/V tile load serves every head of the group (MQA: g = 8 -> K/V traffic / 8).
+//
+// Warps: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..5 = softmax / correction / epilogue.
+// Per KV block j:  MMA issues S[j+1] = Q K_{j+1}^T early, softmax turns S[j] into bf16 P in shared
+// memory (128B-swizzled, K-major), MMA issues O += P V_j.  O is rescaled lazily: only when the running
+// row maximum grew by more than 2^8 since the maximum in use, so the common case touches O never.
+#include "common.cuh"
+#include <limits.h>
+
+namespace otb {
+
+constexpr unsigned KID_ATTN = 2;
+constexpr int ATT_M = 128;
+
+struct AttnParams {
+  int B, Sq, Sk, H, Hkv, D, Dmma, g;
+  float scale_log2;                 // scale * log2(e)
+  const int* q_blk;                 // (B, Sq)
+  const int* k_blk;                 // (B, Sk)
+  const unsigned char* q_valid;     // (B, Sq)
+  const unsigned char* k_valid;     // (B, Sk)
+  __nv_bfloat16* o;                 // (B, Sq, H, D) contiguous
+  float* lse;                       // (B, H, Sq)
+  KernelStatus* status;
+};
+
+template <int DPAD, int BN>
+struct AttnSmem {
+  static constexpr int NCHUNK = DPAD / 64;
+  static constexpr int Q_BYTES = ATT_M * DPAD * 2;
+  static constexpr int KV_TILE = BN * DPAD * 2;        // one K or V tile
+  static constexpr int STAGE_BYTES = 2 * KV_TILE;      // K and V of one block
+  static constexpr int P_BYTES = ATT_M * BN * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_KV = Q_BYTES;
+  static constexpr int OFF_P = OFF_KV + 2 * STAGE_BYTES;
+  static constexpr int OFF_META = OFF_P + 2 * P_BYTES;  // int kmeta[2][BN]
+  static constexpr int OFF_BAR = OFF_META + 2 * BN * 4;
+  static constexpr int NBAR = 16;
+  static constexpr int TOTAL = OFF_BAR + NBAR * 8 + 32 + 1024;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int DPAD, int BN>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                const __grid_constant__ CUtensorMap tma_v, AttnParams p) {
+  using L = AttnSmem<DPAD, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sKV = smem + L::OFF_KV;
+  uint8_t* sP = smem + L::OFF_P;
+  int* kmeta = reinterpret_cast<int*>(smem + L::OFF_META);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;     // [2]
+  uint64_t* s_free = bars + 7;     // [2]
+  uint64_t* p_full = bars + 9;     // [2]
+  uint64_t* p_free = bars + 11;    // [2]
+  uint64_t* o_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* kv_end_smem = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int g = p.g;
+  const int pos_per_tile = ATT_M / g;
+  const int p0 = tile * pos_per_tile;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&p_free[i], 1);
+    }
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    *kv_end_smem = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_q);
+    tma_prefetch_desc(&tma_k);
+    tma_prefetch_desc(&tma_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;            // two buffers of BN columns
+  const uint32_t tmem_O = tmem_base + 2 * BN;   // Dmma columns
+
+  // ---- how many keys can this tile reach?  1 + the last key index j that is valid and has
+  //      k_blk[j] <= the largest valid q_blk in the tile (no monotonicity assumed).
+  {
+    int qmax = INT_MIN;
+    bool any_q = false;
+    for (int i = threadIdx.x; i < pos_per_tile; i += blockDim.x) {
+      int pos = p0 + i;
+      if (pos < p.Sq && p.q_valid[(long long)b * p.Sq + pos]) {
+        qmax = max(qmax, p.q_blk[(long long)b * p.Sq + pos]);
+        any_q = true;
+      }
+    }
+    // block-wide max of qmax (values) through shared atomics on a small scratch word
+    __shared__ int s_qmax, s_any;
+    if (threadIdx.x == 0) {
+      s_qmax = INT_MIN;
+      s_any = 0;
+    }
+    __syncthreads();
+    if (any_q) {
+      atomicMax(&s_qmax, qmax);
+      atomicOr(&s_any, 1);
+    }
+    __syncthreads();
+    int last = -1;
+    if (s_any) {
+      const int qm = s_qmax;
+      for (int j = threadIdx.x; j < p.Sk; j += blockDim.x) {
+        if (p.k_valid[(long long)b * p.Sk + j] && p.k_blk[(long long)b * p.Sk + j] <= qm) last = max(last, j);
+      }
+    }
+    if (last >= 0) atomicMax(kv_end_smem, last + 1);
+    __syncthreads();
+  }
+  const int kv_end = *kv_end_smem;
+  const int nblk = max(1, (kv_end + BN - 1) / BN);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < L::NCHUNK; ++c)
+        tma_load_4d(sQ + c * (ATT_M * 128), &tma_q, q_full, c * 64, kvh * g, p0, b);
+      for (int j = 0; j < nblk; ++j) {
+        const int slot = j & 1, u = j >> 1;
+        mbar_wait(&kv_empty[slot], (u & 1) ^ 1, abort_flag, p.status, KID_ATTN, 1, j);
+        uint8_t* sk = sKV + slot * L::STAGE_BYTES;
+        uint8_t* sv = sk + L::KV_TILE;
+        mbar_expect_tx(&kv_full[slot], L::STAGE_BYTES);
+#pragma unroll
+        for (int c = 0; c < L::NCHUNK; ++c) {
+          tma_load_4d(sk + c * (BN * 128), &tma_k, &kv_full[slot], c * 64, kvh, j * BN, b);
+          tma_load_4d(sv + c * (BN * 128), &tma_v, &kv_full[slot], c * 64, kvh, j * BN, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_qk = make_idesc_bf16(ATT_M, BN, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(ATT_M, p.Dmma, 0, 1);
+      const int ksteps_qk = p.Dmma / 16;
+      const uint32_t q_addr = smem_u32(sQ);
+      auto issue_qk = [&](int j) {
+        const int slot = j & 1, u = j >> 1;
+        mbar_wait(&kv_full[slot], u & 1, abort_flag, p.status, KID_ATTN, 2, j);
+        mbar_wait(&s_free[slot], (u & 1) ^ 1, abort_flag, p.status, KID_ATTN, 3, j);
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sKV + slot * L::STAGE_BYTES);
+        for (int kk = 0; kk < ksteps_qk; ++kk) {
+          const int c = kk >> 2, w = kk & 3;
+          uint64_t ad = make_smem_desc(q_addr + c * (ATT_M * 128) + w * 32, 16, 1024);
+          uint64_t bd = make_smem_desc(k_addr + c * (BN * 128) + w * 32, 16, 1024);
+          umma_ss(tmem_S + slot * BN, ad, bd, idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[slot]);
+      };
+      mbar_wait(q_full, 0, abort_flag, p.status, KID_ATTN, 4, 0);
+      issue_qk(0);
+      for (int j = 0; j < nblk; ++j) {
+        const int slot = j & 1, u = j >> 1;
+        if (j + 1 < nblk) issue_qk(j + 1);
+        mbar_wait(&p_full[slot], u & 1, abort_flag, p.status, KID_ATTN, 5, j);
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP + slot * L::P_BYTES);
+        const uint32_t v_addr = smem_u32(sKV + slot * L::STAGE_BYTES + L::KV_TILE);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          uint64_t ad = make_smem_desc(p_addr + (kk >> 2) * (ATT_M * 128) + (kk & 3) * 32, 16, 1024);
+          uint64_t bd = make_smem_desc(v_addr + kk * 2048, BN * 128, 1024);
+          umma_ss(tmem_O, ad, bd, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[slot]);
+        umma_commit(&p_free[slot]);
+      }
+      umma_commit(o_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;            // TMEM lane owned by this thread
+    const int st = threadIdx.x - 64;             // 0..127 index among softmax threads
+    const int pos = p0 + row / g;
+    const int head = kvh * g + row % g;
+    const bool row_in = pos < p.Sq;
+    const bool q_ok = row_in && p.q_valid[(long long)b * p.Sq + pos] != 0;
+    const int qb = q_ok ? p.q_blk[(long long)b * p.Sq + pos] : 0;
+    const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    float m_used = -INFINITY;   // maximum the accumulators are currently expressed against
+    float l = 0.f;
+    const float scale = p.scale_log2;
+
+    for (int j = 0; j < nblk; ++j) {
+      const int slot = j & 1, u = j >> 1;
+      // key metadata of this block: INT_MAX = invisible to everyone
+      if (st < BN) {
+        const int key = j * BN + st;
+        int kb = INT_MAX;
+        if (key < p.Sk && p.k_valid[(long long)b * p.Sk + key]) kb = p.k_blk[(long long)b * p.Sk + key];
+        kmeta[slot * BN + st] = kb;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int* km = kmeta + slot * BN;
+      mbar_wait(&s_full[slot], u & 1, abort_flag, p.status, KID_ATTN, 6, j);
+      tc_fence_after();
+      const uint32_t s_addr = tmem_S + slot * BN + lane_off;
+      // pass A: row maximum of the masked, scaled scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_x32(s_addr + c * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const bool vis = q_ok && km[c * 32 + e] <= qb;
+          const float s = vis ? __uint_as_float(r[e]) * scale : -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_used, mx);
+      // lazy rescale decision (warp-uniform because tcgen05.ld/st are warp-collective)
+      const bool want = (m_new > m_used + 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
+      const bool any_want = __any_sync(0xffffffffu, want);
+      float alpha = 1.f;
+      if (want) {
+        alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+        m_used = m_new;
+      }
+      // P buffer `slot` was last read by PV(j-2)
+      if (j >= 2) mbar_wait(&p_free[slot], ((u - 1) & 1), abort_flag, p.status, KID_ATTN, 7, j);
+      if (any_want && j > 0) {
+        // O may only be touched once PV(j-1) has retired
+        const int ps = (j - 1) & 1, pu = (j - 1) >> 1;
+        mbar_wait(&p_free[ps], pu & 1, abort_flag, p.status, KID_ATTN, 8, j);
+        tc_fence_after();
+        const uint32_t o_addr = tmem_O + lane_off;
+#pragma unroll 1
+        for (int c = 0; c < p.Dmma / 16; ++c) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_x16(o_addr + c * 16, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+          tmem_st_x16(o_addr + c * 16, r);
+        }
+        tmem_wait_st();
+      }
+      l *= alpha;
+      // pass B: probabilities -> bf16 -> swizzled shared memory (A operand of the PV product)
+      uint8_t* prow = sP + slot * L::P_BYTES + row * 128;
+      float lsum = 0.f;
+      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_x32(s_addr + c * 32, r);
+        tmem_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const bool v0 = q_ok && km[c * 32 + e] <= qb;
+          const bool v1 = q_ok && km[c * 32 + e + 1] <= qb;
+          float p0f = v0 ? fast_exp2(__uint_as_float(r[e]) * scale - m_safe) : 0.f;
+          float p1f = v1 ? fast_exp2(__uint_as_float(r[e + 1]) * scale - m_safe) : 0.f;
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0f, p1f);
+          // the row sum uses the rounded values so that O / l is a true weighted mean of V rows
+          float2 back = __bfloat1622float2(pb);
+          lsum += back.x + back.y;
+          packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+        }
+        // 32 keys = 64 bytes = four 16-byte units; unit index within the 128-byte row is XOR-swizzled
+        const int chunk = (c * 32) / 64;           // 64-key chunk (16 KB apart)
+        const int unit0 = ((c * 32) % 64) / 8;     // first 16-byte unit inside the row
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int unit = (unit0 + q4) ^ (row & 7);
+          uint4 val = make_uint4(packed[q4 * 4 + 0], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          *reinterpret_cast<uint4*>(prow + chunk * (ATT_M * 128) + unit * 16) = val;
+        }
+      }
+      l += lsum;
+      // S buffer is free for QK(j+2); P is visible to the tensor core (async proxy)
+      tc_fence_before();
+      mbar_arrive(&s_free[slot]);
+      fence_async_smem();
+      mbar_arrive(&p_full[slot]);
+    }
+
+    // ---- epilogue: O / l -> bf16 -> global, LSE
+    mbar_wait(o_full, 0, abort_flag, p.status, KID_ATTN, 9, 0);
+    tc_fence_after();
+    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    const uint32_t o_addr = tmem_O + lane_off;
+    __nv_bfloat16* orow = p.o + (((long long)b * p.Sq + pos) * p.H + head) * p.D;
+#pragma unroll 1
+    for (int c = 0; c < p.Dmma / 16; ++c) {
+      uint32_t r[16];
+      __syncwarp();
+      tmem_ld_x16(o_addr + c * 16, r);
+      tmem_wait_ld();
+      if (row_in) {
+#pragma unroll
+        for (int h8 = 0; h8 < 2; ++h8) {
+          const int col = c * 16 + h8 * 8;
+          if (col < p.D) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[h8 * 8 + 0]) * inv_l, __uint_as_float(r[h8 * 8 + 1]) * inv_l);
+            o.y = pack_bf16(__uint_as_float(r[h8 * 8 + 2]) * inv_l, __uint_as_float(r[h8 * 8 + 3]) * inv_l);
+            o.z = pack_bf16(__uint_as_float(r[h8 * 8 + 4]) * inv_l, __uint_as_float(r[h8 * 8 + 5]) * inv_l);
+            o.w = pack_bf16(__uint_as_float(r[h8 * 8 + 6]) * inv_l, __uint_as_float(r[h8 * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + col) = o;
+          }
+        }
+      }
+    }
+    if (row_in) {
+      const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : 0.f;
+      p.lse[((long long)b * p.H + head) * p.Sq + pos] = lse;
+    }
+    tc_fence_before();
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// rank-4 bf16 map over a (B, S, Hx, D) tensor with element strides (sb, ss, sh, 1); dims innermost first
+static int make_map4(CUtensorMap* m, const void* base, int D, int Hx, int S, int B, long long sh, long long ss,
+                     long long sb, int box_h, int box_s) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hx, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)sh * 2, (uint64_t)ss * 2, (uint64_t)sb * 2};
+  uint32_t box[4] = {64, (uint32_t)box_h, (uint32_t)box_s, 1};
+  return make_tmap_bf16(m, base, 4, dims, strides, box);
+}
+
+template <int DPAD, int BN>
+static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                       cudaStream_t stream) {
+  using L = AttnSmem<DPAD, BN>;
+  static bool configured = false;
+  auto kern = attn_fwd_kernel<DPAD, BN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int pos_per_tile = ATT_M / p.g;
+  dim3 grid((p.Sq + pos_per_tile - 1) / pos_per_tile, p.Hkv, p.B);
+  kern<<<grid, 192, L::TOTAL, stream>>>(tq, tk, tv, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace otb
+
+using namespace otb;
+
+// q: (B,Sq,H,D) strides (q_sb,q_ss,q_sh,1); k,v: (B,Sk,Hkv,D); o: (B,Sq,H,D) contiguous; lse: (B,H,Sq).
+extern "C" int otb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* q_blk,
+                            const int* k_blk, const unsigned char* q_valid, const unsigned char* k_valid, int B,
+                            int Sq, int Sk, int H, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh,
+                            long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
+                            long long v_sh, float scale, void* status, cudaStream_t stream) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return -2;
+  const int g = H / Hkv;
+  if (g > 128 || (128 % g)) return -3;
+  if (D % 8 || D > 256 || D < 16) return -4;
+  const long long strides[9] = {q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh};
+  for (int i = 0; i < 9; ++i)
+    if (strides[i] % 8) return -5;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return -6;
+  AttnParams p;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv; p.D = D; p.g = g;
+  p.Dmma = (D + 15) / 16 * 16;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.q_blk = q_blk; p.k_blk = k_blk; p.q_valid = q_valid; p.k_valid = k_valid;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.status = static_cast<KernelStatus*>(status);
+  const int dpad = D <= 64 ? 64 : (D <= 128 ? 128 : 256);
+  const int bn = dpad == 256 ? 64 : 128;
+  CUtensorMap tq, tk, tv;
+  int r = make_map4(&tq, q, D, H, Sq, B, q_sh, q_ss, q_sb, g, ATT_M / g);
+  if (r) return 1000 + r;
+  r = make_map4(&tk, k, D, Hkv, Sk, B, k_sh, k_ss, k_sb, 1, bn);
+  if (r) return 2000 + r;
+  r = make_map4(&tv, v, D, Hkv, Sk, B, v_sh, v_ss, v_sb, 1, bn);
+  if (r) return 3000 + r;
+  switch (dpad) {
+    case 64: return launch_attn<64, 128>(tq, tk, tv, p, stream);
+    case 128: return launch_attn<128, 128>(tq, tk, tv, p, stream);
+    default: return launch_attn<256, 64>(tq, tk, tv, p, stream);
+  }
+}

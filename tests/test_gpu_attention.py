@@ -1,0 +1,112 @@
+"""tcgen05 block-causal attention against the dense fp32 reference (run on a B200)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(B, Sq, H, Hkv, D, cross, dev, seed=0, pad=True, causal_from=None):
+    g = torch.Generator().manual_seed(seed)
+    Sk = Sq + cross
+    q = (torch.randn(B, Sq, H, D, generator=g)).to(torch.bfloat16).to(dev)
+    k = (torch.randn(B, Sk, Hkv, D, generator=g)).to(torch.bfloat16).to(dev)
+    v = (torch.randn(B, Sk, Hkv, D, generator=g)).to(torch.bfloat16).to(dev)
+    att = torch.zeros(B, Sq, dtype=torch.bool)
+    cf = Sq // 2 if causal_from is None else causal_from
+    att[:, cf:] = True
+    padm = torch.ones(B, Sq, dtype=torch.bool)
+    if pad:
+        padm[0, -3:] = False
+        if Sq > 20:
+            padm[-1, 5:9] = False
+    from opentau_b200 import ops
+    q_blk, q_valid = ops.make_block_ids(padm, att)
+    if cross:
+        k_blk = torch.cat([torch.full((B, cross), ops.INT_MIN, dtype=torch.int32), q_blk], 1)
+        cv = torch.ones(B, cross, dtype=torch.bool)
+        if pad:
+            cv[0, 1::7] = False
+        k_valid = torch.cat([cv, q_valid], 1)
+    else:
+        k_blk, k_valid = q_blk, q_valid
+    return q, k, v, q_blk.to(dev), k_blk.to(dev), q_valid.to(dev), k_valid.to(dev)
+
+
+@pytest.mark.parametrize("D", [64, 72, 128, 256])
+@pytest.mark.parametrize("H,Hkv", [(8, 1), (8, 4), (4, 4), (16, 8)])
+@pytest.mark.parametrize("Sq,cross", [(50, 0), (131, 0), (50, 203), (300, 0), (64, 64)])
+def test_attn_fwd_matches_dense(D, H, Hkv, Sq, cross):
+    from opentau_b200 import ops
+    from opentau_b200.ops import attention_native, cuda_ops
+    dev = torch.device("cuda:0")
+    B = 2
+    q, k, v, qb, kb, qv, kv = _case(B, Sq, H, Hkv, D, cross, dev, seed=D + Sq)
+    scale = D ** -0.5
+    assert attention_native.supported(q, k, v)
+    o, lse = attention_native.attn_fwd(q, k, v, qb, kb, qv, kv, scale)
+    cuda_ops.check_status()
+    o_ref, lse_ref = ops.prims.attn_fwd(q.cpu().float(), k.cpu().float(), v.cpu().float(), qb.cpu(), kb.cpu(),
+                                        qv.cpu(), kv.cpu(), scale)
+    valid = qv.cpu()
+    od = o.cpu().float().view(B, Sq, H, D)[valid]
+    ord_ = o_ref.view(B, Sq, H, D)[valid]
+    torch.testing.assert_close(od, ord_, rtol=3e-2, atol=3e-2)
+    lv = lse.cpu().permute(0, 2, 1)[valid]
+    lr = lse_ref.permute(0, 2, 1)[valid]
+    torch.testing.assert_close(lv, lr, rtol=1e-2, atol=2e-2)
+    assert torch.isfinite(o.float()).all()
+
+
+def test_attn_fwd_strided_qkv_views():
+    """q/k/v as column slices of one fused projection output (the layout the model produces)."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import attention_native, cuda_ops
+    dev = torch.device("cuda:0")
+    B, S, H, Hkv, D = 2, 200, 8, 1, 256
+    qkv = torch.randn(B, S, (H + 2 * Hkv) * D, device=dev).to(torch.bfloat16)
+    q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    q, k, v = q.unflatten(-1, (H, D)), k.unflatten(-1, (Hkv, D)), v.unflatten(-1, (Hkv, D))
+    blk = torch.zeros(B, S, dtype=torch.int32, device=dev)
+    ok = torch.ones(B, S, dtype=torch.bool, device=dev)
+    o, _ = attention_native.attn_fwd(q, k, v, blk, blk, ok, ok, D ** -0.5)
+    cuda_ops.check_status()
+    o_ref = ops.ref.block_attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), blk.cpu(), blk.cpu(),
+                                    ok.cpu(), ok.cpu(), D ** -0.5)
+    torch.testing.assert_close(o.cpu().float(), o_ref, rtol=3e-2, atol=3e-2)
+
+
+def test_attn_large_logits_trigger_rescale():
+    """Row maxima that grow late in the key sequence exercise the lazy O-rescale path."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import attention_native, cuda_ops
+    dev = torch.device("cuda:0")
+    B, S, H, D = 1, 512, 4, 64
+    q = torch.randn(B, S, H, D, device=dev).to(torch.bfloat16)
+    k = torch.randn(B, S, H, D, device=dev).to(torch.bfloat16)
+    k[:, 400:] *= 6.0
+    v = torch.randn(B, S, H, D, device=dev).to(torch.bfloat16)
+    blk = torch.zeros(B, S, dtype=torch.int32, device=dev)
+    ok = torch.ones(B, S, dtype=torch.bool, device=dev)
+    o, lse = attention_native.attn_fwd(q, k, v, blk, blk, ok, ok, 1.0)
+    cuda_ops.check_status()
+    o_ref, lse_ref = ops.prims.attn_fwd(q.cpu().float(), k.cpu().float(), v.cpu().float(), blk.cpu(), blk.cpu(),
+                                        ok.cpu(), ok.cpu(), 1.0)
+    torch.testing.assert_close(o.cpu().float(), o_ref, rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(lse.cpu(), lse_ref, rtol=1e-2, atol=5e-2)
+
+
+def test_attention_autograd_on_gpu_matches_cpu():
+    from opentau_b200 import ops
+    dev = torch.device("cuda:0")
+    B, Sq, H, Hkv, D = 2, 70, 8, 1, 64
+    q, k, v, qb, kb, qv, kv = _case(B, Sq, H, Hkv, D, 30, dev, seed=3)
+    qc, kc, vc = (t.cpu().float().requires_grad_() for t in (q, k, v))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    o = ops.block_attention(q, k, v, qb, kb, qv, kv, D ** -0.5)
+    oc = ops.block_attention(qc, kc, vc, qb.cpu(), kb.cpu(), qv.cpu(), kv.cpu(), D ** -0.5)
+    w = torch.randn_like(oc) * qv.cpu()[:, :, None]
+    (o.float() * w.to(dev)).sum().backward()
+    (oc * w).sum().backward()
+    for a, c in ((q.grad, qc.grad), (k.grad, kc.grad), (v.grad, vc.grad)):
+        torch.testing.assert_close(a.cpu().float(), c, rtol=5e-2, atol=5e-2)
