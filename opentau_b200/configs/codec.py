@@ -153,6 +153,10 @@ def decode(tp: Any, value: Any, path: str = "") -> Any:
         return int(value)
     if tp is Path:
         return Path(value)
+    if tp is tuple and isinstance(value, (list, tuple)):
+        return tuple(value)
+    if tp is list and isinstance(value, (list, tuple)):
+        return list(value)
     if tp is bool and isinstance(value, str):
         if value.lower() in ("true", "1", "yes"):
             return True

@@ -1,0 +1,103 @@
+"""Command-line front end: ``@parser.wrap()`` turns ``main(cfg: TrainPipelineConfig)`` into a CLI.
+
+``--config_path=<json | dir | repo@rev>`` selects the base file, every other ``--a.b.c=value`` is a dotted
+override.  Arguments injected by distributed launchers (``--local_rank`` …) are dropped, and
+``--accelerate-config <yaml>`` is accepted and mapped onto ``distributed.*`` for compatibility with the
+reference's launcher (OpenTau ``src/opentau/configs/parser.py:286-400``, ``scripts/launch.py:30-99``).
+"""
+
+from __future__ import annotations
+
+import functools
+import importlib
+import inspect
+import sys
+from typing import Any, Callable
+
+LAUNCHER_ARGS = ("--local_rank", "--local-rank", "--node_rank", "--nproc_per_node", "--master_addr", "--master_port")
+
+
+def filter_distributed_args(argv: list[str]) -> list[str]:
+    out, skip = [], False
+    for a in argv:
+        if skip:
+            skip = False
+            continue
+        key = a.split("=", 1)[0]
+        if key in LAUNCHER_ARGS:
+            skip = "=" not in a
+            continue
+        out.append(a)
+    return out
+
+
+def get_cli_value(argv: list[str], name: str) -> str | None:
+    for i, a in enumerate(argv):
+        if a.startswith(f"--{name}="):
+            return a.split("=", 1)[1]
+        if a == f"--{name}" and i + 1 < len(argv):
+            return argv[i + 1]
+    return None
+
+
+def strip_arg(argv: list[str], name: str) -> list[str]:
+    out, skip = [], False
+    for a in argv:
+        if skip:
+            skip = False
+            continue
+        if a.startswith(f"--{name}="):
+            continue
+        if a == f"--{name}":
+            skip = True
+            continue
+        out.append(a)
+    return out
+
+
+def load_plugin(path: str) -> None:
+    """Imports a user plugin package so that it can register policies / envs / optimizers."""
+    try:
+        importlib.import_module(path)
+    except ModuleNotFoundError as e:
+        raise ModuleNotFoundError(f"plugin {path!r} could not be imported: {e}") from e
+
+
+def parse_config(config_cls, argv: list[str] | None = None):
+    argv = filter_distributed_args(list(sys.argv[1:] if argv is None else argv))
+    plugin = get_cli_value(argv, "plugin")
+    if plugin:
+        load_plugin(plugin)
+        argv = strip_arg(argv, "plugin")
+    accel = get_cli_value(argv, "accelerate-config") or get_cli_value(argv, "accelerate_config")
+    argv = strip_arg(strip_arg(argv, "accelerate-config"), "accelerate_config")
+    config_path = get_cli_value(argv, "config_path")
+    argv = strip_arg(argv, "config_path")
+    if config_path is not None:
+        cfg = config_cls.from_pretrained(config_path, cli_overrides=argv)
+    else:
+        from .codec import apply_overrides
+        raw: dict[str, Any] = apply_overrides({}, [a for a in argv if not a.startswith("--policy.path=")])
+        cfg = config_cls.from_dict(raw)
+    if accel is not None and hasattr(cfg, "distributed"):
+        from .default import DistributedConfig
+        d = DistributedConfig.from_accelerate_yaml(accel)
+        d.comm, d.tp, d.cp = cfg.distributed.comm, cfg.distributed.tp, cfg.distributed.cp
+        cfg.distributed = d
+    return cfg
+
+
+def wrap(config_path: str | None = None) -> Callable:
+    """Decorator: the wrapped function's first parameter annotation names the config class."""
+
+    def deco(fn: Callable) -> Callable:
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            if args or kwargs:
+                return fn(*args, **kwargs)
+            hints = inspect.get_annotations(fn, eval_str=True)
+            first = next(iter(inspect.signature(fn).parameters))
+            cfg = parse_config(hints[first])
+            return fn(cfg)
+        return inner
+    return deco

@@ -1,0 +1,191 @@
+"""``TrainPipelineConfig``: the root configuration of ``opentau-train`` / ``opentau-eval``.
+
+Field names, defaults, the batch-size invariant, the pipeline->policy shape propagation and the
+``train_config.json`` persistence follow the reference (OpenTau ``src/opentau/configs/train.py:83-668``).
+The accelerate YAML surface is replaced by the ``distributed`` block.
+"""
+
+from __future__ import annotations
+
+import json
+import logging
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any
+
+from ..constants import TRAIN_CONFIG_NAME
+from ..optim.optimizers import OptimizerConfig
+from ..optim.schedulers import LRSchedulerConfig
+from .codec import apply_overrides, decode, encode
+from .default import DatasetMixtureConfig, DistributedConfig, EvalConfig, WandBConfig
+from .deployment import PlannerConfig, ServerConfig
+from .policies import PreTrainedConfig
+from .refs import load_json_with_refs
+
+# pipeline field -> policy field: the pipeline value overwrites the policy's
+PIPELINE_TO_POLICY_SHAPE_FIELDS = {
+    "max_state_dim": "max_state_dim",
+    "max_action_dim": "max_action_dim",
+    "action_chunk": "chunk_size",
+}
+
+
+@dataclass
+class TrainPipelineConfig:
+    dataset_mixture: DatasetMixtureConfig = field(default_factory=DatasetMixtureConfig)
+    policy: PreTrainedConfig | None = None
+    output_dir: str | None = None
+    resume: bool = False
+    seed: int | None = 1000
+    resolution: tuple[int, int] = (224, 224)
+    num_cams: int = 2
+    max_state_dim: int = 32
+    max_action_dim: int = 32
+    action_chunk: int = 50
+    loss_weighting: dict[str, float] = field(default_factory=lambda: {"MSE": 1.0, "CE": 1.0})
+    num_workers: int = 4
+    batch_size: int | None = None
+    gradient_accumulation_steps: int = 1
+    dataloader_batch_size: int | None = None
+    prefetch_factor: int | None = None
+    steps: int = 100_000
+    log_freq: int = 200
+    save_checkpoint: bool = True
+    save_freq: int = 20_000
+    use_policy_training_preset: bool = False
+    optimizer: OptimizerConfig | None = None
+    scheduler: LRSchedulerConfig | None = None
+    wandb: WandBConfig = field(default_factory=WandBConfig)
+    debug: bool = False
+    trace_nans: bool = False
+    env: Any | None = None
+    eval: EvalConfig = field(default_factory=EvalConfig)
+    eval_freq: int = 0
+    val_freq: int = 0
+    last_checkpoint_only: bool = True
+    running_best_count: int = 0
+    running_best_metric: str = "auto"
+    server: ServerConfig = field(default_factory=ServerConfig)
+    planner: PlannerConfig = field(default_factory=PlannerConfig)
+    distributed: DistributedConfig = field(default_factory=DistributedConfig)
+
+    _deprecated_fields = ("job_name",)
+
+    def __post_init__(self):
+        self.checkpoint_path: Path | None = None
+        self._resolve_batch_sizes()
+        self._propagate_shape_fields()
+
+    # -- invariants --------------------------------------------------------------------------------
+    def _resolve_batch_sizes(self) -> None:
+        ga = self.gradient_accumulation_steps
+        if ga < 1:
+            raise ValueError("gradient_accumulation_steps must be >= 1")
+        if self.batch_size is None and self.dataloader_batch_size is None:
+            self.dataloader_batch_size = 8
+        if self.batch_size is None:
+            self.batch_size = self.dataloader_batch_size * ga
+        elif self.dataloader_batch_size is None:
+            if self.batch_size % ga:
+                raise ValueError(f"batch_size ({self.batch_size}) must be divisible by "
+                                 f"gradient_accumulation_steps ({ga})")
+            self.dataloader_batch_size = self.batch_size // ga
+        if self.batch_size != self.dataloader_batch_size * ga:
+            raise ValueError(f"batch_size ({self.batch_size}) must equal dataloader_batch_size "
+                             f"({self.dataloader_batch_size}) * gradient_accumulation_steps ({ga})")
+
+    def _propagate_shape_fields(self) -> None:
+        if self.policy is None:
+            return
+        for src, dst in PIPELINE_TO_POLICY_SHAPE_FIELDS.items():
+            if hasattr(self.policy, dst):
+                setattr(self.policy, dst, getattr(self, src))
+        if hasattr(self.policy, "n_action_steps") and hasattr(self.policy, "chunk_size"):
+            if self.policy.n_action_steps > self.policy.chunk_size:
+                self.policy.n_action_steps = self.policy.chunk_size
+
+    def validate(self) -> None:
+        if self.policy is None:
+            raise ValueError("a policy configuration is required (`policy.type=...` or `--policy.path=...`)")
+        if not self.dataset_mixture.datasets and self.env is None:
+            raise ValueError("at least one dataset (or an env for pure evaluation) is required")
+        for k, w in self.loss_weighting.items():
+            if k not in ("MSE", "CE"):
+                raise ValueError(f"unknown loss term {k!r} in loss_weighting (expected MSE / CE)")
+            if w < 0:
+                raise ValueError("loss weights must be non-negative")
+        if all(float(self.loss_weighting.get(k, 1.0)) == 0.0 for k in ("MSE", "CE")):
+            raise ValueError("every loss term has zero weight")
+        if self.running_best_count < 0:
+            raise ValueError("running_best_count must be >= 0")
+        if self.running_best_count > 0 and self.val_freq <= 0 and self.eval_freq <= 0:
+            raise ValueError("running_best_count > 0 needs validation (val_freq) or evaluation (eval_freq)")
+        if self.use_policy_training_preset or self.optimizer is None:
+            self.optimizer = self.optimizer if (self.optimizer and not self.use_policy_training_preset) \
+                else self.policy.get_optimizer_preset()
+            if self.scheduler is None or self.use_policy_training_preset:
+                self.scheduler = self.policy.get_scheduler_preset()
+        if self.output_dir is None:
+            import datetime as dt
+            now = dt.datetime.now()
+            self.output_dir = str(Path("outputs/train") / f"{now:%Y-%m-%d}" / f"{now:%H-%M-%S}_{self.policy.type}")
+        if not self.resume and Path(self.output_dir).is_dir() and any(Path(self.output_dir).iterdir()):
+            ck = Path(self.output_dir) / "checkpoints"
+            if ck.is_dir() and any(ck.iterdir()):
+                raise FileExistsError(f"output directory {self.output_dir} already holds checkpoints and "
+                                      "`resume` is False")
+        self.policy.validate_action_horizon()
+
+    # -- persistence -------------------------------------------------------------------------------
+    def to_dict(self) -> dict[str, Any]:
+        return encode(self)
+
+    def _save_pretrained(self, save_directory: str | Path) -> None:
+        Path(save_directory).mkdir(parents=True, exist_ok=True)
+        with open(Path(save_directory) / TRAIN_CONFIG_NAME, "w") as f:
+            json.dump(self.to_dict(), f, indent=4)
+
+    save_pretrained = _save_pretrained
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "TrainPipelineConfig":
+        _import_policy_configs()
+        return decode(cls, raw)
+
+    @classmethod
+    def from_pretrained(cls, config_path: str | Path, cli_overrides: list[str] | None = None) -> "TrainPipelineConfig":
+        """Loads a JSON config (a file, a checkpoint directory holding ``train_config.json``, or a cached
+        ``repo@rev``); ``$ref`` includes are resolved, then dotted CLI overrides applied.  With
+        ``--resume=true`` the checkpoint's own ``train_config.json`` wins over the CLI for everything but
+        ``steps``/``resume`` (reference ``configs/train.py:352-366``)."""
+        from ..utils.hub import resolve_local_or_hub
+        p = Path(str(config_path))
+        if p.is_dir():
+            p = p / TRAIN_CONFIG_NAME
+        if not p.is_file():
+            p = resolve_local_or_hub(str(config_path), TRAIN_CONFIG_NAME)
+        raw = load_json_with_refs(p)
+        overrides = list(cli_overrides or [])
+        policy_path = None
+        kept = []
+        for a in overrides:
+            if a.startswith("--policy.path="):
+                policy_path = a.split("=", 1)[1]
+            else:
+                kept.append(a)
+        raw = apply_overrides(raw, kept)
+        if policy_path is not None:
+            pcfg = PreTrainedConfig.from_pretrained(policy_path)
+            merged = encode(pcfg)
+            merged.update({k: v for k, v in (raw.get("policy") or {}).items() if k != "type"})
+            merged["pretrained_path"] = policy_path
+            raw["policy"] = merged
+        cfg = cls.from_dict(raw)
+        if cfg.resume:
+            cfg.checkpoint_path = p.parent
+        return cfg
+
+
+def _import_policy_configs() -> None:
+    from ..policies.factory import _import_all_configs
+    _import_all_configs()

@@ -25,7 +25,10 @@ def supported(q: Tensor, k: Tensor, v: Tensor) -> bool:
 
 
 def supported_bwd(q: Tensor, k: Tensor, v: Tensor) -> bool:
-    return False
+    if not supported(q, k, v) or os.environ.get("OPENTAU_B200_DENSE_ATTN_BWD", "0") == "1":
+        return False
+    g = q.shape[2] // k.shape[2]
+    return g <= 32 and 32 % g == 0
 
 
 def _prep(t: Tensor) -> Tensor:
@@ -58,3 +61,36 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor, q_va
         raise RuntimeError(f"native attn_fwd failed with code {rc} (B={B} Sq={Sq} Sk={Sk} H={H} Hkv={Hkv} D={D})")
     cuda_ops.launch_count += 1
     return o, lse
+
+
+def attn_bwd(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, q_blk: Tensor, k_blk: Tensor,
+             q_valid: Tensor, k_valid: Tensor, scale: float):
+    """Returns ``(dq, dk, dv)``; ``delta`` scratch and outputs are allocated here."""
+    from . import cuda_ops
+    B, Sq, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    q, k, v = _prep(q), _prep(k), _prep(v)
+    o = o.contiguous()
+    do = do.contiguous()
+    lse = lse.contiguous()
+    dq = torch.empty(B, Sq, H, D, dtype=q.dtype, device=q.device)
+    dk = torch.empty(B, Sk, Hkv, D, dtype=q.dtype, device=q.device)
+    dv = torch.empty(B, Sk, Hkv, D, dtype=q.dtype, device=q.device)
+    delta = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device)
+    qb = q_blk.to(torch.int32).contiguous()
+    kb = k_blk.to(torch.int32).contiguous()
+    qv = q_valid.to(torch.uint8).contiguous()
+    kv = k_valid.to(torch.uint8).contiguous()
+    rc = _lib.load("attention_bwd_tcgen05").otb_attn_bwd(
+        c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
+        c_void_p(do.data_ptr()), c_void_p(lse.data_ptr()), c_void_p(delta.data_ptr()), c_void_p(dq.data_ptr()),
+        c_void_p(dk.data_ptr()), c_void_p(dv.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()),
+        c_void_p(qv.data_ptr()), c_void_p(kv.data_ptr()), c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hkv),
+        c_int(D), c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
+        c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
+        c_longlong(v.stride(0)), c_longlong(v.stride(1)), c_longlong(v.stride(2)),
+        c_float(scale), c_void_p(cuda_ops.status_pointer()), cuda_ops._stream())
+    if rc != 0:
+        raise RuntimeError(f"native attn_bwd failed with code {rc} (B={B} Sq={Sq} Sk={Sk} H={H} Hkv={Hkv} D={D})")
+    cuda_ops.launch_count += 4
+    return dq, dk, dv

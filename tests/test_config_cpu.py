@@ -1,0 +1,140 @@
+"""Config codec, registries, refs, CLI overrides, pipeline invariants."""
+
+import json
+
+import pytest
+
+from opentau_b200.configs import codec
+from opentau_b200.configs.default import DatasetConfig, DatasetMixtureConfig, DistributedConfig
+from opentau_b200.configs.parser import filter_distributed_args, parse_config
+from opentau_b200.configs.policies import PreTrainedConfig
+from opentau_b200.configs.refs import load_json_with_refs
+from opentau_b200.configs.train import TrainPipelineConfig
+from opentau_b200.configs.types import FeatureType, NormalizationMode
+from opentau_b200.optim.optimizers import AdamWConfig, OptimizerConfig
+from opentau_b200.optim.schedulers import CosineDecayWithWarmupSchedulerConfig, LRSchedulerConfig
+
+
+def _base_cfg():
+    return {
+        "dataset_mixture": {"datasets": [{"synthetic": {"name": "s"}}], "weights": [1.0]},
+        "policy": {"type": "pi05", "chunk_size": 10, "n_action_steps": 10, "num_steps": 5,
+                   "input_features": {"camera0": {"type": "VISUAL", "shape": [3, 224, 224]},
+                                      "state": {"type": "STATE", "shape": [32]}},
+                   "output_features": {"actions": {"type": "ACTION", "shape": [32]}}},
+        "batch_size": 8, "gradient_accumulation_steps": 2, "steps": 10, "action_chunk": 10,
+        "optimizer": {"type": "adamw", "lr": 1e-4, "betas": [0.9, 0.95]},
+        "scheduler": {"type": "cosine_decay_with_warmup", "num_warmup_steps": 2, "num_decay_steps": 10,
+                      "peak_lr": 1e-4, "decay_lr": 1e-5},
+    }
+
+
+def test_roundtrip_and_registry():
+    cfg = TrainPipelineConfig.from_dict(_base_cfg())
+    assert cfg.policy.type == "pi05" and cfg.policy.num_steps == 5
+    assert isinstance(cfg.optimizer, AdamWConfig) and cfg.optimizer.betas == (0.9, 0.95)
+    assert isinstance(cfg.scheduler, CosineDecayWithWarmupSchedulerConfig)
+    assert cfg.policy.input_features["camera0"].type is FeatureType.VISUAL
+    assert cfg.policy.input_features["camera0"].shape == (3, 224, 224)
+    assert cfg.policy.normalization_mapping["STATE"] is NormalizationMode.MIN_MAX
+    d = cfg.to_dict()
+    assert d["policy"]["type"] == "pi05" and d["optimizer"]["type"] == "adamw"
+    cfg2 = TrainPipelineConfig.from_dict(json.loads(json.dumps(d)))
+    assert cfg2.to_dict() == d
+
+
+def test_batch_invariant_and_shape_propagation():
+    cfg = TrainPipelineConfig.from_dict(_base_cfg())
+    assert cfg.dataloader_batch_size == 4
+    assert cfg.policy.chunk_size == 10 and cfg.policy.max_action_dim == 32
+    bad = _base_cfg()
+    bad["dataloader_batch_size"] = 3
+    with pytest.raises(ValueError):
+        TrainPipelineConfig.from_dict(bad)
+    raw = _base_cfg()
+    raw["action_chunk"] = 6
+    cfg = TrainPipelineConfig.from_dict(raw)
+    assert cfg.policy.chunk_size == 6 and cfg.policy.n_action_steps == 6
+
+
+def test_unknown_field_and_unknown_type_raise():
+    raw = _base_cfg()
+    raw["policy"]["not_a_field"] = 1
+    with pytest.raises(KeyError):
+        TrainPipelineConfig.from_dict(raw)
+    raw = _base_cfg()
+    raw["policy"]["type"] = "nope"
+    with pytest.raises(KeyError):
+        TrainPipelineConfig.from_dict(raw)
+    assert "adamw" in OptimizerConfig.get_known_choices()
+    assert "constant" in LRSchedulerConfig.get_known_choices()
+
+
+def test_cli_overrides_and_launcher_arg_filter(tmp_path):
+    f = tmp_path / "cfg.json"
+    f.write_text(json.dumps(_base_cfg()))
+    cfg = parse_config(TrainPipelineConfig, [f"--config_path={f}", "--policy.num_steps=3", "--steps=77",
+                                              "--local_rank=0", "--dataset_mixture.weights.0=2.5",
+                                              "--loss_weighting.CE=0.25"])
+    assert cfg.policy.num_steps == 3 and cfg.steps == 77
+    assert cfg.dataset_mixture.weights == [2.5]
+    assert cfg.loss_weighting["CE"] == 0.25
+    assert filter_distributed_args(["--local_rank", "3", "--a=1", "--master_port=99"]) == ["--a=1"]
+
+
+def test_refs_merge_and_cycle(tmp_path):
+    (tmp_path / "frag.json").write_text(json.dumps({"synthetic": {"name": "x"}, "robot_type": "so101"}))
+    raw = _base_cfg()
+    raw["dataset_mixture"]["datasets"] = [{"$ref": "frag.json", "robot_type": "override"}]
+    (tmp_path / "cfg.json").write_text(json.dumps(raw))
+    loaded = load_json_with_refs(tmp_path / "cfg.json")
+    assert loaded["dataset_mixture"]["datasets"][0] == {"synthetic": {"name": "x"}, "robot_type": "override"}
+    (tmp_path / "a.json").write_text(json.dumps({"$ref": "b.json"}))
+    (tmp_path / "b.json").write_text(json.dumps({"$ref": "a.json"}))
+    with pytest.raises(ValueError):
+        load_json_with_refs(tmp_path / "a.json")
+
+
+def test_dataset_config_validation():
+    with pytest.raises(ValueError):
+        DatasetConfig()
+    with pytest.raises(ValueError):
+        DatasetConfig(repo_id="a", vqa="b")
+    with pytest.raises(ValueError):
+        DatasetConfig(vqa="clevr", prompt_substitutions={"a": ["b"]})
+    with pytest.raises(ValueError):
+        DatasetConfig(repo_id="a", use_delta_joint_actions=True)
+    with pytest.raises(ValueError):
+        DatasetMixtureConfig(datasets=[DatasetConfig(repo_id="a")], weights=[1.0, 2.0])
+
+
+def test_accelerate_yaml_mapping(tmp_path):
+    y = tmp_path / "ds.yaml"
+    y.write_text("distributed_type: DEEPSPEED\ndeepspeed_config:\n  zero_stage: 3\n  gradient_clipping: 10\n")
+    d = DistributedConfig.from_accelerate_yaml(str(y))
+    assert d.strategy == "zero3" and d.gradient_clipping == 10.0
+    y.write_text("distributed_type: FSDP\n")
+    assert DistributedConfig.from_accelerate_yaml(str(y)).strategy == "fsdp"
+    y.write_text("distributed_type: MULTI_GPU\n")
+    assert DistributedConfig.from_accelerate_yaml(str(y)).strategy == "ddp"
+
+
+def test_policy_config_save_load_and_version_semantics(tmp_path):
+    cfg = TrainPipelineConfig.from_dict(_base_cfg()).policy
+    assert cfg.normalization_epsilon == 1e-8 and not cfg.zero_range_centers_on_zero   # no version = legacy
+    cfg._save_pretrained(tmp_path)
+    saved = json.loads((tmp_path / "config.json").read_text())
+    assert saved["config_version"] == 1 and saved["type"] == "pi05"
+    loaded = PreTrainedConfig.from_pretrained(tmp_path)
+    assert loaded.normalization_epsilon == 1e-6 and loaded.zero_range_centers_on_zero
+    assert loaded.num_steps == 5
+
+
+def test_scheduler_formula():
+    s = CosineDecayWithWarmupSchedulerConfig(num_warmup_steps=4, num_decay_steps=20, peak_lr=1.0, decay_lr=0.1)
+    f = s.lr_lambda(100)
+    assert f(0) == pytest.approx(1 / 5)
+    assert f(2) == pytest.approx((1 / 5 - 1) * 0.5 + 1)
+    assert f(20) == pytest.approx(0.1) and f(200) == pytest.approx(0.1)
+    import math
+    assert f(10) == pytest.approx(0.9 * 0.5 * (1 + math.cos(math.pi * 0.5)) + 0.1)

@@ -110,3 +110,31 @@ def test_attention_autograd_on_gpu_matches_cpu():
     (oc * w).sum().backward()
     for a, c in ((q.grad, qc.grad), (k.grad, kc.grad), (v.grad, vc.grad)):
         torch.testing.assert_close(a.cpu().float(), c, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("D", [64, 72, 128, 256])
+@pytest.mark.parametrize("H,Hkv", [(8, 1), (8, 4), (4, 4)])
+@pytest.mark.parametrize("Sq,cross", [(50, 0), (131, 0), (50, 203), (300, 0)])
+def test_attn_bwd_matches_dense(D, H, Hkv, Sq, cross):
+    from opentau_b200 import ops
+    from opentau_b200.ops import attention_native, cuda_ops
+    dev = torch.device("cuda:0")
+    B = 2
+    q, k, v, qb, kb, qv, kv = _case(B, Sq, H, Hkv, D, cross, dev, seed=7 * D + Sq)
+    scale = D ** -0.5
+    assert attention_native.supported_bwd(q, k, v)
+    o, lse = attention_native.attn_fwd(q, k, v, qb, kb, qv, kv, scale)
+    g = torch.Generator().manual_seed(5)
+    do = (torch.randn(B, Sq, H * D, generator=g) * qv.cpu()[:, :, None]).to(torch.bfloat16).to(dev)
+    dq, dk, dv = attention_native.attn_bwd(do, q, k, v, o, lse, qb, kb, qv, kv, scale)
+    cuda_ops.check_status()
+    qc, kc, vc = q.cpu().float(), k.cpu().float(), v.cpu().float()
+    o_ref, lse_ref = ops.prims.attn_fwd(qc, kc, vc, qb.cpu(), kb.cpu(), qv.cpu(), kv.cpu(), scale)
+    dqr, dkr, dvr = ops.prims.attn_bwd(do.cpu().float(), qc, kc, vc, o_ref, lse_ref, qb.cpu(), kb.cpu(), qv.cpu(),
+                                        kv.cpu(), scale)
+    valid_q = qv.cpu()
+    torch.testing.assert_close(dq.cpu().float()[valid_q], dqr[valid_q], rtol=5e-2, atol=5e-2)
+    valid_k = kv.cpu()
+    torch.testing.assert_close(dk.cpu().float()[valid_k], dkr[valid_k], rtol=5e-2, atol=8e-2)
+    torch.testing.assert_close(dv.cpu().float()[valid_k], dvr[valid_k], rtol=5e-2, atol=8e-2)
+    assert torch.isfinite(dq.float()).all() and torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
