@@ -89,6 +89,9 @@ def decode(tp: Any, value: Any, path: str = "") -> Any:
         args = get_args(tp)
         if value is None and type(None) in args:
             return None
+        members = [a for a in args if a is not type(None)]
+        if len(members) == 1:
+            return decode(members[0], value, path)
         last: Exception | None = None
         for a in args:
             if a is type(None):
