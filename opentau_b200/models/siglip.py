@@ -109,7 +109,9 @@ class SiglipMLP(nn.Module):
         self.fc2 = Linear(cfg.intermediate_size, cfg.hidden_size, bias=True)
 
     def forward(self, x: Tensor, residual: Tensor | None = None) -> Tensor:
-        return self.fc2(ops.act_fn(self.fc1(x), self.act), residual=residual)
+        w = self.fc1.weight
+        h = ops.linear_act(x.to(w.dtype) if x.dtype != w.dtype else x, w, self.fc1.bias, self.act)
+        return self.fc2(h, residual=residual)
 
 
 class SiglipEncoderLayer(nn.Module):

@@ -77,6 +77,17 @@ def act_fn(x: Tensor, act: str) -> Tensor:
     return ref.act_fn(x, act)
 
 
+def linear_act(x: Tensor, w: Tensor, bias: Tensor | None, act: str) -> Tensor:
+    """``act(x @ w.T + bias)``; when no gradient is needed the activation runs in the GEMM epilogue."""
+    import torch
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or w.requires_grad)
+    if (not oracle_mode() and not needs_grad and x.is_cuda and x.dtype == torch.bfloat16 and act == "gelu_tanh"):
+        from . import cuda_ops
+        y = cuda_ops.gemm(x.reshape(-1, x.shape[-1]), w, "nt", bias=bias, act="gelu_tanh")
+        return y.view(*x.shape[:-1], w.shape[0])
+    return ref.act_fn(linear(x, w, bias), act)
+
+
 def block_attention(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor,
                     q_valid: Tensor, k_valid: Tensor, scale: float) -> Tensor:
     if oracle_mode():
@@ -119,7 +130,7 @@ def resize_with_pad(img: Tensor, width: int, height: int, pad_value: float = -1.
 
 __all__ = [
     "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "rope",
-    "gated_mlp", "act_fn", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
+    "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
     "resize_with_pad", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
     "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "oracle_mode", "prims", "fused", "ref",
 ]

@@ -76,8 +76,9 @@ def linear(x, w, bias=None, residual=None):
 class GatedMLPFn(torch.autograd.Function):
     """``down(act(gate(x)) * up(x)) (+ residual)`` with a fused, block-interleaved gate/up weight.
 
-    Saves ``x`` and the gate/up GEMM output only; the activation product is recomputed in the
-    backward and its gradient overwrites the saved gate/up buffer in place.
+    The activation product comes out of the gate/up GEMM's epilogue.  For the backward ``x``, the gate/up
+    output and the product are kept (180 GB of HBM make the recompute pointless); the gradient of the
+    gate/up output overwrites that buffer in place.
     """
 
     @staticmethod
@@ -88,18 +89,17 @@ class GatedMLPFn(torch.autograd.Function):
         r2 = _flat2d(residual) if residual is not None else None
         y = prims.mm_nt(h, w_down, residual=r2)
         if need_bwd:
-            ctx.save_for_backward(x2, gu, w_gu, w_down)
+            ctx.save_for_backward(x2, gu, h, w_gu, w_down)
         ctx.wgu, ctx.wdown = w_gu, w_down
         ctx.act, ctx.x_shape, ctx.has_res = act, x.shape, residual is not None
         return y.view(*x.shape[:-1], w_down.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, gu, w_gu, w_down = ctx.saved_tensors
+        x2, gu, h, w_gu, w_down = ctx.saved_tensors
         dy2 = _flat2d(dy)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        h = prims.glu_fwd(gu, ctx.act)
         dwd = _sink_wgrad(ctx.wdown, dy2, h) if ctx.needs_input_grad[2] else None
         dh = prims.mm_nn(dy2, w_down, out=h)  # h is dead after the weight gradient
         dgu = prims.glu_bwd(gu, dh, ctx.act, inplace=True)
