@@ -202,6 +202,14 @@ class PI05FlowMatching(nn.Module):
         u = torch.rand(bsize, dtype=torch.float32, device=device).clamp_min(1e-12)
         return u.pow(1.0 / 1.5) * 0.999 + 0.001
 
+    def _const(self, key, build) -> Tensor:
+        """Device-resident constants (layout masks, indicator ids) are built once, so that repeated calls do
+        no host-to-device copies and the whole sampler can be replayed from a CUDA graph."""
+        cache = self.__dict__.setdefault("_const_cache", {})
+        if key not in cache:
+            cache[key] = build()
+        return cache[key]
+
     def _indicator(self, text: str) -> list[int]:
         if text not in self._indicator_cache:
             self._indicator_cache[text] = list(self.language_tokenizer.encode(text, add_special_tokens=False))
@@ -211,7 +219,8 @@ class PI05FlowMatching(nn.Module):
         ids = self._indicator(text)
         if max_len is not None:
             ids = (ids + [0] * max_len)[:max_len] if len(ids) != max_len else ids
-        tok = torch.tensor([ids], device=device).expand(bsize, -1)
+        tok = self._const(("ind", text, max_len, str(device)),
+                          lambda: torch.tensor([ids], device=device)).expand(bsize, -1)
         e = self.paligemma_with_expert.embed_language_tokens(tok)
         return e * math.sqrt(e.shape[-1])
 
@@ -274,8 +283,10 @@ class PI05FlowMatching(nn.Module):
             seg += [4] * d.shape[1]
         embs_t = torch.cat(embs, dim=1)
         pads_t = torch.cat(pads, dim=1)
-        att_t = torch.tensor(att, dtype=torch.bool, device=device)[None].expand(B, -1)
-        seg_t = torch.tensor(seg, dtype=torch.long, device=device)[None].expand(B, -1)
+        att_t = self._const(("att", tuple(att), str(device)),
+                            lambda: torch.tensor(att, dtype=torch.bool, device=device))[None].expand(B, -1)
+        seg_t = self._const(("seg", tuple(seg), str(device)),
+                            lambda: torch.tensor(seg, dtype=torch.long, device=device))[None].expand(B, -1)
         if self.config.use_modality_embedding:
             embs_t = embs_t + self.modality_embedding(seg_t).to(embs_t.dtype)
         return embs_t, pads_t, att_t, seg_t
@@ -396,24 +407,37 @@ class PI05FlowMatching(nn.Module):
             adarms_cond=[None, cond])
         return self.action_out_proj(suffix_out[:, -self.config.chunk_size:]).float()
 
+    def frozen_mask(self, delay: Tensor | int, batch: int, device) -> Tensor:
+        """``(B, chunk)`` bool: chunk rows fixed by real-time chunking (the first ``delay`` rows)."""
+        c = self.config.chunk_size
+        if isinstance(delay, int):
+            m = torch.zeros(1, c, dtype=torch.bool, device=device)
+            if delay > 0:
+                m[:, :delay] = True
+            return m.expand(batch, -1)
+        d = delay.to(device).reshape(-1, 1)
+        return (torch.arange(c, device=device)[None, :] < d).expand(batch, -1)
+
     @torch.no_grad()
     def denoise_loop(self, cache: KVCache, prefix_len: Tensor, noise: Tensor, action_prefix: Tensor | None = None,
-                     delay: Tensor | int = 0, accel=None) -> Tensor:
-        """``num_steps`` Euler steps from t=1 to t=0 with a fixed trip count (no host sync)."""
+                     delay: Tensor | int = 0, accel=None, frozen: Tensor | None = None) -> Tensor:
+        """``num_steps`` Euler steps from t=1 to t=0 with a fixed trip count and device-only operations
+        (no host round trip, no host-to-device copy), so the loop can be captured in a CUDA graph."""
         cfg = self.config
         n = cfg.num_steps
         dt = -1.0 / n
         x_t = noise.float().clone()
         B = x_t.shape[0]
         device = x_t.device
-        delay_t = torch.as_tensor(delay, device=device)
-        frozen = (torch.arange(cfg.chunk_size, device=device)[None, :] < delay_t.reshape(-1, 1)).expand(B, -1)
+        if frozen is None:
+            frozen = self.frozen_mask(delay, B, device)
+        live = (~frozen).to(torch.float32)
         has_prefix = action_prefix is not None
         for i in range(n):
             t = 1.0 + i * dt
             if has_prefix:
                 x_t = torch.where(frozen[:, :, None], action_prefix.to(x_t.dtype), x_t)
-            time = torch.where(frozen, torch.zeros((), device=device), torch.full((), t, device=device))
+            time = live * t          # frozen rows run at diffusion time 0
             v_t = self.denoise_step(cache, prefix_len, x_t, time)
             if accel is not None:
                 accel.update(v_t)
@@ -424,7 +448,7 @@ class PI05FlowMatching(nn.Module):
 
     @torch.no_grad()
     def sample_actions(self, images, img_masks, lang_tokens, lang_masks, action_prefix=None, delay=0,
-                       noise=None, state=None, n_candidates: int = 1, accel=None) -> Tensor:
+                       noise=None, state=None, n_candidates: int = 1, accel=None, frozen=None) -> Tensor:
         B = lang_tokens.shape[0]
         device = lang_tokens.device
         cfg = self.config
@@ -439,7 +463,9 @@ class PI05FlowMatching(nn.Module):
             prefix_len = prefix_len.repeat_interleave(n_candidates, 0)
             if action_prefix is not None:
                 action_prefix = action_prefix.repeat_interleave(n_candidates, 0)
-        return self.denoise_loop(cache, prefix_len, noise, action_prefix, delay, accel)
+            if frozen is not None:
+                frozen = frozen.repeat_interleave(n_candidates, 0)
+        return self.denoise_loop(cache, prefix_len, noise, action_prefix, delay, accel, frozen)
 
 
 class PI05Policy(PreTrainedPolicy):
@@ -597,10 +623,14 @@ class PI05Policy(PreTrainedPolicy):
         if state.dim() == 3:
             state = state[:, -1]
         n = n_candidates or cfg.n_candidates or 1
-        actions = self.model.sample_actions(images, img_masks, lang_tokens, lang_masks, action_prefix=action_prefix,
-                                            delay=delay, noise=noise,
-                                            state=state if cfg.state_type == "continuous" else None,
-                                            n_candidates=n)
+        st = state if cfg.state_type == "continuous" else None
+        if getattr(self, "_use_graphs", False) and device.type == "cuda":
+            actions = self._graphed_sample(images, img_masks, lang_tokens, lang_masks, action_prefix, delay, noise,
+                                           st, n)
+        else:
+            actions = self.model.sample_actions(images, img_masks, lang_tokens, lang_masks,
+                                                action_prefix=action_prefix, delay=delay, noise=noise, state=st,
+                                                n_candidates=n)
         if n > 1:
             from ..candidates import select_candidate
             actions = select_candidate(actions.view(B, n, *actions.shape[1:]))
@@ -608,6 +638,33 @@ class PI05Policy(PreTrainedPolicy):
         real = feat.shape[0] if feat is not None else actions.shape[-1]
         actions = actions[:, :, :real]
         return self.unnormalize_outputs({"actions": actions}, idx)["actions"]
+
+    def enable_cuda_graphs(self, flag: bool = True) -> None:
+        """Replay the sampler (prefix pass + Euler loop) from a CUDA graph: one launch per action chunk."""
+        self._use_graphs = bool(flag)
+        self._graph_runner = None
+
+    def _graphed_sample(self, images, img_masks, lang_tokens, lang_masks, action_prefix, delay, noise, state, n):
+        from ...runtime.graphs import CudaGraphRunner
+        cfg = self.config
+        B = lang_tokens.shape[0]
+        device = lang_tokens.device
+        if noise is None:
+            noise = self.model.sample_noise((B * n, cfg.chunk_size, cfg.max_action_dim), device)
+        if action_prefix is None:
+            action_prefix = torch.zeros(B, cfg.chunk_size, cfg.max_action_dim, device=device)
+        frozen = self.model.frozen_mask(delay, B, device).contiguous()
+        has_state = state is not None
+        if getattr(self, "_graph_runner", None) is None:
+            def fn(images, img_masks, lang_tokens, lang_masks, noise, action_prefix, frozen, state):
+                return self.model.sample_actions(list(images), list(img_masks), lang_tokens, lang_masks,
+                                                 action_prefix=action_prefix, noise=noise, frozen=frozen,
+                                                 state=state if has_state else None, n_candidates=n)
+            self._graph_runner = CudaGraphRunner(fn)
+        st = state if has_state else torch.zeros(1, device=device)
+        out = self._graph_runner(tuple(images), tuple(img_masks), lang_tokens, lang_masks.bool(), noise.float(),
+                                 action_prefix.float(), frozen, st)
+        return out.clone()
 
     @torch.no_grad()
     def select_action(self, batch: dict[str, Any], noise: Tensor | None = None) -> Tensor:

@@ -1,0 +1,120 @@
+"""Action-chunk latency benchmark: ``sample_actions`` on a fixed observation, batch 1 by default.
+
+Counterpart of the reference script (OpenTau ``src/opentau/scripts/benchmark_inference.py:153-331``): warm-up
+calls, then timed calls each bracketed by a device synchronise, reporting mean / std / p50 / p95 / p99.  The
+"compiled" arm of the reference (``torch.compile`` + CUDA graphs) corresponds here to ``--graphs`` (replay of
+the captured sampler); ``--no-graphs`` is the eager arm.  Environment knobs kept: ``BENCH_N_WARMUP``,
+``BENCH_N_TIMED``, ``BENCH_N_CANDIDATES``, ``BENCH_OUTPUT_DIR``.
+
+    python -m opentau_b200.scripts.benchmark_inference [--policy pi05] [--cams 3] [--prompt-len 200] [--graphs]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import time
+from pathlib import Path
+
+import torch
+
+BENCHMARK_PROMPT = "pick up the red block and place it in the bin"
+
+
+def summarize(ms: list[float]) -> dict:
+    s = sorted(ms)
+
+    def pct(p: float) -> float:
+        k = (len(s) - 1) * p
+        lo, hi = int(k), min(int(k) + 1, len(s) - 1)
+        return s[lo] + (s[hi] - s[lo]) * (k - lo)
+
+    return {"n": len(s), "mean_ms": statistics.fmean(s), "std_ms": statistics.pstdev(s) if len(s) > 1 else 0.0,
+            "p50_ms": pct(0.5), "p95_ms": pct(0.95), "p99_ms": pct(0.99), "min_ms": s[0], "max_ms": s[-1]}
+
+
+def build_pi05(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 10):
+    from ..configs.types import FeatureType, PolicyFeature
+    from ..datasets.synthetic import SyntheticSpec, identity_stats, make_synthetic_batch
+    from ..policies.pi05.configuration_pi05 import PI05Config
+    from ..policies.pi05.modeling_pi05 import PI05Policy
+    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, 224, 224)) for i in range(cams)}
+    feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
+    kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=prompt_len, num_steps=num_steps, dropout=0.0,
+              device=str(device), input_features=feats,
+              output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
+    spec = SyntheticSpec(batch_size=1, num_cams=cams, prompt_len=prompt_len, vocab_size=257152, state_dim=32,
+                         action_dim=32, chunk_size=50, image_dtype=torch.bfloat16)
+    if tiny:
+        kw.update(vlm=dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+                           head_dim=64, intermediate_size=1024, vocab_size=1024),
+                  expert=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+                              head_dim=64, intermediate_size=512, vocab_size=1024),
+                  vision=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4))
+        spec.vocab_size = 1024
+    cfg = PI05Config(**kw)
+    torch.manual_seed(0)
+    with torch.device(device):
+        policy = PI05Policy(cfg, per_dataset_stats=[identity_stats()])
+    policy.to(device).to(torch.bfloat16).eval()
+    batch = make_synthetic_batch(spec, device=device, seed=3)
+    return policy, batch
+
+
+def run(policy, batch, n_warmup: int, n_timed: int, n_candidates: int = 1) -> dict:
+    dev = batch["state"].device
+    cuda = dev.type == "cuda"
+    times = []
+    for i in range(n_warmup + n_timed):
+        if cuda:
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = policy.sample_actions(batch, n_candidates=n_candidates)
+        if cuda:
+            torch.cuda.synchronize()
+        if i >= n_warmup:
+            times.append((time.perf_counter() - t0) * 1e3)
+    assert torch.isfinite(out).all()
+    return summarize(times)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--policy", default="pi05")
+    ap.add_argument("--cams", type=int, default=3)
+    ap.add_argument("--prompt-len", type=int, default=200)
+    ap.add_argument("--num-steps", type=int, default=10)
+    ap.add_argument("--graphs", dest="graphs", action="store_true", default=True)
+    ap.add_argument("--no-graphs", dest="graphs", action="store_false")
+    ap.add_argument("--tiny", action="store_true")
+    args = ap.parse_args(argv)
+    n_warmup = int(os.environ.get("BENCH_N_WARMUP", "5"))
+    n_timed = int(os.environ.get("BENCH_N_TIMED", "50"))
+    n_cand = int(os.environ.get("BENCH_N_CANDIDATES", "1"))
+    device = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    policy, batch = build_pi05(args.cams, args.prompt_len, device, args.tiny, args.num_steps)
+    rec = {"policy": args.policy, "device": torch.cuda.get_device_name(0) if device.type == "cuda" else "cpu",
+           "dtype": "bf16", "num_steps": args.num_steps, "n_candidates": n_cand, "cams": args.cams,
+           "prompt_len": args.prompt_len}
+    if device.type == "cuda":
+        from ..ops import cuda_ops
+        policy.enable_cuda_graphs(False)
+        rec["eager"] = run(policy, batch, n_warmup, n_timed, n_cand)
+        if args.graphs:
+            policy.enable_cuda_graphs(True)
+            rec["cuda_graph"] = run(policy, batch, n_warmup, n_timed, n_cand)
+        cuda_ops.check_status()
+    else:
+        rec["eager"] = run(policy, batch, 1, 3, n_cand)
+    print(json.dumps(rec))
+    out_dir = os.environ.get("BENCH_OUTPUT_DIR")
+    if out_dir:
+        Path(out_dir).mkdir(parents=True, exist_ok=True)
+        (Path(out_dir) / f"benchmark_inference_{args.policy}.json").write_text(json.dumps(rec, indent=2))
+    return rec
+
+
+if __name__ == "__main__":
+    main()
