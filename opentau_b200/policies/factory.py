@@ -17,6 +17,8 @@ _POLICIES: dict[str, tuple[str, str, str]] = {
              "opentau_b200.policies.pi05.configuration_pi05"),
     "pi05_continuous_state": ("opentau_b200.policies.pi05.modeling_pi05", "PI05Policy",
                               "opentau_b200.policies.pi05.configuration_pi05"),
+    "pi06": ("opentau_b200.policies.pi06.modeling_pi06", "PI06Policy",
+             "opentau_b200.policies.pi06.configuration_pi06"),
 }
 
 

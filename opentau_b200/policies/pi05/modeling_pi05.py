@@ -161,7 +161,11 @@ class PaliGemmaWithExpertModel(nn.Module):
         return self.paligemma.model.multi_modal_projector(feats)
 
     def embed_language_tokens(self, tokens: Tensor) -> Tensor:
-        return self.paligemma.language_model.embed_tokens(tokens)
+        """Token embeddings already multiplied by ``sqrt(hidden)`` (the PaliGemma convention)."""
+        return self.paligemma.language_model.embed(tokens)
+
+    def lm_head_weight(self) -> Tensor:
+        return self.paligemma.lm_head_weight()
 
     def embed_discrete_actions(self, actions: Tensor) -> Tensor:
         return self.discrete_action_embedding(actions)
@@ -175,9 +179,9 @@ class PI05FlowMatching(nn.Module):
         super().__init__()
         self.config = config
         self.language_tokenizer = tokenizer
-        self.paligemma_with_expert = PaliGemmaWithExpertModel(config)
-        vlm_d = self.paligemma_with_expert.vlm_cfg.hidden_size
-        w = self.paligemma_with_expert.expert_cfg.hidden_size
+        setattr(self, self.wrapper_attr, self.build_wrapper(config))
+        vlm_d = self.wrapper.vlm_cfg.hidden_size
+        w = self.wrapper.expert_cfg.hidden_size
         if config.state_type == "continuous":
             self.state_proj = Linear(config.max_state_dim, vlm_d, bias=True)
         self.action_in_proj = Linear(config.max_action_dim, w, bias=True)
@@ -190,6 +194,21 @@ class PI05FlowMatching(nn.Module):
             nn.init.zeros_(self.modality_embedding.weight)
             nn.init.zeros_(self.action_modality_embedding.weight)
         self._indicator_cache: dict[str, list[int]] = {}
+
+    wrapper_attr = "paligemma_with_expert"
+
+    def build_wrapper(self, config):
+        return PaliGemmaWithExpertModel(config)
+
+    @property
+    def wrapper(self):
+        """The backbone+expert pair (its attribute name is part of the checkpoint key contract)."""
+        return getattr(self, self.wrapper_attr)
+
+    def discrete_block_len(self) -> int:
+        """Number of trailing prefix tokens that hold the discrete-action block (excluded from the KV
+        cache the expert reads, so training and inference prefixes match)."""
+        return self.config.discrete_action_indicator_max_length + self.config.discrete_action_max_length
 
     # -- sampling helpers ------------------------------------------------------------------------
     @staticmethod
@@ -221,8 +240,7 @@ class PI05FlowMatching(nn.Module):
             ids = (ids + [0] * max_len)[:max_len] if len(ids) != max_len else ids
         tok = self._const(("ind", text, max_len, str(device)),
                           lambda: torch.tensor([ids], device=device)).expand(bsize, -1)
-        e = self.paligemma_with_expert.embed_language_tokens(tok)
-        return e * math.sqrt(e.shape[-1])
+        return self.wrapper.embed_language_tokens(tok)
 
     # -- prefix / suffix -----------------------------------------------------------------------------
     def embed_prefix(self, images: list[Tensor], img_masks: list[Tensor], lang_tokens: Tensor, lang_masks: Tensor,
@@ -230,7 +248,7 @@ class PI05FlowMatching(nn.Module):
                      discrete_actions: Tensor | None = None, discrete_action_masks: Tensor | None = None,
                      state: Tensor | None = None):
         """Returns ``(embs, pad_masks, att_masks, segment_ids)``; att 0 joins the previous block."""
-        pwe = self.paligemma_with_expert
+        pwe = self.wrapper
         dtype = pwe.paligemma.language_model.embed_tokens.weight.dtype
         device = lang_tokens.device
         B = lang_tokens.shape[0]
@@ -245,7 +263,7 @@ class PI05FlowMatching(nn.Module):
             att += [0] * (len(images) * n_img)
             seg += [0] * (len(images) * n_img)
         lang = pwe.embed_language_tokens(lang_tokens)
-        embs.append(lang * math.sqrt(lang.shape[-1]))
+        embs.append(lang)
         pads.append(lang_masks.bool())
         att += [0] * lang.shape[1]
         seg += [1] * lang.shape[1]
@@ -269,7 +287,7 @@ class PI05FlowMatching(nn.Module):
             seg += [3] * e.shape[1]
         if response_tokens is not None:
             r = pwe.embed_language_tokens(response_tokens)
-            embs.append(r * math.sqrt(r.shape[-1])), pads.append(response_masks.bool())
+            embs.append(r), pads.append(response_masks.bool())
             att += [1] * r.shape[1]
             seg += [3] * r.shape[1]
         if discrete_actions is not None:
@@ -314,14 +332,13 @@ class PI05FlowMatching(nn.Module):
                 response_tokens=None, response_masks=None, noise=None, time=None, discrete_actions=None,
                 discrete_action_masks=None, state=None, real_action_dim=None, return_per_sample=False):
         cfg = self.config
-        pwe = self.paligemma_with_expert
+        pwe = self.wrapper
         prefix_embs, prefix_pad, prefix_att, _ = self.embed_prefix(
             images, img_masks, lang_tokens, lang_masks, response_tokens, response_masks, discrete_actions,
             discrete_action_masks, state=state)
         blk, valid = ops.make_block_ids(prefix_pad, prefix_att)
         pos = torch.cumsum(prefix_pad, dim=1) - 1
-        n_disc = (cfg.discrete_action_indicator_max_length + cfg.discrete_action_max_length
-                  if discrete_actions is not None else 0)
+        n_disc = self.discrete_block_len() if discrete_actions is not None else 0
         n_cross = prefix_embs.shape[1] - n_disc
         (prefix_out, _), cache = pwe(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
                                      q_valid=valid, fill_cache_len=n_cross)
@@ -371,7 +388,7 @@ class PI05FlowMatching(nn.Module):
             end = -n_disc - 1 if n_disc else -1
             h = prefix_out[:, start:end]
             labels = response_tokens[:, 1:]
-            r_ce = ops.linear_cross_entropy(h.reshape(B * (Lr - 1), -1), pwe.paligemma.lm_head_weight(), None,
+            r_ce = ops.linear_cross_entropy(h.reshape(B * (Lr - 1), -1), pwe.lm_head_weight(), None,
                                             labels.reshape(-1)).view(B, Lr - 1)
             r_mask = response_masks[:, 1:].to(r_ce.dtype)
             r_ce = r_ce * r_mask
@@ -392,7 +409,7 @@ class PI05FlowMatching(nn.Module):
                                                                    state=state)
         blk, valid = ops.make_block_ids(prefix_pad, prefix_att)
         pos = torch.cumsum(prefix_pad, dim=1) - 1
-        _, cache = self.paligemma_with_expert(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
+        _, cache = self.wrapper(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
                                               q_valid=valid, fill_cache_len=prefix_embs.shape[1])
         return cache, prefix_pad.sum(-1, keepdim=True)
 
@@ -402,7 +419,7 @@ class PI05FlowMatching(nn.Module):
         suffix_embs, suffix_pad, suffix_att, cond = self.embed_suffix(x_t, time)
         s_blk, s_valid = ops.make_block_ids(suffix_pad, suffix_att)
         s_pos = prefix_len + torch.cumsum(suffix_pad, dim=1) - 1
-        (_, suffix_out), _ = self.paligemma_with_expert(
+        (_, suffix_out), _ = self.wrapper(
             inputs_embeds=[None, suffix_embs], position_ids=s_pos, q_blk=s_blk, q_valid=s_valid, past=cache,
             adarms_cond=[None, cond])
         return self.action_out_proj(suffix_out[:, -self.config.chunk_size:]).float()
@@ -473,6 +490,11 @@ class PI05Policy(PreTrainedPolicy):
 
     config_class = PI05Config
     name = "pi05"
+    model_class = PI05FlowMatching
+
+    @staticmethod
+    def _vocab_size(config) -> int:
+        return gemma_2b_config(**(config.vlm or {})).vocab_size
 
     def __init__(self, config: PI05Config, per_dataset_stats: list[dict] | None = None,
                  dataset_names: list[str] | None = None, **_):
@@ -489,11 +511,10 @@ class PI05Policy(PreTrainedPolicy):
         da_map = {"ACTION": NormalizationMode.MIN_MAX}
         self.normalize_discrete_actions = Normalize(config.output_features, da_map, **kw)
         self.unnormalize_outputs = Unnormalize(config.output_features, config.normalization_mapping, **kw)
-        self.language_tokenizer = load_text_tokenizer(config.tokenizer_path,
-                                                       gemma_2b_config(**(config.vlm or {})).vocab_size)
+        self.language_tokenizer = load_text_tokenizer(config.tokenizer_path, self._vocab_size(config))
         self.discrete_action_processor = load_action_tokenizer(config.discrete_action_tokenizer_path,
                                                                config.discrete_action_vocab_size)
-        self.model = PI05FlowMatching(config, tokenizer=self.language_tokenizer)
+        self.model = self.model_class(config, tokenizer=self.language_tokenizer)
         self.reset()
 
     def reset(self) -> None:
