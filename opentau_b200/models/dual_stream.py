@@ -150,15 +150,17 @@ class DualStreamDecoder(nn.Module):
                 q_valid: Tensor, *, adarms_cond: list[Tensor | None] | None = None,
                 past: KVCache | None = None, fill_cache_len: int | None = None,
                 k_blk: Tensor | None = None, k_valid: Tensor | None = None,
-                mrope: bool = False, per_layer_cache: bool = True,
-                ) -> tuple[list[Tensor | None], KVCache | None]:
+                mrope: bool = False, per_layer_cache: bool = True, past_layer_map: list[int] | None = None,
+                layer_hook=None) -> tuple[list[Tensor | None], KVCache | None]:
         """One pass over all layers.
 
         ``position_ids``: ``(B, S_total)`` (or ``(3,B,S_total)`` with ``mrope``) for the
         concatenated present towers.  ``q_blk/q_valid`` describe those tokens; when ``past`` is
         given its tokens are prepended as keys with block id ``INT_MIN`` (visible to every
         query, gated only by ``past.valid``).  ``fill_cache_len=n`` returns a cache holding the
-        first ``n`` tokens' post-RoPE K/V of every layer.
+        first ``n`` tokens' post-RoPE K/V of every layer.  ``past_layer_map[l]`` names the cache layer that
+        decoder layer ``l`` reads (default ``l``; a constant map conditions every layer on one backbone
+        layer).  ``layer_hook(l, xs) -> xs`` runs after layer ``l`` (deepstack feature injection).
         """
         towers = self.towers
         xs = list(inputs_embeds)
@@ -201,14 +203,17 @@ class DualStreamDecoder(nn.Module):
 
         for li in range(self.num_layers):
             theta = towers[0].cfg.layer_theta(li)
-            ck = past.k[li, :, :past.length] if past is not None else None
-            cv = past.v[li, :, :past.length] if past is not None else None
+            pl = past_layer_map[li] if past_layer_map is not None else li
+            ck = past.k[pl, :, :past.length] if past is not None else None
+            cv = past.v[pl, :, :past.length] if past is not None else None
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
                 xs, nk, nv = checkpoint(self._layer, li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid,
                                         ck, cv, mods, use_reentrant=False)
             else:
                 xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods)
+            if layer_hook is not None:
+                xs = layer_hook(li, xs)
             if fill_cache_len is not None:
                 if keep_graph:
                     ks_list.append(nk[:, :fill_cache_len])

@@ -17,6 +17,11 @@ _POLICIES: dict[str, tuple[str, str, str]] = {
              "opentau_b200.policies.pi05.configuration_pi05"),
     "pi05_continuous_state": ("opentau_b200.policies.pi05.modeling_pi05", "PI05Policy",
                               "opentau_b200.policies.pi05.configuration_pi05"),
+    "pi0": ("opentau_b200.policies.pi0.modeling_pi0", "PI0Policy", "opentau_b200.policies.pi0.configuration_pi0"),
+    "cosmos3": ("opentau_b200.policies.cosmos3.modeling_cosmos3", "Cosmos3Policy",
+                "opentau_b200.policies.cosmos3.configuration_cosmos3"),
+    "cosmos3_nano": ("opentau_b200.policies.cosmos3_nano.modeling_cosmos3_nano", "Cosmos3NanoPolicy",
+                     "opentau_b200.policies.cosmos3_nano.configuration_cosmos3_nano"),
     "pi06": ("opentau_b200.policies.pi06.modeling_pi06", "PI06Policy",
              "opentau_b200.policies.pi06.configuration_pi06"),
 }
