@@ -22,6 +22,11 @@ _POLICIES: dict[str, tuple[str, str, str]] = {
                 "opentau_b200.policies.cosmos3.configuration_cosmos3"),
     "cosmos3_nano": ("opentau_b200.policies.cosmos3_nano.modeling_cosmos3_nano", "Cosmos3NanoPolicy",
                      "opentau_b200.policies.cosmos3_nano.configuration_cosmos3_nano"),
+    "pi07_low_level": ("opentau_b200.policies.pi07.low_level.modeling_pi07_low_level", "PI07LowLevelPolicy",
+                       "opentau_b200.policies.pi07.low_level.configuration_pi07_low_level"),
+    "pi07_high_level": ("opentau_b200.policies.pi07.high_level_planner.modeling_pi07_high_level",
+                        "PI07HighLevelPlannerPolicy",
+                        "opentau_b200.policies.pi07.high_level_planner.configuration_pi07_high_level"),
     "pi06": ("opentau_b200.policies.pi06.modeling_pi06", "PI06Policy",
              "opentau_b200.policies.pi06.configuration_pi06"),
 }

@@ -330,12 +330,13 @@ class PI05FlowMatching(nn.Module):
     # -- training ----------------------------------------------------------------------------------
     def forward(self, images, img_masks, lang_tokens, lang_masks, actions, actions_is_pad=None,
                 response_tokens=None, response_masks=None, noise=None, time=None, discrete_actions=None,
-                discrete_action_masks=None, state=None, real_action_dim=None, return_per_sample=False):
+                discrete_action_masks=None, state=None, real_action_dim=None, return_per_sample=False,
+                prefix_kwargs=None):
         cfg = self.config
         pwe = self.wrapper
         prefix_embs, prefix_pad, prefix_att, _ = self.embed_prefix(
             images, img_masks, lang_tokens, lang_masks, response_tokens, response_masks, discrete_actions,
-            discrete_action_masks, state=state)
+            discrete_action_masks, state=state, **(prefix_kwargs or {}))
         blk, valid = ops.make_block_ids(prefix_pad, prefix_att)
         pos = torch.cumsum(prefix_pad, dim=1) - 1
         n_disc = self.discrete_block_len() if discrete_actions is not None else 0
@@ -403,10 +404,11 @@ class PI05FlowMatching(nn.Module):
 
     # -- inference ---------------------------------------------------------------------------------
     @torch.no_grad()
-    def prefill(self, images, img_masks, lang_tokens, lang_masks, state=None) -> tuple[KVCache, Tensor]:
+    def prefill(self, images, img_masks, lang_tokens, lang_masks, state=None,
+                prefix_kwargs=None) -> tuple[KVCache, Tensor]:
         """Prefix pass: returns the KV cache and the per-sample count of valid prefix tokens."""
         prefix_embs, prefix_pad, prefix_att, _ = self.embed_prefix(images, img_masks, lang_tokens, lang_masks,
-                                                                   state=state)
+                                                                   state=state, **(prefix_kwargs or {}))
         blk, valid = ops.make_block_ids(prefix_pad, prefix_att)
         pos = torch.cumsum(prefix_pad, dim=1) - 1
         _, cache = self.wrapper(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
@@ -465,7 +467,8 @@ class PI05FlowMatching(nn.Module):
 
     @torch.no_grad()
     def sample_actions(self, images, img_masks, lang_tokens, lang_masks, action_prefix=None, delay=0,
-                       noise=None, state=None, n_candidates: int = 1, accel=None, frozen=None) -> Tensor:
+                       noise=None, state=None, n_candidates: int = 1, accel=None, frozen=None,
+                       prefix_kwargs=None) -> Tensor:
         B = lang_tokens.shape[0]
         device = lang_tokens.device
         cfg = self.config
@@ -474,7 +477,8 @@ class PI05FlowMatching(nn.Module):
         elif noise.shape[0] != B * n_candidates:
             raise ValueError(f"n_candidates={n_candidates} needs noise with {B * n_candidates} rows "
                              f"(got {tuple(noise.shape)})")
-        cache, prefix_len = self.prefill(images, img_masks, lang_tokens, lang_masks, state=state)
+        cache, prefix_len = self.prefill(images, img_masks, lang_tokens, lang_masks, state=state,
+                                         prefix_kwargs=prefix_kwargs)
         if n_candidates > 1:
             cache = cache.expand_batch(n_candidates)
             prefix_len = prefix_len.repeat_interleave(n_candidates, 0)
@@ -522,6 +526,10 @@ class PI05Policy(PreTrainedPolicy):
 
     def get_optim_params(self):
         return [p for p in self.parameters() if p.requires_grad]
+
+    def _prefix_kwargs(self, batch, normalized_batch) -> dict | None:
+        """Extra prefix inputs of richer policies (state history, metadata, subgoals); none here."""
+        return None
 
     # -- batch preparation ---------------------------------------------------------------------------
     def prepare_images(self, batch: dict[str, Any]) -> tuple[list[Tensor], list[Tensor]]:
@@ -626,7 +634,8 @@ class PI05Policy(PreTrainedPolicy):
                           actions_is_pad=batch.get("action_is_pad"), response_tokens=resp_t, response_masks=resp_m,
                           noise=noise, time=time, discrete_actions=da, discrete_action_masks=dam,
                           state=state if self.config.state_type == "continuous" else None,
-                          real_action_dim=batch.get("real_action_dim"), return_per_sample=return_per_sample)
+                          real_action_dim=batch.get("real_action_dim"), return_per_sample=return_per_sample,
+                          prefix_kwargs=self._prefix_kwargs(batch, nb))
 
     @torch.no_grad()
     def sample_actions(self, batch: dict[str, Any], noise: Tensor | None = None, action_prefix: Tensor | None = None,
@@ -651,7 +660,7 @@ class PI05Policy(PreTrainedPolicy):
         else:
             actions = self.model.sample_actions(images, img_masks, lang_tokens, lang_masks,
                                                 action_prefix=action_prefix, delay=delay, noise=noise, state=st,
-                                                n_candidates=n)
+                                                n_candidates=n, prefix_kwargs=self._prefix_kwargs(batch, nb))
         if n > 1:
             from ..candidates import select_candidate
             actions = select_candidate(actions.view(B, n, *actions.shape[1:]))

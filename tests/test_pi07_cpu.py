@@ -1,0 +1,127 @@
+"""pi0.7 controller / planner, the SpaceTime video encoder and the rank-wide branch decisions."""
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import TINY, tiny_batch
+from opentau_b200.configs.types import FeatureType, PolicyFeature
+from opentau_b200.datasets.synthetic import identity_stats
+from opentau_b200.models.video_encoder import build_temporal_sinusoidal_pe
+from opentau_b200.policies.factory import make_policy, make_policy_config
+from opentau_b200.policies.pi07.common import global_or_branch_decisions
+
+FEATS = {"camera0": PolicyFeature(FeatureType.VISUAL, (3, 224, 224)), "state": PolicyFeature(FeatureType.STATE, (32,))}
+OUT = {"actions": PolicyFeature(FeatureType.ACTION, (32,))}
+G3 = dict(vlm=dict(TINY["vlm"], num_key_value_heads=2, sliding_window_pattern=2), vision=TINY["vision"],
+          vlm_config={"tokens_per_image_side": 8})
+
+
+def _ll(**kw):
+    return make_policy(make_policy_config(
+        "pi07_low_level", n_obs_steps=3, chunk_size=10, n_action_steps=10, prompt_max_length=16,
+        discrete_action_max_length=8, discrete_action_vocab_size=256, dropout=0.0, device="cpu",
+        resize_imgs_with_padding=(224, 224), metadata_max_length=12, response_max_length=8,
+        spacetime_layer_stride=2, input_features=dict(FEATS), output_features=dict(OUT),
+        expert=dict(TINY["expert"], num_key_value_heads=2), **G3, **kw), per_dataset_stats=[identity_stats()])
+
+
+def _history_batch():
+    b = tiny_batch()
+    b["camera0"] = b["camera0"][:, None].repeat(1, 3, 1, 1, 1) * torch.tensor([0.5, 0.8, 1.0]).view(1, 3, 1, 1, 1)
+    b["state"] = b["state"][:, None].repeat(1, 3, 1)
+    b["obs_history_is_pad"] = torch.tensor([[1, 0, 0], [0, 0, 0], [1, 1, 0], [0, 0, 0]], dtype=torch.bool)
+    return b
+
+
+def test_temporal_pe_current_row_is_zero_and_alias_guard():
+    pe = build_temporal_sinusoidal_pe(6, 32)
+    assert pe.shape == (6, 32) and torch.all(pe[-1] == 0) and pe[0].abs().sum() > 0
+    with pytest.raises(ValueError):
+        build_temporal_sinusoidal_pe(50, 32, max_period=40.0)
+
+
+def test_video_encoder_single_frame_equals_plain_siglip_and_history_matters():
+    torch.manual_seed(0)
+    pol = _ll()
+    enc, vt = pol.model.video_encoder, pol.model.wrapper.gemma3.model.vision_tower
+    x = torch.rand(2, 3, 224, 224) * 2 - 1
+    assert torch.equal(enc(x[:, None]), vt(x))
+    vid = torch.rand(2, 3, 3, 224, 224) * 2 - 1
+    a = enc(vid)
+    vid2 = vid.clone()
+    vid2[:, 0] = torch.rand_like(vid2[:, 0])
+    assert not torch.allclose(a, enc(vid2))                       # history reaches the current-frame tokens
+    valid = torch.tensor([[False, True, True], [False, True, True]])
+    assert torch.allclose(enc(vid, valid), enc(vid2, valid), atol=1e-5)   # ... unless that frame is padding
+    assert not any("video_encoder" in k for k in pol.state_dict())    # no duplicated vision weights
+
+
+def test_low_level_optional_blocks_and_training():
+    torch.manual_seed(0)
+    pol = _ll()
+    b = _history_batch()
+    base = pol(b, noise=torch.zeros(4, 10, 32), time=torch.full((4,), 0.5))
+    b["response"] = ["grasp the cup", "", "move left", "open"]
+    b["speed"] = torch.tensor([1, 2, 3, 4])
+    b["robot_type"] = ["so101"] * 4
+    b["subgoal0"] = torch.rand(4, 3, 224, 224)
+    b["subgoal0_is_pad"] = torch.tensor([0, 1, 0, 0], dtype=torch.bool)
+    rich = pol(b, noise=torch.zeros(4, 10, 32), time=torch.full((4,), 0.5))
+    assert not torch.allclose(base["CE"], rich["CE"])
+    (rich["MSE"] + rich["CE"]).backward()
+    assert pol.model.state_proj.weight.grad.abs().sum() > 0
+    pol.eval()
+    assert pol.sample_actions(b).shape == (4, 10, 32)
+
+
+def test_high_level_planner_ce_and_decoding():
+    torch.manual_seed(0)
+    hl = make_policy(make_policy_config(
+        "pi07_high_level", prompt_max_length=16, memory_max_length=6, response_max_length=5, device="cpu",
+        dropout=0.0, resize_imgs_with_padding=(224, 224), input_features=dict(FEATS), **G3))
+    b = tiny_batch()
+    b["next_memory"] = ["cup grasped"] * 4
+    b["response"] = ["lift the cup"] * 4
+    out = hl(b)
+    assert out["MSE"].item() == 0 and out["CE"].item() > 0
+    out["CE"].backward()
+    assert not any("expert_layer" in n for n, _ in hl.named_parameters())
+    mem, sub = hl.plan(b)
+    assert len(mem) == 4 and len(sub) == 4
+    with pytest.raises(NotImplementedError):
+        hl.select_action(b)
+
+
+def test_branch_decisions_single_process():
+    assert global_or_branch_decisions((True, False), (True, False), ("a", "b"), torch.device("cpu")) == (True, False)
+    with pytest.raises(ValueError):
+        global_or_branch_decisions((False,), (True,), ("a",), torch.device("cpu"))
+
+
+def _branch_worker(rank, world, port, diverge, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        present = (True, rank == 0) if diverge else (True, True)
+        anys = (rank == 1, False)
+        try:
+            ret[rank] = global_or_branch_decisions(present, anys, ("response", "metadata"), torch.device("cpu"))
+        except RuntimeError as e:
+            ret[rank] = f"raised: {e}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("diverge", [False, True])
+def test_branch_decisions_two_ranks(diverge):
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_branch_worker, args=(2, 29900 + os.getpid() % 90 + int(diverge), diverge, ret), nprocs=2, join=True)
+    if diverge:
+        assert all(str(ret[r]).startswith("raised") and "metadata" in str(ret[r]) for r in (0, 1))
+    else:
+        assert ret[0] == ret[1] == (True, False)      # rank 1's "some real entries" wins on both ranks
