@@ -567,7 +567,7 @@ class PI05Policy(PreTrainedPolicy):
         if state.dim() == 3:
             state = state[:, -1]
         bins = torch.linspace(-1, 1, 257, device=state.device)[:-1]
-        ids = (torch.bucketize(state.float(), bins) - 1).clamp(0, 255)
+        ids = (torch.bucketize(state.float().clamp(-1.0, 1.0), bins, right=True) - 1).clamp(0, 255)
         return [" ".join(map(str, row)) for row in ids.cpu().tolist()]
 
     def prepare_language(self, batch) -> tuple[Tensor, Tensor]:
