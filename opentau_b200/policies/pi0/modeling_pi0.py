@@ -119,13 +119,13 @@ class PI0FlowMatching(PI05FlowMatching):
 
     @torch.no_grad()
     def sample_actions(self, images, img_masks, lang_tokens, lang_masks, action_prefix=None, delay=0, noise=None,
-                       state=None, n_candidates: int = 1, accel=None, frozen=None):
+                       state=None, n_candidates: int = 1, accel=None, frozen=None, prefix_kwargs=None):
         if state is None:
             raise ValueError("pi0 needs the state vector at inference")
         self._state = state.repeat_interleave(n_candidates, 0) if n_candidates > 1 else state
         try:
             return super().sample_actions(images, img_masks, lang_tokens, lang_masks, action_prefix, delay, noise,
-                                          None, n_candidates, accel, frozen)
+                                          None, n_candidates, accel, frozen, prefix_kwargs)
         finally:
             self._state = None
 

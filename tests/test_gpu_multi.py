@@ -63,3 +63,64 @@ def test_peer_memory_step_matches_nccl_step():
     for x, y in zip(na, nb):
         assert abs(x - y) / max(1e-6, abs(x)) < 2e-2
     torch.testing.assert_close(fa[:n], fb[:n], rtol=2e-2, atol=2e-3)
+
+
+def _tp_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from opentau_b200 import ops
+        from opentau_b200.models.layers import DecoderLayer, TowerConfig
+        from opentau_b200.ops import cuda_ops
+        from opentau_b200.parallel.tp import TensorParallel, TPDecoderLayer
+        torch.manual_seed(0)
+        cfg = TowerConfig(hidden_size=512, num_hidden_layers=1, num_attention_heads=8, num_key_value_heads=2,
+                          head_dim=64, intermediate_size=1024, vocab_size=64, hidden_act="silu", qk_norm=True,
+                          norm_unit_offset=False)
+        layer = DecoderLayer(cfg, 0).to(dev).to(torch.bfloat16)
+        B, S, d = 4, 160, 512
+        x = torch.randn(B, S, d, device=dev).to(torch.bfloat16)
+        dist.broadcast(x, 0)
+        for p in layer.parameters():
+            dist.broadcast(p.data, 0)
+        pos = torch.arange(S, device=dev)[None].expand(B, S)
+        blk = (torch.arange(S, device=dev, dtype=torch.int32) // 40)[None].expand(B, S).contiguous()
+        valid = torch.ones(B, S, dtype=torch.bool, device=dev)
+        cs = ops.rope_angles(pos, cfg.head_dim, cfg.rope_theta)
+        with torch.no_grad():
+            h = layer.input_layernorm(x)[0]
+            q, k, v = layer.self_attn.qkv(h)
+            q, k = ops.rope(q, *cs), ops.rope(k, *cs)
+            att = ops.block_attention(q, k, v, blk, blk, valid, valid, cfg.attn_scale)
+            y = layer.self_attn.o_proj(att, residual=x)
+            want = layer.mlp(layer.post_attention_layernorm(y)[0], residual=y).view(B * S, d)
+            tp = TensorParallel(dev, backend="p2p", wait_budget=4_000_000_000)
+            tpl = TPDecoderLayer(layer, tp)
+            Ml = B * S // world
+            x_local = x.view(B * S, d)[rank * Ml:(rank + 1) * Ml].contiguous()
+            errs = []
+            for _ in range(4):                       # several steps: both parities of every workspace are reused
+                got, _, _ = tpl(x_local, B, S, cs, blk, valid)
+                errs.append(float((got.float() - want[rank * Ml:(rank + 1) * Ml].float()).abs().max()))
+            torch.cuda.synchronize()
+            cuda_ops.check_status()
+        allerr = [None] * world
+        dist.all_gather_object(allerr, max(errs))
+        if rank == 0:
+            ret["tp_err"] = max(allerr)
+            ret["tp_scale"] = float(want.float().abs().max())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_tensor_parallel_layer_matches_unsharded_layer():
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_tp_worker, args=(2, 29900 + os.getpid() % 90, ret), nprocs=2, join=True)
+    assert ret["tp_err"] < 0.03 * max(1.0, ret["tp_scale"])
