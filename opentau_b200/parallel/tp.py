@@ -8,9 +8,10 @@ is where a B200 box wants it.  Layout (Megatron sequence parallelism):
     x_local [M/W, d] --norm--> all-gather + column-parallel GEMM (qkv | gate_up) --> [M, n/W]
                      --attention on the local heads / GLU--> row-parallel GEMM + reduce-scatter --> [M/W, d]
 
-Both collectives run INSIDE the GEMM kernels (``ops/csrc/gemm_dist_tcgen05.cu``): the all-gather is a set of
-TMA loads from the owning rank's memory, the reduce-scatter is the epilogue storing partial tiles into the
-destination rank's staging buffer plus an in-kernel reduction.  ``torch.distributed`` is used to exchange IPC
+Both collectives run INSIDE the GEMM kernels (``ops/csrc/gemm_dist_tcgen05.cu``): for the all-gather a copier
+warp per CTA pulls the peers' rows over NVLink once (bulk async copies) while the tensor cores already work on
+the rows that have landed; for the reduce-scatter the epilogue sends partial tiles with TMA stores into the
+destination rank's staging buffer and the kernel's tail reduces them.  ``torch.distributed`` is used to exchange IPC
 handles once, and as the CPU / fallback data path (``backend="dist"``), which is also the baseline the fused
 kernels are measured against.
 
@@ -45,6 +46,9 @@ class _Site:
             self.numel = Ml * width                      # one parity of the activation shard [Ml, K]
             self.data = ctx._alloc(2 * self.numel * 2)
             self.sync = ctx._alloc(4 * MAX_RANKS, zero=True)   # ready[src]
+            # private to this rank: the gathered rows and the piece counters / dispenser of the copier warps
+            self.gathered = torch.empty(W * Ml, width, dtype=torch.bfloat16, device=ctx.device)
+            self.gcount = torch.zeros(W * ((Ml + 127) // 128) + 1, dtype=torch.int32, device=ctx.device)
         else:
             self.numel = W * Ml * width                  # one parity of the staging [W, Ml, N]
             self.data = ctx._alloc(2 * self.numel * 2)
@@ -90,8 +94,10 @@ class TensorParallel:
         self._bufs.append(buf)
         return buf
 
-    def _site(self, kind: str, Ml: int, width: int) -> _Site:
-        key = (kind, Ml, width)
+    def _site(self, kind: str, Ml: int, width: int, other: int) -> _Site:
+        """Workspace of one call shape.  The in-kernel counters count monotonically and assume that every step on
+        a site launches the same grid, so the key holds the complete GEMM shape."""
+        key = (kind, Ml, width, other)
         if key not in self._sites:
             self._sites[key] = _Site(self, kind, Ml, width)
         return self._sites[key]
@@ -116,10 +122,10 @@ class TensorParallel:
         return w[:, self.rank * per:(self.rank + 1) * per].contiguous()
 
     # -- all-gather -> GEMM -----------------------------------------------------------------------------
-    def ag_buffer(self, Ml: int, K: int) -> Tensor:
+    def ag_buffer(self, Ml: int, K: int, N: int) -> Tensor:
         """The peer-visible ``[Ml, K]`` buffer the NEXT :meth:`all_gather_linear` of this shape reads; writing
         the activation straight into it (e.g. as a norm kernel's output) saves the staging copy."""
-        site = self._site("ag", Ml, K)
+        site = self._site("ag", Ml, K, N)
         return site.local((site.epoch + 1) & 1).view(Ml, K)
 
     def all_gather_linear(self, x_local: Tensor, w: Tensor, bias: Tensor | None = None) -> Tensor:
@@ -136,7 +142,7 @@ class TensorParallel:
             from .. import ops
             return ops.linear(x, w, bias)
         from ..ops import cuda_ops
-        site = self._site("ag", Ml, K)
+        site = self._site("ag", Ml, K, N)
         site.epoch += 1
         par = site.epoch & 1
         buf = site.local(par).view(Ml, K)
@@ -149,9 +155,10 @@ class TensorParallel:
         out = torch.empty(self.world * Ml, N, dtype=torch.bfloat16, device=self.device)
         rc = self.lib.otb_ag_gemm_bf16(
             _ptr_array(site.data_ptrs(par)), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(Ml), c_int(N),
-            c_int(K), c_longlong(K), c_longlong(w.stride(0)), c_longlong(N),
-            c_void_p(bias.data_ptr() if bias is not None else 0), c_void_p(site.sync.local_ptr), c_int(self.rank),
-            c_int(self.world), c_uint(site.epoch), c_longlong(self.wait_budget), c_void_p(self.status), self._stream())
+            c_int(K), c_longlong(w.stride(0)), c_longlong(N), c_void_p(bias.data_ptr() if bias is not None else 0),
+            c_void_p(site.sync.local_ptr), c_void_p(site.gathered.data_ptr()), c_void_p(site.gcount.data_ptr()),
+            c_int(self.rank), c_int(self.world), c_uint(site.epoch), c_longlong(self.wait_budget),
+            c_void_p(self.status), self._stream())
         if rc != 0:
             raise RuntimeError(f"all-gather GEMM launch failed ({rc})")
         cuda_ops.launch_count += 2
@@ -179,7 +186,7 @@ class TensorParallel:
                 part = part + bias
             return part + residual if residual is not None else part
         from ..ops import cuda_ops
-        site = self._site("rs", Ml, N)
+        site = self._site("rs", Ml, N, Kl)
         site.epoch += 1
         par = site.epoch & 1
         x = x if x.is_contiguous() else x.contiguous()

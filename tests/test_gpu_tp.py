@@ -32,18 +32,26 @@ def test_all_gather_gemm_emulated(world, Ml, N, K, bias):
     a = [torch.randn(Ml, K, device=dev).to(torch.bfloat16) for _ in range(world)]
     ws = [(torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16) for _ in range(world)]
     b = torch.randn(N, device=dev).to(torch.bfloat16) if bias else None
-    ready = torch.full((MAXR,), 3, device=dev, dtype=torch.int32)      # every source already published step 3
+    ready = torch.full((MAXR,), 2, device=dev, dtype=torch.int32)      # every source already published 2 steps
     status = c_void_p(cuda_ops.status_pointer())
     full = torch.cat(a, 0).float()
+    nblk = (Ml + 127) // 128
     for r in range(world):
-        out = torch.zeros(world * Ml, N, device=dev, dtype=torch.bfloat16)
-        rc = lib.otb_ag_gemm_bf16(_arr(a), c_void_p(ws[r].data_ptr()), c_void_p(out.data_ptr()), c_int(Ml), c_int(N),
-                                  c_int(K), c_longlong(K), c_longlong(K), c_longlong(N),
-                                  c_void_p(b.data_ptr() if bias else 0), c_void_p(ready.data_ptr()), c_int(r),
-                                  c_int(world), c_uint(3), c_longlong(BUDGET), status, _stream())
-        assert rc == 0
-        want = full @ ws[r].float().t() + (b.float() if bias else 0)
-        torch.testing.assert_close(out.float(), want, atol=3e-2, rtol=2e-2)
+        gathered = torch.zeros(world * Ml, K, device=dev, dtype=torch.bfloat16)
+        gcount = torch.zeros(world * nblk + 1, device=dev, dtype=torch.int32)
+        for epoch in (1, 2):                                           # the piece counters keep counting
+            out = torch.zeros(world * Ml, N, device=dev, dtype=torch.bfloat16)
+            rc = lib.otb_ag_gemm_bf16(_arr(a), c_void_p(ws[r].data_ptr()), c_void_p(out.data_ptr()), c_int(Ml),
+                                      c_int(N), c_int(K), c_longlong(K), c_longlong(N),
+                                      c_void_p(b.data_ptr() if bias else 0), c_void_p(ready.data_ptr()),
+                                      c_void_p(gathered.data_ptr()), c_void_p(gcount.data_ptr()), c_int(r),
+                                      c_int(world), c_uint(epoch), c_longlong(BUDGET), status, _stream())
+            assert rc == 0
+            want = full @ ws[r].float().t() + (b.float() if bias else 0)
+            torch.testing.assert_close(out.float(), want, atol=3e-2, rtol=2e-2)
+        others = [x for i, x in enumerate(a) if i != r]
+        got = torch.cat([gathered[i * Ml:(i + 1) * Ml] for i in range(world) if i != r], 0)
+        assert torch.equal(got, torch.cat(others, 0))                  # every peer row crossed exactly as is
     cuda_ops.check_status()
 
 
@@ -101,11 +109,13 @@ def test_all_gather_gemm_gives_up_on_a_source_that_never_publishes():
     w = torch.zeros(128, 64, device=dev, dtype=torch.bfloat16)
     out = torch.zeros(256, 128, device=dev, dtype=torch.bfloat16)
     ready = torch.zeros(MAXR, device=dev, dtype=torch.int32)
+    gathered = torch.zeros(256, 64, device=dev, dtype=torch.bfloat16)
+    gcount = torch.zeros(3, device=dev, dtype=torch.int32)
     cuda_ops.check_status()
     rc = lib.otb_ag_gemm_bf16(_arr(a), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(128), c_int(128),
-                              c_int(64), c_longlong(64), c_longlong(64), c_longlong(128), c_void_p(0),
-                              c_void_p(ready.data_ptr()), c_int(0), c_int(2), c_uint(1), c_longlong(2_000_000),
-                              c_void_p(cuda_ops.status_pointer()), _stream())
+                              c_int(64), c_longlong(64), c_longlong(128), c_void_p(0), c_void_p(ready.data_ptr()),
+                              c_void_p(gathered.data_ptr()), c_void_p(gcount.data_ptr()), c_int(0), c_int(2),
+                              c_uint(1), c_longlong(2_000_000), c_void_p(cuda_ops.status_pointer()), _stream())
     assert rc == 0
     with pytest.raises(RuntimeError, match="timed out"):
         cuda_ops.check_status()
