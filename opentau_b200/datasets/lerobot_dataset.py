@@ -1,0 +1,736 @@
+"""LeRobot-format datasets: metadata, random-access reader (codebase v2.0 / v2.1 / v3.0) and v2.1 recorder.
+
+Behaviour follows the reference (``src/opentau/datasets/lerobot_dataset.py:184-3321``):
+
+* rows are addressed by a global frame index over the selected episodes; per-feature *delta timestamps* turn
+  into soft (fractional) row offsets at the dataset's fps, clipped to the episode with ``<key>_is_pad`` flags, and
+  are resampled ``nearest`` or ``linear`` (vectors only);
+* camera frames come from parquet-embedded images or from mp4 files (decoded on OpenCV here);
+* ``_to_standard_data_format`` renames features to ``camera{i} / state / actions / prompt / response``, resizes
+  images with padding to the pipeline resolution, applies column indices and delta actions, zero-pads vectors to
+  ``max_state_dim / max_action_dim``, emits the pad masks, optional keys with their dropout rolls, bf16 floats and
+  provenance.
+
+The table backend is pyarrow (all parquet files of the selected episodes are concatenated into one in-memory
+table; numeric columns are materialised as torch tensors once), not HF ``datasets``.
+"""
+
+from __future__ import annotations
+
+import functools
+import io
+import logging
+import random
+import shutil
+from pathlib import Path
+from typing import Any, Callable
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from .. import ops
+from .action_indexing import apply_column_index, apply_delta_actions
+from .compute_stats import aggregate_stats, compute_episode_stats, sample_indices
+from .standard_data_format_mapping import get_mapping
+from .utils import (CODEBASE_VERSION, DEFAULT_CHUNK_SIZE, DEFAULT_FEATURES, DEFAULT_IMAGE_PATH, DEFAULT_PARQUET_PATH,
+                    DEFAULT_VIDEO_PATH, EPISODES_PATH, EPISODES_STATS_PATH, INFO_PATH, TASKS_PATH, append_jsonlines,
+                    check_version_compatibility, get_episode_data_index, get_version, load_episodes,
+                    load_episodes_stats, load_info, load_stats, load_tasks, serialize_stats, validate_frame,
+                    write_json)
+from .video_utils import decode_video_frames, encode_video_frames
+
+HF_HOME = Path.home() / ".cache" / "huggingface" / "lerobot"
+
+
+def retry_random_on_failure(fn: Callable) -> Callable:
+    """``__getitem__`` decorator: on a decode / IO failure, retry a few random indices before giving up."""
+
+    @functools.wraps(fn)
+    def wrapped(self, idx):
+        n = int(getattr(self, "_getitem_retries", 3))
+        last: Exception | None = None
+        for attempt in range(n + 1):
+            try:
+                return fn(self, idx)
+            except (OSError, ValueError, RuntimeError, KeyError) as e:  # noqa: PERF203
+                last = e
+                if attempt == n or not getattr(self, "retry_on_failure", True):
+                    break
+                logging.warning("sample %s of %s failed (%s); retrying a random index", idx,
+                                getattr(self, "repo_id", "?"), e)
+                idx = random.randrange(len(self))
+        raise last  # type: ignore[misc]
+
+    return wrapped
+
+
+class LeRobotDatasetMetadata:
+    def __init__(self, repo_id: str, root: str | Path | None = None, revision: str | None = None):
+        self.repo_id = repo_id
+        self.root = Path(root) if root is not None else HF_HOME / repo_id
+        self.revision = revision
+        if not (self.root / INFO_PATH).exists():
+            raise FileNotFoundError(
+                f"dataset {repo_id!r} not found under {self.root} (no network here: place the dataset on disk and "
+                "pass `root`)")
+        self.load_metadata()
+
+    def load_metadata(self) -> None:
+        self.info = load_info(self.root)
+        self.version = get_version(self.info)
+        check_version_compatibility(self.repo_id, self.version)
+        self.tasks, self.task_to_task_index = load_tasks(self.root, self.version)
+        self.episodes = load_episodes(self.root, self.version)
+        self.stats = load_stats(self.root, self.version)
+        self.episodes_stats = load_episodes_stats(self.root) if self.version == "v2.1" else {}
+        self.advantages: dict | None = None
+        adv = self.root / "meta" / "advantages.json"
+        if adv.exists():
+            import json
+            raw = json.loads(adv.read_text())
+            self.advantages = {(int(k.split(",")[0]), float(k.split(",")[1])): float(v) for k, v in raw.items()}
+
+    # -- simple views ---------------------------------------------------------------------------------
+    @property
+    def fps(self) -> int:
+        return int(self.info["fps"])
+
+    @property
+    def features(self) -> dict[str, dict]:
+        return self.info["features"]
+
+    @property
+    def robot_type(self) -> str | None:
+        return self.info.get("robot_type")
+
+    @property
+    def control_mode(self) -> str | None:
+        return self.info.get("control_mode")
+
+    @property
+    def image_keys(self) -> list[str]:
+        return [k for k, ft in self.features.items() if ft["dtype"] == "image"]
+
+    @property
+    def video_keys(self) -> list[str]:
+        return [k for k, ft in self.features.items() if ft["dtype"] == "video"]
+
+    @property
+    def camera_keys(self) -> list[str]:
+        return [k for k, ft in self.features.items() if ft["dtype"] in ("image", "video")]
+
+    @property
+    def names(self) -> dict[str, Any]:
+        return {k: ft.get("names") for k, ft in self.features.items()}
+
+    @property
+    def shapes(self) -> dict[str, tuple]:
+        return {k: tuple(ft["shape"]) for k, ft in self.features.items()}
+
+    @property
+    def total_episodes(self) -> int:
+        return int(self.info["total_episodes"])
+
+    @property
+    def total_frames(self) -> int:
+        return int(self.info["total_frames"])
+
+    @property
+    def total_tasks(self) -> int:
+        return int(self.info.get("total_tasks", len(self.tasks)))
+
+    @property
+    def chunks_size(self) -> int:
+        return int(self.info.get("chunks_size", DEFAULT_CHUNK_SIZE))
+
+    def get_episode_chunk(self, ep_index: int) -> int:
+        return ep_index // self.chunks_size
+
+    def get_data_file_path(self, ep_index: int) -> Path:
+        if self.version == "v3.0":
+            ep = self.episodes[ep_index]
+            return Path(self.info["data_path"].format(chunk_index=ep["data/chunk_index"], file_index=ep["data/file_index"]))
+        return Path(self.info.get("data_path", DEFAULT_PARQUET_PATH).format(
+            episode_chunk=self.get_episode_chunk(ep_index), episode_index=ep_index))
+
+    def get_video_file_path(self, ep_index: int, vid_key: str) -> Path:
+        if self.version == "v3.0":
+            ep = self.episodes[ep_index]
+            return Path(self.info["video_path"].format(video_key=vid_key, chunk_index=ep[f"videos/{vid_key}/chunk_index"],
+                                                       file_index=ep[f"videos/{vid_key}/file_index"]))
+        return Path(self.info.get("video_path", DEFAULT_VIDEO_PATH).format(
+            episode_chunk=self.get_episode_chunk(ep_index), video_key=vid_key, episode_index=ep_index))
+
+    def video_time_offset(self, ep_index: int, vid_key: str) -> float:
+        """v3.0 packs several episodes into one video file; the episode starts at this timestamp."""
+        if self.version == "v3.0":
+            return float(self.episodes[ep_index].get(f"videos/{vid_key}/from_timestamp", 0.0))
+        return 0.0
+
+    def get_task_index(self, task: str) -> int | None:
+        return self.task_to_task_index.get(task)
+
+    # -- writing (v2.1) ---------------------------------------------------------------------------------
+    def add_task(self, task: str) -> int:
+        if task in self.task_to_task_index:
+            raise ValueError(f"The task '{task}' already exists and can't be added twice.")
+        idx = self.info["total_tasks"]
+        self.task_to_task_index[task] = idx
+        self.tasks[idx] = task
+        self.info["total_tasks"] += 1
+        append_jsonlines({"task_index": idx, "task": task}, self.root / TASKS_PATH)
+        return idx
+
+    def save_episode(self, episode_index: int, length: int, tasks: list[str], stats: dict) -> None:
+        self.info["total_episodes"] += 1
+        self.info["total_frames"] += length
+        chunk = self.get_episode_chunk(episode_index)
+        if chunk >= self.info["total_chunks"]:
+            self.info["total_chunks"] += 1
+        self.info["splits"] = {"train": f"0:{self.info['total_episodes']}"}
+        self.info["total_videos"] += len(self.video_keys)
+        write_json(_jsonable_info(self.info), self.root / INFO_PATH)
+        ep = {"episode_index": episode_index, "tasks": tasks, "length": length}
+        self.episodes[episode_index] = ep
+        append_jsonlines(ep, self.root / EPISODES_PATH)
+        self.episodes_stats[episode_index] = stats
+        self.stats = aggregate_stats([self.stats, stats]) if self.stats else stats
+        append_jsonlines({"episode_index": episode_index, "stats": serialize_stats(stats)},
+                         self.root / EPISODES_STATS_PATH)
+
+    @classmethod
+    def create(cls, repo_id: str, fps: int, root: str | Path | None = None, robot_type: str | None = None,
+               features: dict | None = None, use_videos: bool = True) -> "LeRobotDatasetMetadata":
+        obj = cls.__new__(cls)
+        obj.repo_id = repo_id
+        obj.root = Path(root) if root is not None else HF_HOME / repo_id
+        obj.root.mkdir(parents=True, exist_ok=False)
+        if features is None:
+            raise ValueError("Dataset features must be provided explicitly.")
+        feats = {k: dict(v) for k, v in {**features, **DEFAULT_FEATURES}.items()}
+        for ft in feats.values():
+            ft["shape"] = tuple(ft["shape"])
+            if ft["dtype"] in ("image", "video"):
+                ft["dtype"] = "video" if use_videos else "image"
+        obj.info = {"codebase_version": CODEBASE_VERSION, "robot_type": robot_type, "total_episodes": 0,
+                    "total_frames": 0, "total_tasks": 0, "total_videos": 0, "total_chunks": 0,
+                    "chunks_size": DEFAULT_CHUNK_SIZE, "fps": fps, "splits": {}, "data_path": DEFAULT_PARQUET_PATH,
+                    "video_path": DEFAULT_VIDEO_PATH if use_videos else None, "features": feats}
+        obj.version = CODEBASE_VERSION
+        obj.revision = None
+        obj.tasks, obj.task_to_task_index, obj.episodes, obj.episodes_stats = {}, {}, {}, {}
+        obj.stats, obj.advantages = None, None
+        write_json(_jsonable_info(obj.info), obj.root / INFO_PATH)
+        return obj
+
+
+def _jsonable_info(info: dict) -> dict:
+    out = dict(info)
+    out["features"] = {k: {**ft, "shape": list(ft["shape"])} for k, ft in info["features"].items()}
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ base
+class BaseDataset(torch.utils.data.Dataset):
+    """Shared standard-format conversion (LeRobot and VQA datasets both end here)."""
+
+    def __init__(self, cfg, *, name_map: dict[str, str] | None = None, train: bool = True):
+        self.cfg = cfg
+        self.resolution = tuple(cfg.resolution)
+        self.num_cams = cfg.num_cams
+        self.max_state_dim, self.max_action_dim = cfg.max_state_dim, cfg.max_action_dim
+        self.action_chunk = cfg.action_chunk
+        self.n_obs_history = cfg.dataset_mixture.n_obs_history
+        self.train = train
+        self._name_map = name_map or {}
+        self.state_index: list[int] | None = None
+        self.action_index: list[int] | None = None
+        self.delta_action_state_map: dict | None = None
+        self._opt_rng = random.Random(0)
+
+    # hooks -------------------------------------------------------------------------------------------
+    def _get_name_map(self) -> dict[str, str]:
+        return self._name_map
+
+    def _get_feature_mapping_key(self) -> str:
+        return getattr(self, "repo_id", type(self).__name__)
+
+    @staticmethod
+    def pad_vector(v: Tensor, new_dim: int) -> Tensor:
+        if v.shape[-1] == new_dim:
+            return v
+        if v.shape[-1] > new_dim:
+            raise ValueError(f"vector of width {v.shape[-1]} does not fit into {new_dim}")
+        out = v.new_zeros(*v.shape[:-1], new_dim)
+        out[..., :v.shape[-1]] = v
+        return out
+
+    def _standardize_images(self, item: dict, out: dict, num_cams: int) -> list[bool]:
+        name_map = self._get_name_map()
+        H, W = self.resolution
+        pads: list[bool] = []
+        last = None
+        for i in range(num_cams):
+            raw = name_map.get(f"camera{i}")
+            if raw is not None and raw in item:
+                img = item[raw]
+                img = img.float()
+                if img.shape[-3] not in (1, 3) and img.shape[-1] in (1, 3):
+                    img = img.movedim(-1, -3)
+                lead = img.shape[:-3]
+                flat = img.reshape(-1, *img.shape[-3:])
+                if tuple(flat.shape[-2:]) != (H, W):
+                    flat = ops.resize_with_pad(flat, W, H, pad_value=0.0)
+                img = flat.reshape(*lead, *flat.shape[-3:])
+                out[f"camera{i}"] = img
+                last = img
+                pads.append(False)
+            else:
+                shape = last.shape if last is not None else (
+                    (self.n_obs_history, 3, H, W) if self.n_obs_history else (3, H, W))
+                out[f"camera{i}"] = torch.zeros(shape)
+                pads.append(True)
+        return pads
+
+    def _apply_column_index_and_delta(self, out: dict) -> None:
+        out["state"] = apply_column_index(out["state"], self.state_index)
+        out["actions"] = apply_column_index(out["actions"], self.action_index)
+        if self.delta_action_state_map:
+            out["actions"] = apply_delta_actions(out["actions"], out["state"], self.delta_action_state_map)
+
+    def _roll(self, p: float) -> bool:
+        """True = drop.  Dropout rolls are active in training (or when validation opts in)."""
+        if not self.train:
+            return False
+        return self._opt_rng.random() < p
+
+    def _emit_optional_keys(self, item: dict, out: dict) -> None:
+        mix = self.cfg.dataset_mixture
+        drop_all = self._roll(mix.metadata_drop_all_prob)
+        for key, dtype in (("speed", torch.long), ("quality", torch.long), ("mistake", torch.bool)):
+            raw = item.get(f"{key}_raw")
+            if raw is None:
+                continue
+            dropped = drop_all or self._roll(mix.metadata_drop_each_prob)
+            out[key] = torch.tensor(raw if not dropped else 0, dtype=dtype)
+            out[f"{key}_is_pad"] = torch.tensor(dropped, dtype=torch.bool)
+        for key in ("robot_type", "control_mode"):
+            if item.get(key) is not None:
+                out[key] = "" if drop_all else str(item[key])
+        if "memory_raw" in item:
+            out["memory"] = item["memory_raw"]
+            out["next_memory"] = item.get("next_memory_raw") or ""
+        if mix.emit_fps and "fps" in item:
+            out["fps"] = torch.tensor(int(item["fps"]), dtype=torch.long)
+        if out.get("response") and self._roll(mix.response_drop_prob):
+            out["response"] = ""
+        for k, v in item.items():
+            if k.startswith("subgoal") and isinstance(v, Tensor):
+                dropped = self._roll(mix.subgoal_drop_prob)
+                out[k] = v if not dropped else torch.zeros_like(v)
+                out[f"{k}_is_pad"] = torch.tensor(dropped, dtype=torch.bool)
+
+    def _to_standard_data_format(self, item: dict) -> dict:
+        name_map = self._get_name_map()
+        out: dict[str, Any] = {}
+        img_is_pad = self._standardize_images(item, out, self.num_cams)
+        for new_key, key in name_map.items():
+            if "camera" in new_key or new_key in ("mistake", "success") or key not in item:
+                continue
+            out[new_key] = item[key]
+        out.setdefault("response", "")
+        self._apply_column_index_and_delta(out)
+        real_action_dim = int(out["actions"].shape[-1])
+        if not 0 < real_action_dim <= self.max_action_dim:
+            raise ValueError(f"real action dim {real_action_dim} is outside (0, {self.max_action_dim}] "
+                             f"(dataset={getattr(self, 'repo_id', '?')})")
+        out["real_action_dim"] = torch.tensor(real_action_dim, dtype=torch.long)
+        out["state"] = self.pad_vector(out["state"].float(), self.max_state_dim)
+        out["actions"] = self.pad_vector(out["actions"].float(), self.max_action_dim)
+        out["img_is_pad"] = torch.tensor(img_is_pad, dtype=torch.bool)
+        a_key = name_map.get("actions", "actions")
+        out["action_is_pad"] = item.get(f"{a_key}_is_pad", torch.zeros(out["actions"].shape[0], dtype=torch.bool))
+        s_pad = item.get(f"{name_map.get('state', 'state')}_is_pad")
+        if s_pad is not None:
+            out["obs_history_is_pad"] = s_pad
+        elif self.n_obs_history is not None:
+            out["obs_history_is_pad"] = torch.zeros(self.n_obs_history, dtype=torch.bool)
+        else:
+            out["obs_history_is_pad"] = torch.tensor([False], dtype=torch.bool)
+        self._emit_optional_keys(item, out)
+        for k, v in out.items():
+            if isinstance(v, Tensor) and v.dtype.is_floating_point:
+                out[k] = v.to(torch.bfloat16)
+        out["source"] = self._get_feature_mapping_key()
+        for k in ("episode_index", "frame_index"):
+            v = item.get(k)
+            out[k] = int(v.item() if torch.is_tensor(v) else v) if v is not None else -1
+        return out
+
+
+# ------------------------------------------------------------------------------------------------ reader
+class LeRobotDataset(BaseDataset):
+    def __init__(self, cfg, repo_id: str, root: str | Path | None = None, episodes: list[int] | None = None,
+                 image_transforms: Callable | None = None, delta_timestamps: dict[str, list[float]] | None = None,
+                 tolerance_s: float = 1e-4, revision: str | None = None, video_backend: str | None = None,
+                 image_resample_strategy: str = "nearest", vector_resample_strategy: str = "nearest",
+                 standardize: bool = True, dataset_cfg=None, train: bool = True, meta: LeRobotDatasetMetadata | None = None):
+        self.repo_id = repo_id
+        self.meta = meta or LeRobotDatasetMetadata(repo_id, root, revision)
+        self.root = self.meta.root
+        dcfg = dataset_cfg
+        name_map = get_mapping(repo_id, self.meta.features, getattr(dcfg, "data_features_name_mapping", None))
+        super().__init__(cfg, name_map=name_map, train=train)
+        self.episodes = sorted(episodes) if episodes is not None else sorted(self.meta.episodes)
+        self.image_transforms = image_transforms
+        self.delta_timestamps = {k: np.asarray(v, dtype=np.float64) for k, v in (delta_timestamps or {}).items()}
+        self.tolerance_s = tolerance_s
+        self.video_backend = video_backend
+        if image_resample_strategy not in ("nearest", "linear") or vector_resample_strategy not in ("nearest", "linear"):
+            raise ValueError("resample strategies must be 'nearest' or 'linear'")
+        self.image_resample_strategy, self.vector_resample_strategy = image_resample_strategy, vector_resample_strategy
+        self.standardize = standardize
+        self.retry_on_failure = True
+        if dcfg is not None:
+            self.state_index, self.action_index = dcfg.state_index, dcfg.action_index
+            if dcfg.use_delta_joint_actions:
+                self.delta_action_state_map = dcfg.delta_action_state_map
+            self.prompt_substitutions = dcfg.prompt_substitutions
+            self.robot_type = dcfg.robot_type if dcfg.robot_type is not None else self.meta.robot_type
+            self.control_mode = dcfg.control_mode if dcfg.control_mode is not None else self.meta.control_mode
+        else:
+            self.prompt_substitutions, self.robot_type, self.control_mode = None, self.meta.robot_type, self.meta.control_mode
+        self._load_table()
+        self.episode_data_index = get_episode_data_index(self.meta.episodes, self.episodes)
+        self.epi2idx = {ep: i for i, ep in enumerate(self.episodes)}
+        self.speed_raw_by_episode = {ep: int(self.meta.episodes[ep].get("speed", 0) or 0) for ep in self.episodes}
+
+    # -- table ------------------------------------------------------------------------------------------
+    def _load_table(self) -> None:
+        import pyarrow as pa
+        import pyarrow.parquet as pq
+        files: list[Path] = []
+        for ep in self.episodes:
+            f = self.root / self.meta.get_data_file_path(ep)
+            if f not in files:
+                files.append(f)
+        tables = [pq.read_table(f) for f in files]
+        table = pa.concat_tables(tables, promote_options="default") if len(tables) > 1 else tables[0]
+        ep_col = np.asarray(table.column("episode_index").to_numpy())
+        keep = np.isin(ep_col, np.asarray(self.episodes))
+        if not keep.all():
+            table = table.filter(pa.array(keep))
+        order = np.lexsort((np.asarray(table.column("frame_index").to_numpy()),
+                            np.asarray(table.column("episode_index").to_numpy())))
+        if not (order == np.arange(len(order))).all():
+            table = table.take(pa.array(order))
+        self._table = table
+        self._numeric: dict[str, Tensor] = {}
+        self._image_cols: list[str] = []
+        self._string_cols: list[str] = []
+        for name in table.column_names:
+            ft = self.meta.features.get(name)
+            if ft is not None and ft["dtype"] == "image":
+                self._image_cols.append(name)
+                continue
+            if ft is not None and ft["dtype"] == "string" or pa.types.is_string(table.schema.field(name).type):
+                self._string_cols.append(name)
+                continue
+            col = table.column(name).to_numpy(zero_copy_only=False)
+            if col.dtype == object:
+                col = np.stack([np.asarray(x) for x in col])
+            self._numeric[name] = torch.from_numpy(np.ascontiguousarray(col))
+
+    def __len__(self) -> int:
+        return self._table.num_rows
+
+    @property
+    def num_frames(self) -> int:
+        return len(self)
+
+    @property
+    def num_episodes(self) -> int:
+        return len(self.episodes)
+
+    @property
+    def fps(self) -> int:
+        return self.meta.fps
+
+    @property
+    def features(self) -> dict[str, dict]:
+        return self.meta.features
+
+    # -- queries ----------------------------------------------------------------------------------------
+    def _soft_indices(self, idx: int, ep_idx: int) -> tuple[dict[str, np.ndarray], dict[str, Tensor]]:
+        i = self.epi2idx[ep_idx]
+        ep_start, ep_end = int(self.episode_data_index["from"][i]), int(self.episode_data_index["to"][i])
+        q, pad = {}, {}
+        for key, dts in self.delta_timestamps.items():
+            d = dts * self.fps
+            q[key] = np.clip(idx + d, ep_start, ep_end - 1)
+            pad[f"{key}_is_pad"] = torch.from_numpy((idx + d < ep_start - 1e-9) | (idx + d > ep_end - 1 + 1e-9))
+        return q, pad
+
+    def _query_vectors(self, soft: dict[str, np.ndarray]) -> dict[str, Tensor]:
+        out = {}
+        for key, s in soft.items():
+            if key not in self._numeric:
+                continue
+            col = self._numeric[key]
+            if self.vector_resample_strategy == "nearest" or not col.dtype.is_floating_point:
+                out[key] = col[torch.from_numpy(np.round(s).astype(np.int64))]
+            else:
+                lo = np.floor(s).astype(np.int64)
+                hi = np.minimum(lo + 1, len(col) - 1)
+                w = torch.from_numpy(s - lo).to(col.dtype)
+                while w.dim() < col[lo].dim():
+                    w = w.unsqueeze(-1)
+                out[key] = col[torch.from_numpy(lo)] * (1 - w) + col[torch.from_numpy(hi)] * w
+        return out
+
+    def _decode_image_cell(self, cell) -> Tensor:
+        from PIL import Image
+        if isinstance(cell, dict):
+            raw = cell.get("bytes")
+            img = Image.open(io.BytesIO(raw)) if raw is not None else Image.open(self.root / cell["path"])
+        else:
+            img = Image.open(io.BytesIO(cell))
+        arr = np.asarray(img.convert("RGB"))
+        return torch.from_numpy(arr).permute(2, 0, 1).float() / 255.0
+
+    def _query_images(self, idx: int, soft: dict[str, np.ndarray]) -> dict[str, Tensor]:
+        out = {}
+        for key in self._image_cols:
+            rows = np.round(soft[key]).astype(np.int64).tolist() if key in soft else [idx]
+            col = self._table.column(key)
+            out[key] = torch.stack([self._decode_image_cell(col[r].as_py()) for r in rows])
+            if key not in soft:
+                out[key] = out[key][0]
+        return out
+
+    def _query_videos(self, idx: int, ep_idx: int, soft: dict[str, np.ndarray]) -> dict[str, Tensor]:
+        out = {}
+        ep_start = int(self.episode_data_index["from"][self.epi2idx[ep_idx]])
+        for key in self.meta.video_keys:
+            if key in soft:
+                ts = (np.round(soft[key]) if self.image_resample_strategy == "nearest" else soft[key]) - ep_start
+                ts = (ts / self.fps).tolist()
+            else:
+                ts = [float(self._numeric["timestamp"][idx])]
+            off = self.meta.video_time_offset(ep_idx, key)
+            frames = decode_video_frames(self.root / self.meta.get_video_file_path(ep_idx, key),
+                                         [t + off for t in ts], max(self.tolerance_s, 0.5 / self.fps), self.video_backend,
+                                         fps=float(self.fps))
+            out[key] = frames if key in soft else frames[0]
+        return out
+
+    def _resolve_task(self, task_index: int) -> str:
+        task = self.meta.tasks.get(int(task_index), "")
+        subs = self.prompt_substitutions
+        allow = self.train or self.cfg.dataset_mixture.val_enable_prompt_substitution
+        if subs and allow and task in subs:
+            return self._opt_rng.choice(subs[task])
+        return task
+
+    def _load_subgoal_frames(self, ep_idx: int, frame_in_ep: int) -> dict[str, Tensor]:
+        """Goal frames for datasets that declare subtask segments (``episodes[ep]["segments"] = [[start, end], ..]``):
+        the frame at the end of the current segment, or with probability ``subgoal_end_of_segment_prob`` ... a
+        uniformly drawn later frame of the segment."""
+        segs = self.meta.episodes[ep_idx].get("segments")
+        if not segs:
+            return {}
+        seg = next(((s, e) for s, e in segs if s <= frame_in_ep < e), None)
+        if seg is None:
+            return {}
+        mix = self.cfg.dataset_mixture
+        end = seg[1] - 1
+        if self.train and self._opt_rng.random() >= mix.subgoal_end_of_segment_prob and end > frame_in_ep:
+            end = self._opt_rng.randint(frame_in_ep + 1, end)
+        gidx = int(self.episode_data_index["from"][self.epi2idx[ep_idx]]) + end
+        out = {}
+        imgs = {**self._query_images(gidx, {}), **(self._query_videos(gidx, ep_idx, {}) if self.meta.video_keys else {})}
+        H, W = self.resolution
+        for i in range(self.num_cams):
+            raw = self._name_map.get(f"camera{i}")
+            if raw in imgs:
+                im = imgs[raw][None]
+                if tuple(im.shape[-2:]) != (H, W):
+                    im = ops.resize_with_pad(im, W, H, pad_value=0.0)
+                out[f"subgoal{i}"] = im[0]
+        return out
+
+    @retry_random_on_failure
+    def __getitem__(self, idx: int) -> dict:
+        idx = int(idx)
+        if not 0 <= idx < len(self):
+            raise IndexError(idx)
+        item: dict[str, Any] = {k: v[idx] for k, v in self._numeric.items()}
+        for k in self._string_cols:
+            item[k] = self._table.column(k)[idx].as_py()
+        ep_idx = int(item["episode_index"])
+        soft, padding = self._soft_indices(idx, ep_idx) if self.delta_timestamps else ({}, {})
+        item.update(padding)
+        item.update(self._query_vectors(soft))
+        item.update(self._query_images(idx, soft))
+        if self.meta.video_keys:
+            item.update(self._query_videos(idx, ep_idx, soft))
+        if self.image_transforms is not None:
+            for cam in self.meta.camera_keys:
+                if cam in item:
+                    item[cam] = self.image_transforms(item[cam])
+        item["task"] = self._resolve_task(int(item["task_index"]))
+        for key, dts in self.delta_timestamps.items():
+            if len(dts) == 1 and key in item and isinstance(item[key], Tensor):
+                item[key] = item[key].squeeze(0)
+        if not self.standardize:
+            return item
+        i = self.epi2idx[ep_idx]
+        ep_start, ep_end = int(self.episode_data_index["from"][i]), int(self.episode_data_index["to"][i])
+        frame_in_ep = idx - ep_start
+        item["frame_index"] = frame_in_ep
+        ep_info = self.meta.episodes[ep_idx]
+        item.setdefault("response", "")
+        if "memory" in item:
+            item["memory_raw"] = str(item["memory"])
+        success = ep_info.get("success")
+        if "mistake" in item:
+            item["mistake_raw"] = bool(item["mistake"])
+        if ep_info.get("quality") is not None:
+            item["quality_raw"] = int(ep_info["quality"])
+        item["speed_raw"] = self.speed_raw_by_episode[ep_idx] if "speed" in ep_info else None
+        item["robot_type"], item["control_mode"], item["fps"] = self.robot_type, self.control_mode, self.fps
+        item.update(self._load_subgoal_frames(ep_idx, frame_in_ep))
+        timestamp = float(item["timestamp"])
+        out = self._to_standard_data_format(item)
+        adv = 0.0 if self.meta.advantages is None else self.meta.advantages.get((ep_idx, timestamp), 0.0)
+        out["advantage"] = torch.tensor(adv, dtype=torch.bfloat16)
+        success = True if success is None else bool(success)
+        policy = getattr(self.cfg, "policy", None)
+        rc = getattr(policy, "reward_config", None)
+        if rc is not None and getattr(policy, "type", "") == "value":
+            from ..policies.value.reward import calculate_return_bins_with_equal_width
+            b, r = calculate_return_bins_with_equal_width(success, rc.number_of_bins, ep_end, rc.reward_normalizer, idx,
+                                                          rc.C_neg)
+            out["return_bin_idx"] = torch.tensor(b, dtype=torch.long)
+            out["return_continuous"] = torch.tensor(r, dtype=torch.float32)
+        else:
+            out["return_bin_idx"] = torch.tensor(0, dtype=torch.long)
+            out["return_continuous"] = torch.tensor(0, dtype=torch.float32)
+        if out["actions"].shape[0] != self.action_chunk or out["action_is_pad"].shape[0] != self.action_chunk:
+            raise ValueError(f"action chunk of {out['actions'].shape[0]} steps, expected {self.action_chunk}")
+        return out
+
+    # -- recording API (v2.1) ---------------------------------------------------------------------------
+    @classmethod
+    def create(cls, repo_id: str, fps: int, root: str | Path | None = None, robot_type: str | None = None,
+               features: dict | None = None, use_videos: bool = False, image_writer_threads: int = 0) -> "LeRobotRecorder":
+        meta = LeRobotDatasetMetadata.create(repo_id, fps, root, robot_type, features, use_videos)
+        return LeRobotRecorder(meta, image_writer_threads)
+
+
+class LeRobotRecorder:
+    """Frame-by-frame recording into the v2.1 layout: ``add_frame`` buffers, ``save_episode`` writes the parquet file,
+    images or encoded videos, per-episode stats and the metadata records."""
+
+    def __init__(self, meta: LeRobotDatasetMetadata, image_writer_threads: int = 0):
+        self.meta, self.root, self.fps = meta, meta.root, meta.fps
+        self.features = meta.features
+        self.image_writer = None
+        if image_writer_threads > 0:
+            from .image_writer import AsyncImageWriter
+            self.image_writer = AsyncImageWriter(num_threads=image_writer_threads)
+        self.episode_buffer = self.create_episode_buffer()
+
+    def create_episode_buffer(self, episode_index: int | None = None) -> dict:
+        idx = self.meta.total_episodes if episode_index is None else episode_index
+        return {**{k: [] for k in self.features}, "size": 0, "task": [], "episode_index": idx}
+
+    def _image_path(self, key: str, ep: int, frame: int) -> Path:
+        return self.root / DEFAULT_IMAGE_PATH.format(image_key=key, episode_index=ep, frame_index=frame)
+
+    def add_frame(self, frame: dict) -> None:
+        frame = {k: (v.numpy() if isinstance(v, Tensor) else v) for k, v in frame.items()}
+        validate_frame(frame, self.features)
+        buf = self.episode_buffer
+        fi = buf["size"]
+        buf["frame_index"].append(fi)
+        buf["timestamp"].append(frame.pop("timestamp", fi / self.fps))
+        buf["task"].append(frame.pop("task"))
+        for k, v in frame.items():
+            if self.features[k]["dtype"] in ("image", "video"):
+                path = self._image_path(k, buf["episode_index"], fi)
+                if self.image_writer is not None:
+                    self.image_writer.save_image(v, path)
+                else:
+                    from .image_writer import write_image
+                    write_image(np.asarray(v), path)
+                buf[k].append(str(path))
+            else:
+                buf[k].append(np.asarray(v))
+        buf["size"] += 1
+
+    def save_episode(self) -> None:
+        import pyarrow as pa
+        import pyarrow.parquet as pq
+        buf = self.episode_buffer
+        n, ep = buf["size"], buf["episode_index"]
+        if n == 0:
+            raise ValueError("You must add one or several frames with `add_frame` before calling `save_episode`.")
+        tasks = buf["task"]
+        for t in dict.fromkeys(tasks):
+            if self.meta.get_task_index(t) is None:
+                self.meta.add_task(t)
+        if self.image_writer is not None:
+            self.image_writer.wait_until_done()
+        cols: dict[str, Any] = {}
+        stats_in: dict[str, np.ndarray] = {}
+        start = self.meta.total_frames
+        for k, ft in self.features.items():
+            if k == "index":
+                arr = np.arange(start, start + n)
+            elif k == "episode_index":
+                arr = np.full(n, ep)
+            elif k == "task_index":
+                arr = np.asarray([self.meta.get_task_index(t) for t in tasks])
+            elif ft["dtype"] in ("image", "video"):
+                paths = buf[k]
+                from PIL import Image
+                sel = sample_indices(n)
+                stats_in[k] = np.stack([np.asarray(Image.open(paths[i]).convert("RGB"), dtype=np.float32).transpose(2, 0, 1) / 255.0
+                                        for i in sel])
+                if ft["dtype"] == "image":
+                    cols[k] = pa.array([{"bytes": Path(p).read_bytes(), "path": None} for p in paths],
+                                       type=pa.struct([("bytes", pa.binary()), ("path", pa.string())]))
+                continue
+            elif ft["dtype"] == "string":
+                cols[k] = pa.array([str(x) for x in buf[k]])
+                continue
+            else:
+                arr = np.stack(buf[k]) if len(buf[k]) else np.zeros((0,))
+            arr = np.asarray(arr).astype(ft["dtype"])
+            stats_in[k] = arr
+            cols[k] = pa.array(arr.tolist() if arr.ndim > 1 else arr)
+        path = self.root / self.meta.get_data_file_path(ep)
+        path.parent.mkdir(parents=True, exist_ok=True)
+        pq.write_table(pa.table(cols), path)
+        for k in self.meta.video_keys:
+            encode_video_frames(self._image_path(k, ep, 0).parent, self.root / self.meta.get_video_file_path(ep, k),
+                                self.fps, overwrite=True)
+        stats = compute_episode_stats(stats_in, self.features)
+        self.meta.save_episode(ep, n, list(dict.fromkeys(tasks)), stats)
+        img_dir = self.root / "images"
+        if img_dir.exists():
+            shutil.rmtree(img_dir)
+        self.episode_buffer = self.create_episode_buffer()
+
+    def clear_episode_buffer(self) -> None:
+        img_dir = self.root / "images"
+        if img_dir.exists():
+            shutil.rmtree(img_dir)
+        self.episode_buffer = self.create_episode_buffer()
+
+    def stop_image_writer(self) -> None:
+        if self.image_writer is not None:
+            self.image_writer.stop()
+            self.image_writer = None
