@@ -1,0 +1,370 @@
+"""``opentau-train``: the training loop.
+
+Same stages and user-visible behaviour as the reference trainer (``src/opentau/scripts/train.py:708-1609``) —
+config validation, one process per GPU, rank-0 output directory broadcast, seeding with a per-rank offset, dataset
+mixture (+ validation split), policy construction with normalisation heads from the mixture statistics, bf16
+weights with fp32 masters, gradient accumulation, weighted loss assembly, clipping, cosine schedule, per-step
+metric gathers, periodic logging / checkpoints (with pruning, running-best retention and an interrupted-save
+tripwire) / validation (bucketed per normalisation head and per dataset) / simulated-environment evaluation, and
+resume.  What differs is the machinery underneath: :class:`~opentau_b200.parallel.engine.TrainEngine` owns flat
+bf16 parameter / gradient buffers, sharded fp32 masters and the fused gradient-reduce + AdamW + parameter-gather
+kernels over peer memory, instead of accelerate's DDP / DeepSpeed / FSDP wrappers.
+
+Run one process per GPU::
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m opentau_b200.scripts.train --config_path=cfg.json --steps=1000
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import time
+from pathlib import Path
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from ..configs import parser
+from ..configs.train import TrainPipelineConfig
+from ..datasets.factory import make_dataset_mixture, warn_if_resumed_split_differs
+from ..datasets.utils import cycle
+from ..parallel import control
+from ..parallel.engine import OptimHyper, TrainEngine, assemble_weighted_loss
+from ..policies.factory import make_policy
+from ..utils.logging_utils import AverageMeter, MetricsTracker, format_big_number, init_logging
+from ..utils.random_utils import set_seed
+from ..utils.train_utils import (RunningBestTracker, checkpoint_is_complete, get_step_checkpoint_dir,
+                                 get_step_identifier, load_training_state, prune_checkpoints, save_checkpoint,
+                                 update_last_checkpoint)
+
+CHECKPOINTS_DIR = "checkpoints"
+LAST_LINK = "last"
+
+
+# ---------------------------------------------------------------------------------------------- helpers
+def init_distributed() -> tuple[int, int, torch.device]:
+    """Joins the process group described by the launcher's environment (``RANK`` / ``WORLD_SIZE`` / ...)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local % torch.cuda.device_count())
+        device = torch.device("cuda", local % torch.cuda.device_count())
+    else:
+        device = torch.device("cpu")
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if device.type == "cuda":
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+    return rank, world, device
+
+
+def to_device(batch: dict[str, Any], device: torch.device) -> dict[str, Any]:
+    return {k: (v.to(device, non_blocking=True) if isinstance(v, Tensor) else v) for k, v in batch.items()}
+
+
+class WandBLogger:
+    """Thin tracker: wandb when enabled and importable (offline mode works without network), else a JSONL file."""
+
+    def __init__(self, cfg: TrainPipelineConfig, out_dir: Path, is_main: bool):
+        self.run = None
+        self.file = None
+        if not is_main:
+            return
+        self.file = open(out_dir / "metrics.jsonl", "a")
+        w = cfg.wandb
+        if getattr(w, "enable", False):
+            try:
+                import wandb
+                os.environ.setdefault("WANDB_MODE", getattr(w, "mode", None) or "offline")
+                self.run = wandb.init(project=getattr(w, "project", None) or "opentau", entity=getattr(w, "entity", None),
+                                      name=getattr(w, "name", None) or out_dir.name, dir=str(out_dir),
+                                      config=cfg.to_dict(), resume="allow" if cfg.resume else None,
+                                      id=getattr(w, "run_id", None))
+            except Exception as e:  # noqa: BLE001 - logging must never stop a run
+                logging.warning("wandb disabled: %s", e)
+
+    def log(self, metrics: dict[str, float], step: int) -> None:
+        if self.file is not None:
+            import json
+            self.file.write(json.dumps({"step": step, **{k: float(v) for k, v in metrics.items()}}) + "\n")
+            self.file.flush()
+        if self.run is not None:
+            self.run.log(metrics, step=step, commit=True)
+
+    def finish(self) -> None:
+        if self.file is not None:
+            self.file.close()
+        if self.run is not None:
+            self.run.finish()
+
+
+def bucket_per_sample(per_sample: dict[str, Tensor], dataset_index: Tensor, names: list[str]) -> dict[str, dict[str, float]]:
+    """Groups per-sample ``(sum, count)`` losses by normalisation head: exact masked means per group."""
+    out: dict[str, dict[str, float]] = {}
+    for i, name in enumerate(names):
+        sel = dataset_index == i
+        if not bool(sel.any()):
+            continue
+        row = {}
+        for key in ("MSE", "CE"):
+            s, c = per_sample[f"{key}_sum"][sel].sum(), per_sample[f"{key}_count"][sel].sum()
+            row[key] = float(s / c.clamp(min=1))
+            row[f"{key}_count"] = float(c)
+        row["n"] = float(sel.sum())
+        out[name] = row
+    return out
+
+
+def mixture_weighted_aggregate(buckets: dict[str, dict[str, float]], weights: dict[str, float]) -> dict[str, float]:
+    """Validation losses weighted like the training mixture, over the heads that actually occurred."""
+    tot = sum(weights.get(k, 0.0) for k in buckets) or 1.0
+    return {key: sum(weights.get(k, 0.0) * b[key] for k, b in buckets.items()) / tot for key in ("MSE", "CE")}
+
+
+@torch.no_grad()
+def run_validation(policy, loader, n_batches: int, device, names: list[str], weights: dict[str, float],
+                   loss_weights: dict[str, float]) -> dict[str, float]:
+    policy.eval()
+    acc: dict[str, list[Tensor]] = {k: [] for k in ("MSE_sum", "MSE_count", "CE_sum", "CE_count", "idx")}
+    it = iter(loader)
+    for _ in range(n_batches):
+        try:
+            batch = to_device(next(it), device)
+        except StopIteration:
+            break
+        out = policy(batch, return_per_sample=True)
+        for key in ("MSE", "CE"):
+            ps = out.get(f"{key}_per_sample")
+            B = batch["state"].shape[0]
+            s, c = ps if ps is not None else (torch.zeros(B, device=device), torch.zeros(B, device=device))
+            acc[f"{key}_sum"].append(s.float()), acc[f"{key}_count"].append(c.float())
+        acc["idx"].append(batch.get("dataset_index", torch.zeros(batch["state"].shape[0], dtype=torch.long, device=device)))
+    policy.train()
+    if not acc["idx"]:
+        return {}
+    flat = control.gather_tensors({k: torch.cat(v) for k, v in acc.items()})
+    buckets = bucket_per_sample(flat, flat["idx"], names)
+    metrics: dict[str, float] = {}
+    for name, row in buckets.items():
+        metrics[f"Validation/{name}/MSE Loss"] = row["MSE"]
+        metrics[f"Validation/{name}/CE Loss"] = row["CE"]
+    agg = mixture_weighted_aggregate(buckets, weights)
+    metrics["Validation/MSE Loss"], metrics["Validation/CE Loss"] = agg["MSE"], agg["CE"]
+    metrics["Validation/Loss"] = loss_weights.get("MSE", 1.0) * agg["MSE"] + loss_weights.get("CE", 1.0) * agg["CE"]
+    return metrics
+
+
+def update_policy(engine: TrainEngine, batches: list[dict[str, Any]]) -> dict[str, Tensor]:
+    """One optimizer step over ``len(batches)`` micro-batches (gradient accumulation)."""
+    sums: dict[str, Tensor] = {}
+    for b in batches:
+        out = engine.forward_backward(b)
+        for k, v in out.items():
+            sums[k] = sums.get(k, 0) + v.float() / len(batches)
+    sums["grad_norm"] = engine.optimizer_step().float()
+    return sums
+
+
+# ---------------------------------------------------------------------------------------------- main
+def train(cfg: TrainPipelineConfig) -> dict[str, float]:
+    rank, world, device = init_distributed()
+    is_main = rank == 0
+    init_logging(rank)
+    cfg.validate()
+    out_dir = Path(control.broadcast_object(str(cfg.output_dir)))
+    cfg.output_dir = str(out_dir)
+    if is_main:
+        out_dir.mkdir(parents=True, exist_ok=True)
+    control.wait_for_everyone()
+    if cfg.seed is not None:
+        set_seed(cfg.seed, rank)
+    tracker_wb = WandBLogger(cfg, out_dir, is_main)
+
+    # ---- data
+    res = make_dataset_mixture(cfg)
+    train_mix, val_mix = res if isinstance(res, tuple) else (res, None)
+    if is_main and val_mix is not None:
+        warn_if_resumed_split_differs(out_dir, {d.repo_id: list(getattr(d.dataset, "episodes", []))
+                                                for d in val_mix.datasets})
+    micro_bs = cfg.dataloader_batch_size or cfg.batch_size
+    ga = cfg.gradient_accumulation_steps
+    loader = train_mix.get_dataloader(micro_bs, cfg.num_workers, rank, world, cfg.prefetch_factor)
+    dl_iter = cycle(loader)
+
+    # ---- model
+    policy = make_policy(cfg.policy, ds_meta=train_mix.meta)
+    policy.to(device)
+    if device.type == "cuda":
+        policy.to(torch.bfloat16)
+    policy.train()
+    opt_cfg, sched_cfg = cfg.optimizer, cfg.scheduler
+    dcfg = cfg.distributed
+    clip = dcfg.gradient_clipping if dcfg.gradient_clipping is not None else getattr(opt_cfg, "grad_clip_norm", 10.0)
+    hyper = OptimHyper(lr=opt_cfg.lr, betas=tuple(getattr(opt_cfg, "betas", (0.9, 0.999))),
+                       eps=getattr(opt_cfg, "eps", 1e-8), weight_decay=getattr(opt_cfg, "weight_decay", 0.0),
+                       grad_clip_norm=clip)
+    lr_lambda = sched_cfg.lr_lambda(cfg.steps) if sched_cfg is not None else None
+    engine = TrainEngine(policy, hyper, device=device, lr_lambda=lr_lambda, loss_weights=cfg.loss_weighting,
+                         strategy=getattr(dcfg, "strategy", "zero2"), comm=getattr(dcfg, "comm", "auto"),
+                         grad_accum_steps=ga)
+    n_params = sum(p.numel() for p in policy.parameters())
+    n_train = sum(p.numel() for p in policy.parameters() if p.requires_grad)
+
+    # ---- resume
+    step = 0
+    ckpt_root = out_dir / CHECKPOINTS_DIR
+    if cfg.resume:
+        last = ckpt_root / LAST_LINK
+        if not last.exists():
+            raise FileNotFoundError(f"resume requested but {last} does not exist")
+        last = last.resolve()
+        if not checkpoint_is_complete(last, 1):
+            raise RuntimeError(f"checkpoint {last} is incomplete (interrupted save)")
+        from safetensors.torch import load_file
+        sd = load_file(str(last / "model.safetensors"))
+        missing, unexpected = policy.load_state_dict(type(policy)._fix_state_dict_keys(sd, cfg.policy), strict=False)
+        bad = [k for k in missing if "normalize" not in k]
+        if bad:
+            raise RuntimeError(f"checkpoint misses {len(bad)} tensors, e.g. {bad[:3]}")
+        step = load_training_state(last, engine, rank, world, cfg.seed)
+        engine.step_count = step
+        logging.info("resumed from %s at step %d", last, step)
+
+    best = RunningBestTracker(out_dir, cfg.running_best_count, cfg.running_best_metric) if cfg.running_best_count else None
+    names = list(train_mix.meta.dataset_names)
+    tot_w = float(sum(train_mix.weights)) or 1.0
+    head_w: dict[str, float] = {}
+    for n, w in zip(train_mix.names, train_mix.weights):
+        key = names[train_mix.meta.dataset_to_norm_index[n]]
+        head_w[key] = head_w.get(key, 0.0) + w / tot_w
+
+    if is_main:
+        logging.info("output dir: %s", out_dir)
+        logging.info("steps=%s  global batch=%d (micro %d x accumulation %d x ranks %d)", format_big_number(cfg.steps),
+                     micro_bs * ga * world, micro_bs, ga, world)
+        logging.info("dataset frames=%s  params=%s (trainable %s)  strategy=%s comm=%s",
+                     format_big_number(train_mix.num_frames), format_big_number(n_params), format_big_number(n_train),
+                     engine.strategy, engine.comm)
+
+    meters = {"loss": AverageMeter("loss", ":.3f"), "mse_loss": AverageMeter("mse", ":.3f"),
+              "ce_loss": AverageMeter("ce", ":.3f"), "grad_norm": AverageMeter("grdn", ":.3f"),
+              "lr": AverageMeter("lr", ":0.1e"), "update_s": AverageMeter("updt_s", ":.3f"),
+              "dataloading_s": AverageMeter("data_s", ":.3f")}
+    tracker = MetricsTracker(micro_bs * ga * world, train_mix.num_frames, None, meters, initial_step=step)
+    final: dict[str, float] = {}
+
+    # ---- hot loop
+    while step < cfg.steps:
+        t0 = time.perf_counter()
+        batches = [to_device(next(dl_iter), device) for _ in range(ga)]
+        tracker.dataloading_s = time.perf_counter() - t0
+        t1 = time.perf_counter()
+        out = update_policy(engine, batches)
+        gathered = control.gather_scalars({"loss": out["loss"], "MSE": out.get("MSE", torch.zeros(())),
+                                           "CE": out.get("CE", torch.zeros(())), "grad_norm": out["grad_norm"]},
+                                          device=device)
+        tracker.update_s = time.perf_counter() - t1
+        step += 1
+        tracker.step()
+        tracker.loss = float(gathered["loss"].mean())
+        tracker.mse_loss = float(gathered["MSE"].mean())
+        tracker.ce_loss = float(gathered["CE"].mean())
+        tracker.grad_norm = float(gathered["grad_norm"].mean())
+        tracker.lr = engine.current_lr()
+        if cfg.trace_nans and not all(map(lambda v: v == v, (tracker.loss.val, tracker.grad_norm.val))):
+            raise FloatingPointError(f"NaN at step {step}: loss={tracker.loss.val} grad_norm={tracker.grad_norm.val}")
+        final = {"loss": tracker.loss.val, "mse": tracker.mse_loss.val, "ce": tracker.ce_loss.val,
+                 "grad_norm": tracker.grad_norm.val}
+
+        is_log = cfg.log_freq > 0 and step % cfg.log_freq == 0
+        is_save = cfg.save_checkpoint and (step % cfg.save_freq == 0 or step == cfg.steps)
+        is_val = val_mix is not None and cfg.val_freq > 0 and step % cfg.val_freq == 0
+        is_eval = cfg.env is not None and cfg.eval_freq > 0 and step % cfg.eval_freq == 0
+        metrics: dict[str, float] = {}
+
+        if is_log:
+            if is_main:
+                logging.info(str(tracker))
+            d = tracker.to_dict()
+            metrics.update({"Training/Loss": d["loss"], "Training/MSE Loss": d["mse_loss"], "Training/CE Loss": d["ce_loss"],
+                            "Training/Learning Rate": d["lr"], "Training/Grad Norm": d["grad_norm"],
+                            "Training/Num Samples": float(tracker.samples)})
+            tracker.reset_averages()
+
+        if is_val:
+            vloader = val_mix.get_dataloader(micro_bs, 0, rank, world)
+            n_val = max(1, min(8, len(val_mix) // max(1, micro_bs * world)))
+            vm = run_validation(policy, vloader, n_val, device, names, head_w, cfg.loss_weighting)
+            metrics.update(vm)
+            if is_main and vm:
+                logging.info("validation @%d: loss %.4f (MSE %.4f, CE %.4f)", step, vm["Validation/Loss"],
+                             vm["Validation/MSE Loss"], vm["Validation/CE Loss"])
+
+        if is_eval:
+            from .eval import eval_policy_on_config
+            info = eval_policy_on_config(policy, cfg, device, rank=rank, world=world)
+            metrics["Success Rate"] = info["aggregated"]["pc_success"]
+            for g, v in info.get("per_group", {}).items():
+                metrics[f"Success/{g}"] = v["pc_success"]
+
+        if is_save:
+            control.wait_for_everyone()
+            ckpt = get_step_checkpoint_dir(out_dir, cfg.steps, step)
+            save_checkpoint(ckpt, step, cfg, policy, engine, rank=rank, is_main=is_main)
+            control.wait_for_everyone()
+            if is_main:
+                if not checkpoint_is_complete(ckpt, world):
+                    raise RuntimeError(f"checkpoint {ckpt} is incomplete after the save barrier")
+                update_last_checkpoint(ckpt)
+                keep = {ckpt.name}
+                if best is not None:
+                    keep |= best.kept()
+                if cfg.last_checkpoint_only:
+                    prune_checkpoints(out_dir, keep)
+                logging.info("checkpoint saved: %s", ckpt)
+
+        if best is not None and (is_val or is_eval) and metrics:
+            key = "Success Rate" if "Success Rate" in metrics and cfg.running_best_metric in ("auto", "success") \
+                else "Validation/Loss"
+            if key in metrics:
+                keep_it = control.broadcast_object(best.would_keep(metrics[key]) if is_main else None)
+                if keep_it:
+                    sid = get_step_identifier(step, cfg.steps)
+                    ckpt = get_step_checkpoint_dir(out_dir, cfg.steps, step)
+                    if not ckpt.exists():
+                        save_checkpoint(ckpt, step, cfg, policy, engine, rank=rank, is_main=is_main)
+                    control.wait_for_everyone()
+                    if is_main:
+                        best.update(sid, metrics[key])
+
+        if metrics and is_main:
+            tracker_wb.log(metrics, step)
+
+    control.wait_for_everyone()
+    tracker_wb.finish()
+    if is_main:
+        logging.info("End of training")
+    return final
+
+
+@parser.wrap()
+def train_main(cfg: TrainPipelineConfig):
+    return train(cfg)
+
+
+def main() -> None:
+    train_main()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
