@@ -71,7 +71,10 @@ def build_all(force: bool = False, verbose: bool = False) -> list[Path]:
         return list(ex.map(lambda n: build_one(n, force, verbose), names))
 
 
-if __name__ == "__main__":
-    libs = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    for p in libs:
+def main() -> None:
+    for p in build_all(force="--force" in sys.argv, verbose="-v" in sys.argv):
         print(p)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,43 @@
+"""Smoke inference: N timed ``sample_actions`` calls on a dummy observation
+(reference ``src/opentau/scripts/inference.py:44-136``)."""
+
+from __future__ import annotations
+
+import logging
+import time
+
+import torch
+
+from ..configs import parser
+from ..configs.train import TrainPipelineConfig
+from ..policies.factory import make_policy
+from ..utils.logging_utils import init_logging
+from ..utils.utils import auto_torch_device, create_dummy_observation
+
+
+@parser.wrap()
+def inference_main(cfg: TrainPipelineConfig, n: int = 10):
+    init_logging()
+    device = auto_torch_device()
+    policy = make_policy(cfg.policy).to(device)
+    if device.type == "cuda":
+        policy.to(torch.bfloat16)
+    policy.eval()
+    obs = create_dummy_observation(cfg, device)
+    times = []
+    with torch.inference_mode():
+        for i in range(n):
+            if device.type == "cuda":
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            actions = policy.sample_actions(obs)
+            if device.type == "cuda":
+                torch.cuda.synchronize()
+            times.append((time.perf_counter() - t0) * 1e3)
+            logging.info("call %d: %.2f ms, actions %s", i, times[-1], tuple(actions.shape))
+    logging.info("first %.2f ms; mean of the rest %.2f ms", times[0], sum(times[1:]) / max(1, len(times) - 1))
+    return times
+
+
+if __name__ == "__main__":
+    inference_main()
