@@ -1,0 +1,89 @@
+"""gRPC policy server on the loopback interface with a tiny pi0.5: chunk shape, request validation, streaming,
+health check, API-key enforcement, and wire compatibility of the hand-built message classes."""
+
+import numpy as np
+import pytest
+
+grpc = pytest.importorskip("grpc")
+
+from helpers import TINY  # noqa: E402
+from opentau_b200.configs.train import TrainPipelineConfig  # noqa: E402
+from opentau_b200.scripts.grpc import robot_inference_pb2 as pb  # noqa: E402
+from opentau_b200.scripts.grpc.client import PolicyClient  # noqa: E402
+from opentau_b200.scripts.grpc.server import RobotPolicyServicer, build_server  # noqa: E402
+
+
+def _cfg(path, **server):
+    return TrainPipelineConfig.from_dict({
+        "policy": {"type": "pi05", "pretrained_path": str(path), "chunk_size": 10, "n_action_steps": 10, "prompt_max_length": 24, "dropout": 0.0,
+                   "discrete_action_max_length": 8, "discrete_action_vocab_size": 256, "device": "cpu", "num_steps": 2,
+                   "max_delay": 3,
+                   "input_features": {"camera0": {"type": "VISUAL", "shape": [3, 224, 224]},
+                                      "state": {"type": "STATE", "shape": [32]}},
+                   "output_features": {"actions": {"type": "ACTION", "shape": [32]}}, **TINY},
+        "resolution": [224, 224], "num_cams": 1, "action_chunk": 10, "batch_size": 1,
+        "server": {"port": 50999, "warmup_requests": 1, **server}})
+
+
+@pytest.fixture()
+def running(tmp_path):
+    from helpers import tiny_pi05
+    tiny_pi05(num_steps=2, max_delay=3, prompt_max_length=24).save_pretrained(tmp_path / "ckpt")
+
+    def start(**server):
+        cfg = _cfg(tmp_path / "ckpt", **server)
+        svc = RobotPolicyServicer(cfg)
+        srv, port = build_server(cfg, svc, port=0)
+        srv.start()
+        started.append((srv, svc))
+        return port
+    started = []
+    yield start
+    for srv, svc in started:
+        srv.stop(0)
+        svc.infer.stop()
+
+
+def test_action_chunk_stream_and_health(running):
+    port = running()
+    c = PolicyClient(f"127.0.0.1:{port}")
+    h = c.health()
+    assert h.healthy and h.model_name == "pi05" and h.device == "cpu"
+    img = np.random.default_rng(0).integers(0, 255, (120, 160, 3), dtype=np.uint8)
+    chunk, resp = c.get_action_chunk([img], np.zeros(7), "pick up the block")
+    assert chunk.shape == (10, 32) and np.isfinite(chunk).all() and resp.inference_time_ms > 0 and resp.request_id
+    assert not resp.HasField("accel")
+    # real-time chunking: 3 leftover actions, 2 of them frozen
+    chunk2, _ = c.get_action_chunk([img], np.zeros(7), "pick up the block", prefix_action=chunk[:3], delay=2,
+                                   encoding="raw")
+    assert chunk2.shape == (10, 32)
+    outs = list(c.stream([c.make_request([img], np.zeros(7), "a"), c.make_request([img], np.zeros(7), "b", encoding="png")]))
+    assert len(outs) == 2 and outs[1][0].shape == (10, 32)
+    with pytest.raises(grpc.RpcError) as e:
+        c.get_action_chunk([], np.zeros(7), "no image")
+    assert e.value.code() == grpc.StatusCode.INVALID_ARGUMENT
+    with pytest.raises(grpc.RpcError) as e:
+        c.get_action_chunk([img], np.zeros(40), "state too wide")
+    assert e.value.code() == grpc.StatusCode.INVALID_ARGUMENT
+    c.close()
+
+
+def test_api_key_is_enforced(running):
+    port = running(api_key="s3cret")
+    img = np.zeros((64, 64, 3), np.uint8)
+    anon = PolicyClient(f"127.0.0.1:{port}")
+    assert anon.health().healthy                               # health stays open
+    with pytest.raises(grpc.RpcError) as e:
+        anon.get_action_chunk([img], np.zeros(4), "x")
+    assert e.value.code() == grpc.StatusCode.UNAUTHENTICATED
+    chunk, _ = PolicyClient(f"127.0.0.1:{port}", api_key="s3cret").get_action_chunk([img], np.zeros(4), "x")
+    assert chunk.shape == (10, 32)
+
+
+def test_wire_format_matches_the_proto_field_numbers():
+    r = pb.ObservationRequest(prompt="hi", delay=2, request_id="r")
+    r.robot_state.state.extend([1.0, 2.0])
+    raw = r.SerializeToString()
+    # field 3 (prompt) = tag 0x1a, field 5 (delay) = tag 0x28, field 7 (request_id) = tag 0x3a
+    assert b"\x1a\x02hi" in raw and b"\x28\x02" in raw and b"\x3a\x01r" in raw
+    assert pb.ObservationRequest.FromString(raw).robot_state.state == [1.0, 2.0]
