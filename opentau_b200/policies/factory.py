@@ -29,6 +29,8 @@ _POLICIES: dict[str, tuple[str, str, str]] = {
                         "opentau_b200.policies.pi07.high_level_planner.configuration_pi07_high_level"),
     "pi06": ("opentau_b200.policies.pi06.modeling_pi06", "PI06Policy",
              "opentau_b200.policies.pi06.configuration_pi06"),
+    "pi05_mem": ("opentau_b200.policies.pi05_mem.modeling_pi05_mem", "PI05MemPolicy",
+                 "opentau_b200.policies.pi05_mem.configuration_pi05_mem"),
     "value": ("opentau_b200.policies.value.modeling_value", "ValueFunction",
               "opentau_b200.policies.value.configuration_value"),
 }

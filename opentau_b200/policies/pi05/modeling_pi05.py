@@ -334,15 +334,17 @@ class PI05FlowMatching(nn.Module):
                 prefix_kwargs=None):
         cfg = self.config
         pwe = self.wrapper
-        prefix_embs, prefix_pad, prefix_att, _ = self.embed_prefix(
+        prefix_embs, prefix_pad, prefix_att, pos = self.embed_prefix(
             images, img_masks, lang_tokens, lang_masks, response_tokens, response_masks, discrete_actions,
             discrete_action_masks, state=state, **(prefix_kwargs or {}))
         blk, valid = ops.make_block_ids(prefix_pad, prefix_att)
-        pos = torch.cumsum(prefix_pad, dim=1) - 1
+        if pos is None:
+            pos = torch.cumsum(prefix_pad, dim=1) - 1
+        mrope = pos.dim() == 3          # (3, B, L): interleaved multimodal RoPE, else one scalar position per token
         n_disc = self.discrete_block_len() if discrete_actions is not None else 0
         n_cross = prefix_embs.shape[1] - n_disc
         (prefix_out, _), cache = pwe(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
-                                     q_valid=valid, fill_cache_len=n_cross)
+                                     q_valid=valid, fill_cache_len=n_cross, mrope=mrope)
 
         B = actions.shape[0]
         device = actions.device
@@ -361,12 +363,14 @@ class PI05FlowMatching(nn.Module):
 
         suffix_embs, suffix_pad, suffix_att, cond = self.embed_suffix(x_t, time2)
         s_blk, s_valid = ops.make_block_ids(suffix_pad, suffix_att)
-        offsets = prefix_pad[:, :n_cross].sum(-1, keepdim=True)
+        offsets = self.suffix_offset(pos, prefix_pad, n_cross)
         s_pos = offsets + torch.cumsum(suffix_pad, dim=1) - 1
+        if mrope:
+            s_pos = s_pos[None].expand(3, -1, -1)
         if cfg.knowledge_insulation:
             cache = cache.detach()
         (_, suffix_out), _ = pwe(inputs_embeds=[None, suffix_embs], position_ids=s_pos, q_blk=s_blk,
-                                 q_valid=s_valid, past=cache, adarms_cond=[None, cond])
+                                 q_valid=s_valid, past=cache, adarms_cond=[None, cond], mrope=mrope)
         v_t = self.action_out_proj(suffix_out[:, -cfg.chunk_size:]).float()
         mse = ops.flow_matching_masked_mse(u_t, v_t, frozen, actions_is_pad, real_action_dim, return_per_sample)
         mse_loss, mse_ps = mse if return_per_sample else (mse, None)
@@ -407,13 +411,26 @@ class PI05FlowMatching(nn.Module):
     def prefill(self, images, img_masks, lang_tokens, lang_masks, state=None,
                 prefix_kwargs=None) -> tuple[KVCache, Tensor]:
         """Prefix pass: returns the KV cache and the per-sample count of valid prefix tokens."""
-        prefix_embs, prefix_pad, prefix_att, _ = self.embed_prefix(images, img_masks, lang_tokens, lang_masks,
-                                                                   state=state, **(prefix_kwargs or {}))
+        prefix_embs, prefix_pad, prefix_att, pos = self.embed_prefix(images, img_masks, lang_tokens, lang_masks,
+                                                                     state=state, **(prefix_kwargs or {}))
         blk, valid = ops.make_block_ids(prefix_pad, prefix_att)
-        pos = torch.cumsum(prefix_pad, dim=1) - 1
+        if pos is None:
+            pos = torch.cumsum(prefix_pad, dim=1) - 1
+        self._mrope = pos.dim() == 3
         _, cache = self.wrapper(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
-                                              q_valid=valid, fill_cache_len=prefix_embs.shape[1])
-        return cache, prefix_pad.sum(-1, keepdim=True)
+                                              q_valid=valid, fill_cache_len=prefix_embs.shape[1], mrope=self._mrope)
+        return cache, self.suffix_offset(pos, prefix_pad, prefix_embs.shape[1])
+
+    @staticmethod
+    def suffix_offset(pos: Tensor, prefix_pad: Tensor, n_cross: int) -> Tensor:
+        """First position of the suffix, ``(B, 1)``: the count of real cached tokens for scalar positions; for
+        3-axis positions the largest position any real cached token uses, plus one (a video block compacts its
+        ``grid x grid`` patches into ``grid`` position units, so the token count would leave a gap)."""
+        if pos.dim() == 2:
+            return prefix_pad[:, :n_cross].sum(-1, keepdim=True)
+        cross = pos[:, :, :n_cross]
+        real = torch.where(prefix_pad[None, :, :n_cross], cross, torch.full_like(cross, -1))
+        return real.amax(dim=(0, 2))[:, None] + 1
 
     @torch.no_grad()
     def denoise_step(self, cache: KVCache, prefix_len: Tensor, x_t: Tensor, time: Tensor) -> Tensor:
@@ -421,9 +438,12 @@ class PI05FlowMatching(nn.Module):
         suffix_embs, suffix_pad, suffix_att, cond = self.embed_suffix(x_t, time)
         s_blk, s_valid = ops.make_block_ids(suffix_pad, suffix_att)
         s_pos = prefix_len + torch.cumsum(suffix_pad, dim=1) - 1
+        mrope = getattr(self, "_mrope", False)
+        if mrope:
+            s_pos = s_pos[None].expand(3, -1, -1)
         (_, suffix_out), _ = self.wrapper(
             inputs_embeds=[None, suffix_embs], position_ids=s_pos, q_blk=s_blk, q_valid=s_valid, past=cache,
-            adarms_cond=[None, cond])
+            adarms_cond=[None, cond], mrope=mrope)
         return self.action_out_proj(suffix_out[:, -self.config.chunk_size:]).float()
 
     def frozen_mask(self, delay: Tensor | int, batch: int, device) -> Tensor:
