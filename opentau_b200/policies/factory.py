@@ -31,6 +31,13 @@ _POLICIES: dict[str, tuple[str, str, str]] = {
              "opentau_b200.policies.pi06.configuration_pi06"),
     "pi05_mem": ("opentau_b200.policies.pi05_mem.modeling_pi05_mem", "PI05MemPolicy",
                  "opentau_b200.policies.pi05_mem.configuration_pi05_mem"),
+    "pi07_paligemma_low_level": ("opentau_b200.policies.pi07_paligemma.low_level.modeling_pi07_low_level",
+                                 "PI07PaligemmaLowLevelPolicy",
+                                 "opentau_b200.policies.pi07_paligemma.low_level.configuration_pi07_low_level"),
+    "pi07_paligemma_high_level_planner": (
+        "opentau_b200.policies.pi07_paligemma.high_level_planner.modeling_pi07_high_level",
+        "PI07PaligemmaHighLevelPlannerPolicy",
+        "opentau_b200.policies.pi07_paligemma.high_level_planner.configuration_pi07_high_level"),
     "value": ("opentau_b200.policies.value.modeling_value", "ValueFunction",
               "opentau_b200.policies.value.configuration_value"),
 }

@@ -114,12 +114,13 @@ class PaliGemmaWithExpertModel(nn.Module):
         vis = SiglipConfig(**{**dict(image_size=config.resize_imgs_with_padding[0]), **(config.vision or {})})
         self.vlm_cfg, self.expert_cfg, self.vision_cfg = vlm, exp, vis
         self.paligemma = _PaliGemma(vlm, vis)
-        self.gemma_expert = _GemmaExpert(exp)
+        no_expert = bool(getattr(config, "disable_action_expert", False))      # text-only users (planners)
+        self.gemma_expert = None if no_expert else _GemmaExpert(exp)
         self.discrete_action_embedding = nn.Embedding(config.discrete_action_vocab_size, vlm.hidden_size,
                                                       padding_idx=0)
         self.da_head = Linear(vlm.hidden_size, config.discrete_action_vocab_size, bias=True)
-        self.decoder = DualStreamDecoder([self.paligemma.language_model, self.gemma_expert.model],
-                                         dropout=config.dropout,
+        towers = [self.paligemma.language_model] + ([] if no_expert else [self.gemma_expert.model])
+        self.decoder = DualStreamDecoder(towers, dropout=config.dropout,
                                          gradient_checkpointing=config.gradient_checkpointing)
         self.set_requires_grad()
 
@@ -171,6 +172,10 @@ class PaliGemmaWithExpertModel(nn.Module):
         return self.discrete_action_embedding(actions)
 
     def forward(self, inputs_embeds, position_ids, q_blk, q_valid, **kw):
+        if len(self.decoder.towers) == 1:                   # expert disabled: callers still pass / unpack a pair
+            outs, cache = self.decoder([inputs_embeds[0]], position_ids, q_blk, q_valid, **{
+                k: ([v[0]] if k == "adarms_cond" and v is not None else v) for k, v in kw.items()})
+            return [outs[0], None], cache
         return self.decoder(inputs_embeds, position_ids, q_blk, q_valid, **kw)
 
 

@@ -31,6 +31,13 @@ class PI07HighLevelPlannerModel(nn.Module):
         super().__init__()
         self.config = config
         self.language_tokenizer = tokenizer
+        setattr(self, self.wrapper_attr, self.build_wrapper(config))
+        self.sync_branches = True
+        self._ids: dict[str, list[int]] = {}
+
+    wrapper_attr = "gemma3_with_expert"
+
+    def build_wrapper(self, config):
         vc = dict(config.vlm_config or {})
         wcfg = Gemma3WithExpertConfig(
             text={**vc.get("text", {}), **(config.vlm or {})}, vision={**vc.get("vision", {}), **(config.vision or {})},
@@ -38,13 +45,11 @@ class PI07HighLevelPlannerModel(nn.Module):
             freeze_vision_encoder=config.freeze_vision_encoder, dropout=config.dropout,
             gradient_checkpointing=config.gradient_checkpointing, disable_action_expert=True,
             discrete_action_vocab_size=8)
-        self.gemma3_with_expert = Gemma3WithExpertModel(wcfg)
-        self.sync_branches = True
-        self._ids: dict[str, list[int]] = {}
+        return Gemma3WithExpertModel(wcfg)
 
     @property
-    def wrapper(self) -> Gemma3WithExpertModel:
-        return self.gemma3_with_expert
+    def wrapper(self):
+        return getattr(self, self.wrapper_attr)
 
     def _indicator(self, text: str, B: int, device, max_len: int | None = None) -> tuple[Tensor, Tensor]:
         if text not in self._ids:
@@ -170,6 +175,12 @@ class PI07HighLevelPlannerModel(nn.Module):
 class PI07HighLevelPlannerPolicy(PreTrainedPolicy):
     config_class = PI07HighLevelPlannerConfig
     name = "pi07_high_level"
+    model_class = PI07HighLevelPlannerModel
+
+    @staticmethod
+    def _vocab_size(config) -> int:
+        vc = dict(config.vlm_config or {})
+        return gemma3_4b_config(**{**vc.get("text", {}), **(config.vlm or {})}).vocab_size
 
     def __init__(self, config: PI07HighLevelPlannerConfig, per_dataset_stats=None, dataset_names=None, **_):
         super().__init__(config)
@@ -181,10 +192,8 @@ class PI07HighLevelPlannerPolicy(PreTrainedPolicy):
                                           num_datasets=None if per_dataset_stats is not None else n_heads,
                                           zero_range_center=config.zero_range_centers_on_zero,
                                           eps=config.normalization_epsilon)
-        vc = dict(config.vlm_config or {})
-        vocab = gemma3_4b_config(**{**vc.get("text", {}), **(config.vlm or {})}).vocab_size
-        self.language_tokenizer = load_text_tokenizer(config.tokenizer_path, vocab)
-        self.model = PI07HighLevelPlannerModel(config, self.language_tokenizer)
+        self.language_tokenizer = load_text_tokenizer(config.tokenizer_path, self._vocab_size(config))
+        self.model = self.model_class(config, self.language_tokenizer)
 
     def reset(self) -> None:
         pass

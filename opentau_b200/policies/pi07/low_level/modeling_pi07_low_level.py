@@ -31,19 +31,25 @@ class PI07LowLevelFlowMatching(PI06FlowMatching):
     def __init__(self, config: PI07LowLevelConfig, tokenizer=None):
         super().__init__(config, tokenizer)
         w = self.wrapper
-        self.video_encoder = SpaceTimeSiglipVideoEncoder(w.gemma3.model.vision_tower, max_num_frames=max(
+        self.video_encoder = SpaceTimeSiglipVideoEncoder(self._tower(), max_num_frames=max(
             1, config.n_obs_steps), spacetime_layer_stride=config.spacetime_layer_stride)
         # registering the encoder must not duplicate the tower's parameters in state_dict
         self.video_encoder._modules.pop("vision")
-        object.__setattr__(self.video_encoder, "vision", w.gemma3.model.vision_tower)
+        object.__setattr__(self.video_encoder, "vision", self._tower())
         self.state_proj = Linear(config.max_state_dim, w.vlm_cfg.hidden_size, bias=True)
         self.sync_branches = True
 
     # -- pieces -------------------------------------------------------------------------------------
+    def _tower(self):
+        return self.wrapper.gemma3.model.vision_tower
+
+    def _projector(self):
+        return self.wrapper.gemma3.model.multi_modal_projector
+
     def embed_video(self, video: Tensor, frame_valid: Tensor | None) -> Tensor:
         """``video (B,T,C,H,W)`` -> projected current-frame tokens ``(B, tokens, d)``."""
         feats = self.video_encoder(video, frame_valid)
-        return self.wrapper.gemma3.model.multi_modal_projector(feats)
+        return self._projector()(feats)
 
     def _text(self, text: str, B: int, device) -> Tensor:
         return self._embed_indicator(text, B, device)

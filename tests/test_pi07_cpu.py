@@ -125,3 +125,35 @@ def test_branch_decisions_two_ranks(diverge):
         assert all(str(ret[r]).startswith("raised") and "metadata" in str(ret[r]) for r in (0, 1))
     else:
         assert ret[0] == ret[1] == (True, False)      # rank 1's "some real entries" wins on both ranks
+
+
+def test_paligemma_variants_share_the_pi07_logic():
+    """The legacy PaliGemma controller / planner: same behaviour, ``paligemma_with_expert`` checkpoint keys."""
+    torch.manual_seed(0)
+    ll = make_policy(make_policy_config(
+        "pi07_paligemma_low_level", n_obs_steps=3, chunk_size=10, n_action_steps=10, prompt_max_length=16,
+        discrete_action_max_length=8, discrete_action_vocab_size=256, dropout=0.0, device="cpu",
+        metadata_max_length=12, response_max_length=8, spacetime_layer_stride=2, input_features=dict(FEATS),
+        output_features=dict(OUT), **TINY), per_dataset_stats=[identity_stats()])
+    b = _history_batch()
+    b["response"] = ["grasp the cup", "", "move left", "open"]
+    out = ll(b)
+    (out["MSE"] + out["CE"]).backward()
+    keys = set(ll.state_dict())
+    assert any(k.startswith("model.paligemma_with_expert.paligemma.") for k in keys)
+    assert not any("gemma3" in k or "video_encoder" in k for k in keys)
+    ll.eval()
+    assert ll.sample_actions(b).shape == (4, 10, 32)
+    renamed = {k.replace("paligemma_with_expert", "gemma3_with_expert"): v for k, v in ll.state_dict().items()}
+    assert set(type(ll)._fix_state_dict_keys(renamed, ll.config)) == keys
+
+    hl = make_policy(make_policy_config(
+        "pi07_paligemma_high_level_planner", prompt_max_length=16, memory_max_length=6, response_max_length=5,
+        device="cpu", dropout=0.0, input_features=dict(FEATS), vlm=TINY["vlm"], vision=TINY["vision"]))
+    hb = tiny_batch()
+    hb["next_memory"], hb["response"] = ["cup grasped"] * 4, ["lift the cup"] * 4
+    o = hl(hb)
+    o["CE"].backward()
+    assert o["CE"].item() > 0 and not any("gemma_expert" in n for n, _ in hl.named_parameters())
+    mem, sub = hl.plan(hb)
+    assert len(mem) == 4 and len(sub) == 4
