@@ -1,0 +1,65 @@
+"""PerGroupLinear, outlier detection, master-weight optimizer."""
+
+import torch
+
+from opentau_b200.optim.master_weights import MasterWeightOptimizer
+from opentau_b200.policies.layers import PerGroupLinear, promote_linear_state
+from opentau_b200.policies.outlier_utils import detect_state_action_outliers, log_outlier_records
+
+
+def test_per_group_linear_routes_each_sample_to_its_group():
+    torch.manual_seed(0)
+    m = PerGroupLinear(6, 4, 3)
+    x = torch.randn(5, 7, 6)
+    idx = torch.tensor([2, 0, 2, 1, 0])
+    y = m(x, idx)
+    for b in range(5):
+        want = torch.nn.functional.linear(x[b], m.weight[idx[b]], m.bias[idx[b]])
+        assert torch.allclose(y[b], want, atol=1e-6)
+    y.sum().backward()
+    assert m.weight.grad[1].abs().sum() > 0
+    one = PerGroupLinear(6, 4, 1)
+    assert torch.allclose(one(x), torch.nn.functional.linear(x, one.weight[0], one.bias[0]), atol=1e-6)
+    lin = torch.nn.Linear(6, 4)
+    sd = promote_linear_state({"p.weight": lin.weight.data, "p.bias": lin.bias.data}, "p", 3)
+    assert sd["p.weight"].shape == (3, 4, 6) and torch.equal(sd["p.weight"][2], lin.weight.data)
+
+
+def test_outlier_detection_respects_padding_and_reports_provenance():
+    st = torch.zeros(2, 3, 4)
+    st[0, 0, 1] = 99.0            # padded history step: ignored
+    st[1, 2, 3] = 50.0            # current frame: reported
+    ac = torch.zeros(2, 5, 4)
+    ac[0, 4, 0] = -70.0           # padded action step: ignored
+    ac[0, 1, 2] = 40.0
+    batch = {"state": st, "actions": ac, "obs_history_is_pad": torch.tensor([[True, False, False]] * 2),
+             "action_is_pad": torch.tensor([[False] * 4 + [True]] * 2), "dataset_repo_id": ["a", "b"],
+             "episode_index": torch.tensor([7, 8]), "frame_index": torch.tensor([70, 80])}
+    recs = detect_state_action_outliers(batch, 32.0)
+    got = {(r["key"], r["source"], r["dim"]): r for r in recs}
+    assert set(got) == {("state", "b", 3), ("actions", "a", 2)}
+    assert got[("state", "b", 3)]["value"] == 50.0 and got[("state", "b", 3)]["episode"] == 8
+    assert detect_state_action_outliers(batch, None) == [] and detect_state_action_outliers(batch, 100.0) == []
+    seen: set = set()
+    assert log_outlier_records(recs, 32.0, seen) == 2 and log_outlier_records(recs, 32.0, seen) == 0
+
+
+def test_master_weights_keep_small_updates_that_bf16_would_lose():
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.ones(64, dtype=torch.bfloat16))
+    opt = MasterWeightOptimizer([p], lambda ms: torch.optim.SGD(ms, lr=1e-3))
+    for _ in range(20):                       # each step moves by 1e-3: below bf16 resolution at 1.0 (2^-8)
+        p.grad = torch.ones_like(p)
+        opt.step()
+        opt.zero_grad()
+    assert abs(float(opt.masters[0][0]) - 0.98) < 1e-5 and float(p[0]) < 1.0
+    q = torch.nn.Parameter(torch.ones(64, dtype=torch.bfloat16))
+    naive = torch.optim.SGD([q], lr=1e-3)
+    for _ in range(20):
+        q.grad = torch.ones_like(q)
+        naive.step()
+    assert float(q[0]) == 1.0                 # the plain bf16 update rounds away
+    p.grad = torch.full_like(p, 100.0)
+    assert float(opt.clip_grad_norm_(1.0)) > 1.0
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
