@@ -1,0 +1,184 @@
+"""Context parallelism: block-causal attention over a sequence that is sharded across the ranks of one node.
+
+The reference has no sequence / context parallelism (its longest-context tool is a single-GPU sweep,
+``src/opentau/scripts/benchmark_flash_attn.py:329-388``); the pi0.7 configuration with 16 frames x 3 cameras
+(12 288 vision tokens per sample) is where one GPU's activations and attention time stop being comfortable.
+
+Layout: every rank holds a contiguous ``Sl = S / W`` slice of each sample's tokens and computes q/k/v for it.  The
+forward pass is ONE kernel per rank (``ops/csrc/attention_cp_tcgen05.cu``): copier CTAs pull all ranks' K/V shards
+over NVLink into a local gathered buffer exactly once, in ring order starting with the own shard, while the
+attention CTAs (tcgen05 / TMEM flash attention) consume key blocks as they land.  Block ids / validity of ALL keys
+are an input on every rank (they derive from the batch layout, which is replicated), in source-major order.
+
+The backward pass gathers ``q / dO / LSE / delta`` with the library all-gather and runs the single-GPU backward
+kernels on the gathered tensors (dQ for the local queries against all keys, dK/dV for the local keys against all
+queries) — exact, deterministic, and without a reduction across ranks.
+
+``backend="dist"`` (CPU / gloo, and the baseline the fused kernel is measured against) all-gathers K/V with the
+library and calls the ordinary attention op.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+MAX_RANKS = 8
+DEFAULT_WAIT_BUDGET = 20_000_000_000
+
+
+def _ptr_array(ptrs: list[int]):
+    return (c_void_p * MAX_RANKS)(*[c_void_p(p) for p in ptrs], *[c_void_p(0)] * (MAX_RANKS - len(ptrs)))
+
+
+class _Site:
+    def __init__(self, ctx: "ContextParallel", B: int, Sl: int, Hkv: int, D: int):
+        W = ctx.world
+        self.numel = B * Sl * Hkv * D
+        self.k = ctx._alloc(2 * self.numel * 2)            # two parities of this rank's K shard
+        self.v = ctx._alloc(2 * self.numel * 2)
+        self.ready = ctx._alloc(4 * MAX_RANKS, zero=True)
+        self.kg = torch.empty(W * self.numel, dtype=torch.bfloat16, device=ctx.device)
+        self.vg = torch.empty(W * self.numel, dtype=torch.bfloat16, device=ctx.device)
+        bn = int(ctx.lib.otb_attn_cp_block(c_int(D)))
+        self.gcount = torch.zeros(W * B * ((Sl + bn - 1) // bn) + 1, dtype=torch.int32, device=ctx.device)
+        self.epoch = 0
+
+    def ptrs(self, buf, parity: int) -> list[int]:
+        return [p + parity * self.numel * 2 for p in buf.peer_ptrs]
+
+    def local(self, buf, parity: int) -> Tensor:
+        return buf.view(torch.bfloat16, 2 * self.numel)[parity * self.numel:(parity + 1) * self.numel]
+
+
+class ContextParallel:
+    def __init__(self, device, group=None, backend: str = "auto", num_copiers: int = 16,
+                 wait_budget: int = DEFAULT_WAIT_BUDGET):
+        self.device = torch.device(device)
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > MAX_RANKS:
+            raise ValueError(f"context parallelism spans at most {MAX_RANKS} ranks of one node")
+        if backend == "auto":
+            backend = "p2p" if self.device.type == "cuda" else "dist"
+        self.backend, self.num_copiers, self.wait_budget = backend, num_copiers, wait_budget
+        self._sites: dict[tuple, _Site] = {}
+        self._bufs: list = []
+        if backend == "p2p":
+            from ..ops import _lib, cuda_ops
+            self.lib = _lib.load("attention_cp_tcgen05")
+            self.comm_lib = _lib.load("comm_p2p")
+            self.status = cuda_ops.status_pointer()
+
+    def _alloc(self, nbytes: int, zero: bool = False):
+        from .comm import SymmetricBuffer
+        buf = SymmetricBuffer(self.comm_lib, max(nbytes, 256), self.device, self.group)
+        if zero:
+            buf.bytes_tensor.zero_()
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        self._bufs.append(buf)
+        return buf
+
+    def shard(self, x: Tensor, dim: int = 1) -> Tensor:
+        """This rank's contiguous slice of a full-sequence tensor along ``dim``."""
+        n = x.shape[dim]
+        if n % self.world:
+            raise ValueError(f"sequence length {n} is not divisible by {self.world} ranks")
+        per = n // self.world
+        return x.narrow(dim, self.rank * per, per)
+
+    def all_gather_seq(self, x: Tensor, dim: int = 1) -> Tensor:
+        """Library all-gather along the sequence axis (source-major order)."""
+        if self.world == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim)
+
+    # -- forward ------------------------------------------------------------------------------------------
+    def attention_forward(self, q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk_all: Tensor, q_valid: Tensor,
+                          k_valid_all: Tensor, scale: float) -> tuple[Tensor, Tensor]:
+        """``q (B,Sl,H,D)``, ``k, v (B,Sl,Hkv,D)`` local; ``k_blk_all / k_valid_all (B, W*Sl)`` for all keys.
+        Returns ``o (B, Sl, H*D)`` and ``lse (B, H, Sl)``."""
+        B, Sl, H, D = q.shape
+        Hkv = k.shape[2]
+        if self.backend == "dist":
+            from ..ops import prims
+            kf, vf = self.all_gather_seq(k), self.all_gather_seq(v)
+            return prims.attn_fwd(q, kf, vf, q_blk, k_blk_all, q_valid, k_valid_all, scale)
+        from ..ops import cuda_ops
+        key = (B, Sl, Hkv, D)
+        if key not in self._sites:
+            self._sites[key] = _Site(self, *key)
+        site = self._sites[key]
+        site.epoch += 1
+        par = site.epoch & 1
+        site.local(site.k, par).view(B, Sl, Hkv, D).copy_(k)
+        site.local(site.v, par).view(B, Sl, Hkv, D).copy_(v)
+        rc = self.lib.otb_cp_publish(_ptr_array(site.ready.peer_ptrs), c_int(self.rank), c_int(self.world),
+                                     c_uint(site.epoch), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"publish launch failed ({rc})")
+        if q.stride(-1) != 1 or any(s % 8 for s in q.stride()[:3]) or q.data_ptr() % 16:
+            q = q.contiguous()
+        o = torch.empty(B, Sl, H, D, dtype=torch.bfloat16, device=self.device)
+        lse = torch.empty(B, H, Sl, dtype=torch.float32, device=self.device)
+        qb, kb = q_blk.to(torch.int32).contiguous(), k_blk_all.to(torch.int32).contiguous()
+        qv, kv = q_valid.to(torch.uint8).contiguous(), k_valid_all.to(torch.uint8).contiguous()
+        rc = self.lib.otb_attn_fwd_cp(
+            c_void_p(q.data_ptr()), c_void_p(o.data_ptr()), c_void_p(lse.data_ptr()), c_void_p(qb.data_ptr()),
+            c_void_p(kb.data_ptr()), c_void_p(qv.data_ptr()), c_void_p(kv.data_ptr()), c_int(B), c_int(Sl), c_int(Sl),
+            c_int(H), c_int(Hkv), c_int(D), c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
+            _ptr_array(site.ptrs(site.k, par)), _ptr_array(site.ptrs(site.v, par)), c_void_p(site.kg.data_ptr()),
+            c_void_p(site.vg.data_ptr()), c_void_p(site.gcount.data_ptr()), c_void_p(site.ready.local_ptr),
+            c_int(self.rank), c_int(self.world), c_uint(site.epoch), c_int(self.num_copiers), c_float(scale),
+            c_longlong(self.wait_budget), c_void_p(self.status), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"context-parallel attention launch failed ({rc})")
+        cuda_ops.launch_count += 2
+        self._last_site = site
+        return o.view(B, Sl, H * D), lse
+
+    def _stream(self) -> c_void_p:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # -- autograd -------------------------------------------------------------------------------------------
+    def attention(self, q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk_all: Tensor, q_valid: Tensor,
+                  k_valid_all: Tensor, scale: float) -> Tensor:
+        return _CPAttention.apply(self, q, k, v, q_blk, k_blk_all, q_valid, k_valid_all, scale)
+
+
+class _CPAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, cp: ContextParallel, q, k, v, q_blk, k_blk_all, q_valid, k_valid_all, scale):
+        o, lse = cp.attention_forward(q, k, v, q_blk, k_blk_all, q_valid, k_valid_all, scale)
+        ctx.cp, ctx.scale = cp, scale
+        ctx.save_for_backward(q, k, v, o, lse, q_blk, k_blk_all, q_valid, k_valid_all)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from ..ops import prims
+        cp: ContextParallel = ctx.cp
+        q, k, v, o, lse, q_blk, k_blk_all, q_valid, k_valid_all = ctx.saved_tensors
+        Sl = q.shape[1]
+        r = cp.rank
+        do = do.contiguous()
+        # all keys / values for dQ of the local queries
+        kf, vf = cp.all_gather_seq(k), cp.all_gather_seq(v)
+        dq, _, _ = prims.attn_bwd(do, q, kf, vf, o, lse, q_blk, k_blk_all, q_valid, k_valid_all, ctx.scale)
+        # all queries (and their dO / O / LSE) for dK, dV of the local keys
+        qf, dof, of_ = cp.all_gather_seq(q), cp.all_gather_seq(do), cp.all_gather_seq(o)
+        lsef = cp.all_gather_seq(lse, dim=2)
+        q_blk_all = cp.all_gather_seq(q_blk)
+        q_valid_all = cp.all_gather_seq(q_valid.to(torch.uint8)).bool()
+        k_blk = k_blk_all[:, r * Sl:(r + 1) * Sl].contiguous()
+        k_valid = k_valid_all[:, r * Sl:(r + 1) * Sl].contiguous()
+        _, dk, dv = prims.attn_bwd(dof, qf, k, v, of_, lsef, q_blk_all, k_blk, q_valid_all, k_valid, ctx.scale)
+        return None, dq, dk, dv, None, None, None, None, None

@@ -124,3 +124,57 @@ def test_fused_tensor_parallel_layer_matches_unsharded_layer():
     ret = mgr.dict()
     mp.spawn(_tp_worker, args=(2, 29900 + os.getpid() % 90, ret), nprocs=2, join=True)
     assert ret["tp_err"] < 0.03 * max(1.0, ret["tp_scale"])
+
+
+def _cp_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from opentau_b200 import ops
+        from opentau_b200.ops import cuda_ops
+        from opentau_b200.parallel.cp import ContextParallel
+        torch.manual_seed(0)
+        B, S, H, Hkv, D = 2, 640, 8, 4, 256
+        q = torch.randn(B, S, H, D, device=dev).to(torch.bfloat16)
+        k = torch.randn(B, S, Hkv, D, device=dev).to(torch.bfloat16)
+        v = torch.randn(B, S, Hkv, D, device=dev).to(torch.bfloat16)
+        do = torch.randn(B, S, H * D, device=dev).to(torch.bfloat16)
+        for t in (q, k, v, do):
+            dist.broadcast(t, 0)
+        blk = (torch.arange(S, device=dev, dtype=torch.int32) // 100)[None].expand(B, S).contiguous()
+        valid = torch.ones(B, S, dtype=torch.bool, device=dev)
+        valid[1, 37] = False
+        qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+        want = ops.block_attention(qr, kr, vr, blk, blk, valid, valid, D ** -0.5)
+        want.backward(do)
+        cp = ContextParallel(dev, backend="p2p", wait_budget=4_000_000_000)
+        errs = []
+        for _ in range(3):                           # both parities of the K/V shards are reused
+            ql, kl, vl = (cp.shard(t).clone().requires_grad_(True) for t in (q, k, v))
+            got = cp.attention(ql, kl, vl, cp.shard(blk).contiguous(), blk, cp.shard(valid).contiguous(), valid, D ** -0.5)
+            got.backward(cp.shard(do).contiguous())
+            errs += [float((got.float() - cp.shard(want).float()).abs().max()),
+                     float((ql.grad.float() - cp.shard(qr.grad).float()).abs().max()),
+                     float((kl.grad.float() - cp.shard(kr.grad).float()).abs().max()),
+                     float((vl.grad.float() - cp.shard(vr.grad).float()).abs().max())]
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        allerr = [None] * world
+        dist.all_gather_object(allerr, max(errs))
+        if rank == 0:
+            ret["cp_err"] = max(allerr)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_context_parallel_attention_matches_single_gpu():
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_cp_worker, args=(2, 29990 + os.getpid() % 9, ret), nprocs=2, join=True)
+    assert ret["cp_err"] < 0.06
