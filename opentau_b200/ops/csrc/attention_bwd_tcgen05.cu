@@ -149,8 +149,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
     int last = -1;
     if (s_any) {
       const int qm = s_ext;
-      for (int j = threadIdx.x; j < p.Sk; j += blockDim.x)
-        if (p.k_valid[(long long)b * p.Sk + j] && p.k_blk[(long long)b * p.Sk + j] <= qm) last = max(last, j);
+#pragma unroll 8
+      for (int j = threadIdx.x; j < p.Sk; j += blockDim.x) {
+        const int kbj = p.k_blk[(long long)b * p.Sk + j];
+        const int kvj = p.k_valid[(long long)b * p.Sk + j];
+        if (kvj && kbj <= qm) last = max(last, j);
+      }
     }
     if (last >= 0) atomicMax(&range_smem[1], last + 1);
     if (threadIdx.x == 0) range_smem[0] = 0;
@@ -173,11 +177,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
     int first = INT_MAX, last = -1;
     if (s_any) {
       const int km = s_ext;
-      for (int i = threadIdx.x; i < p.Sq; i += blockDim.x)
-        if (p.q_valid[(long long)b * p.Sq + i] && p.q_blk[(long long)b * p.Sq + i] >= km) {
+#pragma unroll 8
+      for (int i = threadIdx.x; i < p.Sq; i += blockDim.x) {
+        const int qbi = p.q_blk[(long long)b * p.Sq + i];
+        const int qvi = p.q_valid[(long long)b * p.Sq + i];
+        if (qvi && qbi >= km) {
           first = min(first, i);
           last = max(last, i);
         }
+      }
     }
     if (last >= 0) {
       atomicMin(&range_smem[0], first);
@@ -319,17 +327,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
         if (MODE == MODE_DQ) {
           const int key = blk * BN + st;
           int kb = INT_MAX;
-          if (key < p.Sk && p.k_valid[(long long)b * p.Sk + key]) kb = p.k_blk[(long long)b * p.Sk + key];
+          if (key < p.Sk) {
+            const int kbv = p.k_blk[(long long)b * p.Sk + key];
+            const int kvv = p.k_valid[(long long)b * p.Sk + key];
+            kb = kvv ? kbv : INT_MAX;
+          }
           meta_blk[slot * BN + st] = kb;
         } else {
           const int pos = blk * pos_per_blk + st / g;
           const int head = kvh * g + st % g;
           int qb = INT_MIN;
           float l2 = INFINITY, dl = 0.f;
-          if (pos < p.Sq && p.q_valid[(long long)b * p.Sq + pos]) {
-            qb = p.q_blk[(long long)b * p.Sq + pos];
-            l2 = p.lse[((long long)b * p.H + head) * p.Sq + pos] * LOG2E;
-            dl = p.delta[((long long)b * p.H + head) * p.Sq + pos];
+          if (pos < p.Sq) {
+            // four independent loads; the validity only selects afterwards
+            const int qvv = p.q_valid[(long long)b * p.Sq + pos];
+            const int qbv = p.q_blk[(long long)b * p.Sq + pos];
+            const float lv = p.lse[((long long)b * p.H + head) * p.Sq + pos];
+            const float dv2 = p.delta[((long long)b * p.H + head) * p.Sq + pos];
+            if (qvv) {
+              qb = qbv;
+              l2 = lv * LOG2E;
+              dl = dv2;
+            }
           }
           meta_blk[slot * BN + st] = qb;
           meta_lse[slot * BN + st] = l2;

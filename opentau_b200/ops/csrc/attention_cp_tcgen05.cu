@@ -106,9 +106,15 @@ struct AttnSmem {
   static constexpr int OFF_KV = Q_BYTES;
   static constexpr int OFF_P = OFF_KV + 2 * STAGE_BYTES;
   static constexpr int OFF_META = OFF_P + 2 * P_BYTES;  // int kmeta[2][BN]
-  static constexpr int OFF_BAR = OFF_META + 2 * BN * 4;
+  static constexpr int OFF_RED = OFF_META + 2 * BN * 4;  // float red[2][128]: row max / row sum exchange
+  static constexpr int OFF_KMM = OFF_RED + 2 * ATT_M * 4;  // int kmm[2][BN/32][2]: min / max block id per 32 keys
+  static constexpr int OFF_BAR = OFF_KMM + 2 * (BN / 32) * 2 * 4;
   static constexpr int NBAR = 16;
-  static constexpr int TOTAL = OFF_BAR + NBAR * 8 + 64 + 1024;
+  static constexpr int USED = OFF_BAR + NBAR * 8 + 64;
+  // room for rounding the base up to 1024 bytes (the kernel has no static shared memory, so the base normally is
+  // aligned already); capped at the 227 KB a CTA may own, and checked at run time
+  static constexpr int TOTAL = USED + 1024 <= 232448 ? USED + 1024 : 232448;
+  static_assert(USED <= 232448, "shared memory budget");
   static constexpr int NBUF = (OFF_BAR / CP_PIECE) >= 12 ? 12 : 8;  // copier buffers (copier CTAs use the tile area)
 };
 
@@ -119,7 +125,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int DPAD, int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ PtrArray k_peers,
                    const __grid_constant__ PtrArray v_peers, AttnParams p) {
@@ -130,6 +136,8 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   uint8_t* sKV = smem + L::OFF_KV;
   uint8_t* sP = smem + L::OFF_P;
   int* kmeta = reinterpret_cast<int*>(smem + L::OFF_META);
+  float* red = reinterpret_cast<float*>(smem + L::OFF_RED);
+  int* kmm = reinterpret_cast<int*>(smem + L::OFF_KMM);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* q_full = bars + 0;
   uint64_t* kv_full = bars + 1;    // [2]
@@ -142,6 +150,12 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* nb_smem = reinterpret_cast<int*>(tmem_slot + 2);  // [W] key blocks to visit per source
+  int& s_qmax = *reinterpret_cast<int*>(tmem_slot + 2 + CP_MAX_RANKS);
+  int& s_any = *reinterpret_cast<int*>(tmem_slot + 3 + CP_MAX_RANKS);
+  if ((int)(smem - smem_raw) + L::USED > L::TOTAL) {   // base less aligned than assumed: refuse instead of overrunning
+    if (threadIdx.x == 0) report_timeout(p.status, KID_ATTN, 99, (unsigned)(smem - smem_raw));
+    return;
+  }
 
   const int W = p.W;
   const int rowbytes = p.Hkv * p.D * 2;
@@ -257,8 +271,8 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&s_free[i], 256);
+      mbar_init(&p_full[i], 256);
       mbar_init(&p_free[i], 1);
     }
     mbar_init(o_full, 1);
@@ -292,7 +306,6 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         any_q = true;
       }
     }
-    __shared__ int s_qmax, s_any;
     if (threadIdx.x == 0) {
       s_qmax = INT_MIN;
       s_any = 0;
@@ -305,8 +318,11 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     __syncthreads();
     if (s_any) {
       const int qm = s_qmax;
+#pragma unroll 8
       for (int j = threadIdx.x; j < p.Sk; j += blockDim.x) {
-        if (p.k_valid[(long long)b * p.Sk + j] && p.k_blk[(long long)b * p.Sk + j] <= qm) {
+        const int kbj = p.k_blk[(long long)b * p.Sk + j];
+        const int kvj = p.k_valid[(long long)b * p.Sk + j];
+        if (kvj && kbj <= qm) {
           const int src = j / p.Sl;
           atomicMax(&nb_smem[src], (j - src * p.Sl) / BN + 1);
         }
@@ -407,18 +423,29 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
+    // Eight warps: two per TMEM lane quadrant.  Both threads of a pair own the same row (TMEM lane) and split the
+    // columns of S, of P and of O between them; the row maximum (per block) and the row sum (once, at the end) are
+    // exchanged through shared memory.  The scores of a block are read from TMEM once and stay in registers.
+    // Masking is decided per 32 keys from the min / max block id of those keys: fully visible and fully hidden
+    // groups take paths without per-element tests.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;            // 0: first half of the columns, 1: second half
     const int row = quad * 32 + lane;            // TMEM lane owned by this thread
-    const int st = threadIdx.x - 64;             // 0..127 index among softmax threads
+    const int st = threadIdx.x - 64;             // 0..255 index among softmax threads
     const int pos = p0 + row / g;
     const int head = kvh * g + row % g;
     const bool row_in = pos < p.Sq;
     const bool q_ok = row_in && p.q_valid[(long long)b * p.Sq + pos] != 0;
-    const int qb = q_ok ? p.q_blk[(long long)b * p.Sq + pos] : 0;
+    const int qb = q_ok ? p.q_blk[(long long)b * p.Sq + pos] : INT_MIN;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    constexpr int HB = BN / 2;                   // columns per thread
+    constexpr int NCH = HB / 32;                 // 32-column groups per thread
+    const int c0 = half * HB;
     float m_used = -INFINITY;   // maximum the accumulators are currently expressed against
-    float l = 0.f;
+    float l = 0.f;              // this thread's part of the row sum
     const float scale = p.scale_log2;
+    const int n16 = p.Dmma / 16;
+    const int o_lo = half ? (n16 + 1) / 2 : 0, o_hi = half ? n16 : (n16 + 1) / 2;   // this thread's O column groups
 
     int j = 0;  // running block counter over all sources (pipeline slot / phase)
     for (int rs = 0; rs < W; ++rs) {
@@ -426,35 +453,59 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       const int nb = nb_smem[src];
       for (int jb = 0; jb < nb; ++jb, ++j) {
       const int slot = j & 1, u = j >> 1;
-      // key metadata of this block: INT_MAX = invisible to everyone
-      if (st < BN) {
+      if (st < BN) {                              // whole warps: st < BN covers warps 0 .. BN/32-1 of the group
         const int kin = jb * BN + st;             // index inside the source's shard
         const long long key = (long long)src * p.Sl + kin;
-        int kb = INT_MAX;
-        if (kin < p.Sl && p.k_valid[(long long)b * p.Sk + key]) kb = p.k_blk[(long long)b * p.Sk + key];
-        kmeta[slot * BN + st] = kb;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const int* km = kmeta + slot * BN;
-      mbar_wait(&s_full[slot], u & 1, abort_flag, p.status, KID_ATTN, 6, j);
-      tc_fence_after();
-      const uint32_t s_addr = tmem_S + slot * BN + lane_off;
-      // pass A: row maximum of the masked, scaled scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_x32(s_addr + c * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const bool vis = q_ok && km[c * 32 + e] <= qb;
-          const float sc = vis ? __uint_as_float(r[e]) * scale : -INFINITY;
-          mx = fmaxf(mx, sc);
+        int kbm = INT_MAX;                        // INT_MAX = invisible to everyone
+        if (kin < p.Sl) {
+          const int kbv = p.k_blk[(long long)b * p.Sk + key];
+          const int kvv = p.k_valid[(long long)b * p.Sk + key];
+          kbm = kvv ? kbv : INT_MAX;
+        }
+        kmeta[slot * BN + st] = kbm;
+        const int mn = __reduce_min_sync(0xffffffffu, kbm);
+        const int mxk = __reduce_max_sync(0xffffffffu, kbm);
+        if (lane == 0) {
+          kmm[(slot * (BN / 32) + st / 32) * 2 + 0] = mn;
+          kmm[(slot * (BN / 32) + st / 32) * 2 + 1] = mxk;
         }
       }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const int* km = kmeta + slot * BN + c0;
+      mbar_wait(&s_full[slot], u & 1, abort_flag, p.status, KID_ATTN, 6, j);
+      tc_fence_after();
+      const uint32_t s_addr = tmem_S + slot * BN + c0 + lane_off;
+      // ---- read this thread's scores once; visibility class per 32 keys: 2 = all, 0 = none, 1 = test each
+      uint32_t r[NCH][32];
+      int cls[NCH];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        __syncwarp();
+        tmem_ld_x32(s_addr + c * 32, r[c]);
+        const int gi = (slot * (BN / 32) + (c0 / 32) + c) * 2;
+        const int gmin = kmm[gi], gmax = kmm[gi + 1];
+        cls[c] = (!q_ok || gmin > qb) ? 0 : (gmax <= qb ? 2 : 1);
+      }
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        if (cls[c] == 2) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[c][e]));
+        } else if (cls[c] == 1) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (km[c * 32 + e] <= qb) mx = fmaxf(mx, __uint_as_float(r[c][e]));
+        }
+      }
+      mx *= scale;                                // scale > 0: max commutes with it
+      red[half * ATT_M + row] = mx;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      mx = fmaxf(mx, red[(half ^ 1) * ATT_M + row]);
       const float m_new = fmaxf(m_used, mx);
+      // lazy rescale decision (warp-uniform because tcgen05.ld/st are warp-collective; both warps of a pair hold
+      // the same rows and the same maxima, so they decide alike)
       const bool want = (m_new > m_used + 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
       const bool any_want = __any_sync(0xffffffffu, want);
       float alpha = 1.f;
@@ -462,48 +513,59 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
         m_used = m_new;
       }
+      // P buffer `slot` was last read by PV(j-2)
       if (j >= 2) mbar_wait(&p_free[slot], ((u - 1) & 1), abort_flag, p.status, KID_ATTN, 7, j);
       if (any_want && j > 0) {
+        // O may only be touched once PV(j-1) has retired
         const int ps = (j - 1) & 1, pu = (j - 1) >> 1;
         mbar_wait(&p_free[ps], pu & 1, abort_flag, p.status, KID_ATTN, 8, j);
         tc_fence_after();
         const uint32_t o_addr = tmem_O + lane_off;
 #pragma unroll 1
-        for (int c = 0; c < p.Dmma / 16; ++c) {
-          uint32_t r[16];
+        for (int c = o_lo; c < o_hi; ++c) {
+          uint32_t ro[16];
           __syncwarp();
-          tmem_ld_x16(o_addr + c * 16, r);
+          tmem_ld_x16(o_addr + c * 16, ro);
           tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tmem_st_x16(o_addr + c * 16, r);
+          for (int e = 0; e < 16; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
+          tmem_st_x16(o_addr + c * 16, ro);
         }
         tmem_wait_st();
       }
       l *= alpha;
+      // ---- probabilities -> bf16 -> swizzled shared memory (A operand of the PV product)
       uint8_t* prow = sP + slot * L::P_BYTES + row * 128;
       float lsum = 0.f;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_x32(s_addr + c * 32, r);
-        tmem_wait_ld();
-        uint32_t packed[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const bool v0 = q_ok && km[c * 32 + e] <= qb;
-          const bool v1 = q_ok && km[c * 32 + e + 1] <= qb;
-          float p0f = v0 ? fast_exp2(__uint_as_float(r[e]) * scale - m_safe) : 0.f;
-          float p1f = v1 ? fast_exp2(__uint_as_float(r[e + 1]) * scale - m_safe) : 0.f;
-          __nv_bfloat162 pb = __floats2bfloat162_rn(p0f, p1f);
-          float2 back = __bfloat1622float2(pb);
-          lsum += back.x + back.y;
-          packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t packed[16];
+        if (cls[c] == 2) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0f = fast_exp2(fmaf(__uint_as_float(r[c][e]), scale, -m_safe));
+            const float p1f = fast_exp2(fmaf(__uint_as_float(r[c][e + 1]), scale, -m_safe));
+            lsum += p0f + p1f;
+            packed[e >> 1] = pack_bf16(p0f, p1f);
+          }
+        } else if (cls[c] == 1) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0f = km[c * 32 + e] <= qb ? fast_exp2(fmaf(__uint_as_float(r[c][e]), scale, -m_safe)) : 0.f;
+            const float p1f =
+                km[c * 32 + e + 1] <= qb ? fast_exp2(fmaf(__uint_as_float(r[c][e + 1]), scale, -m_safe)) : 0.f;
+            lsum += p0f + p1f;
+            packed[e >> 1] = pack_bf16(p0f, p1f);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) packed[e] = 0u;
         }
-        const int chunk = (c * 32) / 64;
-        const int unit0 = ((c * 32) % 64) / 8;
+        // 32 keys = 64 bytes = four 16-byte units; unit index within the 128-byte row is XOR-swizzled
+        const int col = c0 + c * 32;
+        const int chunk = col / 64;                // 64-key chunk (16 KB apart)
+        const int unit0 = (col % 64) / 8;          // first 16-byte unit inside the row
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int unit = (unit0 + q4) ^ (row & 7);
@@ -512,6 +574,7 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         }
       }
       l += lsum;
+      // S buffer is free for QK(j+2); P is visible to the tensor core (async proxy)
       tc_fence_before();
       mbar_arrive(&s_free[slot]);
       fence_async_smem();
@@ -519,17 +582,21 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       }
     }
 
-    // ---- epilogue: O / l -> bf16 -> global, LSE
+    // ---- epilogue: O / l -> bf16 -> global, LSE.  The two threads of a row add their partial sums first.
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // every read of `red` from the last block is done
+    red[half * ATT_M + row] = l;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    l += red[(half ^ 1) * ATT_M + row];
     mbar_wait(o_full, 0, abort_flag, p.status, KID_ATTN, 9, 0);
     tc_fence_after();
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
     const uint32_t o_addr = tmem_O + lane_off;
     __nv_bfloat16* orow = p.o + (((long long)b * p.Sq + pos) * p.H + head) * p.D;
 #pragma unroll 1
-    for (int c = 0; c < p.Dmma / 16; ++c) {
-      uint32_t r[16];
+    for (int c = o_lo; c < o_hi; ++c) {
+      uint32_t ro[16];
       __syncwarp();
-      tmem_ld_x16(o_addr + c * 16, r);
+      tmem_ld_x16(o_addr + c * 16, ro);
       tmem_wait_ld();
       if (row_in) {
 #pragma unroll
@@ -537,16 +604,16 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           const int col = c * 16 + h8 * 8;
           if (col < p.D) {
             uint4 o;
-            o.x = pack_bf16(__uint_as_float(r[h8 * 8 + 0]) * inv_l, __uint_as_float(r[h8 * 8 + 1]) * inv_l);
-            o.y = pack_bf16(__uint_as_float(r[h8 * 8 + 2]) * inv_l, __uint_as_float(r[h8 * 8 + 3]) * inv_l);
-            o.z = pack_bf16(__uint_as_float(r[h8 * 8 + 4]) * inv_l, __uint_as_float(r[h8 * 8 + 5]) * inv_l);
-            o.w = pack_bf16(__uint_as_float(r[h8 * 8 + 6]) * inv_l, __uint_as_float(r[h8 * 8 + 7]) * inv_l);
+            o.x = pack_bf16(__uint_as_float(ro[h8 * 8 + 0]) * inv_l, __uint_as_float(ro[h8 * 8 + 1]) * inv_l);
+            o.y = pack_bf16(__uint_as_float(ro[h8 * 8 + 2]) * inv_l, __uint_as_float(ro[h8 * 8 + 3]) * inv_l);
+            o.z = pack_bf16(__uint_as_float(ro[h8 * 8 + 4]) * inv_l, __uint_as_float(ro[h8 * 8 + 5]) * inv_l);
+            o.w = pack_bf16(__uint_as_float(ro[h8 * 8 + 6]) * inv_l, __uint_as_float(ro[h8 * 8 + 7]) * inv_l);
             *reinterpret_cast<uint4*>(orow + col) = o;
           }
         }
       }
     }
-    if (row_in) {
+    if (row_in && half == 0) {
       const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : 0.f;
       p.lse[((long long)b * p.H + head) * p.Sq + pos] = lse;
     }
@@ -598,7 +665,7 @@ static int launch_attn_cp(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   const int pos_per_tile = ATT_M / p.g;
   const int ntile = (p.Sq + pos_per_tile - 1) / pos_per_tile;
   const int grid = p.NC + ntile * p.Hkv * p.B;
-  kern<<<grid, 192, L::TOTAL, stream>>>(tq, tk, tv, kp, vp, p);
+  kern<<<grid, 320, L::TOTAL, stream>>>(tq, tk, tv, kp, vp, p);
   return (int)cudaGetLastError();
 }
 
