@@ -1,7 +1,9 @@
 // Block-causal flash attention backward for sm_100a (tcgen05 + TMEM + TMA).
 //
 // Three launches of one templated kernel, each an "inner products -> elementwise -> accumulate" pipeline
-// with the same warp roles as the forward kernel (warp 0 TMA, warp 1 MMA, warps 2..5 elementwise):
+// with the same warp roles as the forward kernel (warp 0 TMA, warp 1 MMA, warps 2..9 elementwise: two warps per
+// TMEM lane quadrant split the columns of a block; groups of 32 columns that are fully visible or fully hidden for a
+// row skip the per-element mask test):
 //
 //   MODE_DQ  tile = 128 query rows (position x head-of-group); stream key blocks j:
 //              S = Q K_j^T, dP = dO V_j^T  ->  dS = P o (dP - delta) * scale  ->  dQ += dS K_j
@@ -50,7 +52,8 @@ struct BwdSmem {
   static constexpr int OFF_Y = NF * F_BYTES;
   static constexpr int OFF_T = OFF_Y + 2 * STAGE_BYTES;
   static constexpr int OFF_META = OFF_T + 2 * T_BYTES;        // per slot: int blk[BN], float lse2[BN], float delta[BN]
-  static constexpr int OFF_BAR = OFF_META + 2 * BN * 12;
+  static constexpr int OFF_KMM = OFF_META + 2 * BN * 12;       // int kmm[2][BN/32][2]: min / max block id per 32 columns
+  static constexpr int OFF_BAR = OFF_KMM + 2 * (BN / 32) * 2 * 4;
   static constexpr int NBAR = 16;
   static constexpr int TOTAL = OFF_BAR + NBAR * 8 + 32 + 1024;
   static constexpr int NS = MODE == MODE_DV ? 1 : 2;          // score tiles per block
@@ -64,7 +67,7 @@ __device__ __forceinline__ float bw_exp2(float x) {
 }
 
 template <int MODE, int DPAD, int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ CUtensorMap tm_f2,
                 const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2, BwdParams p) {
   using L = BwdSmem<MODE, DPAD, BN>;
@@ -99,8 +102,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
       mbar_init(&y_full[i], 1);
       mbar_init(&y_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
-      mbar_init(&t_full[i], 128);
+      mbar_init(&s_free[i], 256);
+      mbar_init(&t_full[i], 256);
       mbar_init(&t_free[i], 1);
     }
     mbar_init(acc_full, 1);
@@ -288,8 +291,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
   } else {
     // ------------------------------------------------------------------ elementwise + epilogue
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;            // which half of a block's columns this thread handles
     const int row = quad * 32 + lane;
-    const int st = threadIdx.x - 64;
+    const int st = threadIdx.x - 64;             // 0..255
+    int* kmm = reinterpret_cast<int*>(smem + L::OFF_KMM);
+    constexpr int HB = BN / 2;                   // columns per thread per block
+    constexpr int PIECE = HB >= 32 ? 32 : 16;    // columns per TMEM read
+    constexpr int NP = HB / PIECE;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
     float* meta_lse = reinterpret_cast<float*>(meta_blk + 2 * BN);
     float* meta_delta = meta_lse + 2 * BN;
@@ -333,6 +341,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
             kb = kvv ? kbv : INT_MAX;
           }
           meta_blk[slot * BN + st] = kb;
+          const int mn = __reduce_min_sync(0xffffffffu, kb), mxk = __reduce_max_sync(0xffffffffu, kb);
+          if (lane == 0) {
+            kmm[(slot * (BN / 32) + st / 32) * 2 + 0] = mn;
+            kmm[(slot * (BN / 32) + st / 32) * 2 + 1] = mxk;
+          }
         } else {
           const int pos = blk * pos_per_blk + st / g;
           const int head = kvh * g + st % g;
@@ -353,9 +366,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
           meta_blk[slot * BN + st] = qb;
           meta_lse[slot * BN + st] = l2;
           meta_delta[slot * BN + st] = dl;
+          const int mn = __reduce_min_sync(0xffffffffu, qb), mxk = __reduce_max_sync(0xffffffffu, qb);
+          if (lane == 0) {
+            kmm[(slot * (BN / 32) + st / 32) * 2 + 0] = mn;
+            kmm[(slot * (BN / 32) + st / 32) * 2 + 1] = mxk;
+          }
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       const int* mb = meta_blk + slot * BN;
       const float* ml = meta_lse + slot * BN;
       const float* md = meta_delta + slot * BN;
@@ -364,43 +382,59 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
       if (j >= 2) mbar_wait(&t_free[slot], (u - 1) & 1, abort_flag, p.status, KID_ATTN_BWD, 7, j);
       const uint32_t s_addr = tmem_base + slot * (L::NS * BN) + lane_off;
       uint8_t* trow = sT + slot * L::T_BYTES + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t rs[32];
-        uint32_t rd[32];
+#pragma unroll
+      for (int c = 0; c < NP; ++c) {
+        const int col0 = half * HB + c * PIECE;
+        uint32_t rs[PIECE];
+        uint32_t rd[PIECE];
         __syncwarp();
-        tmem_ld_x32(s_addr + c * 32, rs);
-        if (MODE != MODE_DV) tmem_ld_x32(s_addr + BN + c * 32, rd);
-        tmem_wait_ld();
-        uint32_t packed[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int col = c * 32 + e + h;
-            bool vis;
-            float l2, dl;
-            if (MODE == MODE_DQ) {
-              vis = row_ok && mb[col] <= row_blk;
-              l2 = row_lse2;
-              dl = row_delta;
-            } else {
-              vis = row_ok && row_blk <= mb[col];
-              l2 = ml[col];
-              dl = md[col];
-            }
-            float pr = vis ? bw_exp2(__uint_as_float(rs[e + h]) * p.scale_log2 - l2) : 0.f;
-            if (MODE == MODE_DV) v[h] = pr;
-            else v[h] = pr * (__uint_as_float(rd[e + h]) - dl) * p.scale;
-          }
-          __nv_bfloat162 pb = __floats2bfloat162_rn(v[0], v[1]);
-          packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+        if (PIECE == 32) {
+          tmem_ld_x32(s_addr + col0, rs);
+          if (MODE != MODE_DV) tmem_ld_x32(s_addr + BN + col0, rd);
+        } else {
+          tmem_ld_x16(s_addr + col0, rs);
+          if (MODE != MODE_DV) tmem_ld_x16(s_addr + BN + col0, rd);
         }
-        const int chunk = (c * 32) / 64;
-        const int unit0 = ((c * 32) % 64) / 8;
+        // visibility of this group of columns for this row: 2 = all, 0 = none, 1 = test each
+        const int gi = (slot * (BN / 32) + col0 / 32) * 2;
+        const int gmin = kmm[gi], gmax = kmm[gi + 1];
+        int cls;
+        if (MODE == MODE_DQ) cls = (!row_ok || gmin > row_blk) ? 0 : (gmax <= row_blk ? 2 : 1);
+        else cls = (!row_ok || gmax < row_blk) ? 0 : (gmin >= row_blk ? 2 : 1);
+        tmem_wait_ld();
+        uint32_t packed[PIECE / 2];
+        if (cls == 0) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+          for (int e = 0; e < PIECE / 2; ++e) packed[e] = 0u;
+        } else {
+#pragma unroll
+          for (int e = 0; e < PIECE; e += 2) {
+            float v[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col = col0 + e + h;
+              bool vis = true;
+              float l2, dl;
+              if (MODE == MODE_DQ) {
+                if (cls == 1) vis = mb[col] <= row_blk;
+                l2 = row_lse2;
+                dl = row_delta;
+              } else {
+                if (cls == 1) vis = row_blk <= mb[col];
+                l2 = ml[col];
+                dl = md[col];
+              }
+              float pr = vis ? bw_exp2(fmaf(__uint_as_float(rs[e + h]), p.scale_log2, -l2)) : 0.f;
+              if (MODE == MODE_DV) v[h] = pr;
+              else v[h] = pr * (__uint_as_float(rd[e + h]) - dl) * p.scale;
+            }
+            packed[e >> 1] = pack_bf16(v[0], v[1]);
+          }
+        }
+        const int chunk = col0 / 64;
+        const int unit0 = (col0 % 64) / 8;
+#pragma unroll
+        for (int q4 = 0; q4 < PIECE / 8; ++q4) {
           const int unit = (unit0 + q4) ^ (row & 7);
           uint4 val = make_uint4(packed[q4 * 4 + 0], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
           *reinterpret_cast<uint4*>(trow + chunk * (BW_M * 128) + unit * 16) = val;
@@ -415,8 +449,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant
     mbar_wait(acc_full, 0, abort_flag, p.status, KID_ATTN_BWD, 9, 0);
     tc_fence_after();
     __nv_bfloat16* orow = p.out + out_off;
+    const int n16 = p.Dmma / 16;
+    const int a_lo = half ? (n16 + 1) / 2 : 0, a_hi = half ? n16 : (n16 + 1) / 2;
 #pragma unroll 1
-    for (int c = 0; c < p.Dmma / 16; ++c) {
+    for (int c = a_lo; c < a_hi; ++c) {
       uint32_t r[16];
       __syncwarp();
       tmem_ld_x16(tmem_acc + lane_off + c * 16, r);
@@ -530,7 +566,7 @@ static int launch_bwd(const void* q, Strides qs, const void* k, Strides ks, cons
   dim3 grid;
   if (MODE == MODE_DQ) grid = dim3((p.Sq + BW_M / g - 1) / (BW_M / g), p.Hkv, p.B);
   else grid = dim3((p.Sk + BW_M - 1) / BW_M, p.Hkv, p.B);
-  kern<<<grid, 192, L::TOTAL, stream>>>(f1, f2, y1, y2, p);
+  kern<<<grid, 320, L::TOTAL, stream>>>(f1, f2, y1, y2, p);
   return (int)cudaGetLastError();
 }
 
