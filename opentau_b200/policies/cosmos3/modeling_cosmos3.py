@@ -86,8 +86,18 @@ class Qwen3VLWithExpertModel(nn.Module):
             self.backbone.eval()
         return self
 
+    def enable_tensor_parallel(self, tp, free_replicated_weights: bool = False) -> None:
+        """Shards the (frozen) backbone decoder over the ranks of ``tp``; the prefix pass then runs tensor parallel
+        over the union of the ranks' batches and returns each rank the KV cache of its own samples."""
+        if any(p.requires_grad for p in self.backbone.language_model.parameters()):
+            raise ValueError("tensor parallelism covers the frozen backbone only (train_expert_only=True)")
+        from .tensor_parallel import TPBackbone
+        self.tp_backbone = TPBackbone(self, tp, free_replicated_weights)
+
     def run_prefix(self, images, img_masks, lang_tokens, lang_masks) -> tuple[KVCache, Tensor]:
         """Backbone pass -> ``(cache, prefix positions (3,B,S))``; gradients only if the backbone trains."""
+        if getattr(self, "tp_backbone", None) is not None:
+            return self.tp_backbone.run_prefix(images, img_masks, lang_tokens, lang_masks)
         frozen = not any(p.requires_grad for p in self.backbone.parameters())
         with torch.set_grad_enabled(torch.is_grad_enabled() and not frozen):
             embs, pad, pos, deep, n_img = self.backbone.embed_prefix(images, img_masks, lang_tokens, lang_masks)
@@ -246,6 +256,9 @@ class Cosmos3Policy(PreTrainedPolicy):
         self.language_tokenizer = load_text_tokenizer(config.tokenizer_path, vocab)
         self.model = Cosmos3FlowMatching(config)
         self.reset()
+
+    def enable_tensor_parallel(self, tp, free_replicated_weights: bool = False) -> None:
+        self.model.qwen3vl_with_expert.enable_tensor_parallel(tp, free_replicated_weights)
 
     def reset(self) -> None:
         self._action_queue: deque = deque([], maxlen=self.config.n_action_steps)

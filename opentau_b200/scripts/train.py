@@ -205,6 +205,12 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
     if device.type == "cuda":
         policy.to(torch.bfloat16)
     policy.train()
+    if cfg.distributed.tp > 1:
+        if cfg.distributed.tp != world or not hasattr(policy, "enable_tensor_parallel"):
+            raise ValueError("distributed.tp must equal the number of ranks and needs a policy with a frozen, "
+                             "shardable backbone (cosmos3)")
+        from ..parallel.tp import TensorParallel
+        policy.enable_tensor_parallel(TensorParallel(device), free_replicated_weights=True)
     opt_cfg, sched_cfg = cfg.optimizer, cfg.scheduler
     dcfg = cfg.distributed
     clip = dcfg.gradient_clipping if dcfg.gradient_clipping is not None else getattr(opt_cfg, "grad_clip_norm", 10.0)

@@ -72,3 +72,48 @@ def test_kv_heads_are_replicated_when_fewer_than_ranks():
     wq, wk, wv = layer.self_attn.qkv_proj.weight.split([128, 32, 32], 0)
     assert torch.equal(tpl.w_qkv[:32], wq[96:128]) and torch.equal(tpl.w_qkv[32:64], wk)
     assert tpl.w_o.shape == (128, 32) and tpl.w_gu.shape == (128, 128) and tpl.w_down.shape == (128, 64)
+
+
+def _cosmos_rank(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from helpers import tiny_batch
+        from test_policies_cpu import _cosmos3
+        from opentau_b200.datasets.synthetic import identity_stats
+        from opentau_b200.parallel.tp import TensorParallel
+        from opentau_b200.policies.cosmos3.tensor_parallel import TPBackbone
+        from opentau_b200.policies.factory import make_policy
+        errs = []
+        for col in (None, 1):
+            torch.manual_seed(0)
+            pol = make_policy(_cosmos3(col=col), per_dataset_stats=[identity_stats()]).eval()
+            b = tiny_batch(batch_size=4)
+            images, masks = pol.prepare_images(b)
+            lt, lm = pol.prepare_language(b)
+            w = pol.model.qwen3vl_with_expert
+            with torch.no_grad():
+                full, pos_full = w.run_prefix(images, masks, lt, lm)
+            sl = slice(rank * 2, rank * 2 + 2)
+            tpb = TPBackbone(w, TensorParallel("cpu"))
+            cache, pos = tpb.run_prefix([im[sl] for im in images], [m[sl] for m in masks], lt[sl], lm[sl])
+            layers = [col] if col is not None else range(full.k.shape[0])
+            for li in layers:
+                errs.append(float((cache.k[li] - full.k[li, sl]).abs().max()))
+                errs.append(float((cache.v[li] - full.v[li, sl]).abs().max()))
+            assert torch.equal(pos, pos_full[:, sl]) and torch.equal(cache.valid, full.valid[sl])
+        gathered = [None] * world
+        dist.all_gather_object(gathered, max(errs))
+        if rank == 0:
+            ret["err"] = max(gathered)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_cosmos3_tensor_parallel_prefix_equals_replicated_backbone():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_cosmos_rank, args=(2, 29650 + os.getpid() % 300, ret), nprocs=2, join=True)
+    assert ret["err"] < 1e-4
