@@ -44,6 +44,37 @@ class _TaggedDataset(Dataset):
         return item
 
 
+def standardized_stats(ds) -> dict:
+    """Statistics of one member under the STANDARD feature names (``state``, ``actions``, ``camera{i}``): raw LeRobot
+    keys go through the dataset's name map, the column selection is applied, and vectors are zero-padded to the
+    pipeline's ``max_state_dim`` / ``max_action_dim`` (a padded dim has zero range, which normalisation maps to 0)."""
+    explicit = getattr(ds, "stats", None)
+    if explicit:
+        return explicit
+    raw = getattr(getattr(ds, "meta", None), "stats", None) or {}
+    name_map = getattr(ds, "_name_map", None)
+    if not raw or not name_map:
+        return raw
+    out: dict[str, dict[str, np.ndarray]] = {}
+    for std, key in name_map.items():
+        if key not in raw:
+            continue
+        st = {k: np.asarray(v, np.float32) for k, v in raw[key].items()}
+        index = {"state": getattr(ds, "state_index", None), "actions": getattr(ds, "action_index", None)}.get(std)
+        width = {"state": getattr(ds, "max_state_dim", None), "actions": getattr(ds, "max_action_dim", None)}.get(std)
+        if std in ("state", "actions"):
+            for k, v in list(st.items()):
+                if k == "count" or v.ndim != 1:
+                    continue
+                if index is not None:
+                    v = v[np.asarray(index)]
+                if width is not None and v.shape[0] < width:
+                    v = np.concatenate([v, np.zeros(width - v.shape[0], np.float32)])
+                st[k] = v
+        out[std] = st
+    return out
+
+
 class DatasetMixtureMetadata:
     """Aggregated view over the members: features, one statistics dict per normalisation head, names."""
 
@@ -56,7 +87,7 @@ class DatasetMixtureMetadata:
             if key not in per_head:
                 per_head[key] = []
                 self.norm_keys.append(key)
-            per_head[key].append(getattr(ds, "stats", None) or getattr(getattr(ds, "meta", None), "stats", None) or {})
+            per_head[key].append(standardized_stats(ds))
             self.dataset_to_norm_index[name] = self.norm_keys.index(key)
         self.per_dataset_stats = [aggregate_stats(per_head[k]) for k in self.norm_keys]
         self.dataset_names = list(self.norm_keys)

@@ -146,7 +146,7 @@ def make_dataset(dataset_cfg: DatasetConfig, cfg, return_advantage_input: bool =
               tolerance_s=dataset_cfg.tolerance_s if dataset_cfg.tolerance_s is not None else mix.tolerance_s,
               revision=dataset_cfg.revision, video_backend=dataset_cfg.video_backend,
               image_resample_strategy=mix.image_resample_strategy, vector_resample_strategy=mix.vector_resample_strategy,
-              dataset_cfg=dataset_cfg, meta=meta)
+              dataset_cfg=dataset_cfg, meta=meta, return_advantage_input=return_advantage_input)
     if mix.require_non_empty_robot_type and not (dataset_cfg.robot_type or meta.robot_type):
         raise ValueError(f"dataset {dataset_cfg.repo_id} has no robot_type")
     if mix.require_non_empty_control_mode and not (dataset_cfg.control_mode or meta.control_mode):

@@ -375,7 +375,8 @@ class LeRobotDataset(BaseDataset):
                  image_transforms: Callable | None = None, delta_timestamps: dict[str, list[float]] | None = None,
                  tolerance_s: float = 1e-4, revision: str | None = None, video_backend: str | None = None,
                  image_resample_strategy: str = "nearest", vector_resample_strategy: str = "nearest",
-                 standardize: bool = True, dataset_cfg=None, train: bool = True, meta: LeRobotDatasetMetadata | None = None):
+                 standardize: bool = True, dataset_cfg=None, train: bool = True, meta: LeRobotDatasetMetadata | None = None,
+                 return_advantage_input: bool = False):
         self.repo_id = repo_id
         self.meta = meta or LeRobotDatasetMetadata(repo_id, root, revision)
         self.root = self.meta.root
@@ -391,6 +392,7 @@ class LeRobotDataset(BaseDataset):
             raise ValueError("resample strategies must be 'nearest' or 'linear'")
         self.image_resample_strategy, self.vector_resample_strategy = image_resample_strategy, vector_resample_strategy
         self.standardize = standardize
+        self.return_advantage_input = return_advantage_input
         self.retry_on_failure = True
         if dcfg is not None:
             self.state_index, self.action_index = dcfg.state_index, dcfg.action_index
@@ -614,6 +616,9 @@ class LeRobotDataset(BaseDataset):
                                                           rc.C_neg)
             out["return_bin_idx"] = torch.tensor(b, dtype=torch.long)
             out["return_continuous"] = torch.tensor(r, dtype=torch.float32)
+            if self.return_advantage_input:              # what the advantage tool needs to form n-step returns
+                out.update(success=success, episode_end_idx=ep_end, current_idx=idx,
+                           last_step=idx + rc.N_steps_look_ahead >= ep_end, episode_index=ep_idx, timestamp=timestamp)
         else:
             out["return_bin_idx"] = torch.tensor(0, dtype=torch.long)
             out["return_continuous"] = torch.tensor(0, dtype=torch.float32)

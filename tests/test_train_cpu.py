@@ -49,3 +49,18 @@ def test_validation_buckets_are_exact_masked_means():
     assert b["a"]["MSE"] == 6.0 / 4.0 and b["a"]["CE"] == 3.0 and b["b"]["MSE"] == 3.0 and b["b"]["n"] == 1.0
     agg = mixture_weighted_aggregate(b, {"a": 0.75, "b": 0.25})
     assert abs(agg["MSE"] - (0.75 * 1.5 + 0.25 * 3.0)) < 1e-9
+
+
+def test_train_on_a_recorded_lerobot_dataset(tmp_path):
+    """Raw LeRobot feature names / widths flow into the normalisation heads through the mixture metadata."""
+    from test_datasets_cpu import _record
+    _record(tmp_path / "toy", episodes=(12, 12))
+    raw = {
+        "dataset_mixture": {"datasets": [{"repo_id": "local/toy", "root": str(tmp_path / "toy")}], "action_freq": 10.0},
+        "policy": {"type": "pi05", "chunk_size": 10, "n_action_steps": 10, "prompt_max_length": 32,
+                   "discrete_action_max_length": 8, "discrete_action_vocab_size": 256, "dropout": 0.0, "device": "cpu", **TINY},
+        "output_dir": str(tmp_path / "run"), "seed": 1, "resolution": [224, 224], "num_cams": 1, "action_chunk": 10,
+        "batch_size": 2, "steps": 2, "log_freq": 1, "save_checkpoint": False, "num_workers": 0,
+        "use_policy_training_preset": True}
+    out = train(TrainPipelineConfig.from_dict(raw))
+    assert out["loss"] == out["loss"] and out["grad_norm"] > 0
