@@ -1,0 +1,63 @@
+"""Online buffer, streaming delta-action statistics, speed buckets."""
+
+import numpy as np
+import pytest
+import torch
+
+from opentau_b200.datasets.delta_action_stats import HistogramQuantiles, RunningStats, cache_key
+from opentau_b200.datasets.online_buffer import OnlineBuffer, compute_sampler_weights
+from opentau_b200.datasets.speed_percentiles import episode_speed, speed_buckets
+
+
+def _episode(n, fps=10):
+    return {"index": np.arange(n), "frame_index": np.arange(n), "episode_index": np.zeros(n, np.int64),
+            "timestamp": np.arange(n) / fps, "observation.state": np.arange(n, dtype=np.float32)[:, None].repeat(2, 1),
+            "action": np.ones((n, 2), np.float32)}
+
+
+def test_online_buffer_fifo_and_delta_queries(tmp_path):
+    spec = {"observation.state": {"dtype": "float32", "shape": (2,)}, "action": {"dtype": "float32", "shape": (2,)}}
+    buf = OnlineBuffer(tmp_path / "b", spec, buffer_capacity=10, fps=10,
+                       delta_timestamps={"observation.state": [-0.1, 0.0], "action": [0.0, 0.1, 0.2]})
+    buf.add_data(_episode(4))
+    buf.add_data(_episode(4))
+    assert len(buf) == 8 and buf.num_episodes == 2
+    it = buf[5]                                           # second episode, frame 1
+    assert it["episode_index"].item() == 1 and it["observation.state"][:, 0].tolist() == [0.0, 1.0]
+    assert it["action_is_pad"].tolist() == [False, False, False]
+    assert buf[7]["action_is_pad"].tolist() == [False, True, True]
+    buf.add_data(_episode(4))                             # wraps: overwrites the oldest two frames
+    assert len(buf) == 10 and buf.num_episodes == 3
+    reopened = OnlineBuffer(tmp_path / "b", spec, buffer_capacity=10, fps=10)
+    assert len(reopened) == 10
+    with pytest.raises(ValueError, match="reserved"):
+        OnlineBuffer(tmp_path / "c", {"_x": {"dtype": "float32", "shape": ()}}, 4)
+
+    class Off:
+        episode_data_index = {"from": torch.tensor([0, 5]), "to": torch.tensor([5, 10])}
+        def __len__(self): return 10
+    w = compute_sampler_weights(Off(), 1, buf, 0.25, 0)
+    assert w.shape == (20,) and abs(float(w[10:].sum()) - 0.25) < 1e-6 and float(w[4]) == 0.0 and float(w[9]) == 0.0
+
+
+def test_streaming_stats_equal_batch_stats():
+    rng = np.random.default_rng(0)
+    x = rng.normal(2.0, 3.0, size=(5000, 3))
+    rs = RunningStats(3)
+    for part in np.array_split(x, 17):
+        rs.update(part)
+    r = rs.result()
+    np.testing.assert_allclose(r["mean"], x.mean(0), rtol=1e-6)
+    np.testing.assert_allclose(r["std"], x.std(0), rtol=1e-6)
+    hq = HistogramQuantiles(r["min"], r["max"])
+    hq.update(x)
+    np.testing.assert_allclose(hq.quantile(0.99), np.quantile(x, 0.99, axis=0), atol=0.02)
+    assert cache_key("a/b", 50, 30.0, {"0": 1}, None) != cache_key("a/b", 50, 30.0, {"0": 2}, None)
+
+
+def test_speed_buckets_per_task():
+    assert episode_speed(np.array([[0.0, 0.0], [3.0, 4.0], [6.0, 8.0]]), fps=2) == 10.0
+    speeds = {0: 1.0, 1: 2.0, 2: 3.0, 3: 4.0, 4: 0.5, 5: 9.0}
+    tasks = {0: "a", 1: "a", 2: "a", 3: "a", 4: "b", 5: "b"}
+    b = speed_buckets(speeds, tasks, n_buckets=2)
+    assert [b[i] for i in range(6)] == [1, 1, 2, 2, 1, 2]
