@@ -1,0 +1,23 @@
+"""``opentau-so101-find-port``: unplug the arm when asked; the serial device that disappears is its port."""
+
+import glob
+import time
+
+
+def list_ports() -> set[str]:
+    return set(glob.glob("/dev/ttyACM*") + glob.glob("/dev/ttyUSB*") + glob.glob("/dev/tty.usbmodem*"))
+
+
+def main(argv=None):
+    before = list_ports()
+    input("Unplug the USB cable of the arm and press Enter...")
+    time.sleep(0.5)
+    gone = before - list_ports()
+    if len(gone) == 1:
+        print(f"The port of this arm is {gone.pop()}. Plug the cable back in.")
+    else:
+        print(f"Could not identify the port (candidates: {sorted(gone) or 'none'}).")
+
+
+if __name__ == "__main__":
+    main()
