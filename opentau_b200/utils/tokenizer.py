@@ -145,3 +145,118 @@ def pad_tokens(rows: list[list[int]], max_length: int, pad_id: int = 0) -> tuple
             ids[i, :len(r)] = torch.tensor(r, dtype=torch.long)
             mask[i, :len(r)] = True
     return ids, mask
+
+
+class BpeDctActionTokenizer:
+    """FAST-style tokenizer with a learned merge table: DCT-II per action dimension, quantisation, low frequencies
+    first, then byte-pair merges fitted on a corpus of action chunks (what
+    ``src/opentau/scripts/fit_fast_tokenizer.py`` produces in the reference; there through the FAST processor).
+
+    Base symbols are the quantised coefficients in ``[-radius, radius]`` (ids ``1 .. 2*radius+1``; 0 pads); every
+    merge adds one id.  ``save`` / ``load`` use one JSON file.
+    """
+
+    def __init__(self, scale: float = 10.0, radius: int = 127, merges: list[tuple[int, int]] | None = None,
+                 time_horizon: int | None = None, action_dim: int | None = None):
+        self.scale, self.radius = scale, radius
+        self.base = 2 * radius + 2
+        self.merges = [tuple(m) for m in (merges or [])]
+        self.time_horizon, self.action_dim = time_horizon, action_dim
+        self._rank = {m: i for i, m in enumerate(self.merges)}
+
+    @property
+    def vocab_size(self) -> int:
+        return self.base + len(self.merges)
+
+    def _symbols(self, actions) -> list[list[int]]:
+        a = np.asarray(actions.detach().float().cpu() if isinstance(actions, Tensor) else actions, dtype=np.float64)
+        if a.ndim == 2:
+            a = a[None]
+        B, T, D = a.shape
+        coef = np.einsum("kt,btd->bkd", DctActionTokenizer._dct_matrix(T), a)
+        q = np.clip(np.rint(coef * self.scale), -self.radius, self.radius).astype(np.int64)
+        out = []
+        for b in range(B):
+            flat = q[b].reshape(-1)
+            nz = np.nonzero(flat)[0]
+            end = int(nz[-1]) + 1 if len(nz) else 0
+            out.append((flat[:end] + self.radius + 1).tolist())
+        return out
+
+    @staticmethod
+    def _merge(seq: list[int], pair: tuple[int, int], new_id: int) -> list[int]:
+        out, i = [], 0
+        while i < len(seq):
+            if i + 1 < len(seq) and seq[i] == pair[0] and seq[i + 1] == pair[1]:
+                out.append(new_id)
+                i += 2
+            else:
+                out.append(seq[i])
+                i += 1
+        return out
+
+    def fit(self, chunks, vocab_size: int = 2048, min_count: int = 2) -> "BpeDctActionTokenizer":
+        """``chunks (N, T, D)`` normalised action chunks."""
+        arr = np.asarray(chunks)
+        self.time_horizon, self.action_dim = int(arr.shape[1]), int(arr.shape[2])
+        seqs = self._symbols(arr)
+        self.merges = []
+        while self.base + len(self.merges) < vocab_size:
+            counts: dict[tuple[int, int], int] = {}
+            for s in seqs:
+                for a, b in zip(s[:-1], s[1:]):
+                    counts[(a, b)] = counts.get((a, b), 0) + 1
+            if not counts:
+                break
+            pair, c = max(counts.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))
+            if c < min_count:
+                break
+            new_id = self.base + len(self.merges)
+            self.merges.append(pair)
+            seqs = [self._merge(s, pair, new_id) for s in seqs]
+        self._rank = {m: i for i, m in enumerate(self.merges)}
+        return self
+
+    def __call__(self, actions) -> list[list[int]]:
+        out = []
+        for s in self._symbols(actions):
+            while len(s) > 1:
+                best = min(((self._rank.get((a, b), 1 << 30), i) for i, (a, b) in enumerate(zip(s[:-1], s[1:]))))
+                if best[0] == 1 << 30:
+                    break
+                pair = self.merges[best[0]]
+                s = self._merge(s, pair, self.base + best[0])
+            out.append(s)
+        return out
+
+    def _expand(self, tid: int) -> list[int]:
+        if tid < self.base:
+            return [tid]
+        a, b = self.merges[tid - self.base]
+        return self._expand(a) + self._expand(b)
+
+    def decode(self, tokens: list[list[int]], time_horizon: int | None = None, action_dim: int | None = None) -> np.ndarray:
+        T, D = time_horizon or self.time_horizon, action_dim or self.action_dim
+        out = np.zeros((len(tokens), T, D))
+        m = DctActionTokenizer._dct_matrix(T)
+        for b, ids in enumerate(tokens):
+            sym = [x for t in ids if t > 0 for x in self._expand(int(t))][: T * D]
+            flat = np.zeros(T * D)
+            flat[:len(sym)] = np.asarray(sym, dtype=np.float64) - self.radius - 1
+            out[b] = m.T @ (flat.reshape(T, D) / self.scale)
+        return out
+
+    def save(self, path) -> None:
+        import json
+        from pathlib import Path
+        Path(path).parent.mkdir(parents=True, exist_ok=True)
+        Path(path).write_text(json.dumps({"type": "bpe_dct", "scale": self.scale, "radius": self.radius,
+                                          "merges": self.merges, "time_horizon": self.time_horizon,
+                                          "action_dim": self.action_dim}))
+
+    @classmethod
+    def load(cls, path) -> "BpeDctActionTokenizer":
+        import json
+        from pathlib import Path
+        d = json.loads(Path(path).read_text())
+        return cls(d["scale"], d["radius"], [tuple(m) for m in d["merges"]], d["time_horizon"], d["action_dim"])
