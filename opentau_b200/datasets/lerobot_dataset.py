@@ -569,7 +569,7 @@ class LeRobotDataset(BaseDataset):
             raise IndexError(idx)
         item: dict[str, Any] = {k: v[idx] for k, v in self._numeric.items()}
         for k in self._string_cols:
-            item[k] = self._table.column(k)[idx].as_py()
+            item[k] = self._table.column(k)[idx].as_py() or ""     # files without the column contribute nulls
         ep_idx = int(item["episode_index"])
         soft, padding = self._soft_indices(idx, ep_idx) if self.delta_timestamps else ({}, {})
         item.update(padding)
