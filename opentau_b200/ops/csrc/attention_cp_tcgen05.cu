@@ -318,14 +318,18 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     __syncthreads();
     if (s_any) {
       const int qm = s_qmax;
+      // per source: each thread keeps its own maximum and issues ONE shared-memory atomic (an atomic per visible key
+      // would serialise thousands of same-address operations per CTA)
+      for (int src = 0; src < W; ++src) {
+        int last = -1;
+        const long long base_k = (long long)b * p.Sk + (long long)src * p.Sl;
 #pragma unroll 8
-      for (int j = threadIdx.x; j < p.Sk; j += blockDim.x) {
-        const int kbj = p.k_blk[(long long)b * p.Sk + j];
-        const int kvj = p.k_valid[(long long)b * p.Sk + j];
-        if (kvj && kbj <= qm) {
-          const int src = j / p.Sl;
-          atomicMax(&nb_smem[src], (j - src * p.Sl) / BN + 1);
+        for (int j = threadIdx.x; j < p.Sl; j += blockDim.x) {
+          const int kbj = p.k_blk[base_k + j];
+          const int kvj = p.k_valid[base_k + j];
+          if (kvj && kbj <= qm) last = max(last, j);
         }
+        if (last >= 0) atomicMax(&nb_smem[src], last / BN + 1);
       }
     }
     __syncthreads();
