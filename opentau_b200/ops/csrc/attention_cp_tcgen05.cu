@@ -4,11 +4,12 @@
 //
 // Each rank keeps its K and V shard, laid out (B, Sl, Hkv, D), in peer-visible memory.  The grid has two kinds of
 // CTAs.  The first NC blocks are copiers: one thread each drives bulk async copies (peer -> shared -> local), 16 KB
-// at a time and a dozen in flight, that pull every rank's shard into a local gathered buffer (W, B, Sl, Hkv, D)
-// exactly once, in ring order starting with the own shard, and count the landed pieces per (source, batch, key
-// block).  The remaining blocks are attention CTAs (same tcgen05 / TMEM pipeline as the single-GPU kernel): their
-// TMA producer walks the sources in the same ring order and starts a key block as soon as its count is complete, so
-// the NVLink transfer of later shards overlaps the softmax / tensor-core work on earlier ones.  (Reading remote K/V
+// at a time and a dozen in flight, that pull every OTHER rank's shard into a local gathered buffer
+// (W, B, Sl, Hkv, D) exactly once, in ring order after the own rank, and count the landed pieces per (source,
+// batch, key block).  The remaining blocks are attention CTAs (same tcgen05 / TMEM pipeline as the single-GPU
+// kernel): their TMA producer reads the own shard in place first (no copy, no wait: the diagonal work starts at
+// once), then walks the other sources in the same ring order and starts a key block as soon as its count is
+// complete, so the NVLink transfer overlaps the softmax / tensor-core work on earlier keys.  (Reading remote K/V
 // tiles directly would cross the link once per query tile: peer lines are not kept in the local L2.)
 //
 // Key metadata (block id, validity) is passed for the full sequence in gathered order (source-major); it derives
@@ -42,6 +43,7 @@ struct AttnParams {
   float* lse;                       // (B, H, Sq)
   const unsigned* ready;            // local flags[W]: ready[r] >= epoch once rank r published its K/V shard
   unsigned* gcount;                 // local [W*B*nblk_src] landed pieces per (source, batch, key block); monotonic
+  unsigned* gtotal;                 // local [W*B] landed pieces per (source, batch); monotonic
   unsigned* ticket;                 // local piece dispenser; monotonic
   uint8_t* kg;                      // local gathered K (W, B, Sl, Hkv, D) bf16
   uint8_t* vg;                      // local gathered V
@@ -127,7 +129,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 template <int DPAD, int BN>
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                   const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ PtrArray k_peers,
+                   const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_k_own,
+                   const __grid_constant__ CUtensorMap tma_v_own, const __grid_constant__ PtrArray k_peers,
                    const __grid_constant__ PtrArray v_peers, AttnParams p) {
   using L = AttnSmem<DPAD, BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -163,33 +166,41 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   // ====================================================================== copier CTAs
   if ((int)blockIdx.x < p.NC) {
     if (threadIdx.x != 0) return;
-    constexpr int NBUF = L::NBUF, HALF = NBUF / 2;
+    constexpr int NBUF = L::NBUF;
+    // LD peer loads in flight (they carry the NVLink latency); a buffer is free again once its store has READ it
+    // (ST stores reading), while pieces are counted CL stores late, when their writes have certainly completed, so
+    // that no wait in the loop is on the latency of a store
+    constexpr int ST = 2, LD = NBUF - ST, CL = 8, RING = 4 * NBUF;
+    static_assert(LD + CL + 2 <= RING, "bookkeeping ring too small");
     uint64_t* cbar = bars;  // NBUF barriers (the attention barriers are unused in a copier CTA)
     for (int i = 0; i < NBUF; ++i) mbar_init(&cbar[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
-    const int ppb = (int)(((long long)BN * rowbytes + CP_PIECE - 1) / CP_PIECE);
-    const long long per_src = (long long)p.B * p.nblk_src * 2 * ppb;
-    const long long total = per_src * W;
+    // one ticket = K or V of one (ring step, batch, key block): up to ppb pieces.  A ticket per piece would put a
+    // global atomic round trip and the index arithmetic on the serial path of every 16 KB.
+    const long long per_src = (long long)p.B * p.nblk_src * 2;
+    const long long total = per_src * (W - 1);  // the own shard is read in place, never copied
     const unsigned per_step = (unsigned)total + (unsigned)p.NC;
     const unsigned base = (p.epoch - 1u) * per_step;
     const long long shard_bytes = (long long)p.B * p.Sl * rowbytes;
     unsigned seen = 1u << p.rank;
-    unsigned* cnt_of[2 * NBUF] = {};
-    uint8_t* dst_of[2 * NBUF] = {};
-    uint32_t bytes_of[2 * NBUF] = {};
+    unsigned* cnt_of[RING] = {};
+    uint8_t* dst_of[RING] = {};
+    uint32_t bytes_of[RING] = {};
     long long issued = 0, stored = 0, counted = 0;
     auto store_one = [&]() {
-      const int m = (int)(stored % NBUF), q = (int)(stored % (2 * NBUF));
+      const int m = (int)(stored % NBUF), q = (int)(stored % RING);
       mbar_wait(&cbar[m], (uint32_t)((stored / NBUF) & 1), abort_flag, p.status, KID_ATTN, 20, m);
       bulk_store(dst_of[q], smem + m * CP_PIECE, bytes_of[q]);
       bulk_commit();
       ++stored;
     };
     auto count_upto = [&](long long upto) {
+      if (counted < upto) fence_proxy_async_all();
       while (counted < upto) {
-        fence_proxy_async_all();
-        red_release_gpu_add(cnt_of[counted % (2 * NBUF)], 1u);
+        unsigned* c = cnt_of[counted % RING];
+        red_release_gpu_add(c, 1u);
+        red_release_gpu_add(p.gtotal + (c - p.gcount) / p.nblk_src, 1u);   // (source, batch) total
         ++counted;
       }
     };
@@ -197,20 +208,15 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       if (*abort_flag) break;
       const unsigned tk = atomicAdd(p.ticket, 1u) - base;
       if (tk >= (unsigned)total) break;
-      // ticket -> (ring step s, batch b, key block j, K|V, chunk c)
+      // ticket -> (ring step s, batch b, key block j, K|V)
       const int s = (int)(tk / per_src);
-      long long r = tk - (long long)s * per_src;
-      const int b = (int)(r / ((long long)p.nblk_src * 2 * ppb));
-      r -= (long long)b * p.nblk_src * 2 * ppb;
-      const int j = (int)(r / (2 * ppb));
-      r -= (long long)j * 2 * ppb;
-      const int is_v = (int)(r / ppb);
-      const int c = (int)(r - (long long)is_v * ppb);
-      const int src = (p.rank + s) % W;
+      int r = (int)(tk - (long long)s * per_src);
+      const int b = r / (p.nblk_src * 2);
+      r -= b * p.nblk_src * 2;
+      const int j = r >> 1;
+      const int is_v = r & 1;
+      const int src = (p.rank + 1 + s) % W;
       const long long blk_bytes = (long long)min(BN, p.Sl - j * BN) * rowbytes;
-      const long long off_in_blk = (long long)c * CP_PIECE;
-      if (off_in_blk >= blk_bytes) continue;  // a short last block has fewer pieces
-      const uint32_t bytes = (uint32_t)min((long long)CP_PIECE, blk_bytes - off_in_blk);
       if (!(seen & (1u << src))) {
         if ((int)(ld_acquire_sys_u32(p.ready + src) - p.epoch) < 0) {
           const long long t0 = clock64();
@@ -226,22 +232,27 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         seen |= 1u << src;
         if (*abort_flag) break;
       }
-      const long long off = ((long long)b * p.Sl + (long long)j * BN) * rowbytes + off_in_blk;
-      const uint8_t* gsrc = static_cast<const uint8_t*>(is_v ? v_peers.p[src] : k_peers.p[src]) + off;
-      uint8_t* gdst = (is_v ? p.vg : p.kg) + (long long)src * shard_bytes + off;
-      // the buffer about to be refilled was read by the store issued NBUF pieces ago
-      if (issued >= NBUF) bulk_wait_read<NBUF - HALF - 1>();
-      const int m = (int)(issued % NBUF), q = (int)(issued % (2 * NBUF));
-      cnt_of[q] = p.gcount + ((long long)src * p.B + b) * p.nblk_src + j;
-      dst_of[q] = gdst;
-      bytes_of[q] = bytes;
-      mbar_expect_tx(&cbar[m], bytes);
-      bulk_load(smem + m * CP_PIECE, gsrc, bytes, &cbar[m]);
-      ++issued;
-      if (issued - stored >= HALF) {
-        store_one();
-        bulk_wait<HALF>();  // every store but the latest HALF has completed: those pieces may be counted
-        count_upto(stored - HALF);
+      const long long off0 = ((long long)b * p.Sl + (long long)j * BN) * rowbytes;
+      const uint8_t* gsrc0 = static_cast<const uint8_t*>(is_v ? v_peers.p[src] : k_peers.p[src]) + off0;
+      uint8_t* gdst0 = (is_v ? p.vg : p.kg) + (long long)src * shard_bytes + off0;
+      unsigned* cnt = p.gcount + ((long long)src * p.B + b) * p.nblk_src + j;
+      for (long long off_in_blk = 0; off_in_blk < blk_bytes; off_in_blk += CP_PIECE) {
+        const uint32_t bytes = (uint32_t)min((long long)CP_PIECE, blk_bytes - off_in_blk);
+        // the buffer about to be refilled was read by the store issued NBUF pieces ago
+        if (issued >= NBUF) bulk_wait_read<ST - 1>();
+        const int m = (int)(issued % NBUF), q = (int)(issued % RING);
+        cnt_of[q] = cnt;
+        dst_of[q] = gdst0 + off_in_blk;
+        bytes_of[q] = bytes;
+        mbar_expect_tx(&cbar[m], bytes);
+        bulk_load(smem + m * CP_PIECE, gsrc0 + off_in_blk, bytes, &cbar[m]);
+        ++issued;
+        if (issued - stored >= LD) {
+          store_one();
+          bulk_wait<CL>();  // every store but the latest CL has completed: those pieces may be counted
+          count_upto(stored - CL);
+        }
+        if (*abort_flag) break;
       }
     }
     if (*abort_flag) {
@@ -282,6 +293,8 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     tma_prefetch_desc(&tma_q);
     tma_prefetch_desc(&tma_k);
     tma_prefetch_desc(&tma_v);
+    tma_prefetch_desc(&tma_k_own);
+    tma_prefetch_desc(&tma_v_own);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -349,35 +362,52 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       for (int c = 0; c < L::NCHUNK; ++c)
         tma_load_4d(sQ + c * (ATT_M * 128), &tma_q, q_full, c * 64, kvh * g, p0, b);
       int it = 0;
+      unsigned per_sb = 0;  // pieces of one (source, batch): K and V of every key block
+      for (int jj = 0; jj < p.nblk_src; ++jj) per_sb += 2u * (unsigned)cp_pieces(jj, BN, p.Sl, rowbytes);
       for (int s = 0; s < W; ++s) {
         const int src = (p.rank + s) % W;
         const int nb = nb_smem[src];
+        // every piece of (src, b) has landed: no more polling, no more proxy fences.  The own shard is read where
+        // the host wrote it, so the diagonal work starts at once while the copiers fetch the other ranks' keys.
+        const bool own = src == p.rank;
+        bool src_done = own;
         for (int j = 0; j < nb; ++j, ++it) {
           const int slot = it & 1, u = it >> 1;
-          // wait until the copiers have landed K and V of this (source, batch, key block)
-          const unsigned target = p.epoch * 2u * (unsigned)cp_pieces(j, BN, p.Sl, rowbytes);
-          const unsigned* cnt = p.gcount + ((long long)src * p.B + b) * p.nblk_src + j;
-          if ((int)(ld_acquire_gpu_u32(cnt) - target) < 0) {
-            const long long t0 = clock64();
-            while ((int)(ld_acquire_gpu_u32(cnt) - target) < 0) {
-              if (*abort_flag) break;
-              if (clock64() - t0 > p.budget) {
-                *abort_flag = 1;
-                report_timeout(p.status, KID_ATTN, 22, (unsigned)(src * 1024 + j));
-                break;
+          if (!src_done) {
+            if ((int)(ld_acquire_gpu_u32(p.gtotal + src * p.B + b) - p.epoch * per_sb) >= 0) {
+              src_done = true;
+            } else {
+              // wait until the copiers have landed K and V of this (source, batch, key block)
+              const unsigned target = p.epoch * 2u * (unsigned)cp_pieces(j, BN, p.Sl, rowbytes);
+              const unsigned* cnt = p.gcount + ((long long)src * p.B + b) * p.nblk_src + j;
+              if ((int)(ld_acquire_gpu_u32(cnt) - target) < 0) {
+                const long long t0 = clock64();
+                while ((int)(ld_acquire_gpu_u32(cnt) - target) < 0) {
+                  if (*abort_flag) break;
+                  if (clock64() - t0 > p.budget) {
+                    *abort_flag = 1;
+                    report_timeout(p.status, KID_ATTN, 22, (unsigned)(src * 1024 + j));
+                    break;
+                  }
+                  __nanosleep(100);
+                }
               }
-              __nanosleep(100);
             }
+            fence_proxy_async_all();  // the pieces were written through the async proxy by other CTAs
           }
-          fence_proxy_async_all();
           mbar_wait(&kv_empty[slot], (u & 1) ^ 1, abort_flag, p.status, KID_ATTN, 1, it);
           uint8_t* sk = sKV + slot * L::STAGE_BYTES;
           uint8_t* sv = sk + L::KV_TILE;
           mbar_expect_tx(&kv_full[slot], L::STAGE_BYTES);
 #pragma unroll
           for (int c = 0; c < L::NCHUNK; ++c) {
-            tma_load_5d(sk + c * (BN * 128), &tma_k, &kv_full[slot], c * 64, kvh, j * BN, b, src);
-            tma_load_5d(sv + c * (BN * 128), &tma_v, &kv_full[slot], c * 64, kvh, j * BN, b, src);
+            if (own) {
+              tma_load_4d(sk + c * (BN * 128), &tma_k_own, &kv_full[slot], c * 64, kvh, j * BN, b);
+              tma_load_4d(sv + c * (BN * 128), &tma_v_own, &kv_full[slot], c * 64, kvh, j * BN, b);
+            } else {
+              tma_load_5d(sk + c * (BN * 128), &tma_k, &kv_full[slot], c * 64, kvh, j * BN, b, src);
+              tma_load_5d(sv + c * (BN * 128), &tma_v, &kv_full[slot], c * 64, kvh, j * BN, b, src);
+            }
           }
         }
       }
@@ -451,6 +481,27 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const int n16 = p.Dmma / 16;
     const int o_lo = half ? (n16 + 1) / 2 : 0, o_hi = half ? n16 : (n16 + 1) / 2;   // this thread's O column groups
 
+    // key metadata (INT_MAX = invisible to everyone) of block (source, jb), fetched one block ahead so that the
+    // global-load latency overlaps the softmax work of the current block
+    auto load_meta = [&](int src, int jb) -> int {
+      const int kin = jb * BN + st;               // index inside the source's shard
+      if (st >= BN || kin >= p.Sl) return INT_MAX;
+      const long long key = (long long)b * p.Sk + (long long)src * p.Sl + kin;
+      const int kbv = p.k_blk[key];
+      const int kvv = p.k_valid[key];
+      return kvv ? kbv : INT_MAX;
+    };
+    // the block after (rs, jb) in ring order, skipping sources this tile does not reach; rs == W: none
+    auto next_block = [&](int& rs, int& jb) {
+      ++jb;
+      while (rs < W && jb >= nb_smem[(p.rank + rs) % W]) {
+        ++rs;
+        jb = 0;
+      }
+    };
+    int nrs = 0, njb = -1;
+    next_block(nrs, njb);                         // first block
+    int kb_next = nrs < W ? load_meta((p.rank + nrs) % W, njb) : INT_MAX;
     int j = 0;  // running block counter over all sources (pipeline slot / phase)
     for (int rs = 0; rs < W; ++rs) {
       const int src = (p.rank + rs) % W;
@@ -458,22 +509,16 @@ attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       for (int jb = 0; jb < nb; ++jb, ++j) {
       const int slot = j & 1, u = j >> 1;
       if (st < BN) {                              // whole warps: st < BN covers warps 0 .. BN/32-1 of the group
-        const int kin = jb * BN + st;             // index inside the source's shard
-        const long long key = (long long)src * p.Sl + kin;
-        int kbm = INT_MAX;                        // INT_MAX = invisible to everyone
-        if (kin < p.Sl) {
-          const int kbv = p.k_blk[(long long)b * p.Sk + key];
-          const int kvv = p.k_valid[(long long)b * p.Sk + key];
-          kbm = kvv ? kbv : INT_MAX;
-        }
-        kmeta[slot * BN + st] = kbm;
-        const int mn = __reduce_min_sync(0xffffffffu, kbm);
-        const int mxk = __reduce_max_sync(0xffffffffu, kbm);
+        kmeta[slot * BN + st] = kb_next;
+        const int mn = __reduce_min_sync(0xffffffffu, kb_next);
+        const int mxk = __reduce_max_sync(0xffffffffu, kb_next);
         if (lane == 0) {
           kmm[(slot * (BN / 32) + st / 32) * 2 + 0] = mn;
           kmm[(slot * (BN / 32) + st / 32) * 2 + 1] = mxk;
         }
       }
+      next_block(nrs, njb);
+      kb_next = nrs < W ? load_meta((p.rank + nrs) % W, njb) : INT_MAX;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       const int* km = kmeta + slot * BN + c0;
       mbar_wait(&s_full[slot], u & 1, abort_flag, p.status, KID_ATTN, 6, j);
@@ -656,8 +701,8 @@ static int cp_make_map5(CUtensorMap* m, const void* base, int D, int Hkv, int Sl
 }
 
 template <int DPAD, int BN>
-static int launch_attn_cp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PtrArray& kp,
-                          const PtrArray& vp, const AttnParams& p, cudaStream_t stream) {
+static int launch_attn_cp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tko,
+                          const CUtensorMap& tvo, const PtrArray& kp, const PtrArray& vp, const AttnParams& p, cudaStream_t stream) {
   using L = AttnSmem<DPAD, BN>;
   static bool configured = false;
   auto kern = attn_fwd_cp_kernel<DPAD, BN>;
@@ -669,7 +714,7 @@ static int launch_attn_cp(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   const int pos_per_tile = ATT_M / p.g;
   const int ntile = (p.Sq + pos_per_tile - 1) / pos_per_tile;
   const int grid = p.NC + ntile * p.Hkv * p.B;
-  kern<<<grid, 320, L::TOTAL, stream>>>(tq, tk, tv, kp, vp, p);
+  kern<<<grid, 320, L::TOTAL, stream>>>(tq, tk, tv, tko, tvo, kp, vp, p);
   return (int)cudaGetLastError();
 }
 
@@ -682,7 +727,7 @@ extern "C" int otb_attn_cp_block(int D) { return D > 128 ? 64 : 128; }
 
 // q: local queries (B,Sq,H,D) with strides (q_sb,q_ss,q_sh,1); o: (B,Sq,H,D) contiguous; lse: (B,H,Sq).
 // k_peers[r] / v_peers[r]: rank r's contiguous (B,Sl,Hkv,D) shard as mapped into this process (this step's parity).
-// kg / vg: local gathered buffers (W,B,Sl,Hkv,D).  gcount: local unsigned[W*B*ceil(Sl/BN) + 1], zeroed once and owned
+// kg / vg: local gathered buffers (W,B,Sl,Hkv,D).  gcount: local unsigned[W*B*(ceil(Sl/BN) + 1) + 1], zeroed once and owned
 // by this call site; `epoch` must go 1, 2, 3, ... on it.  k_blk / k_valid: (B, W*Sl) for all keys, source-major.
 extern "C" int otb_attn_fwd_cp(const void* q, void* o, float* lse, const int* q_blk, const int* k_blk,
                                const unsigned char* q_valid, const unsigned char* k_valid, int B, int Sq, int Sl, int H,
@@ -721,22 +766,28 @@ extern "C" int otb_attn_fwd_cp(const void* q, void* o, float* lse, const int* q_
   p.lse = lse;
   p.ready = static_cast<const unsigned*>(ready);
   p.gcount = static_cast<unsigned*>(gcount);
-  p.ticket = p.gcount + (size_t)W * B * p.nblk_src;
+  p.gtotal = p.gcount + (size_t)W * B * p.nblk_src;
+  p.ticket = p.gtotal + (size_t)W * B;
   p.kg = static_cast<uint8_t*>(kg);
   p.vg = static_cast<uint8_t*>(vg);
   p.budget = budget;
   p.status = static_cast<KernelStatus*>(status);
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, tko, tvo;
   int r = cp_make_map4(&tq, q, D, H, Sq, B, q_sh, q_ss, q_sb, g, ATT_M / g);
   if (r) return 1000 + r;
   r = cp_make_map5(&tk, kg, D, Hkv, Sl, B, W, bn);
   if (r) return 2000 + r;
   r = cp_make_map5(&tv, vg, D, Hkv, Sl, B, W, bn);
   if (r) return 3000 + r;
+  const long long row = (long long)Hkv * D;
+  r = cp_make_map4(&tko, k_peers[rank], D, Hkv, Sl, B, D, row, row * Sl, 1, bn);
+  if (r) return 4000 + r;
+  r = cp_make_map4(&tvo, v_peers[rank], D, Hkv, Sl, B, D, row, row * Sl, 1, bn);
+  if (r) return 5000 + r;
   switch (dpad) {
-    case 64: return launch_attn_cp<64, 128>(tq, tk, tv, kp, vp, p, stream);
-    case 128: return launch_attn_cp<128, 128>(tq, tk, tv, kp, vp, p, stream);
-    default: return launch_attn_cp<256, 64>(tq, tk, tv, kp, vp, p, stream);
+    case 64: return launch_attn_cp<64, 128>(tq, tk, tv, tko, tvo, kp, vp, p, stream);
+    case 128: return launch_attn_cp<128, 128>(tq, tk, tv, tko, tvo, kp, vp, p, stream);
+    default: return launch_attn_cp<256, 64>(tq, tk, tv, tko, tvo, kp, vp, p, stream);
   }
 }
 

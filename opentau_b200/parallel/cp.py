@@ -45,8 +45,12 @@ class _Site:
         self.kg = torch.empty(W * self.numel, dtype=torch.bfloat16, device=ctx.device)
         self.vg = torch.empty(W * self.numel, dtype=torch.bfloat16, device=ctx.device)
         bn = int(ctx.lib.otb_attn_cp_block(c_int(D)))
-        self.gcount = torch.zeros(W * B * ((Sl + bn - 1) // bn) + 1, dtype=torch.int32, device=ctx.device)
+        self.gcount = torch.zeros(W * B * ((Sl + bn - 1) // bn + 1) + 1, dtype=torch.int32, device=ctx.device)
         self.epoch = 0
+        # one copier CTA moves 10-30 GB/s (its shared memory bounds the bytes in flight): one per MB of remote K/V,
+        # between 4 and 32
+        remote_mb = (W - 1) * 2 * self.numel * 2 >> 20
+        self.copiers = ctx.num_copiers or min(32, max(4, remote_mb))
 
     def ptrs(self, buf, parity: int) -> list[int]:
         return [p + parity * self.numel * 2 for p in buf.peer_ptrs]
@@ -56,7 +60,7 @@ class _Site:
 
 
 class ContextParallel:
-    def __init__(self, device, group=None, backend: str = "auto", num_copiers: int = 16,
+    def __init__(self, device, group=None, backend: str = "auto", num_copiers: int | None = None,
                  wait_budget: int = DEFAULT_WAIT_BUDGET):
         self.device = torch.device(device)
         self.group = group
@@ -137,7 +141,7 @@ class ContextParallel:
             c_int(H), c_int(Hkv), c_int(D), c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
             _ptr_array(site.ptrs(site.k, par)), _ptr_array(site.ptrs(site.v, par)), c_void_p(site.kg.data_ptr()),
             c_void_p(site.vg.data_ptr()), c_void_p(site.gcount.data_ptr()), c_void_p(site.ready.local_ptr),
-            c_int(self.rank), c_int(self.world), c_uint(site.epoch), c_int(self.num_copiers), c_float(scale),
+            c_int(self.rank), c_int(self.world), c_uint(site.epoch), c_int(site.copiers), c_float(scale),
             c_longlong(self.wait_budget), c_void_p(self.status), self._stream())
         if rc != 0:
             raise RuntimeError(f"context-parallel attention launch failed ({rc})")

@@ -31,6 +31,7 @@ def main() -> None:
     ap.add_argument("--block", type=int, default=256, help="tokens per attention block (frame) of the mask")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--copiers", type=int, default=0, help="copier CTAs of the fused kernel (0: sized from the shape)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -39,7 +40,7 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=dev)
     from opentau_b200.ops import cuda_ops, prims
     from opentau_b200.parallel.cp import ContextParallel
-    cp = ContextParallel(dev, backend="p2p")
+    cp = ContextParallel(dev, backend="p2p", num_copiers=a.copiers or None)
     B, S, H, Hkv, D = a.batch, a.seq, a.heads, a.kv_heads, a.dim
     Sl = S // world
     torch.manual_seed(rank)
