@@ -6,7 +6,9 @@ insulation, 256 FAST-style action tokens co-trained with the flow loss, bf16, ba
 synthetic inputs, random-init weights.  One step = forward + backward + gradient sync + clip +
 AdamW + parameter refresh.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|oracle]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|oracle] [--mode train|infer]
+
+``--mode infer`` measures the second headline number instead: the p50 latency of one 10-step action chunk at batch 1.
 
 For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
 Rank 0 prints ONE JSON line.  ``--impl reference`` reports that the reference cannot be imported in
@@ -120,6 +122,89 @@ def build_policy(args, device):
     return policy, spec, cfg
 
 
+def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
+    """Second headline metric: p50 latency of one 10-step flow-matching action chunk (pi0.5 full, batch 1, three
+    cameras, 200 prompt tokens) through ``policy.sample_actions``.  Every rank serves its own replica; the reported
+    value is the slowest rank's median.  The device-timed region is the call alone on resident inputs; the end-to-end
+    region adds the pinned-host -> device copy of the observation and the device -> host read of the actions."""
+    import torch
+    import torch.distributed as dist
+    from opentau_b200.ops import cuda_ops
+    from opentau_b200.scripts.benchmark_inference import build_pi05, summarize
+
+    policy, batch = build_pi05(3, 200, device, tiny=args.tiny, num_steps=10)
+    if use_cuda and args.impl == "ours":
+        policy.enable_cuda_graphs(True)
+    host = {k: (v.cpu().pin_memory() if use_cuda else v.cpu()) for k, v in batch.items() if hasattr(v, "cpu")}
+    h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        if use_cuda:
+            torch.cuda.synchronize()
+
+    def one(e2e: bool) -> float:
+        if use_cuda:
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        t0 = time.perf_counter()
+        b = {k: v.to(device, non_blocking=True) for k, v in host.items()} if e2e else batch
+        out = policy.sample_actions(b)
+        if e2e:
+            out = out.float().cpu()                      # device -> host read of the action chunk
+        if use_cuda:
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1), out
+        return (time.perf_counter() - t0) * 1e3, out
+
+    for _ in range(max(args.warmup, 3)):
+        one(False)
+    if use_cuda and args.impl == "ours":
+        cuda_ops.check_status()
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and use_cuda:
+        sampler.start()
+    launches0 = cuda_ops.launch_count
+    sync()
+    dev_ms = [one(False)[0] for _ in range(args.steps)]
+    sync()
+    launches = cuda_ops.launch_count - launches0
+    one(True)
+    sync()
+    res = [one(True) for _ in range(args.steps)]
+    sync()
+    e2e_ms, out = [r[0] for r in res], res[-1][1]
+    clocks = sampler.stop() if (rank == 0 and use_cuda) else {}
+    d2h_bytes = out.numel() * out.element_size()
+    stats = torch.tensor([summarize(dev_ms)["p50_ms"], summarize(e2e_ms)["p50_ms"], sum(dev_ms) / len(dev_ms)],
+                         dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        n_params = sum(p.numel() for p in policy.parameters())
+        print(json.dumps({
+            "metric": "pi0.5 p50 10-step action-chunk latency", "value": round(float(stats[0]), 3), "unit": "ms",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(float(stats[2]), 3), "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+            "config": {"model": "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"
+                       if not args.tiny else "pi0.5 tiny (plumbing)",
+                       "global_batch": world, "seq_len": 3 * 256 + 200 + 50, "parallelism": f"replica x{world}",
+                       "params": n_params, "denoise_steps": 10, "action_chunk": "50x32",
+                       "cuda_graph": bool(use_cuda and args.impl == "ours"),
+                       "l2": "each call streams the 6.6 GB of bf16 weights, far more than the 126 MB L2; no "
+                             "explicit flush"},
+            "clocks": clocks,
+            "e2e": {"value": round(float(stats[1]), 3), "unit": "ms", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": d2h_bytes},
+            "gpu_launches": launches,
+        }))
+    return 0
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -146,6 +231,12 @@ def main():
         torch.cuda.set_device(device)
     if world > 1:
         dist.init_process_group("nccl" if use_cuda else "gloo", device_id=device if use_cuda else None)
+
+    if args.mode == "infer":
+        rc = run_infer(args, device, rank, world, local_rank, use_cuda)
+        if world > 1:
+            dist.destroy_process_group()
+        return rc
 
     from opentau_b200.datasets.synthetic import make_synthetic_batch
     from opentau_b200.parallel.engine import OptimHyper, TrainEngine

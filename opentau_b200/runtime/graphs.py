@@ -57,9 +57,11 @@ class CudaGraphRunner:
         if entry is None:
             entry = self._capture(args)
             self._graphs[key] = entry
-        graph, static_in, static_out = entry
+        graph, static_in, static_out, n_kernels = entry
         _copy_into(static_in, args)
         graph.replay()
+        from ..ops import cuda_ops
+        cuda_ops.launch_count += n_kernels     # the replay runs every kernel node recorded at capture
         return static_out
 
     def _capture(self, args):
@@ -71,10 +73,14 @@ class CudaGraphRunner:
                 self.fn(*static_in)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..ops import cuda_ops
         graph = torch.cuda.CUDAGraph()
+        before = cuda_ops.launch_count
         with torch.cuda.graph(graph):
             static_out = self.fn(*static_in)
-        return graph, static_in, static_out
+        n_kernels = cuda_ops.launch_count - before
+        cuda_ops.launch_count = before         # capture records, it does not run
+        return graph, static_in, static_out, n_kernels
 
     @property
     def num_graphs(self) -> int:
