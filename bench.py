@@ -40,6 +40,8 @@ def parse_args():
     ap.add_argument("--strategy", default="zero2")
     ap.add_argument("--tiny", action="store_true", help="small geometry (plumbing check, not a benchmark)")
     ap.add_argument("--mode", default="train", choices=["train", "infer"])
+    ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3"],
+                    help="--mode infer only: cosmos3 is the workload of the reference's published B200 latency table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (profiling runs only)")
     return ap.parse_args()
 
@@ -130,9 +132,13 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
     import torch
     import torch.distributed as dist
     from opentau_b200.ops import cuda_ops
-    from opentau_b200.scripts.benchmark_inference import build_pi05, summarize
+    from opentau_b200.scripts.benchmark_inference import BUILDERS, summarize
 
-    policy, batch = build_pi05(3, 200, device, tiny=args.tiny, num_steps=10)
+    # published by the reference for this exact cosmos3 workload on 1 x B200 with torch.compile reduce-overhead
+    # (docs/source/tutorials/benchmarking.rst:437-510): p50 106.86 ms
+    published_p50 = {"cosmos3": 106.86}.get(args.model)
+    prompt_len = 64 if args.model == "cosmos3" else 200
+    policy, batch = BUILDERS[args.model](3, prompt_len, device, tiny=args.tiny, num_steps=10)
     if use_cuda and args.impl == "ours":
         policy.enable_cuda_graphs(True)
     host = {k: (v.cpu().pin_memory() if use_cuda else v.cpu()) for k, v in batch.items() if hasattr(v, "cpu")}
@@ -186,16 +192,21 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
     if rank == 0:
         n_params = sum(p.numel() for p in policy.parameters())
         print(json.dumps({
-            "metric": "pi0.5 p50 10-step action-chunk latency", "value": round(float(stats[0]), 3), "unit": "ms",
+            "metric": f"{args.model} p50 10-step action-chunk latency", "value": round(float(stats[0]), 3),
+            "unit": "ms",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(float(stats[2]), 3), "higher_is_better": False, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
-            "config": {"model": "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"
-                       if not args.tiny else "pi0.5 tiny (plumbing)",
-                       "global_batch": world, "seq_len": 3 * 256 + 200 + 50, "parallelism": f"replica x{world}",
+            "vs_baseline": (round(float(stats[0]) / published_p50, 4) if published_p50 and not args.tiny else None),
+            "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+            "config": {"model": ("tiny (plumbing)" if args.tiny else
+                                 "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"
+                                 if args.model == "pi05" else
+                                 "cosmos3 (Qwen3-VL-32B-shaped backbone, 64-layer 0.9B expert, 3 cams @224, "
+                                 "prompt <= 64 tokens)"),
+                       "global_batch": world, "parallelism": f"replica x{world}",
                        "params": n_params, "denoise_steps": 10, "action_chunk": "50x32",
                        "cuda_graph": bool(use_cuda and args.impl == "ours"),
-                       "l2": "each call streams the 6.6 GB of bf16 weights, far more than the 126 MB L2; no "
+                       "l2": "each call streams every bf16 weight once (GBs, far more than the 126 MB L2); no "
                              "explicit flush"},
             "clocks": clocks,
             "e2e": {"value": round(float(stats[1]), 3), "unit": "ms", "h2d_bytes_per_step": h2d_bytes,

@@ -12,6 +12,7 @@ import math
 from dataclasses import dataclass, field
 
 import torch
+import torch.nn.functional as F
 from torch import Tensor, nn
 
 from .. import ops
@@ -35,6 +36,15 @@ class Linear(nn.Module):
         w, b = self.weight, self.bias
         if x.dtype != w.dtype:
             x = x.to(w.dtype)
+        pad_o, pad_i = -self.out_features % 8, -self.in_features % 8
+        if (pad_o or pad_i) and x.is_cuda:
+            # the tensor-core path moves rows of 16 bytes: widths that are not a multiple of 8 (a 201-bin value head)
+            # run on zero-padded copies; autograd slices the gradients back
+            w = F.pad(w, (0, pad_i, 0, pad_o))
+            b = F.pad(b, (0, pad_o)) if b is not None else None
+            x = F.pad(x, (0, pad_i)) if pad_i else x
+            y = ops.linear(x, w, b)[..., :self.out_features]
+            return y + residual if residual is not None else y
         return ops.linear(x, w, b, residual)
 
     def extra_repr(self) -> str:

@@ -334,11 +334,37 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_
 // ------------------------------------------------------------------------------------------ RoPE
 // x: (B,S,H,D) with element strides (sb, ss, sh, 1); cos/sin: (B,S,D/2) fp32; y contiguous (B,S,H,D).
 // Split-half rotation; inverse rotates by the negative angle.
+// V = pairs per thread: 8 (16-byte accesses, head_dim % 16 == 0) or 4 (8-byte accesses, head_dim % 8 == 0, e.g. the
+// 72-wide heads of the Qwen3-VL vision tower)
+template <int V>
+__device__ __forceinline__ void load_v(const __nv_bfloat16* p, float* v) {
+  if constexpr (V == 8) {
+    load8(p, v);
+  } else {
+    uint2 u = *reinterpret_cast<const uint2*>(p);
+    float2 f;
+    f = unpack_bf16(u.x); v[0] = f.x; v[1] = f.y;
+    f = unpack_bf16(u.y); v[2] = f.x; v[3] = f.y;
+  }
+}
+template <int V>
+__device__ __forceinline__ void store_v(__nv_bfloat16* p, const float* v) {
+  if constexpr (V == 8) {
+    store8(p, v);
+  } else {
+    uint2 o;
+    o.x = pack_bf16(v[0], v[1]);
+    o.y = pack_bf16(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = o;
+  }
+}
+
+template <int V>
 __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long sb, long long ss, long long sh,
                             const float* __restrict__ cosb, const float* __restrict__ sinb,
                             __nv_bfloat16* __restrict__ y, int B, int S, int H, int D, int inverse) {
   const int half = D >> 1;
-  const int vec_per_head = half >> 3;            // 8 pairs per thread
+  const int vec_per_head = half / V;             // V pairs per thread
   const long long total = (long long)B * S * H * vec_per_head;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total;
        t += (long long)gridDim.x * blockDim.x) {
@@ -348,21 +374,21 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long sb, l
     r /= H;
     int s = int(r % S);
     int b = int(r / S);
-    const __nv_bfloat16* xp = x + b * sb + s * ss + h * sh + v * 8;
-    float x1[8], x2[8], o1[8], o2[8];
-    load8(xp, x1);
-    load8(xp + half, x2);
-    const float* cp = cosb + ((long long)b * S + s) * half + v * 8;
-    const float* sp = sinb + ((long long)b * S + s) * half + v * 8;
+    const __nv_bfloat16* xp = x + b * sb + s * ss + h * sh + v * V;
+    float x1[V], x2[V], o1[V], o2[V];
+    load_v<V>(xp, x1);
+    load_v<V>(xp + half, x2);
+    const float* cp = cosb + ((long long)b * S + s) * half + v * V;
+    const float* sp = sinb + ((long long)b * S + s) * half + v * V;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
+    for (int e = 0; e < V; ++e) {
       float c = cp[e], sn = inverse ? -sp[e] : sp[e];
       o1[e] = x1[e] * c - x2[e] * sn;
       o2[e] = x2[e] * c + x1[e] * sn;
     }
-    __nv_bfloat16* yp = y + (((long long)b * S + s) * H + h) * D + v * 8;
-    store8(yp, o1);
-    store8(yp + half, o2);
+    __nv_bfloat16* yp = y + (((long long)b * S + s) * H + h) * D + v * V;
+    store_v<V>(yp, o1);
+    store_v<V>(yp + half, o2);
   }
 }
 
@@ -583,10 +609,16 @@ extern "C" int otb_glu_bwd(const void* gu, const void* dh, void* dgu, long long 
 
 extern "C" int otb_rope(const void* x, long long sb, long long ss, long long sh, const float* cosb,
                         const float* sinb, void* y, int B, int S, int H, int D, int inverse, cudaStream_t stream) {
-  if (D % 16 || (sb % 8) || (ss % 8) || (sh % 8)) return -1;
-  long long work = (long long)B * S * H * (D / 16);
-  rope_kernel<<<grid_for(work, 256), 256, 0, stream>>>((const bf16*)x, sb, ss, sh, cosb, sinb, (bf16*)y, B, S, H, D,
-                                                       inverse);
+  if (D % 8 || (sb % 8) || (ss % 8) || (sh % 8)) return -1;
+  if (D % 16 == 0) {
+    long long work = (long long)B * S * H * (D / 16);
+    rope_kernel<8><<<grid_for(work, 256), 256, 0, stream>>>((const bf16*)x, sb, ss, sh, cosb, sinb, (bf16*)y, B, S, H,
+                                                            D, inverse);
+  } else {
+    long long work = (long long)B * S * H * (D / 8);
+    rope_kernel<4><<<grid_for(work, 256), 256, 0, stream>>>((const bf16*)x, sb, ss, sh, cosb, sinb, (bf16*)y, B, S, H,
+                                                            D, inverse);
+  }
   return (int)cudaGetLastError();
 }
 

@@ -93,19 +93,19 @@ def mrope_angles(positions: Tensor, head_dim: int, theta: float, interleaved: bo
     half = head_dim // 2
     frac = 2.0 * torch.arange(half, dtype=torch.float32, device=positions.device) / head_dim
     timescale = theta**frac
+    # built from device-side arithmetic only (no host tensor, no data-dependent size): safe inside a CUDA-graph capture
+    ar = torch.arange(half, device=positions.device)
     if interleaved:
-        axis = torch.arange(half, device=positions.device) % 3
+        axis = ar % 3
         if sections is not None:
             # Qwen3-VL: interleave only inside the first 3*min-section bands, rest use axis 0.
             lim = [3 * s for s in sections]
             axis = torch.zeros(half, dtype=torch.long, device=positions.device)
             for a in (1, 2):
-                idx = torch.arange(a, lim[a], 3, device=positions.device)
-                axis[idx] = a
+                axis = torch.where((ar % 3 == a) & (ar < lim[a]), a, axis)
     else:
         assert sections is not None and sum(sections) == half
-        axis = torch.repeat_interleave(torch.arange(3, device=positions.device),
-                                       torch.tensor(sections, device=positions.device))
+        axis = (ar >= sections[0]).long() + (ar >= sections[0] + sections[1]).long()
     pos = positions.float().permute(1, 2, 0)  # (B,S,3)
     sel = pos[..., axis]  # (B,S,half)
     ang = sel / timescale

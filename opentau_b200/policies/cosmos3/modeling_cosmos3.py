@@ -314,10 +314,31 @@ class Cosmos3Policy(PreTrainedPolicy):
     def sample_actions(self, batch, noise=None, n_candidates: int | None = None, **_) -> Tensor:
         self.eval()
         idx, images, masks, lt, lm, state = self._common(batch)
-        actions = self.model.sample_actions(images, masks, lt, lm, state, noise=noise)
+        if getattr(self, "_use_graphs", False) and state.device.type == "cuda":
+            actions = self._graphed_sample(images, masks, lt, lm, state, noise)
+        else:
+            actions = self.model.sample_actions(images, masks, lt, lm, state, noise=noise)
         feat = self.config.action_feature
         real = feat.shape[0] if feat is not None else actions.shape[-1]
         return self.unnormalize_outputs({"actions": actions[:, :, :real]}, idx)["actions"]
+
+    def enable_cuda_graphs(self, flag: bool = True) -> None:
+        """Replay the sampler (backbone prefix pass + Euler loop over the expert) from one CUDA graph per input
+        signature; the reference's counterpart is ``torch.compile(mode="reduce-overhead")``
+        (``src/opentau/scripts/benchmark_inference.py:249-259``)."""
+        self._use_graphs = bool(flag)
+        self._graph_runner = None
+
+    def _graphed_sample(self, images, masks, lt, lm, state, noise):
+        from ...runtime.graphs import CudaGraphRunner
+        cfg = self.config
+        if noise is None:
+            noise = self.model.sample_noise((lt.shape[0], cfg.chunk_size, cfg.max_action_dim), lt.device)
+        if getattr(self, "_graph_runner", None) is None:
+            def fn(images, masks, lt, lm, state, noise):
+                return self.model.sample_actions(list(images), list(masks), lt, lm, state, noise=noise)
+            self._graph_runner = CudaGraphRunner(fn)
+        return self._graph_runner(tuple(images), tuple(masks), lt, lm.bool(), state, noise.float()).clone()
 
     @torch.no_grad()
     def select_action(self, batch, noise=None) -> Tensor:

@@ -35,7 +35,8 @@ def summarize(ms: list[float]) -> dict:
             "p50_ms": pct(0.5), "p95_ms": pct(0.95), "p99_ms": pct(0.99), "min_ms": s[0], "max_ms": s[-1]}
 
 
-def build_pi05(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 10):
+def build_pi05(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 10,
+               depth: int | None = None):
     from ..configs.types import FeatureType, PolicyFeature
     from ..datasets.synthetic import SyntheticSpec, identity_stats, make_synthetic_batch
     from ..policies.pi05.configuration_pi05 import PI05Config
@@ -63,6 +64,52 @@ def build_pi05(cams: int, prompt_len: int, device, tiny: bool = False, num_steps
     return policy, batch
 
 
+def build_cosmos3(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 10,
+                  depth: int | None = None):
+    """The workload of the reference's published cosmos3 latency table (``docs/source/tutorials/benchmarking.rst:
+    437-510``): the full 64-layer Qwen3-VL-32B-shaped backbone, the 64-layer action expert reading a per-layer KV
+    cache, ``cams`` cameras at 224x224, a prompt capped at ``prompt_len`` tokens, a 50-action chunk.  Weights are
+    random (no checkpoint offline)."""
+    from ..configs.types import FeatureType, PolicyFeature
+    from ..datasets.synthetic import SyntheticSpec, identity_stats, make_synthetic_batch
+    from ..policies.cosmos3.configuration_cosmos3 import Cosmos3Config
+    from ..policies.cosmos3.modeling_cosmos3 import Cosmos3Policy
+    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, 224, 224)) for i in range(cams)}
+    feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
+    kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=prompt_len, num_steps=num_steps, dropout=0.0,
+              device=str(device), input_features=feats, load_pretrained_backbone=False, image_resize=224,
+              output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
+    vocab = 151936
+    if tiny:
+        kw.update(backbone=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                head_dim=32, intermediate_size=256, vocab_size=512, mrope_sections=(6, 5, 5)),
+                  vision=dict(hidden_size=64, depth=2, num_heads=4, intermediate_size=128, out_hidden_size=128,
+                              num_position_embeddings=256, deepstack_visual_indexes=(0,)),
+                  expert_hidden_size=64, expert_intermediate_size=128, expert_num_hidden_layers=2,
+                  expert_num_attention_heads=4, expert_num_key_value_heads=2, expert_head_dim=32, proj_width=64,
+                  expert_adarms_cond_dim=32)
+        vocab = 512
+    if depth is not None:                       # same layers, fewer of them: a small case for profiling
+        kw.update(backbone=dict(num_hidden_layers=depth), expert_num_hidden_layers=depth)
+    cfg = Cosmos3Config(**kw)
+    spec = SyntheticSpec(batch_size=1, num_cams=cams, prompt_len=prompt_len, vocab_size=vocab, state_dim=32,
+                         action_dim=32, chunk_size=50, image_dtype=torch.bfloat16)
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)     # 33 B parameters: never materialise them in fp32
+    try:
+        with torch.device(device):
+            policy = Cosmos3Policy(cfg, per_dataset_stats=[identity_stats()])
+    finally:
+        torch.set_default_dtype(prev)
+    policy.to(device).to(torch.bfloat16).eval()
+    batch = make_synthetic_batch(spec, device=device, seed=3)
+    return policy, batch
+
+
+BUILDERS = {"pi05": build_pi05, "cosmos3": build_cosmos3}
+
+
 def run(policy, batch, n_warmup: int, n_timed: int, n_candidates: int = 1) -> dict:
     dev = batch["state"].device
     cuda = dev.type == "cuda"
@@ -82,19 +129,22 @@ def run(policy, batch, n_warmup: int, n_timed: int, n_candidates: int = 1) -> di
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--policy", default="pi05")
+    ap.add_argument("--policy", default="pi05", choices=sorted(BUILDERS))
     ap.add_argument("--cams", type=int, default=3)
-    ap.add_argument("--prompt-len", type=int, default=200)
+    ap.add_argument("--prompt-len", type=int, default=None, help="default: 200 (pi05), 64 (cosmos3)")
     ap.add_argument("--num-steps", type=int, default=10)
     ap.add_argument("--graphs", dest="graphs", action="store_true", default=True)
     ap.add_argument("--no-graphs", dest="graphs", action="store_false")
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--depth", type=int, default=None, help="cosmos3: truncate backbone and expert to this many layers")
     args = ap.parse_args(argv)
     n_warmup = int(os.environ.get("BENCH_N_WARMUP", "5"))
     n_timed = int(os.environ.get("BENCH_N_TIMED", "50"))
     n_cand = int(os.environ.get("BENCH_N_CANDIDATES", "1"))
     device = torch.device("cuda" if torch.cuda.is_available() else "cpu")
-    policy, batch = build_pi05(args.cams, args.prompt_len, device, args.tiny, args.num_steps)
+    if args.prompt_len is None:
+        args.prompt_len = 64 if args.policy == "cosmos3" else 200
+    policy, batch = BUILDERS[args.policy](args.cams, args.prompt_len, device, args.tiny, args.num_steps, args.depth)
     rec = {"policy": args.policy, "device": torch.cuda.get_device_name(0) if device.type == "cuda" else "cpu",
            "dtype": "bf16", "num_steps": args.num_steps, "n_candidates": n_cand, "cams": args.cams,
            "prompt_len": args.prompt_len}

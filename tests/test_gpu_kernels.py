@@ -140,10 +140,11 @@ def test_layer_norm_kernel(dev):
     torch.testing.assert_close(mean.cpu(), mr, rtol=1e-3, atol=1e-4)
 
 
-def test_rope_kernel_strided(dev):
+@pytest.mark.parametrize("D", [64, 72])     # 72: Qwen3-VL vision heads (8-byte accesses)
+def test_rope_kernel_strided(dev, D):
     from opentau_b200 import ops
     from opentau_b200.ops import cuda_ops
-    B, S, H, D = 2, 33, 4, 64
+    B, S, H = 2, 33, 4
     qkv = torch.randn(B, S, (H + 2) * D, device=dev).to(torch.bfloat16)
     q = qkv[..., :H * D].unflatten(-1, (H, D))
     pos = torch.arange(S, device=dev)[None].expand(B, -1)
