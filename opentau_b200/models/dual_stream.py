@@ -39,7 +39,15 @@ class KVCache:
         L, B, S, H, D = self.k.shape
         return KVCache(self.k.expand(L, n, S, H, D) if B == 1 else self.k.repeat_interleave(n, 1),
                        self.v.expand(L, n, S, H, D) if B == 1 else self.v.repeat_interleave(n, 1),
-                       self.valid.expand(n, S) if B == 1 else self.valid.repeat_interleave(n, 0), self.length)
+                       self.valid.expand(n, self.valid.shape[1]) if B == 1 else self.valid.repeat_interleave(n, 0),
+                       self.length)
+
+    def writable_room(self) -> int:
+        """Tokens that fit behind the cached prefix in place (0 when the buffers are expanded views)."""
+        k = self.k
+        dense = k.stride(4) == 1 and k.stride(3) == k.shape[4] and k.stride(2) == k.shape[3] * k.shape[4] \
+            and k.stride(1) >= k.shape[2] * k.stride(2)
+        return k.shape[2] - self.length if dense and self.v.stride() == k.stride() else 0
 
 
 class DualStreamDecoder(nn.Module):
@@ -77,9 +85,15 @@ class DualStreamDecoder(nn.Module):
         return list(chunks)
 
     def _layer(self, li: int, xs: list[Tensor | None], cos_sin, q_blk, k_blk, q_valid, k_valid,
-               cache_k, cache_v, mods) -> tuple[list[Tensor | None], Tensor | None, Tensor | None]:
+               cache_k, cache_v, mods, kv_dst=None) -> tuple[list[Tensor | None], Tensor | None, Tensor | None]:
+        """``kv_dst = (k_buf, v_buf, offset)``: inference with one tower present writes the new keys / values into
+        these ``(B, S_buf, Hkv, D)`` buffers at ``offset`` (behind a cached prefix, or at 0 when a cache is being
+        filled) and attends over ``[:offset + T]`` in place: no concatenation, no copy."""
         towers = self.towers
         qs, ks, vs, gates1, lens = [], [], [], [], []
+        present = [(tower, x) for tower, x in zip(towers, xs) if x is not None]
+        cos, sin = cos_sin
+        fused_post = len(present) == 1 and ops.can_fuse_qkv_post(present[0][1], present[0][0].cfg.head_dim)
         for ti, (tower, x) in enumerate(zip(towers, xs)):
             if x is None:
                 continue
@@ -88,18 +102,37 @@ class DualStreamDecoder(nn.Module):
                 h, g1 = layer.input_layernorm(x, precomputed=mods[ti][2 * li])
             else:
                 h, g1 = layer.input_layernorm(x)
+            gates1.append(g1), lens.append(x.shape[1])
+            if fused_post:
+                # one kernel: split + qk-norm + rotation + K/V store (into the cache when there is room)
+                attn, cfg = layer.self_attn, tower.cfg
+                T = x.shape[1]
+                k_dst = v_dst = None
+                if kv_dst is not None:
+                    off = kv_dst[2]
+                    k_dst, v_dst = kv_dst[0][:, off:off + T], kv_dst[1][:, off:off + T]
+                q, new_k, new_v = ops.qkv_post(attn.qkv_proj(h), cfg.num_attention_heads, cfg.num_key_value_heads,
+                                               cfg.head_dim, attn.q_norm if cfg.qk_norm else None,
+                                               attn.k_norm if cfg.qk_norm else None, cos, sin, k_dst, v_dst)
+                if kv_dst is not None:
+                    k, v = kv_dst[0][:, :off + T], kv_dst[1][:, :off + T]
+                elif cache_k is not None:
+                    k, v = torch.cat([cache_k, new_k], dim=1), torch.cat([cache_v, new_v], dim=1)
+                else:
+                    k, v = new_k, new_v
+                continue
             q, k, v = layer.self_attn.qkv(h)
-            qs.append(q), ks.append(k), vs.append(v), gates1.append(g1), lens.append(x.shape[1])
-        q = qs[0] if len(qs) == 1 else torch.cat(qs, dim=1)
-        k = ks[0] if len(ks) == 1 else torch.cat(ks, dim=1)
-        v = vs[0] if len(vs) == 1 else torch.cat(vs, dim=1)
-        cos, sin = cos_sin
-        q = ops.rope(q, cos, sin)
-        k = ops.rope(k, cos, sin)
-        new_k, new_v = k, v
-        if cache_k is not None:
-            k = torch.cat([cache_k, k], dim=1)
-            v = torch.cat([cache_v, v], dim=1)
+            qs.append(q), ks.append(k), vs.append(v)
+        if not fused_post:
+            q = qs[0] if len(qs) == 1 else torch.cat(qs, dim=1)
+            k = ks[0] if len(ks) == 1 else torch.cat(ks, dim=1)
+            v = vs[0] if len(vs) == 1 else torch.cat(vs, dim=1)
+            q = ops.rope(q, cos, sin)
+            k = ops.rope(k, cos, sin)
+            new_k, new_v = k, v
+            if cache_k is not None:
+                k = torch.cat([cache_k, k], dim=1)
+                v = torch.cat([cache_v, v], dim=1)
         first = next(t for t, x in zip(towers, xs) if x is not None)
         att = ops.block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, first.cfg.attn_scale)
         outs: list[Tensor | None] = []
@@ -151,7 +184,7 @@ class DualStreamDecoder(nn.Module):
                 past: KVCache | None = None, fill_cache_len: int | None = None,
                 k_blk: Tensor | None = None, k_valid: Tensor | None = None,
                 mrope: bool = False, per_layer_cache: bool = True, past_layer_map: list[int] | None = None,
-                layer_hook=None) -> tuple[list[Tensor | None], KVCache | None]:
+                layer_hook=None, cache_room: int = 0) -> tuple[list[Tensor | None], KVCache | None]:
         """One pass over all layers.
 
         ``position_ids``: ``(B, S_total)`` (or ``(3,B,S_total)`` with ``mrope``) for the
@@ -161,6 +194,8 @@ class DualStreamDecoder(nn.Module):
         first ``n`` tokens' post-RoPE K/V of every layer.  ``past_layer_map[l]`` names the cache layer that
         decoder layer ``l`` reads (default ``l``; a constant map conditions every layer on one backbone
         layer).  ``layer_hook(l, xs) -> xs`` runs after layer ``l`` (deepstack feature injection).
+        ``cache_room`` allocates the returned cache with that many spare token slots, so that a later
+        single-tower inference pass can append its keys / values in place instead of concatenating.
         """
         towers = self.towers
         xs = list(inputs_embeds)
@@ -195,11 +230,18 @@ class DualStreamDecoder(nn.Module):
             hk = present[0].cfg.num_key_value_heads
             ref_x = next(x for x in xs if x is not None)
             new_cache = KVCache(
-                ref_x.new_empty(self.num_layers, B, fill_cache_len, hk, hd),
-                ref_x.new_empty(self.num_layers, B, fill_cache_len, hk, hd),
+                ref_x.new_empty(self.num_layers, B, fill_cache_len + cache_room, hk, hd),
+                ref_x.new_empty(self.num_layers, B, fill_cache_len + cache_room, hk, hd),
                 q_valid[:, :fill_cache_len], fill_cache_len)
         keep_graph = fill_cache_len is not None and torch.is_grad_enabled()
         ks_list, vs_list = [], []
+        live = [x for x in xs if x is not None]
+        T_new = sum(x.shape[1] for x in live)
+        one_tower_inference = len(live) == 1 and ops.can_fuse_qkv_post(live[0], hd)
+        # in-place K/V: append behind the cached prefix (room permitting), or write a fresh cache directly
+        append_in_place = one_tower_inference and past is not None and past.writable_room() >= T_new
+        fill_in_place = (one_tower_inference and past is None and fill_cache_len is not None and not keep_graph
+                         and fill_cache_len == T_new)
 
         for li in range(self.num_layers):
             theta = towers[0].cfg.layer_theta(li)
@@ -211,16 +253,21 @@ class DualStreamDecoder(nn.Module):
                 xs, nk, nv = checkpoint(self._layer, li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid,
                                         ck, cv, mods, use_reentrant=False)
             else:
-                xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods)
+                kv_dst = None
+                if append_in_place:
+                    kv_dst = (past.k[pl], past.v[pl], past.length)
+                elif fill_in_place:
+                    kv_dst = (new_cache.k[li], new_cache.v[li], 0)
+                xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods, kv_dst)
             if layer_hook is not None:
                 xs = layer_hook(li, xs)
-            if fill_cache_len is not None:
+            if fill_cache_len is not None and not fill_in_place:
                 if keep_graph:
                     ks_list.append(nk[:, :fill_cache_len])
                     vs_list.append(nv[:, :fill_cache_len])
                 else:
-                    new_cache.k[li].copy_(nk[:, :fill_cache_len])
-                    new_cache.v[li].copy_(nv[:, :fill_cache_len])
+                    new_cache.k[li, :, :fill_cache_len].copy_(nk[:, :fill_cache_len])
+                    new_cache.v[li, :, :fill_cache_len].copy_(nv[:, :fill_cache_len])
         if keep_graph:
             new_cache = KVCache(torch.stack(ks_list), torch.stack(vs_list), new_cache.valid, fill_cache_len)
 

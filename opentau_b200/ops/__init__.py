@@ -49,8 +49,33 @@ def layer_norm(x: Tensor, weight: Tensor, bias: Tensor, eps: float = 1e-6) -> Te
     return fused.layer_norm(x, weight, bias, eps)
 
 
+def _native_nograd(*ts: Tensor) -> bool:
+    """Inference fusions: CUDA bf16 tensors, nothing to differentiate, not the oracle arm."""
+    import torch
+    return (not oracle_mode() and ts[0].is_cuda and ts[0].dtype == torch.bfloat16
+            and not (torch.is_grad_enabled() and any(t.requires_grad for t in ts if t is not None)))
+
+
 def gated_residual(x: Tensor, y: Tensor, gate: Tensor | None) -> Tensor:
+    if gate is not None and x.dim() == 3 and _native_nograd(x, y, gate) and x.shape[-1] % 8 == 0 \
+            and gate.dtype == x.dtype and y.dtype == x.dtype:
+        from . import cuda_ops
+        return cuda_ops.gated_residual(x, y, gate)
     return ref.gated_residual(x, y, gate)
+
+
+def qkv_post(qkv: Tensor, heads: int, kv_heads: int, head_dim: int, q_norm, k_norm, cos: Tensor, sin: Tensor,
+             k_dst: Tensor | None = None, v_dst: Tensor | None = None):
+    """Inference-only fusion after the q/k/v projection of one tower: split, optional per-head RMSNorm of q and k
+    (``q_norm / k_norm``: modules with ``weight, eps, unit_offset``, or None), rotation of q and k, and the store of k
+    and v, optionally straight into ``k_dst / v_dst`` (strided ``(B,T,Hkv,D)`` views, e.g. the tail of a KV cache).
+    Returns ``(q (B,T,H,D), k, v)``."""
+    from . import cuda_ops
+    return cuda_ops.qkv_post(qkv, heads, kv_heads, head_dim, q_norm, k_norm, cos, sin, k_dst, v_dst)
+
+
+def can_fuse_qkv_post(x: Tensor, head_dim: int) -> bool:
+    return _native_nograd(x) and head_dim % 8 == 0 and head_dim <= 256
 
 
 def rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
@@ -129,7 +154,7 @@ def resize_with_pad(img: Tensor, width: int, height: int, pad_value: float = -1.
 
 
 __all__ = [
-    "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "rope",
+    "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
     "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
     "resize_with_pad", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
     "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "oracle_mode", "prims", "fused", "ref",

@@ -31,6 +31,12 @@ def supported_bwd(q: Tensor, k: Tensor, v: Tensor) -> bool:
     return g <= 32 and 32 % g == 0
 
 
+def _u8(m: Tensor) -> Tensor:
+    """Validity mask as bytes; a bool tensor is reinterpreted (one byte per element, 0 / 1), not converted."""
+    m = m.contiguous()
+    return m.view(torch.uint8) if m.dtype == torch.bool else m.to(torch.uint8)
+
+
 def _prep(t: Tensor) -> Tensor:
     if t.stride(3) != 1 or any(s % 8 for s in t.stride()[:3]) or t.data_ptr() % 16:
         t = t.contiguous()
@@ -47,8 +53,8 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor, q_va
     lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device)
     qb = q_blk.to(torch.int32).contiguous()
     kb = k_blk.to(torch.int32).contiguous()
-    qv = q_valid.to(torch.uint8).contiguous()
-    kv = k_valid.to(torch.uint8).contiguous()
+    qv = _u8(q_valid)
+    kv = _u8(k_valid)
     rc = _lib.load("attention_tcgen05").otb_attn_fwd(
         c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
         c_void_p(lse.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()), c_void_p(qv.data_ptr()),
@@ -79,8 +85,8 @@ def attn_bwd(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor
     delta = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device)
     qb = q_blk.to(torch.int32).contiguous()
     kb = k_blk.to(torch.int32).contiguous()
-    qv = q_valid.to(torch.uint8).contiguous()
-    kv = k_valid.to(torch.uint8).contiguous()
+    qv = _u8(q_valid)
+    kv = _u8(k_valid)
     rc = _lib.load("attention_bwd_tcgen05").otb_attn_bwd(
         c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
         c_void_p(do.data_ptr()), c_void_p(lse.data_ptr()), c_void_p(delta.data_ptr()), c_void_p(dq.data_ptr()),

@@ -392,6 +392,73 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long sb, l
   }
 }
 
+// ------------------------------------------------------------------------------------------ inference fusions
+// After the fused q/k/v projection of ONE tower (no autograd): per (token, head) split the row, RMS-normalise q and
+// k heads (Qwen3 / Gemma-3 qk-norm; optional), rotate q and k, and write q densely and k / v through strides, so
+// that new keys and values can land directly behind the cached prefix.  One warp per (token, head slot).
+__global__ void qkv_post_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, const __nv_bfloat16* __restrict__ qw,
+                                const __nv_bfloat16* __restrict__ kw, float eps, int unit_offset,
+                                const float* __restrict__ cosb, const float* __restrict__ sinb,
+                                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out, long long k_sb,
+                                long long k_ss, __nv_bfloat16* __restrict__ v_out, long long v_sb, long long v_ss, int B,
+                                int T, int H, int Hkv, int D) {
+  const int slots = H + 2 * Hkv;
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * T * slots) return;
+  const int slot = int(wid % slots);
+  const long long tok = wid / slots;
+  const int t = int(tok % T), b = int(tok / T);
+  const __nv_bfloat16* src = qkv + tok * ld + (long long)slot * D;
+  const int half = D >> 1;
+  const int kind = slot < H ? 0 : (slot < H + Hkv ? 1 : 2);   // q | k | v
+  __nv_bfloat16* dst;
+  if (kind == 0) dst = q_out + (tok * H + slot) * D;
+  else if (kind == 1) dst = k_out + b * k_sb + t * k_ss + (long long)(slot - H) * D;
+  else dst = v_out + b * v_sb + t * v_ss + (long long)(slot - H - Hkv) * D;
+  if (kind == 2) {
+    for (int i = lane; i < D; i += 32) dst[i] = src[i];
+    return;
+  }
+  float x1[4], x2[4];                                          // D <= 256: at most 4 pairs per lane
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = lane + 32 * j;
+    x1[j] = i < half ? __bfloat162float(src[i]) : 0.f;
+    x2[j] = i < half ? __bfloat162float(src[i + half]) : 0.f;
+    ss += x1[j] * x1[j] + x2[j] * x2[j];
+  }
+  const __nv_bfloat16* w = kind == 0 ? qw : kw;
+  if (w != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = lane + 32 * j;
+      if (i < half) {
+        const float w1 = __bfloat162float(w[i]) + (unit_offset ? 1.f : 0.f);
+        const float w2 = __bfloat162float(w[i + half]) + (unit_offset ? 1.f : 0.f);
+        // the unfused path stores the normalised head in bf16 before rotating it
+        x1[j] = __bfloat162float(__float2bfloat16(x1[j] * rstd * w1));
+        x2[j] = __bfloat162float(__float2bfloat16(x2[j] * rstd * w2));
+      }
+    }
+  }
+  const float* cp = cosb + tok * half;
+  const float* sp = sinb + tok * half;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = lane + 32 * j;
+    if (i < half) {
+      const float c = cp[i], sn = sp[i];
+      dst[i] = __float2bfloat16(x1[j] * c - x2[j] * sn);
+      dst[i + half] = __float2bfloat16(x2[j] * c + x1[j] * sn);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ cross entropy
 // logits fp32 [R][V] -> loss[r] = lse - logit[label], lse[r].  One block per row.
 __global__ void ce_fwd_kernel(const float* __restrict__ logits, const long long* __restrict__ labels,
@@ -619,6 +686,19 @@ extern "C" int otb_rope(const void* x, long long sb, long long ss, long long sh,
     rope_kernel<4><<<grid_for(work, 256), 256, 0, stream>>>((const bf16*)x, sb, ss, sh, cosb, sinb, (bf16*)y, B, S, H,
                                                             D, inverse);
   }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_qkv_post(const void* qkv, long long ld, const void* qw, const void* kw, float eps, int unit_offset,
+                            const float* cosb, const float* sinb, void* q_out, void* k_out, long long k_sb,
+                            long long k_ss, void* v_out, long long v_sb, long long v_ss, int B, int T, int H, int Hkv,
+                            int D, cudaStream_t stream) {
+  if (D % 2 || D > 256 || B <= 0 || T <= 0) return -1;
+  const long long warps = (long long)B * T * (H + 2 * Hkv);
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  qkv_post_kernel<<<blocks, 256, 0, stream>>>((const bf16*)qkv, ld, (const bf16*)qw, (const bf16*)kw, eps, unit_offset,
+                                              cosb, sinb, (bf16*)q_out, (bf16*)k_out, k_sb, k_ss, (bf16*)v_out, v_sb,
+                                              v_ss, B, T, H, Hkv, D);
   return (int)cudaGetLastError();
 }
 

@@ -9,6 +9,7 @@ bounded waits write when they give up.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -60,11 +61,25 @@ def check_status(reset: bool = True) -> None:
 
 
 # --------------------------------------------------------------------------------------------- GEMM
+SKINNY = os.environ.get("OPENTAU_B200_SKINNY_GEMM", "1") != "0"
+
+
+def use_skinny(layout: str, M: int, N: int, accumulate: bool, bn: int) -> bool:
+    """``x @ W^T`` with few rows goes to the weight-streaming split-K kernel: always up to 256 rows (the weights
+    cross shared memory once), and up to 1024 rows while the 128-row tiling would leave most SMs without a tile."""
+    if not SKINNY or layout != "nt" or accumulate or bn:
+        return False
+    if M <= 256:
+        return True
+    return M <= 1024 and ((M + 127) // 128) * ((N + 127) // 128) < 100
+
+
 def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual: Tensor | None = None,
          out: Tensor | None = None, accumulate: bool = False, out_dtype: torch.dtype | None = None,
          glu: str | None = None, glu_out: Tensor | None = None, store_out: bool = True, act: str | None = None,
-         bn: int = 0) -> Tensor:
-    """tcgen05 GEMM.  layout 'nt': a(M,K) b(N,K); 'nn': a(M,K) b(K,N); 'tn': a(K,M) b(K,N)."""
+         bn: int = 0, splits: int = 0) -> Tensor:
+    """tcgen05 GEMM.  layout 'nt': a(M,K) b(N,K); 'nn': a(M,K) b(K,N); 'tn': a(K,M) b(K,N).  ``bn`` forces the column
+    tile of the persistent kernel, ``splits`` (1, 2, 4, 8) forces the weight-streaming split-K kernel."""
     global launch_count
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm expects bf16 operands"
     if a.stride(-1) != 1 or (a.stride(0) % 8) or (a.data_ptr() % 16):
@@ -129,6 +144,18 @@ def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual
         if glu_out is None:
             glu_out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=a.device)
         ldo2 = glu_out.stride(0)
+    if splits and (layout != "nt" or accumulate):
+        raise ValueError("the split-K kernel computes a @ b^T without accumulation")
+    if splits or use_skinny(layout, M, N, accumulate, bn):
+        rc = _lib.load("gemm_skinny_tcgen05").otb_gemm_skinny_bf16(
+            _p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
+            c_longlong(out.stride(0) if out is not None else N), _p(bias), _p(residual), c_longlong(ldr), _p(glu_out),
+            c_longlong(ldo2), c_int(flags), c_int(splits), c_void_p(status_pointer()), _stream())
+        _check(rc, f"gemm_skinny[{M}x{N}x{K}]")
+        launch_count += 1
+        if glu is not None:
+            return glu_out if not store_out else (out, glu_out)
+        return out
     rc = _lib.load("gemm_tcgen05").otb_gemm_bf16(
         _p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
         c_longlong(out.stride(0) if out is not None else N), c_int(a_mn), c_int(b_mn), _p(bias), _p(residual),
@@ -398,6 +425,37 @@ def gated_residual(x: Tensor, y: Tensor, gate: Tensor) -> Tensor:
                                                        _stream()), "gated_residual")
     launch_count += 1
     return out.view(x.shape)
+
+
+def qkv_post(qkv: Tensor, H: int, Hkv: int, D: int, q_norm, k_norm, cos: Tensor, sin: Tensor,
+             k_dst: Tensor | None = None, v_dst: Tensor | None = None):
+    global launch_count
+    B, T, W = qkv.shape
+    assert W == (H + 2 * Hkv) * D and qkv.dtype == torch.bfloat16
+    if qkv.stride(-1) != 1 or qkv.stride(0) != T * qkv.stride(1):
+        qkv = qkv.contiguous()
+    cos = cos.float().contiguous()
+    sin = sin.float().contiguous()
+    if cos.shape != (B, T, D // 2):
+        cos = cos.expand(B, T, D // 2).contiguous()
+        sin = sin.expand(B, T, D // 2).contiguous()
+    q = torch.empty(B, T, H, D, dtype=qkv.dtype, device=qkv.device)
+    if k_dst is None:
+        k_dst = torch.empty(B, T, Hkv, D, dtype=qkv.dtype, device=qkv.device)
+        v_dst = torch.empty(B, T, Hkv, D, dtype=qkv.dtype, device=qkv.device)
+    for t in (k_dst, v_dst):
+        if t.shape != (B, T, Hkv, D) or t.stride(3) != 1 or t.stride(2) != D or t.dtype != qkv.dtype:
+            raise ValueError("k / v destination must be (B,T,Hkv,D) with dense heads")
+    norm = q_norm is not None
+    qw = q_norm.weight.to(qkv.dtype) if norm else None
+    kw = k_norm.weight.to(qkv.dtype) if norm else None
+    _check(_lib.load("elementwise").otb_qkv_post(
+        _p(qkv), c_longlong(qkv.stride(1)), _p(qw), _p(kw), c_float(q_norm.eps if norm else 0.0),
+        c_int(int(q_norm.unit_offset) if norm else 0), _p(cos), _p(sin), _p(q), _p(k_dst), c_longlong(k_dst.stride(0)),
+        c_longlong(k_dst.stride(1)), _p(v_dst), c_longlong(v_dst.stride(0)), c_longlong(v_dst.stride(1)), c_int(B),
+        c_int(T), c_int(H), c_int(Hkv), c_int(D), _stream()), "qkv_post")
+    launch_count += 1
+    return q, k_dst, v_dst
 
 
 # --------------------------------------------------------------------------------------------- attention

@@ -113,7 +113,8 @@ class Qwen3VLWithExpertModel(nn.Module):
                 return xs
 
             _, cache = self.backbone_decoder([embs], pos, blk, valid, fill_cache_len=S, mrope=True,
-                                             layer_hook=hook if deep else None)
+                                             layer_hook=hook if deep else None,
+                                             cache_room=0 if torch.is_grad_enabled() else self.config.chunk_size + 8)
         return cache, pos
 
     def run_expert(self, cache: KVCache, suffix_embs: Tensor, suffix_pos: Tensor, cond: Tensor) -> Tensor:

@@ -423,7 +423,8 @@ class PI05FlowMatching(nn.Module):
             pos = torch.cumsum(prefix_pad, dim=1) - 1
         self._mrope = pos.dim() == 3
         _, cache = self.wrapper(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
-                                              q_valid=valid, fill_cache_len=prefix_embs.shape[1], mrope=self._mrope)
+                                              q_valid=valid, fill_cache_len=prefix_embs.shape[1], mrope=self._mrope,
+                                              cache_room=self.config.chunk_size + 8)   # the suffix appends in place
         return cache, self.suffix_offset(pos, prefix_pad, prefix_embs.shape[1])
 
     @staticmethod

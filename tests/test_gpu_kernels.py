@@ -68,6 +68,60 @@ def test_gemm_epilogues(dev):
     cuda_ops.check_status()
 
 
+@pytest.mark.parametrize("shape", [(51, 1024, 2048), (1, 256, 64), (64, 4096, 1024), (100, 1152, 4304), (128, 128, 128),
+                                   (211, 5120, 1000), (588, 1152, 1152), (300, 200, 72)])
+@pytest.mark.parametrize("splits", [0, 1, 2, 4, 8])
+def test_skinny_gemm_matches_fp32(shape, splits, dev):
+    """Weight-streaming split-K kernel: all token-tile widths, several token chunks, ragged N and K, every cluster size."""
+    from opentau_b200.ops import cuda_ops
+    M, N, K = shape
+    a, b = _operands("nt", M, N, K, dev)
+    out = cuda_ops.gemm(a, b, "nt", splits=splits or (0 if cuda_ops.use_skinny("nt", M, N, False, 0) else 2))
+    again = cuda_ops.gemm(a, b, "nt", splits=splits or (0 if cuda_ops.use_skinny("nt", M, N, False, 0) else 2))
+    cuda_ops.check_status()
+    ref = _ref_gemm(a, b, "nt")
+    err = (out.float() - ref).abs().max().item()
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    assert err <= tol, f"{shape} splits={splits}: max err {err} (tol {tol})"
+    assert torch.equal(out, again)                    # the cluster reduction has a fixed order
+
+
+@pytest.mark.parametrize("splits", [1, 4])
+def test_skinny_gemm_epilogues(splits, dev):
+    from opentau_b200.ops import cuda_ops
+    M, N, K = 51, 520, 320
+    a, b = _operands("nt", M, N, K, dev)
+    bias = torch.randn(N, device=dev).to(torch.bfloat16)
+    res = torch.randn(M, N, device=dev).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    out = cuda_ops.gemm(a, b, "nt", bias=bias, residual=res, splits=splits)
+    torch.testing.assert_close(out.float(), ref + bias.float() + res.float(), rtol=2e-2, atol=8e-2)
+    out32 = cuda_ops.gemm(a, b, "nt", bias=bias.float(), out_dtype=torch.float32, splits=splits)
+    torch.testing.assert_close(out32, ref + bias.float(), rtol=1e-3, atol=1e-2)
+    g = cuda_ops.gemm(a, b, "nt", bias=bias, act="gelu_tanh", splits=splits)
+    torch.testing.assert_close(g.float(), torch.nn.functional.gelu(ref + bias.float(), approximate="tanh"),
+                               rtol=2e-2, atol=8e-2)
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("splits", [1, 2, 8])
+@pytest.mark.parametrize("M", [51, 200])
+def test_skinny_gemm_glu(act, splits, M, dev):
+    from opentau_b200.ops import cuda_ops, prims
+    K, I = 256, 384
+    x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(dev)
+    w = (torch.randn(2 * I, K) * 0.1).to(torch.bfloat16).to(dev)
+    gu, h = cuda_ops.gemm(x, w, "nt", glu=act, splits=splits)
+    gu_ref = (x.float() @ w.float().t()).to(torch.bfloat16)
+    torch.testing.assert_close(gu.float(), gu_ref.float(), rtol=2e-2, atol=3e-2)
+    h_ref = prims.glu_fwd(gu_ref.cpu().float(), act).to(dev)
+    torch.testing.assert_close(h.float(), h_ref, rtol=3e-2, atol=3e-2)
+    h_only = cuda_ops.gemm(x, w, "nt", glu=act, store_out=False, splits=splits)
+    torch.testing.assert_close(h_only.float(), h.float())
+    cuda_ops.check_status()
+
+
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
 def test_gemm_glu_epilogue(act, dev):
     from opentau_b200.ops import cuda_ops, prims
@@ -217,3 +271,48 @@ def test_native_libraries_are_loaded(dev):
         maps = f.read()
     assert "libotb_gemm_tcgen05.so" in maps
     assert any("gemm_tcgen05" in p for p in _lib.loaded_libraries())
+
+
+@pytest.mark.parametrize("H,Hkv,D,norm", [(8, 1, 256, False), (16, 8, 128, True), (4, 2, 72, True), (2, 2, 64, False)])
+def test_qkv_post_matches_unfused_ops(H, Hkv, D, norm, dev):
+    """split + qk-norm + rotation + strided K/V store in one launch == rms_norm, rope and copies done separately."""
+    from opentau_b200 import ops
+    from opentau_b200.models.layers import RMSNorm
+    B, T, P = 2, 51, 37
+    torch.manual_seed(0)
+    qkv = torch.randn(B, T, (H + 2 * Hkv) * D, device=dev).to(torch.bfloat16)
+    pos = torch.arange(T, device=dev)[None].expand(B, -1) + 5
+    cos, sin = ops.rope_angles(pos, D, 10000.0)
+    qn = kn = None
+    if norm:
+        qn, kn = RMSNorm(D, 1e-6, False).to(dev).to(torch.bfloat16), RMSNorm(D, 1e-6, False).to(dev).to(torch.bfloat16)
+        with torch.no_grad():
+            qn.weight.add_(torch.randn_like(qn.weight) * 0.1), kn.weight.add_(torch.randn_like(kn.weight) * 0.1)
+    with torch.no_grad():
+        q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], dim=-1)
+        q, k, v = q.unflatten(-1, (H, D)), k.unflatten(-1, (Hkv, D)), v.unflatten(-1, (Hkv, D))
+        if norm:
+            q, k = qn(q)[0], kn(k)[0]
+        want_q, want_k = ops.rope(q, cos, sin), ops.rope(k, cos, sin)
+        got_q, got_k, got_v = ops.qkv_post(qkv, H, Hkv, D, qn, kn, cos, sin)
+        kbuf = torch.zeros(B, P + T + 3, Hkv, D, device=dev, dtype=torch.bfloat16)
+        vbuf = torch.zeros_like(kbuf)
+        ops.qkv_post(qkv, H, Hkv, D, qn, kn, cos, sin, kbuf[:, P:P + T], vbuf[:, P:P + T])
+    torch.testing.assert_close(got_q.float(), want_q.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got_k.float(), want_k.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(got_v, v)
+    assert torch.equal(kbuf[:, P:P + T], got_k) and torch.equal(vbuf[:, P:P + T], got_v)
+    assert float(kbuf[:, :P].abs().sum()) == 0 and float(kbuf[:, P + T:].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("per_token", [False, True])
+def test_gated_residual_native(per_token, dev):
+    from opentau_b200 import ops
+    B, T, H = 3, 51, 1024
+    x, y = (torch.randn(B, T, H, device=dev).to(torch.bfloat16) for _ in range(2))
+    mod = torch.randn(B, T if per_token else 1, 3 * H, device=dev).to(torch.bfloat16)
+    gate = mod[..., 2 * H:]                                    # a strided slice, as the adaptive norm hands it out
+    with torch.no_grad():
+        got = ops.gated_residual(x, y, gate)
+    want = x.float() + y.float() * gate.float()
+    torch.testing.assert_close(got.float(), want, atol=3e-2, rtol=2e-2)

@@ -101,8 +101,9 @@ def _cosmos_rank(rank, world, port, ret):
             cache, pos = tpb.run_prefix([im[sl] for im in images], [m[sl] for m in masks], lt[sl], lm[sl])
             layers = [col] if col is not None else range(full.k.shape[0])
             for li in layers:
-                errs.append(float((cache.k[li] - full.k[li, sl]).abs().max()))
-                errs.append(float((cache.v[li] - full.v[li, sl]).abs().max()))
+                n = full.length                         # the replicated cache carries spare slots behind the prefix
+                errs.append(float((cache.k[li][:, :n] - full.k[li, sl, :n]).abs().max()))
+                errs.append(float((cache.v[li][:, :n] - full.v[li, sl, :n]).abs().max()))
             assert torch.equal(pos, pos_full[:, sl]) and torch.equal(cache.valid, full.valid[sl])
         gathered = [None] * world
         dist.all_gather_object(gathered, max(errs))
