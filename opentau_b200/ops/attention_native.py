@@ -43,8 +43,24 @@ def _prep(t: Tensor) -> Tensor:
     return t
 
 
+NUM_SMS = 148
+
+
+def split_kv(B: int, Sq: int, Sk: int, H: int, Hkv: int, D: int) -> int:
+    """Key splits per query tile: only when the tiles alone would leave three quarters of the SMs idle and every split
+    still gets two key blocks (a 51-token suffix against a 1000-token prefix: 4 CTAs become 32)."""
+    g = H // Hkv
+    if D % 4 or g > 128 or 128 % g:
+        return 1
+    ctas = -(-Sq // (128 // g)) * Hkv * B
+    nblk = -(-Sk // (64 if D > 128 else 128))
+    if ctas * 4 > NUM_SMS:
+        return 1
+    return max(1, min(8, NUM_SMS // ctas, nblk // 2))
+
+
 def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor, q_valid: Tensor, k_valid: Tensor,
-             scale: float):
+             scale: float, nsplit: int | None = None):
     from . import cuda_ops
     B, Sq, H, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
@@ -55,14 +71,23 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk: Tensor, q_va
     kb = k_blk.to(torch.int32).contiguous()
     qv = _u8(q_valid)
     kv = _u8(k_valid)
-    rc = _lib.load("attention_tcgen05").otb_attn_fwd(
-        c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
-        c_void_p(lse.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()), c_void_p(qv.data_ptr()),
-        c_void_p(kv.data_ptr()), c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hkv), c_int(D),
-        c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
-        c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
-        c_longlong(v.stride(0)), c_longlong(v.stride(1)), c_longlong(v.stride(2)),
-        c_float(scale), c_void_p(cuda_ops.status_pointer()), cuda_ops._stream())
+    lib = _lib.load("attention_tcgen05")
+    args = [c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
+            c_void_p(lse.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()), c_void_p(qv.data_ptr()),
+            c_void_p(kv.data_ptr()), c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hkv), c_int(D),
+            c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
+            c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
+            c_longlong(v.stride(0)), c_longlong(v.stride(1)), c_longlong(v.stride(2)), c_float(scale)]
+    nsplit = split_kv(B, Sq, Sk, H, Hkv, D) if nsplit is None else nsplit
+    if nsplit > 1:
+        part_o = torch.empty(nsplit, B, Sq, H, D, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(nsplit, B, H, Sq, 2, dtype=torch.float32, device=q.device)
+        rc = lib.otb_attn_fwd_splitkv(*args, c_int(nsplit), c_void_p(part_o.data_ptr()),
+                                      c_void_p(part_ml.data_ptr()), c_void_p(cuda_ops.status_pointer()),
+                                      cuda_ops._stream())
+        cuda_ops.launch_count += 1
+    else:
+        rc = lib.otb_attn_fwd(*args, c_void_p(cuda_ops.status_pointer()), cuda_ops._stream())
     if rc != 0:
         raise RuntimeError(f"native attn_fwd failed with code {rc} (B={B} Sq={Sq} Sk={Sk} H={H} Hkv={Hkv} D={D})")
     cuda_ops.launch_count += 1

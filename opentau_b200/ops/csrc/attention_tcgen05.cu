@@ -30,6 +30,11 @@ struct AttnParams {
   const unsigned char* k_valid;     // (B, Sk)
   __nv_bfloat16* o;                 // (B, Sq, H, D) contiguous
   float* lse;                       // (B, H, Sq)
+  // split-KV (few query tiles, many keys: a denoising step against a cached prefix): CTA (tile, split) covers its
+  // share of the key blocks and leaves an unnormalised partial; attn_combine_kernel merges the partials
+  int nsplit;                       // 1: write o / lse directly
+  float* part_o;                    // (nsplit, B, Sq, H, D) fp32, accumulators expressed against part m
+  float2* part_ml;                  // (nsplit, B, H, Sq): (running maximum in log2 units, row sum)
   KernelStatus* status;
 };
 
@@ -94,7 +99,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tile = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit, kvh = blockIdx.y, b = blockIdx.z;
   const int g = p.g;
   const int pos_per_tile = ATT_M / g;
   const int p0 = tile * pos_per_tile;
@@ -166,7 +171,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     __syncthreads();
   }
   const int kv_end = *kv_end_smem;
-  const int nblk = max(1, (kv_end + BN - 1) / BN);
+  const int nblk_all = max(1, (kv_end + BN - 1) / BN);
+  // this CTA's key blocks [jb0, jb0 + nblk).  A split beyond the reachable keys still runs one block: every key in
+  // it is invisible to the tile, so it contributes a zero row sum that the combine step ignores.
+  const int per_split = (nblk_all + p.nsplit - 1) / p.nsplit;
+  const int jb0 = split * per_split;
+  const int nblk = max(1, min(nblk_all, jb0 + per_split) - jb0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -183,8 +193,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         mbar_expect_tx(&kv_full[slot], L::STAGE_BYTES);
 #pragma unroll
         for (int c = 0; c < L::NCHUNK; ++c) {
-          tma_load_4d(sk + c * (BN * 128), &tma_k, &kv_full[slot], c * 64, kvh, j * BN, b);
-          tma_load_4d(sv + c * (BN * 128), &tma_v, &kv_full[slot], c * 64, kvh, j * BN, b);
+          tma_load_4d(sk + c * (BN * 128), &tma_k, &kv_full[slot], c * 64, kvh, (jb0 + j) * BN, b);
+          tma_load_4d(sv + c * (BN * 128), &tma_v, &kv_full[slot], c * 64, kvh, (jb0 + j) * BN, b);
         }
       }
     }
@@ -256,7 +266,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const int o_lo = half ? (n16 + 1) / 2 : 0, o_hi = half ? n16 : (n16 + 1) / 2;   // this thread's O column groups
 
     auto load_meta = [&](int jj) -> int {
-      const int key = jj * BN + st;
+      const int key = (jb0 + jj) * BN + st;
       if (st >= BN || key >= p.Sk) return INT_MAX;
       const int kbv = p.k_blk[(long long)b * p.Sk + key];
       const int kvv = p.k_valid[(long long)b * p.Sk + key];
@@ -396,13 +406,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
     const uint32_t o_addr = tmem_O + lane_off;
     __nv_bfloat16* orow = p.o + (((long long)b * p.Sq + pos) * p.H + head) * p.D;
+    float* prow_o = p.nsplit > 1
+                        ? p.part_o + ((((long long)split * p.B + b) * p.Sq + pos) * p.H + head) * (long long)p.D
+                        : nullptr;
 #pragma unroll 1
     for (int c = o_lo; c < o_hi; ++c) {
       uint32_t ro[16];
       __syncwarp();
       tmem_ld_x16(o_addr + c * 16, ro);
       tmem_wait_ld();
-      if (row_in) {
+      if (row_in && prow_o != nullptr) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int col = c * 16 + q4 * 4;
+          if (col < p.D)
+            *reinterpret_cast<float4*>(prow_o + col) =
+                make_float4(__uint_as_float(ro[q4 * 4 + 0]), __uint_as_float(ro[q4 * 4 + 1]),
+                            __uint_as_float(ro[q4 * 4 + 2]), __uint_as_float(ro[q4 * 4 + 3]));
+        }
+      } else if (row_in) {
 #pragma unroll
         for (int h8 = 0; h8 < 2; ++h8) {
           const int col = c * 16 + h8 * 8;
@@ -418,8 +440,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
     }
     if (row_in && half == 0) {
-      const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : 0.f;
-      p.lse[((long long)b * p.H + head) * p.Sq + pos] = lse;
+      if (p.nsplit > 1) {
+        p.part_ml[(((long long)split * p.B + b) * p.H + head) * p.Sq + pos] = make_float2(m_used, l);
+      } else {
+        const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : 0.f;
+        p.lse[((long long)b * p.H + head) * p.Sq + pos] = lse;
+      }
     }
     tc_fence_before();
   }
@@ -435,6 +461,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Merge of the split-KV partials: one warp per (batch, position, head) row.
+//   M = max_s m_s over splits with l_s > 0,  L = sum_s l_s 2^(m_s - M),  O = sum_s O_s 2^(m_s - M) / L
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int nsplit, int B, int Sq,
+                                    int H, int D) {
+  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)B * Sq * H;
+  if (row >= rows) return;
+  const int head = int(row % H);
+  const long long bp = row / H;                    // b * Sq + pos
+  const int pos = int(bp % Sq), b = int(bp / Sq);
+  float w[8];
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) {
+    const float2 ml = part_ml[(((long long)s * B + b) * H + head) * Sq + pos];
+    w[s] = ml.y > 0.f ? ml.x : -INFINITY;          // reuse w[] for the maxima first
+    M = fmaxf(M, w[s]);
+  }
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float2 ml = part_ml[(((long long)s * B + b) * H + head) * Sq + pos];
+    w[s] = (w[s] == -INFINITY) ? 0.f : fast_exp2(w[s] - M);
+    L += ml.y * w[s];
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = lane; d < D; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s)
+      if (w[s] != 0.f) acc += part_o[(((long long)s * B + b) * Sq + pos) * H * D + (long long)head * D + d] * w[s];
+    o[row * D + d] = __float2bfloat16(acc * inv);
+  }
+  if (lane == 0) lse[((long long)b * H + head) * Sq + pos] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : 0.f;
 }
 
 // rank-4 bf16 map over a (B, S, Hx, D) tensor with element strides (sb, ss, sh, 1); dims innermost first
@@ -458,8 +519,13 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     configured = true;
   }
   const int pos_per_tile = ATT_M / p.g;
-  dim3 grid((p.Sq + pos_per_tile - 1) / pos_per_tile, p.Hkv, p.B);
+  dim3 grid(((p.Sq + pos_per_tile - 1) / pos_per_tile) * p.nsplit, p.Hkv, p.B);
   kern<<<grid, 320, L::TOTAL, stream>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || p.nsplit == 1) return (int)e;
+  const long long rows = (long long)p.B * p.Sq * p.H;
+  attn_combine_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p.part_o, p.part_ml, p.o, p.lse,
+                                                                              p.nsplit, p.B, p.Sq, p.H, p.D);
   return (int)cudaGetLastError();
 }
 
@@ -468,11 +534,12 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
 using namespace otb;
 
 // q: (B,Sq,H,D) strides (q_sb,q_ss,q_sh,1); k,v: (B,Sk,Hkv,D); o: (B,Sq,H,D) contiguous; lse: (B,H,Sq).
-extern "C" int otb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* q_blk,
-                            const int* k_blk, const unsigned char* q_valid, const unsigned char* k_valid, int B,
-                            int Sq, int Sk, int H, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh,
-                            long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
-                            long long v_sh, float scale, void* status, cudaStream_t stream) {
+static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, float* lse, const int* q_blk,
+                         const int* k_blk, const unsigned char* q_valid, const unsigned char* k_valid, int B, int Sq,
+                         int Sk, int H, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
+                         long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh, float scale,
+                         int nsplit, float* part_o, float* part_ml, void* status, cudaStream_t stream) {
+  if (nsplit < 1 || nsplit > 8 || (nsplit > 1 && (part_o == nullptr || part_ml == nullptr || D % 4))) return -7;
   if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return -2;
   const int g = H / Hkv;
   if (g > 128 || (128 % g)) return -3;
@@ -490,6 +557,9 @@ extern "C" int otb_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.q_blk = q_blk; p.k_blk = k_blk; p.q_valid = q_valid; p.k_valid = k_valid;
   p.o = static_cast<__nv_bfloat16*>(o);
   p.lse = lse;
+  p.nsplit = nsplit;
+  p.part_o = part_o;
+  p.part_ml = reinterpret_cast<float2*>(part_ml);
   p.status = static_cast<KernelStatus*>(status);
   const int dpad = D <= 64 ? 64 : (D <= 128 ? 128 : 256);
   const int bn = dpad == 256 ? 64 : 128;
@@ -506,3 +576,27 @@ extern "C" int otb_attn_fwd(const void* q, const void* k, const void* v, void* o
     default: return launch_attn<256, 64>(tq, tk, tv, p, stream);
   }
 }
+
+extern "C" int otb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* q_blk,
+                            const int* k_blk, const unsigned char* q_valid, const unsigned char* k_valid, int B,
+                            int Sq, int Sk, int H, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh,
+                            long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
+                            long long v_sh, float scale, void* status, cudaStream_t stream) {
+  return attn_fwd_impl(q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, B, Sq, Sk, H, Hkv, D, q_sb, q_ss, q_sh, k_sb,
+                       k_ss, k_sh, v_sb, v_ss, v_sh, scale, 1, nullptr, nullptr, status, stream);
+}
+
+// Split-KV form: `nsplit` (2..8) CTAs per query tile share the key blocks; part_o holds nsplit*B*Sq*H*D floats and
+// part_ml 2*nsplit*B*H*Sq floats of scratch.  Same result as otb_attn_fwd up to fp32 rounding of the merge.
+extern "C" int otb_attn_fwd_splitkv(const void* q, const void* k, const void* v, void* o, float* lse, const int* q_blk,
+                                    const int* k_blk, const unsigned char* q_valid, const unsigned char* k_valid,
+                                    int B, int Sq, int Sk, int H, int Hkv, int D, long long q_sb, long long q_ss,
+                                    long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb,
+                                    long long v_ss, long long v_sh, float scale, int nsplit, float* part_o,
+                                    float* part_ml, void* status, cudaStream_t stream) {
+  return attn_fwd_impl(q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, B, Sq, Sk, H, Hkv, D, q_sb, q_ss, q_sh, k_sb,
+                       k_ss, k_sh, v_sb, v_ss, v_sh, scale, nsplit, part_o, part_ml, status, stream);
+}
+
+// key-block width the forward kernel uses for this head dimension (callers size split-KV from it)
+extern "C" int otb_attn_block(int D) { return D > 128 ? 64 : 128; }

@@ -138,3 +138,30 @@ def test_attn_bwd_matches_dense(D, H, Hkv, Sq, cross):
     torch.testing.assert_close(dk.cpu().float()[valid_k], dkr[valid_k], rtol=5e-2, atol=8e-2)
     torch.testing.assert_close(dv.cpu().float()[valid_k], dvr[valid_k], rtol=5e-2, atol=8e-2)
     assert torch.isfinite(dq.float()).all() and torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,Hkv,D", [(1, 51, 1019, 8, 1, 256), (2, 51, 700, 16, 8, 128), (1, 10, 300, 4, 4, 64),
+                                             (1, 51, 1019, 8, 8, 72)])
+@pytest.mark.parametrize("nsplit", [2, 5, 8])
+def test_split_kv_matches_single_pass(B, Sq, Sk, H, Hkv, D, nsplit):
+    """A suffix attending to a cached prefix plus itself: the key blocks split over several CTAs and merged give the
+    single-pass result (also when some splits reach no visible key)."""
+    from opentau_b200.ops import attention_native, cuda_ops
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    q = torch.randn(B, Sq, H, D, device=dev).to(torch.bfloat16)
+    k = torch.randn(B, Sk, Hkv, D, device=dev).to(torch.bfloat16)
+    v = torch.randn(B, Sk, Hkv, D, device=dev).to(torch.bfloat16)
+    P = Sk - Sq
+    k_blk = torch.cat([torch.full((B, P), -2**31, dtype=torch.int32, device=dev),
+                       torch.arange(Sq, device=dev, dtype=torch.int32)[None].expand(B, -1) // 7], 1).contiguous()
+    q_blk = k_blk[:, P:].contiguous()
+    k_valid = torch.rand(B, Sk, device=dev) > 0.1
+    q_valid = torch.ones(B, Sq, dtype=torch.bool, device=dev)
+    q_valid[:, -3:] = False
+    scale = D ** -0.5
+    want_o, want_lse = attention_native.attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale, nsplit=1)
+    got_o, got_lse = attention_native.attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale, nsplit=nsplit)
+    cuda_ops.check_status()
+    torch.testing.assert_close(got_o.float(), want_o.float(), atol=1e-2, rtol=1e-2)
+    torch.testing.assert_close(got_lse, want_lse, atol=1e-3, rtol=1e-3)
