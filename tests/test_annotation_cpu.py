@@ -1,0 +1,79 @@
+"""Subtask / mistake annotation tools with a scripted vision-language client (no network), on a recorded video dataset."""
+
+import json
+
+import pyarrow.parquet as pq
+
+from opentau_b200.planner.high_level_planner import CallableClient
+from opentau_b200.scripts import add_subtask_response, annotate_mistakes, annotate_subtasks
+from test_datasets_cpu import _record
+
+
+def test_build_response_array_rules():
+    subs = [{"time": 0.5, "subtask": "b"}, {"time": 0.0, "subtask": "a"}, {"time": 9.0, "subtask": "late"}]
+    out = add_subtask_response.build_response_array(subs, fps=10, length=12)
+    assert out == ["a"] * 5 + ["b"] * 7                       # sorted by time; a start beyond the episode is dropped
+    assert add_subtask_response.build_response_array([{"time": 0.3, "subtask": "x"}], 10, 5) == ["", "", "", "x", "x"]
+    assert add_subtask_response.build_response_array([], 10, 3) == ["", "", ""]
+
+
+def test_parsers():
+    assert annotate_subtasks.parse_json_response('```json\n[{"time": 0, "subtask": "go"}]\n```')[0]["subtask"] == "go"
+    assert annotate_subtasks.parse_json_response('Sure! [{"time": 1, "subtask": "x"}] done')[0]["time"] == 1
+    assert annotate_subtasks.coerce_subtasks([{"time": "2", "subtask": " b "}, {"time": 0, "subtask": "a"}, {"oops": 1},
+                                              {"time": 1, "subtask": ""}]) == [{"time": 0.0, "subtask": "a"},
+                                                                              {"time": 2.0, "subtask": "b"}]
+    assert annotate_mistakes.parse_success_response('{"success": false, "reason": "dropped"}') is False
+    assert annotate_mistakes.parse_success_response("success: TRUE because ...") is True
+    assert annotate_mistakes.find_response_runs(["a", "a", "", "b", "b", "b", "a"]) == [(0, 1, "a"), (3, 5, "b"), (6, 6, "a")]
+
+
+def test_annotate_subtasks_then_mistakes(tmp_path):
+    _record(tmp_path / "toy", use_videos=True, episodes=(12, 9))
+    root = tmp_path / "toy"
+    cfg = tmp_path / "mix.json"
+    cfg.write_text(json.dumps({"dataset_mixture": {"datasets": [{"repo_id": "local/toy", "root": str(root)}]}}))
+    datasets = annotate_subtasks.load_datasets_from_config(cfg)
+    calls = []
+
+    def subtask_model(messages, images):
+        calls.append(len(images))
+        assert "Frame timestamps" in messages[-1]["content"]
+        return 'Here you go:\n```json\n[{"time": 0.0, "subtask": "reach"}, {"time": 0.6, "subtask": "grasp"}]\n```'
+
+    done = annotate_subtasks.run(datasets, CallableClient(subtask_model), sample_fps=5.0, target_size=32)
+    assert done == {str(root.resolve()): 2} and calls == [6, 5]              # every 2nd frame of 12 and of 9
+    info = json.loads((root / "meta/info.json").read_text())
+    assert info["subtask_path"] == annotate_subtasks.SUBTASK_TEMPLATE and info["features"]["response"]["dtype"] == "string"
+    resp = pq.read_table(add_subtask_response.episode_parquet(root, info, 0)).column("response").to_pylist()
+    assert resp == ["reach"] * 6 + ["grasp"] * 6
+    # a second run finds the subtask files and asks nothing
+    assert annotate_subtasks.run(datasets, CallableClient(subtask_model), sample_fps=5.0)[str(root.resolve())] == 0
+    assert len(calls) == 2
+
+    def judge(messages, images):
+        assert len(images) == 1
+        failed = "Subtask: grasp" in messages[-1]["content"]
+        return json.dumps({"success": not failed, "reason": "scripted"})
+
+    done = annotate_mistakes.run(datasets, CallableClient(judge), target_size=32)
+    assert done[str(root.resolve())] == 2
+    mist = pq.read_table(add_subtask_response.episode_parquet(root, info, 0)).column("mistake").to_pylist()
+    assert mist == [0] * 6 + [1] * 6
+    info = json.loads((root / "meta/info.json").read_text())
+    assert info["features"]["mistake"]["dtype"] == "int64"
+    assert annotate_mistakes.run(datasets, CallableClient(judge))[str(root.resolve())] == 0     # resumable
+
+
+def test_unusable_answers_leave_no_mistake(tmp_path):
+    _record(tmp_path / "toy", use_videos=True, episodes=(6,))
+    root = tmp_path / "toy"
+    (root / "subtasks").mkdir()
+    (root / "subtasks/episode_000000.json").write_text(json.dumps([{"time": 0, "subtask": "only"}]))
+    info = json.loads((root / "meta/info.json").read_text())
+    info["subtask_path"] = annotate_subtasks.SUBTASK_TEMPLATE
+    (root / "meta/info.json").write_text(json.dumps(info))
+    assert add_subtask_response.process_dataset(root) == 1
+    done = annotate_mistakes.run([{"repo_id": "local/toy", "root": str(root)}], CallableClient(lambda m, i: "no idea"))
+    assert done[str(root.resolve())] == 1
+    assert pq.read_table(add_subtask_response.episode_parquet(root, info, 0)).column("mistake").to_pylist() == [0] * 6
