@@ -2,6 +2,7 @@
 
 import json
 
+import numpy as np
 import pyarrow.parquet as pq
 
 from opentau_b200.planner.high_level_planner import CallableClient
@@ -77,3 +78,38 @@ def test_unusable_answers_leave_no_mistake(tmp_path):
     done = annotate_mistakes.run([{"repo_id": "local/toy", "root": str(root)}], CallableClient(lambda m, i: "no idea"))
     assert done[str(root.resolve())] == 1
     assert pq.read_table(add_subtask_response.episode_parquet(root, info, 0)).column("mistake").to_pylist() == [0] * 6
+
+
+def test_norm_distribution_flags_stale_metadata(tmp_path):
+    """Metadata whose std was inflated by a removed outlier shows up as z_std << 1 and is listed first."""
+    from opentau_b200.scripts import diagnose_norm_distribution as dn
+    _record(tmp_path / "toy", episodes=(12, 9, 15))
+    root = tmp_path / "toy"
+    stats = json.loads((root / "meta/stats.json").read_text()) if (root / "meta/stats.json").exists() else None
+    rows = dn.run([{"repo_id": "local/toy", "root": str(root)}], tmp_path / "diag")
+    fresh = [r for r in rows if r["feature"] == "action"]
+    assert len(fresh) == 6 and all(abs(r["z_std"] - 1.0) < 1e-3 and abs(r["z_mean"]) < 1e-6 for r in fresh)
+    # make the metadata stale: tenfold std for the state of every episode
+    import opentau_b200.datasets.utils as du
+    path = root / "meta/episodes_stats.jsonl"
+    lines = [json.loads(x) for x in path.read_text().splitlines()]
+    for ln in lines:
+        ln["stats"]["observation.state"]["std"] = [10 * v for v in ln["stats"]["observation.state"]["std"]]
+    path.write_text("\n".join(json.dumps(x) for x in lines) + "\n")
+    if stats is not None:
+        stats["observation.state"]["std"] = [10 * v for v in stats["observation.state"]["std"]]
+        (root / "meta/stats.json").write_text(json.dumps(stats))
+    rows = dn.run([{"repo_id": "local/toy", "root": str(root)}], tmp_path / "diag2")
+    assert rows[0]["feature"] == "observation.state" and rows[0]["z_std"] < 0.5
+    rep = json.loads((tmp_path / "diag2/report.json").read_text())
+    assert len(rep["rows"]) == 12 and (tmp_path / "diag2/report.csv").exists()
+    fixed = json.loads((tmp_path / "diag2/corrected_stats.json").read_text())
+    head = next(iter(fixed))
+    assert abs(fixed[head]["observation.state"]["mean"][0] - 17.5) < 1e-6 and du is not None
+    a, b = dn.DimStats(2), dn.DimStats(2)
+    x = np.random.default_rng(0).normal(size=(50, 2))
+    a.update(x[:20], x[:20]), b.update(x[20:], x[20:])
+    whole = dn.DimStats(2)
+    whole.update(x, x)
+    a.merge(b)
+    assert np.allclose(a.moments()[1], whole.moments()[1]) and (a.hist == whole.hist).all()
