@@ -91,6 +91,13 @@ class FlatParamStore:
                     p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                     p.grad = None
 
+    def layout(self) -> list[dict]:
+        """Name / shape / offset of every parameter inside each flat group: what an offline tool needs to turn the
+        per-rank optimizer shards back into named tensors."""
+        return [{"dtype": str(g.dtype).replace("torch.", ""), "numel": g.numel,
+                 "params": [{"name": n, "shape": list(p.shape), "offset": o}
+                            for n, p, o in zip(g.names, g.params, g.offsets)]} for g in self.groups]
+
     @property
     def num_trainable(self) -> int:
         return sum(p.numel() for g in self.groups for p in g.params)

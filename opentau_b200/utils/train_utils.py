@@ -8,6 +8,7 @@ Directory layout (same as the reference, OpenTau ``src/opentau/utils/train_utils
         training_step.json                      {"step": N}
         rng_state.safetensors                   python / numpy / torch / cuda RNG
         optimizer_rank<r>.safetensors           this rank's shard of Adam moments (+ fp32 masters)
+        flat_layout.json                        parameter name / shape / offset inside the flat groups
         random_states_<r>.marker                one per rank: the completeness tripwire counts them
     <output_dir>/checkpoints/last -> <step>     symlink
     <output_dir>/checkpoints/running_best.json  RunningBestTracker state
@@ -66,6 +67,9 @@ def save_checkpoint(checkpoint_dir: Path, step: int, cfg, policy, engine=None, r
         cfg.save_pretrained(checkpoint_dir)
         save_training_step(step, checkpoint_dir)
         save_rng_state(checkpoint_dir)
+    if engine is not None and is_main:
+        with open(checkpoint_dir / "flat_layout.json", "w") as f:
+            json.dump(engine.store.layout(), f)
     if engine is not None:
         sd = engine.state_dict()
         tensors = {k: v.detach().cpu().contiguous() for k, v in sd.items() if isinstance(v, torch.Tensor)}

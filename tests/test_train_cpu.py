@@ -36,6 +36,15 @@ def test_train_checkpoint_resume(tmp_path):
     assert (ck / "last").resolve().name == "000008" and not (ck / "000004").exists()     # pruned to the last one
     for f in ("model.safetensors", "config.json", "train_config.json", "training_step.json", "optimizer_rank0.safetensors"):
         assert (ck / "000008" / f).exists(), f
+    # the per-rank shards + layout consolidate into named fp32 masters that round to the saved bf16 / fp32 weights
+    from safetensors.torch import load_file
+    from opentau_b200.scripts.zero_to_fp32 import consolidate
+    full = consolidate(ck / "000008", moments=True)
+    saved = load_file(str(ck / "000008" / "model.safetensors"))
+    name = next(k for k in saved if k.endswith("action_in_proj.weight"))
+    assert full[name].dtype == torch.float32 and full[name].shape == saved[name].shape
+    torch.testing.assert_close(full[name].to(saved[name].dtype), saved[name])
+    assert full[name + ".exp_avg_sq"].min() >= 0 and (ck / "000008" / "flat_layout.json").exists()
     resumed = train(_cfg(out, 10, resume=True))
     rows = [json.loads(line) for line in (out / "metrics.jsonl").read_text().splitlines()]
     assert rows[-1]["step"] == 10 and (ck / "last").resolve().name == "000010"
