@@ -113,3 +113,32 @@ def test_norm_distribution_flags_stale_metadata(tmp_path):
     whole.update(x, x)
     a.merge(b)
     assert np.allclose(a.moments()[1], whole.moments()[1]) and (a.hist == whole.hist).all()
+
+
+def test_memory_generator_and_nav_planner(tmp_path):
+    from PIL import Image
+    from opentau_b200.scripts import download_assets, nav_high_level_planner_inference, pi_mem_data_generator as gen
+    data = [{"subtask": "open drawer", "success": False, "time": 1.5, "prompt": "tidy up"},
+            {"subtask": "open drawer", "success": True, "memory": "kept"}, {"subtask": "pick cup"}]
+    path = tmp_path / "segs.json"
+    path.write_text(json.dumps(data))
+    seen = []
+
+    def model(messages, images):
+        seen.append(messages[-1]["content"])
+        return f" memory {len(seen)} "
+
+    assert gen.main([str(path), "--skip-existing"], client=CallableClient(model)) == 0
+    out = json.loads(path.read_text())
+    assert [o["memory"] for o in out] == ["memory 1", "kept", "memory 2"]
+    assert "1. [FAILED] (t=1.5s) open drawer" in seen[0] and "Previous memory: (none)" in seen[0]
+    assert "Previous memory: kept" in seen[1] and "3. [UNKNOWN] pick cup" in seen[1] and "2. [SUCCESS] open drawer" in seen[1]
+    assert gen.main([str(tmp_path / "missing.json")], client=CallableClient(model)) == 1
+    frames = tmp_path / "frames"
+    frames.mkdir()
+    for i in range(3):
+        Image.fromarray(np.full((8, 8, 3), 40 * i, np.uint8)).save(frames / f"f{i}.png")
+    acts = nav_high_level_planner_inference.main(
+        ["--img_path", str(frames)], client=CallableClient(lambda m, i: json.dumps([f"{len(i)} views", "go forward"])))
+    assert acts == ["3 views", "go forward"]
+    assert download_assets.main(["libero"]) in (2, 3) and download_assets.main(["robocasa"]) in (2, 3)
