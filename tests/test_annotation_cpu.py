@@ -142,3 +142,18 @@ def test_memory_generator_and_nav_planner(tmp_path):
         ["--img_path", str(frames)], client=CallableClient(lambda m, i: json.dumps([f"{len(i)} views", "go forward"])))
     assert acts == ["3 views", "go forward"]
     assert download_assets.main(["libero"]) in (2, 3) and download_assets.main(["robocasa"]) in (2, 3)
+
+
+def test_value_visualizer_pages(tmp_path):
+    from opentau_b200.scripts import value_visualizer as vv
+    _record(tmp_path / "toy", episodes=(12, 9))
+    a = tmp_path / "a.json"
+    a.write_text(json.dumps({"(0, 0.0)": -1.0, "(0, 0.5)": -0.5, "(0, 1.1)": 0.0, "1,0.2": 0.3}))
+    b = tmp_path / "b.json"
+    b.write_text(json.dumps({"0": [{"frame": i, "value": -1 + i / 12, "return": -1 + i / 11} for i in range(12)]}))
+    va, vb = vv.load_values(a), vv.load_values(b, fps=10)
+    assert [r["t"] for r in va[0]] == [0.0, 0.5, 1.1] and va[1][0]["value"] == 0.3 and vb[0][5]["t"] == 0.5
+    pages = vv.render(vb, tmp_path / "viz", dataset_root=tmp_path / "toy", n_frames=4)
+    text = pages[0].read_text()
+    assert text.count("<img src=\"data:image/jpeg;base64,") == 4 and text.count("<polyline") == 2
+    assert len(vv.render(va, tmp_path / "viz2")) == 2
