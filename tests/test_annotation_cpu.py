@@ -157,3 +157,55 @@ def test_value_visualizer_pages(tmp_path):
     text = pages[0].read_text()
     assert text.count("<img src=\"data:image/jpeg;base64,") == 4 and text.count("<polyline") == 2
     assert len(vv.render(va, tmp_path / "viz2")) == 2
+
+
+def test_ros_bag_conversion_with_fake_messages(tmp_path):
+    """Joint states at 20 Hz, commands at 7 Hz and JPEG frames at 5 Hz are aligned to 10 fps; a broken bag is skipped."""
+    import io
+    from types import SimpleNamespace as NS
+
+    from PIL import Image
+
+    from opentau_b200.configs.ros2lerobot import RosToLeRobotConfig
+    from opentau_b200.configs.types import ROSFeature
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDatasetMetadata
+    from opentau_b200.scripts.convert_ros_to_lerobot import convert
+    from opentau_b200.utils.ros2lerobot import synchronize_sensor_data
+
+    assert synchronize_sensor_data([(0, "a"), (0.26e9, "b"), (0.5e9, "c")], 10, 0.0) == ["a", "a", "b", "b", "c"]
+    for name in ("bag_a", "bag_b"):
+        (tmp_path / "bags" / name / "recording").mkdir(parents=True)
+
+    def jpeg(v):
+        buf = io.BytesIO()
+        Image.fromarray(np.full((24, 32, 3), v, np.uint8)).save(buf, format="PNG")
+        return buf.getvalue()
+
+    def reader(path):
+        if "bag_b" in str(path):
+            raise OSError("truncated bag")
+        t0 = 100.0
+        for i in range(41):                                              # 2 s of joint states at 20 Hz
+            t = t0 + i / 20
+            stamp = NS(sec=int(t), nanosec=int((t % 1) * 1e9))
+            yield "/joint_states", 0, NS(header=NS(stamp=stamp), name=["j2", "j1"], position=[2.0 + i, 1.0 + i],
+                                         velocity=[0.2, 0.1])
+        for i in range(15):
+            yield "/cmd", int((t0 + i / 7) * 1e9), NS(joint_names=["j1", "j2"], motor_cmd=[NS(q=10.0 + i), NS(q=20.0 + i)])
+        for i in range(11):
+            yield "/cam/compressed", int((t0 + i / 5) * 1e9), NS(data=jpeg(20 * i))
+
+    cfg = RosToLeRobotConfig(
+        input_path=str(tmp_path / "bags"), output_path=str(tmp_path / "out"), fps=10, joint_order=["j1", "j2"],
+        robot_type="arm", dataset_features={
+            "observation.state": ROSFeature("/joint_states", "position", "state", "float32", (4,)),
+            "action": ROSFeature("/cmd", "motor_cmd", "action", "float32", (2,)),
+            "observation.images.cam": ROSFeature("/cam/compressed", "data", "image", "video", (24, 32, 3))})
+    done = convert(cfg, reader=reader, info=lambda p: ("stack the cups", 100.0))
+    assert done == {"episodes": 1, "frames": 20, "failed": 1}             # every stream spans 2.0 s: int(2.0 * fps)
+    meta = LeRobotDatasetMetadata("out", root=tmp_path / "out")
+    assert meta.total_episodes == 1 and meta.total_frames == 20 and meta.tasks[0] == "stack the cups"
+    rows = pq.read_table(add_subtask_response.episode_parquet(tmp_path / "out", meta.info, 0)).to_pydict()
+    assert np.allclose(rows["observation.state"][0], [1.0, 2.0, 0.1, 0.2])           # reordered to j1, j2; velocities appended
+    assert rows["observation.state"][4][0] == 1.0 + 8                     # 0.4 s -> the 20 Hz sample number 8
+    assert rows["action"][7] == [15.0, 25.0]                              # 0.7 s -> command number 5
