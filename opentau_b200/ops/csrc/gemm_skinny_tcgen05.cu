@@ -8,7 +8,7 @@
 //   * the WEIGHT rows are the 128-row M operand of tcgen05.mma, the tokens are the N operand (64 / 128 / 256 wide),
 //     so every weight element crosses shared memory exactly once per 256 tokens and the accumulator
 //     D^T[128 weight rows, tokens] sits in TMEM with one weight row per lane;
-//   * K is split over the CTAs of a thread-block cluster (1, 2, 4 or 8): grid = (N/128, splits, token chunks), so even
+//   * K is split over the CTAs of a thread-block cluster (1 to 8): grid = (N/128, splits, token chunks), so even
 //     an N = 1024 projection puts 64 CTAs to work.  Each CTA leaves its fp32 partial tile in its own shared memory
 //     (the TMA ring is free by then), the cluster synchronises, and every CTA reduces 1/splits of the tile over
 //     distributed shared memory in fixed rank order (deterministic, no global workspace, no atomics) and applies the
@@ -242,8 +242,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   if (!direct && !*abort_flag) {
     const uint32_t pbase = smem_u32(partial);
     if (!(p.flags & SK_NO_OUT)) {
-      // plain output: this rank reduces weight rows [r0, r0 + rows)
-      const int rows = SK_BW / S, r0 = split * rows;
+      // plain output: this rank reduces weight rows [r0, r0 + rows) (the last rank takes the remainder)
+      const int rows_per = (SK_BW + S - 1) / S, r0 = split * rows_per;
+      const int rows = max(0, min(rows_per, SK_BW - r0));
       for (int i = threadIdx.x; i < m_valid * rows; i += blockDim.x) {
         const int m = i / rows, wr = r0 + i % rows;
         if (n0 + wr >= p.N) continue;
@@ -252,7 +253,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
     if (glu) {
       // rows come in blocks of 32: [gate | up | gate | up]; 64 output columns per tile, split evenly over the ranks
-      const int units = 64 / S, u0 = split * units;
+      const int units_per = (64 + S - 1) / S, u0 = split * units_per;
+      const int units = max(0, min(units_per, 64 - u0));
       for (int i = threadIdx.x; i < m_valid * units; i += blockDim.x) {
         const int m = i / units, u = u0 + i % units;
         const int gr = (u >> 5) * 64 + (u & 31);      // gate row inside the tile; its up row is 32 further
@@ -317,7 +319,8 @@ static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Ski
 using namespace otb;
 
 // out[M,N] = X[M,K] W[N,K]^T (+ epilogue).  Returns 0, a CUDA / driver error code, or a negative argument-check code.
-// `splits_override`: 0 = choose (1, 2, 4 or 8 so that the grid fills the GPU once).
+// `splits_override`: 0 = choose (the largest cluster size up to 8 with which the grid still fits the GPU at once and
+// every CTA keeps at least two k-blocks).
 extern "C" int otb_gemm_skinny_bf16(const void* X, const void* W, void* out, int M, int N, int K, long long ldx,
                                     long long ldw, long long ldo, const void* bias, const void* residual,
                                     long long ldr, void* out2, long long ldo2, int flags, int splits_override,
@@ -343,9 +346,10 @@ extern "C" int otb_gemm_skinny_bf16(const void* X, const void* W, void* out, int
   if (splits == 0) {
     const long long slots = (long long)g_sk_sms * (nt <= 128 ? 2 : 1);
     splits = 1;
-    while (splits < 8 && (long long)n_tiles * chunks * (splits * 2) <= slots && num_kb / (splits * 2) >= 2) splits *= 2;
+    for (int s = 2; s <= 8; ++s)
+      if ((long long)n_tiles * chunks * s <= slots && num_kb / s >= 2) splits = s;
   }
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -8;
+  if (splits < 1 || splits > 8) return -8;
   CUtensorMap tw, tx;
   {
     uint64_t dims[2], strides[1];

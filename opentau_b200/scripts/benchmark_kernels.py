@@ -82,6 +82,49 @@ def bench_gemm(M, N, K, layout="nt", iters=20, with_torch=True, glu=None) -> dic
     return rec
 
 
+def bench_skinny(shapes: list[tuple[int, int, int]], iters: int = 20) -> list[dict]:
+    """Few-row ``x @ W^T`` products (inference): the weight-streaming split-K kernel at every cluster size, the
+    persistent 128-row kernel, and the library GEMM; weights rotate through buffers larger than L2."""
+    from opentau_b200.ops import cuda_ops
+    dev = torch.device("cuda")
+    pk = peaks()
+    rows = []
+    for M, N, K in shapes:
+        nb = _n_buffers(2 * N * K)
+        xs = [torch.randn(M, K, device=dev).to(torch.bfloat16) for _ in range(nb)]
+        ws = [torch.randn(N, K, device=dev).to(torch.bfloat16) for _ in range(nb)]
+        rec = {"kernel": "gemm_skinny_tcgen05", "M": M, "N": N, "K": K}
+        best = None
+        for s_ in (0, 1, 2, 3, 4, 6, 8):
+            if s_ and (K + 63) // 64 < 2 * s_:
+                continue
+            try:
+                ms = time_ms([lambda x=x, w=w: cuda_ops.gemm(x, w, "nt", splits=s_ or (0 if cuda_ops.use_skinny(
+                    "nt", M, N, False, 0) else 1)) for x, w in zip(xs, ws)], iters)
+            except RuntimeError:
+                continue
+            rec[f"splits{s_ or '_auto'}_us"] = round(ms * 1e3, 2)
+            if s_:
+                best = ms if best is None else min(best, ms)
+        cuda_ops.check_status()
+        rec["persistent_us"] = round(time_ms([lambda x=x, w=w: cuda_ops.gemm(x, w, "nt", bn=128 if N < 4096 else 256)
+                                              for x, w in zip(xs, ws)], iters) * 1e3, 2)
+        rec["library_us"] = round(time_ms([lambda x=x, w=w: x @ w.t() for x, w in zip(xs, ws)], iters) * 1e3, 2)
+        stream_gbs = 2 * N * K / (rec["splits_auto_us"] * 1e-6) / 1e9
+        rec["weight_stream_gbs_auto"] = round(stream_gbs, 1)
+        rec[f"frac_of_{pk['source']}_hbm"] = round(stream_gbs / pk["gbs"], 3)
+        rows.append(rec)
+        print(json.dumps(rec))
+    return rows
+
+
+# (rows, out features, in features): pi0.5 expert / cosmos3 expert, backbone prefix and vision tower products
+SKINNY_SHAPES = [(51, 2560, 1024), (51, 1024, 2048), (51, 8192, 1024), (51, 1024, 4096),
+                 (51, 4096, 1024), (51, 1024, 2048), (211, 10240, 5120), (211, 5120, 8192), (211, 51200, 5120),
+                 (211, 5120, 25600), (588, 3456, 1152), (588, 1152, 1152), (588, 4304, 1152), (588, 1152, 4304),
+                 (968, 2560, 2048), (968, 32768, 2048), (968, 2048, 16384)]
+
+
 def bench_attention(B, Sq, H, Hkv, D, cross=0, causal_tail=0, iters=20, with_sdpa=True, backward=False) -> dict:
     from opentau_b200 import ops
     from opentau_b200.ops import attention_native, cuda_ops
@@ -187,6 +230,9 @@ def main(argv=None):
     a.add_argument("--no-sdpa", action="store_true")
     a.add_argument("--backward", action="store_true")
     sub.add_parser("membound")
+    sk = sub.add_parser("skinny")
+    sk.add_argument("--shape", type=int, nargs=3, action="append", default=None, metavar=("M", "N", "K"))
+    sk.add_argument("--iters", type=int, default=20)
     sub.add_parser("suite")
     args = ap.parse_args(argv)
     if args.cmd == "gemm":
@@ -197,6 +243,8 @@ def main(argv=None):
     elif args.cmd == "membound":
         for r in bench_membound():
             print(json.dumps(r))
+    elif args.cmd == "skinny":
+        bench_skinny([tuple(x) for x in args.shape] if args.shape else SKINNY_SHAPES, args.iters)
     else:
         M = 39264
         for (l, m, n, k, glu) in [("nt", 8192, 8192, 8192, None), ("nt", M, 2560, 2048, None),

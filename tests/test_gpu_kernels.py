@@ -70,7 +70,7 @@ def test_gemm_epilogues(dev):
 
 @pytest.mark.parametrize("shape", [(51, 1024, 2048), (1, 256, 64), (64, 4096, 1024), (100, 1152, 4304), (128, 128, 128),
                                    (211, 5120, 1000), (588, 1152, 1152), (300, 200, 72)])
-@pytest.mark.parametrize("splits", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 4, 7, 8])
 def test_skinny_gemm_matches_fp32(shape, splits, dev):
     """Weight-streaming split-K kernel: all token-tile widths, several token chunks, ragged N and K, every cluster size."""
     from opentau_b200.ops import cuda_ops
@@ -105,7 +105,7 @@ def test_skinny_gemm_epilogues(splits, dev):
 
 
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
-@pytest.mark.parametrize("splits", [1, 2, 8])
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
 @pytest.mark.parametrize("M", [51, 200])
 def test_skinny_gemm_glu(act, splits, M, dev):
     from opentau_b200.ops import cuda_ops, prims
