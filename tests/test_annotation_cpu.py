@@ -209,3 +209,26 @@ def test_ros_bag_conversion_with_fake_messages(tmp_path):
     assert np.allclose(rows["observation.state"][0], [1.0, 2.0, 0.1, 0.2])           # reordered to j1, j2; velocities appended
     assert rows["observation.state"][4][0] == 1.0 + 8                     # 0.4 s -> the 20 Hz sample number 8
     assert rows["action"][7] == [15.0, 25.0]                              # 0.7 s -> command number 5
+
+
+def test_human_video_conversion_with_a_stub_detector(tmp_path):
+    import cv2
+    from types import SimpleNamespace as NS
+
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDatasetMetadata
+    from opentau_b200.scripts.human_video_to_lerobot import convert, landmarks_to_state
+    st = landmarks_to_state([[NS(x=1, y=2, z=3), NS(x=4, y=5, z=6)], [NS(x=7, y=8, z=9)]], 12, 6)
+    assert st.tolist() == [1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 0, 0]
+    assert landmarks_to_state(None, 6, 6).tolist() == [0] * 6
+    video = tmp_path / "in.mp4"
+    wr = cv2.VideoWriter(str(video), cv2.VideoWriter_fourcc(*"mp4v"), 20.0, (64, 48))
+    for i in range(20):
+        wr.write(np.full((48, 64, 3), 10 * i, np.uint8))
+    wr.release()
+    rep = convert(video, tmp_path / "ds", "wave", lambda rgb: np.full(6, rgb[0, 0, 0] / 10.0), 6, fps=10)
+    assert rep == {"frames": 10, "fps": 10, "state_dim": 6}
+    meta = LeRobotDatasetMetadata("ds", root=tmp_path / "ds")
+    rows = pq.read_table(add_subtask_response.episode_parquet(tmp_path / "ds", meta.info, 0)).to_pydict()
+    s, a = np.array(rows["observation.state"]), np.array(rows["action"])
+    assert np.allclose(a[:-1], s[1:], atol=1e-6) and np.allclose(a[-1], s[-1]) and meta.tasks[0] == "wave"
+    assert abs(s[3, 0] - 6.0) < 0.5                                    # every 2nd frame of the 20 fps video
