@@ -161,10 +161,11 @@ class DualStreamDecoder(nn.Module):
                 continue
             if g1 is None and drop is None:
                 y = layer.self_attn.o_proj(a, residual=x)
+            elif drop is None:
+                op = layer.self_attn.o_proj
+                y = ops.linear_gated_residual(a.to(op.weight.dtype), op.weight, op.bias, x, g1)
             else:
-                o = layer.self_attn.o_proj(a)
-                if drop is not None:
-                    o = drop(o)
+                o = drop(layer.self_attn.o_proj(a))
                 y = ops.gated_residual(x, o, g1)
             if mods[ti] is not None:
                 n, g2 = layer.post_attention_layernorm(y, precomputed=mods[ti][2 * li + 1])
@@ -172,10 +173,12 @@ class DualStreamDecoder(nn.Module):
                 n, g2 = layer.post_attention_layernorm(y)
             if g2 is None and drop is None:
                 outs.append(layer.mlp(n, residual=y))
+            elif drop is None:
+                mlp = layer.mlp
+                outs.append(ops.gated_mlp_gated_residual(n.to(mlp.gate_up_proj.weight.dtype), mlp.gate_up_proj.weight,
+                                                         mlp.down_proj.weight, mlp.act, y, g2))
             else:
-                m = layer.mlp(n)
-                if drop is not None:
-                    m = drop(m)
+                m = drop(layer.mlp(n))
                 outs.append(ops.gated_residual(y, m, g2))
         return outs, new_k, new_v
 

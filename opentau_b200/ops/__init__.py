@@ -64,6 +64,43 @@ def gated_residual(x: Tensor, y: Tensor, gate: Tensor | None) -> Tensor:
     return ref.gated_residual(x, y, gate)
 
 
+def _gate_rows(gate: Tensor, x: Tensor):
+    """``gate (B,1,H) | (B,T,H)`` as 2-D rows for the GEMM epilogue, or None when it cannot be passed as is."""
+    g = gate.reshape(-1, gate.shape[-1])
+    if g.dtype != x.dtype or g.stride(1) != 1 or g.stride(0) % 8 or g.data_ptr() % 16:
+        return None
+    rows = x.shape[0] * x.shape[1]
+    return g if rows % g.shape[0] == 0 else None
+
+
+def linear_gated_residual(x: Tensor, w: Tensor, bias: Tensor | None, residual: Tensor, gate: Tensor | None) -> Tensor:
+    """``residual + gate * linear(x)``.  At inference with few rows the gate and the residual are applied in the
+    epilogue of the projection (one launch); otherwise projection and gated residual run separately."""
+    if gate is not None and x.dim() == 3 and _native_nograd(x, w, residual, gate):
+        from . import cuda_ops
+        rows, g2 = x.shape[0] * x.shape[1], _gate_rows(gate, x)
+        if g2 is not None and cuda_ops.use_skinny("nt", rows, w.shape[0], False, 0) and w.shape[0] % 8 == 0 \
+                and x.shape[-1] % 8 == 0:
+            out = cuda_ops.gemm(x.reshape(rows, -1), w, "nt", bias=bias, residual=residual.reshape(rows, -1).contiguous(),
+                                gate=g2)
+            return out.view(*x.shape[:-1], w.shape[0])
+    return gated_residual(residual, linear(x, w, bias), gate)
+
+
+def gated_mlp_gated_residual(x: Tensor, w_gate_up: Tensor, w_down: Tensor, act: str, residual: Tensor,
+                             gate: Tensor | None) -> Tensor:
+    """``residual + gate * down(act(gate_proj x) * up_proj x)`` with the same epilogue fusion at inference."""
+    if gate is not None and x.dim() == 3 and _native_nograd(x, w_gate_up, residual, gate):
+        from . import cuda_ops
+        rows, g2 = x.shape[0] * x.shape[1], _gate_rows(gate, x)
+        if g2 is not None and cuda_ops.use_skinny("nt", rows, w_down.shape[0], False, 0) \
+                and cuda_ops.use_skinny("nt", rows, w_gate_up.shape[0], False, 0):
+            h = cuda_ops.gemm(x.reshape(rows, -1), w_gate_up, "nt", glu=act, store_out=False)
+            out = cuda_ops.gemm(h, w_down, "nt", residual=residual.reshape(rows, -1).contiguous(), gate=g2)
+            return out.view(*x.shape[:-1], w_down.shape[0])
+    return gated_residual(residual, gated_mlp(x, w_gate_up, w_down, act), gate)
+
+
 def qkv_post(qkv: Tensor, heads: int, kv_heads: int, head_dim: int, q_norm, k_norm, cos: Tensor, sin: Tensor,
              k_dst: Tensor | None = None, v_dst: Tensor | None = None):
     """Inference-only fusion after the q/k/v projection of one tower: split, optional per-head RMSNorm of q and k
@@ -154,7 +191,7 @@ def resize_with_pad(img: Tensor, width: int, height: int, pad_value: float = -1.
 
 
 __all__ = [
-    "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
+    "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "linear_gated_residual", "gated_mlp_gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
     "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
     "resize_with_pad", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
     "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "oracle_mode", "prims", "fused", "ref",

@@ -475,25 +475,40 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   const int head = int(row % H);
   const long long bp = row / H;                    // b * Sq + pos
   const int pos = int(bp % Sq), b = int(bp / Sq);
-  float w[8];
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) {
-    const float2 ml = part_ml[(((long long)s * B + b) * H + head) * Sq + pos];
-    w[s] = ml.y > 0.f ? ml.x : -INFINITY;          // reuse w[] for the maxima first
-    M = fmaxf(M, w[s]);
+  // lane s < nsplit owns split s: (maximum, row sum); the weights travel by shuffle
+  float m_s = -INFINITY, l_s = 0.f;
+  if (lane < nsplit) {
+    const float2 ml = part_ml[(((long long)lane * B + b) * H + head) * Sq + pos];
+    l_s = ml.y;
+    m_s = ml.y > 0.f ? ml.x : -INFINITY;
   }
-  float L = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    const float2 ml = part_ml[(((long long)s * B + b) * H + head) * Sq + pos];
-    w[s] = (w[s] == -INFINITY) ? 0.f : fast_exp2(w[s] - M);
-    L += ml.y * w[s];
-  }
+  float M = m_s;
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));   // nsplit <= 8
+  const float w_s = (m_s == -INFINITY) ? 0.f : fast_exp2(m_s - M);
+  float L = l_s * w_s;
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+  M = __shfl_sync(0xffffffffu, M, 0);
+  L = __shfl_sync(0xffffffffu, L, 0);
   const float inv = L > 0.f ? 1.f / L : 0.f;
-  for (int d = lane; d < D; d += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < nsplit; ++s)
-      if (w[s] != 0.f) acc += part_o[(((long long)s * B + b) * Sq + pos) * H * D + (long long)head * D + d] * w[s];
-    o[row * D + d] = __float2bfloat16(acc * inv);
+  float w[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) w[s] = __shfl_sync(0xffffffffu, w_s, s) * inv;   // zero for s >= nsplit
+  const long long split_stride = (long long)B * Sq * H * D;
+  const float* src = part_o + (bp * H + head) * (long long)D;
+  for (int c = lane; c < D / 4; c += 32) {
+    float4 v[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      v[s] = s < nsplit ? *reinterpret_cast<const float4*>(src + s * split_stride + c * 4) : make_float4(0, 0, 0, 0);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      acc.x += v[s].x * w[s]; acc.y += v[s].y * w[s]; acc.z += v[s].z * w[s]; acc.w += v[s].w * w[s];
+    }
+    uint2 packed = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    *reinterpret_cast<uint2*>(o + row * D + c * 4) = packed;
   }
   if (lane == 0) lse[((long long)b * H + head) * Sq + pos] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : 0.f;
 }

@@ -35,6 +35,7 @@ enum SkinnyFlags {  // same values as the big GEMM's epilogue flags
   SK_BIAS_F32 = 64,
   SK_NO_OUT = 128,
   SK_ACT_GELU = 256,
+  SK_GATE = 512,       // with SK_RESIDUAL: out = residual + gate * result (adaptive-norm gate of the residual branch)
 };
 
 struct SkinnyParams {
@@ -46,6 +47,9 @@ struct SkinnyParams {
   long long ldr;
   __nv_bfloat16* out2;
   long long ldo2;
+  const __nv_bfloat16* gate;      // rows of N gates; row (m / rows_per_gate), row stride gate_stride
+  long long gate_stride;
+  int rows_per_gate;
   int flags;
   int splits;
   KernelStatus* status;
@@ -98,7 +102,10 @@ __device__ __forceinline__ void skinny_store(const SkinnyParams& p, int m, int n
                                : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
   }
   if (flags & SK_ACT_GELU) v = gelu_tanh_f(v);
-  if (flags & SK_RESIDUAL) v += __bfloat162float(p.residual[(long long)m * p.ldr + n]);
+  if (flags & SK_RESIDUAL) {
+    if (flags & SK_GATE) v *= __bfloat162float(p.gate[(long long)(m / p.rows_per_gate) * p.gate_stride + n]);
+    v += __bfloat162float(p.residual[(long long)m * p.ldr + n]);
+  }
   if (flags & SK_OUT_F32) {
     static_cast<float*>(p.out)[(long long)m * p.ldo + n] = v;
   } else {
@@ -323,12 +330,14 @@ using namespace otb;
 // every CTA keeps at least two k-blocks).
 extern "C" int otb_gemm_skinny_bf16(const void* X, const void* W, void* out, int M, int N, int K, long long ldx,
                                     long long ldw, long long ldo, const void* bias, const void* residual,
-                                    long long ldr, void* out2, long long ldo2, int flags, int splits_override,
+                                    long long ldr, void* out2, long long ldo2, const void* gate,
+                                    long long gate_stride, int rows_per_gate, int flags, int splits_override,
                                     void* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -2;
   if ((ldx % 8) || (ldw % 8)) return -3;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15) return -4;
   if (flags & 4) return -9;                                  // accumulate-into-output is the big GEMM's job
+  if ((flags & SK_GATE) && (!(flags & SK_RESIDUAL) || gate == nullptr || rows_per_gate < 1)) return -10;
   const bool glu = (flags & (SK_GLU_GELU | SK_GLU_SILU)) != 0;
   if (glu && ((N % 64) || out2 == nullptr)) return -6;
   if (!(flags & SK_NO_OUT) && out == nullptr) return -6;
@@ -369,6 +378,7 @@ extern "C" int otb_gemm_skinny_bf16(const void* X, const void* W, void* out, int
   p.bias = bias;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
   p.out2 = static_cast<__nv_bfloat16*>(out2); p.ldo2 = ldo2;
+  p.gate = static_cast<const __nv_bfloat16*>(gate); p.gate_stride = gate_stride; p.rows_per_gate = rows_per_gate;
   p.flags = flags;
   p.splits = splits;
   p.status = static_cast<KernelStatus*>(status);

@@ -20,7 +20,7 @@ from . import _lib
 launch_count = 0  # number of native kernel launches issued through this module (for benchmarks)
 
 EPI_BIAS, EPI_RESIDUAL, EPI_ACCUM, EPI_OUT_F32 = 1, 2, 4, 8
-EPI_GLU_GELU, EPI_GLU_SILU, EPI_BIAS_F32, EPI_NO_OUT, EPI_ACT_GELU = 16, 32, 64, 128, 256
+EPI_GLU_GELU, EPI_GLU_SILU, EPI_BIAS_F32, EPI_NO_OUT, EPI_ACT_GELU, EPI_GATE = 16, 32, 64, 128, 256, 512
 
 _status_ptr: dict[int, int] = {}
 
@@ -65,19 +65,18 @@ SKINNY = os.environ.get("OPENTAU_B200_SKINNY_GEMM", "1") != "0"
 
 
 def use_skinny(layout: str, M: int, N: int, accumulate: bool, bn: int) -> bool:
-    """``x @ W^T`` with few rows goes to the weight-streaming split-K kernel: always up to 256 rows (the weights
-    cross shared memory once), and up to 1024 rows while the 128-row tiling would leave most SMs without a tile."""
+    """``x @ W^T`` with few rows goes to the weight-streaming split-K kernel."""
     if not SKINNY or layout != "nt" or accumulate or bn:
         return False
-    if M <= 256:
-        return True
-    return M <= 1024 and ((M + 127) // 128) * ((N + 127) // 128) < 100
+    # measured: up to 128 rows the split-K kernel always wins; a 129..256-row product keeps its advantage only while
+    # the 128 x 256 tiling has too few tiles (N <= 8192); beyond that the persistent kernel is faster
+    return M <= 128 or (M <= 256 and N <= 8192)
 
 
 def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual: Tensor | None = None,
          out: Tensor | None = None, accumulate: bool = False, out_dtype: torch.dtype | None = None,
          glu: str | None = None, glu_out: Tensor | None = None, store_out: bool = True, act: str | None = None,
-         bn: int = 0, splits: int = 0) -> Tensor:
+         bn: int = 0, splits: int = 0, gate: Tensor | None = None) -> Tensor:
     """tcgen05 GEMM.  layout 'nt': a(M,K) b(N,K); 'nn': a(M,K) b(K,N); 'tn': a(K,M) b(K,N).  ``bn`` forces the column
     tile of the persistent kernel, ``splits`` (1, 2, 4, 8) forces the weight-streaming split-K kernel."""
     global launch_count
@@ -146,11 +145,21 @@ def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual
         ldo2 = glu_out.stride(0)
     if splits and (layout != "nt" or accumulate):
         raise ValueError("the split-K kernel computes a @ b^T without accumulation")
-    if splits or use_skinny(layout, M, N, accumulate, bn):
+    skinny = bool(splits) or use_skinny(layout, M, N, accumulate, bn)
+    g_stride, g_rows = 0, 1
+    if gate is not None:
+        # out = residual + gate * (a @ b^T): rows of N gates, one per `M / gate rows` consecutive output rows
+        if not skinny or residual is None or gate.dim() != 2 or gate.shape[1] != N or gate.stride(1) != 1 \
+                or gate.dtype != torch.bfloat16 or M % gate.shape[0]:
+            raise ValueError("a gated residual epilogue needs the few-row kernel, a residual and (rows, N) bf16 gates")
+        flags |= EPI_GATE
+        g_stride, g_rows = gate.stride(0), M // gate.shape[0]
+    if skinny:
         rc = _lib.load("gemm_skinny_tcgen05").otb_gemm_skinny_bf16(
             _p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
             c_longlong(out.stride(0) if out is not None else N), _p(bias), _p(residual), c_longlong(ldr), _p(glu_out),
-            c_longlong(ldo2), c_int(flags), c_int(splits), c_void_p(status_pointer()), _stream())
+            c_longlong(ldo2), _p(gate), c_longlong(g_stride), c_int(g_rows), c_int(flags), c_int(splits),
+            c_void_p(status_pointer()), _stream())
         _check(rc, f"gemm_skinny[{M}x{N}x{K}]")
         launch_count += 1
         if glu is not None:

@@ -316,3 +316,34 @@ def test_gated_residual_native(per_token, dev):
         got = ops.gated_residual(x, y, gate)
     want = x.float() + y.float() * gate.float()
     torch.testing.assert_close(got.float(), want, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("per_token", [False, True])
+@pytest.mark.parametrize("splits", [0, 1, 4])
+def test_skinny_gemm_gated_residual_epilogue(per_token, splits, dev):
+    """out = residual + gate * (x @ W^T): the adaptive-norm gate of a residual branch applied in the projection."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import cuda_ops
+    B, T, K, N = 2, 51, 512, 1024
+    x = (torch.randn(B, T, K, device=dev) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    res = torch.randn(B, T, N, device=dev).to(torch.bfloat16)
+    mod = torch.randn(B, T if per_token else 1, 3 * N, device=dev).to(torch.bfloat16)
+    gate = mod[..., 2 * N:]
+    want = res.float() + gate.float() * (x.float() @ w.float().t())
+    g2 = gate.reshape(-1, N)
+    got = cuda_ops.gemm(x.view(B * T, K), w, "nt", residual=res.view(B * T, N), gate=g2, splits=splits)
+    torch.testing.assert_close(got.float().view(B, T, N), want, atol=6e-2, rtol=3e-2)
+    with torch.no_grad():
+        via_ops = ops.linear_gated_residual(x, w, None, res, gate)
+    torch.testing.assert_close(via_ops.float(), want, atol=6e-2, rtol=3e-2)
+    wgu = (torch.randn(2 * 768, K, device=dev) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(K, 768, device=dev) * 0.05).to(torch.bfloat16)
+    resk = torch.randn(B, T, K, device=dev).to(torch.bfloat16)
+    modk = torch.randn(B, T if per_token else 1, 3 * K, device=dev).to(torch.bfloat16)
+    gk = modk[..., 2 * K:]
+    with torch.no_grad():
+        fused = ops.gated_mlp_gated_residual(x, wgu, wd, "silu", resk, gk)
+        plain = ops.gated_residual(resk, ops.gated_mlp(x, wgu, wd, "silu"), gk)
+    torch.testing.assert_close(fused.float(), plain.float(), atol=6e-2, rtol=3e-2)
+    cuda_ops.check_status()
