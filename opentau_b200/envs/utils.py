@@ -48,6 +48,14 @@ def add_envs_task(env, observation: dict[str, Any]) -> dict[str, Any]:
     return observation
 
 
+def add_subgoal_images(observation: dict[str, Any], generator) -> dict[str, Any]:
+    """Merges ``subgoal{k}`` / ``subgoal_is_pad`` from a subgoal generator into the observation (no-op for None; the
+    policy then falls back to zero subgoals marked as padding).  ``generator.start_episode`` must have run."""
+    if generator is not None:
+        observation.update(generator(observation))
+    return observation
+
+
 def check_env_attributes_and_types(env) -> None:
     import warnings
     for attr in ("task_description", "task"):

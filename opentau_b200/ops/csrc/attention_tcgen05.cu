@@ -132,6 +132,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base;            // two buffers of BN columns
   const uint32_t tmem_O = tmem_base + 2 * BN;   // Dmma columns
+  pdl_launch_dependents();                      // after the TMEM allocation (see common.cuh)
+  pdl_wait();                                   // q / k / v and the masks come from the preceding kernels
 
   // ---- how many keys can this tile reach?  1 + the last key index j that is valid and has
   //      k_blk[j] <= the largest valid q_blk in the tile (no monotonicity assumed).
@@ -468,6 +470,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int nsplit, int B, int Sq,
                                     int H, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long rows = (long long)B * Sq * H;
@@ -535,13 +539,12 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   }
   const int pos_per_tile = ATT_M / p.g;
   dim3 grid(((p.Sq + pos_per_tile - 1) / pos_per_tile) * p.nsplit, p.Hkv, p.B);
-  kern<<<grid, 320, L::TOTAL, stream>>>(tq, tk, tv, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kern, grid, dim3(320), (size_t)L::TOTAL, stream, 0u, tq, tk, tv, p);
   if (e != cudaSuccess || p.nsplit == 1) return (int)e;
   const long long rows = (long long)p.B * p.Sq * p.H;
-  attn_combine_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p.part_o, p.part_ml, p.o, p.lse,
-                                                                              p.nsplit, p.B, p.Sq, p.H, p.D);
-  return (int)cudaGetLastError();
+  e = launch_pdl(attn_combine_kernel, dim3((unsigned)((rows * 32 + 255) / 256)), dim3(256), 0, stream, 0u,
+                 (const float*)p.part_o, (const float2*)p.part_ml, p.o, p.lse, p.nsplit, p.B, p.Sq, p.H, p.D);
+  return (int)e;
 }
 
 }  // namespace otb

@@ -33,6 +33,18 @@ __device__ __forceinline__ void report_timeout(KernelStatus* st, unsigned kernel
   }
 }
 
+// ---------------------------------------------------------------------------------------- dependent launch
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may become resident while
+// its predecessor still runs.  Pattern used by every kernel here that opts in:
+//   set-up that touches no global data (barriers, TMEM allocation)  ->  pdl_launch_dependents()  ->  pdl_wait()
+//   ->  everything that reads inputs or writes outputs.
+// launch_dependents comes AFTER the TMEM allocation on purpose: a successor is scheduled only once every CTA of this
+// grid has passed that point, so it can never hold tensor-memory columns that a CTA of this grid is still waiting
+// for.  pdl_wait() returns when the predecessor grid has completed and its writes are visible; in a kernel launched
+// without the attribute both calls are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------- misc
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -257,12 +269,52 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 
 // ---------------------------------------------------------------------------------------- host side
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 namespace otb {
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// OPENTAU_B200_PDL=0 turns programmatic dependent launch off (every kernel then starts after its predecessor ended)
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("OPENTAU_B200_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+// Kernel launch with the dependent-launch attribute (and an optional cluster shape along y).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              unsigned cluster_y, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_y > 0) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = cluster_y;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 inline PFN_encodeTiled get_encode_fn() {
   static PFN_encodeTiled fn = nullptr;

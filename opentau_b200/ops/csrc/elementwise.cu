@@ -64,6 +64,8 @@ __global__ void rms_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long x_
                                long long mod_stride, int rows_per_mod, __nv_bfloat16* __restrict__ y,
                                float* __restrict__ rstd_out, int H, float eps, int mode) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * x_stride;
   float v[MAXV][8];
@@ -402,6 +404,8 @@ __global__ void qkv_post_kernel(const __nv_bfloat16* __restrict__ qkv, long long
                                 __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out, long long k_sb,
                                 long long k_ss, __nv_bfloat16* __restrict__ v_out, long long v_sb, long long v_ss, int B,
                                 int T, int H, int Hkv, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int slots = H + 2 * Hkv;
   const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -605,6 +609,19 @@ static inline int grid_for(long long work_items, int block, int max_blocks = 148
 using namespace otb;
 typedef __nv_bfloat16 bf16;
 
+// same dispatch through launch_pdl (the kernel must call pdl_wait() before it touches global memory)
+#define LAUNCH_BY_H_PDL(KERNEL, H, ...)                                                                     \
+  do {                                                                                                      \
+    int nvec = (H) >> 3;                                                                                    \
+    cudaError_t e_;                                                                                         \
+    if (nvec <= 128) e_ = launch_pdl(KERNEL<1>, grid, dim3(128), 0, stream, 0u, __VA_ARGS__);               \
+    else if (nvec <= 256) e_ = launch_pdl(KERNEL<1>, grid, dim3(256), 0, stream, 0u, __VA_ARGS__);          \
+    else if (nvec <= 512) e_ = launch_pdl(KERNEL<2>, grid, dim3(256), 0, stream, 0u, __VA_ARGS__);          \
+    else if (nvec <= 1024) e_ = launch_pdl(KERNEL<4>, grid, dim3(256), 0, stream, 0u, __VA_ARGS__);         \
+    else return -10;                                                                                        \
+    if (e_ != cudaSuccess) return (int)e_;                                                                  \
+  } while (0)
+
 #define LAUNCH_BY_H(KERNEL, H, ...)                                                    \
   do {                                                                                 \
     int nvec = (H) >> 3;                                                               \
@@ -620,8 +637,8 @@ extern "C" int otb_rms_fwd(const void* x, long long x_stride, const void* w, con
                            cudaStream_t stream) {
   if (H % 8 || rows <= 0) return -1;
   dim3 grid((unsigned)rows);
-  LAUNCH_BY_H(rms_fwd_kernel, H, (const bf16*)x, x_stride, (const bf16*)w, (const bf16*)mod, mod_stride,
-              rows_per_mod < 1 ? 1 : rows_per_mod, (bf16*)y, rstd, H, eps, mode);
+  LAUNCH_BY_H_PDL(rms_fwd_kernel, H, (const bf16*)x, x_stride, (const bf16*)w, (const bf16*)mod, mod_stride,
+                  rows_per_mod < 1 ? 1 : rows_per_mod, (bf16*)y, rstd, H, eps, mode);
   return (int)cudaGetLastError();
 }
 
@@ -696,10 +713,10 @@ extern "C" int otb_qkv_post(const void* qkv, long long ld, const void* qw, const
   if (D % 2 || D > 256 || B <= 0 || T <= 0) return -1;
   const long long warps = (long long)B * T * (H + 2 * Hkv);
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
-  qkv_post_kernel<<<blocks, 256, 0, stream>>>((const bf16*)qkv, ld, (const bf16*)qw, (const bf16*)kw, eps, unit_offset,
-                                              cosb, sinb, (bf16*)q_out, (bf16*)k_out, k_sb, k_ss, (bf16*)v_out, v_sb,
-                                              v_ss, B, T, H, Hkv, D);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(qkv_post_kernel, dim3(blocks), dim3(256), 0, stream, 0u, (const bf16*)qkv, ld,
+                             (const bf16*)qw, (const bf16*)kw, eps, unit_offset, cosb, sinb, (bf16*)q_out, (bf16*)k_out,
+                             k_sb, k_ss, (bf16*)v_out, v_sb, v_ss, B, T, H, Hkv, D);
+  return (int)e;
 }
 
 extern "C" int otb_ce_fwd(const float* logits, const long long* labels, float* loss, float* lse, long long rows,

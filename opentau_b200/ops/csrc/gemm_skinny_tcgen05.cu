@@ -161,13 +161,24 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();                 // after the TMEM allocation (see common.cuh)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      // The weights do not depend on the preceding kernel: the first ring of weight tiles is requested before the
+      // dependency wait, so their HBM latency overlaps the predecessor's tail.  Activations follow after the wait.
+      const int early = min(STAGES, nkb);
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
+        tma_load_2d(smem + i * L::STAGE_BYTES, &tma_w, &full_bar[i], (kb0 + i) * SK_BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(smem + i * L::STAGE_BYTES + L::W_BYTES, &tma_x, &full_bar[i], (kb0 + i) * SK_BK, m_base);
+      int stage = early == STAGES ? 0 : early;
+      uint32_t phase = early == STAGES ? 1 : 0;
+      for (int kb = kb0 + early; kb < kb1; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KID_SKINNY, 1, stage)) break;
         uint8_t* sw = smem + stage * L::STAGE_BYTES;
         uint8_t* sx = sw + L::W_BYTES;
@@ -207,6 +218,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
   } else {
     // ------------------------------------------------------------------ TMEM readers (warps 2..5)
+    pdl_wait();                                       // residual / gate / output buffers belong to the predecessor
     const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
     const int wrow = quad * 32 + lane;                // weight row inside the tile
     const int n = n0 + wrow;
@@ -246,6 +258,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 
   // ---------------------------------------------------------------------- cluster reduction + epilogue
   cluster_sync_all();                                 // every CTA's partial tile is complete and visible
+  pdl_wait();                                         // warps 0 / 1 join the reduction: they write outputs too
   if (!direct && !*abort_flag) {
     const uint32_t pbase = smem_u32(partial);
     if (!(p.flags & SK_NO_OUT)) {
@@ -304,20 +317,8 @@ static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Ski
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)n_tiles, (unsigned)p.splits, (unsigned)chunks);
-  cfg.blockDim = dim3(192, 1, 1);
-  cfg.dynamicSmemBytes = L::TOTAL;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = (unsigned)p.splits;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
+  cudaError_t e = launch_pdl(kern, dim3((unsigned)n_tiles, (unsigned)p.splits, (unsigned)chunks), dim3(192, 1, 1),
+                             (size_t)L::TOTAL, stream, (unsigned)p.splits, tw, tx, p);
   return (int)e;
 }
 

@@ -25,7 +25,7 @@ from ..configs import parser
 from ..configs.train import TrainPipelineConfig
 from ..envs.configs import EnvConfig
 from ..envs.factory import make_envs
-from ..envs.utils import add_envs_task, check_env_attributes_and_types, preprocess_observation
+from ..envs.utils import add_envs_task, add_subgoal_images, check_env_attributes_and_types, preprocess_observation
 from ..parallel import control
 
 
@@ -44,12 +44,16 @@ def _rank_seed_offset(rank: int, decorrelate: bool) -> int:
 
 
 def rollout(env, policy, seeds: list[int] | None = None, cfg=None, device=None, return_observations: bool = False,
-            extra_batch: dict[str, Any] | None = None) -> dict[str, Tensor]:
-    """One batch of episodes.  Returns ``action (B,T,A)``, ``reward (B,T)``, ``success (B,T)``, ``done (B,T)``."""
+            extra_batch: dict[str, Any] | None = None, subgoal_generator=None) -> dict[str, Tensor]:
+    """One batch of episodes.  Returns ``action (B,T,A)``, ``reward (B,T)``, ``success (B,T)``, ``done (B,T)``.
+    ``subgoal_generator`` (``envs.subgoal``) pins one subgoal per sub-environment at the reset and feeds it to the
+    policy at every step."""
     device = device or next(policy.parameters()).device
     policy.reset()
     obs, _ = env.reset(seed=seeds)
     check_env_attributes_and_types(env)
+    if subgoal_generator is not None:
+        subgoal_generator.start_episode(list(add_envs_task(env, preprocess_observation(obs, cfg))["prompt"]), seeds)
     max_steps = int(env.call("_max_episode_steps")[0])
     done = np.zeros(env.num_envs, dtype=bool)
     all_a, all_r, all_s, all_d, all_o = [], [], [], [], []
@@ -57,6 +61,7 @@ def rollout(env, policy, seeds: list[int] | None = None, cfg=None, device=None, 
     while not done.all() and step < max_steps:
         batch = preprocess_observation(obs, cfg)
         batch = add_envs_task(env, batch)
+        batch = add_subgoal_images(batch, subgoal_generator)
         batch = {k: (v.to(device) if isinstance(v, Tensor) else v) for k, v in batch.items()}
         if extra_batch:
             batch.update(extra_batch)

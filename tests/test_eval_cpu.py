@@ -63,3 +63,39 @@ def test_launcher_commands():
     assert cmd[-3:] == ["-m", "opentau_b200.scripts.train", "--steps=3"] and "127.0.0.1" in cmd
     cmd, _ = build_command("opentau_b200.scripts.eval", ["--num_processes=1", "--x=1"])
     assert cmd[1:] == ["-m", "opentau_b200.scripts.eval", "--x=1"]
+
+
+def test_subgoal_generators_feed_the_rollout(tmp_path):
+    """The dataset-backed generator serves the last frame of an episode with the environment's task string; the
+    goal-frame generator indexes pre-rendered frames by the rollout seed; both reach the policy at every step."""
+    from PIL import Image
+    from opentau_b200.envs.subgoal import GoalFrameSubgoalGenerator, LastFrameSubgoalGenerator
+    from test_datasets_cpu import _record
+    import pytest
+    _record(tmp_path / "toy", episodes=(5, 7, 4))                 # tasks: "task 0", "task 1", "task 0"
+    gen = LastFrameSubgoalGenerator(tmp_path / "toy", resolution=(32, 32), seed=0)
+    assert gen.known_languages == ["task 0", "task 1"]
+    envs = make_envs(FakeEnvConfig(tasks=["task 1"], episode_length=6), n_envs=2)
+    env = envs[next(iter(envs))][0]
+    seen = []
+
+    class Watch(Scripted):
+        def select_action(self, batch):
+            seen.append((batch["subgoal0"].clone(), batch["subgoal_is_pad"].clone()))
+            return super().select_action(batch)
+
+    rollout(env, Watch(1.0), seeds=[3, 4], device="cpu", subgoal_generator=gen)
+    sg, pad = seen[0]
+    assert sg.shape == (2, 3, 32, 32) and not pad.any() and len(seen) >= 1
+    # episode 1 (the only "task 1" episode) ends at global frame 11 -> pixel value (11 * 3) % 256 = 33
+    assert abs(float(sg[0, 0, 20, 16]) * 255 - 33) < 1.5 and torch.equal(seen[0][0], seen[-1][0])
+    with pytest.raises(ValueError, match="no episode"):
+        gen.start_episode(["unknown task"])
+    for s in range(3):
+        (tmp_path / "goals" / f"scene_{s}").mkdir(parents=True)
+        Image.fromarray(np.full((32, 32, 3), 50 * s, np.uint8)).save(tmp_path / "goals" / f"scene_{s}" / "0.png")
+    goals = GoalFrameSubgoalGenerator(tmp_path / "goals", resolution=(32, 32))
+    goals.start_episode(["a", "b"], seeds=[4, 2])
+    out = goals({"state": torch.zeros(2, 8)})
+    assert goals.num_scenes == 3 and abs(float(out["subgoal0"][0, 0, 0, 0]) * 255 - 50) < 1 \
+        and abs(float(out["subgoal0"][1, 0, 0, 0]) * 255 - 100) < 1
