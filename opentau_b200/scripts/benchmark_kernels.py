@@ -118,6 +118,60 @@ def bench_skinny(shapes: list[tuple[int, int, int]], iters: int = 20) -> list[di
     return rows
 
 
+def graph_us(fns, reps: int = 10) -> float:
+    """Per-call device time of a chain of launches replayed from one CUDA graph (no host launch cost): what a call
+    costs inside the captured sampler."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in fns:
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(fns))
+
+
+def bench_skinny_graph(shapes: list[tuple[int, int, int]], chain: int = 32) -> list[dict]:
+    """The few-row products replayed from a CUDA graph, `chain` launches over rotating weights, per cluster size."""
+    from opentau_b200.ops import cuda_ops
+    dev = torch.device("cuda")
+    rows = []
+    for M, N, K in shapes:
+        nb = max(_n_buffers(2 * N * K), 4)
+        xs = [torch.randn(M, K, device=dev).to(torch.bfloat16) for _ in range(nb)]
+        ws = [torch.randn(N, K, device=dev).to(torch.bfloat16) for _ in range(nb)]
+        outs = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(nb)]
+        rec = {"kernel": "gemm_skinny_tcgen05 (graph replay)", "M": M, "N": N, "K": K}
+        for s_ in (1, 2, 3, 4, 6, 8):
+            if (K + 63) // 64 < 2 * s_:
+                continue
+            fns = [lambda i=i: cuda_ops.gemm(xs[i % nb], ws[i % nb], "nt", out=outs[i % nb], splits=s_)
+                   for i in range(chain)]
+            rec[f"splits{s_}_us"] = round(graph_us(fns), 2)
+        fns = [lambda i=i: cuda_ops.gemm(xs[i % nb], ws[i % nb], "nt", out=outs[i % nb], bn=128 if N < 4096 else 256)
+               for i in range(chain)]
+        rec["persistent_us"] = round(graph_us(fns), 2)
+        fns = [lambda i=i: torch.matmul(xs[i % nb], ws[i % nb].t(), out=outs[i % nb]) for i in range(chain)]
+        rec["library_us"] = round(graph_us(fns), 2)
+        rec["hbm_floor_us"] = round(2 * N * K / peaks()["gbs"] / 1e3, 2)
+        cuda_ops.check_status()
+        rows.append(rec)
+        print(json.dumps(rec), flush=True)
+    return rows
+
+
 # (rows, out features, in features): pi0.5 expert / cosmos3 expert, backbone prefix and vision tower products
 SKINNY_SHAPES = [(51, 2560, 1024), (51, 1024, 2048), (51, 8192, 1024), (51, 1024, 4096),
                  (51, 4096, 1024), (51, 1024, 2048), (211, 10240, 5120), (211, 5120, 8192), (211, 51200, 5120),
@@ -233,6 +287,7 @@ def main(argv=None):
     sk = sub.add_parser("skinny")
     sk.add_argument("--shape", type=int, nargs=3, action="append", default=None, metavar=("M", "N", "K"))
     sk.add_argument("--iters", type=int, default=20)
+    sk.add_argument("--graph", action="store_true", help="time the launches inside a replayed CUDA graph")
     sub.add_parser("suite")
     args = ap.parse_args(argv)
     if args.cmd == "gemm":
@@ -244,7 +299,8 @@ def main(argv=None):
         for r in bench_membound():
             print(json.dumps(r))
     elif args.cmd == "skinny":
-        bench_skinny([tuple(x) for x in args.shape] if args.shape else SKINNY_SHAPES, args.iters)
+        shapes = [tuple(x) for x in args.shape] if args.shape else SKINNY_SHAPES
+        bench_skinny_graph(shapes) if args.graph else bench_skinny(shapes, args.iters)
     else:
         M = 39264
         for (l, m, n, k, glu) in [("nt", 8192, 8192, 8192, None), ("nt", M, 2560, 2048, None),
