@@ -136,8 +136,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   pdl_wait();                                   // q / k / v and the masks come from the preceding kernels
 
   // ---- how many keys can this tile reach?  1 + the last key index j that is valid and has
-  //      k_blk[j] <= the largest valid q_blk in the tile (no monotonicity assumed).
-  {
+  //      k_blk[j] <= the largest valid q_blk in the tile (no monotonicity assumed).  With split keys the scan is
+  //      skipped: the few tiles of such a launch reach (almost) every key, blocks without a visible key cost one
+  //      masked pass, and the scan itself is a serial prologue of two dependent global reads per key.
+  if (p.nsplit > 1) {
+    if (threadIdx.x == 0) *kv_end_smem = p.Sk;
+    __syncthreads();
+  } else {
     int qmax = INT_MIN;
     bool any_q = false;
     for (int i = threadIdx.x; i < pos_per_tile; i += blockDim.x) {

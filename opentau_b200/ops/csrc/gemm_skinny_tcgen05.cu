@@ -142,6 +142,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   const bool glu = (p.flags & (SK_GLU_GELU | SK_GLU_SILU)) != 0;
   const bool direct = S == 1 && !glu;                // straight from TMEM to global memory
 
+  const int early = min(STAGES, nkb);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -150,8 +151,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     mbar_init(tfull_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tma_w);
     tma_prefetch_desc(&tma_x);
+    // The weights do not depend on the preceding kernel: the first ring of weight tiles is requested at once, before
+    // the TMEM allocation, the block barrier and the dependency wait, so that their HBM latency overlaps all three
+    // (and, under programmatic dependent launch, the predecessor's tail).  Activations follow after the wait.
+    for (int i = 0; i < early; ++i) {
+      mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
+      tma_load_2d(smem + i * L::STAGE_BYTES, &tma_w, &full_bar[i], (kb0 + i) * SK_BK, n0);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, NT);   // 64 / 128 / 256 columns
@@ -166,13 +173,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      // The weights do not depend on the preceding kernel: the first ring of weight tiles is requested before the
-      // dependency wait, so their HBM latency overlaps the predecessor's tail.  Activations follow after the wait.
-      const int early = min(STAGES, nkb);
-      for (int i = 0; i < early; ++i) {
-        mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
-        tma_load_2d(smem + i * L::STAGE_BYTES, &tma_w, &full_bar[i], (kb0 + i) * SK_BK, n0);
-      }
       pdl_wait();
       for (int i = 0; i < early; ++i)
         tma_load_2d(smem + i * L::STAGE_BYTES + L::W_BYTES, &tma_x, &full_bar[i], (kb0 + i) * SK_BK, m_base);
