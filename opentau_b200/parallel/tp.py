@@ -164,6 +164,19 @@ class TensorParallel:
         cuda_ops.launch_count += 2
         return out
 
+    def fsdp_linear(self, x: Tensor, w_shard: Tensor, bias: Tensor | None = None) -> Tensor:
+        """Parameter-sharded (FSDP / ZeRO-3 style) linear: every rank owns ``w_shard [N/W, K]`` (consecutive output
+        rows of the weight) and has its OWN activations ``x [M, K]``; returns ``x @ W_full^T (+ bias)`` as ``[M, N]``.
+
+        The parameter all-gather is fused into the GEMM that consumes it: the weight shards are the gathered operand
+        of the all-gather -> GEMM kernel (copier warps pull each peer's shard over NVLink once while the tensor-core
+        tiles of shards that already arrived run), the local activations are the stationary operand, and the kernel
+        produces ``W_full @ x^T``; the result is returned as its transposed view (call ``.contiguous()`` where a
+        row-major tensor is required).  Nothing of the full weight outlives the call."""
+        yt = self.all_gather_linear(w_shard, x)          # [N, M]
+        y = yt.t()
+        return y + bias if bias is not None else y
+
     # -- GEMM -> reduce-scatter -------------------------------------------------------------------------
     def linear_reduce_scatter(self, x: Tensor, w: Tensor, bias: Tensor | None = None,
                               residual: Tensor | None = None) -> Tensor:

@@ -105,6 +105,14 @@ def _tp_worker(rank, world, port, ret):
             for _ in range(4):                       # several steps: both parities of every workspace are reused
                 got, _, _ = tpl(x_local, B, S, cs, blk, valid)
                 errs.append(float((got.float() - want[rank * Ml:(rank + 1) * Ml].float()).abs().max()))
+            # parameter-sharded linear: weight rows split over the ranks, every rank with its own activations
+            w_full = (torch.randn(1024, d, device=dev) * 0.05).to(torch.bfloat16)
+            dist.broadcast(w_full, 0)
+            xa = torch.randn(192, d, device=dev).to(torch.bfloat16)          # differs per rank (seeded per device)
+            shard = w_full[rank * 512:(rank + 1) * 512].contiguous()
+            for _ in range(3):
+                got = tp.fsdp_linear(xa, shard)
+                errs.append(float((got.float() - xa.float() @ w_full.float().t()).abs().max()) / 4.0)
             torch.cuda.synchronize()
             cuda_ops.check_status()
         allerr = [None] * world

@@ -47,6 +47,12 @@ def _rank_main(rank, world, port, ret):
         got, k, v = tpl(x_local, B, S, cs, blk, valid)
         assert k.shape == (B, S, 1, 32) and v.shape == (B, S, 1, 32)
         err = (got - want.view(B * S, d)[rank * Ml:(rank + 1) * Ml]).abs().max().item()
+        # parameter-sharded linear: each rank owns half of the weight rows and has its own activations
+        w_full = torch.randn(24, d)
+        xa = torch.randn(5, d, generator=torch.Generator().manual_seed(100 + rank))
+        bias = torch.randn(24)
+        y = tp.fsdp_linear(xa, w_full[rank * 12:(rank + 1) * 12].contiguous(), bias)
+        err = max(err, (y - (xa @ w_full.t() + bias)).abs().max().item())
         gathered = [None] * world
         dist.all_gather_object(gathered, err)
         if rank == 0:
