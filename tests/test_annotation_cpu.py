@@ -232,3 +232,41 @@ def test_human_video_conversion_with_a_stub_detector(tmp_path):
     s, a = np.array(rows["observation.state"]), np.array(rows["action"])
     assert np.allclose(a[:-1], s[1:], atol=1e-6) and np.allclose(a[-1], s[-1]) and meta.tasks[0] == "wave"
     assert abs(s[3, 0] - 6.0) < 0.5                                    # every 2nd frame of the 20 fps video
+
+
+def test_headset_recording_conversion(tmp_path):
+    import cv2
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDatasetMetadata
+    from opentau_b200.scripts import recordhuman_to_lerobot as rh
+    # quaternion algebra: a 90 degree turn about z, its inverse and the composition
+    qz = np.array([0, 0, np.sin(np.pi / 4), np.cos(np.pi / 4)])
+    assert np.allclose(rh.quat_to_rotation_matrix(qz) @ [1, 0, 0], [0, 1, 0], atol=1e-9)
+    assert np.allclose(rh.quat_multiply(qz, rh.quat_inverse(qz)), [0, 0, 0, 1], atol=1e-9)
+    # a point one metre ahead of a head turned by qz, seen from that head, lies on the camera's own x axis
+    cam = rh.world_to_camera(np.array([[0.0, 1.0, 0.0]]), np.zeros(3), qz)
+    assert np.allclose(cam, [[1, 0, 0]], atol=1e-9)
+    px, py, ok = rh.project_camera_to_pixel(np.array([[0.0, 0.5, 1.0], [0, 0, -1.0]]), 100, 100, 50, 40)
+    assert ok.tolist() == [True, False] and px[0] == 50 and py[0] == -10 and np.isnan(px[1])
+    video = tmp_path / "rec.mp4"
+    wr = cv2.VideoWriter(str(video), cv2.VideoWriter_fourcc(*"mp4v"), 10.0, (64, 48))
+    for i in range(10):
+        wr.write(np.full((48, 64, 3), 20 * i, np.uint8))
+    wr.release()
+    ident = [0, 0, 0, 1]
+    frames = []
+    for i in range(10):
+        joints = np.tile(np.array([0.1 * i, 0.0, 1.0] + ident, float), 26)
+        frames.append({"t": i / 10, "head_pos": [0.01 * i, 0, 0], "head_rot": ident, "left_joints": joints.tolist(),
+                       "left_tracked": True, "right_joints": joints.tolist(), "right_tracked": i % 2 == 0})
+    (tmp_path / "rec.json").write_text(json.dumps({"frames": frames}))
+    rep = rh.convert(video, tmp_path / "rec.json", tmp_path / "ds", "pick", tracking_origin=(0, 0, 0), eye_offset=0.0,
+                     overlay=tmp_path / "overlay.mp4")
+    assert rep == {"frames": 10, "fps": 10} and (tmp_path / "overlay.mp4").stat().st_size > 0
+    meta = LeRobotDatasetMetadata("ds", root=tmp_path / "ds")
+    rows = pq.read_table(add_subtask_response.episode_parquet(tmp_path / "ds", meta.info, 0)).to_pydict()
+    s, a = np.array(rows["observation.state"]), np.array(rows["action"])
+    assert s.shape == (10, 364) and a.shape == (10, 371)
+    assert abs(s[3, 0] - (0.3 - 0.03)) < 1e-5 and s[3, 2] == 1.0          # joint x minus head x, z kept
+    assert np.all(s[1, 182:] == 0) and np.any(s[2, 182:] != 0)            # right hand untracked on odd frames
+    assert np.allclose(a[:-1, :364], s[1:]) and np.allclose(a[2, 364:], [0.01, 0, 0, 0, 0, 0, 1], atol=1e-6)
+    assert np.allclose(a[-1, 364:], [0, 0, 0, 0, 0, 0, 1])
