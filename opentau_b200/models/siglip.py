@@ -71,11 +71,8 @@ class PatchEmbedding(nn.Module):
             pixels = F.pad(pixels, (0, (-W) % p, 0, (-H) % p), value=-1.0)
             H, W = pixels.shape[-2:]
         gh, gw = H // p, W // p
-        x = pixels.float().view(B, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(B, gh * gw, C * p * p)
-        w = self.patch_embedding.weight.view(self.cfg.hidden_size, -1)
-        y = F.linear(x, w, self.patch_embedding.bias)
-        y = y + self.interpolated_positions(gh, gw)
-        return y.to(out_dtype)
+        return ops.patch_embed(pixels, self.patch_embedding.weight, self.patch_embedding.bias,
+                               self.interpolated_positions(gh, gw), p, out_dtype)
 
 
 class SiglipAttention(nn.Module):

@@ -20,8 +20,8 @@ def oracle_mode() -> bool:
 
 
 from . import reference as ref  # noqa: E402
-from .reference import (BIG_NEG, INT_MIN, apply_rope, dense_mask_from_blocks, flow_interpolate,  # noqa: E402
-                        make_block_ids, mrope_angles, rope_angles, sinusoidal_time_embedding)
+from .reference import (BIG_NEG, INT_MIN, apply_rope, dense_mask_from_blocks, make_block_ids,  # noqa: E402
+                        mrope_angles, rope_angles)
 from . import prims, fused  # noqa: E402
 
 
@@ -47,6 +47,58 @@ def layer_norm(x: Tensor, weight: Tensor, bias: Tensor, eps: float = 1e-6) -> Te
     if oracle_mode():
         return ref.layer_norm(x, weight, bias, eps)
     return fused.layer_norm(x, weight, bias, eps)
+
+
+def patch_embed(pixels: Tensor, weight: Tensor, bias: Tensor, pos: Tensor, patch: int, out_dtype) -> Tensor:
+    """Non-overlapping patch convolution + bias + position table, computed in fp32 and cast to ``out_dtype``:
+    ``pixels (B,C,H,W)`` with ``H, W`` multiples of ``patch``, ``weight (N,C,p,p)``, ``pos (gh*gw, N)``."""
+    import torch
+    import torch.nn.functional as F
+    if pixels.is_cuda and not oracle_mode() and not (torch.is_grad_enabled() and pixels.requires_grad):
+        return fused.patch_embed(pixels, weight, bias, pos, patch, out_dtype)
+    B, C, H, W = pixels.shape
+    gh, gw = H // patch, W // patch
+    x = pixels.float().view(B, C, gh, patch, gw, patch).permute(0, 2, 4, 1, 3, 5).reshape(B, gh * gw, C * patch * patch)
+    y = F.linear(x, weight.float().view(weight.shape[0], -1), bias.float()) + pos.float()
+    return y.to(out_dtype)
+
+
+def sinusoidal_time_embedding(time: Tensor, dim: int, min_period: float = 4e-3, max_period: float = 4.0,
+                              out_dtype=None) -> Tensor:
+    """``[sin | cos]`` embedding of scalar times ``(B,T) -> (B,T,dim)`` (fp32 unless ``out_dtype`` says otherwise): one
+    kernel on CUDA, the fp64 / fp32 statement of ``reference.py`` elsewhere."""
+    import torch
+    if time.is_cuda and not oracle_mode() and not time.requires_grad and time.dim() == 2:
+        from . import cuda_ops
+        return cuda_ops.time_embed(time, dim, min_period, max_period, out_dtype or torch.float32)
+    e = ref.sinusoidal_time_embedding(time, dim, min_period, max_period)
+    return e.to(out_dtype) if out_dtype is not None else e
+
+
+def flow_interpolate(actions: Tensor, noise: Tensor, time: Tensor):
+    """``x_t = t*eps + (1-t)*a``, ``u_t = eps - a`` with ``time (B,T)``; one kernel on CUDA when nothing needs a
+    gradient (actions and noise are data)."""
+    import torch
+    if actions.is_cuda and not oracle_mode() and actions.shape == noise.shape and time.shape == actions.shape[:2] \
+            and not (torch.is_grad_enabled() and (actions.requires_grad or noise.requires_grad or time.requires_grad)):
+        from . import cuda_ops
+        return cuda_ops.flow_interpolate(actions, noise, time)
+    return ref.flow_interpolate(actions, noise, time)
+
+
+def euler_step(x_t: Tensor, v_t: Tensor, dt: float, frozen: Tensor | None = None,
+               action_prefix: Tensor | None = None) -> Tensor:
+    """One Euler step of the flow ODE, ``x_t + dt * v_t``, with rows of a committed action prefix (``frozen (B,T)``)
+    held at ``action_prefix``.  On CUDA the fp32 sample is updated in place by one kernel."""
+    import torch
+    if x_t.is_cuda and not oracle_mode() and x_t.dtype == torch.float32 and x_t.is_contiguous() \
+            and not torch.is_grad_enabled():
+        from . import cuda_ops
+        return cuda_ops.euler_step_(x_t, v_t, dt, frozen if action_prefix is not None else None, action_prefix)
+    x = x_t + dt * v_t.to(x_t.dtype)
+    if action_prefix is not None and frozen is not None:
+        x = torch.where(frozen[:, :, None], action_prefix.to(x.dtype), x)
+    return x
 
 
 def _native_nograd(*ts: Tensor) -> bool:
@@ -194,5 +246,5 @@ __all__ = [
     "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "linear_gated_residual", "gated_mlp_gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
     "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
     "resize_with_pad", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
-    "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "oracle_mode", "prims", "fused", "ref",
+    "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "euler_step", "patch_embed", "oracle_mode", "prims", "fused", "ref",
 ]

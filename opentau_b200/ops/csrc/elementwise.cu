@@ -463,6 +463,140 @@ __global__ void qkv_post_kernel(const __nv_bfloat16* __restrict__ qkv, long long
   }
 }
 
+// ------------------------------------------------------------------------------------------ patch embedding
+// SigLIP patch embedding in ONE kernel and in fp32 (the model keeps this island in fp32 under every bf16 cast):
+//   out[b, gy*gw + gx, n] = bias[n] + pos[gy*gw + gx, n] + sum_{c,py,px} W[n, (c,py,px)] * pix[b, c, gy*p+py, gx*p+px]
+// The non-overlapping patches are gathered straight from the image (no unfolded copy), the product runs on the fp32
+// pipes as a 64 x 64 x 16 shared-memory tiled GEMM with 4 x 4 outputs per thread, and bias, position table and the
+// cast to the encoder dtype are the epilogue.  PixT = float or bf16, OutT = float or bf16.
+template <typename PixT, typename OutT>
+__global__ void __launch_bounds__(256)
+patch_embed_kernel(const PixT* __restrict__ pix, const float* __restrict__ w, const float* __restrict__ bias,
+                   const float* __restrict__ pos, OutT* __restrict__ out, int B, int C, int H, int W, int p, int N) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  const int gh = H / p, gw = W / p, P = gh * gw, K = C * p * p;
+  const long long M = (long long)B * P;
+  const long long m0 = (long long)blockIdx.x * BM;
+  const int n0 = blockIdx.y * BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, 4 x 4 outputs each
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    // A tile: 64 patches x 16 taps, gathered from the image
+    for (int e = threadIdx.x; e < BM * BK; e += 256) {
+      const int mm = e / BK, kk = e % BK;
+      const long long m = m0 + mm;
+      const int k = k0 + kk;
+      float v = 0.f;
+      if (m < M && k < K) {
+        const int b = int(m / P), pi = int(m % P), gy = pi / gw, gx = pi % gw;
+        const int c = k / (p * p), r = k % (p * p), py = r / p, px = r % p;
+        const PixT x = pix[(((long long)b * C + c) * H + gy * p + py) * W + gx * p + px];
+        if constexpr (sizeof(PixT) == 4) v = x; else v = __bfloat162float(x);
+      }
+      As[kk][mm] = v;
+    }
+    // B tile: 64 output features x 16 taps of the flattened convolution weight
+    for (int e = threadIdx.x; e < BN * BK; e += 256) {
+      const int nn = e / BK, kk = e % BK;
+      const int n = n0 + nn, k = k0 + kk;
+      Bs[kk][nn] = (n < N && k < K) ? w[(long long)n * K + k] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[4], bb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bb[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+    const int pi = int(m % P);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      const float v = acc[i][j] + bias[n] + pos[(long long)pi * N + n];
+      if constexpr (sizeof(OutT) == 4) out[m * N + n] = v; else out[m * N + n] = __float2bfloat16(v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ flow matching
+// [sin | cos] embedding of scalar times with log-spaced periods: out[r, j] = sin(2 pi t_r / P_j),
+// out[r, half + j] = cos(...), P_j = min * (max / min)^(j / (half - 1)).  One launch instead of a linspace / pow / mul /
+// sin / cos / cat / cast chain per denoise step.  OutT = float or bf16.
+template <typename OutT>
+__global__ void time_embed_kernel(const float* __restrict__ t, OutT* __restrict__ out, long long rows, int dim,
+                                  float min_period, float max_period) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = dim >> 1;
+  const long long total = rows * half;
+  const float log_ratio = logf(max_period / min_period);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / half;
+    const int j = int(i - r * half);
+    const float frac = half > 1 ? (float)j / (float)(half - 1) : 0.f;
+    const float period = min_period * expf(frac * log_ratio);
+    const float ang = 6.283185307179586f / period * t[r];
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    if constexpr (sizeof(OutT) == 4) {
+      out[r * dim + j] = sn;
+      out[r * dim + half + j] = cs;
+    } else {
+      out[r * dim + j] = __float2bfloat16(sn);
+      out[r * dim + half + j] = __float2bfloat16(cs);
+    }
+  }
+}
+
+// Euler update of the denoise loop, in place on the fp32 sample: x += dt * v; rows marked frozen (a committed action
+// prefix) are overwritten with the prefix instead.  v is bf16 or fp32; x, prefix are (rows, D); frozen is per row.
+template <typename VT>
+__global__ void euler_step_kernel(float* __restrict__ x, const VT* __restrict__ v, float dt,
+                                  const unsigned char* __restrict__ frozen, const float* __restrict__ prefix,
+                                  long long rows, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = rows * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / D;
+    float vi;
+    if constexpr (sizeof(VT) == 4) vi = v[i]; else vi = __bfloat162float(v[i]);
+    float xi = x[i] + dt * vi;
+    if (frozen != nullptr && frozen[r]) xi = prefix[i];
+    x[i] = xi;
+  }
+}
+
+// Training-side interpolation: x_t = t * noise + (1 - t) * a and the target u_t = noise - a, time per (batch, step) row.
+__global__ void flow_interpolate_kernel(const float* __restrict__ a, const float* __restrict__ noise,
+                                        const float* __restrict__ t, float* __restrict__ x_t, float* __restrict__ u_t,
+                                        long long rows, int D) {
+  const long long total = rows * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float tt = t[i / D], ai = a[i], ni = noise[i];
+    x_t[i] = tt * ni + (1.f - tt) * ai;
+    u_t[i] = ni - ai;
+  }
+}
+
 // ------------------------------------------------------------------------------------------ cross entropy
 // logits fp32 [R][V] -> loss[r] = lse - logit[label], lse[r].  One block per row.
 __global__ void ce_fwd_kernel(const float* __restrict__ logits, const long long* __restrict__ labels,
@@ -717,6 +851,49 @@ extern "C" int otb_qkv_post(const void* qkv, long long ld, const void* qw, const
                              (const bf16*)qw, (const bf16*)kw, eps, unit_offset, cosb, sinb, (bf16*)q_out, (bf16*)k_out,
                              k_sb, k_ss, (bf16*)v_out, v_sb, v_ss, B, T, H, Hkv, D);
   return (int)e;
+}
+
+extern "C" int otb_patch_embed(const void* pix, int pix_bf16, const float* w, const float* bias, const float* pos,
+                               void* out, int out_bf16, int B, int C, int H, int W, int p, int N, cudaStream_t stream) {
+  if (B <= 0 || C <= 0 || p <= 0 || H % p || W % p || N <= 0) return -1;
+  const long long M = (long long)B * (H / p) * (W / p);
+  dim3 grid((unsigned)((M + 63) / 64), (unsigned)((N + 63) / 64));
+#define OTB_PE(PT, OT) patch_embed_kernel<PT, OT><<<grid, 256, 0, stream>>>((const PT*)pix, w, bias, pos, (OT*)out, B, C, H, W, p, N)
+  if (pix_bf16 && out_bf16) OTB_PE(bf16, bf16);
+  else if (pix_bf16) OTB_PE(bf16, float);
+  else if (out_bf16) OTB_PE(float, bf16);
+  else OTB_PE(float, float);
+#undef OTB_PE
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_time_embed(const float* t, void* out, long long rows, int dim, float min_period, float max_period,
+                              int out_bf16, cudaStream_t stream) {
+  if (rows <= 0 || dim < 2 || dim % 2) return -1;
+  const dim3 grid(grid_for(rows * (dim / 2), 256));
+  cudaError_t e = out_bf16 ? launch_pdl(time_embed_kernel<bf16>, grid, dim3(256), 0, stream, 0u, t, (bf16*)out, rows,
+                                        dim, min_period, max_period)
+                           : launch_pdl(time_embed_kernel<float>, grid, dim3(256), 0, stream, 0u, t, (float*)out, rows,
+                                        dim, min_period, max_period);
+  return (int)e;
+}
+
+extern "C" int otb_euler_step(float* x, const void* v, int v_bf16, float dt, const unsigned char* frozen,
+                              const float* prefix, long long rows, int D, cudaStream_t stream) {
+  if (rows <= 0 || D <= 0 || (frozen != nullptr && prefix == nullptr)) return -1;
+  const dim3 grid(grid_for(rows * D, 256));
+  cudaError_t e = v_bf16 ? launch_pdl(euler_step_kernel<bf16>, grid, dim3(256), 0, stream, 0u, x, (const bf16*)v, dt,
+                                      frozen, prefix, rows, D)
+                         : launch_pdl(euler_step_kernel<float>, grid, dim3(256), 0, stream, 0u, x, (const float*)v, dt,
+                                      frozen, prefix, rows, D);
+  return (int)e;
+}
+
+extern "C" int otb_flow_interpolate(const float* a, const float* noise, const float* t, float* x_t, float* u_t,
+                                    long long rows, int D, cudaStream_t stream) {
+  if (rows <= 0 || D <= 0) return -1;
+  flow_interpolate_kernel<<<grid_for(rows * D, 256), 256, 0, stream>>>(a, noise, t, x_t, u_t, rows, D);
+  return (int)cudaGetLastError();
 }
 
 extern "C" int otb_ce_fwd(const float* logits, const long long* labels, float* loss, float* lse, long long rows,

@@ -467,6 +467,66 @@ def qkv_post(qkv: Tensor, H: int, Hkv: int, D: int, q_norm, k_norm, cos: Tensor,
     return q, k_dst, v_dst
 
 
+def patch_embed(pixels: Tensor, weight: Tensor, bias: Tensor, pos: Tensor, patch: int, out_dtype: torch.dtype) -> Tensor:
+    """``pixels (B,C,H,W)`` fp32 / bf16, ``weight (N, C*p*p)``, ``bias (N)``, ``pos (gh*gw, N)`` all fp32 ->
+    ``(B, gh*gw, N)`` in ``out_dtype``."""
+    global launch_count
+    B, C, H, W = pixels.shape
+    N = weight.shape[0]
+    if pixels.dtype not in (torch.float32, torch.bfloat16):
+        pixels = pixels.float()
+    pixels = pixels.contiguous()
+    weight, bias, pos = weight.float().contiguous(), bias.float().contiguous(), pos.float().contiguous()
+    out = torch.empty(B, (H // patch) * (W // patch), N, dtype=out_dtype, device=pixels.device)
+    _check(_lib.load("elementwise").otb_patch_embed(
+        _p(pixels), c_int(int(pixels.dtype == torch.bfloat16)), _p(weight), _p(bias), _p(pos), _p(out),
+        c_int(int(out_dtype == torch.bfloat16)), c_int(B), c_int(C), c_int(H), c_int(W), c_int(patch), c_int(N),
+        _stream()), "patch_embed")
+    launch_count += 1
+    return out
+
+
+def time_embed(time: Tensor, dim: int, min_period: float, max_period: float, out_dtype: torch.dtype) -> Tensor:
+    global launch_count
+    t = time.float().contiguous()
+    out = torch.empty(*t.shape, dim, dtype=out_dtype, device=t.device)
+    _check(_lib.load("elementwise").otb_time_embed(_p(t), _p(out), c_longlong(t.numel()), c_int(dim),
+                                                   c_float(min_period), c_float(max_period),
+                                                   c_int(int(out_dtype == torch.bfloat16)), _stream()), "time_embed")
+    launch_count += 1
+    return out
+
+
+def euler_step_(x: Tensor, v: Tensor, dt: float, frozen: Tensor | None = None, prefix: Tensor | None = None) -> Tensor:
+    """In place: ``x += dt * v``; rows with ``frozen`` set take ``prefix`` instead.  ``x`` fp32 contiguous (B,T,D)."""
+    global launch_count
+    assert x.dtype == torch.float32 and x.is_contiguous() and v.shape == x.shape
+    v = v.contiguous()
+    fz = pf = None
+    if frozen is not None and prefix is not None:
+        fz = frozen.contiguous()
+        fz = fz.view(torch.uint8) if fz.dtype == torch.bool else fz.to(torch.uint8)
+        pf = prefix.float().contiguous()
+    D = x.shape[-1]
+    _check(_lib.load("elementwise").otb_euler_step(_p(x), _p(v), c_int(int(v.dtype == torch.bfloat16)), c_float(dt),
+                                                   _p(fz), _p(pf), c_longlong(x.numel() // D), c_int(D), _stream()),
+           "euler_step")
+    launch_count += 1
+    return x
+
+
+def flow_interpolate(actions: Tensor, noise: Tensor, time: Tensor) -> tuple[Tensor, Tensor]:
+    global launch_count
+    a, n, t = actions.float().contiguous(), noise.float().contiguous(), time.float().contiguous()
+    x_t, u_t = torch.empty_like(a), torch.empty_like(a)
+    D = a.shape[-1]
+    _check(_lib.load("elementwise").otb_flow_interpolate(_p(a), _p(n), _p(t), _p(x_t), _p(u_t),
+                                                         c_longlong(a.numel() // D), c_int(D), _stream()),
+           "flow_interpolate")
+    launch_count += 1
+    return x_t, u_t
+
+
 # --------------------------------------------------------------------------------------------- attention
 def attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale):
     from . import attention

@@ -240,3 +240,38 @@ class LinearCEFn(torch.autograd.Function):
 
 def linear_cross_entropy(h, w, bias, labels):
     return LinearCEFn.apply(h, w, bias, labels)
+
+
+
+class PatchEmbedFn(torch.autograd.Function):
+    """SigLIP patch embedding: forward is one native kernel (gather + fp32 product + bias + position table + cast);
+    the backward needs only parameter gradients (pixels are data) and states them with library calls on the unfolded
+    patches: three reductions per step, outside the forward hot path."""
+
+    @staticmethod
+    def forward(ctx, pixels, weight, bias, pos, patch, out_dtype):
+        from . import cuda_ops
+        ctx.save_for_backward(pixels)
+        ctx.patch = patch
+        return cuda_ops.patch_embed(pixels, weight.reshape(weight.shape[0], -1), bias, pos, patch, out_dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (pixels,) = ctx.saved_tensors
+        p = ctx.patch
+        B, C, H, W = pixels.shape
+        gh, gw = H // p, W // p
+        g = dy.float()
+        dw = db = dpos = None
+        if ctx.needs_input_grad[1]:
+            x = pixels.float().view(B, C, gh, p, gw, p).permute(0, 2, 4, 1, 3, 5).reshape(B * gh * gw, C * p * p)
+            dw = (g.reshape(B * gh * gw, -1).t() @ x).view(-1, C, p, p)
+        if ctx.needs_input_grad[2]:
+            db = g.sum(dim=(0, 1))
+        if ctx.needs_input_grad[3]:
+            dpos = g.sum(dim=0)
+        return None, dw, db, dpos, None, None
+
+
+def patch_embed(pixels, weight, bias, pos, patch, out_dtype):
+    return PatchEmbedFn.apply(pixels, weight, bias, pos, patch, out_dtype)

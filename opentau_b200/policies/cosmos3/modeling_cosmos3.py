@@ -157,7 +157,7 @@ class Cosmos3FlowMatching(nn.Module):
     def _time_to_adarms(self, time: Tensor) -> Tensor:
         """``(B, N)`` times -> ``(B, N, cond_dim)`` conditioning vectors."""
         dtype = self.action_in_proj.weight.dtype
-        e = ops.sinusoidal_time_embedding(time, self.config.proj_width, 4e-3, 4.0).to(dtype)
+        e = ops.sinusoidal_time_embedding(time, self.config.proj_width, 4e-3, 4.0, out_dtype=dtype)
         x = F.silu(self.time_mlp_in(e))
         x = F.silu(self.time_mlp_out(x))
         return self.adarms_proj(x)
@@ -226,15 +226,13 @@ class Cosmos3FlowMatching(nn.Module):
             frozen = torch.zeros(Bn, cfg.chunk_size, dtype=torch.bool, device=device)
         live = (~frozen).float()
         dt = -1.0 / cfg.num_steps
+        if action_prefix is not None:
+            x_t = torch.where(frozen[:, :, None], action_prefix.float(), x_t)
         for i in range(cfg.num_steps):
-            if action_prefix is not None:
-                x_t = torch.where(frozen[:, :, None], action_prefix.float(), x_t)
             v_t = self._run_expert(cache, ppos, x_t, live * (1.0 + i * dt), state)
             if accel is not None:
                 accel.update(v_t)
-            x_t = x_t + dt * v_t
-        if action_prefix is not None:
-            x_t = torch.where(frozen[:, :, None], action_prefix.float(), x_t)
+            x_t = ops.euler_step(x_t, v_t, dt, frozen if action_prefix is not None else None, action_prefix)
         return x_t
 
 

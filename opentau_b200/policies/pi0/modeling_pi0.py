@@ -64,7 +64,7 @@ class PI0FlowMatching(PI05FlowMatching):
         w = self.action_in_proj.out_features
         state_emb = self.state_proj(state.to(dtype))[:, None, :]
         t2 = timestep if timestep.dim() == 2 else timestep[:, None].expand(B, T)
-        time_emb = ops.sinusoidal_time_embedding(t2, w, 4e-3, 4.0).to(dtype)
+        time_emb = ops.sinusoidal_time_embedding(t2, w, 4e-3, 4.0, out_dtype=dtype)
         action_emb = self.action_in_proj(noisy_actions.to(dtype))
         h = self.action_time_mlp_out(F.silu(self.action_time_mlp_in(torch.cat([action_emb, time_emb], dim=2))))
         embs = torch.cat([state_emb, h], dim=1)

@@ -320,7 +320,7 @@ class PI05FlowMatching(nn.Module):
         B = noisy_actions.shape[0]
         device = noisy_actions.device
         w = self.action_in_proj.out_features
-        time_emb = ops.sinusoidal_time_embedding(timestep, w, 4e-3, 4.0).to(dtype)
+        time_emb = ops.sinusoidal_time_embedding(timestep, w, 4e-3, 4.0, out_dtype=dtype)
         action_emb = self.action_in_proj(noisy_actions.to(dtype))
         x = F.silu(self.time_mlp_in(time_emb))
         cond = F.silu(self.time_mlp_out(x))
@@ -478,17 +478,16 @@ class PI05FlowMatching(nn.Module):
             frozen = self.frozen_mask(delay, B, device)
         live = (~frozen).to(torch.float32)
         has_prefix = action_prefix is not None
+        if has_prefix:               # committed actions enter every step unchanged ...
+            x_t = torch.where(frozen[:, :, None], action_prefix.to(x_t.dtype), x_t)
         for i in range(n):
             t = 1.0 + i * dt
-            if has_prefix:
-                x_t = torch.where(frozen[:, :, None], action_prefix.to(x_t.dtype), x_t)
             time = live * t          # frozen rows run at diffusion time 0
             v_t = self.denoise_step(cache, prefix_len, x_t, time)
             if accel is not None:
                 accel.update(v_t)
-            x_t = x_t + dt * v_t
-        if has_prefix:
-            x_t = torch.where(frozen[:, :, None], action_prefix.to(x_t.dtype), x_t)
+            # ... and are restored by the same kernel that takes the Euler step
+            x_t = ops.euler_step(x_t, v_t, dt, frozen if has_prefix else None, action_prefix)
         return x_t
 
     @torch.no_grad()

@@ -347,3 +347,54 @@ def test_skinny_gemm_gated_residual_epilogue(per_token, splits, dev):
         plain = ops.gated_residual(resk, ops.gated_mlp(x, wgu, wd, "silu"), gk)
     torch.testing.assert_close(fused.float(), plain.float(), atol=6e-2, rtol=3e-2)
     cuda_ops.check_status()
+
+
+def test_flow_matching_kernels(dev):
+    """Time embedding, flow interpolation and the Euler step against their fp32 statements."""
+    from opentau_b200 import ops
+    B, T, D = 3, 51, 32
+    time = torch.rand(B, T, device=dev)
+    for dim, dt_ in ((1024, torch.float32), (256, torch.bfloat16)):
+        got = ops.sinusoidal_time_embedding(time, dim, 4e-3, 4.0, out_dtype=dt_)
+        want = ops.ref.sinusoidal_time_embedding(time.cpu(), dim, 4e-3, 4.0)
+        assert got.dtype == dt_ and got.shape == (B, T, dim)
+        # the largest angle is 2 pi / 4e-3 ~ 1571 rad: fp32 argument rounding bounds the error near 1e-4
+        torch.testing.assert_close(got.float().cpu(), want, atol=1e-2 if dt_ == torch.bfloat16 else 2e-3, rtol=0)
+    a, n = torch.randn(B, T, D, device=dev), torch.randn(B, T, D, device=dev)
+    x_t, u_t = ops.flow_interpolate(a, n, time)
+    wx, wu = ops.ref.flow_interpolate(a, n, time)
+    torch.testing.assert_close(x_t, wx), torch.testing.assert_close(u_t, wu)
+    frozen = torch.zeros(B, T, dtype=torch.bool, device=dev)
+    frozen[:, :7] = True
+    prefix = torch.randn(B, T, D, device=dev)
+    for v in (torch.randn(B, T, D, device=dev), torch.randn(B, T, D, device=dev).to(torch.bfloat16)):
+        x0 = torch.randn(B, T, D, device=dev)
+        want = torch.where(frozen[:, :, None], prefix, x0 + (-0.1) * v.float())
+        with torch.no_grad():
+            got = ops.euler_step(x0.clone(), v, -0.1, frozen, prefix)
+            plain = ops.euler_step(x0.clone(), v, -0.1)
+        torch.testing.assert_close(got, want), torch.testing.assert_close(plain, x0 + (-0.1) * v.float())
+
+
+@pytest.mark.parametrize("pix_dtype,out_dtype", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_patch_embed_kernel(pix_dtype, out_dtype, dev):
+    """Fused gather + fp32 product + bias + position table against the unfold + linear statement, with gradients."""
+    from opentau_b200 import ops
+    B, C, H, W, p, N = 3, 3, 56, 42, 14, 200
+    torch.manual_seed(0)
+    pix = (torch.rand(B, C, H, W, device=dev) * 2 - 1).to(pix_dtype)
+    w = (torch.randn(N, C, p, p, device=dev) * 0.05).requires_grad_(True)
+    b = torch.randn(N, device=dev).requires_grad_(True)
+    pos = torch.randn((H // p) * (W // p), N, device=dev).requires_grad_(True)
+    got = ops.patch_embed(pix, w, b, pos, p, out_dtype)
+    x = pix.float().view(B, C, H // p, p, W // p, p).permute(0, 2, 4, 1, 3, 5).reshape(B, -1, C * p * p)
+    w2, b2, pos2 = (t.detach().clone().requires_grad_(True) for t in (w, b, pos))
+    want = torch.nn.functional.linear(x, w2.view(N, -1), b2) + pos2
+    assert got.dtype == out_dtype and got.shape == want.shape
+    torch.testing.assert_close(got.float(), want, atol=2e-2 if out_dtype == torch.bfloat16 else 1e-4, rtol=1e-2)
+    g = torch.randn_like(want)
+    got.backward(g.to(out_dtype))
+    want.backward(g.to(out_dtype).float())
+    torch.testing.assert_close(w.grad, w2.grad, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(b.grad, b2.grad, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(pos.grad, pos2.grad, atol=1e-3, rtol=1e-3)
