@@ -27,4 +27,13 @@ def make_envs(cfg: EnvConfig, n_envs: int = 1, use_async_envs: bool = False) -> 
                                         cfg.resolution, cfg.tolerance, cfg.action_scale, cfg.episode_length, tid)
                 out[g][tid] = SyncVectorEnv([fn] * n_envs)
         return out
+    try:
+        if cfg.type == "libero":
+            from .libero import create_libero_envs
+            return create_libero_envs(cfg, n_envs)
+        if cfg.type == "robocasa":
+            from .robocasa import create_robocasa_envs
+            return create_robocasa_envs(cfg, n_envs)
+    except ImportError as e:
+        raise RuntimeError(UNAVAILABLE.format(name=cfg.type) + f" ({e})") from e
     raise RuntimeError(UNAVAILABLE.format(name=cfg.type))
