@@ -30,16 +30,51 @@ class HashTokenizer:
 
     pad_token_id, eos_token_id, bos_token_id = 0, 1, 2
 
+    PALIGEMMA_VOCAB, PALIGEMMA_LOC_BASE = 257152, 256000     # <loc0000>.. live at 256000..257023 in that vocabulary
+
     def __init__(self, vocab_size: int = 257152):
         self.vocab_size = vocab_size
+        # pieces hash below the range a PaliGemma-sized vocabulary reserves for location / segmentation tokens
+        self._hash_range = (self.PALIGEMMA_LOC_BASE if vocab_size == self.PALIGEMMA_VOCAB else vocab_size) - 3
+        self.added_tokens: dict[str, int] = {}
+        self._added_re: re.Pattern | None = None
+
+    def __len__(self) -> int:
+        return self.vocab_size
+
+    def add_tokens(self, tokens, special_tokens: bool = True) -> int:
+        """Registers strings that must map to ONE id each.  ``<locNNNN>`` in a PaliGemma-sized vocabulary takes its
+        reserved id; anything else is appended.  Returns the number of ids appended (0 when nothing grew)."""
+        grown = 0
+        for t in tokens:
+            t = str(getattr(t, "content", t))
+            if t in self.added_tokens:
+                continue
+            m = re.fullmatch(r"<loc(\d{4})>", t)
+            if m and self.vocab_size >= self.PALIGEMMA_VOCAB and int(m.group(1)) < 1024 \
+                    and self._hash_range == self.PALIGEMMA_LOC_BASE - 3:
+                self.added_tokens[t] = self.PALIGEMMA_LOC_BASE + int(m.group(1))
+            else:
+                self.added_tokens[t] = self.vocab_size
+                self.vocab_size += 1
+                grown += 1
+        self._added_re = re.compile("(" + "|".join(re.escape(t) for t in sorted(self.added_tokens, key=len,
+                                                                                reverse=True)) + ")")
+        return grown
 
     @lru_cache(maxsize=65536)
     def _piece_id(self, piece: str) -> int:
         h = int.from_bytes(hashlib.blake2b(piece.encode("utf-8"), digest_size=8).digest(), "little")
-        return 3 + h % (self.vocab_size - 3)
+        return 3 + h % self._hash_range
 
     def encode(self, text: str, add_special_tokens: bool = True) -> list[int]:
-        ids = [self._piece_id(p) for p in _PIECE.findall(text)]
+        chunks = self._added_re.split(text) if self._added_re is not None else [text]
+        ids: list[int] = []
+        for c in chunks:
+            if c in self.added_tokens:
+                ids.append(self.added_tokens[c])
+            elif c:
+                ids += [self._piece_id(p) for p in _PIECE.findall(c)]
         return ([self.bos_token_id] + ids) if add_special_tokens else ids
 
     def __call__(self, texts, max_length: int | None = None, padding: str | bool = "max_length",

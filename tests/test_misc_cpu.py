@@ -63,3 +63,35 @@ def test_master_weights_keep_small_updates_that_bf16_would_lose():
     assert float(opt.clip_grad_norm_(1.0)) > 1.0
     sd = opt.state_dict()
     opt.load_state_dict(sd)
+
+
+def test_loc_tokens_become_single_tokens_and_grow_other_vocabularies():
+    import torch
+    from torch import nn
+    from opentau_b200.datasets.grounding.tokenizer_utils import LOC_TOKENS, ensure_loc_tokens
+    from opentau_b200.utils.tokenizer import HashTokenizer
+    pg = HashTokenizer(257152)
+    assert len(pg.encode("<loc0007> cup", add_special_tokens=False)) > 2             # fragmented before
+    assert ensure_loc_tokens(pg) == 0 and len(pg) == 257152                         # reserved ids, nothing grows
+    ids = pg.encode("<loc0007><loc1023> cup", add_special_tokens=False)
+    assert ids[:2] == [256007, 257023] and all(i < 256000 for i in ids[2:])
+    assert ensure_loc_tokens(pg) == 0
+
+    class Tiny(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed_tokens = nn.Embedding(500, 16)
+
+    small, model = HashTokenizer(500), Tiny()
+    old = model.embed_tokens.weight.detach().clone()
+    torch.manual_seed(7)
+    expect_next = torch.rand(1)
+    torch.manual_seed(7)
+    assert ensure_loc_tokens(small, model) == 1024 and len(small) == 1524
+    assert torch.equal(torch.rand(1), expect_next)                                  # the caller's RNG stream is untouched
+    w = model.embed_tokens.weight
+    assert w.shape == (1524, 16) and torch.equal(w[:500], old) and w.requires_grad
+    again = Tiny()
+    ensure_loc_tokens(HashTokenizer(500), again)
+    assert torch.equal(again.embed_tokens.weight[500:], w[500:])                    # same new rows on every run
+    assert small.encode(LOC_TOKENS[3], add_special_tokens=False) == [503] and ensure_loc_tokens(small, model) == 0
