@@ -32,6 +32,7 @@ struct AttnParams {
   float* lse;                       // (B, H, Sq)
   // split-KV (few query tiles, many keys: a denoising step against a cached prefix): CTA (tile, split) covers its
   // share of the key blocks and leaves an unnormalised partial; attn_combine_kernel merges the partials
+  int skip_reach;                   // visit every key block: skip the prologue scan for the last reachable key
   int nsplit;                       // 1: write o / lse directly
   float* part_o;                    // (nsplit, B, Sq, H, D) fp32, accumulators expressed against part m
   float2* part_ml;                  // (nsplit, B, H, Sq): (running maximum in log2 units, row sum)
@@ -138,8 +139,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   // ---- how many keys can this tile reach?  1 + the last key index j that is valid and has
   //      k_blk[j] <= the largest valid q_blk in the tile (no monotonicity assumed).  With split keys the scan is
   //      skipped: the few tiles of such a launch reach (almost) every key, blocks without a visible key cost one
-  //      masked pass, and the scan itself is a serial prologue of two dependent global reads per key.
-  if (p.nsplit > 1) {
+  //      masked pass, and the scan itself is a serial prologue of two dependent global reads per key.  The same holds
+  //      for a launch with ONE query tile per (batch, kv head): a short suffix attending to a cached prefix.
+  if (p.skip_reach) {
     if (threadIdx.x == 0) *kv_end_smem = p.Sk;
     __syncthreads();
   } else {
@@ -581,6 +583,7 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   p.o = static_cast<__nv_bfloat16*>(o);
   p.lse = lse;
   p.nsplit = nsplit;
+  p.skip_reach = (nsplit > 1 || Sq <= ATT_M / g) ? 1 : 0;
   p.part_o = part_o;
   p.part_ml = reinterpret_cast<float2*>(part_ml);
   p.status = static_cast<KernelStatus*>(status);
