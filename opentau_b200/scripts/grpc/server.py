@@ -153,18 +153,32 @@ class RobotPolicyServicer(pb_grpc.RobotPolicyServiceServicer):
             raise ValueError("delay > 0 needs prefix_action")
         return batch, prefix, delay
 
-    def _apply_planner(self, request) -> None:
-        if self.planner is not None:
-            sub = self.planner.current_subtask(request.prompt)
-            if sub:
-                request.prompt = sub
+    def _apply_planner(self, request, batch: dict[str, Any]) -> None:
+        """The request prompt is the OVERALL task.  The planner sees every observation (its background loop replans
+        from the latest one), the policy is prompted with the current subtask and never waits for the planner, except
+        on the first request of a task, where one plan is computed in line so that the episode starts on a real
+        subtask (a failing planner call leaves the overall task as the prompt)."""
+        if self.planner is None:
+            return
+        task = request.prompt
+        images = {k: v[0] for k, v in batch.items() if k.startswith("camera")}
+        state = list(request.robot_state.state)
+        sub = self.planner.current_subtask(task)          # resets the planner's memory when the task changed
+        self.planner.observe(images, state)
+        if not sub:
+            try:
+                sub = self.planner.plan(task, images, state).subtask
+            except Exception as e:  # noqa: BLE001 - serving continues on the overall task
+                logger.warning("first plan for %r failed: %s", task, e)
+        if sub:
+            batch["prompt"] = [sub]
 
     # -- RPCs ---------------------------------------------------------------------------------------------
     def _respond(self, request) -> "pb.ActionChunkResponse":
         t0 = time.perf_counter()
         resp = pb.ActionChunkResponse(request_id=request.request_id, timestamp_ns=time.time_ns())
-        self._apply_planner(request)
         batch, prefix, delay = self._prepare_observation(request)
+        self._apply_planner(request, batch)
         chunk = self.infer.submit(lambda: self._sample(batch, prefix, delay).squeeze(0).float().cpu()).result()
         accel = getattr(self.policy, "last_accel", None)
         if accel:

@@ -87,3 +87,35 @@ def test_wire_format_matches_the_proto_field_numbers():
     # field 3 (prompt) = tag 0x1a, field 5 (delay) = tag 0x28, field 7 (request_id) = tag 0x3a
     assert b"\x1a\x02hi" in raw and b"\x28\x02" in raw and b"\x3a\x01r" in raw
     assert pb.ObservationRequest.FromString(raw).robot_state.state == [1.0, 2.0]
+
+
+def test_planner_sees_observations_and_sets_the_subtask(tmp_path):
+    """With a planner attached the request prompt is the overall task: the first request plans in line, every request
+    feeds the planner's observation cache, and the policy is prompted with the planner's subtask."""
+    from helpers import tiny_pi05
+    from opentau_b200.planner.high_level_planner import CallableClient, SubtaskPlanner
+    tiny_pi05(num_steps=2, max_delay=3, prompt_max_length=24).save_pretrained(tmp_path / "ckpt")
+    calls = []
+
+    def model(messages, images):
+        calls.append((messages[-1]["content"], len(images)))
+        return "Updated Memory: started\nSubtask: open the drawer"
+
+    planner = SubtaskPlanner(CallableClient(model))
+    svc = RobotPolicyServicer(_cfg(tmp_path / "ckpt"), planner=planner)
+    seen = []
+    real_sample = svc._sample
+    svc._sample = lambda batch, prefix, delay: (seen.append(batch["prompt"][0]), real_sample(batch, prefix, delay))[1]
+    try:
+        img = np.zeros((32, 32, 3), np.uint8)
+        req = PolicyClient.make_request(None, [img], np.arange(3, dtype=np.float32), "tidy the desk")
+        resp = svc._respond(req)
+        assert len(resp.action_chunk) == 10 and seen[-1] == "open the drawer"
+        assert len(calls) == 1 and calls[0][1] == 1 and "tidy the desk" in calls[0][0]
+        assert planner._latest is not None and list(planner._latest[1]) == [0.0, 1.0, 2.0]
+        svc._respond(req)                                   # the subtask is cached: no further in-line call
+        assert len(calls) == 1 and seen[-1] == "open the drawer"
+        svc._respond(PolicyClient.make_request(None, [img], np.zeros(3, np.float32), "water the plant"))
+        assert len(calls) == 2 and "water the plant" in calls[1][0]        # a new task plans afresh
+    finally:
+        svc.infer.stop()
