@@ -12,7 +12,7 @@ AdamW + parameter refresh.
 
 For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
 Rank 0 prints ONE JSON line.  ``--impl reference`` reports that the reference cannot be imported in
-this image; ``--impl oracle`` runs this repository's plain-PyTorch/cuBLAS statement of
+this image: its dependencies are not in the offline wheelhouse; ``--impl oracle`` runs this repository's plain-PyTorch/cuBLAS statement of
 the same model (a library baseline, not the reference).
 """
 
