@@ -30,7 +30,7 @@ def attach(root: str | Path, labels: dict) -> dict:
     touched = {"episodes": 0, "frames_labelled": 0}
     for key, lab in labels.get("episodes", {}).items():
         ep = by_idx[int(key)]
-        for f in ("quality", "speed", "success"):
+        for f in ("quality", "speed", "success", "sum_reward"):
             if f in lab:
                 ep[f] = lab[f]
         segs = lab.get("segments")

@@ -99,3 +99,24 @@ def test_subgoal_generators_feed_the_rollout(tmp_path):
     out = goals({"state": torch.zeros(2, 8)})
     assert goals.num_scenes == 3 and abs(float(out["subgoal0"][0, 0, 0, 0]) * 255 - 50) < 1 \
         and abs(float(out["subgoal0"][1, 0, 0, 0]) * 255 - 100) < 1
+
+
+def test_rollouts_become_a_dataset(tmp_path):
+    """Two rollouts (one succeeding, one standing still) are merged and written as episodes cut at the first done,
+    with the outcome in the episode metadata; the result loads like any recorded dataset."""
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDatasetMetadata
+    from opentau_b200.utils.rollout_recorder import aggregate_rollouts, record_rollouts
+    envs = make_envs(FakeEnvConfig(tasks=["reach the goal"], episode_length=12), n_envs=2)
+    env = envs[next(iter(envs))][0]
+    good = rollout(env, Scripted(1.0), seeds=[1, 2], device="cpu", return_observations=True)
+    bad = rollout(env, Scripted(0.0), seeds=[3, 4], device="cpu", return_observations=True)
+    data = aggregate_rollouts([good, bad])
+    assert data["done"].shape[0] == 4 and len(data["observation"]) == data["done"].shape[1]
+    rep = record_rollouts(data, tmp_path / "ds", fps=10, prompts=["reach the goal"] * 4)
+    assert rep["episodes"] == 4 and rep["successes"] == 2
+    meta = LeRobotDatasetMetadata("ds", root=tmp_path / "ds")
+    assert meta.total_episodes == 4 and meta.total_frames == rep["frames"] and meta.tasks[0] == "reach the goal"
+    assert [meta.episodes[i]["success"] for i in range(4)] == [True, True, False, False]
+    assert meta.episodes[2]["length"] == 12 and meta.episodes[0]["length"] < 12          # success ends the episode early
+    only = record_rollouts(data, tmp_path / "ok", fps=10, prompts=["reach the goal"] * 4, only_successful=True)
+    assert only["episodes"] == 2 and only["successes"] == 2
