@@ -327,8 +327,7 @@ static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Ski
 using namespace otb;
 
 // out[M,N] = X[M,K] W[N,K]^T (+ epilogue).  Returns 0, a CUDA / driver error code, or a negative argument-check code.
-// `splits_override`: 0 = choose (the largest cluster size up to 8 with which the grid still fits the GPU at once and
-// every CTA keeps at least two k-blocks).
+// `splits_override`: 0 = choose (see the rule at the selection below).
 extern "C" int otb_gemm_skinny_bf16(const void* X, const void* W, void* out, int M, int N, int K, long long ldx,
                                     long long ldw, long long ldo, const void* bias, const void* residual,
                                     long long ldr, void* out2, long long ldo2, const void* gate,
@@ -354,10 +353,25 @@ extern "C" int otb_gemm_skinny_bf16(const void* X, const void* W, void* out, int
   const int num_kb = (K + SK_BK - 1) / SK_BK;
   int splits = splits_override;
   if (splits == 0) {
-    const long long slots = (long long)g_sk_sms * (nt <= 128 ? 2 : 1);
+    // OPENTAU_B200_SKINNY_SLOTS: CTAs the automatic choice may fill, per SM (default 2 for the <= 128-token tiles);
+    // OPENTAU_B200_SKINNY_MAX_SPLITS caps the cluster size.  Tuning knobs for measurements.
+    static int slots_per_sm = -1, max_splits = -1;
+    if (slots_per_sm < 0) {
+      const char* e = getenv("OPENTAU_B200_SKINNY_SLOTS");
+      slots_per_sm = (e != nullptr && atoi(e) > 0) ? atoi(e) : 2;
+      e = getenv("OPENTAU_B200_SKINNY_MAX_SPLITS");
+      max_splits = (e != nullptr && atoi(e) >= 1 && atoi(e) <= 8) ? atoi(e) : 8;
+    }
+    // Largest cluster size whose grid is resident at once and leaves every CTA two k-blocks, with one refinement
+    // measured on the action-expert chains: going beyond ONE CTA per SM only pays while each CTA still streams four
+    // k-blocks; a 256-CTA launch of two-k-block CTAs fills every SM twice and keeps the next kernel of the chain
+    // (programmatic dependent launch) from becoming resident early.
+    const long long slots = (long long)g_sk_sms * (nt <= 128 ? slots_per_sm : 1);
     splits = 1;
-    for (int s = 2; s <= 8; ++s)
-      if ((long long)n_tiles * chunks * s <= slots && num_kb / s >= 2) splits = s;
+    for (int s = 2; s <= max_splits; ++s) {
+      const long long ctas = (long long)n_tiles * chunks * s;
+      if (ctas <= slots && num_kb / s >= 2 && (ctas <= g_sk_sms || num_kb / s >= 4)) splits = s;
+    }
   }
   if (splits < 1 || splits > 8) return -8;
   CUtensorMap tw, tx;
