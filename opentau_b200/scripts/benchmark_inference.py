@@ -4,7 +4,8 @@ Counterpart of the reference script (OpenTau ``src/opentau/scripts/benchmark_inf
 calls, then timed calls each bracketed by a device synchronise, reporting mean / std / p50 / p95 / p99.  The
 "compiled" arm of the reference (``torch.compile`` + CUDA graphs) corresponds here to ``--graphs`` (replay of
 the captured sampler); ``--no-graphs`` is the eager arm.  Environment knobs kept: ``BENCH_N_WARMUP``,
-``BENCH_N_TIMED``, ``BENCH_N_CANDIDATES``, ``BENCH_OUTPUT_DIR``.
+``BENCH_N_TIMED``, ``BENCH_N_CANDIDATES``, ``BENCH_OUTPUT_DIR``, ``BENCH_NO_COMPILE`` (eager only) and
+``BENCH_COMPILE_MODE`` (any value: graph replay).
 
     python -m opentau_b200.scripts.benchmark_inference [--policy pi05] [--cams 3] [--prompt-len 200] [--graphs]
 """
@@ -138,6 +139,11 @@ def main(argv=None):
     ap.add_argument("--tiny", action="store_true")
     ap.add_argument("--depth", type=int, default=None, help="cosmos3: truncate backbone and expert to this many layers")
     args = ap.parse_args(argv)
+    # the reference's knobs: BENCH_NO_COMPILE=1 is its eager arm; any BENCH_COMPILE_MODE maps to graph replay here
+    if os.environ.get("BENCH_NO_COMPILE", "0").lower() in ("1", "true"):
+        args.graphs = False
+    elif os.environ.get("BENCH_COMPILE_MODE"):
+        args.graphs = True
     n_warmup = int(os.environ.get("BENCH_N_WARMUP", "5"))
     n_timed = int(os.environ.get("BENCH_N_TIMED", "50"))
     n_cand = int(os.environ.get("BENCH_N_CANDIDATES", "1"))
