@@ -142,3 +142,19 @@ def test_robocasa_wrapper_and_eval_pipeline():
     assert venv.call("task_description")[0] == "open the drawer"
     res = eval_policy(venv, _Push(12), n_episodes=2, start_seed=0, device="cpu")
     assert res["aggregated"]["pc_success"] == 100.0
+
+
+def test_libero_eval_config_validation():
+    from opentau_b200.configs.libero import LiberoEnvConfig, TrainConfigWithLiberoEval
+    c = LiberoEnvConfig(suite="libero_goal", id=3)
+    assert c.suite == "goal" and c.suite_name == "libero_goal"
+    with pytest.raises(ValueError, match="Invalid suite"):
+        LiberoEnvConfig(suite="kitchen", id=0)
+    with pytest.raises(ValueError, match="Invalid task id"):
+        LiberoEnvConfig(suite="object", id=10)
+    cfg = TrainConfigWithLiberoEval(libero=LiberoEnvConfig(suite="10", id=2), action_chunk=8)
+    assert cfg.libero.chunk_usage == 8
+    with pytest.raises(ValueError, match="chunk_usage"):
+        TrainConfigWithLiberoEval(libero=LiberoEnvConfig(suite="10", id=2, chunk_usage=9), action_chunk=8)
+    with pytest.raises(ValueError, match="must be provided"):
+        TrainConfigWithLiberoEval()
