@@ -78,11 +78,47 @@ class DualStreamDecoder(nn.Module):
         for layer in tower.layers:
             norms += [layer.input_layernorm, layer.post_attention_layernorm]
         norms.append(tower.norm)
-        w = torch.cat([n.dense.weight for n in norms], dim=0)
-        b = torch.cat([n.dense.bias for n in norms], dim=0)
+        w, b = DualStreamDecoder._stacked_dense(tower, norms)
         out = ops.linear(cond.to(w.dtype), w, b)
         chunks = out.split(3 * tower.cfg.hidden_size, dim=-1)
         return list(chunks)
+
+    @staticmethod
+    def _stacked_dense(tower: Tower, norms: list) -> tuple[Tensor, Tensor]:
+        """Weights / biases of all adaptive-norm projections of a tower as ONE matrix and ONE vector.
+
+        Training (or parameters owned by a flat training buffer): concatenated per call, so autograd and the optimizer
+        see the individual parameters.  Inference: the parameters are re-homed ONCE as views of a stacked buffer (a
+        deep tower's stack is hundreds of MB: concatenating it for every denoise step cost more than the product that
+        consumes it).  In-place updates (``load_state_dict``) write through the views, so neither eager calls nor a
+        captured CUDA graph can see stale values; a dtype / device move re-allocates the parameters, which the
+        pointer check below notices."""
+        ws, bs = [n.dense.weight for n in norms], [n.dense.bias for n in norms]
+        managed = any(hasattr(p, "main_grad") for p in ws + bs)
+        if managed or (torch.is_grad_enabled() and any(p.requires_grad for p in ws + bs)):
+            return torch.cat(ws, dim=0), torch.cat(bs, dim=0)
+        stack = getattr(tower, "_ada_stack", None)
+        rows = [p.shape[0] for p in ws]
+
+        def is_view(buf: Tensor, parts: list, row_elems: int) -> bool:
+            off = 0
+            for p in parts:
+                if p.dtype != buf.dtype or p.device != buf.device or \
+                        p.data_ptr() != buf.data_ptr() + off * row_elems * buf.element_size():
+                    return False
+                off += p.shape[0]
+            return True
+
+        if stack is None or not (is_view(stack[0], ws, ws[0].shape[1]) and is_view(stack[1], bs, 1)):
+            with torch.no_grad():
+                w_all, b_all = torch.cat(ws, dim=0), torch.cat(bs, dim=0)
+                off = 0
+                for p, pb, r in zip(ws, bs, rows):
+                    p.data, pb.data = w_all[off:off + r], b_all[off:off + r]
+                    off += r
+            stack = (w_all, b_all)
+            tower._ada_stack = stack
+        return stack
 
     def _layer(self, li: int, xs: list[Tensor | None], cos_sin, q_blk, k_blk, q_valid, k_valid,
                cache_k, cache_v, mods, kv_dst=None) -> tuple[list[Tensor | None], Tensor | None, Tensor | None]:

@@ -185,3 +185,29 @@ def test_config_validation():
         tiny_pi05_config(train_expert_only=True, freeze_vision_encoder=False)
     with pytest.raises(ValueError):
         tiny_pi05_config(state_type="weird")
+
+
+def test_stacked_adaptive_norm_weights_follow_in_place_updates():
+    """At inference the adaptive-norm projections live in one stacked buffer: sampling does not concatenate per step,
+    and weights loaded afterwards are seen (no stale copy)."""
+    import torch
+    from helpers import tiny_batch, tiny_pi05
+    pol = tiny_pi05(num_steps=2).eval()
+    b = tiny_batch(batch_size=2)
+    noise = torch.randn(2, 10, 32)
+    a1 = pol.sample_actions(b, noise=noise)
+    tower = pol.model.wrapper.decoder.towers[1]
+    stack = tower._ada_stack
+    first = tower.layers[0].input_layernorm.dense.weight
+    assert first.data_ptr() == stack[0].data_ptr()                     # a view of the stack, not a copy
+    assert torch.equal(pol.sample_actions(b, noise=noise), a1) and tower._ada_stack is stack
+    sd = {k: v.clone() for k, v in pol.state_dict().items()}
+    for k in sd:
+        if "layernorm.dense.weight" in k:
+            sd[k] = sd[k] + 0.05
+    pol.load_state_dict(sd)
+    a2 = pol.sample_actions(b, noise=noise)
+    assert tower._ada_stack is stack and not torch.allclose(a1, a2)     # in-place load wrote through the views
+    out = pol.train()(b)                                                # training still reaches the individual parameters
+    (out["MSE"] + out["CE"]).backward()
+    assert first.grad is not None and first.grad.abs().sum() > 0
