@@ -98,6 +98,34 @@ class OpenAIClient(ChatClient):
         return self._usd
 
 
+class GeminiClient(ChatClient):
+    """Google Gemini endpoint (the reference plans with ``gemini-robotics-er``, ``src/opentau/planner/
+    gemini_er_planner.py:147-262``); needs the ``google-genai`` package, ``GEMINI_API_KEY`` / ``GOOGLE_API_KEY`` and
+    network access.  Images go as inline PNG parts before the text of the last user turn."""
+
+    def __init__(self, model: str = "gemini-robotics-er-1.5-preview", api_key: str | None = None):
+        try:
+            from google import genai
+        except ImportError as e:  # pragma: no cover - optional dependency
+            raise ImportError("the `google-genai` package is required for the Gemini planner") from e
+        import os
+        key = api_key or os.environ.get("GEMINI_API_KEY") or os.environ.get("GOOGLE_API_KEY")
+        if not key:
+            raise RuntimeError("GEMINI_API_KEY (or GOOGLE_API_KEY) is not set")
+        self.client, self.model = genai.Client(api_key=key), model
+
+    def complete(self, messages, images):  # pragma: no cover - needs network
+        from google.genai import types
+        system = "\n".join(m["content"] for m in messages if m["role"] == "system")
+        turns = [m for m in messages if m["role"] != "system"]
+        parts = [types.Part.from_bytes(data=base64.b64decode(b), mime_type="image/png") for b in images]
+        contents = [types.Content(role="model" if m["role"] == "assistant" else "user",
+                                  parts=([*parts] if m is turns[-1] else []) + [types.Part.from_text(text=m["content"])])
+                    for m in turns]
+        cfg = types.GenerateContentConfig(system_instruction=system or None)
+        return self.client.models.generate_content(model=self.model, contents=contents, config=cfg).text or ""
+
+
 class PolicyPlannerClient(ChatClient):
     """Uses a local planner policy (``plan(batch) -> (memories, subtasks)``) as the model."""
 
@@ -245,6 +273,8 @@ def make_planner(cfg, client: ChatClient | None = None):
     if client is None:
         if cfg.kind == "gpt":
             client = OpenAIClient(cfg.model or "gpt-4o")
+        elif cfg.kind == "gemini":
+            client = GeminiClient(cfg.model or "gemini-robotics-er-1.5-preview")
         else:
             raise RuntimeError(f"planner kind {cfg.kind!r} needs a hosted SDK or local weights that are not available "
                                "here; pass a ChatClient explicitly")
