@@ -43,6 +43,9 @@ def parse_args():
     ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3"],
                     help="--mode infer only: cosmos3 is the workload of the reference's published B200 latency table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (profiling runs only)")
+    ap.add_argument("--kernel-table", default="", metavar="PATH",
+                    help="train mode: after the warm-up, trace ONE step with the activity profiler, write the "
+                         "per-kernel device-time shares to PATH and exit without a benchmark line")
     return ap.parse_args()
 
 
@@ -216,6 +219,44 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
     return 0
 
 
+def write_kernel_table(path: str, step, sync, top: int = 60) -> None:
+    """Trace one call of ``step`` with the CUDA activity profiler and write device time per kernel name.
+
+    The figures are shares of one traced step (tracing perturbs the absolute time); the benchmark number is
+    never taken from such a run.
+    """
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        e0.record()
+        step()
+        e1.record()
+        sync()
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    for ev in prof.events():
+        if ev.device_type == torch.autograd.DeviceType.CUDA:
+            a = agg[ev.name[:120]]
+            a[0] += 1
+            a[1] += ev.device_time_total
+    total = sum(v[1] for v in agg.values())
+    ours = sum(v[1] for k, v in agg.items() if "otb" in k)
+    n_all = sum(v[0] for v in agg.values())
+    lines = [f"traced step {e0.elapsed_time(e1):.1f} ms between events; {n_all} device activities, "
+             f"{total / 1e3:.1f} ms summed device time; kernels of this repository (otb::*) "
+             f"{ours / 1e3:.1f} ms = {100 * ours / max(total, 1e-9):.1f} %"]
+    for name, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:top]:
+        lines.append(f"{t / 1e3:9.2f} ms {100 * t / total:5.1f} % n={n:5d} {t / n:9.1f} us  {name}")
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    print(lines[0])
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -308,6 +349,14 @@ def main():
     run_device_only(args.warmup)
     if use_cuda and args.impl == "ours":
         cuda_ops.check_status()
+    if args.kernel_table:
+        if rank == 0:
+            write_kernel_table(args.kernel_table, lambda: run_device_only(1), sync)
+        else:
+            run_device_only(1)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     sampler = ClockSampler(local_rank)
     if rank == 0 and use_cuda:
         sampler.start()

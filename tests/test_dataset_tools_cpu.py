@@ -71,3 +71,88 @@ def test_extract_reasoner_keys():
     st = {"reasoner.model.language_model.layers.0.w": torch.zeros(1), "generator.x": torch.zeros(1)}
     out = extract(st)
     assert list(out) == ["model.qwen3vl_with_expert.backbone.model.language_model.layers.0.w"]
+
+
+def _write_v16(root, n_eps=3, ep_len=5, with_col=False):
+    """A codebase-v1.6 directory: sharded parquet, flat metadata, safetensors statistics."""
+    import json
+
+    import numpy as np
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from safetensors.numpy import save_file
+
+    (root / "data").mkdir(parents=True)
+    (root / "meta_data").mkdir()
+    rows = {"observation.state": [], "action": [], "episode_index": [], "frame_index": [], "timestamp": [],
+            "index": [], "next.done": []}
+    if with_col:
+        rows["language_instruction"] = []
+    i = 0
+    for e in range(n_eps):
+        for f in range(ep_len):
+            rows["observation.state"].append([float(i), float(e), 0.5])
+            rows["action"].append([float(f), -1.0])
+            rows["episode_index"].append(e)
+            rows["frame_index"].append(f)
+            rows["timestamp"].append(f / 10.0)
+            rows["index"].append(i)
+            rows["next.done"].append(f == ep_len - 1)
+            if with_col:
+                rows["language_instruction"].append(
+                    "tf.Tensor(b'open the drawer', shape=(), dtype=string)" if e < 2 else "close the drawer")
+            i += 1
+    t = pa.table({k: pa.array(v, type=pa.list_(pa.float32())) if k in ("observation.state", "action") else pa.array(v)
+                  for k, v in rows.items()})
+    half = t.num_rows // 2
+    pq.write_table(t.slice(0, half), root / "data" / "train-00000-of-00002.parquet")
+    pq.write_table(t.slice(half), root / "data" / "train-00001-of-00002.parquet")
+    (root / "meta_data" / "info.json").write_text(json.dumps({"fps": 10, "video": False}))
+    st = np.asarray(rows["observation.state"], dtype=np.float32)
+    save_file({"observation.state/mean": st.mean(0), "observation.state/std": st.std(0),
+               "observation.state/min": st.min(0), "observation.state/max": st.max(0)},
+              str(root / "meta_data" / "stats.safetensors"))
+    return st
+
+
+def test_convert_v16_to_v20_then_v21(tmp_path):
+    import json
+
+    import numpy as np
+    import pyarrow.parquet as pq
+
+    from opentau_b200.datasets.utils import load_jsonlines
+    from opentau_b200.datasets.v2.convert_dataset_v1_to_v2 import batch_convert, convert_dataset
+    from opentau_b200.datasets.v2.convert_dataset_v20_to_v21 import convert
+
+    st = _write_v16(tmp_path / "v1")
+    info = convert_dataset(tmp_path / "v1", tmp_path / "v2", single_task="stack the cubes", robot_type="so101",
+                           motor_names={"action": ["shoulder", "gripper"]})
+    assert info["codebase_version"] == "v2.0" and info["total_episodes"] == 3 and info["total_frames"] == 15
+    assert info["features"]["action"]["names"] == {"motors": ["shoulder", "gripper"]}
+    assert info["features"]["observation.state"]["shape"] == [3] and info["video_path"] is None
+    eps = load_jsonlines(tmp_path / "v2" / "meta" / "episodes.jsonl")
+    assert [e["length"] for e in eps] == [5, 5, 5] and eps[1]["tasks"] == ["stack the cubes"]
+    t = pq.read_table(tmp_path / "v2" / "data" / "chunk-000" / "episode_000001.parquet")
+    assert t.num_rows == 5 and set(t.column("task_index").to_pylist()) == {0}
+    assert t.column("index").to_pylist() == list(range(5, 10))
+    stats = json.loads((tmp_path / "v2" / "meta" / "stats.json").read_text())
+    np.testing.assert_allclose(stats["observation.state"]["mean"], st.mean(0), rtol=1e-6)
+    # the v2.0 result is a valid input of the next converter
+    assert convert(tmp_path / "v2") == 3
+    assert json.loads((tmp_path / "v2" / "meta" / "info.json").read_text())["codebase_version"] == "v2.1"
+
+    # tasks from a column (Open-X tensor reprs are cleaned), and the batch driver that survives a bad job
+    _write_v16(tmp_path / "v1c", with_col=True)
+    status = batch_convert([
+        {"v1_dir": tmp_path / "v1c", "v2_dir": tmp_path / "v2c", "single_task": "ignored: the column wins"},
+        {"v1_dir": tmp_path / "missing", "v2_dir": tmp_path / "v2x", "single_task": "x"},
+    ], log_path=tmp_path / "log.txt")
+    assert status[str(tmp_path / "v1c")] == "converted" and status[str(tmp_path / "missing")].startswith("failed")
+    tasks = load_jsonlines(tmp_path / "v2c" / "meta" / "tasks.jsonl")
+    assert [x["task"] for x in tasks] == ["open the drawer", "close the drawer"]
+    eps = load_jsonlines(tmp_path / "v2c" / "meta" / "episodes.jsonl")
+    assert eps[2]["tasks"] == ["close the drawer"]
+    t = pq.read_table(tmp_path / "v2c" / "data" / "chunk-000" / "episode_000002.parquet")
+    assert "language_instruction" not in t.column_names and set(t.column("task_index").to_pylist()) == {1}
+    assert len((tmp_path / "log.txt").read_text().splitlines()) >= 2
