@@ -161,7 +161,87 @@ class SOLeader(_SOArm):
         return {f"{n}.pos": v for n, v in self.bus.sync_read("Present_Position").items()}
 
 
-def teleoperate_step(leader: SOLeader, follower: SOFollower) -> tuple[dict, dict]:
+@dataclass
+class BiSOArmConfig:
+    """Two SO arms driven as one device (reference ``src/opentau/scripts/so101/robots/bi_so_follower/
+    config_bi_so_follower.py:21-31`` and ``teleoperators/bi_so_leader/config_bi_so_leader.py``)."""
+    left: SOArmConfig = field(default_factory=SOArmConfig)
+    right: SOArmConfig = field(default_factory=lambda: SOArmConfig(port="/dev/ttyACM1"))
+    id: str | None = None
+    calibration_dir: str | None = None
+
+
+class _BiSOArm:
+    """Pair of arms; every key of the pair is the single arm's key with a ``left_`` / ``right_`` prefix, and each
+    side keeps its own calibration file ``<id>_left`` / ``<id>_right`` (reference ``bi_so_follower.py:33-159``,
+    ``bi_so_leader.py:30-118``)."""
+    arm_cls: type = _SOArm
+
+    def __init__(self, cfg: BiSOArmConfig):
+        from dataclasses import replace
+        self.cfg = cfg
+        sides = {}
+        for side in ("left", "right"):
+            c: SOArmConfig = getattr(cfg, side)
+            sides[side] = self.arm_cls(replace(
+                c, id=f"{cfg.id}_{side}" if cfg.id else c.id,
+                calibration_dir=cfg.calibration_dir if cfg.calibration_dir else c.calibration_dir))
+        self.left_arm, self.right_arm = sides["left"], sides["right"]
+        self.cameras = {**{f"left_{n}": c for n, c in self.left_arm.cameras.items()},
+                        **{f"right_{n}": c for n, c in self.right_arm.cameras.items()}}
+
+    @property
+    def arms(self):
+        return (("left", self.left_arm), ("right", self.right_arm))
+
+    @property
+    def is_calibrated(self) -> bool:
+        return all(a.is_calibrated for _, a in self.arms)
+
+    def connect(self, calibrate: bool = False) -> None:
+        for _, a in self.arms:
+            a.connect(calibrate)
+
+    def configure(self) -> None:
+        for _, a in self.arms:
+            a.configure()
+
+    def calibrate(self, ranges: dict[str, dict[str, tuple[int, int]]] | None = None) -> dict:
+        return {side: a.calibrate(None if ranges is None else ranges[side]) for side, a in self.arms}
+
+    def disconnect(self) -> None:
+        for _, a in self.arms:
+            a.disconnect()
+
+    @staticmethod
+    def _split(values: dict[str, Any]) -> dict[str, dict[str, Any]]:
+        out: dict[str, dict[str, Any]] = {"left": {}, "right": {}}
+        for k, v in values.items():
+            for side in out:
+                if k.startswith(side + "_"):
+                    out[side][k[len(side) + 1:]] = v
+        return out
+
+
+class BiSOFollower(_BiSOArm):
+    arm_cls = SOFollower
+
+    def get_observation(self) -> dict[str, Any]:
+        return {f"{side}_{k}": v for side, a in self.arms for k, v in a.get_observation().items()}
+
+    def send_action(self, action: dict[str, float]) -> dict[str, float]:
+        parts = self._split(action)
+        return {f"{side}_{k}": v for side, a in self.arms for k, v in a.send_action(parts[side]).items()}
+
+
+class BiSOLeader(_BiSOArm):
+    arm_cls = SOLeader
+
+    def get_action(self) -> dict[str, float]:
+        return {f"{side}_{k}": v for side, a in self.arms for k, v in a.get_action().items()}
+
+
+def teleoperate_step(leader, follower) -> tuple[dict, dict]:
     action = leader.get_action()
     sent = follower.send_action(action)
     return follower.get_observation(), sent

@@ -79,3 +79,26 @@ def test_record_episode_writes_a_lerobot_dataset(tmp_path):
     meta = LeRobotDatasetMetadata("local/so101", root=tmp_path / "ds")
     assert meta.total_frames == 5 and meta.robot_type == "so101" and meta.tasks == {0: "wave"}
     assert np.allclose(meta.stats["action"]["mean"][:5], 0.0, atol=0.1)
+
+
+def test_bimanual_pair_prefixes_keys_and_keeps_one_calibration_per_side(tmp_path):
+    from opentau_b200.scripts.so101.devices import BiSOArmConfig, BiSOFollower, BiSOLeader
+    ports = {k: FakeFeetechPort(IDS) for k in ("ll", "lr", "fl", "fr")}
+    leader = BiSOLeader(BiSOArmConfig(SOArmConfig(port=ports["ll"]), SOArmConfig(port=ports["lr"]), id="lead",
+                                      calibration_dir=str(tmp_path)))
+    follower = BiSOFollower(BiSOArmConfig(SOArmConfig(port=ports["fl"]), SOArmConfig(port=ports["fr"]), id="follow",
+                                          calibration_dir=str(tmp_path)))
+    ranges = {n: (1024, 3072) for n in leader.left_arm.bus.motors}
+    for pair in (leader, follower):
+        for _, arm in pair.arms:
+            arm.bus.connect()
+        pair.calibrate({"left": ranges, "right": ranges})
+        pair.configure()
+    assert follower.is_calibrated and follower.left_arm.calibration_path.name == "follow_left.json"
+    assert follower.right_arm.calibration_path.exists() and leader.right_arm.calibration_path.name == "lead_right.json"
+    ports["ll"]._set(1, "Present_Position", 3072)          # only the LEFT leader moves
+    obs, sent = teleoperate_step(leader, follower)
+    assert set(sent) == {f"{s}_{n}.pos" for s in ("left", "right") for n in ranges}
+    assert abs(sent["left_shoulder_pan.pos"] - 100.0) < 0.1 and abs(sent["right_shoulder_pan.pos"]) < 0.1
+    assert ports["fl"]._get(1, "Goal_Position") == 3072 and ports["fr"]._get(1, "Goal_Position") == 2048
+    assert abs(obs["left_shoulder_pan.pos"] - 100.0) < 0.1 and "right_gripper.pos" in obs
