@@ -156,3 +156,41 @@ def test_convert_v16_to_v20_then_v21(tmp_path):
     t = pq.read_table(tmp_path / "v2c" / "data" / "chunk-000" / "episode_000002.parquet")
     assert "language_instruction" not in t.column_names and set(t.column("task_index").to_pylist()) == {1}
     assert len((tmp_path / "log.txt").read_text().splitlines()) >= 2
+
+
+def test_convert_v20_to_v21_workers_check_metadata_fix_and_batch(tmp_path):
+    from opentau_b200.datasets.compute_stats import aggregate_stats
+    from opentau_b200.datasets.utils import load_episodes_stats, serialize_stats
+    from opentau_b200.datasets.v2.convert_dataset_v20_to_v21 import batch_convert, convert, fix_language_instruction
+    import pytest
+
+    def back_to_v20(root, wrong_stats=False):
+        agg = aggregate_stats(list(load_episodes_stats(root).values()))
+        if wrong_stats:
+            agg["observation.state"]["mean"] = agg["observation.state"]["mean"] + 1.0
+        (root / "meta/stats.json").write_text(json.dumps(serialize_stats(agg)))
+        info = json.loads((root / "meta/info.json").read_text())
+        info["codebase_version"] = "v2.0"
+        (root / "meta/info.json").write_text(json.dumps(info))
+        (root / "meta/episodes_stats.jsonl").unlink()
+        return info
+
+    a, b = tmp_path / "a", tmp_path / "b"
+    _record(a, episodes=(6, 5))
+    _record(b, episodes=(4, 4))
+    info = back_to_v20(a)
+    # a stale metadata entry that no parquet file holds is repaired; anything else is refused
+    info["features"]["language_instruction"] = {"dtype": "string", "shape": [1], "names": None}
+    (a / "meta/info.json").write_text(json.dumps(info))
+    assert fix_language_instruction(a) == "removed 'language_instruction'"
+    assert fix_language_instruction(a) == "skipped (no difference)"
+    assert "language_instruction" not in json.loads((a / "meta/info.json").read_text())["features"]
+    # threads + the check that the aggregated episode statistics reproduce the old dataset-level ones
+    assert convert(a, num_workers=2, check=True, delete_old_stats=True) == 2
+    assert not (a / "meta/stats.json").exists()
+    assert LeRobotDatasetMetadata("local/toy", root=a).version == "v2.1"
+    back_to_v20(b, wrong_stats=True)
+    with pytest.raises(AssertionError, match="observation.state"):
+        convert(b, check=True)
+    status = batch_convert([b, tmp_path / "nope"], log_path=tmp_path / "log.txt")
+    assert status[str(b)] == "converted 2 episodes" and status[str(tmp_path / "nope")].startswith("failed")
