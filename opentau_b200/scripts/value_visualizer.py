@@ -72,9 +72,11 @@ def jpeg_b64(img: np.ndarray, max_side: int = 224) -> str:
     return base64.b64encode(buf.tobytes()).decode() if ok else ""
 
 
-def episode_frames(dataset_root: str | Path, episode: int, n: int) -> list[tuple[float, np.ndarray]]:
-    """``n`` evenly spaced frames ``(seconds, HxWx3 uint8)`` of the first camera of ``episode``, read straight from the
-    episode's video file or, for image datasets, from the frames embedded in its parquet."""
+def episode_frames(dataset_root: str | Path, episode: int, n: int,
+                   indices: list[int] | None = None) -> list[tuple[float, np.ndarray]]:
+    """``n`` evenly spaced frames (or the frames at ``indices``) ``(seconds, HxWx3 uint8)`` of the first camera of
+    ``episode``, read straight from the episode's video file or, for image datasets, from the frames embedded in its
+    parquet."""
     import io
 
     import pyarrow.parquet as pq
@@ -85,7 +87,10 @@ def episode_frames(dataset_root: str | Path, episode: int, n: int) -> list[tuple
     root = Path(dataset_root)
     info = load_info(root)
     length = int(load_episodes(root, get_version(info))[episode]["length"])
-    idx = sorted(set(np.linspace(0, length - 1, min(n, length)).round().astype(int).tolist()))
+    if indices is None:
+        idx = sorted(set(np.linspace(0, length - 1, min(n, length)).round().astype(int).tolist()))
+    else:
+        idx = sorted({min(max(int(i), 0), length - 1) for i in indices})
     cams = [k for k, f in info["features"].items() if f["dtype"] in ("video", "image")]
     if not cams:
         return []

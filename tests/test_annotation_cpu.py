@@ -159,6 +159,45 @@ def test_value_visualizer_pages(tmp_path):
     assert len(vv.render(va, tmp_path / "viz2")) == 2
 
 
+def test_value_visualizer_app_serves_page_episode_and_frames(tmp_path):
+    import threading
+    import urllib.error
+    import urllib.request
+
+    from opentau_b200.scripts import value_visualizer as vv
+    from opentau_b200.scripts import value_visualizer_app as app
+    _record(tmp_path / "toy", episodes=(12, 9))
+    (tmp_path / "dc.json").write_text(json.dumps({"datasets": [{"root": str(tmp_path / "toy"), "episodes": [1, 0]}]}))
+    root, repo, eps = app.load_dataset_config(tmp_path / "dc.json")
+    assert root == (tmp_path / "toy").resolve() and eps == [0, 1] and repo == "local/dataset"
+    b = tmp_path / "b.json"
+    b.write_text(json.dumps({"0": [{"frame": i, "value": -1 + i / 12, "return": None} for i in range(12)]}))
+    state = app.ViewerState(vv.load_values(b, fps=10), 0, root, fps=10.0)
+    assert state.payload["frame"] == list(range(12)) and abs(state.payload["final"] - (-1 + 11 / 12)) < 1e-9
+    server = app.make_server(state, port=0)
+    th = threading.Thread(target=server.serve_forever, daemon=True)
+    th.start()
+    base = f"http://127.0.0.1:{server.server_address[1]}"
+    try:
+        page = urllib.request.urlopen(base + "/", timeout=10).read().decode()
+        assert "Timeline" not in page and 'type="range"' in page and "/api/episode" in page
+        ep = json.loads(urllib.request.urlopen(base + "/api/episode", timeout=10).read())
+        assert ep["episode"] == 0 and len(ep["value"]) == 12 and abs(ep["t"][5] - 0.5) < 1e-9
+        jpg = urllib.request.urlopen(base + "/frame/3.jpg", timeout=10).read()
+        assert jpg[:2] == b"\xff\xd8" and state.frame_jpeg(3) is jpg or state.frame_jpeg(3) == jpg
+        try:
+            urllib.request.urlopen(base + "/nothing", timeout=10)
+            raise AssertionError("expected 404")
+        except urllib.error.HTTPError as e:
+            assert e.code == 404
+    finally:
+        server.shutdown()
+        server.server_close()
+    import pytest
+    with pytest.raises(KeyError):
+        app.episode_payload(vv.load_values(b, fps=10), 7, 10.0)
+
+
 def test_ros_bag_conversion_with_fake_messages(tmp_path):
     """Joint states at 20 Hz, commands at 7 Hz and JPEG frames at 5 Hz are aligned to 10 fps; a broken bag is skipped."""
     import io
