@@ -95,3 +95,17 @@ def test_loc_tokens_become_single_tokens_and_grow_other_vocabularies():
     ensure_loc_tokens(HashTokenizer(500), again)
     assert torch.equal(again.embed_tokens.weight[500:], w[500:])                    # same new rows on every run
     assert small.encode(LOC_TOKENS[3], add_special_tokens=False) == [503] and ensure_loc_tokens(small, model) == 0
+
+
+def test_diagnose_host_script_writes_a_report(tmp_path):
+    import subprocess
+    from pathlib import Path
+
+    import opentau_b200
+    script = Path(opentau_b200.__file__).parent / "scripts" / "diagnose_host.sh"
+    out = subprocess.run(["bash", str(script), str(tmp_path)], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and "report:" in out.stdout
+    reports = list(tmp_path.glob("*_host.txt"))
+    assert len(reports) == 1
+    text = reports[0].read_text()
+    assert "## GPUs" in text and "## python stack" in text and "torch" in text
