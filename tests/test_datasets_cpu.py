@@ -137,3 +137,26 @@ def test_mixture_with_vqa_and_validation_split(tmp_path):
 def test_missing_dataset_raises_clear_error(tmp_path):
     with pytest.raises(FileNotFoundError, match="no network"):
         LeRobotDatasetMetadata("nobody/nothing", root=tmp_path / "absent")
+
+
+def test_push_to_hub_helpers(tmp_path):
+    import pytest
+
+    from opentau_b200.datasets.push_dataset_to_hub.utils import (calculate_episode_data_index, check_repo_id,
+                                                                  concatenate_episodes, get_default_encoding,
+                                                                  save_images_concurrently)
+    eps = [{"frame_index": torch.arange(3), "action": torch.ones(3, 2), "task": ["a"] * 3},
+           {"frame_index": torch.arange(2), "action": torch.zeros(2, 2), "task": ["b"] * 2}]
+    cat = concatenate_episodes(eps)
+    assert cat["index"].tolist() == [0, 1, 2, 3, 4] and cat["action"].shape == (5, 2) and cat["task"][3] == "b"
+    idx = calculate_episode_data_index([0, 0, 0, 1, 1, 1, 1, 2, 2, 2, 2, 2])
+    assert idx["from"].tolist() == [0, 3, 7] and idx["to"].tolist() == [3, 7, 12]
+    assert calculate_episode_data_index({"episode_index": []})["from"].numel() == 0
+    paths = save_images_concurrently(np.zeros((3, 4, 5, 3), np.uint8), tmp_path / "imgs", max_workers=2)
+    assert [p.name for p in paths] == ["frame_000000.png", "frame_000001.png", "frame_000002.png"]
+    assert all(p.exists() for p in paths)
+    check_repo_id("lerobot/pusht")
+    for bad in ("pusht", "a/b/c", "/x"):
+        with pytest.raises(ValueError):
+            check_repo_id(bad)
+    assert isinstance(get_default_encoding(), dict)
