@@ -3,6 +3,8 @@
 import glob
 import time
 
+from .device_paths import stable_serial_path
+
 
 def list_ports() -> set[str]:
     return set(glob.glob("/dev/ttyACM*") + glob.glob("/dev/ttyUSB*") + glob.glob("/dev/tty.usbmodem*"))
@@ -14,7 +16,12 @@ def main(argv=None):
     time.sleep(0.5)
     gone = before - list_ports()
     if len(gone) == 1:
-        print(f"The port of this arm is {gone.pop()}. Plug the cable back in.")
+        port = gone.pop()
+        print(f"The port of this arm is {port}. Plug the cable back in.")
+        input("Press Enter once it is plugged in again...")
+        stable = stable_serial_path(port)
+        if stable:
+            print(f"Use the stable name in configs (it survives reboots and replugs): {stable}")
     else:
         print(f"Could not identify the port (candidates: {sorted(gone) or 'none'}).")
 

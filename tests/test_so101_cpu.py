@@ -102,3 +102,23 @@ def test_bimanual_pair_prefixes_keys_and_keeps_one_calibration_per_side(tmp_path
     assert abs(sent["left_shoulder_pan.pos"] - 100.0) < 0.1 and abs(sent["right_shoulder_pan.pos"]) < 0.1
     assert ports["fl"]._get(1, "Goal_Position") == 3072 and ports["fr"]._get(1, "Goal_Position") == 2048
     assert abs(obs["left_shoulder_pan.pos"] - 100.0) < 0.1 and "right_gripper.pos" in obs
+
+
+def test_stable_device_aliases(tmp_path):
+    from opentau_b200.scripts.so101.device_paths import stable_link_map, stable_serial_path, stable_video_path
+    dev = tmp_path / "dev"
+    by_id = dev / "serial" / "by-id"
+    by_path = dev / "v4l" / "by-path"
+    by_id.mkdir(parents=True)
+    by_path.mkdir(parents=True)
+    (dev / "ttyACM0").write_text("")
+    (dev / "video0").write_text("")
+    (by_id / "usb-1a86_USB_Single_Serial_5A46-if00").symlink_to(dev / "ttyACM0")
+    (by_path / "pci-0000:00:14.0-usb-0:2:1.0-video-index0").symlink_to(dev / "video0")
+    (by_path / "pci-0000:00:14.0-usbv2-0:2:1.0-video-index0").symlink_to(dev / "video0")
+    assert stable_serial_path(str(dev / "ttyACM0"), by_id).endswith("usb-1a86_USB_Single_Serial_5A46-if00")
+    # two aliases of one node: the first in sorted order, every time
+    assert stable_video_path(str(dev / "video0"), by_path).endswith("-usb-0:2:1.0-video-index0")
+    assert len(stable_link_map(by_path)) == 1
+    assert stable_video_path(0, by_path) is None and stable_serial_path(str(dev / "ttyACM9"), by_id) is None
+    assert stable_link_map(tmp_path / "missing") == {}
