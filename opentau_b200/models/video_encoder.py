@@ -90,6 +90,12 @@ class SpaceTimeSiglipVideoEncoder(nn.Module):
         B, T, C, Hh, Ww = video.shape
         if T > self.max_num_frames:
             raise ValueError(f"{T} frames exceed max_num_frames={self.max_num_frames}")
+        if frame_valid is not None:
+            # The current (last) frame is always real, also when the history-drop augmentation flags every step as
+            # padding (reference tests/policies/test_history_drop_current_frame.py); on a copy: the caller's mask
+            # stays as it was.
+            frame_valid = frame_valid.bool().clone()
+            frame_valid[:, -1] = True
         vm = self.vision.vision_model
         dtype = vm.post_layernorm.weight.dtype
         x = vm.embeddings(video.flatten(0, 1), dtype)            # (B*T, N, d)

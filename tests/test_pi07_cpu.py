@@ -57,6 +57,13 @@ def test_video_encoder_single_frame_equals_plain_siglip_and_history_matters():
     assert not torch.allclose(a, enc(vid2))                       # history reaches the current-frame tokens
     valid = torch.tensor([[False, True, True], [False, True, True]])
     assert torch.allclose(enc(vid, valid), enc(vid2, valid), atol=1e-5)   # ... unless that frame is padding
+    # a forced history drop flags EVERY step as padding: the current frame is kept all the same, the result equals
+    # "only the current frame is real" and is finite, and the caller's mask is not modified
+    none_valid = torch.zeros(2, 3, dtype=torch.bool)
+    only_current = torch.tensor([[False, False, True]] * 2)
+    dropped = enc(vid, none_valid)
+    assert torch.isfinite(dropped).all() and torch.allclose(dropped, enc(vid, only_current), atol=1e-6)
+    assert not none_valid.any()
     assert not any("video_encoder" in k for k in pol.state_dict())    # no duplicated vision weights
 
 
