@@ -141,6 +141,48 @@ class PreTrainedConfig(ChoiceRegistry, abc.ABC):
         if delay and delay >= chunk:
             raise ValueError(f"{self.action_horizon_delay_field} ({delay}) must be < chunk_size ({chunk})")
 
+    def _bound_image_resolutions(self) -> dict[str, tuple[int, int]]:
+        """``(H, W)`` of every bound visual feature with a ``(C, H, W)`` shape."""
+        out = {}
+        for key, ft in self.image_features.items():
+            shape = tuple(getattr(ft, "shape", ()) or ())
+            if len(shape) == 3:
+                out[key] = (int(shape[1]), int(shape[2]))
+        return out
+
+    def validate_input_resolution(self, *, strict: bool) -> None:
+        """``resize_imgs_with_padding`` must equal the resolution of the bound image features, else every frame is
+        letterboxed a second time inside the policy; with ``None`` (native pass-through) all cameras must agree with
+        each other.  ``strict`` (training-shaped construction) raises unless ``skip_input_resolution_check``; an
+        eval / inference load only warns so that checkpoints trained with the mismatch stay loadable (reference
+        ``src/opentau/configs/policies.py:732-799``)."""
+        import dataclasses
+        if "resize_imgs_with_padding" not in {f.name for f in dataclasses.fields(self)}:
+            return                       # no such setting (or a derived one: the policy always resizes to it)
+        target = self.resize_imgs_with_padding
+        bound = self._bound_image_resolutions()
+        if target is None:
+            if len(set(bound.values())) <= 1:
+                return
+            listed = ", ".join(f"{k}={v}" for k, v in sorted(bound.items()))
+            msg = (f"resize_imgs_with_padding is null (native pass-through) but the bound image features have mixed "
+                   f"resolutions: {listed}; give one (H, W) target instead.")
+        else:
+            target = tuple(int(x) for x in target)
+            off = {k: v for k, v in bound.items() if v != target}
+            if not off:
+                return
+            listed = ", ".join(f"{k}={v}" for k, v in sorted(off.items()))
+            msg = (f"resize_imgs_with_padding={target} (H, W) differs from the bound image features: {listed}. The "
+                   "policy would resample and pad every frame a second time. Set it to the input resolution, or to "
+                   "null to pass frames through (PaliGemma-family policies only).")
+        if strict and not self.skip_input_resolution_check:
+            raise ValueError(msg + " To resume a checkpoint trained with this mismatch set "
+                                   "policy.skip_input_resolution_check=true.")
+        import logging
+        logging.warning("%s Proceeding because this is %s.", msg,
+                        "skip_input_resolution_check=true" if strict else "an eval / inference load")
+
     # -- persistence -----------------------------------------------------------------------------
     def to_dict(self) -> dict[str, Any]:
         return encode(self)

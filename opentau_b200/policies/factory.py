@@ -96,6 +96,7 @@ def make_policy(cfg: PreTrainedConfig, ds_meta: Any | None = None, per_dataset_s
     if dataset_names is not None:
         cfg.dataset_names = list(dataset_names)
         cfg.dataset_to_norm_index = {n: i for i, n in enumerate(dataset_names)}
+    cfg.validate_input_resolution(strict=True)
     if cfg.pretrained_path:
         policy = policy_cls.from_pretrained(cfg.pretrained_path, config=cfg, **kwargs)
         if per_dataset_stats is not None and cfg.skip_normalization_weights:

@@ -146,6 +146,7 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
         from ..utils.hub import resolve_local_or_hub
         if config is None:
             config = PreTrainedConfig.from_pretrained(pretrained_name_or_path)
+            config.validate_input_resolution(strict=False)       # a stored config: warn, keep loading
         model_dir = resolve_local_or_hub(str(pretrained_name_or_path))
         policy = cls(config, **kwargs)
         weights = Path(model_dir) / SAFETENSORS_SINGLE_FILE

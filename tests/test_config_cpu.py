@@ -138,3 +138,29 @@ def test_scheduler_formula():
     assert f(20) == pytest.approx(0.1) and f(200) == pytest.approx(0.1)
     import math
     assert f(10) == pytest.approx(0.9 * 0.5 * (1 + math.cos(math.pi * 0.5)) + 0.1)
+
+
+def test_input_resolution_validation(caplog):
+    import logging
+
+    import pytest
+
+    from opentau_b200.configs.types import FeatureType, PolicyFeature
+    from opentau_b200.policies.factory import make_policy_config
+
+    def cfg(resize, shapes, **kw):
+        feats = {f"camera{i}": PolicyFeature(type=FeatureType.VISUAL, shape=(3, *hw)) for i, hw in enumerate(shapes)}
+        feats["state"] = PolicyFeature(type=FeatureType.STATE, shape=(8,))
+        return make_policy_config("pi05", resize_imgs_with_padding=resize, input_features=feats,
+                                  output_features={"actions": PolicyFeature(type=FeatureType.ACTION, shape=(7,))}, **kw)
+
+    cfg((224, 224), [(224, 224), (224, 224)]).validate_input_resolution(strict=True)       # matches: silent
+    cfg(None, [(180, 320), (180, 320)]).validate_input_resolution(strict=True)             # native, one geometry
+    with pytest.raises(ValueError, match="camera1=\\(180, 320\\)"):
+        cfg((224, 224), [(224, 224), (180, 320)]).validate_input_resolution(strict=True)
+    with pytest.raises(ValueError, match="mixed resolutions"):
+        cfg(None, [(224, 224), (180, 320)]).validate_input_resolution(strict=True)
+    with caplog.at_level(logging.WARNING):
+        cfg((224, 224), [(180, 320)]).validate_input_resolution(strict=False)              # eval load: warn only
+        cfg((224, 224), [(180, 320)], skip_input_resolution_check=True).validate_input_resolution(strict=True)
+    assert sum("differs from the bound image features" in r.getMessage() for r in caplog.records) == 2
