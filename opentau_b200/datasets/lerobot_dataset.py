@@ -331,6 +331,60 @@ class BaseDataset(torch.utils.data.Dataset):
                 out[k] = v if not dropped else torch.zeros_like(v)
                 out[f"{k}_is_pad"] = torch.tensor(dropped, dtype=torch.bool)
 
+    @staticmethod
+    def _resolve_episode_success(item: dict, episodes_info: dict, name_map: dict[str, str],
+                                 episode_stats: dict | None = None) -> bool | None:
+        """The ``success`` role of the current sample, first hit wins: the column mapped to ``success`` read from the
+        frame, then from the episode's metadata record; that column's per-episode ``mean`` thresholded at 0.5; the
+        plain ``success`` key of the episode record.  ``None`` = unlabelled (not the same as "failed").  Pass only
+        genuinely per-episode statistics (reference ``src/opentau/datasets/lerobot_dataset.py:2596-2650``)."""
+        def first(v):
+            return np.asarray(v.cpu() if isinstance(v, Tensor) else v).reshape(-1)[0]
+
+        col = name_map.get("success")
+        if col is not None:
+            value = item.get(col)
+            if value is None:
+                value = episodes_info.get(col)
+            if value is not None:
+                return bool(first(value))
+            stat = ((episode_stats or {}).get(col) or {}).get("mean")
+            if stat is not None:
+                return float(first(stat)) >= 0.5
+        value = episodes_info.get("success")
+        return None if value is None else bool(first(value))
+
+    @staticmethod
+    def _count_success_role_varying_episodes(episodes_stats, success_col: str) -> tuple[int, int]:
+        """``(varying, checked)``: episodes whose mapped success column has min != max, among those that have both
+        aggregates (0 checked = nothing provable)."""
+        varying = checked = 0
+        entries = episodes_stats.values() if isinstance(episodes_stats, dict) else episodes_stats
+        for st in entries:
+            col = (st or {}).get(success_col) or {}
+            if col.get("min") is None or col.get("max") is None:
+                continue
+            checked += 1
+            lo, hi = np.asarray(col["min"]).reshape(-1)[0], np.asarray(col["max"]).reshape(-1)[0]
+            varying += int(lo != hi)
+        return varying, checked
+
+    def _attach_mistake_raw(self, item: dict, episodes_info: dict, ep_idx: int) -> bool | None:
+        """``mistake_raw`` from the frame column mapped to ``mistake`` (segment-grained, wins), else the inverse of the
+        resolved ``success`` role; neither -> no key.  Returns the resolved success for the return bins."""
+        name_map = self._get_name_map()
+        stats = None
+        if getattr(self.meta, "version", "") != "v2.0":       # v2.0 has dataset-level statistics only
+            stats = (getattr(self.meta, "episodes_stats", None) or {}).get(ep_idx)
+        success = self._resolve_episode_success(item, episodes_info, name_map, stats)
+        mistake_col = name_map.get("mistake", "mistake")
+        if mistake_col in item:
+            item["mistake_raw"] = bool(np.asarray(item[mistake_col].cpu() if isinstance(item[mistake_col], Tensor)
+                                                  else item[mistake_col]).reshape(-1)[0])
+        elif success is not None:
+            item["mistake_raw"] = not success
+        return success
+
     def _to_standard_data_format(self, item: dict) -> dict:
         name_map = self._get_name_map()
         out: dict[str, Any] = {}
@@ -595,9 +649,7 @@ class LeRobotDataset(BaseDataset):
         item.setdefault("response", "")
         if "memory" in item:
             item["memory_raw"] = str(item["memory"])
-        success = ep_info.get("success")
-        if "mistake" in item:
-            item["mistake_raw"] = bool(item["mistake"])
+        success = self._attach_mistake_raw(item, ep_info, ep_idx)
         if ep_info.get("quality") is not None:
             item["quality_raw"] = int(ep_info["quality"])
         item["speed_raw"] = self.speed_raw_by_episode[ep_idx] if "speed" in ep_info else None

@@ -61,3 +61,46 @@ def test_speed_buckets_per_task():
     tasks = {0: "a", 1: "a", 2: "a", 3: "a", 4: "b", 5: "b"}
     b = speed_buckets(speeds, tasks, n_buckets=2)
     assert [b[i] for i in range(6)] == [1, 1, 2, 2, 1, 2]
+
+
+def test_success_role_resolution_chain_and_mistake_polarity():
+    import numpy as np
+    import torch
+
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDataset
+    res = LeRobotDataset._resolve_episode_success
+    nm = {"success": "is_episode_successful"}
+    # 1. mapped column in the frame, then in the episode record
+    assert res({"is_episode_successful": torch.tensor([0.0])}, {"success": True}, nm) is False
+    assert res({}, {"is_episode_successful": 1, "success": False}, nm) is True
+    # 2. the per-episode mean of the mapped column, thresholded at 0.5
+    assert res({}, {}, nm, {"is_episode_successful": {"mean": np.array([0.8])}}) is True
+    assert res({}, {}, nm, {"is_episode_successful": {"mean": [0.2]}}) is False
+    # 3. the plain per-episode key; nothing at all -> None (unlabelled, not failed)
+    assert res({}, {"success": np.bool_(False)}, {}) is False and res({}, {}, nm) is None
+    cnt = LeRobotDataset._count_success_role_varying_episodes
+    stats = {0: {"s": {"min": [0.0], "max": [0.0]}}, 1: {"s": {"min": [0.0], "max": [1.0]}}, 2: {"other": {}}}
+    assert cnt(stats, "s") == (1, 2) and cnt([], "s") == (0, 0)
+
+    class Fake:
+        meta = type("M", (), {"version": "v2.1", "episodes_stats": {3: {"done_ok": {"mean": [1.0]}}}})()
+
+        def __init__(self, name_map):
+            self._nm = name_map
+
+        def _get_name_map(self):
+            return self._nm
+
+        _resolve_episode_success = staticmethod(LeRobotDataset._resolve_episode_success)
+
+    attach = LeRobotDataset._attach_mistake_raw
+    item = {"mistake": torch.tensor(True)}
+    assert attach(Fake({}), item, {"success": True}, 0) is True and item["mistake_raw"] is True     # the column wins
+    item = {}
+    assert attach(Fake({}), item, {"success": False}, 0) is False and item["mistake_raw"] is True   # inverted success
+    item = {}
+    assert attach(Fake({"success": "done_ok"}), item, {}, 3) is True and item["mistake_raw"] is False
+    item = {}
+    assert attach(Fake({}), item, {}, 0) is None and "mistake_raw" not in item
+    item = {"oops": torch.tensor([0])}
+    assert attach(Fake({"mistake": "oops"}), item, {}, 0) is None and item["mistake_raw"] is False
