@@ -79,6 +79,11 @@ class Qwen3VLWithExpertModel(nn.Module):
                 p.requires_grad = False
             for p in self.backbone.model.visual.parameters():
                 p.requires_grad = True
+        if getattr(c, "train_state_action_representation_only", False):
+            # no discrete-action pathway here: the whole wrapper is frozen, only the policy-level state / action
+            # projections keep training
+            from ..utils import freeze_with_expert_params_for_state_action_representation_only
+            freeze_with_expert_params_for_state_action_representation_only(self)
 
     def train(self, mode: bool = True):
         super().train(mode)
@@ -254,6 +259,8 @@ class Cosmos3Policy(PreTrainedPolicy):
         vocab = qwen3_text_config(**(config.backbone or {})).vocab_size
         self.language_tokenizer = load_text_tokenizer(config.tokenizer_path, vocab)
         self.model = Cosmos3FlowMatching(config)
+        from ..utils import apply_policy_level_freezes
+        apply_policy_level_freezes(self.model, self.model.qwen3vl_with_expert, config)
         self.reset()
 
     def enable_tensor_parallel(self, tp, free_replicated_weights: bool = False) -> None:

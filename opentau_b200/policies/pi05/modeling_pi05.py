@@ -154,6 +154,9 @@ class PaliGemmaWithExpertModel(nn.Module):
             self.paligemma.vision_tower.eval()
         if self.config.train_expert_only:
             self.paligemma.eval()
+        if getattr(self.config, "train_state_action_representation_only", False):
+            from ..utils import set_with_expert_train_mode_for_state_action_representation_only
+            set_with_expert_train_mode_for_state_action_representation_only(self, mode)
         return self
 
     # -- embedders -----------------------------------------------------------------------------
@@ -544,6 +547,8 @@ class PI05Policy(PreTrainedPolicy):
         self.discrete_action_processor = load_action_tokenizer(config.discrete_action_tokenizer_path,
                                                                config.discrete_action_vocab_size)
         self.model = self.model_class(config, tokenizer=self.language_tokenizer)
+        from ..utils import apply_policy_level_freezes
+        apply_policy_level_freezes(self.model, self.model.wrapper, config)
         self.reset()
 
     def reset(self) -> None:

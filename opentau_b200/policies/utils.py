@@ -79,3 +79,85 @@ def log_model_loading_keys(missing_keys: list[str], unexpected_keys: list[str]) 
         logging.warning("Missing key(s) when loading model: %s", missing_keys)
     if unexpected_keys:
         logging.warning("Unexpected key(s) when loading model: %s", unexpected_keys)
+
+
+# -- policy-level halves of the "train only ..." flags -----------------------------------------------------------
+#: Projections on the flow-matching module that face the dataset's state / action spaces.
+STATE_ACTION_PROJECTION_ATTRS: tuple[str, ...] = ("state_proj", "action_in_proj", "action_out_proj")
+#: Modules on the backbone+expert wrapper that hold the discrete-action (FAST token) representation.
+DISCRETE_ACTION_REPRESENTATION_ATTRS: tuple[str, ...] = ("discrete_action_embedding", "da_head")
+
+
+def _param_ids_of_attrs(module: nn.Module, attrs: tuple[str, ...]) -> set[int]:
+    ids: set[int] = set()
+    for a in attrs:
+        sub = getattr(module, a, None)
+        if isinstance(sub, nn.Module):
+            ids.update(id(p) for p in sub.parameters())
+        elif isinstance(sub, nn.Parameter):
+            ids.add(id(sub))
+    return ids
+
+
+def freeze_policy_level_params_for_vision_only(policy_module: nn.Module, with_expert_module: nn.Module) -> None:
+    """``train_vision_encoder_only``, outer half: the wrapper has already left exactly the vision tower and its
+    projector trainable; every parameter of the enclosing module that is not the wrapper's is frozen here (state /
+    action projections, time MLPs, modality embeddings ...), except a video encoder's ``motion_module``, which is part
+    of the vision pathway.  Default-deny instead of a list of names, so that a projection added later cannot keep
+    training unnoticed (reference ``src/opentau/policies/utils.py:401-440``)."""
+    protected = {id(p) for p in with_expert_module.parameters()}
+    for name, p in policy_module.named_parameters():
+        if id(p) in protected or "motion_module" in name:
+            continue
+        p.requires_grad = False
+
+
+def freeze_with_expert_params_for_state_action_representation_only(with_expert_module: nn.Module) -> list[str]:
+    """``train_state_action_representation_only``, inner half: everything the wrapper owns is frozen except the
+    discrete-action embedding and head.  Returns the names left trainable (empty for policies without a
+    discrete-action pathway; reference ``policies/utils.py:550-584``)."""
+    keep = _param_ids_of_attrs(with_expert_module, DISCRETE_ACTION_REPRESENTATION_ATTRS)
+    left = []
+    for name, p in with_expert_module.named_parameters():
+        p.requires_grad = id(p) in keep
+        if p.requires_grad:
+            left.append(name)
+    return sorted(left)
+
+
+def set_with_expert_train_mode_for_state_action_representation_only(with_expert_module: nn.Module, mode: bool) -> None:
+    """Under that flag the frozen trunk runs in eval mode (its dropout would only add noise in front of the two
+    trainable modules); the discrete-action modules follow ``mode`` (reference ``policies/utils.py:587-615``)."""
+    for child in with_expert_module.children():
+        child.eval()
+    for a in DISCRETE_ACTION_REPRESENTATION_ATTRS:
+        sub = getattr(with_expert_module, a, None)
+        if isinstance(sub, nn.Module):
+            sub.train(mode)
+
+
+def freeze_policy_level_params_for_state_action_representation_only(policy_module: nn.Module,
+                                                                    with_expert_module: nn.Module) -> list[str]:
+    """``train_state_action_representation_only``, outer half: of the enclosing module's own parameters only the
+    state / action projections stay trainable; time MLPs, modality embeddings and any video-encoder parameters
+    (a freshly initialised ``motion_module`` included) are frozen.  Returns the outer names left trainable
+    (reference ``policies/utils.py:618-660``)."""
+    protected = {id(p) for p in with_expert_module.parameters()}
+    keep = _param_ids_of_attrs(policy_module, STATE_ACTION_PROJECTION_ATTRS)
+    left = []
+    for name, p in policy_module.named_parameters():
+        if id(p) in protected:
+            continue
+        p.requires_grad = id(p) in keep
+        if p.requires_grad:
+            left.append(name)
+    return sorted(left)
+
+
+def apply_policy_level_freezes(policy_module: nn.Module, with_expert_module: nn.Module, config) -> None:
+    """Call once the flow-matching module is fully built (subclasses add projections after their parent's
+    constructor)."""
+    if getattr(config, "train_vision_encoder_only", False):
+        freeze_policy_level_params_for_vision_only(policy_module, with_expert_module)
+    if getattr(config, "train_state_action_representation_only", False):
+        freeze_policy_level_params_for_state_action_representation_only(policy_module, with_expert_module)

@@ -116,3 +116,41 @@ def test_factory_registry():
         assert get_policy_class(name).name == name
     with pytest.raises(NotImplementedError):
         get_policy_class("nope")
+
+
+def test_policy_level_freeze_flags():
+    """The "train only ..." flags reach the projections on the flow-matching module, not just the wrapper."""
+    from opentau_b200.policies.utils import (freeze_policy_level_params_for_state_action_representation_only,
+                                             freeze_policy_level_params_for_vision_only)
+
+    from helpers import tiny_pi05_config as _pi05
+
+    pol = make_policy(_pi05(train_vision_encoder_only=True, freeze_vision_encoder=False, train_expert_only=False), per_dataset_stats=[identity_stats()])
+    names = {n for n, p in pol.model.named_parameters() if p.requires_grad}
+    assert names and all("vision_tower" in n or "multi_modal_projector" in n for n in names)
+
+    pol = make_policy(_pi05(train_state_action_representation_only=True, train_expert_only=False), per_dataset_stats=[identity_stats()])
+    names = {n for n, p in pol.model.named_parameters() if p.requires_grad}
+    heads = {n.split(".")[-2] for n in names}
+    assert heads - {"state_proj"} == {"action_in_proj", "action_out_proj", "discrete_action_embedding", "da_head"}
+    pol.train()
+    w = pol.model.wrapper
+    assert not w.paligemma.training and w.da_head.training          # the frozen trunk stays in eval mode
+
+    class Outer(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.inner = torch.nn.Linear(2, 2)
+            self.state_proj = torch.nn.Linear(2, 2)
+            self.time_mlp_in = torch.nn.Linear(2, 2)
+            self.video = torch.nn.Module()
+            self.video.motion_module = torch.nn.Linear(2, 2)
+
+    o = Outer()
+    freeze_policy_level_params_for_vision_only(o, o.inner)
+    assert {n for n, p in o.named_parameters() if p.requires_grad} == {
+        "inner.weight", "inner.bias", "video.motion_module.weight", "video.motion_module.bias"}
+    o = Outer()
+    left = freeze_policy_level_params_for_state_action_representation_only(o, o.inner)
+    assert left == ["state_proj.bias", "state_proj.weight"] and not o.video.motion_module.weight.requires_grad
+    assert o.inner.weight.requires_grad            # the wrapper's own parameters are not touched here
