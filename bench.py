@@ -40,7 +40,7 @@ def parse_args():
     ap.add_argument("--strategy", default="zero2")
     ap.add_argument("--tiny", action="store_true", help="small geometry (plumbing check, not a benchmark)")
     ap.add_argument("--mode", default="train", choices=["train", "infer"])
-    ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3"],
+    ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3", "pi06"],
                     help="--mode infer only: cosmos3 is the workload of the reference's published B200 latency table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (profiling runs only)")
     ap.add_argument("--kernel-table", default="", metavar="PATH",
@@ -141,7 +141,8 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
     # (docs/source/tutorials/benchmarking.rst:437-510): p50 106.86 ms
     published_p50 = {"cosmos3": 106.86}.get(args.model)
     prompt_len = 64 if args.model == "cosmos3" else 200
-    policy, batch = BUILDERS[args.model](3, prompt_len, device, tiny=args.tiny, num_steps=10)
+    num_steps = 5 if args.model == "pi06" else 10          # each policy's reference default
+    policy, batch = BUILDERS[args.model](3, prompt_len, device, tiny=args.tiny, num_steps=num_steps)
     if use_cuda and args.impl == "ours":
         policy.enable_cuda_graphs(True)
     host = {k: (v.cpu().pin_memory() if use_cuda else v.cpu()) for k, v in batch.items() if hasattr(v, "cpu")}
@@ -195,7 +196,7 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
     if rank == 0:
         n_params = sum(p.numel() for p in policy.parameters())
         print(json.dumps({
-            "metric": f"{args.model} p50 10-step action-chunk latency", "value": round(float(stats[0]), 3),
+            "metric": f"{args.model} p50 {num_steps}-step action-chunk latency", "value": round(float(stats[0]), 3),
             "unit": "ms",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(float(stats[2]), 3), "higher_is_better": False, "scaling": "weak",
@@ -204,10 +205,12 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
             "config": {"model": ("tiny (plumbing)" if args.tiny else
                                  "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"
                                  if args.model == "pi05" else
+                                 "pi0.6 (Gemma-3-4B backbone, SigLIP @448 x3 cams pooled to 256 tokens each, "
+                                 "1280-wide 34-layer expert)" if args.model == "pi06" else
                                  "cosmos3 (Qwen3-VL-32B-shaped backbone, 64-layer 0.9B expert, 3 cams @224, "
                                  "prompt <= 64 tokens)"),
                        "global_batch": world, "parallelism": f"replica x{world}",
-                       "params": n_params, "denoise_steps": 10, "action_chunk": "50x32",
+                       "params": n_params, "denoise_steps": num_steps, "action_chunk": "50x32",
                        "cuda_graph": bool(use_cuda and args.impl == "ours"),
                        "l2": "each call streams every bf16 weight once (GBs, far more than the 126 MB L2); no "
                              "explicit flush"},

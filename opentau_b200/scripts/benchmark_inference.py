@@ -108,7 +108,48 @@ def build_cosmos3(cams: int, prompt_len: int, device, tiny: bool = False, num_st
     return policy, batch
 
 
-BUILDERS = {"pi05": build_pi05, "cosmos3": build_cosmos3}
+def build_pi06(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 5,
+               depth: int | None = None):
+    """pi0.6 at its reference geometry (``src/opentau/policies/pi06/configuration_pi06.py:38-276``): Gemma-3-4B
+    backbone, ``cams`` cameras at 448x448 pooled to 256 tokens each, the 1280-wide 34-layer action expert, a
+    50-action chunk in 5 flow-matching steps (the reference quotes the model card's "~63 ms per chunk on an H100"
+    for this shape).  Random weights."""
+    from ..configs.types import FeatureType, PolicyFeature
+    from ..datasets.synthetic import SyntheticSpec, identity_stats, make_synthetic_batch
+    from ..policies.pi06.configuration_pi06 import PI06Config
+    from ..policies.pi06.modeling_pi06 import PI06Policy
+    res = (224, 224) if tiny else (448, 448)
+    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, *res)) for i in range(cams)}
+    feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
+    kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=prompt_len, num_steps=num_steps, dropout=0.0,
+              device=str(device), input_features=feats, resize_imgs_with_padding=res,
+              output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
+    vocab = 262208
+    if tiny:
+        kw.update(vlm=dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=64, intermediate_size=1024, vocab_size=1024, sliding_window_pattern=2),
+                  expert=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                              head_dim=64, intermediate_size=512, vocab_size=1024),
+                  vision=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4),
+                  vlm_config={"tokens_per_image_side": 8})
+        vocab = 1024
+    cfg = PI06Config(**kw)
+    spec = SyntheticSpec(batch_size=1, num_cams=cams, resolution=res, prompt_len=prompt_len, vocab_size=vocab,
+                         state_dim=32, action_dim=32, chunk_size=50, image_dtype=torch.bfloat16)
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(device):
+            policy = PI06Policy(cfg, per_dataset_stats=[identity_stats()])
+    finally:
+        torch.set_default_dtype(prev)
+    policy.to(device).to(torch.bfloat16).eval()
+    batch = make_synthetic_batch(spec, device=device, seed=3)
+    return policy, batch
+
+
+BUILDERS = {"pi05": build_pi05, "cosmos3": build_cosmos3, "pi06": build_pi06}
 
 
 def run(policy, batch, n_warmup: int, n_timed: int, n_candidates: int = 1) -> dict:

@@ -46,3 +46,19 @@ def test_bin_to_safetensors(tmp_path):
     assert convert(tmp_path / "m.bin", tmp_path / "m.safetensors") == 3
     sd = load_file(str(tmp_path / "m.safetensors"))
     assert set(sd) == {"a.weight", "b.weight", "c"} and torch.equal(sd["a.weight"], sd["b.weight"])
+
+
+def test_latency_benchmark_builders_on_tiny_geometries():
+    """Every policy of the latency benchmark builds at its plumbing size and produces one action chunk."""
+    import torch
+
+    from opentau_b200.scripts.benchmark_inference import BUILDERS, run, summarize
+    assert set(BUILDERS) == {"pi05", "cosmos3", "pi06"}
+    for name, steps in (("pi05", 3), ("pi06", 2)):
+        policy, batch = BUILDERS[name](1, 16, torch.device("cpu"), True, steps)
+        with torch.no_grad():
+            out = policy.sample_actions(batch)
+        assert out.shape[0] == 1 and out.shape[1] == 50 and torch.isfinite(out.float()).all()
+    rec = run(policy, batch, 1, 2)
+    assert rec["n_timed"] == 2 if "n_timed" in rec else True
+    assert summarize([1.0, 2.0, 3.0])["p50_ms"] == 2.0
