@@ -140,6 +140,8 @@ class TrainEngine:
         self._micro += 1
         out = {k: v.detach() for k, v in losses.items() if isinstance(v, Tensor)}
         out["loss"] = loss.detach() * self.grad_accum_steps
+        if losses.get("outlier_records"):
+            out["outlier_records"] = losses["outlier_records"]     # host-side debug records, logged by the trainer
         return out
 
     def optimizer_step(self) -> Tensor:

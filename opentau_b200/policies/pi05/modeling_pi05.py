@@ -660,12 +660,21 @@ class PI05Policy(PreTrainedPolicy):
         state = nb["state"]
         if state.dim() == 3:
             state = state[:, -1]
-        return self.model(images, img_masks, lang_tokens, lang_masks, tb["actions"],
-                          actions_is_pad=batch.get("action_is_pad"), response_tokens=resp_t, response_masks=resp_m,
-                          noise=noise, time=time, discrete_actions=da, discrete_action_masks=dam,
-                          state=state if self.config.state_type == "continuous" else None,
-                          real_action_dim=batch.get("real_action_dim"), return_per_sample=return_per_sample,
-                          prefix_kwargs=self._prefix_kwargs(batch, nb))
+        out = self.model(images, img_masks, lang_tokens, lang_masks, tb["actions"],
+                         actions_is_pad=batch.get("action_is_pad"), response_tokens=resp_t, response_masks=resp_m,
+                         noise=noise, time=time, discrete_actions=da, discrete_action_masks=dam,
+                         state=state if self.config.state_type == "continuous" else None,
+                         real_action_dim=batch.get("real_action_dim"), return_per_sample=return_per_sample,
+                         prefix_kwargs=self._prefix_kwargs(batch, nb))
+        threshold = getattr(self.config, "warn_outlier_threshold", None)
+        if threshold is not None and threshold > 0 and isinstance(out, dict):
+            # Debug aid of the policies that carry the setting (reference pi07 low level ``forward``,
+            # ``modeling_pi07_low_level.py:1003-1006``): pure and collective-free here; the trainer gathers and logs.
+            from ..outlier_utils import detect_state_action_outliers
+            probe = dict(batch)
+            probe["state"], probe["actions"] = nb["state"], tb["actions"]
+            out["outlier_records"] = detect_state_action_outliers(probe, threshold)
+        return out
 
     @torch.no_grad()
     def sample_actions(self, batch: dict[str, Any], noise: Tensor | None = None, action_prefix: Tensor | None = None,

@@ -165,11 +165,19 @@ def run_validation(policy, loader, n_batches: int, device, names: list[str], wei
 def update_policy(engine: TrainEngine, batches: list[dict[str, Any]]) -> dict[str, Tensor]:
     """One optimizer step over ``len(batches)`` micro-batches (gradient accumulation)."""
     sums: dict[str, Tensor] = {}
+    records: list[dict[str, Any]] = []
     for b in batches:
         out = engine.forward_backward(b)
+        records += out.pop("outlier_records", [])
         for k, v in out.items():
             sums[k] = sums.get(k, 0) + v.float() / len(batches)
     sums["grad_norm"] = engine.optimizer_step().float()
+    # State / action outliers found inside forward (policies with ``warn_outlier_threshold``): every rank takes part,
+    # rank 0 warns once per offender, whichever rank held the sample (reference scripts/train.py:282-287, 350-425).
+    threshold = getattr(getattr(engine.policy, "config", None), "warn_outlier_threshold", None)
+    if threshold is not None and threshold > 0:
+        from ..policies.outlier_utils import log_outlier_records_distributed
+        log_outlier_records_distributed(records, threshold)
     return sums
 
 

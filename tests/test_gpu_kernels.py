@@ -254,6 +254,32 @@ def test_adamw_and_clip_kernels(dev):
     assert abs(out[0].item() - 0.25 * min(1.0, 1.0 / (norm + 1e-6))) < 1e-6
 
 
+@pytest.mark.parametrize("offset,grad_dtype,with_p16", [(0, torch.bfloat16, True), (1, torch.bfloat16, True),
+                                                          (0, torch.float32, False), (4, torch.float32, True)])
+def test_adamw_vector_and_scalar_paths_agree_with_reference(dev, offset, grad_dtype, with_p16):
+    """Aligned buffers take the 8-wide kernel plus a scalar tail; views that start off a 16-byte boundary take the
+    scalar kernel for everything.  Both must give the fp32 reference."""
+    from opentau_b200.ops import cuda_ops
+    from opentau_b200.ops import reference as ref
+    n = 65_536 + 5
+    base = [torch.randn(n + 8, device=dev) for _ in range(2)]
+    p = base[0][offset:offset + n]
+    g = base[1].to(grad_dtype)[offset:offset + n]
+    m, v = torch.zeros(n + 8, device=dev)[offset:offset + n], torch.zeros(n + 8, device=dev)[offset:offset + n]
+    p16 = torch.empty(n + 8, device=dev, dtype=torch.bfloat16)[offset:offset + n] if with_p16 else None
+    pr, mr, vr = p.clone().cpu(), m.clone().cpu(), v.clone().cpu()
+    guard = base[0][offset + n:].clone()
+    for step in (1, 2):
+        cuda_ops.adamw(p, g, m, v, p16, lr=3e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+        ref.adamw_flat(pr, g.cpu(), mr, vr, None, lr=3e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+    torch.testing.assert_close(p.cpu(), pr, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(m.cpu(), mr, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(v.cpu(), vr, rtol=1e-4, atol=1e-7)
+    if with_p16:
+        torch.testing.assert_close(p16.cpu().float(), pr, rtol=1e-2, atol=1e-2)
+    assert torch.equal(base[0][offset + n:], guard)            # nothing written past the end
+
+
 def test_resize_pad_kernel(dev):
     from opentau_b200 import ops
     from opentau_b200.ops import cuda_ops

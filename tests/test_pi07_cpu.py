@@ -164,3 +164,25 @@ def test_paligemma_variants_share_the_pi07_logic():
     assert o["CE"].item() > 0 and not any("gemma_expert" in n for n, _ in hl.named_parameters())
     mem, sub = hl.plan(hb)
     assert len(mem) == 4 and len(sub) == 4
+
+
+def test_outlier_records_travel_from_forward_to_the_trainer(caplog):
+    import logging
+
+    from opentau_b200.parallel.engine import OptimHyper, TrainEngine
+    from opentau_b200.scripts.train import update_policy
+    torch.manual_seed(0)
+    pol = _ll(warn_outlier_threshold=5.0)
+    b = _history_batch()
+    b["state"] = b["state"].clone()
+    b["state"][2, -1, 3] = 80.0                                   # identity statistics: normalised value = raw value
+    out = pol(b, noise=torch.zeros(4, 10, 32), time=torch.full((4,), 0.5))
+    recs = out["outlier_records"]
+    assert len(recs) == 1 and recs[0]["key"] == "state" and recs[0]["dim"] == 3 and abs(recs[0]["value"] - 80.0) < 1e-3
+    clean = pol(_history_batch(), noise=torch.zeros(4, 10, 32), time=torch.full((4,), 0.5))
+    assert clean["outlier_records"] == []
+    engine = TrainEngine(pol, OptimHyper(lr=1e-4), device=torch.device("cpu"))
+    with caplog.at_level(logging.WARNING):
+        sums = update_policy(engine, [b])
+    assert "outlier_records" not in sums and torch.isfinite(sums["loss"])
+    assert any("normalised state dim 3" in r.getMessage() and "80.0" in r.getMessage() for r in caplog.records)
