@@ -315,11 +315,12 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_
     for (int e = 0; e < 8; ++e) {
       float x = gv[e], a, da;
       if (act == 0) {
+        // s = sigmoid(2u) = 0.5 (1 + tanh u); 1 - tanh^2 u = 4 s (1 - s)
         const float k = 0.7978845608028654f;
-        float inner = k * (x + 0.044715f * x * x * x);
-        float th = tanhf(inner);
-        a = 0.5f * x * (1.f + th);
-        da = 0.5f * (1.f + th) + 0.5f * x * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * x * x);
+        const float inner = k * (x + 0.044715f * x * x * x);
+        const float s = __fdividef(1.f, 1.f + __expf(-2.f * inner));
+        a = x * s;
+        da = s + 2.f * x * s * (1.f - s) * k * (1.f + 3.f * 0.044715f * x * x);
       } else {
         float s = 1.f / (1.f + __expf(-x));
         a = x * s;
@@ -632,15 +633,31 @@ __global__ void ce_bwd_kernel(const float* __restrict__ logits, const long long*
 
 // ------------------------------------------------------------------------------------------ optimizer
 // Sum of squares of a bf16/fp32 gradient buffer into per-block fp32 partials (deterministic two-stage).
+__device__ __forceinline__ void sumsq_load8(const __nv_bfloat16* p, float* v) { load8(p, v); }
+__device__ __forceinline__ void sumsq_load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+// `nvec` groups of 8 elements are read with 128-bit loads (0 when the buffer does not start on a 16-byte boundary);
+// the elements after them one by one.  Fixed grid and fixed per-thread order: the result is deterministic.
 template <typename T>
-__global__ void sumsq_kernel(const T* __restrict__ g, long long n, float* __restrict__ partial) {
+__global__ void sumsq_kernel(const T* __restrict__ g, long long n, long long nvec, float* __restrict__ partial) {
   __shared__ float red[32];
-  float s = 0.f;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    float v = static_cast<float>(g[i]);
-    s += v * v;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec; t += stride) {
+    float v[8];
+    sumsq_load8(g + t * 8, v);
+    s0 += v[0] * v[0] + v[4] * v[4];
+    s1 += v[1] * v[1] + v[5] * v[5];
+    s2 += v[2] * v[2] + v[6] * v[6];
+    s3 += v[3] * v[3] + v[7] * v[7];
   }
-  s = block_sum(s, red);
+  for (long long i = nvec * 8 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v = static_cast<float>(g[i]);
+    s0 += v * v;
+  }
+  float s = block_sum((s0 + s1) + (s2 + s3), red);
   if (threadIdx.x == 0) partial[blockIdx.x] = s;
 }
 // total = sum(partials) (+ extra terms added by the caller); writes the clip coefficient:
@@ -959,8 +976,9 @@ extern "C" int otb_ce_bwd(const float* logits, const long long* labels, const fl
 // nblocks partial sums are written to `partial` (caller provides >= nblocks floats); returns nblocks in *out_n.
 extern "C" int otb_sumsq(const void* g, long long n, int is_bf16, float* partial, int nblocks,
                          cudaStream_t stream) {
-  if (is_bf16) sumsq_kernel<bf16><<<nblocks, 512, 0, stream>>>((const bf16*)g, n, partial);
-  else sumsq_kernel<float><<<nblocks, 512, 0, stream>>>((const float*)g, n, partial);
+  const long long nvec = (reinterpret_cast<uintptr_t>(g) & 15) == 0 ? n / 8 : 0;
+  if (is_bf16) sumsq_kernel<bf16><<<nblocks, 512, 0, stream>>>((const bf16*)g, n, nvec, partial);
+  else sumsq_kernel<float><<<nblocks, 512, 0, stream>>>((const float*)g, n, nvec, partial);
   return (int)cudaGetLastError();
 }
 
