@@ -43,6 +43,11 @@ def parse_args():
     ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3", "pi06"],
                     help="--mode infer only: cosmos3 is the workload of the reference's published B200 latency table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (profiling runs only)")
+    ap.add_argument("--train-vision", action="store_true",
+                    help="train mode: also train the SigLIP tower (no frozen weights at all).  The default keeps the "
+                         "policy config's own default, freeze_vision_encoder=true (reference "
+                         "pi05/configuration_pi05.py:172): backbone, expert and every head train, the tower runs "
+                         "forward only.  With the tower trained the step holds 166 GiB on one GPU at batch 32.")
     ap.add_argument("--kernel-table", default="", metavar="PATH",
                     help="train mode: after the warm-up, trace ONE step with the activity profiler, write the "
                          "per-kernel device-time shares to PATH and exit without a benchmark line")
@@ -106,6 +111,7 @@ def build_policy(args, device):
     feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
     kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=200, discrete_action_max_length=256,
               discrete_action_vocab_size=2048, dropout=0.0, knowledge_insulation=True, device=str(device),
+              freeze_vision_encoder=not args.train_vision, train_expert_only=False,
               input_features=feats, output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
     spec = SyntheticSpec(batch_size=args.batch, num_cams=cams, prompt_len=200, vocab_size=257152, state_dim=32,
                          action_dim=32, chunk_size=50, discrete_action_len=256, discrete_action_vocab=2048,
@@ -390,6 +396,9 @@ def main():
                        "global_batch": global_batch, "seq_len": 3 * 256 + 200 + 3 + 256,
                        "parallelism": f"dp{world}-{engine.strategy}-{engine.comm}", "params": n_params,
                        "knowledge_insulation": True, "fast_tokens": 256, "action_chunk": "50x32",
+                       "frozen_weights": "none" if args.train_vision else "SigLIP tower (policy default "
+                                                                           "freeze_vision_encoder=true)",
+                       "trainable_params": sum(p.numel() for p in policy.parameters() if p.requires_grad),
                        "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; "
                              "no explicit flush", "peak_mem_gib": round(peak_gb, 2)},
             "clocks": clocks,
