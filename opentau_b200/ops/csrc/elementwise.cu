@@ -197,6 +197,78 @@ __global__ void rms_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
   }
 }
 
+// LayerNorm backward.  xhat = (x - mean) * rstd, g = dy * w:
+//   dx = (g - mean(g) - xhat * mean(g * xhat)) * rstd,   dw = sum_rows dy * xhat,   db = sum_rows dy.
+// Same work split as rms_bwd_kernel: a block owns `rows_per_block` consecutive rows and writes one fp32 row of
+// dw_partial[gridDim.x][H] and of db_partial[gridDim.x][H]; colsum_partials_kernel adds them up in a fixed order.
+template <int MAXV>
+__global__ void ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                              const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                              const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                              float* __restrict__ dw_partial, float* __restrict__ db_partial, long long rows, int H,
+                              int rows_per_block) {
+  __shared__ float red[32];
+  const int nvec = H >> 3;
+  float dwacc[MAXV][8], dbacc[MAXV][8], wf[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = dbacc[i][e] = wf[i][e] = 0.f;
+    if (idx < nvec) load8(w + idx * 8, wf[i]);
+  }
+  const long long r0 = (long long)blockIdx.x * rows_per_block;
+  for (long long row = r0; row < min(r0 + (long long)rows_per_block, rows); ++row) {
+    const float mu = mean_in[row], rstd = rstd_in[row];
+    const __nv_bfloat16* xr = x + row * (long long)H;
+    const __nv_bfloat16* dyr = dy + row * (long long)H;
+    float g[MAXV][8], xh[MAXV][8];
+    float sum_g = 0.f, sum_gx = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nvec) {
+        float xv[8], dv[8];
+        load8(xr + idx * 8, xv);
+        load8(dyr + idx * 8, dv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[i][e] = (xv[e] - mu) * rstd;
+          g[i][e] = dv[e] * wf[i][e];
+          sum_g += g[i][e];
+          sum_gx += g[i][e] * xh[i][e];
+          dwacc[i][e] += dv[e] * xh[i][e];
+          dbacc[i][e] += dv[e];
+        }
+      }
+    }
+    const float m1 = block_sum(sum_g, red) / H;
+    const float m2 = block_sum(sum_gx, red) / H;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (g[i][e] - m1 - xh[i][e] * m2) * rstd;
+        store8(dx + row * (long long)H + idx * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      float* ow = dw_partial + (long long)blockIdx.x * H + idx * 8;
+      float* ob = db_partial + (long long)blockIdx.x * H + idx * 8;
+      *reinterpret_cast<float4*>(ow) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      *reinterpret_cast<float4*>(ow + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+      *reinterpret_cast<float4*>(ob) = make_float4(dbacc[i][0], dbacc[i][1], dbacc[i][2], dbacc[i][3]);
+      *reinterpret_cast<float4*>(ob + 4) = make_float4(dbacc[i][4], dbacc[i][5], dbacc[i][6], dbacc[i][7]);
+    }
+  }
+}
+
 // out[c] = sum_r partial[r][c]  (fixed order -> deterministic), cast to bf16; optionally += into out.
 __global__ void colsum_partials_kernel(const float* __restrict__ partial, int nrows, int H,
                                        __nv_bfloat16* __restrict__ out, int accumulate) {
@@ -865,6 +937,17 @@ extern "C" int otb_colsum_bf16(const void* a, long long rows, int H, long long l
   if (H % 8) return -1;
   dim3 grid((H / 8 + 127) / 128, (unsigned)((rows + rows_per_block - 1) / rows_per_block));
   colsum_bf16_kernel<<<grid, 128, 0, stream>>>((const bf16*)a, rows, H, lda, partial, rows_per_block);
+  return (int)cudaGetLastError();
+}
+
+// dw_partial and db_partial each hold nblocks*H floats, nblocks = ceil(rows / rows_per_block); x, dy contiguous rows.
+extern "C" int otb_ln_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                          float* dw_partial, float* db_partial, long long rows, int H, int rows_per_block,
+                          cudaStream_t stream) {
+  if (H % 8 || rows <= 0 || rows_per_block <= 0 || !dw_partial || !db_partial) return -1;
+  dim3 grid((unsigned)((rows + rows_per_block - 1) / rows_per_block));
+  LAUNCH_BY_H(ln_bwd_kernel, H, (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw_partial,
+              db_partial, rows, H, rows_per_block);
   return (int)cudaGetLastError();
 }
 

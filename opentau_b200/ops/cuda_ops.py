@@ -286,6 +286,29 @@ def ln_fwd(x: Tensor, w: Tensor, b: Tensor, eps: float):
     return y.view(x.shape), mean, rstd
 
 
+def ln_bwd(dy: Tensor, x: Tensor, w: Tensor, mean: Tensor, rstd: Tensor):
+    """-> ``dx`` (like x), ``dw``, ``db`` (like w).  One kernel for dx and the per-block weight / bias partials, two
+    fixed-order column sums."""
+    global launch_count
+    x2, R, H = _rows(x)
+    dy2, _, _ = _rows(dy)
+    if x2.stride(0) != H:
+        x2 = x2.contiguous()
+    if dy2.stride(0) != H:
+        dy2 = dy2.contiguous()
+    dx = torch.empty(R, H, dtype=x.dtype, device=x.device)
+    rpb, nb = _bwd_blocks(R)
+    partial = torch.empty(2, nb, H, dtype=torch.float32, device=x.device)
+    lib = _lib.load("elementwise")
+    _check(lib.otb_ln_bwd(_p(dy2), _p(x2), _p(w.to(torch.bfloat16).contiguous()), _p(mean), _p(rstd), _p(dx),
+                          _p(partial[0]), _p(partial[1]), c_longlong(R), c_int(H), c_int(rpb), _stream()), "ln_bwd")
+    out = torch.empty(2, H, dtype=torch.bfloat16, device=x.device)
+    for k in range(2):
+        _check(lib.otb_colsum_partials(_p(partial[k]), c_int(nb), c_int(H), _p(out[k]), c_int(0), _stream()), "colsum")
+    launch_count += 3
+    return dx.view(x.shape), out[0].to(w.dtype), out[1].to(w.dtype)
+
+
 # --------------------------------------------------------------------------------------------- GLU / RoPE
 _ACT = {"gelu_tanh": 0, "silu": 1}
 

@@ -171,6 +171,9 @@ def ln_fwd(x: Tensor, w: Tensor, b: Tensor, eps: float) -> tuple[Tensor, Tensor,
 
 
 def ln_bwd(dy: Tensor, x: Tensor, w: Tensor, mean: Tensor, rstd: Tensor):
+    if _cuda(x) and x.dtype == torch.bfloat16 and dy.dtype == torch.bfloat16:
+        from . import cuda_ops
+        return cuda_ops.ln_bwd(dy, x, w, mean, rstd)
     H = x.shape[-1]
     xf = x.float().reshape(-1, H)
     dyf = dy.float().reshape(-1, H)

@@ -280,6 +280,29 @@ def test_adamw_vector_and_scalar_paths_agree_with_reference(dev, offset, grad_dt
     assert torch.equal(base[0][offset + n:], guard)            # nothing written past the end
 
 
+@pytest.mark.parametrize("rows,H", [(1000, 1152), (37, 64), (600, 4096)])
+def test_layer_norm_backward_kernel(dev, rows, H):
+    """dx, dw, db of the native LayerNorm backward against autograd on the fp32 statement of the same op."""
+    from opentau_b200.ops import cuda_ops
+    torch.manual_seed(rows + H)
+    x = (torch.randn(rows, H, device=dev) * 2 + 0.5).to(torch.bfloat16)
+    w = (torch.randn(H, device=dev) * 0.3 + 1).to(torch.bfloat16)
+    b = (torch.randn(H, device=dev) * 0.1).to(torch.bfloat16)
+    dy = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+    y, mean, rstd = cuda_ops.ln_fwd(x, w, b, 1e-6)
+    dx, dw, db = cuda_ops.ln_bwd(dy, x, w, mean, rstd)
+    xr = x.float().cpu().requires_grad_(True)
+    wr, br = w.float().cpu().requires_grad_(True), b.float().cpu().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (H,), wr, br, 1e-6)
+    yr.backward(dy.float().cpu())
+    torch.testing.assert_close(y.float().cpu(), yr.detach(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dx.float().cpu(), xr.grad, rtol=2e-2, atol=2e-2)
+    scale = max(1.0, rows ** 0.5)
+    torch.testing.assert_close(dw.float().cpu() / scale, wr.grad / scale, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(db.float().cpu() / scale, br.grad / scale, rtol=2e-2, atol=2e-2)
+    assert dx.dtype == x.dtype and dw.shape == (H,) and db.shape == (H,)
+
+
 def test_resize_pad_kernel(dev):
     from opentau_b200 import ops
     from opentau_b200.ops import cuda_ops
