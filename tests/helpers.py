@@ -34,3 +34,12 @@ def tiny_pi05(device="cpu", seed=0, **over) -> PI05Policy:
 
 def tiny_batch(device="cpu", seed=1, **over):
     return make_synthetic_batch(SyntheticSpec(**over), device=device, seed=seed)
+
+
+def free_port() -> int:
+    """A TCP port that is free right now on the loopback interface (the kernel picks it), for rendezvous in
+    multi-process tests: a port derived from the pid can collide with another process or an earlier test."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]

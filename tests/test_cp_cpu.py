@@ -6,6 +6,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from helpers import free_port
+
 from opentau_b200 import ops
 
 
@@ -46,5 +48,5 @@ def _rank_main(rank, world, port, ret):
 def test_context_parallel_attention_matches_unsharded_on_two_ranks():
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(2, 29100 + os.getpid() % 300, ret), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret["err"] < 1e-5

@@ -7,7 +7,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from helpers import tiny_batch, tiny_pi05
+from helpers import tiny_batch, tiny_pi05, free_port
 from opentau_b200.parallel.engine import OptimHyper, TrainEngine, assemble_weighted_loss
 
 
@@ -94,7 +94,7 @@ def _rank_main(rank, world, port, strategy, ret):
 
 @pytest.mark.parametrize("strategy", ["zero2", "ddp"])
 def test_two_rank_gloo_step_keeps_replicas_identical_and_matches_single_rank(strategy):
-    port = 29500 + (os.getpid() % 500) + (0 if strategy == "zero2" else 1)
+    port = free_port()
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_rank_main, args=(2, port, strategy, ret), nprocs=2, join=True)

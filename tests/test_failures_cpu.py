@@ -6,6 +6,7 @@ import json
 import os
 
 import pytest
+from helpers import free_port
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -77,7 +78,7 @@ def _leaver(rank, world, port, ret):
 def test_surviving_rank_gets_an_error_not_a_hang():
     mgr = mp.Manager()
     ret = mgr.dict()
-    ctx = mp.spawn(_leaver, args=(2, 29700 + os.getpid() % 200, ret), nprocs=2, join=False)
+    ctx = mp.spawn(_leaver, args=(2, free_port(), ret), nprocs=2, join=False)
     for p in ctx.processes:
         p.join(timeout=60)
         assert not p.is_alive(), "a rank is still waiting for the one that left"
@@ -105,7 +106,7 @@ def _disagree(rank, world, port, ret):
 def test_branch_decisions_are_made_uniform_before_collectives():
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_disagree, args=(2, 29300 + os.getpid() % 200, ret), nprocs=2, join=True)
+    mp.spawn(_disagree, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret[0] == ret[1] == ([True, False], 1, True, False)
 
 

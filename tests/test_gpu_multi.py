@@ -7,6 +7,7 @@ leaves only between steps with nothing in flight.
 import os
 
 import pytest
+from helpers import free_port
 import torch
 
 pytestmark = pytest.mark.gpu
@@ -54,9 +55,8 @@ def test_peer_memory_step_matches_nccl_step():
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
-    base = 29700 + os.getpid() % 200
-    for i, comm in enumerate(("nccl", "p2p")):
-        mp.spawn(_worker, args=(2, base + i, comm, ret), nprocs=2, join=True)
+    for comm in ("nccl", "p2p"):
+        mp.spawn(_worker, args=(2, free_port(), comm, ret), nprocs=2, join=True)
     assert ret["nccl_same"] and ret["p2p_same"]
     (fa, na), (fb, nb) = ret["nccl"], ret["p2p"]
     n = min(fa.numel(), fb.numel())
@@ -130,7 +130,7 @@ def test_fused_tensor_parallel_layer_matches_unsharded_layer():
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_tp_worker, args=(2, 29900 + os.getpid() % 90, ret), nprocs=2, join=True)
+    mp.spawn(_tp_worker, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret["tp_err"] < 0.03 * max(1.0, ret["tp_scale"])
 
 
@@ -184,5 +184,5 @@ def test_fused_context_parallel_attention_matches_single_gpu():
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_cp_worker, args=(2, 29990 + os.getpid() % 9, ret), nprocs=2, join=True)
+    mp.spawn(_cp_worker, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret["cp_err"] < 0.06

@@ -7,7 +7,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from helpers import TINY, tiny_batch
+from helpers import TINY, tiny_batch, free_port
 from opentau_b200.configs.types import FeatureType, PolicyFeature
 from opentau_b200.datasets.synthetic import identity_stats
 from opentau_b200.models.video_encoder import build_temporal_sinusoidal_pe
@@ -127,7 +127,7 @@ def _branch_worker(rank, world, port, diverge, ret):
 def test_branch_decisions_two_ranks(diverge):
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_branch_worker, args=(2, 29900 + os.getpid() % 90 + int(diverge), diverge, ret), nprocs=2, join=True)
+    mp.spawn(_branch_worker, args=(2, free_port(), diverge, ret), nprocs=2, join=True)
     if diverge:
         assert all(str(ret[r]).startswith("raised") and "metadata" in str(ret[r]) for r in (0, 1))
     else:

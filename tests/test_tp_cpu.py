@@ -8,6 +8,7 @@ import torch.multiprocessing as mp
 
 from opentau_b200 import ops
 from opentau_b200.models.layers import DecoderLayer, TowerConfig
+from helpers import free_port
 
 CFG = dict(hidden_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
            intermediate_size=256, vocab_size=64, hidden_act="silu", qk_norm=True, norm_unit_offset=False)
@@ -64,7 +65,7 @@ def _rank_main(rank, world, port, ret):
 def test_tp_layer_matches_unsharded_layer_on_two_ranks():
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(2, 29300 + os.getpid() % 300, ret), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret["err"] < 1e-4
 
 
@@ -122,5 +123,5 @@ def _cosmos_rank(rank, world, port, ret):
 def test_cosmos3_tensor_parallel_prefix_equals_replicated_backbone():
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_cosmos_rank, args=(2, 29650 + os.getpid() % 300, ret), nprocs=2, join=True)
+    mp.spawn(_cosmos_rank, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret["err"] < 1e-4
