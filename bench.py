@@ -48,6 +48,13 @@ def parse_args():
                          "policy config's own default, freeze_vision_encoder=true (reference "
                          "pi05/configuration_pi05.py:172): backbone, expert and every head train, the tower runs "
                          "forward only.  With the tower trained the step holds 166 GiB on one GPU at batch 32.")
+    ap.add_argument("--dropout", type=float, default=0.1,
+                    help="dropout after the attention output projection and the MLP (reference default 0.1, "
+                         "pi05/configuration_pi05.py:148); printed in the config block")
+    ap.add_argument("--ref-attn", default="sdpa", choices=["eager", "sdpa"],
+                    help="--impl reference: the reference's attention_implementation (its docs recommend sdpa)")
+    ap.add_argument("--ref-compile", default="on", choices=["on", "off"],
+                    help="--impl reference: the reference's use_torch_compile (its pi0.5 default is on)")
     ap.add_argument("--kernel-table", default="", metavar="PATH",
                     help="train mode: after the warm-up, trace ONE step with the activity profiler, write the "
                          "per-kernel device-time shares to PATH and exit without a benchmark line")
@@ -110,7 +117,7 @@ def build_policy(args, device):
     feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, 224, 224)) for i in range(cams)}
     feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
     kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=200, discrete_action_max_length=256,
-              discrete_action_vocab_size=2048, dropout=0.0, knowledge_insulation=True, device=str(device),
+              discrete_action_vocab_size=2048, dropout=args.dropout, knowledge_insulation=True, device=str(device),
               freeze_vision_encoder=not args.train_vision, train_expert_only=False,
               input_features=feats, output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
     spec = SyntheticSpec(batch_size=args.batch, num_cams=cams, prompt_len=200, vocab_size=257152, state_dim=32,
@@ -269,11 +276,12 @@ def write_kernel_table(path: str, step, sync, top: int = 60) -> None:
 def main():
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "reference (opentau 0.13.0) installs only with --no-deps --ignore-requires-python and "
-                          "fails at import: draccus, accelerate, datasets are not in the offline wheelhouse and "
-                          "its HF monkey-patches target transformers 4.57 (image has 5.5)"}))
-        return 0
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        import reference_arm
+        args.clock_sampler = ClockSampler
+        if args.mode == "infer":
+            return reference_arm.run_infer(args)
+        return reference_arm.run_train(args)
     if args.impl == "oracle":
         os.environ["OPENTAU_B200_ORACLE"] = "1"
 
@@ -396,6 +404,7 @@ def main():
                        "global_batch": global_batch, "seq_len": 3 * 256 + 200 + 3 + 256,
                        "parallelism": f"dp{world}-{engine.strategy}-{engine.comm}", "params": n_params,
                        "knowledge_insulation": True, "fast_tokens": 256, "action_chunk": "50x32",
+                       "dropout": args.dropout,
                        "frozen_weights": "none" if args.train_vision else "SigLIP tower (policy default "
                                                                            "freeze_vision_encoder=true)",
                        "trainable_params": sum(p.numel() for p in policy.parameters() if p.requires_grad),

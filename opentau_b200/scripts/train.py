@@ -240,7 +240,7 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
         if not last.exists():
             raise FileNotFoundError(f"resume requested but {last} does not exist")
         last = last.resolve()
-        if not checkpoint_is_complete(last, 1):
+        if not checkpoint_is_complete(last):      # against the world size recorded by the save
             raise RuntimeError(f"checkpoint {last} is incomplete (interrupted save)")
         from safetensors.torch import load_file
         sd = load_file(str(last / "model.safetensors"))
@@ -252,7 +252,12 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
         engine.step_count = step
         logging.info("resumed from %s at step %d", last, step)
 
-    best = RunningBestTracker(out_dir, cfg.running_best_count, cfg.running_best_metric) if cfg.running_best_count else None
+    # success rates are kept highest-first, losses lowest-first (reference scripts/train.py: higher_is_better is
+    # true only for the eval-success metric); "auto" means success when an environment is evaluated in training
+    best_on_success = cfg.running_best_metric in ("success", "eval_success") or (
+        cfg.running_best_metric == "auto" and cfg.env is not None and cfg.eval_freq > 0)
+    best = RunningBestTracker(out_dir, cfg.running_best_count, cfg.running_best_metric,
+                              higher_is_better=best_on_success) if cfg.running_best_count else None
     names = list(train_mix.meta.dataset_names)
     tot_w = float(sum(train_mix.weights)) or 1.0
     head_w: dict[str, float] = {}
@@ -340,24 +345,34 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
                 update_last_checkpoint(ckpt)
                 keep = {ckpt.name}
                 if best is not None:
-                    keep |= best.kept()
+                    keep |= best.kept
                 if cfg.last_checkpoint_only:
                     prune_checkpoints(out_dir, keep)
                 logging.info("checkpoint saved: %s", ckpt)
 
         if best is not None and (is_val or is_eval) and metrics:
-            key = "Success Rate" if "Success Rate" in metrics and cfg.running_best_metric in ("auto", "success") \
-                else "Validation/Loss"
+            key = "Success Rate" if best_on_success else "Validation/Loss"
             if key in metrics:
-                keep_it = control.broadcast_object(best.would_keep(metrics[key]) if is_main else None)
+                # rank 0 decides BEFORE anything is written and every rank follows the broadcast decision: a rank
+                # that looked at the directory instead would skip its own shard once rank 0 had created it
+                decision = None
+                if is_main:
+                    ckpt0 = get_step_checkpoint_dir(out_dir, cfg.steps, step)
+                    decision = (bool(best.would_keep(metrics[key])), not (is_save and ckpt0.exists()))
+                keep_it, need_save = control.broadcast_object(decision)
                 if keep_it:
                     sid = get_step_identifier(step, cfg.steps)
                     ckpt = get_step_checkpoint_dir(out_dir, cfg.steps, step)
-                    if not ckpt.exists():
+                    if need_save:
                         save_checkpoint(ckpt, step, cfg, policy, engine, rank=rank, is_main=is_main)
                     control.wait_for_everyone()
                     if is_main:
+                        if not checkpoint_is_complete(ckpt, world):
+                            raise RuntimeError(f"running-best checkpoint {ckpt} is incomplete after the save barrier")
                         best.update(sid, metrics[key])
+                        if cfg.last_checkpoint_only:
+                            last_name = (ckpt_root / LAST_LINK).resolve().name if (ckpt_root / LAST_LINK).exists() else ""
+                            prune_checkpoints(out_dir, best.kept | {last_name})
 
         if metrics and is_main:
             tracker_wb.log(metrics, step)

@@ -78,15 +78,31 @@ def deserialize_rng_state(d: dict[str, torch.Tensor]) -> None:
     deserialize_torch_rng_state(d)
 
 
-def save_rng_state(save_dir: Path) -> None:
+def rng_state_file(save_dir: Path, rank: int | None = None) -> Path:
+    """``rng_state.safetensors`` (single process) or ``rng_state_rank<r>.safetensors`` (one per rank: every rank
+    draws its own flow-matching noise / time / augmentation stream, so every rank saves and restores its own;
+    the reference keeps one ``random_states_<i>.pkl`` per process, ``utils/train_utils.py:115-132``)."""
+    if rank is None:
+        return Path(save_dir) / RNG_STATE
+    stem, ext = RNG_STATE.rsplit(".", 1)
+    return Path(save_dir) / f"{stem}_rank{rank}.{ext}"
+
+
+def save_rng_state(save_dir: Path, rank: int | None = None) -> None:
     from safetensors.torch import save_file
     save_dir.mkdir(parents=True, exist_ok=True)
-    save_file({k: v.contiguous() for k, v in serialize_rng_state().items()}, str(save_dir / RNG_STATE))
+    save_file({k: v.contiguous() for k, v in serialize_rng_state().items()}, str(rng_state_file(save_dir, rank)))
 
 
-def load_rng_state(save_dir: Path) -> None:
+def load_rng_state(save_dir: Path, rank: int | None = None) -> None:
+    """Restores this rank's stream; raises FileNotFoundError when the checkpoint holds none for it."""
     from safetensors.torch import load_file
-    deserialize_rng_state(load_file(str(save_dir / RNG_STATE)))
+    f = rng_state_file(save_dir, rank)
+    if not f.exists() and rank == 0 and (Path(save_dir) / RNG_STATE).exists():
+        f = Path(save_dir) / RNG_STATE          # checkpoints written before the per-rank files existed
+    if not f.exists():
+        raise FileNotFoundError(str(f))
+    deserialize_rng_state(load_file(str(f)))
 
 
 @contextmanager

@@ -6,7 +6,7 @@ Directory layout (same as the reference, OpenTau ``src/opentau/utils/train_utils
         model.safetensors, config.json          policy weights + policy config
         train_config.json                       the full pipeline config
         training_step.json                      {"step": N}
-        rng_state.safetensors                   python / numpy / torch / cuda RNG
+        rng_state_rank<r>.safetensors           python / numpy / torch / cuda RNG of rank r (one file per rank)
         optimizer_rank<r>.safetensors           this rank's shard of Adam moments (+ fp32 masters)
         flat_layout.json                        parameter name / shape / offset inside the flat groups
         random_states_<r>.marker                one per rank: the completeness tripwire counts them
@@ -59,14 +59,16 @@ def update_last_checkpoint(checkpoint_dir: Path) -> Path:
 
 def save_checkpoint(checkpoint_dir: Path, step: int, cfg, policy, engine=None, rank: int = 0,
                     is_main: bool = True) -> None:
-    """Rank 0 writes the policy / configs / step / RNG; every rank writes its optimizer shard + marker."""
+    """Rank 0 writes the policy / configs / step; every rank writes its RNG state, its optimizer shard and, last,
+    its marker.  Every rank must call this (no rank may decide on its own from the directory's existence)."""
     from safetensors.torch import save_file
     checkpoint_dir.mkdir(parents=True, exist_ok=True)
     if is_main:
         policy.save_pretrained(checkpoint_dir)
         cfg.save_pretrained(checkpoint_dir)
         save_training_step(step, checkpoint_dir)
-        save_rng_state(checkpoint_dir)
+        (checkpoint_dir / "world_size.json").write_text(json.dumps({"world_size": getattr(engine, "world", 1)}))
+    save_rng_state(checkpoint_dir, rank)
     if engine is not None and is_main:
         with open(checkpoint_dir / "flat_layout.json", "w") as f:
             json.dump(engine.store.layout(), f)
@@ -78,8 +80,18 @@ def save_checkpoint(checkpoint_dir: Path, step: int, cfg, policy, engine=None, r
     (checkpoint_dir / f"random_states_{rank}.marker").write_text(str(step))
 
 
-def checkpoint_is_complete(checkpoint_dir: Path, world_size: int) -> bool:
-    """Tripwire for interrupted saves: one marker per rank must exist."""
+def saved_world_size(checkpoint_dir: Path) -> int:
+    """World size the checkpoint was written with (1 for checkpoints that predate the record)."""
+    f = Path(checkpoint_dir) / "world_size.json"
+    if f.exists():
+        return int(json.loads(f.read_text())["world_size"])
+    return max(1, len(list(Path(checkpoint_dir).glob("optimizer_rank*.safetensors"))))
+
+
+def checkpoint_is_complete(checkpoint_dir: Path, world_size: int | None = None) -> bool:
+    """Tripwire for interrupted saves: one marker per rank of the SAVING job must exist."""
+    if world_size is None:
+        world_size = saved_world_size(checkpoint_dir)
     return len(list(checkpoint_dir.glob("random_states_*.marker"))) >= world_size
 
 
@@ -91,9 +103,13 @@ def load_training_state(checkpoint_dir: Path, engine=None, rank: int = 0, world_
     from safetensors import safe_open
     step = load_training_step(checkpoint_dir)
     try:
-        load_rng_state(checkpoint_dir)
+        load_rng_state(checkpoint_dir, rank)
     except FileNotFoundError:
-        logging.warning("no RNG state in %s; continuing with the current RNG", checkpoint_dir)
+        # a rank the checkpoint never had (world grew) or a checkpoint without RNG files: a fresh, rank-specific,
+        # step-specific stream -- never another rank's
+        logging.warning("no RNG state for rank %d in %s; reseeding from (seed, step, rank)", rank, checkpoint_dir)
+        if seed is not None:
+            set_seed(seed + step, rank)
     if engine is not None:
         f = checkpoint_dir / f"optimizer_rank{rank}.safetensors"
         saved_world = len(list(checkpoint_dir.glob("optimizer_rank*.safetensors")))
@@ -111,8 +127,6 @@ def load_training_state(checkpoint_dir: Path, engine=None, rank: int = 0, world_
                             "the live weights and restarting Adam moments", saved_world, world_size)
             engine.step_count = step
             engine.rebuild_masters_from_live()
-            if seed is not None and rank >= saved_world:
-                set_seed(seed + step, rank)
     return step
 
 

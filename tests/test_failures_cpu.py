@@ -115,3 +115,38 @@ def test_metrics_file_survives_a_crash_between_steps(tmp_path):
     out, _ = _trained(tmp_path)
     lines = (out / "metrics.jsonl").read_text().splitlines()
     assert lines and all(json.loads(x)["step"] for x in lines)
+
+
+def _rng_rank(rank, world, port, ckdir, q):
+    import os
+    import torch
+    import torch.distributed as dist
+    from pathlib import Path
+    from opentau_b200.utils.random_utils import load_rng_state, save_rng_state, set_seed
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    set_seed(11, rank)
+    torch.rand(3)                                   # advance the stream a little
+    save_rng_state(Path(ckdir), rank)
+    expected = torch.rand(4)                        # what the uninterrupted run would draw next
+    dist.barrier()
+    set_seed(999, 0)                                # a restarted process: every rank starts from the same state
+    load_rng_state(Path(ckdir), rank)
+    q.put((rank, expected.tolist(), torch.rand(4).tolist()))
+    dist.destroy_process_group()
+
+
+def test_every_rank_resumes_its_own_rng_stream(tmp_path):
+    """After a resume the ranks must not share one stream (identical noise / time draws on every rank) and each
+    must continue exactly where it stopped."""
+    import torch.multiprocessing as mp
+    from helpers import free_port
+    ctx = mp.get_context("spawn")
+    q, port = ctx.Queue(), free_port()
+    procs = [ctx.Process(target=_rng_rank, args=(r, 2, port, str(tmp_path), q)) for r in range(2)]
+    [p.start() for p in procs]
+    got = sorted(q.get(timeout=120) for _ in procs)
+    [p.join(30) for p in procs]
+    assert got[0][1] == got[0][2] and got[1][1] == got[1][2]      # each rank continues its own stream
+    assert got[0][2] != got[1][2]                                  # and the two streams differ
+    assert (tmp_path / "rng_state_rank0.safetensors").exists() and (tmp_path / "rng_state_rank1.safetensors").exists()

@@ -73,3 +73,25 @@ def test_train_on_a_recorded_lerobot_dataset(tmp_path):
         "use_policy_training_preset": True}
     out = train(TrainPipelineConfig.from_dict(raw))
     assert out["loss"] == out["loss"] and out["grad_norm"] > 0
+
+
+def test_running_best_checkpoints_are_kept_and_complete(tmp_path):
+    """Periodic saves with a running-best tracker: the best validation steps survive pruning next to the last one,
+    every kept checkpoint carries its rank marker and optimizer shard, and the tracker orders losses lowest-first."""
+    from opentau_b200.utils.train_utils import RunningBestTracker, checkpoint_is_complete
+    out = tmp_path / "run"
+    torch.manual_seed(0)
+    train(_cfg(out, 8, running_best_count=1))
+    ck = out / "checkpoints"
+    best = json.loads((ck / "running_best.json").read_text())
+    assert best["higher_is_better"] is False and len(best["entries"]) == 1
+    kept = ck / best["entries"][0]["step"]
+    assert kept.is_dir() and checkpoint_is_complete(kept, 1) and (kept / "optimizer_rank0.safetensors").exists()
+    assert (kept / "rng_state_rank0.safetensors").exists()
+    assert (ck / "last").resolve().name == "000008"
+    # a success-rate tracker keeps the HIGHEST values
+    t = RunningBestTracker(tmp_path / "t", 2, "eval_success", higher_is_better=True)
+    for sid, v in (("a", 0.2), ("b", 0.9), ("c", 0.5)):
+        if t.would_keep(v):
+            t.update(sid, v)
+    assert t.kept == {"b", "c"}
