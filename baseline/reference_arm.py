@@ -19,6 +19,7 @@ disclosed in the printed line:
 
 from __future__ import annotations
 
+import contextlib
 import json
 import os
 import sys
@@ -225,18 +226,30 @@ def run_train(args) -> int:
     h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
     weights = {"MSE": 1.0, "CE": 1.0}
 
+    accum = max(1, int(getattr(args, "ref_accum", 1)))   # the reference's gradient_accumulation_steps
+    micro = B // accum
+
     def step(batch):
-        losses = model(batch) if world > 1 else policy.forward(batch)
-        losses.pop("outlier_records", None)
-        # scripts/train.py: _assemble_weighted_loss with the default loss_weighting {"MSE": 1, "CE": 1}, summed in
-        # the fixed (MSE, CE) order (importing that script would pull the whole launcher stack)
-        loss = weights["MSE"] * losses["MSE"] + weights["CE"] * losses["CE"]
-        loss.backward()
+        """One optimizer step over ``accum`` micro-batches (accelerate's ``accumulate``: gradients are synchronised
+        on the last micro-batch only, the loss is divided by the number of micro-batches)."""
+        total = None
+        for a in range(accum):
+            mb = batch if accum == 1 else {k: v[a * micro:(a + 1) * micro] for k, v in batch.items()}
+            last = a == accum - 1
+            ctx = model.no_sync() if (world > 1 and not last) else contextlib.nullcontext()
+            with ctx:
+                losses = model(mb) if world > 1 else policy.forward(mb)
+                losses.pop("outlier_records", None)
+                # scripts/train.py: _assemble_weighted_loss with the default loss_weighting {"MSE": 1, "CE": 1},
+                # summed in the fixed (MSE, CE) order (importing that script would pull the whole launcher stack)
+                loss = weights["MSE"] * losses["MSE"] + weights["CE"] * losses["CE"]
+                (loss / accum if accum > 1 else loss).backward()
+            total = loss.detach() if total is None else total + loss.detach()
         optimizer.clip_grad_norm_(10.0)
         optimizer.step()
         optimizer.zero_grad()
         scheduler.step()
-        return loss
+        return total / accum
 
     def to_device(hb, non_blocking):
         b = {k: v.to(device, non_blocking=non_blocking) for k, v in hb.items()}
@@ -285,6 +298,7 @@ def run_train(args) -> int:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), res
 
+    failure = None
     try:
         t_first = time.perf_counter()
         run_device_only(1)
@@ -295,18 +309,29 @@ def run_train(args) -> int:
     except Exception as exc:
         import traceback
         traceback.print_exc(file=sys.stderr)
-        if compile_on:
-            # the reference's default (use_torch_compile) does not build on this image: fall back to its eager path
-            args.ref_compile, args.compile_error = "off", f"{type(exc).__name__}: {str(exc)[:160]}"
-            policy = model = optimizer = inner = scheduler = dev_batches = None  # noqa: F841  (drops the closures' cells)
-            import gc
-            torch._dynamo.reset()
-            gc.collect()
-            if use_cuda:
-                torch.cuda.empty_cache()
-            return run_train(args)
-        return _unavailable(f"reference training step failed on this image (attention={attn}, compile={compile_on}): "
-                            f"{type(exc).__name__}: {str(exc)[:200]}")
+        failure = (type(exc).__name__, str(exc)[:160])
+    if failure is not None:
+        # outside the except block, so the failed step's frames (and their activations) are gone before the retry
+        oom = "OutOfMemory" in failure[0]
+        retry = None
+        if compile_on and not oom:
+            # the reference's default (use_torch_compile) does not build on this image: its eager path
+            retry = dict(ref_compile="off", compile_error=f"{failure[0]}: {failure[1]}")
+        elif oom and accum < 4 and B % (accum * 2) == 0:
+            # batch 32 does not fit in one pass of the reference: its own lever, gradient_accumulation_steps
+            retry = dict(ref_accum=accum * 2, oom_at=getattr(args, "oom_at", []) + [f"micro-batch {micro}"])
+        if retry is None:
+            return _unavailable(f"reference training step failed on this image (attention={attn}, "
+                                f"compile={compile_on}, micro-batch {micro}): {failure[0]}: {failure[1]}")
+        for k, v in retry.items():
+            setattr(args, k, v)
+        policy = model = optimizer = inner = scheduler = dev_batches = None  # noqa: F841  (drops the closures' cells)
+        import gc
+        torch._dynamo.reset()
+        gc.collect()
+        if use_cuda:
+            torch.cuda.empty_cache()
+        return run_train(args)
 
     sampler = args.clock_sampler(local_rank) if (rank == 0 and use_cuda) else None
     if sampler:
@@ -329,11 +354,14 @@ def run_train(args) -> int:
                        "optimizer": "MasterWeightOptimizer(AdamW fused) + clip 10", "attention_implementation": attn,
                        "use_torch_compile": compile_on, "dropout": args.dropout,
                        **({"torch_compile_failed": args.compile_error} if getattr(args, "compile_error", None) else {}),
+                       "gradient_accumulation_steps": accum, "micro_batch": micro,
+                       **({"out_of_memory_at": args.oom_at} if getattr(args, "oom_at", None) else {}),
                        "knowledge_insulation": True, "fast_tokens": fast_len,
                        "frozen_weights": "none" if args.train_vision else "SigLIP tower (policy default)",
                        "first_step_s": round(first_step_s, 1), "peak_mem_gib": round(peak_gb, 2),
                        "l2": "per-step working set far exceeds the 126 MB L2; no explicit flush"},
             "reference_shims": shims,
+            "env": {k: os.environ.get(k) for k in ("PYTORCH_CUDA_ALLOC_CONF", "CXX", "CC", "FIND_UNUSED_PARAMS")},
             "tokenizer_assets": "synthetic (hub tokenizers unavailable offline): uniform-random ids, 200 prompt + "
                                 "256 FAST tokens",
             "clocks": clocks,

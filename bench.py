@@ -35,13 +35,15 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "oracle"])
-    ap.add_argument("--batch", type=int, default=32, help="per-GPU batch size")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="per-GPU batch size (default: 32 for pi0.5, 16 for pi0.6: the baseline configs)")
     ap.add_argument("--comm", default="auto", choices=["auto", "p2p", "nccl"])
     ap.add_argument("--strategy", default="zero2")
     ap.add_argument("--tiny", action="store_true", help="small geometry (plumbing check, not a benchmark)")
     ap.add_argument("--mode", default="train", choices=["train", "infer"])
     ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3", "pi06"],
-                    help="--mode infer only: cosmos3 is the workload of the reference's published B200 latency table")
+                    help="train mode: pi05 (headline) or pi06; infer mode: also cosmos3, the workload of the "
+                         "reference's published B200 latency table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (profiling runs only)")
     ap.add_argument("--train-vision", action="store_true",
                     help="train mode: also train the SigLIP tower (no frozen weights at all).  The default keeps the "
@@ -53,12 +55,18 @@ def parse_args():
                          "pi05/configuration_pi05.py:148); printed in the config block")
     ap.add_argument("--ref-attn", default="sdpa", choices=["eager", "sdpa"],
                     help="--impl reference: the reference's attention_implementation (its docs recommend sdpa)")
+    ap.add_argument("--ref-accum", type=int, default=1,
+                    help="--impl reference: its gradient_accumulation_steps (doubled automatically when a pass of "
+                         "the full per-GPU batch runs out of memory)")
     ap.add_argument("--ref-compile", default="on", choices=["on", "off"],
                     help="--impl reference: the reference's use_torch_compile (its pi0.5 default is on)")
     ap.add_argument("--kernel-table", default="", metavar="PATH",
                     help="train mode: after the warm-up, trace ONE step with the activity profiler, write the "
                          "per-kernel device-time shares to PATH and exit without a benchmark line")
-    return ap.parse_args()
+    a = ap.parse_args()
+    if a.batch is None:
+        a.batch = 16 if a.model == "pi06" else 32
+    return a
 
 
 class ClockSampler:
@@ -106,7 +114,53 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def build_policy_pi06(args, device):
+    """pi0.6 training geometry: Gemma-3-4B backbone (34 layers, width 2560, 8 heads / 4 KV heads, head dim 256, MLP
+    10240), SigLIP at 448x448 pooled to 256 tokens per camera, 3 cameras, the 1280-wide 34-layer action expert,
+    256 prompt tokens, state 32, action chunk 50x32, knowledge insulation + 256 FAST tokens like pi0.5
+    (reference ``policies/pi06/configuration_pi06.py:38-276``)."""
+    import torch
+    from opentau_b200.configs.types import FeatureType, PolicyFeature
+    from opentau_b200.datasets.synthetic import SyntheticSpec, identity_stats
+    from opentau_b200.policies.pi06.configuration_pi06 import PI06Config
+    from opentau_b200.policies.pi06.modeling_pi06 import PI06Policy
+    cams = 3
+    res = (224, 224) if args.tiny else (448, 448)
+    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, *res)) for i in range(cams)}
+    feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
+    kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=256, discrete_action_max_length=256,
+              discrete_action_vocab_size=2048, dropout=args.dropout, knowledge_insulation=True, device=str(device),
+              freeze_vision_encoder=not args.train_vision, train_expert_only=False, resize_imgs_with_padding=res,
+              input_features=feats, output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
+    vocab = 262208
+    spec = SyntheticSpec(batch_size=args.batch, num_cams=cams, resolution=res, prompt_len=256, vocab_size=vocab,
+                         state_dim=32, action_dim=32, chunk_size=50, discrete_action_len=256,
+                         discrete_action_vocab=2048, image_dtype=torch.bfloat16)
+    if args.tiny:
+        kw.update(vlm=dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=64, intermediate_size=1024, vocab_size=1024, sliding_window_pattern=2),
+                  expert=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                              head_dim=64, intermediate_size=512, vocab_size=1024),
+                  vision=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4),
+                  vlm_config={"tokens_per_image_side": 8}, discrete_action_vocab_size=256, proj_width=128)
+        spec.vocab_size, spec.discrete_action_vocab = 1024, 256
+    cfg = PI06Config(**kw)
+    torch.manual_seed(1234)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)       # 5.6 B parameters: build them in bf16, not fp32 first
+    try:
+        with torch.device(device):
+            policy = PI06Policy(cfg, per_dataset_stats=[identity_stats()])
+    finally:
+        torch.set_default_dtype(prev)
+    policy.to(torch.bfloat16)
+    policy.train()
+    return policy, spec, cfg
+
+
 def build_policy(args, device):
+    if args.model == "pi06":
+        return build_policy_pi06(args, device)
     import torch
     from opentau_b200.configs.types import FeatureType, PolicyFeature
     from opentau_b200.datasets.synthetic import SyntheticSpec, identity_stats
@@ -276,6 +330,12 @@ def write_kernel_table(path: str, step, sync, top: int = 60) -> None:
 def main():
     args = parse_args()
     if args.impl == "reference":
+        # the reference's launcher default (scripts/launch.py:27-34); must be set before CUDA is initialised
+        os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+        # torch.compile (the reference's default for pi0.5) builds host code with OpenMP; the image's CXX points
+        # at a compiler wrapper without libgomp.spec, the system compiler has it
+        if os.path.exists("/usr/bin/g++") and os.path.exists("/usr/bin/gcc"):
+            os.environ["CXX"], os.environ["CC"] = "/usr/bin/g++", "/usr/bin/gcc"
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
         import reference_arm
         args.clock_sampler = ClockSampler
@@ -363,9 +423,12 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), res
 
-    run_device_only(args.warmup)
+    first = engine.train_step(dev_batches[0])
+    first_grad_norm = float(first["grad_norm"])      # same seeds and batches for every --comm: comparable across runs
+    run_device_only(args.warmup - 1)
     if use_cuda and args.impl == "ours":
         cuda_ops.check_status()
+        engine.check()
     if args.kernel_table:
         if rank == 0:
             write_kernel_table(args.kernel_table, lambda: run_device_only(1), sync)
@@ -388,6 +451,16 @@ def main():
     clocks = sampler.stop() if (rank == 0 and use_cuda) else {}
     if use_cuda and args.impl == "ours":
         cuda_ops.check_status()
+        engine.check()
+    # cross-rank evidence that the replicas stayed identical through the timed region
+    checksum = torch.zeros(1, dtype=torch.float64, device=device)
+    for g in engine.store.groups:
+        checksum += g.data.double().sum()
+    sums = [checksum.clone() for _ in range(world)]
+    if world > 1:
+        dist.all_gather(sums, checksum)
+    sums = [float(x.item()) for x in sums]
+    replicas_equal = all(x == sums[0] for x in sums)
 
     global_batch = args.batch * world
     value = global_batch * args.steps / (ms_dev / 1e3)
@@ -395,13 +468,16 @@ def main():
     if rank == 0:
         peak_gb = torch.cuda.max_memory_allocated() / 2**30 if use_cuda else 0.0
         print(json.dumps({
-            "metric": "pi0.5 train samples/s/box", "value": round(value, 3), "unit": "samples/s",
+            "metric": f"{'pi0.6' if args.model == 'pi06' else 'pi0.5'} train samples/s/box", "value": round(value, 3),
+            "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
-            "config": {"model": "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"
-                       if not args.tiny else "pi0.5 tiny (plumbing)",
-                       "global_batch": global_batch, "seq_len": 3 * 256 + 200 + 3 + 256,
+            "config": {"model": ("tiny (plumbing)" if args.tiny else
+                                 "pi0.6 (SigLIP-So400m/14@448 x3 cams pooled to 256 tokens each, Gemma-3-4B, 1280-wide "
+                                 "34-layer expert)" if args.model == "pi06" else
+                                 "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"),
+                       "global_batch": global_batch, "seq_len": 3 * 256 + spec.prompt_len + 3 + 256,
                        "parallelism": f"dp{world}-{engine.strategy}-{engine.comm}", "params": n_params,
                        "knowledge_insulation": True, "fast_tokens": 256, "action_chunk": "50x32",
                        "dropout": args.dropout,
@@ -414,6 +490,9 @@ def main():
             "e2e": {"value": round(e2e_value, 3), "unit": "samples/s", "ms_per_step": round(ms_e2e / args.steps, 3),
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": last_loss},
             "gpu_launches": launches,
+            "checks": {"replicas_equal": replicas_equal, "param_checksum": sums[0],
+                       "first_step_grad_norm": round(first_grad_norm, 4),
+                       "overlap_grad_reduce": bool(getattr(engine, "overlap", False))},
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -5,8 +5,9 @@
 // loads and stores.  On top of that:
 //
 //   barrier           flag exchange with release/acquire at system scope
-//   reduce_scatter    this rank's shard of the gradient = sum over ranks (peer LOADS), bf16 -> fp32,
-//                     plus block partials of the squared norm
+//   reduce_scatter    this rank's slice of one gradient bucket = sum over ranks (peer LOADS), bf16 / fp32 -> fp32,
+//                     plus block partials of the squared norm; launched per bucket on a side stream as soon as the
+//                     bucket's last weight-gradient product has been issued, so it runs under the rest of backward
 //   norm_exchange     all-gather of the per-rank squared norms through peer STORES, clip coefficient
 //   adamw_allgather   fused AdamW on the fp32 master shard, result written as bf16 into EVERY rank's
 //                     parameter buffer (peer stores) -- the all-gather costs no extra pass
@@ -52,22 +53,50 @@ __global__ void barrier_kernel(PeerTable flags, int rank, int world, int slot, i
   }
 }
 
+// Eight consecutive elements of a bf16 / fp32 buffer as floats (16-byte loads).
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 t;
+  t = unpack_bf16(u.x); f[0] = t.x; f[1] = t.y;
+  t = unpack_bf16(u.y); f[2] = t.x; f[3] = t.y;
+  t = unpack_bf16(u.z); f[4] = t.x; f[5] = t.y;
+  t = unpack_bf16(u.w); f[6] = t.x; f[7] = t.y;
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* f);
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* f) {
+  uint4 o;
+  o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]); o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* f) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+
 // out32[i] = sum_r grad_r[lo + i]; partial[blockIdx.x] = sum of squares of this block's outputs.
+// A wait that gave up earlier in this step left a record in `status`: the peers' buffers cannot be trusted then, so
+// the kernel writes nothing (the optimizer kernel behind it does the same and the parameters stay as they were).
+template <typename T>
 __global__ void reduce_scatter_kernel(PeerTable grads, int world, long long lo, long long n,
-                                      float* __restrict__ out32, float* __restrict__ partial) {
+                                      float* __restrict__ out32, float* __restrict__ partial,
+                                      const KernelStatus* status) {
   __shared__ float red[32];
+  if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
   float ss = 0.f;
   const long long nvec = n >> 3;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
        t += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = 0; r < world; ++r) {
-      const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.ptr[r]) + lo + t * 8);
-      float2 f;
-      f = unpack_bf16(u.x); acc[0] += f.x; acc[1] += f.y;
-      f = unpack_bf16(u.y); acc[2] += f.x; acc[3] += f.y;
-      f = unpack_bf16(u.z); acc[4] += f.x; acc[5] += f.y;
-      f = unpack_bf16(u.w); acc[6] += f.x; acc[7] += f.y;
+      float f[8];
+      load8<T>(static_cast<const T*>(grads.ptr[r]) + lo + t * 8, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += acc[e] * acc[e];
@@ -98,6 +127,8 @@ __global__ void norm_exchange_kernel(const float* __restrict__ partial, int n_pa
                                      KernelStatus* status) {
   __shared__ float red[32];
   __shared__ float total_s;
+  // a wait already gave up in this step: do not start another full-length wait on the same peers
+  if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
   float s = 0.f;
   for (int i = threadIdx.x; i < n_partial; i += blockDim.x) s += partial[i];
 #pragma unroll
@@ -138,11 +169,14 @@ __global__ void norm_exchange_kernel(const float* __restrict__ partial, int n_pa
   }
 }
 
-// AdamW on the shard, then the new bf16 values are stored into every rank's parameter buffer.
+// AdamW on the shard, then the new values are stored (in the parameters' own dtype) into every rank's parameter
+// buffer.  Writes nothing when a wait gave up earlier in this step (see reduce_scatter_kernel).
+template <typename T>
 __global__ void adamw_allgather_kernel(float* __restrict__ p32, const float* __restrict__ g32, float* __restrict__ m,
                                        float* __restrict__ v, PeerTable params, int world, long long lo, long long n,
                                        float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
-                                       const float* __restrict__ scale_ptr) {
+                                       const float* __restrict__ scale_ptr, const KernelStatus* status) {
+  if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
   const float gs = scale_ptr[0];
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
   const long long nvec = n >> 3;
@@ -172,13 +206,7 @@ __global__ void adamw_allgather_kernel(float* __restrict__ p32, const float* __r
       *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
       *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
     }
-    uint4 o;
-    o.x = pack_bf16(pn[0], pn[1]);
-    o.y = pack_bf16(pn[2], pn[3]);
-    o.z = pack_bf16(pn[4], pn[5]);
-    o.w = pack_bf16(pn[6], pn[7]);
-    for (int r = 0; r < world; ++r)
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.ptr[r]) + lo + t * 8) = o;
+    for (int r = 0; r < world; ++r) store8<T>(static_cast<T*>(params.ptr[r]) + lo + t * 8, pn);
   }
 }
 
@@ -220,10 +248,20 @@ extern "C" int otb_comm_barrier(void* const* flag_ptrs, int rank, int world, int
   return (int)cudaGetLastError();
 }
 
+// elem_bytes: 2 = bf16 gradients, 4 = fp32 gradients.
 extern "C" int otb_comm_reduce_scatter(void* const* grad_ptrs, int world, long long lo, long long n, float* out32,
-                                       float* partial, int nblocks, cudaStream_t stream) {
-  if (world < 1 || world > MAX_RANKS || (n % 8) || (lo % 8)) return -1;
-  reduce_scatter_kernel<<<nblocks, 512, 0, stream>>>(table_from(grad_ptrs, world), world, lo, n, out32, partial);
+                                       float* partial, int nblocks, int elem_bytes, void* status,
+                                       cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || (lo % 8) || nblocks < 1) return -1;
+  const KernelStatus* st = static_cast<const KernelStatus*>(status);
+  if (elem_bytes == 2)
+    reduce_scatter_kernel<__nv_bfloat16><<<nblocks, 512, 0, stream>>>(table_from(grad_ptrs, world), world, lo, n,
+                                                                       out32, partial, st);
+  else if (elem_bytes == 4)
+    reduce_scatter_kernel<float><<<nblocks, 512, 0, stream>>>(table_from(grad_ptrs, world), world, lo, n, out32,
+                                                               partial, st);
+  else
+    return -1;
   return (int)cudaGetLastError();
 }
 
@@ -241,9 +279,18 @@ extern "C" int otb_comm_norm_exchange(const float* partial, int n_partial, void*
 extern "C" int otb_comm_adamw_allgather(float* p32, const float* g32, float* m, float* v, void* const* param_ptrs,
                                         int world, long long lo, long long n, float lr, float beta1, float beta2,
                                         float eps, float wd, float bc1, float bc2, const float* scale_ptr,
-                                        int nblocks, cudaStream_t stream) {
-  if (world < 1 || world > MAX_RANKS || (n % 8) || (lo % 8)) return -1;
-  adamw_allgather_kernel<<<nblocks, 512, 0, stream>>>(p32, g32, m, v, table_from(param_ptrs, world), world, lo, n, lr,
-                                                      beta1, beta2, eps, wd, bc1, bc2, scale_ptr);
+                                        int nblocks, int elem_bytes, void* status, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || (lo % 8) || nblocks < 1) return -1;
+  const KernelStatus* st = static_cast<const KernelStatus*>(status);
+  if (elem_bytes == 2)
+    adamw_allgather_kernel<__nv_bfloat16><<<nblocks, 512, 0, stream>>>(p32, g32, m, v, table_from(param_ptrs, world),
+                                                                        world, lo, n, lr, beta1, beta2, eps, wd, bc1,
+                                                                        bc2, scale_ptr, st);
+  else if (elem_bytes == 4)
+    adamw_allgather_kernel<float><<<nblocks, 512, 0, stream>>>(p32, g32, m, v, table_from(param_ptrs, world), world,
+                                                                lo, n, lr, beta1, beta2, eps, wd, bc1, bc2, scale_ptr,
+                                                                st);
+  else
+    return -1;
   return (int)cudaGetLastError();
 }

@@ -17,6 +17,21 @@ from torch import Tensor
 from . import prims
 
 
+# Called with a parameter every time a backward pass has QUEUED the last kernel that writes that parameter's
+# ``main_grad`` for one use of the parameter.  The training engine hangs its bucketed gradient reduction on it.
+_grad_ready_hook = None
+
+
+def set_grad_ready_hook(fn) -> None:
+    global _grad_ready_hook
+    _grad_ready_hook = fn
+
+
+def _notify(pref) -> None:
+    if _grad_ready_hook is not None:
+        _grad_ready_hook(pref)
+
+
 def _flat2d(x: Tensor) -> Tensor:
     return x.reshape(-1, x.shape[-1])
 
@@ -26,6 +41,7 @@ def _sink_wgrad(wref, a: Tensor, b: Tensor):
     mg = getattr(wref, "main_grad", None)
     if mg is not None:
         prims.mm_tn(a, b, out=mg, accumulate=True)
+        _notify(wref)
         return None
     return prims.mm_tn(a, b)
 
@@ -34,6 +50,7 @@ def _sink_vec(pref, g: Tensor):
     mg = getattr(pref, "main_grad", None)
     if mg is not None:
         mg.add_(g.to(mg.dtype))
+        _notify(pref)
         return None
     return g
 
@@ -232,6 +249,7 @@ class LinearCEFn(torch.autograd.Function):
         mg = getattr(ctx.wref, "main_grad", None)
         if mg is not None:
             mg.add_(dw.to(mg.dtype))
+            _notify(ctx.wref)
             dw = None
         if db is not None:
             db = _sink_vec(ctx.bref, db)

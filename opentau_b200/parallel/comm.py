@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 MAX_RANKS = 8
-N_SLOTS = 4
+N_SLOTS = 4            # flag slots of a communicator before a parameter store registers its buckets
 DEFAULT_WAIT_BUDGET = 20_000_000_000  # cycles (~10 s): a peer that is this late is treated as failed
 
 
@@ -73,6 +73,22 @@ class SymmetricBuffer:
 
 
 class PeerComm:
+    """Flag protocol (all waits bounded, every flag carries the step's epoch):
+
+    * slot ``b`` (one per gradient bucket): "my gradients of bucket b are complete".  A rank signals it behind the
+      last weight-gradient product of the bucket and waits for every peer's signal before it reads their buckets.
+    * slot ``NB``: the squared-norm exchange;  slot ``NB + 1``: "my parameter stores have landed and I no longer
+      read anybody's gradients" (end of the step).
+
+    A wait that gives up records ``{kernel, slot, peer}`` in the status word.  From then on the data kernels of the
+    step write nothing (they test the word first), so a late or dead peer can stall a step but cannot make this
+    rank average half-written gradients into its weights; ``check()`` turns the record into an exception.
+    """
+
+    OVERLAP_BLOCKS = 48      # CTAs of a reduce-scatter that runs under the backward pass (leaves the SMs to the GEMMs)
+    FLUSH_BLOCKS = 512       # CTAs of a reduce-scatter / optimizer kernel that runs alone
+    PARTIALS_PER_BUCKET = 512
+
     def __init__(self, device: torch.device, group=None, wait_budget: int = DEFAULT_WAIT_BUDGET):
         from ..ops import _lib
         self.lib = _lib.load("comm_p2p")
@@ -87,7 +103,10 @@ class PeerComm:
         self.flags = SymmetricBuffer(self.lib, 4 * MAX_RANKS * N_SLOTS, self.device, group)
         self.norms = SymmetricBuffer(self.lib, 4 * MAX_RANKS, self.device, group)
         self.epoch = 0
-        self.groups: list[dict] = []
+        self.buckets: list[dict] = []
+        self._reduced: set[int] = set()
+        self._pending_check = None
+        self.side = torch.cuda.Stream(device=self.device)
         dist.barrier(group=group)
 
     # -- allocation hook for FlatParamStore -----------------------------------------------------------
@@ -100,18 +119,27 @@ class PeerComm:
         return t
 
     def register(self, store, shards) -> None:
-        """Remembers, per flat group, the symmetric tables of the parameter and gradient buffers."""
+        """Remembers, per gradient bucket, the symmetric tables of its group's parameter and gradient buffers and
+        where this rank's slice of it lives inside the local fp32 shard arrays."""
         from ..ops import cuda_ops
         self.status = cuda_ops.status_pointer()
+        nb = len(store.buckets)
+        if nb + 2 > N_SLOTS:    # one flag slot per bucket + norm exchange + end of step
+            self.flags = SymmetricBuffer(self.lib, 4 * MAX_RANKS * (nb + 2), self.device, self.group)
+        self.slot_norm, self.slot_end = nb, nb + 1
+        ppb = self.PARTIALS_PER_BUCKET
+        self.partial = torch.zeros(nb * ppb, dtype=torch.float32, device=self.device)
         for g, sh in zip(store.groups, shards):
-            if g.dtype != torch.bfloat16:
-                raise NotImplementedError("the peer-memory step handles bf16 parameter groups")
-            n = sh.hi - sh.lo
-            self.groups.append(dict(
-                group=g, shard=sh, params=g.data._symm, grads=g.grad._symm,
-                g32=torch.empty(n, dtype=torch.float32, device=self.device),
-                partial=torch.zeros(1024, dtype=torch.float32, device=self.device)))
+            if g.dtype not in (torch.bfloat16, torch.float32):
+                raise NotImplementedError(f"peer-memory step: unsupported parameter dtype {g.dtype}")
+            sh.g32 = torch.empty(sh.numel, dtype=torch.float32, device=self.device)
+            for b, (lo, hi), off in zip(g.buckets, sh.slices, sh.offsets):
+                self.buckets.append(dict(bucket=b, shard=sh, lo=lo, n=hi - lo, off=off, params=g.data._symm,
+                                         grads=g.grad._symm, elem=g.data.element_size(),
+                                         partial=self.partial[b.index * ppb:(b.index + 1) * ppb]))
+        self.buckets.sort(key=lambda d: d["bucket"].index)
         self.scale = torch.ones(2, dtype=torch.float32, device=self.device)
+        dist.barrier(group=self.group)
 
     def _stream(self) -> c_void_p:
         return c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -125,37 +153,85 @@ class PeerComm:
             raise RuntimeError(f"peer barrier launch failed ({rc})")
         cuda_ops.launch_count += 1
 
-    def fused_step(self, *, lr: float, hyper, step: int) -> torch.Tensor:
-        """reduce-scatter -> norm exchange -> AdamW + all-gather, all over peer memory."""
-        from ..ops import cuda_ops
-        if len(self.groups) != 1:
-            raise NotImplementedError("one bf16 flat group expected")
+    # -- step ------------------------------------------------------------------------------------------
+    def begin_step(self) -> None:
+        """Called before the backward pass whose gradients will be reduced: opens a new epoch."""
         self.epoch += 1
-        G = self.groups[0]
-        sh = G["shard"]
-        n = sh.hi - sh.lo
-        nblocks = 1024
-        self.barrier(0)  # every rank's backward has finished writing its gradient buffer
-        rc = self.lib.otb_comm_reduce_scatter(G["grads"].table, c_int(self.world), c_longlong(sh.lo), c_longlong(n),
-                                              c_void_p(G["g32"].data_ptr()), c_void_p(G["partial"].data_ptr()),
-                                              c_int(nblocks), self._stream())
+        self._reduced.clear()
+
+    def _reduce_bucket(self, B: dict, nblocks: int) -> None:
+        """On the CURRENT stream: wait until every rank has finished bucket ``B``, then sum this rank's slice."""
+        from ..ops import cuda_ops
+        self.barrier(B["bucket"].index)
+        sh = B["shard"]
+        n = B["n"]
+        nblocks = max(1, min(nblocks, self.PARTIALS_PER_BUCKET, (n // 8 + 511) // 512))
+        if nblocks < self.PARTIALS_PER_BUCKET and B.get("nblocks") not in (None, nblocks):
+            B["partial"].zero_()         # fewer blocks than the last launch: stale partials must not be counted
+        B["nblocks"] = nblocks
+        rc = self.lib.otb_comm_reduce_scatter(B["grads"].table, c_int(self.world), c_longlong(B["lo"]), c_longlong(n),
+                                              c_void_p(sh.g32.data_ptr() + 4 * B["off"]),
+                                              c_void_p(B["partial"].data_ptr()), c_int(nblocks), c_int(B["elem"]),
+                                              c_void_p(self.status), self._stream())
         if rc != 0:
             raise RuntimeError(f"reduce_scatter launch failed ({rc})")
+        cuda_ops.launch_count += 1
+        self._reduced.add(B["bucket"].index)
+
+    def reduce_bucket_async(self, index: int) -> None:
+        """Bucket ``index`` is complete on this rank as of the work already queued on the current stream: reduce
+        it on the side stream, under whatever the backward pass launches next."""
+        if index in self._reduced:
+            raise RuntimeError(f"gradient bucket {index} was reduced twice in one step")
+        main = torch.cuda.current_stream()
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            self._reduce_bucket(self.buckets[index], self.OVERLAP_BLOCKS)
+
+    def fused_step(self, *, lr: float, hyper, step: int) -> torch.Tensor:
+        """Reduce what the backward pass has not reduced yet -> norm exchange -> AdamW + all-gather, all over peer
+        memory.  Returns the pre-clip norm of the rank-mean gradient (a device scalar)."""
+        from ..ops import cuda_ops
+        self.check(blocking=False)
+        main = torch.cuda.current_stream()
+        main.wait_stream(self.side)                      # overlapped reductions are part of this step
+        for B in self.buckets:
+            if B["bucket"].index not in self._reduced:
+                self._reduce_bucket(B, self.FLUSH_BLOCKS)
         rc = self.lib.otb_comm_norm_exchange(
-            c_void_p(G["partial"].data_ptr()), c_int(nblocks), self.norms.table, self.flags.table, c_int(self.rank),
-            c_int(self.world), c_int(1), c_int(self.epoch), c_float(1.0 / self.world),
+            c_void_p(self.partial.data_ptr()), c_int(self.partial.numel()), self.norms.table, self.flags.table,
+            c_int(self.rank), c_int(self.world), c_int(self.slot_norm), c_int(self.epoch), c_float(1.0 / self.world),
             c_float(hyper.grad_clip_norm or 0.0), c_void_p(self.scale.data_ptr()), c_longlong(self.wait_budget),
             c_void_p(self.status), self._stream())
         if rc != 0:
             raise RuntimeError(f"norm_exchange launch failed ({rc})")
-        rc = self.lib.otb_comm_adamw_allgather(
-            c_void_p(sh.master.data_ptr()), c_void_p(G["g32"].data_ptr()), c_void_p(sh.m.data_ptr()),
-            c_void_p(sh.v.data_ptr()), G["params"].table, c_int(self.world), c_longlong(sh.lo), c_longlong(n),
-            c_float(lr), c_float(hyper.betas[0]), c_float(hyper.betas[1]), c_float(hyper.eps),
-            c_float(hyper.weight_decay), c_float(1.0 - hyper.betas[0] ** step), c_float(1.0 - hyper.betas[1] ** step),
-            c_void_p(self.scale.data_ptr()), c_int(nblocks), self._stream())
-        if rc != 0:
-            raise RuntimeError(f"adamw_allgather launch failed ({rc})")
-        cuda_ops.launch_count += 3
-        self.barrier(2)  # all ranks' parameter stores have landed; gradients may be cleared
+        bc1, bc2 = 1.0 - hyper.betas[0] ** step, 1.0 - hyper.betas[1] ** step
+        for B in self.buckets:
+            sh, off, n = B["shard"], B["off"], B["n"]
+            nblocks = max(1, min(self.FLUSH_BLOCKS, (n // 8 + 511) // 512))
+            rc = self.lib.otb_comm_adamw_allgather(
+                c_void_p(sh.master.data_ptr() + 4 * off), c_void_p(sh.g32.data_ptr() + 4 * off),
+                c_void_p(sh.m.data_ptr() + 4 * off), c_void_p(sh.v.data_ptr() + 4 * off), B["params"].table,
+                c_int(self.world), c_longlong(B["lo"]), c_longlong(n), c_float(lr), c_float(hyper.betas[0]),
+                c_float(hyper.betas[1]), c_float(hyper.eps), c_float(hyper.weight_decay), c_float(bc1), c_float(bc2),
+                c_void_p(self.scale.data_ptr()), c_int(nblocks), c_int(B["elem"]), c_void_p(self.status),
+                self._stream())
+            if rc != 0:
+                raise RuntimeError(f"adamw_allgather launch failed ({rc})")
+        cuda_ops.launch_count += 1 + len(self.buckets)
+        self.barrier(self.slot_end)  # all ranks' parameter stores have landed; gradients may be cleared
+        self._pending_check = torch.cuda.Event()
+        self._pending_check.record(main)
         return self.scale[1].clone()
+
+    def check(self, blocking: bool = True) -> None:
+        """Raises if a wait of an earlier step gave up.  ``blocking=False`` looks only when that step has already
+        finished on the device (no synchronisation is added to a pipelined loop); the trainer calls the blocking
+        form where it synchronises anyway (reading the loss)."""
+        from ..ops import cuda_ops
+        ev = self._pending_check
+        if ev is None:
+            return
+        if blocking or ev.query():
+            self._pending_check = None
+            cuda_ops.check_status()

@@ -12,10 +12,16 @@ fp32 masters for trainable parameters, L2 clip of the (rank-averaged) gradient a
 with the pre-clip norm reported, decoupled weight decay, masters rounded to bf16 after the update.
 The gradient mean is taken in fp32 (the reference's DDP averages in bf16).
 
-``strategy``: ``"ddp"`` keeps full optimizer state on every rank (all-reduce); ``"zero2"`` / ``"fsdp"``
-shard the optimizer state (reduce-scatter + all-gather).  Parameters stay replicated in bf16 in both:
-with 180 GB of HBM3e a 3.4 B-parameter policy has no reason to re-gather weights every layer.
-``comm``: ``"p2p"`` runs the fused peer-memory kernels, ``"nccl"`` the library collectives (baseline).
+``strategy``: ``"ddp"`` keeps full optimizer state on every rank (all-reduce); ``"zero1"`` / ``"zero2"`` shard the
+optimizer state (reduce-scatter + all-gather) and keep the bf16 parameters replicated.  ``comm``: ``"p2p"`` runs the
+fused peer-memory kernels, ``"nccl"`` the library collectives (baseline).  Under ``p2p`` the optimizer state is always
+sharded (``ddp`` then only names the replicated-parameter layout): a full-state step over peer memory would make
+every rank write every parameter into every peer.
+
+Sharding is by gradient bucket: every rank owns an equal slice of EVERY bucket (``parallel/flat.py``), so the
+reduce-scatter of a bucket spreads over all ranks and all links, and it starts as soon as the bucket's last
+weight-gradient product has been issued (under the rest of the backward pass) instead of after ``backward()``
+returns.  The reference gets its overlap from the DDP reducer's buckets (``scripts/train.py:234,594-609``).
 """
 
 from __future__ import annotations
@@ -57,21 +63,38 @@ def assemble_weighted_loss(losses: dict[str, Tensor], weights: dict[str, float])
 
 
 class _ShardState:
-    """fp32 master / moments for the slice ``[lo, hi)`` of one flat group."""
+    """fp32 masters / moments of this rank's part of one flat group: one slice ``[lo, hi)`` per gradient bucket
+    (sharded) or the whole group (replicated), stored back to back; ``offsets[i]`` is where slice ``i`` starts."""
 
-    def __init__(self, group: FlatGroup, lo: int, hi: int):
-        self.lo, self.hi = lo, hi
+    def __init__(self, group: FlatGroup, rank: int, world: int, sharded: bool):
+        if sharded and world > 1:
+            self.slices = [(b.lo + rank * (b.numel // world), b.lo + (rank + 1) * (b.numel // world))
+                           for b in group.buckets]
+        else:
+            self.slices = [(0, group.numel)]
+        self.offsets, off = [], 0
+        for lo, hi in self.slices:
+            self.offsets.append(off)
+            off += hi - lo
+        self.numel = off
         dev = group.data.device
-        self.master = group.data[lo:hi].float().clone() if group.dtype != torch.float32 else None
-        self.m = torch.zeros(hi - lo, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(hi - lo, dtype=torch.float32, device=dev)
+        self.master = torch.cat([group.data[lo:hi].float() for lo, hi in self.slices])
+        self.m = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.contiguous = len(self.slices) == 1
+        # staging for the library path when the owned slices are not one contiguous range
+        self.grad_stage = None if self.contiguous else torch.empty(off, dtype=group.dtype, device=dev)
+        self.param_stage = None if self.contiguous else torch.empty(off, dtype=group.dtype, device=dev)
+
+    def slices_tensor(self) -> Tensor:
+        return torch.tensor(self.slices, dtype=torch.int64).reshape(-1, 2)
 
 
 class TrainEngine:
     def __init__(self, policy: nn.Module, hyper: OptimHyper, *, device: torch.device | str,
                  lr_lambda: Callable[[int], float] | None = None, loss_weights: dict[str, float] | None = None,
                  strategy: str = "zero2", comm: str = "auto", process_group=None,
-                 grad_accum_steps: int = 1):
+                 grad_accum_steps: int = 1, overlap: bool = True, bucket_elems: int | None = None):
         self.policy = policy
         self.hyper = hyper
         self.device = torch.device(device)
@@ -80,8 +103,12 @@ class TrainEngine:
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
-        if strategy in ("fsdp", "zero1", "zero3", "deepspeed"):
-            strategy = "zero2"
+        if strategy in ("zero1", "deepspeed"):
+            strategy = "zero2"          # gradients are reduce-scattered in both; only the optimizer state is sharded
+        if strategy in ("fsdp", "zero3", "fsdp2"):
+            raise ValueError(
+                f"strategy {strategy!r} shards the PARAMETERS; build the engine with parallel.fsdp.make_engine (or "
+                "distributed.strategy in the training config), which wires the per-unit gather into the model")
         if strategy not in ("ddp", "zero2"):
             raise ValueError(f"unknown strategy {strategy!r}")
         self.strategy = strategy if self.world > 1 else "ddp"
@@ -95,19 +122,19 @@ class TrainEngine:
             self.p2p = PeerComm(self.device, process_group)
             allocator = self.p2p.alloc_symmetric
         self.comm = comm
-        self.store = FlatParamStore(policy, self.device, pad_to=self.world, allocator=allocator)
+        if self.p2p is not None:
+            self.strategy = "zero2"
+        from .flat import DEFAULT_BUCKET_ELEMS
+        self.store = FlatParamStore(policy, self.device, pad_to=self.world, allocator=allocator,
+                                    bucket_elems=bucket_elems or DEFAULT_BUCKET_ELEMS)
         if self.world > 1:
             self._broadcast_params()
-        self.shards: list[_ShardState] = []
-        for g in self.store.groups:
-            if self.strategy == "zero2":
-                per = g.numel // self.world
-                lo, hi = self.rank * per, (self.rank + 1) * per
-            else:
-                lo, hi = 0, g.numel
-            self.shards.append(_ShardState(g, lo, hi))
+        sharded = self.strategy == "zero2"
+        self.shards: list[_ShardState] = [_ShardState(g, self.rank, self.world, sharded) for g in self.store.groups]
+        self.overlap = bool(overlap) and self.p2p is not None
         if self.p2p is not None:
             self.p2p.register(self.store, self.shards)
+            self._install_grad_hooks()
         self.step_count = 0
         self._micro = 0
         n_part = 1024
@@ -126,6 +153,71 @@ class TrainEngine:
             if not p.requires_grad:
                 dist.broadcast(p.data, src=0, group=self.pg)
 
+    # -- gradient-ready tracking (peer-memory path) ----------------------------------------------------
+    def _install_grad_hooks(self) -> None:
+        """Every route a parameter gradient can take ends in ``_on_grad``: the fused backward passes that write
+        into ``main_grad`` call it through ``ops.fused.set_grad_ready_hook``; gradients that autograd delivers in
+        ``.grad`` are folded into ``main_grad`` by a post-accumulate hook first.  The first step only counts how
+        many deliveries each parameter gets; later steps reduce a bucket when all its deliveries have happened."""
+        from ..ops import fused
+        self._bucket_of = self.store.bucket_of_param()
+        self._expected: dict[int, int] | None = None
+        self._counts: dict[int, int] = {}
+        self._remaining: dict[int, int] = {}
+        self._bucket_open: dict[int, int] = {}
+        self._armed = self._step_open = False
+        fused.set_grad_ready_hook(self._on_grad)
+        for g in self.store.groups:
+            for p in g.params:
+                p.register_post_accumulate_grad_hook(self._on_autograd_grad)
+
+    def _on_autograd_grad(self, p) -> None:
+        if p.grad is not None:
+            p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+            p.grad = None
+        self._on_grad(p)
+
+    def _on_grad(self, p) -> None:
+        b = self._bucket_of.get(id(p))
+        if b is None:
+            return
+        if not self._armed:
+            self._counts[id(p)] = self._counts.get(id(p), 0) + 1
+            return
+        left = self._remaining.get(id(p), 0) - 1
+        self._remaining[id(p)] = left
+        if left < 0:
+            if b.index in self.p2p._reduced:
+                raise RuntimeError(
+                    "a gradient arrived for a bucket that was already reduced: the backward graph changed since the "
+                    "first step (build the engine with overlap=False for models whose graph varies)")
+            return
+        if left == 0:
+            self._bucket_open[b.index] -= 1
+            if self._bucket_open[b.index] == 0:
+                self.p2p.reduce_bucket_async(b.index)
+
+    def _arm(self) -> None:
+        """Before the backward pass whose gradients get reduced (the last micro-batch of the step)."""
+        self.p2p.begin_step()
+        self._step_open = True
+        self._armed = self.overlap and self._expected is not None
+        if self._armed:
+            self._remaining = dict(self._expected)
+            self._bucket_open = {}
+            for pid, n in self._expected.items():
+                if n > 0:
+                    i = self._bucket_of[pid].index
+                    self._bucket_open[i] = self._bucket_open.get(i, 0) + 1
+        else:
+            self._counts = {}
+
+    def check(self, blocking: bool = True) -> None:
+        """Raises if a bounded wait of the peer-memory step gave up (a peer was late or gone): the step wrote
+        nothing, parameters are those of the last good step."""
+        if self.p2p is not None:
+            self.p2p.check(blocking)
+
     def current_lr(self) -> float:
         mult = self.lr_lambda(self.step_count) if self.lr_lambda is not None else 1.0
         return self.hyper.lr * mult
@@ -136,6 +228,8 @@ class TrainEngine:
         loss = assemble_weighted_loss(losses, self.loss_weights)
         if self.grad_accum_steps > 1:
             loss = loss / self.grad_accum_steps
+        if self.p2p is not None and self._micro == self.grad_accum_steps - 1:
+            self._arm()
         loss.backward()
         self._micro += 1
         out = {k: v.detach() for k, v in losses.items() if isinstance(v, Tensor)}
@@ -151,6 +245,11 @@ class TrainEngine:
         h = self.hyper
         lr = self.hyper.lr * (self.lr_lambda(self.step_count - 1) if self.lr_lambda is not None else 1.0)
         if self.p2p is not None:
+            if not self._step_open:
+                self.p2p.begin_step()        # optimizer_step() without forward_backward() (tests, tools)
+            if not self._armed and self._expected is None and self._counts:
+                self._expected = dict(self._counts)      # deliveries per parameter in one backward pass
+            self._armed = self._step_open = False
             norm = self.p2p.fused_step(lr=lr, hyper=h, step=self.step_count)
         else:
             norm = self._library_step(lr)
@@ -162,20 +261,22 @@ class TrainEngine:
     def _library_step(self, lr: float) -> Tensor:
         h = self.hyper
         world = self.world
+        nccl = world > 1 and dist.get_backend(self.pg) == "nccl"
         grads: list[Tensor] = []
         for g, sh in zip(self.store.groups, self.shards):
-            if world > 1:
-                if self.strategy == "zero2":
-                    if dist.get_backend(self.pg) == "nccl":
-                        shard = torch.empty(sh.hi - sh.lo, dtype=g.dtype, device=self.device)
-                        dist.reduce_scatter_tensor(shard, g.grad, op=dist.ReduceOp.SUM, group=self.pg)
-                    else:
-                        dist.all_reduce(g.grad, op=dist.ReduceOp.SUM, group=self.pg)
-                        shard = g.grad[sh.lo:sh.hi]
+            if world > 1 and self.strategy == "zero2":
+                if nccl:
+                    for b, (lo, hi), off in zip(g.buckets, sh.slices, sh.offsets):
+                        dist.reduce_scatter_tensor(sh.grad_stage[off:off + hi - lo], g.grad[b.lo:b.hi],
+                                                   op=dist.ReduceOp.SUM, group=self.pg)
                 else:
                     dist.all_reduce(g.grad, op=dist.ReduceOp.SUM, group=self.pg)
-                    shard = g.grad
+                    for (lo, hi), off in zip(sh.slices, sh.offsets):
+                        sh.grad_stage[off:off + hi - lo].copy_(g.grad[lo:hi])
+                shard = sh.grad_stage
             else:
+                if world > 1:
+                    dist.all_reduce(g.grad, op=dist.ReduceOp.SUM, group=self.pg)
                 shard = g.grad
             grads.append(shard)
         # global L2 norm of the rank-averaged gradient
@@ -199,27 +300,30 @@ class TrainEngine:
         self._scale[0] = coef * inv_world
         self._scale[1] = norm
         for g, sh, sg in zip(self.store.groups, self.shards, grads):
-            p_shard = g.data[sh.lo:sh.hi]
+            # the refreshed parameters of this rank's part, in the group's dtype
+            p_out = g.data if sh.contiguous else sh.param_stage
             if native:
                 from ..ops import cuda_ops
-                if sh.master is not None:
-                    cuda_ops.adamw(sh.master, sg, sh.m, sh.v, p_shard, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
+                if g.dtype == torch.bfloat16:
+                    cuda_ops.adamw(sh.master, sg, sh.m, sh.v, p_out, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
                                    eps=h.eps, weight_decay=h.weight_decay, step=self.step_count, scale=self._scale)
                 else:
-                    cuda_ops.adamw(p_shard, sg, sh.m, sh.v, None, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
+                    cuda_ops.adamw(sh.master, sg, sh.m, sh.v, None, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
                                    eps=h.eps, weight_decay=h.weight_decay, step=self.step_count, scale=self._scale)
+                    p_out.copy_(sh.master)
             else:
-                master = sh.master if sh.master is not None else p_shard
-                ops.ref.adamw_flat(master, sg, sh.m, sh.v, p_shard if sh.master is not None else None, lr=lr,
-                                   beta1=h.betas[0], beta2=h.betas[1], eps=h.eps, weight_decay=h.weight_decay,
-                                   step=self.step_count, grad_scale=float(self._scale[0]))
+                ops.ref.adamw_flat(sh.master, sg, sh.m, sh.v, p_out, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
+                                   eps=h.eps, weight_decay=h.weight_decay, step=self.step_count,
+                                   grad_scale=float(self._scale[0]))
             if world > 1 and self.strategy == "zero2":
-                if dist.get_backend(self.pg) == "nccl":
-                    dist.all_gather_into_tensor(g.data, p_shard.clone(), group=self.pg)
-                else:
-                    parts = [torch.empty_like(p_shard) for _ in range(world)]
-                    dist.all_gather(parts, p_shard.clone(), group=self.pg)
-                    g.data.copy_(torch.cat(parts))
+                for b, (lo, hi), off in zip(g.buckets, sh.slices, sh.offsets):
+                    mine = sh.param_stage[off:off + hi - lo]
+                    if nccl:
+                        dist.all_gather_into_tensor(g.data[b.lo:b.hi], mine, group=self.pg)
+                    else:
+                        parts = [torch.empty_like(mine) for _ in range(world)]
+                        dist.all_gather(parts, mine, group=self.pg)
+                        g.data[b.lo:b.hi].copy_(torch.cat(parts))
         return norm
 
     def train_step(self, batch: dict[str, Any]) -> dict[str, Tensor]:
@@ -235,26 +339,29 @@ class TrainEngine:
         sd: dict[str, Any] = {"step": self.step_count, "rank": self.rank, "world": self.world,
                               "strategy": self.strategy}
         for i, sh in enumerate(self.shards):
-            sd[f"group{i}.lo"], sd[f"group{i}.hi"] = sh.lo, sh.hi
+            sd[f"group{i}.slices"] = sh.slices_tensor()      # [[lo, hi], ...] inside the flat group, in storage order
             sd[f"group{i}.m"], sd[f"group{i}.v"] = sh.m, sh.v
-            if sh.master is not None:
-                sd[f"group{i}.master"] = sh.master
+            sd[f"group{i}.master"] = sh.master
         return sd
 
     def load_state_dict(self, sd: dict[str, Any], rebuild_masters_from_live: bool = False) -> None:
         self.step_count = int(sd["step"])
         for i, sh in enumerate(self.shards):
-            if (sd[f"group{i}.lo"], sd[f"group{i}.hi"]) != (sh.lo, sh.hi):
-                raise ValueError("optimizer shard layout differs (world size changed); use rebuild")
+            saved = sd.get(f"group{i}.slices")
+            if saved is None or saved.reshape(-1, 2).tolist() != [list(x) for x in sh.slices]:
+                raise ValueError("optimizer shard layout differs (world size or bucket layout changed); use rebuild")
             sh.m.copy_(sd[f"group{i}.m"])
             sh.v.copy_(sd[f"group{i}.v"])
-            if sh.master is not None:
-                if rebuild_masters_from_live or f"group{i}.master" not in sd:
-                    sh.master.copy_(self.store.groups[i].data[sh.lo:sh.hi].float())
-                else:
-                    sh.master.copy_(sd[f"group{i}.master"])
+            if rebuild_masters_from_live or f"group{i}.master" not in sd:
+                self._master_from_live(self.store.groups[i], sh)
+            else:
+                sh.master.copy_(sd[f"group{i}.master"])
+
+    @staticmethod
+    def _master_from_live(g: FlatGroup, sh: _ShardState) -> None:
+        for (lo, hi), off in zip(sh.slices, sh.offsets):
+            sh.master[off:off + hi - lo].copy_(g.data[lo:hi].float())
 
     def rebuild_masters_from_live(self) -> None:
         for g, sh in zip(self.store.groups, self.shards):
-            if sh.master is not None:
-                sh.master.copy_(g.data[sh.lo:sh.hi].float())
+            self._master_from_live(g, sh)

@@ -290,6 +290,7 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
         gathered = control.gather_scalars({"loss": out["loss"], "MSE": out.get("MSE", torch.zeros(())),
                                            "CE": out.get("CE", torch.zeros(())), "grad_norm": out["grad_norm"]},
                                           device=device)
+        engine.check()      # the gather above synchronised: a peer-memory wait that gave up is fatal here, not later
         tracker.update_s = time.perf_counter() - t1
         step += 1
         tracker.step()

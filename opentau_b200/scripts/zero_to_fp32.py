@@ -1,7 +1,7 @@
 """Merge the per-rank optimizer shards of a checkpoint into one full-precision state dict.
 
 The reference ships DeepSpeed's ``zero_to_fp32.py`` for its ZeRO checkpoints (``src/opentau/scripts/zero_to_fp32.py``,
-used by ``convert_checkpoint.sh``).  Here every rank saves its slice ``[lo, hi)`` of each flat parameter group as
+used by ``convert_checkpoint.sh``).  Here every rank saves its slices ``[lo, hi)`` (one per gradient bucket) of each flat parameter group as
 ``optimizer_rank<r>.safetensors`` (fp32 masters and Adam moments) and rank 0 saves ``flat_layout.json`` (parameter name,
 shape and offset inside the flat groups), so the consolidation is a concatenation followed by slicing:
 
@@ -43,9 +43,15 @@ def merge_flat(checkpoint_dir: str | Path, what: str = "master") -> list[torch.T
         flat = torch.zeros(g["numel"], dtype=torch.float32)
         covered = 0
         for tensors, meta in shards:
-            lo, hi = int(meta[f"group{gi}.lo"]), int(meta[f"group{gi}.hi"])
-            flat[lo:hi] = tensors[key].float()
-            covered += hi - lo
+            if f"group{gi}.slices" in tensors:           # one [lo, hi) per gradient bucket, stored back to back
+                slices = tensors[f"group{gi}.slices"].reshape(-1, 2).tolist()
+            else:                                        # older checkpoints: one contiguous range per rank
+                slices = [[int(meta[f"group{gi}.lo"]), int(meta[f"group{gi}.hi"])]]
+            off = 0
+            for lo, hi in slices:
+                flat[lo:hi] = tensors[key][off:off + hi - lo].float()
+                off += hi - lo
+                covered += hi - lo
         if covered < g["numel"]:
             raise ValueError(f"group {gi}: shards cover {covered} of {g['numel']} elements (a rank file is missing)")
         out.append(flat)

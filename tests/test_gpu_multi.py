@@ -13,7 +13,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, comm, ret):
+def _worker(rank, world, port, comm, ret, variant="plain"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
@@ -25,44 +25,113 @@ def _worker(rank, world, port, comm, ret):
         from helpers import tiny_batch, tiny_pi05
         from opentau_b200.ops import cuda_ops
         from opentau_b200.parallel.engine import OptimHyper, TrainEngine
-        pol = tiny_pi05(device="cuda", seed=20 + rank).to(torch.bfloat16).train()
-        eng = TrainEngine(pol, OptimHyper(lr=1e-3, grad_clip_norm=1.0), device=dev, strategy="zero2", comm=comm)
+        train_vision = variant == "mixed"            # the SigLIP patch / position tables stay fp32: a second flat group
+        pol = tiny_pi05(device="cuda", seed=20 + rank, freeze_vision_encoder=not train_vision).to(torch.bfloat16)
+        pol.train()
+        eng = TrainEngine(pol, OptimHyper(lr=1e-3, grad_clip_norm=1.0), device=dev,
+                          strategy="ddp" if variant == "ddp" else "zero2", comm=comm,
+                          overlap=variant != "no_overlap", bucket_elems=150_000)
+        key = f"{comm}:{variant}"
         batch = tiny_batch(device=dev, seed=100 + rank)
         g = torch.Generator().manual_seed(7 + rank)
         noise = torch.randn(4, 10, 32, generator=g).to(dev)
         time = torch.full((4,), 0.5, device=dev)
         norms = []
-        for _ in range(3):
+        for _ in range(4):                   # step 1 learns the delivery counts, steps 2+ reduce under the backward
             out = pol(batch, noise=noise, time=time)
-            (out["MSE"] + out["CE"]).backward()
+            loss = out["MSE"] + out["CE"]
+            if eng.p2p is not None:
+                eng._arm()
+            loss.backward()
             norms.append(float(eng.optimizer_step()))
         torch.cuda.synchronize()
         cuda_ops.check_status()
-        flat = eng.store.groups[0].data.float().cpu()
+        eng.check()
+        named = {n: p.detach().float().cpu() for n, p in pol.named_parameters() if p.requires_grad}
         if rank == 0:
-            ret[comm] = (flat, norms)
+            ret[key] = (named, norms, len(eng.store.groups), len(eng.store.buckets),
+                        bool(eng.p2p is not None and eng._expected is not None))
         gathered = [None] * world
-        dist.all_gather_object(gathered, float(flat.double().sum()))
+        dist.all_gather_object(gathered, float(sum(v.double().sum() for v in named.values())))
         if rank == 0:
-            ret[comm + "_same"] = all(abs(x - gathered[0]) < 1e-6 for x in gathered)
+            ret[key + "_same"] = all(abs(x - gathered[0]) < 1e-6 for x in gathered)
         dist.barrier()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_memory_step_matches_nccl_step():
+@pytest.mark.parametrize("variant", ["plain", "no_overlap", "ddp", "mixed"])
+def test_peer_memory_step_matches_nccl_step(variant):
+    """The bucketed, overlapped peer-memory step gives the parameters and gradient norms of the library step:
+    with the reduction under the backward pass and without, under the ``ddp`` label (the norm must not be counted
+    once per rank), and for a model with an fp32 parameter group beside the bf16 one."""
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
     for comm in ("nccl", "p2p"):
-        mp.spawn(_worker, args=(2, free_port(), comm, ret), nprocs=2, join=True)
-    assert ret["nccl_same"] and ret["p2p_same"]
-    (fa, na), (fb, nb) = ret["nccl"], ret["p2p"]
-    n = min(fa.numel(), fb.numel())
+        mp.spawn(_worker, args=(2, free_port(), comm, ret, variant), nprocs=2, join=True)
+    assert ret[f"nccl:{variant}_same"] and ret[f"p2p:{variant}_same"]
+    (fa, na, _, _, _), (fb, nb, ngroups, nbuckets, learned) = ret[f"nccl:{variant}"], ret[f"p2p:{variant}"]
+    assert nbuckets > 3 and learned
+    if variant == "mixed":
+        assert ngroups == 2
     for x, y in zip(na, nb):
         assert abs(x - y) / max(1e-6, abs(x)) < 2e-2
-    torch.testing.assert_close(fa[:n], fb[:n], rtol=2e-2, atol=2e-3)
+    for n in fa:
+        torch.testing.assert_close(fa[n], fb[n], rtol=2e-2, atol=2e-3, msg=n)
+
+
+def _timeout_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from helpers import tiny_batch, tiny_pi05
+        from opentau_b200.parallel.engine import OptimHyper, TrainEngine
+        pol = tiny_pi05(device="cuda", seed=3).to(torch.bfloat16).train()
+        eng = TrainEngine(pol, OptimHyper(lr=1e-2, grad_clip_norm=1.0), device=dev, comm="p2p", overlap=False)
+        batch = tiny_batch(device=dev, seed=100 + rank)
+        eng.train_step(batch)                                # a good step first
+        torch.cuda.synchronize()
+        eng.check()
+        before = [g.data.clone() for g in eng.store.groups]
+        dist.barrier()
+        # Both ranks now wait on a flag value that nobody will ever write (the epoch jumps ahead on the waiting
+        # side only, by a different amount per rank), with a budget of a few milliseconds: every wait gives up,
+        # records it, and the data kernels behind it must leave the parameters alone.
+        eng.p2p.wait_budget = 5_000_000
+        eng.p2p.epoch += 1000 * (rank + 1)
+        out = pol(batch)
+        (out["MSE"] + out["CE"]).backward()
+        eng.optimizer_step()
+        torch.cuda.synchronize()
+        raised = False
+        try:
+            eng.check()
+        except RuntimeError:
+            raised = True
+        unchanged = all(torch.equal(a, g.data) for a, g in zip(before, eng.store.groups))
+        flags = [None] * world
+        dist.all_gather_object(flags, (raised, unchanged))
+        if rank == 0:
+            ret["timeout"] = flags
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_a_wait_that_gives_up_is_fatal_and_leaves_the_parameters_alone():
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_timeout_worker, args=(2, free_port(), ret), nprocs=2, join=True)
+    assert all(r and u for r, u in ret["timeout"]), ret["timeout"]
 
 
 def _tp_worker(rank, world, port, ret):
