@@ -41,7 +41,10 @@ def parse_args():
     ap.add_argument("--strategy", default="zero2")
     ap.add_argument("--tiny", action="store_true", help="small geometry (plumbing check, not a benchmark)")
     ap.add_argument("--mode", default="train", choices=["train", "infer"])
-    ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3", "pi06"],
+    ap.add_argument("--cp", type=int, default=1,
+                    help="--model pi07: context-parallel width (ranks that share every sequence); must equal --gpus "
+                         "or 1")
+    ap.add_argument("--model", default="pi05", choices=["pi05", "cosmos3", "pi06", "pi07"],
                     help="train mode: pi05 (headline) or pi06; infer mode: also cosmos3, the workload of the "
                          "reference's published B200 latency table")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (profiling runs only)")
@@ -65,7 +68,7 @@ def parse_args():
                          "per-kernel device-time shares to PATH and exit without a benchmark line")
     a = ap.parse_args()
     if a.batch is None:
-        a.batch = 16 if a.model == "pi06" else 32
+        a.batch = {"pi06": 16, "pi07": 2}.get(a.model, 32)
     return a
 
 
@@ -158,9 +161,78 @@ def build_policy_pi06(args, device):
     return policy, spec, cfg
 
 
+def build_policy_pi07(args, device):
+    """Long-context pi0.7 controller: SpaceTime-SigLIP video encoder over 16 frames x 3 cameras at 448x448, every
+    frame's 256 pooled tokens kept in the decoder (12 288 vision tokens as 48 frame blocks), Gemma-3-4B backbone, a
+    1024-wide ("300 M") action expert, 128 prompt tokens, a 128-token plan segment (the subtask text of the
+    planner), action chunk 50x32, knowledge insulation + FAST tokens.  The decoder sequence is split over
+    ``--cp`` ranks (``parallel/cp.py``)."""
+    import torch
+    from opentau_b200.configs.types import FeatureType, PolicyFeature
+    from opentau_b200.datasets.synthetic import SyntheticSpec, identity_stats
+    from opentau_b200.policies.factory import make_policy, make_policy_config
+    cams, frames = 3, (3 if args.tiny else 16)
+    res = (224, 224) if args.tiny else (448, 448)
+    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, *res)) for i in range(cams)}
+    feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
+    fast = 8 if args.tiny else 32
+    kw = dict(n_obs_steps=frames, chunk_size=50, n_action_steps=50, prompt_max_length=128, response_max_length=128,
+              discrete_action_max_length=fast, discrete_action_vocab_size=2048, dropout=args.dropout,
+              knowledge_insulation=True, device=str(device), freeze_vision_encoder=not args.train_vision,
+              train_expert_only=False, resize_imgs_with_padding=res, keep_history_tokens=True,
+              input_features=feats, output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))},
+              expert=dict(hidden_size=1024, intermediate_size=4096), proj_width=1024)
+    vocab = 262208
+    if args.tiny:
+        kw.update(vlm=dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=64, intermediate_size=1024, vocab_size=1024, sliding_window_pattern=2),
+                  expert=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                              head_dim=64, intermediate_size=512, vocab_size=1024),
+                  vision=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4),
+                  vlm_config={"tokens_per_image_side": 8}, discrete_action_vocab_size=256, proj_width=128,
+                  spacetime_layer_stride=2, prompt_max_length=16, response_max_length=8)
+        vocab = 1024
+    cfg = make_policy_config("pi07_low_level", **kw)
+    spec = SyntheticSpec(batch_size=args.batch, num_cams=cams, resolution=res, prompt_len=cfg.prompt_max_length,
+                         vocab_size=vocab, state_dim=32, action_dim=32, chunk_size=50, discrete_action_len=fast,
+                         discrete_action_vocab=cfg.discrete_action_vocab_size, image_dtype=torch.bfloat16)
+    spec.history, spec.response_len = frames, cfg.response_max_length
+    torch.manual_seed(1234)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(device):
+            policy = make_policy(cfg, per_dataset_stats=[identity_stats()])
+    finally:
+        torch.set_default_dtype(prev)
+    policy.to(torch.bfloat16)
+    policy.train()
+    return policy, spec, cfg
+
+
+def pi07_batch(spec, device, seed: int, pinned: bool):
+    """Synthetic pi0.7 batch: the standard one plus a frame axis on cameras / state and the plan tokens."""
+    import torch
+    from opentau_b200.datasets.synthetic import make_synthetic_batch
+    b = make_synthetic_batch(spec, device="cpu", seed=seed)
+    g = torch.Generator().manual_seed(seed + 17)
+    T = spec.history
+    for k in [k for k in b if k.startswith("camera")]:
+        img = b[k]
+        b[k] = (img[:, None] * torch.linspace(0.5, 1.0, T).view(1, T, 1, 1, 1).to(img.dtype)).contiguous()
+    b["state"] = b["state"][:, None].repeat(1, T, 1).contiguous()
+    b["response_tokens"] = torch.randint(3, spec.vocab_size, (spec.batch_size, spec.response_len), generator=g)
+    b["response_masks"] = torch.ones(spec.batch_size, spec.response_len, dtype=torch.bool)
+    if pinned:
+        b = {k: (v.pin_memory() if hasattr(v, "pin_memory") else v) for k, v in b.items()}
+    return {k: (v.to(device) if hasattr(v, "to") else v) for k, v in b.items()}
+
+
 def build_policy(args, device):
     if args.model == "pi06":
         return build_policy_pi06(args, device)
+    if args.model == "pi07":
+        return build_policy_pi07(args, device)
     import torch
     from opentau_b200.configs.types import FeatureType, PolicyFeature
     from opentau_b200.datasets.synthetic import SyntheticSpec, identity_stats
@@ -371,6 +443,11 @@ def main():
     from opentau_b200.parallel.engine import OptimHyper, TrainEngine
 
     policy, spec, cfg = build_policy(args, device)
+    if args.model == "pi07" and args.cp > 1:
+        if args.cp != world:
+            raise SystemExit("--cp must equal the number of ranks (one context-parallel group per node) or 1")
+        from opentau_b200.parallel.cp import ContextParallel
+        policy.model.context_parallel = ContextParallel(device)
     engine = TrainEngine(policy, OptimHyper(lr=cfg.optimizer_lr, betas=tuple(cfg.optimizer_betas),
                                             eps=cfg.optimizer_eps, weight_decay=cfg.optimizer_weight_decay,
                                             grad_clip_norm=10.0),
@@ -380,7 +457,11 @@ def main():
 
     # host batches in pinned memory (distinct per step so no step reuses a cached input)
     n_host = 4
-    host = [make_synthetic_batch(spec, device="cpu", seed=1000 * rank + i, pinned=use_cuda) for i in range(n_host)]
+    if args.model == "pi07":
+        host = [pi07_batch(spec, "cpu", 1000 * rank + i, use_cuda) for i in range(n_host)]
+    else:
+        host = [make_synthetic_batch(spec, device="cpu", seed=1000 * rank + i, pinned=use_cuda)
+                for i in range(n_host)]
     dev_batches = [{k: v.to(device) for k, v in b.items()} for b in host[:2]]
     h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
 
@@ -468,7 +549,7 @@ def main():
     if rank == 0:
         peak_gb = torch.cuda.max_memory_allocated() / 2**30 if use_cuda else 0.0
         print(json.dumps({
-            "metric": f"{'pi0.6' if args.model == 'pi06' else 'pi0.5'} train samples/s/box", "value": round(value, 3),
+            "metric": f"{ {'pi06': 'pi0.6', 'pi07': 'pi0.7 long-context'}.get(args.model, 'pi0.5') } train samples/s/box", "value": round(value, 3),
             "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "weak",
@@ -476,10 +557,17 @@ def main():
             "config": {"model": ("tiny (plumbing)" if args.tiny else
                                  "pi0.6 (SigLIP-So400m/14@448 x3 cams pooled to 256 tokens each, Gemma-3-4B, 1280-wide "
                                  "34-layer expert)" if args.model == "pi06" else
+                                 "pi0.7 controller, long context (SpaceTime SigLIP, 16 frames x 3 cams x 256 tokens "
+                                 "kept in the decoder, Gemma-3-4B, 1024-wide expert, 128 prompt + 128 plan tokens)"
+                                 if args.model == "pi07" else
                                  "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"),
-                       "global_batch": global_batch, "seq_len": 3 * 256 + spec.prompt_len + 3 + 256,
-                       "parallelism": f"dp{world}-{engine.strategy}-{engine.comm}", "params": n_params,
-                       "knowledge_insulation": True, "fast_tokens": 256, "action_chunk": "50x32",
+                       "global_batch": global_batch,
+                       "seq_len": (getattr(spec, "history", 1) * 3 * 256 + spec.prompt_len + getattr(spec, "response_len", 0)
+                                   + spec.discrete_action_len + 3) if args.model == "pi07"
+                       else 3 * 256 + spec.prompt_len + 3 + 256,
+                       "parallelism": f"dp{world}-{engine.strategy}-{engine.comm}" + (
+                           f"+cp{args.cp}" if args.model == "pi07" else ""), "params": n_params,
+                       "knowledge_insulation": True, "fast_tokens": spec.discrete_action_len, "action_chunk": "50x32",
                        "dropout": args.dropout,
                        "frozen_weights": "none" if args.train_vision else "SigLIP tower (policy default "
                                                                            "freeze_vision_encoder=true)",

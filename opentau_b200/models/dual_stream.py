@@ -121,7 +121,7 @@ class DualStreamDecoder(nn.Module):
         return stack
 
     def _layer(self, li: int, xs: list[Tensor | None], cos_sin, q_blk, k_blk, q_valid, k_valid,
-               cache_k, cache_v, mods, kv_dst=None) -> tuple[list[Tensor | None], Tensor | None, Tensor | None]:
+               cache_k, cache_v, mods, kv_dst=None, cp=None) -> tuple[list[Tensor | None], Tensor | None, Tensor | None]:
         """``kv_dst = (k_buf, v_buf, offset)``: inference with one tower present writes the new keys / values into
         these ``(B, S_buf, Hkv, D)`` buffers at ``offset`` (behind a cached prefix, or at 0 when a cache is being
         filled) and attends over ``[:offset + T]`` in place: no concatenation, no copy."""
@@ -170,7 +170,11 @@ class DualStreamDecoder(nn.Module):
                 k = torch.cat([cache_k, k], dim=1)
                 v = torch.cat([cache_v, v], dim=1)
         first = next(t for t, x in zip(towers, xs) if x is not None)
-        att = ops.block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, first.cfg.attn_scale)
+        if cp is not None:
+            # the sequence is sharded over the ranks: q / k / v are this rank's slice, k_blk / k_valid cover all keys
+            att = cp.attention(q, k, v, q_blk, k_blk, q_valid, k_valid, first.cfg.attn_scale)
+        else:
+            att = ops.block_attention(q, k, v, q_blk, k_blk, q_valid, k_valid, first.cfg.attn_scale)
         outs: list[Tensor | None] = []
         start, j = 0, 0
         for ti, (tower, x) in enumerate(zip(towers, xs)):
@@ -223,7 +227,7 @@ class DualStreamDecoder(nn.Module):
                 past: KVCache | None = None, fill_cache_len: int | None = None,
                 k_blk: Tensor | None = None, k_valid: Tensor | None = None,
                 mrope: bool = False, per_layer_cache: bool = True, past_layer_map: list[int] | None = None,
-                layer_hook=None, cache_room: int = 0) -> tuple[list[Tensor | None], KVCache | None]:
+                layer_hook=None, cache_room: int = 0, cp=None) -> tuple[list[Tensor | None], KVCache | None]:
         """One pass over all layers.
 
         ``position_ids``: ``(B, S_total)`` (or ``(3,B,S_total)`` with ``mrope``) for the
@@ -235,7 +239,13 @@ class DualStreamDecoder(nn.Module):
         layer).  ``layer_hook(l, xs) -> xs`` runs after layer ``l`` (deepstack feature injection).
         ``cache_room`` allocates the returned cache with that many spare token slots, so that a later
         single-tower inference pass can append its keys / values in place instead of concatenating.
+        ``cp`` (a :class:`opentau_b200.parallel.cp.ContextParallel`): the tokens given are this rank's slice of
+        every sequence; ``k_blk / k_valid`` must then describe the keys of ALL ranks (rank-major), attention runs
+        across the ranks, and a filled cache holds this rank's keys / values only.
         """
+        if cp is not None and (past is not None or k_blk is None):
+            raise ValueError("a context-parallel pass needs the block ids of all keys and takes no cached prefix")
+        cp = cp if (cp is not None and cp.world > 1) else None
         towers = self.towers
         xs = list(inputs_embeds)
         present = [t for t, x in zip(towers, xs) if x is not None]
@@ -290,14 +300,15 @@ class DualStreamDecoder(nn.Module):
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
                 xs, nk, nv = checkpoint(self._layer, li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid,
-                                        ck, cv, mods, use_reentrant=False)
+                                        ck, cv, mods, None, cp, use_reentrant=False)
             else:
                 kv_dst = None
                 if append_in_place:
                     kv_dst = (past.k[pl], past.v[pl], past.length)
                 elif fill_in_place:
                     kv_dst = (new_cache.k[li], new_cache.v[li], 0)
-                xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods, kv_dst)
+                xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods, kv_dst,
+                                         cp)
             if layer_hook is not None:
                 xs = layer_hook(li, xs)
             if fill_cache_len is not None and not fill_in_place:

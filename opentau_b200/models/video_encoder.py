@@ -84,7 +84,10 @@ class SpaceTimeSiglipVideoEncoder(nn.Module):
     def is_spacetime_layer(self, li: int) -> bool:
         return self.stride > 0 and (li + 1) % self.stride == 0
 
-    def forward(self, video: Tensor, frame_valid: Tensor | None = None) -> Tensor:
+    def forward(self, video: Tensor, frame_valid: Tensor | None = None, keep_history: bool = False) -> Tensor:
+        """``keep_history=False`` (the reference behaviour, ``pi07/video_encoder.py:767-778``): only the current
+        frame's tokens ``(B, N, d)`` leave the encoder.  ``keep_history=True`` (long-context variant): every
+        frame's tokens, ``(B, T, N, d)``, oldest first."""
         if video.dim() == 4:
             video = video[:, None]
         B, T, C, Hh, Ww = video.shape
@@ -104,5 +107,7 @@ class SpaceTimeSiglipVideoEncoder(nn.Module):
                 x = spacetime_layer_forward(layer, x, B, T, self._temporal_pe, frame_valid)
             else:
                 x = layer(x)
+        if keep_history:
+            return vm.post_layernorm(x).view(B, T, *x.shape[1:])
         cur = x.view(B, T, *x.shape[1:])[:, -1]                  # past-frame tokens are dropped here
         return vm.post_layernorm(cur)

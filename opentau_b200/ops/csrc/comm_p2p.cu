@@ -118,6 +118,39 @@ __global__ void reduce_scatter_kernel(PeerTable grads, int world, long long lo, 
   }
 }
 
+// out[r * n + i] = src_r[i]: all-gather of every rank's n-element (16-byte multiple) buffer by peer LOADS, in rank
+// order.  Writes nothing when a wait gave up earlier (the buffers it would read cannot be trusted).
+__global__ void allgather_pull_kernel(PeerTable src, int world, long long n_vec16, uint4* __restrict__ out,
+                                      const KernelStatus* status) {
+  if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
+  for (int r = 0; r < world; ++r) {
+    const uint4* s = static_cast<const uint4*>(src.ptr[r]);
+    uint4* o = out + (long long)r * n_vec16;
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < n_vec16;
+         t += (long long)gridDim.x * blockDim.x)
+      o[t] = s[t];
+  }
+}
+
+// out[i] = sum_r src_r[lo + i] for bf16 buffers, summed in fp32 in rank order, stored as bf16: the reduce-scatter of
+// partial results (context-parallel dK / dV) back to the rank that owns the slice.
+__global__ void reduce_scatter_bf16_kernel(PeerTable src, int world, long long lo, long long n,
+                                           __nv_bfloat16* __restrict__ out, const KernelStatus* status) {
+  if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
+  const long long nvec = n >> 3;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
+       t += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(src.ptr[r]) + lo + t * 8, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    store8<__nv_bfloat16>(out + t * 8, acc);
+  }
+}
+
 // One block.  Sums this rank's partials, publishes the total to every rank's norms[rank] (peer store),
 // signals, waits for every peer's total, then writes scale[0] = grad_scale * clip coefficient and
 // scale[1] = global gradient norm (of the rank-mean gradient).
@@ -262,6 +295,25 @@ extern "C" int otb_comm_reduce_scatter(void* const* grad_ptrs, int world, long l
                                                                partial, st);
   else
     return -1;
+  return (int)cudaGetLastError();
+}
+
+// src_ptrs[r]: rank r's buffer of `bytes` bytes (multiple of 16); out: world * bytes bytes, local.
+extern "C" int otb_comm_allgather_pull(void* const* src_ptrs, int world, long long bytes, void* out, int nblocks,
+                                       void* status, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || (bytes % 16) || nblocks < 1) return -1;
+  allgather_pull_kernel<<<nblocks, 512, 0, stream>>>(table_from(src_ptrs, world), world, bytes / 16,
+                                                     static_cast<uint4*>(out),
+                                                     static_cast<const KernelStatus*>(status));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_comm_reduce_scatter_bf16(void* const* src_ptrs, int world, long long lo, long long n, void* out,
+                                            int nblocks, void* status, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || (lo % 8) || nblocks < 1) return -1;
+  reduce_scatter_bf16_kernel<<<nblocks, 512, 0, stream>>>(table_from(src_ptrs, world), world, lo, n,
+                                                          static_cast<__nv_bfloat16*>(out),
+                                                          static_cast<const KernelStatus*>(status));
   return (int)cudaGetLastError();
 }
 

@@ -10,9 +10,16 @@ over NVLink into a local gathered buffer exactly once, in ring order starting wi
 attention CTAs (tcgen05 / TMEM flash attention) consume key blocks as they land.  Block ids / validity of ALL keys
 are an input on every rank (they derive from the batch layout, which is replicated), in source-major order.
 
-The backward pass gathers ``q / dO / LSE / delta`` with the library all-gather and runs the single-GPU backward
-kernels on the gathered tensors (dQ for the local queries against all keys, dK/dV for the local keys against all
-queries) — exact, deterministic, and without a reduction across ranks.
+The backward pass keeps everything query-sided (q, dO, O, LSE) local, so its memory scales with 1 / W: every rank
+gathers K / V of all ranks (peer loads into a local buffer; with grouped-query attention they are the small
+tensors), runs ONE backward over its own queries against all keys -- which yields dQ of its queries and its
+contribution to dK / dV of every key -- and the dK / dV contributions go back to the ranks that own the keys by a
+reduce-scatter over peer memory that sums in rank order (deterministic).  No query, output or gradient-of-output
+tensor ever leaves its rank.
+
+``seq_scatter`` / ``seq_gather`` switch a batch between "my samples, whole sequences" and "all samples of the
+group, my slice of every sequence" with an all-to-all (and its transpose in the backward pass): the vision encoder
+and the loss heads work per sample, the decoder layers per sequence slice.
 
 ``backend="dist"`` (CPU / gloo, and the baseline the fused kernel is measured against) all-gathers K/V with the
 library and calls the ordinary attention op.
@@ -152,6 +159,125 @@ class ContextParallel:
     def _stream(self) -> c_void_p:
         return c_void_p(torch.cuda.current_stream().cuda_stream)
 
+    # -- sequence <-> sample layouts -------------------------------------------------------------------------
+    def seq_scatter(self, x: Tensor) -> Tensor:
+        """``(B, S, ...)`` for this rank's ``B`` samples -> ``(W * B, S / W, ...)``: this rank's slice of every
+        sample of the group (rank-major sample order).  Differentiable."""
+        return _SeqExchange.apply(self, x, True) if self.world > 1 else x
+
+    def seq_gather(self, x: Tensor) -> Tensor:
+        """Inverse of :meth:`seq_scatter`.  Differentiable."""
+        return _SeqExchange.apply(self, x, False) if self.world > 1 else x
+
+    def _exchange(self, x: Tensor, scatter: bool) -> Tensor:
+        W = self.world
+        if scatter:
+            B, S = x.shape[:2]
+            if S % W:
+                raise ValueError(f"sequence length {S} is not divisible by {W} ranks")
+            send = x.reshape(B, W, S // W, *x.shape[2:]).transpose(0, 1).contiguous()      # (W, B, Sl, ...)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=self.group)
+            return recv.reshape(W * B, S // W, *x.shape[2:])
+        WB, Sl = x.shape[:2]
+        B = WB // W
+        send = x.reshape(W, B, Sl, *x.shape[2:]).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)                               # recv[j] = slice j
+        return recv.transpose(0, 1).reshape(B, W * Sl, *x.shape[2:])
+
+    def batch_all_gather(self, x: Tensor, dim: int = 0) -> Tensor:
+        """Concatenates every rank's tensor along ``dim`` (rank-major): masks / ids of all samples of the group."""
+        if self.world == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim)
+
+    # -- backward data movement ------------------------------------------------------------------------------
+    def _bwd_site(self, numel: int):
+        """Symmetric staging for the backward pass of one K/V shape: this rank's K and V (gathered by peers) and
+        its dK / dV contributions for all keys (reduced by their owners), two parities each."""
+        key = ("bwd", numel)
+        if key not in self._sites:
+            W = self.world
+            site = type("BwdSite", (), {})()
+            site.kv = self._alloc(2 * 2 * numel * 2)                # [parity][k|v][numel] bf16
+            site.dkv = self._alloc(2 * 2 * W * numel * 2)           # [parity][dk|dv][W * numel] bf16
+            site.flags = self._alloc(4 * MAX_RANKS * 2, zero=True)  # slot 0: K/V staged, slot 1: dK/dV staged
+            site.epoch = 0
+            self._sites[key] = site
+        return self._sites[key]
+
+    def _barrier(self, site, slot: int) -> None:
+        rc = self.comm_lib.otb_comm_barrier(_ptr_array(site.flags.peer_ptrs), c_int(self.rank), c_int(self.world),
+                                            c_int(slot), c_int(site.epoch), c_longlong(self.wait_budget),
+                                            c_void_p(self.status), self._stream())
+        if rc != 0:
+            raise RuntimeError(f"barrier launch failed ({rc})")
+
+    def gather_kv(self, k: Tensor, v: Tensor):
+        """K / V of all ranks, sequence-concatenated in rank order: ``(B, W * Sl, Hkv, D)`` each."""
+        if self.world == 1:
+            return k, v, None
+        if self.backend == "dist":
+            return self.all_gather_seq(k), self.all_gather_seq(v), None
+        from ..ops import cuda_ops
+        W, n = self.world, k.numel()
+        site = self._bwd_site(n)
+        site.epoch += 1
+        par = site.epoch & 1
+        stage = site.kv.view(torch.bfloat16, 4 * n)[par * 2 * n:(par + 1) * 2 * n]
+        stage[:n].view(k.shape).copy_(k)
+        stage[n:].view(v.shape).copy_(v)
+        self._barrier(site, 0)
+        out = torch.empty(W, 2, *k.shape, dtype=torch.bfloat16, device=self.device)
+        src = [p + par * 2 * n * 2 for p in site.kv.peer_ptrs]
+        rc = self.comm_lib.otb_comm_allgather_pull(_ptr_array(src), c_int(W), c_longlong(2 * n * 2),
+                                                   c_void_p(out.data_ptr()), c_int(296), c_void_p(self.status),
+                                                   self._stream())
+        if rc != 0:
+            raise RuntimeError(f"all-gather launch failed ({rc})")
+        cuda_ops.launch_count += 2
+        B, Sl = k.shape[:2]
+        # (W, B, Sl, ...) -> (B, W * Sl, ...)
+        kf = out[:, 0].transpose(0, 1).reshape(B, W * Sl, *k.shape[2:])
+        vf = out[:, 1].transpose(0, 1).reshape(B, W * Sl, *k.shape[2:])
+        return kf, vf, site
+
+    def reduce_scatter_kv_grads(self, dkf: Tensor, dvf: Tensor, site) -> tuple[Tensor, Tensor]:
+        """``dkf, dvf (B, W * Sl, Hkv, D)``: this rank's contributions for ALL keys -> the sums over ranks for the
+        keys this rank owns, ``(B, Sl, Hkv, D)``."""
+        W = self.world
+        if W == 1:
+            return dkf, dvf
+        B, S = dkf.shape[:2]
+        Sl = S // W
+        tail = dkf.shape[2:]
+        if self.backend == "dist":
+            both = torch.stack([dkf, dvf]).float()
+            dist.all_reduce(both, group=self.group)
+            mine = both[:, :, self.rank * Sl:(self.rank + 1) * Sl]
+            return mine[0].to(dkf.dtype).contiguous(), mine[1].to(dvf.dtype).contiguous()
+        from ..ops import cuda_ops
+        n = B * Sl * tail.numel()
+        par = site.epoch & 1
+        stage = site.dkv.view(torch.bfloat16, 4 * W * n)[par * 2 * W * n:(par + 1) * 2 * W * n]
+        # owner-major: [dk | dv][owner][B, Sl, ...], so every owner's slice is one contiguous range
+        stage[:W * n].view(W, B, Sl, *tail).copy_(dkf.reshape(B, W, Sl, *tail).transpose(0, 1))
+        stage[W * n:].view(W, B, Sl, *tail).copy_(dvf.reshape(B, W, Sl, *tail).transpose(0, 1))
+        self._barrier(site, 1)
+        out = torch.empty(2, B, Sl, *tail, dtype=torch.bfloat16, device=self.device)
+        src = [p + par * 2 * W * n * 2 for p in site.dkv.peer_ptrs]
+        for which in range(2):
+            rc = self.comm_lib.otb_comm_reduce_scatter_bf16(
+                _ptr_array(src), c_int(W), c_longlong(which * W * n + self.rank * n), c_longlong(n),
+                c_void_p(out[which].data_ptr()), c_int(296), c_void_p(self.status), self._stream())
+            if rc != 0:
+                raise RuntimeError(f"reduce-scatter launch failed ({rc})")
+        cuda_ops.launch_count += 3
+        return out[0], out[1]
+
     # -- autograd -------------------------------------------------------------------------------------------
     def attention(self, q: Tensor, k: Tensor, v: Tensor, q_blk: Tensor, k_blk_all: Tensor, q_valid: Tensor,
                   k_valid_all: Tensor, scale: float) -> Tensor:
@@ -171,18 +297,23 @@ class _CPAttention(torch.autograd.Function):
         from ..ops import prims
         cp: ContextParallel = ctx.cp
         q, k, v, o, lse, q_blk, k_blk_all, q_valid, k_valid_all = ctx.saved_tensors
-        Sl = q.shape[1]
-        r = cp.rank
         do = do.contiguous()
-        # all keys / values for dQ of the local queries
-        kf, vf = cp.all_gather_seq(k), cp.all_gather_seq(v)
-        dq, _, _ = prims.attn_bwd(do, q, kf, vf, o, lse, q_blk, k_blk_all, q_valid, k_valid_all, ctx.scale)
-        # all queries (and their dO / O / LSE) for dK, dV of the local keys
-        qf, dof, of_ = cp.all_gather_seq(q), cp.all_gather_seq(do), cp.all_gather_seq(o)
-        lsef = cp.all_gather_seq(lse, dim=2)
-        q_blk_all = cp.all_gather_seq(q_blk)
-        q_valid_all = cp.all_gather_seq(q_valid.to(torch.uint8)).bool()
-        k_blk = k_blk_all[:, r * Sl:(r + 1) * Sl].contiguous()
-        k_valid = k_valid_all[:, r * Sl:(r + 1) * Sl].contiguous()
-        _, dk, dv = prims.attn_bwd(dof, qf, k, v, of_, lsef, q_blk_all, k_blk, q_valid_all, k_valid, ctx.scale)
-        return None, dq, dk, dv, None, None, None, None, None
+        kf, vf, site = cp.gather_kv(k, v)
+        # own queries against all keys: dQ is final, dK / dV are this rank's contributions for every key
+        dq, dkf, dvf = prims.attn_bwd(do, q, kf.contiguous(), vf.contiguous(), o, lse, q_blk, k_blk_all, q_valid,
+                                      k_valid_all, ctx.scale)
+        dk, dv = cp.reduce_scatter_kv_grads(dkf, dvf, site)
+        return None, dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
+
+
+class _SeqExchange(torch.autograd.Function):
+    """All-to-all between the per-sample and the per-sequence-slice layout; the backward is the opposite exchange."""
+
+    @staticmethod
+    def forward(ctx, cp: ContextParallel, x, scatter: bool):
+        ctx.cp, ctx.scatter = cp, scatter
+        return cp._exchange(x, scatter)
+
+    @staticmethod
+    def backward(ctx, g):
+        return None, ctx.cp._exchange(g.contiguous(), not ctx.scatter), None

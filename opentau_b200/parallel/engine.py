@@ -81,7 +81,7 @@ class _ShardState:
         self.master = torch.cat([group.data[lo:hi].float() for lo, hi in self.slices])
         self.m = torch.zeros(off, dtype=torch.float32, device=dev)
         self.v = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.contiguous = len(self.slices) == 1
+        self.contiguous = not (sharded and world > 1)      # the part IS the whole group (no staging needed)
         # staging for the library path when the owned slices are not one contiguous range
         self.grad_stage = None if self.contiguous else torch.empty(off, dtype=group.dtype, device=dev)
         self.param_stage = None if self.contiguous else torch.empty(off, dtype=group.dtype, device=dev)

@@ -351,8 +351,12 @@ class PI05FlowMatching(nn.Module):
         mrope = pos.dim() == 3          # (3, B, L): interleaved multimodal RoPE, else one scalar position per token
         n_disc = self.discrete_block_len() if discrete_actions is not None else 0
         n_cross = prefix_embs.shape[1] - n_disc
-        (prefix_out, _), cache = pwe(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
-                                     q_valid=valid, fill_cache_len=n_cross, mrope=mrope)
+        cp = getattr(self, "context_parallel", None)
+        if cp is not None and cp.world > 1:
+            prefix_out, cache = self._prefix_pass_context_parallel(cp, prefix_embs, pos, blk, valid, n_cross, mrope)
+        else:
+            (prefix_out, _), cache = pwe(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
+                                         q_valid=valid, fill_cache_len=n_cross, mrope=mrope)
 
         B = actions.shape[0]
         device = actions.device
@@ -413,6 +417,49 @@ class PI05FlowMatching(nn.Module):
         if return_per_sample:
             out["MSE_per_sample"], out["CE_per_sample"] = mse_ps, ce_ps
         return out
+
+    def _prefix_pass_context_parallel(self, cp, prefix_embs, pos, blk, valid, n_cross: int, mrope: bool):
+        """The backbone's prefix pass with every sequence split over the ranks of ``cp``.
+
+        Embeddings, masks and losses stay per sample (each rank has its own samples); only the decoder layers see
+        the other layout, "all samples of the group, my slice of every sequence": the embeddings go through one
+        all-to-all before layer 0 and the hidden states through the opposite one after the last layer (both
+        differentiable), block-causal attention runs across the ranks inside the layers
+        (``parallel/cp.py``), and the per-layer keys / values come back per sample for the action expert, which
+        then runs on this rank's samples alone.  The reference has no counterpart (it drops history tokens before
+        the decoder, ``policies/pi07/video_encoder.py:767-778``).  Needs knowledge insulation: the cache exchange
+        carries no gradient."""
+        if not self.config.knowledge_insulation:
+            raise NotImplementedError("context parallelism needs knowledge_insulation (the prefix cache is detached)")
+        W, r = cp.world, cp.rank
+        B, S, _ = prefix_embs.shape
+        pad = (-S) % (W * 8)                                 # slices of equal length, 16-byte rows for the kernels
+        if pad:
+            prefix_embs = torch.nn.functional.pad(prefix_embs, (0, 0, 0, pad))
+            blk = torch.nn.functional.pad(blk, (0, pad), value=int(blk.max()) + 1)
+            valid = torch.nn.functional.pad(valid, (0, pad), value=False)
+            pos = torch.nn.functional.pad(pos, (0, pad))
+        Sp = S + pad
+        Sl = Sp // W
+        x = cp.seq_scatter(prefix_embs)                                      # (W*B, Sl, d)
+        blk_all = cp.batch_all_gather(blk.contiguous())                      # (W*B, Sp)
+        valid_all = cp.batch_all_gather(valid.to(torch.uint8).contiguous()).bool()
+        pos_all = cp.batch_all_gather(pos.contiguous(), dim=1 if mrope else 0)
+        sl = slice(r * Sl, (r + 1) * Sl)
+        (out_l, _), cache_l = self.wrapper(
+            inputs_embeds=[x, None], position_ids=pos_all[..., sl].contiguous(), q_blk=blk_all[:, sl].contiguous(),
+            q_valid=valid_all[:, sl].contiguous(), k_blk=blk_all, k_valid=valid_all, fill_cache_len=Sl, mrope=mrope,
+            cp=cp)
+        prefix_out = cp.seq_gather(out_l)[:, :S]
+        with torch.no_grad():
+            # (L, W*B, Sl, Hkv, D) -> per layer (B, Sp, Hkv, D) for this rank's samples; one exchange for all layers
+            L = cache_l.k.shape[0]
+            kv = torch.stack([cache_l.k.detach(), cache_l.v.detach()])       # (2, L, W*B, Sl, Hkv, D)
+            kv = kv.permute(2, 3, 0, 1, 4, 5).contiguous()                   # (W*B, Sl, 2, L, Hkv, D)
+            kv = cp._exchange(kv, scatter=False)                             # (B, Sp, 2, L, Hkv, D)
+            kv = kv[:, :n_cross].permute(2, 3, 0, 1, 4, 5).contiguous()      # (2, L, B, n_cross, Hkv, D)
+            cache = KVCache(kv[0], kv[1], valid[:, :n_cross].contiguous(), n_cross)
+        return prefix_out, cache
 
     # -- inference ---------------------------------------------------------------------------------
     @torch.no_grad()

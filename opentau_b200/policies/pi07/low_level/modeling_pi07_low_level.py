@@ -2,7 +2,9 @@
 
 Prefix layout (reference ``src/opentau/policies/pi07/low_level/modeling_pi07_low_level.py:1611-2013``):
 
-    videos (one bidirectional block per camera, current-frame tokens) | prompt (causal) | "State: " |
+    videos (one bidirectional block per camera, current-frame tokens; with ``keep_history_tokens`` one block per
+    camera AND frame, oldest first -- the long-context variant whose decoder sequence is split over GPUs by
+    ``parallel/cp.py``) | prompt (causal) | "State: " |
     T per-step state tokens (bidirectional) | state end | response? | metadata? | ";\\n "? |
     "Subgoal: " + subgoal images (bidirectional per camera) + ", "? | FAST action tokens (training only)
 
@@ -47,7 +49,13 @@ class PI07LowLevelFlowMatching(PI06FlowMatching):
         return self.wrapper.gemma3.model.multi_modal_projector
 
     def embed_video(self, video: Tensor, frame_valid: Tensor | None) -> Tensor:
-        """``video (B,T,C,H,W)`` -> projected current-frame tokens ``(B, tokens, d)``."""
+        """``video (B,T,C,H,W)`` -> projected current-frame tokens ``(B, tokens, d)``; with
+        ``config.keep_history_tokens`` the tokens of all ``T`` frames, ``(B, T, tokens, d)``."""
+        if getattr(self.config, "keep_history_tokens", False):
+            feats = self.video_encoder(video, frame_valid, keep_history=True)       # (B, T, N, d)
+            B, T = feats.shape[:2]
+            out = self._projector()(feats.flatten(0, 1))
+            return out.view(B, T, *out.shape[1:])
         feats = self.video_encoder(video, frame_valid)
         return self._projector()(feats)
 
@@ -73,6 +81,18 @@ class PI07LowLevelFlowMatching(PI06FlowMatching):
             vid = img if img.dim() == 5 else img[:, None]
             fv = frame_valid[:, -vid.shape[1]:] if frame_valid is not None else None
             e = self.embed_video(vid, fv)
+            if e.dim() == 4:
+                # long-context variant: every frame of every camera stays in the decoder as its own bidirectional
+                # block, oldest first; a block sees the blocks before it (frame-block-causal), padded history
+                # frames are masked out like padded cameras
+                T, n = e.shape[1], e.shape[2]
+                fm = m[:, None].expand(B, T) if fv is None else (m[:, None] & fv.bool())
+                fm = fm.clone()
+                fm[:, -1] = m                                   # the current frame is real whenever the camera is
+                for t in range(T):
+                    first = [1] if (embs or t > 0) else [0]
+                    add(e[:, t], fm[:, t, None].expand(B, n), first + [0] * (n - 1))
+                continue
             add(e, m[:, None].expand(B, e.shape[1]), [1] + [0] * (e.shape[1] - 1) if embs else [0] * e.shape[1])
         lang = w.embed_language_tokens(lang_tokens)
         add(lang, lang_masks.bool(), [1] * lang.shape[1])

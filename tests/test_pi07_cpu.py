@@ -186,3 +186,35 @@ def test_outlier_records_travel_from_forward_to_the_trainer(caplog):
         sums = update_policy(engine, [b])
     assert "outlier_records" not in sums and torch.isfinite(sums["loss"])
     assert any("normalised state dim 3" in r.getMessage() and "80.0" in r.getMessage() for r in caplog.records)
+
+
+def test_keep_history_tokens_puts_every_frame_in_the_decoder():
+    """Long-context variant: T frames x cameras stay in the decoder as frame blocks (reference drops them after the
+    encoder); the prefix grows by (T - 1) x tokens-per-frame, padded history frames are masked, the model trains and
+    samples, and the last frame block equals the default variant's only block."""
+    torch.manual_seed(0)
+    base, long = _ll(), _ll(keep_history_tokens=True)
+    long.load_state_dict(base.state_dict())
+    b = _history_batch()
+    vid = b["camera0"] * 2 - 1
+    e0 = base.model.embed_video(vid, None)
+    e1 = long.model.embed_video(vid, None)
+    assert e1.shape == (4, 3, *e0.shape[1:]) and torch.allclose(e1[:, -1], e0, atol=1e-5)
+    lang = torch.randint(3, 1000, (4, 16))
+    ones = torch.ones(4, 16, dtype=torch.bool)
+    fv = b["obs_history_is_pad"]
+    embs, pads, att, _ = long.model.embed_prefix([vid], [torch.ones(4, dtype=torch.bool)], lang, ones,
+                                                  history_is_pad=fv)
+    n = e0.shape[1]
+    assert embs.shape[1] == 3 * n + 16
+    assert not pads[0, :n].any() and pads[0, n:3 * n].all() and not pads[2, :2 * n].any() and pads[2, 2 * n:3 * n].all()
+    blocks = torch.cumsum(att[0].int(), 0)
+    assert blocks[0] == blocks[n - 1] and blocks[n] == blocks[0] + 1 and blocks[2 * n] == blocks[0] + 2
+    long.train()
+    out = long(b)
+    (out["MSE"] + out["CE"]).backward()
+    assert torch.isfinite(out["MSE"]) and torch.isfinite(out["CE"])
+    long.eval()
+    with torch.no_grad():
+        a = long.sample_actions({k: v for k, v in b.items() if k != "actions"})
+    assert a.shape[-2:] == (10, 32) and torch.isfinite(a).all()
