@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--strategy", default="zero2")
     ap.add_argument("--tiny", action="store_true", help="small geometry (plumbing check, not a benchmark)")
     ap.add_argument("--mode", default="train", choices=["train", "infer"])
+    ap.add_argument("--tp", type=int, default=1,
+                    help="--model cosmos3: tensor-parallel width of the frozen backbone; must equal --gpus or 1")
     ap.add_argument("--cp", type=int, default=1,
                     help="--model pi07: context-parallel width (ranks that share every sequence); must equal --gpus "
                          "or 1")
@@ -68,7 +70,7 @@ def parse_args():
                          "per-kernel device-time shares to PATH and exit without a benchmark line")
     a = ap.parse_args()
     if a.batch is None:
-        a.batch = {"pi06": 16, "pi07": 2}.get(a.model, 32)
+        a.batch = {"pi06": 16, "pi07": 2, "cosmos3": 8}.get(a.model, 32)
     return a
 
 
@@ -228,7 +230,31 @@ def pi07_batch(spec, device, seed: int, pinned: bool):
     return {k: (v.to(device) if hasattr(v, "to") else v) for k, v in b.items()}
 
 
+def build_policy_cosmos3(args, device):
+    """cosmos3 training geometry: frozen Qwen3-VL-32B-shaped backbone (64 layers, width 5120, 64 heads / 8 KV heads,
+    head dim 128, SwiGLU 25600), 2 cameras at 448x448 (patch 16, 2x2 merge: 196 tokens each), 128 prompt tokens,
+    a trainable 24-layer 1024-wide action expert that reads the last backbone layer (``condition_on_layer=63``),
+    state 32, action chunk 50x32.  ``--tp N`` shards the backbone over the N ranks with the GEMM -> reduce-scatter
+    and all-gather -> GEMM kernels (``parallel/tp.py``); the expert stays data parallel."""
+    from opentau_b200.scripts.benchmark_inference import build_cosmos3
+    policy, spec, cfg = build_cosmos3(2, 128, device, tiny=args.tiny, num_steps=10, image=448, expert_layers=24,
+                                      condition_on_layer=63, batch=args.batch, train=True, dropout=args.dropout)
+    spec.discrete_action_len = 0
+    return policy, spec, cfg
+
+
+def enable_tp(args, policy, device, world):
+    if args.tp <= 1:
+        return
+    if args.tp != world:
+        raise SystemExit("--tp must equal the number of ranks (one tensor-parallel group per node) or 1")
+    from opentau_b200.parallel.tp import TensorParallel
+    policy.enable_tensor_parallel(TensorParallel(device), free_replicated_weights=True)
+
+
 def build_policy(args, device):
+    if args.model == "cosmos3":
+        return build_policy_cosmos3(args, device)
     if args.model == "pi06":
         return build_policy_pi06(args, device)
     if args.model == "pi07":
@@ -281,8 +307,17 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
     published_p50 = {"cosmos3": 106.86}.get(args.model)
     prompt_len = 64 if args.model == "cosmos3" else 200
     num_steps = 5 if args.model == "pi06" else 10          # each policy's reference default
-    policy, batch = BUILDERS[args.model](3, prompt_len, device, tiny=args.tiny, num_steps=num_steps)
-    if use_cuda and args.impl == "ours":
+    if args.model == "cosmos3" and args.tp > 1:
+        # the 8-GPU serving geometry: 2 cameras at 448x448, 128 prompt tokens, 24-layer expert on backbone layer 63,
+        # backbone tensor parallel over the ranks, one observation per rank
+        policy, batch = BUILDERS["cosmos3"](2, 128, device, tiny=args.tiny, num_steps=num_steps, image=448,
+                                            expert_layers=24, condition_on_layer=63)
+        enable_tp(args, policy, device, world)
+    else:
+        policy, batch = BUILDERS[args.model](3, prompt_len, device, tiny=args.tiny, num_steps=num_steps)
+    # graph replay would repeat the flag epochs of the tensor-parallel kernels: those passes run eagerly
+    use_graphs = use_cuda and args.impl == "ours" and not (args.model == "cosmos3" and args.tp > 1)
+    if use_graphs:
         policy.enable_cuda_graphs(True)
     host = {k: (v.cpu().pin_memory() if use_cuda else v.cpu()) for k, v in batch.items() if hasattr(v, "cpu")}
     h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
@@ -350,7 +385,7 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
                                  "prompt <= 64 tokens)"),
                        "global_batch": world, "parallelism": f"replica x{world}",
                        "params": n_params, "denoise_steps": num_steps, "action_chunk": "50x32",
-                       "cuda_graph": bool(use_cuda and args.impl == "ours"),
+                       "cuda_graph": bool(use_graphs), "tensor_parallel": args.tp,
                        "l2": "each call streams every bf16 weight once (GBs, far more than the 126 MB L2); no "
                              "explicit flush"},
             "clocks": clocks,
@@ -440,7 +475,8 @@ def main():
         return rc
 
     from opentau_b200.datasets.synthetic import make_synthetic_batch
-    from opentau_b200.parallel.engine import OptimHyper, TrainEngine
+    from opentau_b200.parallel.engine import OptimHyper
+    from opentau_b200.parallel.fsdp import make_engine
 
     policy, spec, cfg = build_policy(args, device)
     if args.model == "pi07" and args.cp > 1:
@@ -448,7 +484,9 @@ def main():
             raise SystemExit("--cp must equal the number of ranks (one context-parallel group per node) or 1")
         from opentau_b200.parallel.cp import ContextParallel
         policy.model.context_parallel = ContextParallel(device)
-    engine = TrainEngine(policy, OptimHyper(lr=cfg.optimizer_lr, betas=tuple(cfg.optimizer_betas),
+    if args.model == "cosmos3":
+        enable_tp(args, policy, device, world)
+    engine = make_engine(policy, OptimHyper(lr=cfg.optimizer_lr, betas=tuple(cfg.optimizer_betas),
                                             eps=cfg.optimizer_eps, weight_decay=cfg.optimizer_weight_decay,
                                             grad_clip_norm=10.0),
                          device=device, strategy=args.strategy,
@@ -534,9 +572,7 @@ def main():
         cuda_ops.check_status()
         engine.check()
     # cross-rank evidence that the replicas stayed identical through the timed region
-    checksum = torch.zeros(1, dtype=torch.float64, device=device)
-    for g in engine.store.groups:
-        checksum += g.data.double().sum()
+    checksum = engine.param_checksum()
     sums = [checksum.clone() for _ in range(world)]
     if world > 1:
         dist.all_gather(sums, checksum)
@@ -549,7 +585,7 @@ def main():
     if rank == 0:
         peak_gb = torch.cuda.max_memory_allocated() / 2**30 if use_cuda else 0.0
         print(json.dumps({
-            "metric": f"{ {'pi06': 'pi0.6', 'pi07': 'pi0.7 long-context'}.get(args.model, 'pi0.5') } train samples/s/box", "value": round(value, 3),
+            "metric": f"{ {'pi06': 'pi0.6', 'pi07': 'pi0.7 long-context', 'cosmos3': 'cosmos3'}.get(args.model, 'pi0.5') } train samples/s/box", "value": round(value, 3),
             "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "weak",
@@ -560,13 +596,17 @@ def main():
                                  "pi0.7 controller, long context (SpaceTime SigLIP, 16 frames x 3 cams x 256 tokens "
                                  "kept in the decoder, Gemma-3-4B, 1024-wide expert, 128 prompt + 128 plan tokens)"
                                  if args.model == "pi07" else
+                                 "cosmos3 (frozen Qwen3-VL-32B-shaped backbone, 2 cams @448 -> 196 tokens each, 128 "
+                                 "prompt tokens, trainable 24-layer 1024-wide expert on backbone layer 63)"
+                                 if args.model == "cosmos3" else
                                  "pi0.5 full (SigLIP-So400m/14@224 x3 cams, Gemma-2B, Gemma-300M expert)"),
                        "global_batch": global_batch,
                        "seq_len": (getattr(spec, "history", 1) * 3 * 256 + spec.prompt_len + getattr(spec, "response_len", 0)
                                    + spec.discrete_action_len + 3) if args.model == "pi07"
                        else 3 * 256 + spec.prompt_len + 3 + 256,
                        "parallelism": f"dp{world}-{engine.strategy}-{engine.comm}" + (
-                           f"+cp{args.cp}" if args.model == "pi07" else ""), "params": n_params,
+                           f"+cp{args.cp}" if args.model == "pi07" else f"+tp{args.tp}" if args.model == "cosmos3"
+                           else ""), "params": n_params,
                        "knowledge_insulation": True, "fast_tokens": spec.discrete_action_len, "action_chunk": "50x32",
                        "dropout": args.dropout,
                        "frozen_weights": "none" if args.train_vision else "SigLIP tower (policy default "

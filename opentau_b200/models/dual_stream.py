@@ -63,6 +63,9 @@ class DualStreamDecoder(nn.Module):
         if len(n) != 1:
             raise ValueError(f"towers must have the same depth, got {n}")
         self.num_layers = n.pop()
+        # set by the parameter-sharded engine (parallel/fsdp.py): makes a layer's weights resident before the layer
+        # runs and before its backward pass; None for replicated parameters
+        self.param_gate = None
 
     # -- adaptive-norm conditions: one GEMM for all layers of a tower ------------------------------
     @staticmethod
@@ -292,7 +295,9 @@ class DualStreamDecoder(nn.Module):
         fill_in_place = (one_tower_inference and past is None and fill_cache_len is not None and not keep_graph
                          and fill_cache_len == T_new)
 
+        gate = self.param_gate
         for li in range(self.num_layers):
+            units = gate.enter([t.layers[li] for t, x in zip(towers, xs) if x is not None]) if gate is not None else None
             theta = towers[0].cfg.layer_theta(li)
             pl = past_layer_map[li] if past_layer_map is not None else li
             ck = past.k[pl, :, :past.length] if past is not None else None
@@ -309,6 +314,10 @@ class DualStreamDecoder(nn.Module):
                     kv_dst = (new_cache.k[li], new_cache.v[li], 0)
                 xs, nk, nv = self._layer(li, xs, tables(theta), q_blk, k_blk, q_valid, k_valid, ck, cv, mods, kv_dst,
                                          cp)
+            if units:
+                xs = gate.leave(xs, units)
+                if nk is not None and nk.requires_grad:       # keys / values that feed a later pass carry gradients too
+                    nk, nv = gate.leave([nk, nv], units)
             if layer_hook is not None:
                 xs = layer_hook(li, xs)
             if fill_cache_len is not None and not fill_in_place:

@@ -71,6 +71,19 @@ class SymmetricBuffer:
     def view(self, dtype: torch.dtype, numel: int) -> torch.Tensor:
         return self.bytes_tensor[: numel * torch.empty(0, dtype=dtype).element_size()].view(dtype)
 
+    def free(self, group=None) -> None:
+        """Collective: every rank unmaps its peers' allocations, then releases its own.  The caller must have
+        dropped every tensor that aliases the buffer."""
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        for p in self._opened:
+            self.lib.otb_comm_close_handle(c_void_p(p))
+        self._opened = []
+        dist.barrier(group=group)
+        self.bytes_tensor = self._holder = None
+        self.lib.otb_comm_free(c_void_p(self.local_ptr))
+        self.local_ptr = 0
+
 
 class PeerComm:
     """Flag protocol (all waits bounded, every flag carries the step's epoch):
@@ -134,11 +147,18 @@ class PeerComm:
                 raise NotImplementedError(f"peer-memory step: unsupported parameter dtype {g.dtype}")
             sh.g32 = torch.empty(sh.numel, dtype=torch.float32, device=self.device)
             for b, (lo, hi), off in zip(g.buckets, sh.slices, sh.offsets):
-                self.buckets.append(dict(bucket=b, shard=sh, lo=lo, n=hi - lo, off=off, params=g.data._symm,
+                # where the refreshed parameters of this rank's slice go: every rank's flat parameter buffer
+                # (replicated parameters); the parameter-sharded engine redirects it to the local at-rest shard
+                self.buckets.append(dict(bucket=b, shard=sh, lo=lo, n=hi - lo, off=off,
+                                         param_table=g.data._symm.table, param_world=self.world, param_lo=lo,
                                          grads=g.grad._symm, elem=g.data.element_size(),
                                          partial=self.partial[b.index * ppb:(b.index + 1) * ppb]))
         self.buckets.sort(key=lambda d: d["bucket"].index)
         self.scale = torch.ones(2, dtype=torch.float32, device=self.device)
+        # the status word as a tensor + a pinned mirror: each step ends with an asynchronous copy into the mirror,
+        # so the next step can look at it without synchronising the device
+        self._status_dev = torch.as_tensor(_DeviceBuffer(self.status, 16), device=self.device).view(torch.int32)
+        self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
         dist.barrier(group=self.group)
 
     def _stream(self) -> c_void_p:
@@ -178,15 +198,16 @@ class PeerComm:
         cuda_ops.launch_count += 1
         self._reduced.add(B["bucket"].index)
 
-    def reduce_bucket_async(self, index: int) -> None:
+    def reduce_bucket_async(self, index: int, last: bool = False) -> None:
         """Bucket ``index`` is complete on this rank as of the work already queued on the current stream: reduce
-        it on the side stream, under whatever the backward pass launches next."""
+        it on the side stream, under whatever the backward pass launches next.  ``last``: nothing else of the
+        backward pass is left to hide it behind, so it gets the whole GPU."""
         if index in self._reduced:
             raise RuntimeError(f"gradient bucket {index} was reduced twice in one step")
         main = torch.cuda.current_stream()
         self.side.wait_stream(main)
         with torch.cuda.stream(self.side):
-            self._reduce_bucket(self.buckets[index], self.OVERLAP_BLOCKS)
+            self._reduce_bucket(self.buckets[index], self.FLUSH_BLOCKS if last else self.OVERLAP_BLOCKS)
 
     def fused_step(self, *, lr: float, hyper, step: int) -> torch.Tensor:
         """Reduce what the backward pass has not reduced yet -> norm exchange -> AdamW + all-gather, all over peer
@@ -211,8 +232,9 @@ class PeerComm:
             nblocks = max(1, min(self.FLUSH_BLOCKS, (n // 8 + 511) // 512))
             rc = self.lib.otb_comm_adamw_allgather(
                 c_void_p(sh.master.data_ptr() + 4 * off), c_void_p(sh.g32.data_ptr() + 4 * off),
-                c_void_p(sh.m.data_ptr() + 4 * off), c_void_p(sh.v.data_ptr() + 4 * off), B["params"].table,
-                c_int(self.world), c_longlong(B["lo"]), c_longlong(n), c_float(lr), c_float(hyper.betas[0]),
+                c_void_p(sh.m.data_ptr() + 4 * off), c_void_p(sh.v.data_ptr() + 4 * off), B["param_table"],
+                c_int(B["param_world"]), c_longlong(B["param_lo"]), c_longlong(n), c_float(lr),
+                c_float(hyper.betas[0]),
                 c_float(hyper.betas[1]), c_float(hyper.eps), c_float(hyper.weight_decay), c_float(bc1), c_float(bc2),
                 c_void_p(self.scale.data_ptr()), c_int(nblocks), c_int(B["elem"]), c_void_p(self.status),
                 self._stream())
@@ -220,6 +242,7 @@ class PeerComm:
                 raise RuntimeError(f"adamw_allgather launch failed ({rc})")
         cuda_ops.launch_count += 1 + len(self.buckets)
         self.barrier(self.slot_end)  # all ranks' parameter stores have landed; gradients may be cleared
+        self._status_host.copy_(self._status_dev, non_blocking=True)
         self._pending_check = torch.cuda.Event()
         self._pending_check.record(main)
         return self.scale[1].clone()
@@ -232,6 +255,10 @@ class PeerComm:
         ev = self._pending_check
         if ev is None:
             return
-        if blocking or ev.query():
+        if blocking:
             self._pending_check = None
             cuda_ops.check_status()
+        elif ev.query():
+            self._pending_check = None
+            if int(self._status_host[0]) != 0:      # the mirror is complete once the event is: no device sync here
+                cuda_ops.check_status()

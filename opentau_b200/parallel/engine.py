@@ -66,8 +66,9 @@ class _ShardState:
     """fp32 masters / moments of this rank's part of one flat group: one slice ``[lo, hi)`` per gradient bucket
     (sharded) or the whole group (replicated), stored back to back; ``offsets[i]`` is where slice ``i`` starts."""
 
-    def __init__(self, group: FlatGroup, rank: int, world: int, sharded: bool):
-        if sharded and world > 1:
+    def __init__(self, group: FlatGroup, rank: int, world: int, sharded: bool, per_bucket: bool = False):
+        sharded = sharded and (world > 1 or per_bucket)
+        if sharded:
             self.slices = [(b.lo + rank * (b.numel // world), b.lo + (rank + 1) * (b.numel // world))
                            for b in group.buckets]
         else:
@@ -81,7 +82,7 @@ class _ShardState:
         self.master = torch.cat([group.data[lo:hi].float() for lo, hi in self.slices])
         self.m = torch.zeros(off, dtype=torch.float32, device=dev)
         self.v = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.contiguous = not (sharded and world > 1)      # the part IS the whole group (no staging needed)
+        self.contiguous = not sharded                      # the part IS the whole group (no staging needed)
         # staging for the library path when the owned slices are not one contiguous range
         self.grad_stage = None if self.contiguous else torch.empty(off, dtype=group.dtype, device=dev)
         self.param_stage = None if self.contiguous else torch.empty(off, dtype=group.dtype, device=dev)
@@ -91,6 +92,8 @@ class _ShardState:
 
 
 class TrainEngine:
+    _slice_per_bucket = False     # the parameter-sharded engine keeps one slice per bucket even on a single rank
+
     def __init__(self, policy: nn.Module, hyper: OptimHyper, *, device: torch.device | str,
                  lr_lambda: Callable[[int], float] | None = None, loss_weights: dict[str, float] | None = None,
                  strategy: str = "zero2", comm: str = "auto", process_group=None,
@@ -111,7 +114,7 @@ class TrainEngine:
                 "distributed.strategy in the training config), which wires the per-unit gather into the model")
         if strategy not in ("ddp", "zero2"):
             raise ValueError(f"unknown strategy {strategy!r}")
-        self.strategy = strategy if self.world > 1 else "ddp"
+        self.strategy = strategy if (self.world > 1 or self._slice_per_bucket) else "ddp"
         self.grad_accum_steps = grad_accum_steps
         self.p2p = None
         if comm == "auto":
@@ -124,13 +127,12 @@ class TrainEngine:
         self.comm = comm
         if self.p2p is not None:
             self.strategy = "zero2"
-        from .flat import DEFAULT_BUCKET_ELEMS
-        self.store = FlatParamStore(policy, self.device, pad_to=self.world, allocator=allocator,
-                                    bucket_elems=bucket_elems or DEFAULT_BUCKET_ELEMS)
+        self.store = self._make_store(policy, allocator, bucket_elems)
         if self.world > 1:
             self._broadcast_params()
-        sharded = self.strategy == "zero2"
-        self.shards: list[_ShardState] = [_ShardState(g, self.rank, self.world, sharded) for g in self.store.groups]
+        sharded = self.sharded_state = self.strategy == "zero2"   # optimizer state (and gradients) sharded by bucket
+        self.shards: list[_ShardState] = [_ShardState(g, self.rank, self.world, sharded, self._slice_per_bucket)
+                                          for g in self.store.groups]
         self.overlap = bool(overlap) and self.p2p is not None
         if self.p2p is not None:
             self.p2p.register(self.store, self.shards)
@@ -143,6 +145,34 @@ class TrainEngine:
         self._scale = torch.ones(2, dtype=torch.float32, device=self.device)
         self.last_grad_norm: Tensor | None = None
         self.store.zero_grad()
+        self._after_setup()
+
+    # -- extension points of the parameter-sharded engine (parallel/fsdp.py) ---------------------------------
+    def _make_store(self, policy, allocator, bucket_elems) -> FlatParamStore:
+        from .flat import DEFAULT_BUCKET_ELEMS
+        return FlatParamStore(policy, self.device, pad_to=self.world, allocator=allocator,
+                              bucket_elems=bucket_elems or DEFAULT_BUCKET_ELEMS)
+
+    def _after_setup(self) -> None:
+        pass
+
+    def _param_out(self, gi: int):
+        """Where the library step writes this rank's refreshed parameters of group ``gi`` (None: the replicated
+        flat buffer / its staging, followed by an all-gather)."""
+        return None
+
+    def _params_refreshed(self) -> None:
+        pass
+
+    def _live_slice(self, gi: int, lo: int, hi: int, off: int) -> Tensor:
+        return self.store.groups[gi].data[lo:hi]
+
+    def param_checksum(self) -> Tensor:
+        """Sum of all trainable parameters as one fp64 device scalar (equal on every rank when the replicas are)."""
+        s = torch.zeros(1, dtype=torch.float64, device=self.device)
+        for g in self.store.groups:
+            s += g.data.double().sum()
+        return s
 
     # -------------------------------------------------------------------------------------------
     def _broadcast_params(self) -> None:
@@ -195,7 +225,8 @@ class TrainEngine:
         if left == 0:
             self._bucket_open[b.index] -= 1
             if self._bucket_open[b.index] == 0:
-                self.p2p.reduce_bucket_async(b.index)
+                del self._bucket_open[b.index]
+                self.p2p.reduce_bucket_async(b.index, last=not self._bucket_open)
 
     def _arm(self) -> None:
         """Before the backward pass whose gradients get reduced (the last micro-batch of the step)."""
@@ -253,6 +284,7 @@ class TrainEngine:
             norm = self.p2p.fused_step(lr=lr, hyper=h, step=self.step_count)
         else:
             norm = self._library_step(lr)
+        self._params_refreshed()
         self.last_grad_norm = norm
         self.store.zero_grad()
         self._micro = 0
@@ -264,7 +296,7 @@ class TrainEngine:
         nccl = world > 1 and dist.get_backend(self.pg) == "nccl"
         grads: list[Tensor] = []
         for g, sh in zip(self.store.groups, self.shards):
-            if world > 1 and self.strategy == "zero2":
+            if world > 1 and self.sharded_state:
                 if nccl:
                     for b, (lo, hi), off in zip(g.buckets, sh.slices, sh.offsets):
                         dist.reduce_scatter_tensor(sh.grad_stage[off:off + hi - lo], g.grad[b.lo:b.hi],
@@ -289,7 +321,7 @@ class TrainEngine:
             total_sq = self._partials.sum()
         else:
             total_sq = sum((sg.float().pow(2).sum() for sg in grads), torch.zeros((), device=self.device))
-        if world > 1 and self.strategy == "zero2":
+        if world > 1 and self.sharded_state:
             dist.all_reduce(total_sq, group=self.pg)
         inv_world = 1.0 / world
         norm = total_sq.sqrt() * inv_world
@@ -299,9 +331,10 @@ class TrainEngine:
             coef = torch.ones((), device=self.device)
         self._scale[0] = coef * inv_world
         self._scale[1] = norm
-        for g, sh, sg in zip(self.store.groups, self.shards, grads):
+        for gi, (g, sh, sg) in enumerate(zip(self.store.groups, self.shards, grads)):
             # the refreshed parameters of this rank's part, in the group's dtype
-            p_out = g.data if sh.contiguous else sh.param_stage
+            local_only = self._param_out(gi)
+            p_out = local_only if local_only is not None else (g.data if sh.contiguous else sh.param_stage)
             if native:
                 from ..ops import cuda_ops
                 if g.dtype == torch.bfloat16:
@@ -315,7 +348,7 @@ class TrainEngine:
                 ops.ref.adamw_flat(sh.master, sg, sh.m, sh.v, p_out, lr=lr, beta1=h.betas[0], beta2=h.betas[1],
                                    eps=h.eps, weight_decay=h.weight_decay, step=self.step_count,
                                    grad_scale=float(self._scale[0]))
-            if world > 1 and self.strategy == "zero2":
+            if world > 1 and self.sharded_state and local_only is None:
                 for b, (lo, hi), off in zip(g.buckets, sh.slices, sh.offsets):
                     mine = sh.param_stage[off:off + hi - lo]
                     if nccl:
@@ -353,15 +386,14 @@ class TrainEngine:
             sh.m.copy_(sd[f"group{i}.m"])
             sh.v.copy_(sd[f"group{i}.v"])
             if rebuild_masters_from_live or f"group{i}.master" not in sd:
-                self._master_from_live(self.store.groups[i], sh)
+                self._master_from_live(i, sh)
             else:
                 sh.master.copy_(sd[f"group{i}.master"])
 
-    @staticmethod
-    def _master_from_live(g: FlatGroup, sh: _ShardState) -> None:
+    def _master_from_live(self, gi: int, sh: _ShardState) -> None:
         for (lo, hi), off in zip(sh.slices, sh.offsets):
-            sh.master[off:off + hi - lo].copy_(g.data[lo:hi].float())
+            sh.master[off:off + hi - lo].copy_(self._live_slice(gi, lo, hi, off).float())
 
     def rebuild_masters_from_live(self) -> None:
-        for g, sh in zip(self.store.groups, self.shards):
-            self._master_from_live(g, sh)
+        for gi, sh in enumerate(self.shards):
+            self._master_from_live(gi, sh)

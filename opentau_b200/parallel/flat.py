@@ -67,9 +67,13 @@ class FlatParamStore:
     """Re-homes the trainable parameters of ``module`` into flat buffers on ``device``."""
 
     def __init__(self, module: nn.Module, device: torch.device | str, pad_to: int = 1,
-                 allocator=None, bucket_elems: int = DEFAULT_BUCKET_ELEMS):
+                 allocator=None, bucket_elems: int = DEFAULT_BUCKET_ELEMS, bucket_key=None):
+        """``bucket_key(name) -> str`` (optional) names the bucket of every parameter: parameters with one key are
+        laid out together as ONE bucket whatever its size (keys in order of first appearance).  The
+        parameter-sharded engine uses it to make a bucket the unit it gathers before a layer runs."""
         self.device = torch.device(device)
         self.world = max(1, pad_to)
+        self.bucket_keys: list[str] = []
         by_dtype: dict[torch.dtype, list[tuple[str, nn.Parameter]]] = {}
         seen: set[int] = set()
         for name, p in module.named_parameters():
@@ -82,18 +86,32 @@ class FlatParamStore:
         self.buckets: list[Bucket] = []
         step = ALIGN_ELEMS * self.world
         for gi, (dtype, items) in enumerate(by_dtype.items()):
-            items.sort(key=lambda it: _late_gradient(it[0]))         # stable: late-gradient parameters go last
+            keys = None
+            if bucket_key is not None:
+                order: dict[str, int] = {}
+                for name, _ in items:
+                    order.setdefault(bucket_key(name), len(order))
+                items.sort(key=lambda it: order[bucket_key(it[0])])  # stable: one run of parameters per key
+                keys = [bucket_key(name) for name, _ in items]
+            else:
+                items.sort(key=lambda it: _late_gradient(it[0]))     # stable: late-gradient parameters go last
             offsets, off = [], 0
             buckets: list[Bucket] = []
             b_lo, b_first = 0, 0
             for pi, (_, p) in enumerate(items):
-                if off - b_lo >= bucket_elems:                       # close the bucket in front of this parameter
+                close = (keys[pi] != keys[pi - 1]) if (keys is not None and pi > 0) else \
+                    (keys is None and off - b_lo >= bucket_elems)
+                if close:                                            # close the bucket in front of this parameter
+                    if keys is not None:
+                        self.bucket_keys.append(keys[pi - 1])
                     off = _round_up(off, step)
                     buckets.append(Bucket(len(self.buckets) + len(buckets), gi, b_lo, off, b_first, pi))
                     b_lo, b_first = off, pi
                 offsets.append(off)
                 off = _round_up(off + p.numel(), ALIGN_ELEMS)
             total = _round_up(off, step)
+            if keys is not None:
+                self.bucket_keys.append(keys[-1])
             buckets.append(Bucket(len(self.buckets) + len(buckets), gi, b_lo, total, b_first, len(items)))
             self.buckets += buckets
             data = alloc(total, dtype)

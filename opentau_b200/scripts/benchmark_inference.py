@@ -66,7 +66,8 @@ def build_pi05(cams: int, prompt_len: int, device, tiny: bool = False, num_steps
 
 
 def build_cosmos3(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 10,
-                  depth: int | None = None):
+                  depth: int | None = None, image: int = 224, expert_layers: int | None = None,
+                  condition_on_layer: int | None = None, batch: int = 1, train: bool = False, dropout: float = 0.0):
     """The workload of the reference's published cosmos3 latency table (``docs/source/tutorials/benchmarking.rst:
     437-510``): the full 64-layer Qwen3-VL-32B-shaped backbone, the 64-layer action expert reading a per-layer KV
     cache, ``cams`` cameras at 224x224, a prompt capped at ``prompt_len`` tokens, a 50-action chunk.  Weights are
@@ -75,11 +76,18 @@ def build_cosmos3(cams: int, prompt_len: int, device, tiny: bool = False, num_st
     from ..datasets.synthetic import SyntheticSpec, identity_stats, make_synthetic_batch
     from ..policies.cosmos3.configuration_cosmos3 import Cosmos3Config
     from ..policies.cosmos3.modeling_cosmos3 import Cosmos3Policy
-    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, 224, 224)) for i in range(cams)}
+    if tiny:
+        image = 224
+    feats = {f"camera{i}": PolicyFeature(FeatureType.VISUAL, (3, image, image)) for i in range(cams)}
     feats["state"] = PolicyFeature(FeatureType.STATE, (32,))
-    kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=prompt_len, num_steps=num_steps, dropout=0.0,
-              device=str(device), input_features=feats, load_pretrained_backbone=False, image_resize=224,
+    kw = dict(chunk_size=50, n_action_steps=50, prompt_max_length=prompt_len, num_steps=num_steps, dropout=dropout,
+              device=str(device), input_features=feats, load_pretrained_backbone=False, image_resize=image,
               output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))})
+    if expert_layers is not None:
+        # an expert whose depth differs from the backbone's reads ONE backbone layer's keys / values
+        # (reference cosmos3/qwen3vl_with_expert.py:405-432)
+        kw.update(expert_num_hidden_layers=expert_layers,
+                  condition_on_layer=condition_on_layer if condition_on_layer is not None else -1)
     vocab = 151936
     if tiny:
         kw.update(backbone=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
@@ -92,9 +100,11 @@ def build_cosmos3(cams: int, prompt_len: int, device, tiny: bool = False, num_st
         vocab = 512
     if depth is not None:                       # same layers, fewer of them: a small case for profiling
         kw.update(backbone=dict(num_hidden_layers=depth), expert_num_hidden_layers=depth)
+    if tiny and expert_layers is not None:
+        kw.update(expert_num_hidden_layers=3, condition_on_layer=1)
     cfg = Cosmos3Config(**kw)
-    spec = SyntheticSpec(batch_size=1, num_cams=cams, prompt_len=prompt_len, vocab_size=vocab, state_dim=32,
-                         action_dim=32, chunk_size=50, image_dtype=torch.bfloat16)
+    spec = SyntheticSpec(batch_size=batch, num_cams=cams, resolution=(image, image), prompt_len=prompt_len,
+                         vocab_size=vocab, state_dim=32, action_dim=32, chunk_size=50, image_dtype=torch.bfloat16)
     torch.manual_seed(0)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)     # 33 B parameters: never materialise them in fp32
@@ -103,9 +113,11 @@ def build_cosmos3(cams: int, prompt_len: int, device, tiny: bool = False, num_st
             policy = Cosmos3Policy(cfg, per_dataset_stats=[identity_stats()])
     finally:
         torch.set_default_dtype(prev)
-    policy.to(device).to(torch.bfloat16).eval()
-    batch = make_synthetic_batch(spec, device=device, seed=3)
-    return policy, batch
+    policy.to(device).to(torch.bfloat16)
+    policy.train() if train else policy.eval()
+    if train:
+        return policy, spec, cfg
+    return policy, make_synthetic_batch(spec, device=device, seed=3)
 
 
 def build_pi06(cams: int, prompt_len: int, device, tiny: bool = False, num_steps: int = 5,

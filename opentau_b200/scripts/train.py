@@ -33,6 +33,7 @@ from ..configs.train import TrainPipelineConfig
 from ..datasets.factory import make_dataset_mixture, warn_if_resumed_split_differs
 from ..datasets.utils import cycle
 from ..parallel import control
+from ..parallel.fsdp import make_engine
 from ..parallel.engine import OptimHyper, TrainEngine, assemble_weighted_loss
 from ..policies.factory import make_policy
 from ..utils.logging_utils import AverageMeter, MetricsTracker, format_big_number, init_logging
@@ -226,7 +227,7 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
                        eps=getattr(opt_cfg, "eps", 1e-8), weight_decay=getattr(opt_cfg, "weight_decay", 0.0),
                        grad_clip_norm=clip)
     lr_lambda = sched_cfg.lr_lambda(cfg.steps) if sched_cfg is not None else None
-    engine = TrainEngine(policy, hyper, device=device, lr_lambda=lr_lambda, loss_weights=cfg.loss_weighting,
+    engine = make_engine(policy, hyper, device=device, lr_lambda=lr_lambda, loss_weights=cfg.loss_weighting,
                          strategy=getattr(dcfg, "strategy", "zero2"), comm=getattr(dcfg, "comm", "auto"),
                          grad_accum_steps=ga)
     n_params = sum(p.numel() for p in policy.parameters())
@@ -244,7 +245,11 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
             raise RuntimeError(f"checkpoint {last} is incomplete (interrupted save)")
         from safetensors.torch import load_file
         sd = load_file(str(last / "model.safetensors"))
-        missing, unexpected = policy.load_state_dict(type(policy)._fix_state_dict_keys(sd, cfg.policy), strict=False)
+        import contextlib
+        # a parameter-sharded engine holds slices: load into a temporary full copy and write the slices back
+        with (engine.full_params(writeback=True) if hasattr(engine, "full_params") else contextlib.nullcontext()):
+            missing, unexpected = policy.load_state_dict(type(policy)._fix_state_dict_keys(sd, cfg.policy),
+                                                         strict=False)
         bad = [k for k in missing if "normalize" not in k]
         if bad:
             raise RuntimeError(f"checkpoint misses {len(bad)} tensors, e.g. {bad[:3]}")

@@ -63,8 +63,12 @@ def save_checkpoint(checkpoint_dir: Path, step: int, cfg, policy, engine=None, r
     its marker.  Every rank must call this (no rank may decide on its own from the directory's existence)."""
     from safetensors.torch import save_file
     checkpoint_dir.mkdir(parents=True, exist_ok=True)
+    # a parameter-sharded engine holds 1 / W of every weight: all ranks gather (a collective), rank 0 writes
+    import contextlib
+    with (engine.full_params() if hasattr(engine, "full_params") else contextlib.nullcontext()):
+        if is_main:
+            policy.save_pretrained(checkpoint_dir)
     if is_main:
-        policy.save_pretrained(checkpoint_dir)
         cfg.save_pretrained(checkpoint_dir)
         save_training_step(step, checkpoint_dir)
         (checkpoint_dir / "world_size.json").write_text(json.dumps({"world_size": getattr(engine, "world", 1)}))

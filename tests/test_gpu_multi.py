@@ -28,8 +28,9 @@ def _worker(rank, world, port, comm, ret, variant="plain"):
         train_vision = variant == "mixed"            # the SigLIP patch / position tables stay fp32: a second flat group
         pol = tiny_pi05(device="cuda", seed=20 + rank, freeze_vision_encoder=not train_vision).to(torch.bfloat16)
         pol.train()
-        eng = TrainEngine(pol, OptimHyper(lr=1e-3, grad_clip_norm=1.0), device=dev,
-                          strategy="ddp" if variant == "ddp" else "zero2", comm=comm,
+        from opentau_b200.parallel.fsdp import make_engine
+        strategy = {"ddp": "ddp", "fsdp": "fsdp" if comm == "p2p" else "zero2"}.get(variant, "zero2")
+        eng = make_engine(pol, OptimHyper(lr=1e-3, grad_clip_norm=1.0), device=dev, strategy=strategy, comm=comm,
                           overlap=variant != "no_overlap", bucket_elems=150_000)
         key = f"{comm}:{variant}"
         batch = tiny_batch(device=dev, seed=100 + rank)
@@ -47,7 +48,9 @@ def _worker(rank, world, port, comm, ret, variant="plain"):
         torch.cuda.synchronize()
         cuda_ops.check_status()
         eng.check()
-        named = {n: p.detach().float().cpu() for n, p in pol.named_parameters() if p.requires_grad}
+        import contextlib
+        with (eng.full_params() if hasattr(eng, "full_params") else contextlib.nullcontext()):
+            named = {n: p.detach().float().cpu() for n, p in pol.named_parameters() if p.requires_grad}
         if rank == 0:
             ret[key] = (named, norms, len(eng.store.groups), len(eng.store.buckets),
                         bool(eng.p2p is not None and eng._expected is not None))
@@ -61,11 +64,12 @@ def _worker(rank, world, port, comm, ret, variant="plain"):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("variant", ["plain", "no_overlap", "ddp", "mixed"])
+@pytest.mark.parametrize("variant", ["plain", "no_overlap", "ddp", "mixed", "fsdp"])
 def test_peer_memory_step_matches_nccl_step(variant):
     """The bucketed, overlapped peer-memory step gives the parameters and gradient norms of the library step:
     with the reduction under the backward pass and without, under the ``ddp`` label (the norm must not be counted
-    once per rank), and for a model with an fp32 parameter group beside the bf16 one."""
+    once per rank), for a model with an fp32 parameter group beside the bf16 one, and with the parameters
+    themselves sharded (``fsdp``: per-layer gathers by peer loads into rotating slots)."""
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
@@ -255,3 +259,134 @@ def test_fused_context_parallel_attention_matches_single_gpu():
     ret = mgr.dict()
     mp.spawn(_cp_worker, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret["cp_err"] < 0.06
+
+
+def _cp_policy_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from helpers import tiny_batch, tiny_pi05
+        from opentau_b200.ops import cuda_ops
+        from opentau_b200.parallel.cp import ContextParallel
+        batch = tiny_batch(device=dev, batch_size=2, seed=50 + rank)
+        g = torch.Generator().manual_seed(3 + rank)
+        noise, time = torch.randn(2, 10, 32, generator=g).to(dev), torch.full((2,), 0.4, device=dev)
+        results = []
+        for use_cp in (False, True):
+            pol = tiny_pi05(device="cuda", seed=7).to(torch.bfloat16).train()
+            if use_cp:
+                pol.model.context_parallel = ContextParallel(dev, backend="p2p", wait_budget=4_000_000_000)
+            for _ in range(2):                      # twice: both parities of the staging buffers
+                pol.zero_grad(set_to_none=True)
+                out = pol(batch, noise=noise, time=time)
+                (out["MSE"] + out["CE"]).backward()
+            grads = {}
+            for n, p in pol.named_parameters():
+                if p.requires_grad and p.grad is not None:
+                    gsum = p.grad.float().clone()
+                    dist.all_reduce(gsum)
+                    grads[n] = gsum
+            results.append((float(out["MSE"]), float(out["CE"]), grads))
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        (m0, c0, g0), (m1, c1, g1) = results
+        worst = max(float((g0[n] - g1[n]).abs().max()) / (float(g0[n].abs().max()) + 1e-3) for n in g0)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (abs(m0 - m1) / max(1.0, abs(m0)), abs(c0 - c1) / max(1.0, abs(c0)), worst))
+        if rank == 0:
+            ret["cp_policy"] = gathered
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_policy_under_context_parallelism_matches_the_unsharded_policy():
+    """Tiny pi0.5 in bf16 with the prefix split over two GPUs (fused forward kernel, sharded backward, peer-memory
+    K/V gather and dK/dV reduce-scatter): losses and rank-summed gradients equal the unsharded pass."""
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_cp_policy_worker, args=(2, free_port(), ret), nprocs=2, join=True)
+    for dm, dc, worst in ret["cp_policy"]:
+        assert dm < 3e-2 and dc < 3e-2 and worst < 0.15, ret["cp_policy"]
+
+
+def _tp_backbone_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from helpers import tiny_batch
+        from opentau_b200.configs.types import FeatureType, PolicyFeature
+        from opentau_b200.datasets.synthetic import identity_stats
+        from opentau_b200.ops import cuda_ops
+        from opentau_b200.parallel.tp import TensorParallel
+        from opentau_b200.policies.cosmos3.tensor_parallel import TPBackbone
+        from opentau_b200.policies.factory import make_policy, make_policy_config
+        feats = {"camera0": PolicyFeature(FeatureType.VISUAL, (3, 224, 224)),
+                 "state": PolicyFeature(FeatureType.STATE, (32,))}
+        errs, scale = [], 1.0
+        for col in (None, 1):
+            torch.manual_seed(0)
+            cfg = make_policy_config(
+                "cosmos3", chunk_size=10, n_action_steps=10, prompt_max_length=32, dropout=0.0, device=str(dev),
+                image_resize=128, input_features=dict(feats), num_steps=3, load_pretrained_backbone=False,
+                output_features={"actions": PolicyFeature(FeatureType.ACTION, (32,))},
+                backbone=dict(hidden_size=512, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+                              head_dim=64, intermediate_size=1024, vocab_size=1024, mrope_sections=(12, 10, 10)),
+                vision=dict(hidden_size=64, depth=2, num_heads=4, intermediate_size=128, out_hidden_size=512,
+                            num_position_embeddings=64, deepstack_visual_indexes=(0,)),
+                expert_hidden_size=128, expert_intermediate_size=256, expert_num_hidden_layers=2,
+                expert_num_attention_heads=4, expert_num_key_value_heads=2, expert_head_dim=64,
+                expert_adarms_cond_dim=32, proj_width=128, condition_on_layer=col)
+            pol = make_policy(cfg, per_dataset_stats=[identity_stats()]).to(dev).to(torch.bfloat16).eval()
+            for p in pol.parameters():
+                dist.broadcast(p.data, 0)
+            b = tiny_batch(device=dev, batch_size=4, prompt_len=32)
+            images, masks = pol.prepare_images(b)
+            lt, lm = pol.prepare_language(b)
+            w = pol.model.qwen3vl_with_expert
+            with torch.no_grad():
+                full, pos_full = w.run_prefix(images, masks, lt, lm)
+            sl = slice(rank * 2, rank * 2 + 2)
+            tpb = TPBackbone(w, TensorParallel(dev, backend="p2p", wait_budget=4_000_000_000))
+            for _ in range(2):                      # twice: both parities of the kernels' workspaces
+                cache, pos = tpb.run_prefix([im[sl] for im in images], [m[sl] for m in masks], lt[sl], lm[sl])
+            layers = [col] if col is not None else range(full.k.shape[0])
+            n = full.length
+            for li in layers:
+                errs.append(float((cache.k[li][:, :n].float() - full.k[li, sl, :n].float()).abs().max()))
+                errs.append(float((cache.v[li][:, :n].float() - full.v[li, sl, :n].float()).abs().max()))
+                scale = max(scale, float(full.k[li].float().abs().max()), float(full.v[li].float().abs().max()))
+            assert torch.equal(pos, pos_full[:, sl])
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (max(errs), scale))
+        if rank == 0:
+            ret["tpb"] = gathered
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_cosmos3_tensor_parallel_backbone_matches_the_replicated_backbone_on_gpus():
+    """``TPBackbone.run_prefix`` with the fused GEMM + collective kernels on two GPUs leaves each rank the same
+    per-layer keys / values for its own samples as the replicated backbone (all layers, and one conditioning layer)."""
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_tp_backbone_worker, args=(2, free_port(), ret), nprocs=2, join=True)
+    for err, scale in ret["tpb"]:
+        assert err < 0.04 * scale, ret["tpb"]

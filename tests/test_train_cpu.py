@@ -95,3 +95,19 @@ def test_running_best_checkpoints_are_kept_and_complete(tmp_path):
         if t.would_keep(v):
             t.update(sid, v)
     assert t.kept == {"b", "c"}
+
+
+def test_train_and_resume_with_sharded_parameters(tmp_path):
+    """``distributed.strategy = fsdp`` through the trainer: the checkpoint holds full weights (gathered for the
+    export), and a resumed run loads them back into the shards and continues."""
+    from safetensors.torch import load_file
+    out = tmp_path / "run"
+    torch.manual_seed(0)
+    first = train(_cfg(out, 4, distributed={"strategy": "fsdp"}, val_freq=0))
+    assert first["loss"] == first["loss"]
+    saved = load_file(str(out / "checkpoints" / "000004" / "model.safetensors"))
+    name = next(k for k in saved if k.endswith("layers.1.mlp.down_proj.weight"))
+    assert saved[name].abs().sum() > 0
+    resumed = train(_cfg(out, 6, resume=True, distributed={"strategy": "fsdp"}, val_freq=0))
+    rows = [json.loads(line) for line in (out / "metrics.jsonl").read_text().splitlines()]
+    assert rows[-1]["step"] == 6 and resumed["loss"] < rows[0]["Training/Loss"] * 1.5
