@@ -584,6 +584,9 @@ def main():
     e2e_value = global_batch * args.steps / (ms_e2e / 1e3)
     if rank == 0:
         peak_gb = torch.cuda.max_memory_allocated() / 2**30 if use_cuda else 0.0
+        # the symmetric (peer-mapped) buffers are allocated outside the caching allocator: the device-wide figure
+        # is the one that compares strategies
+        free_b, total_b = torch.cuda.mem_get_info() if use_cuda else (0, 0)
         print(json.dumps({
             "metric": f"{ {'pi06': 'pi0.6', 'pi07': 'pi0.7 long-context', 'cosmos3': 'cosmos3'}.get(args.model, 'pi0.5') } train samples/s/box", "value": round(value, 3),
             "unit": "samples/s",
@@ -613,7 +616,8 @@ def main():
                                                                            "freeze_vision_encoder=true)",
                        "trainable_params": sum(p.numel() for p in policy.parameters() if p.requires_grad),
                        "l2": "per-step working set (tens of GB of activations) far exceeds the 126 MB L2; "
-                             "no explicit flush", "peak_mem_gib": round(peak_gb, 2)},
+                             "no explicit flush", "peak_mem_gib": round(peak_gb, 2),
+                       "device_mem_in_use_gib": round((total_b - free_b) / 2**30, 2)},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 3), "unit": "samples/s", "ms_per_step": round(ms_e2e / args.steps, 3),
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": last_loss},

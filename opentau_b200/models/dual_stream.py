@@ -208,8 +208,7 @@ class DualStreamDecoder(nn.Module):
                 op = layer.self_attn.o_proj
                 y = ops.linear_gated_residual(a.to(op.weight.dtype), op.weight, op.bias, x, g1)
             else:
-                o = drop(layer.self_attn.o_proj(a))
-                y = ops.gated_residual(x, o, g1)
+                y = ops.dropout_gated_residual(x, layer.self_attn.o_proj(a), g1, drop.p, True)
             if mods[ti] is not None:
                 n, g2 = layer.post_attention_layernorm(y, precomputed=mods[ti][2 * li + 1])
             else:
@@ -221,8 +220,7 @@ class DualStreamDecoder(nn.Module):
                 outs.append(ops.gated_mlp_gated_residual(n.to(mlp.gate_up_proj.weight.dtype), mlp.gate_up_proj.weight,
                                                          mlp.down_proj.weight, mlp.act, y, g2))
             else:
-                m = drop(layer.mlp(n))
-                outs.append(ops.gated_residual(y, m, g2))
+                outs.append(ops.dropout_gated_residual(y, layer.mlp(n), g2, drop.p, True))
         return outs, new_k, new_v
 
     def forward(self, inputs_embeds: list[Tensor | None], position_ids: Tensor, q_blk: Tensor,

@@ -18,6 +18,7 @@ from dataclasses import dataclass, field
 import torch
 from torch import Tensor, nn
 
+from .. import ops
 from .dual_stream import DualStreamDecoder
 from .layers import DecoderLayer, Linear, TowerConfig, make_norm
 from .siglip import Gemma3Projector, SiglipConfig, SiglipVisionModel
@@ -170,11 +171,11 @@ class Gemma3WithExpertModel(nn.Module):
 
     def embed_language_tokens(self, tokens: Tensor) -> Tensor:
         """Gemma-3 token embeddings are scaled by ``sqrt(hidden)`` inside the embedding layer."""
-        e = self.gemma3.model.language_model.embed_tokens(tokens)
-        return e * math.sqrt(self.vlm_cfg.hidden_size)
+        return ops.embedding(self.gemma3.model.language_model.embed_tokens.weight, tokens,
+                             math.sqrt(self.vlm_cfg.hidden_size))
 
     def embed_discrete_actions(self, actions: Tensor) -> Tensor:
-        return self.discrete_action_embedding(actions)
+        return ops.embedding(self.discrete_action_embedding.weight, actions, padding_idx=0)
 
     def lm_head_weight(self) -> Tensor:
         return self.gemma3.model.language_model.embed_tokens.weight

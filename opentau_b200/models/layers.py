@@ -260,7 +260,5 @@ class Tower(nn.Module):
         self.norm = make_norm(cfg)
 
     def embed(self, tokens: Tensor) -> Tensor:
-        e = self.embed_tokens(tokens)
-        if self.cfg.embed_scale:
-            e = e * math.sqrt(self.cfg.hidden_size)
-        return e
+        scale = math.sqrt(self.cfg.hidden_size) if self.cfg.embed_scale else 1.0
+        return ops.embedding(self.embed_tokens.weight, tokens, scale)

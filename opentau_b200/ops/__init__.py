@@ -225,8 +225,38 @@ def mha(q: Tensor, k: Tensor, v: Tensor, scale: float, add_mask: Tensor | None =
 
 def flow_matching_masked_mse(u_t, v_t, prefix_mask=None, actions_is_pad=None, real_action_dim=None,
                              return_per_sample=False):
+    if u_t.is_cuda and not oracle_mode():
+        loss, sums, counts = fused.MaskedMSEFn.apply(u_t, v_t, prefix_mask, actions_is_pad, real_action_dim)
+        return (loss, (sums, counts)) if return_per_sample else loss
     return ref.flow_matching_masked_mse(u_t, v_t, prefix_mask, actions_is_pad, real_action_dim,
                                         return_per_sample)
+
+
+def dropout_gated_residual(x: Tensor, y: Tensor, gate: Tensor | None, p: float, training: bool) -> Tensor:
+    """``x + gate * dropout(y, p)`` (``gate=None``: plain residual).  The reference applies ``nn.Dropout`` after the
+    attention output projection and after the MLP, then the (gated) residual
+    (``pi05/paligemma_with_expert.py:783-792``); on the GPU the three are one kernel in each direction."""
+    import torch
+    if not training or p <= 0.0:
+        return gated_residual(x, y, gate)
+    if (x.is_cuda and not oracle_mode() and x.dtype == torch.bfloat16 and y.dtype == x.dtype and x.dim() == 3
+            and x.shape[-1] % 8 == 0 and (gate is None or (gate.dtype == x.dtype and gate.dim() == 3 and (
+                x.shape[0] * x.shape[1]) % (gate.shape[0] * gate.shape[1]) == 0 and gate.shape[0] == x.shape[0]))):
+        return fused.dropout_residual(x, y, gate, p)
+    return gated_residual(x, torch.nn.functional.dropout(y, p, True), gate)
+
+
+def embedding(table: Tensor, ids: Tensor, scale: float = 1.0, padding_idx: int | None = None) -> Tensor:
+    """``table[ids] * scale``: gather kernel forward, deterministic scatter-add backward (no dense one-hot product,
+    no atomics; row ``padding_idx`` takes no gradient); plain indexing on the CPU / in oracle mode."""
+    import torch
+    if table.is_cuda and not oracle_mode() and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0:
+        if torch.is_grad_enabled() and table.requires_grad:
+            return fused.embedding(table, ids, scale, padding_idx)
+        from . import cuda_ops
+        return cuda_ops.embed_fwd(table, ids, scale)
+    out = torch.nn.functional.embedding(ids, table, padding_idx=padding_idx)
+    return out * scale if scale != 1.0 else out
 
 
 def linear_cross_entropy(h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor) -> Tensor:
@@ -245,6 +275,6 @@ def resize_with_pad(img: Tensor, width: int, height: int, pad_value: float = -1.
 __all__ = [
     "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "linear_gated_residual", "gated_mlp_gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
     "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
-    "resize_with_pad", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
+    "resize_with_pad", "dropout_gated_residual", "embedding", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
     "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "euler_step", "patch_embed", "oracle_mode", "prims", "fused", "ref",
 ]

@@ -1,0 +1,336 @@
+// Training-side elementwise kernels that replace short chains of library launches in the step:
+//
+//   drop_res_fwd / drop_res_bwd   out = x + gate * dropout(y): the dropout after the attention output projection and
+//                                 after the MLP, its (optional, per-sample) gate and the residual add in ONE pass.
+//                                 The keep mask is never stored: both directions regenerate it from a counter-based
+//                                 generator (Philox4x32-10 keyed by the call's seed, one call per 8 elements).
+//   masked_mse_fwd / _bwd         flow-matching loss: sum and count of (u - v)^2 over the unmasked elements, per
+//                                 sample, in one pass; the backward writes dv directly.
+//   embed_fwd / embed_bwd         token embedding gather (with the sqrt(d) scale) and its scatter-add backward into
+//                                 an fp32 or bf16 gradient table without a dense one-hot product: rows are processed
+//                                 by token ORDER (sorted ids), so each table row is written by one warp, in a fixed
+//                                 order, without atomics.
+//
+// All kernels are bandwidth bound: 16-byte accesses, grid-stride loops, fp32 math.
+#include "common.cuh"
+
+namespace otb {
+
+// ------------------------------------------------------------------------------------------ Philox4x32-10
+struct U4 {
+  unsigned x, y, z, w;
+};
+__device__ __forceinline__ U4 philox4x32_10(U4 c, unsigned k0, unsigned k1) {
+  constexpr unsigned M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned hi0 = __umulhi(M0, c.x), lo0 = M0 * c.x;
+    const unsigned hi1 = __umulhi(M1, c.z), lo1 = M1 * c.z;
+    c = U4{hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0};
+    k0 += W0;
+    k1 += W1;
+  }
+  return c;
+}
+// keep flags of the 8 elements of vector `vec` (16 random bits each); keep when r16 >= thresh16 (thresh = p * 65536)
+__device__ __forceinline__ void keep8(unsigned long long vec, unsigned seed_lo, unsigned seed_hi, unsigned thresh16,
+                                      bool* keep) {
+  const U4 r = philox4x32_10(U4{(unsigned)vec, (unsigned)(vec >> 32), 0u, 0u}, seed_lo, seed_hi);
+  const unsigned w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    keep[2 * i] = (w[i] & 0xFFFFu) >= thresh16;
+    keep[2 * i + 1] = (w[i] >> 16) >= thresh16;
+  }
+}
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float* f) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 t;
+  t = unpack_bf16(u.x); f[0] = t.x; f[1] = t.y;
+  t = unpack_bf16(u.y); f[2] = t.x; f[3] = t.y;
+  t = unpack_bf16(u.z); f[4] = t.x; f[5] = t.y;
+  t = unpack_bf16(u.w); f[6] = t.x; f[7] = t.y;
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float* f) {
+  uint4 o;
+  o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]); o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+
+// out[r, :] = x[r, :] + gate[r / rows_per_gate, :] * keep * y[r, :] / (1 - p)       (gate == nullptr: 1)
+__global__ void drop_res_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
+                                    const __nv_bfloat16* __restrict__ gate, long long gate_stride, int rows_per_gate,
+                                    __nv_bfloat16* __restrict__ out, long long rows, int H, unsigned thresh16,
+                                    float inv_keep, unsigned seed_lo, unsigned seed_hi) {
+  const int hv = H >> 3;
+  const long long nvec = rows * hv;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
+       t += (long long)gridDim.x * blockDim.x) {
+    const long long r = t / hv;
+    const int c = (int)(t - r * hv) * 8;
+    float xv[8], yv[8], gv[8];
+    ld8(x + r * H + c, xv);
+    ld8(y + r * H + c, yv);
+    if (gate != nullptr) ld8(gate + (r / rows_per_gate) * gate_stride + c, gv);
+    bool keep[8];
+    keep8((unsigned long long)t, seed_lo, seed_hi, thresh16, keep);
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float d = keep[e] ? yv[e] * inv_keep : 0.f;
+      o[e] = xv[e] + (gate != nullptr ? gv[e] * d : d);
+    }
+    st8(out + r * H + c, o);
+  }
+}
+
+// dy[r, :] = dout[r, :] * gate * keep / (1 - p).  With a gate, one thread owns a (gate row, 8 columns) pair and walks
+// its rows_per_gate rows, so dgate[g, :] = sum_r dout * keep * y / (1 - p) needs no atomics and no second pass.
+__global__ void drop_res_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y,
+                                    const __nv_bfloat16* __restrict__ gate, long long gate_stride, int rows_per_gate,
+                                    __nv_bfloat16* __restrict__ dy, float* __restrict__ dgate, long long rows, int H,
+                                    unsigned thresh16, float inv_keep, unsigned seed_lo, unsigned seed_hi) {
+  const int hv = H >> 3;
+  if (gate == nullptr) {
+    const long long nvec = rows * hv;
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
+         t += (long long)gridDim.x * blockDim.x) {
+      float g[8];
+      ld8(dout + t * 8, g);
+      bool keep[8];
+      keep8((unsigned long long)t, seed_lo, seed_hi, thresh16, keep);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] = keep[e] ? g[e] * inv_keep : 0.f;
+      st8(dy + t * 8, g);
+    }
+    return;
+  }
+  const long long n_gates = rows / rows_per_gate;
+  const long long work = n_gates * hv;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < work;
+       t += (long long)gridDim.x * blockDim.x) {
+    const long long gr = t / hv;
+    const int c = (int)(t - gr * hv) * 8;
+    float gv[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    ld8(gate + gr * gate_stride + c, gv);
+    for (int i = 0; i < rows_per_gate; ++i) {
+      const long long r = gr * rows_per_gate + i;
+      float g[8], yv[8], o[8];
+      ld8(dout + r * H + c, g);
+      ld8(y + r * H + c, yv);
+      bool keep[8];
+      keep8((unsigned long long)(r * hv + (c >> 3)), seed_lo, seed_hi, thresh16, keep);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float m = keep[e] ? inv_keep : 0.f;
+        o[e] = g[e] * gv[e] * m;
+        acc[e] += g[e] * yv[e] * m;
+      }
+      st8(dy + r * H + c, o);
+    }
+    float4* d = reinterpret_cast<float4*>(dgate + gr * H + c);
+    d[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    d[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ masked MSE
+// u, v: (B, T, D) fp32.  Element (b, t, d) counts when !frozen[b, t] && !pad[b, t] && d < real_dim[b] (null pointers
+// mean "no such mask").  One block per sample: sums[b] = sum of squared differences, counts[b] = counted elements.
+__global__ void masked_mse_fwd_kernel(const float* __restrict__ u, const float* __restrict__ v,
+                                      const unsigned char* __restrict__ frozen, const unsigned char* __restrict__ pad,
+                                      const long long* __restrict__ real_dim, int T, int D, float* __restrict__ sums,
+                                      float* __restrict__ counts) {
+  __shared__ float red_s[32], red_c[32];
+  const int b = blockIdx.x;
+  const int rd = real_dim != nullptr ? (int)real_dim[b] : D;
+  float s = 0.f, c = 0.f;
+  for (int i = threadIdx.x; i < T * D; i += blockDim.x) {
+    const int t = i / D, d = i - t * D;
+    const bool on = d < rd && !(frozen != nullptr && frozen[b * T + t]) && !(pad != nullptr && pad[b * T + t]);
+    if (on) {
+      const float e = u[((long long)b * T + t) * D + d] - v[((long long)b * T + t) * D + d];
+      s += e * e;
+      c += 1.f;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) red_s[w] = s, red_c[w] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ts = 0.f, tc = 0.f;
+    for (int i = 0; i < nw; ++i) ts += red_s[i], tc += red_c[i];
+    sums[b] = ts;
+    counts[b] = tc;
+  }
+}
+// dv = -2 (u - v) * mask * coef[0]      (coef = upstream gradient / (total count + 1e-8), a device scalar)
+__global__ void masked_mse_bwd_kernel(const float* __restrict__ u, const float* __restrict__ v,
+                                      const unsigned char* __restrict__ frozen, const unsigned char* __restrict__ pad,
+                                      const long long* __restrict__ real_dim, int B, int T, int D,
+                                      const float* __restrict__ coef, float* __restrict__ dv) {
+  const float k = -2.f * coef[0];
+  const long long n = (long long)B * T * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D);
+    const long long bt = i / D;
+    const int b = (int)(bt / T);
+    const int rd = real_dim != nullptr ? (int)real_dim[b] : D;
+    const bool on = d < rd && !(frozen != nullptr && frozen[bt]) && !(pad != nullptr && pad[bt]);
+    dv[i] = on ? k * (u[i] - v[i]) : 0.f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ embedding
+// out[i, :] = table[ids[i], :] * scale
+__global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ ids,
+                                 __nv_bfloat16* __restrict__ out, long long n_tok, int H, long long vocab,
+                                 float scale) {
+  const int hv = H >> 3;
+  const long long nvec = n_tok * hv;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
+       t += (long long)gridDim.x * blockDim.x) {
+    const long long r = t / hv;
+    const int c = (int)(t - r * hv) * 8;
+    long long id = ids[r];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);          // ids are validated on the host; never read outside
+    float f[8];
+    ld8(table + id * H + c, f);
+    if (scale != 1.f) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] *= scale;
+    }
+    st8(out + r * H + c, f);
+  }
+}
+// sorted_ids ascending with order[j] = position of the j-th smallest id.  One warp per (j, 256-column chunk): it
+// works only when j starts a run of equal ids; then it sums the dout rows of the run in order and ADDS the sum (times
+// scale) to grad[id, :], which no other warp touches.  No atomics, fixed summation order, no host-side run count.
+template <typename G>
+__global__ void embed_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const long long* __restrict__ sorted_ids,
+                                 const long long* __restrict__ order, long long n_tok, G* __restrict__ grad, int H,
+                                 long long vocab, long long pad_id, float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int chunks = (H + 255) / 256;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long wk = warp; wk < n_tok * chunks; wk += n_warps) {
+    const long long j0 = wk / chunks;
+    const int c = (int)(wk - j0 * chunks) * 256 + lane * 8;
+    const long long id = sorted_ids[j0];
+    if (j0 > 0 && sorted_ids[j0 - 1] == id) continue;        // not the first of its run
+    if (c >= H || id < 0 || id >= vocab || id == pad_id) continue;   // the padding row takes no gradient
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long j = j0; j < n_tok && sorted_ids[j] == id; ++j) {
+      float f[8];
+      ld8(dout + order[j] * H + c, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    G* g = grad + id * H + c;
+    if constexpr (sizeof(G) == 4) {
+      float4* g4 = reinterpret_cast<float4*>(g);
+      float4 a = g4[0], b = g4[1];
+      a.x += acc[0] * scale; a.y += acc[1] * scale; a.z += acc[2] * scale; a.w += acc[3] * scale;
+      b.x += acc[4] * scale; b.y += acc[5] * scale; b.z += acc[6] * scale; b.w += acc[7] * scale;
+      g4[0] = a;
+      g4[1] = b;
+    } else {
+      float cur[8];
+      ld8(reinterpret_cast<const __nv_bfloat16*>(g), cur);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) cur[e] += acc[e] * scale;
+      st8(reinterpret_cast<__nv_bfloat16*>(g), cur);
+    }
+  }
+}
+
+}  // namespace otb
+
+using namespace otb;
+
+static int grid_for(long long work, int block) {
+  long long g = (work + block - 1) / block;
+  if (g < 1) g = 1;
+  if (g > 148LL * 16) g = 148LL * 16;
+  return (int)g;
+}
+
+extern "C" int otb_drop_res_fwd(const void* x, const void* y, const void* gate, long long gate_stride,
+                                int rows_per_gate, void* out, long long rows, int H, float p,
+                                unsigned long long seed, cudaStream_t stream) {
+  if (H % 8 || rows < 0 || p < 0.f || p >= 1.f || (gate != nullptr && (rows_per_gate < 1 || rows % rows_per_gate ||
+                                                                          gate_stride % 8)))
+    return -1;
+  if (rows == 0) return 0;
+  const unsigned thresh = (unsigned)(p * 65536.f);
+  drop_res_fwd_kernel<<<grid_for(rows * (H / 8), 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y),
+      static_cast<const __nv_bfloat16*>(gate), gate_stride, rows_per_gate, static_cast<__nv_bfloat16*>(out), rows, H,
+      thresh, 65536.f / (65536.f - (float)thresh), (unsigned)seed, (unsigned)(seed >> 32));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_drop_res_bwd(const void* dout, const void* y, const void* gate, long long gate_stride,
+                                int rows_per_gate, void* dy, float* dgate, long long rows, int H, float p,
+                                unsigned long long seed, cudaStream_t stream) {
+  if (H % 8 || rows < 0 || p < 0.f || p >= 1.f ||
+      (gate != nullptr && (rows_per_gate < 1 || rows % rows_per_gate || gate_stride % 8 || y == nullptr ||
+                           dgate == nullptr)))
+    return -1;
+  if (rows == 0) return 0;
+  const unsigned thresh = (unsigned)(p * 65536.f);
+  const long long work = gate != nullptr ? (rows / rows_per_gate) * (H / 8) : rows * (H / 8);
+  drop_res_bwd_kernel<<<grid_for(work, gate != nullptr ? 128 : 256), gate != nullptr ? 128 : 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(y),
+      static_cast<const __nv_bfloat16*>(gate), gate_stride, rows_per_gate, static_cast<__nv_bfloat16*>(dy), dgate,
+      rows, H, thresh, 65536.f / (65536.f - (float)thresh), (unsigned)seed, (unsigned)(seed >> 32));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_masked_mse_fwd(const float* u, const float* v, const unsigned char* frozen,
+                                  const unsigned char* pad, const long long* real_dim, int B, int T, int D,
+                                  float* sums, float* counts, cudaStream_t stream) {
+  if (B < 1 || T < 1 || D < 1) return -1;
+  masked_mse_fwd_kernel<<<B, 256, 0, stream>>>(u, v, frozen, pad, real_dim, T, D, sums, counts);
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_masked_mse_bwd(const float* u, const float* v, const unsigned char* frozen,
+                                  const unsigned char* pad, const long long* real_dim, int B, int T, int D,
+                                  const float* coef, float* dv, cudaStream_t stream) {
+  if (B < 1 || T < 1 || D < 1) return -1;
+  masked_mse_bwd_kernel<<<grid_for((long long)B * T * D, 256), 256, 0, stream>>>(u, v, frozen, pad, real_dim, B, T, D,
+                                                                                 coef, dv);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_embed_fwd(const void* table, const long long* ids, void* out, long long n_tok, int H,
+                             long long vocab, float scale, cudaStream_t stream) {
+  if (H % 8 || n_tok < 0 || vocab < 1) return -1;
+  if (n_tok == 0) return 0;
+  embed_fwd_kernel<<<grid_for(n_tok * (H / 8), 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), n_tok, H, vocab, scale);
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_embed_bwd(const void* dout, const long long* sorted_ids, const long long* order, long long n_tok,
+                             void* grad, int grad_fp32, int H, long long vocab, long long pad_id, float scale,
+                             cudaStream_t stream) {
+  if (H % 8 || n_tok < 0 || vocab < 1) return -1;
+  if (n_tok == 0) return 0;
+  const long long warps = n_tok * ((H + 255) / 256);
+  const int grid = grid_for(warps * 32, 256);
+  if (grad_fp32)
+    embed_bwd_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout), sorted_ids, order,
+                                                      n_tok, static_cast<float*>(grad), H, vocab, pad_id, scale);
+  else
+    embed_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout), sorted_ids,
+                                                              order, n_tok, static_cast<__nv_bfloat16*>(grad), H,
+                                                              vocab, pad_id, scale);
+  return (int)cudaGetLastError();
+}

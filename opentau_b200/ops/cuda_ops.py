@@ -559,3 +559,107 @@ def attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale):
 def attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale):
     from . import attention
     return attention.attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)
+
+
+# --------------------------------------------------------------------------------------------- training elementwise
+def dropout_residual_fwd(x: Tensor, y: Tensor, gate: Tensor | None, p: float, seed: int) -> Tensor:
+    """``x + gate * dropout(y, p)`` for ``(B, T, H)`` bf16 tensors (``gate (B, 1 | T, H)`` or None), one pass; the keep
+    mask comes from ``seed`` and is never stored."""
+    global launch_count
+    H = x.shape[-1]
+    x2, y2 = x.reshape(-1, H), y.reshape(-1, H)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    y2 = y2 if y2.is_contiguous() else y2.contiguous()
+    rows = x2.shape[0]
+    g2, stride, rpg = None, 0, 1
+    if gate is not None:
+        g2 = gate.reshape(-1, H)
+        if g2.stride(1) != 1 or g2.stride(0) % 8 or g2.data_ptr() % 16:
+            g2 = g2.contiguous()
+        stride, rpg = g2.stride(0), rows // g2.shape[0]
+    out = torch.empty_like(x2)
+    _check(_lib.load("train_elementwise").otb_drop_res_fwd(
+        _p(x2), _p(y2), _p(g2), c_longlong(stride), c_int(rpg), _p(out), c_longlong(rows), c_int(H), c_float(p),
+        ctypes.c_ulonglong(seed), _stream()), "drop_res_fwd")
+    launch_count += 1
+    return out.view(x.shape)
+
+
+def dropout_residual_bwd(dout: Tensor, y: Tensor | None, gate: Tensor | None, p: float, seed: int):
+    """Gradients of :func:`dropout_residual_fwd` w.r.t. ``y`` (and ``gate``, as fp32 ``(gate rows, H)``)."""
+    global launch_count
+    H = dout.shape[-1]
+    d2 = dout.reshape(-1, H)
+    d2 = d2 if d2.is_contiguous() else d2.contiguous()
+    rows = d2.shape[0]
+    g2, stride, rpg, dgate, y2 = None, 0, 1, None, None
+    if gate is not None:
+        g2 = gate.reshape(-1, H)
+        if g2.stride(1) != 1 or g2.stride(0) % 8 or g2.data_ptr() % 16:
+            g2 = g2.contiguous()
+        stride, rpg = g2.stride(0), rows // g2.shape[0]
+        dgate = torch.empty(g2.shape[0], H, dtype=torch.float32, device=dout.device)
+        y2 = y.reshape(-1, H)
+        y2 = y2 if y2.is_contiguous() else y2.contiguous()
+    dy = torch.empty_like(d2)
+    _check(_lib.load("train_elementwise").otb_drop_res_bwd(
+        _p(d2), _p(y2), _p(g2), c_longlong(stride), c_int(rpg), _p(dy), _p(dgate), c_longlong(rows), c_int(H),
+        c_float(p), ctypes.c_ulonglong(seed), _stream()), "drop_res_bwd")
+    launch_count += 1
+    return dy.view(dout.shape), dgate
+
+
+def masked_mse_fwd(u: Tensor, v: Tensor, frozen: Tensor | None, pad: Tensor | None, real_dim: Tensor | None):
+    """Per-sample ``(sum of squared differences, number of counted elements)`` of ``(B, T, D)`` fp32 tensors."""
+    global launch_count
+    B, T, D = u.shape
+    sums = torch.empty(B, dtype=torch.float32, device=u.device)
+    counts = torch.empty(B, dtype=torch.float32, device=u.device)
+    _check(_lib.load("train_elementwise").otb_masked_mse_fwd(_p(u), _p(v), _p(frozen), _p(pad), _p(real_dim), c_int(B),
+                                                             c_int(T), c_int(D), _p(sums), _p(counts), _stream()),
+           "masked_mse_fwd")
+    launch_count += 1
+    return sums, counts
+
+
+def masked_mse_bwd(u: Tensor, v: Tensor, frozen: Tensor | None, pad: Tensor | None, real_dim: Tensor | None,
+                   coef: Tensor) -> Tensor:
+    global launch_count
+    B, T, D = u.shape
+    dv = torch.empty_like(v)
+    _check(_lib.load("train_elementwise").otb_masked_mse_bwd(_p(u), _p(v), _p(frozen), _p(pad), _p(real_dim), c_int(B),
+                                                             c_int(T), c_int(D), _p(coef), _p(dv), _stream()),
+           "masked_mse_bwd")
+    launch_count += 1
+    return dv
+
+
+def embed_fwd(table: Tensor, ids: Tensor, scale: float) -> Tensor:
+    global launch_count
+    H = table.shape[1]
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty(flat.numel(), H, dtype=table.dtype, device=table.device)
+    _check(_lib.load("train_elementwise").otb_embed_fwd(_p(table), _p(flat), _p(out), c_longlong(flat.numel()), c_int(H),
+                                                        c_longlong(table.shape[0]), c_float(scale), _stream()),
+           "embed_fwd")
+    launch_count += 1
+    return out.view(*ids.shape, H)
+
+
+def embed_bwd(dout: Tensor, ids: Tensor, grad: Tensor, scale: float, padding_idx: int | None = None) -> None:
+    """``grad[ids[i], :] += scale * dout[i, :]`` for a ``(V, H)`` bf16 or fp32 gradient table, deterministic (rows
+    with the same id are summed in token order by one warp)."""
+    global launch_count
+    H = grad.shape[1]
+    flat = ids.reshape(-1).to(torch.int64)
+    sorted_ids, order = torch.sort(flat, stable=True)
+    n = flat.numel()
+    if n == 0:
+        return
+    d2 = dout.reshape(-1, H)
+    d2 = d2 if d2.is_contiguous() else d2.contiguous()
+    _check(_lib.load("train_elementwise").otb_embed_bwd(
+        _p(d2), _p(sorted_ids), _p(order), c_longlong(n), _p(grad), c_int(int(grad.dtype == torch.float32)), c_int(H),
+        c_longlong(grad.shape[0]), c_longlong(-1 if padding_idx is None else padding_idx), c_float(scale), _stream()),
+        "embed_bwd")
+    launch_count += 1

@@ -293,3 +293,89 @@ class PatchEmbedFn(torch.autograd.Function):
 
 def patch_embed(pixels, weight, bias, pos, patch, out_dtype):
     return PatchEmbedFn.apply(pixels, weight, bias, pos, patch, out_dtype)
+
+
+class DropoutResidualFn(torch.autograd.Function):
+    """``x + gate * dropout(y, p)`` in one native pass each way; the keep mask is regenerated from the call's seed in
+    the backward (nothing but the seed is kept for it; ``y`` only when a gate needs its gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, y, gate, p: float):
+        from . import cuda_ops
+        seed = int(torch.randint(0, 2**62, (1,), device="cpu").item())      # from the host generator (seedable)
+        out = cuda_ops.dropout_residual_fwd(x, y, gate, p, seed)
+        ctx.p, ctx.seed = p, seed
+        ctx.has_gate = gate is not None
+        ctx.gate_shape = gate.shape if gate is not None else None
+        ctx.save_for_backward(*( (y, gate) if gate is not None else () ))
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import cuda_ops
+        y, gate = ctx.saved_tensors if ctx.has_gate else (None, None)
+        dy, dgate = cuda_ops.dropout_residual_bwd(dout, y, gate, ctx.p, ctx.seed)
+        if dgate is not None:
+            dgate = dgate.view(ctx.gate_shape).to(gate.dtype)
+        return dout, dy, dgate, None
+
+
+def dropout_residual(x, y, gate, p: float):
+    return DropoutResidualFn.apply(x, y, gate, p)
+
+
+class MaskedMSEFn(torch.autograd.Function):
+    """Flow-matching masked MSE: per-sample sums and counts in one native pass; the backward writes the gradient of
+    the prediction directly."""
+
+    @staticmethod
+    def forward(ctx, u, v, frozen, pad, real_dim):
+        from . import cuda_ops
+        u32, v32 = u.float().contiguous(), v.float().contiguous()
+        fz = frozen.to(torch.uint8).contiguous() if frozen is not None else None
+        pd = pad.to(torch.uint8).contiguous() if pad is not None else None
+        rd = real_dim.to(torch.int64).contiguous() if real_dim is not None else None
+        sums, counts = cuda_ops.masked_mse_fwd(u32, v32, fz, pd, rd)
+        total = counts.sum() + 1e-8
+        ctx.save_for_backward(u32, v32, total)
+        ctx.masks = (fz, pd, rd)
+        ctx.mark_non_differentiable(sums, counts)
+        return sums.sum() / total, sums, counts
+
+    @staticmethod
+    def backward(ctx, dloss, _ds, _dc):
+        from . import cuda_ops
+        u32, v32, total = ctx.saved_tensors
+        coef = (dloss.float() / total).reshape(1).contiguous()
+        dv = cuda_ops.masked_mse_bwd(u32, v32, *ctx.masks, coef)
+        return None, dv, None, None, None
+
+
+class EmbeddingFn(torch.autograd.Function):
+    """``table[ids] * scale`` with a gather kernel forward and a sort-by-id scatter-add backward that goes straight
+    into the parameter's flat gradient (``main_grad``) when there is one."""
+
+    @staticmethod
+    def forward(ctx, table, ids, scale: float, padding_idx):
+        from . import cuda_ops
+        ctx.save_for_backward(ids)
+        ctx.tref, ctx.scale, ctx.pad = table, scale, padding_idx
+        return cuda_ops.embed_fwd(table, ids, scale)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import cuda_ops
+        (ids,) = ctx.saved_tensors
+        t = ctx.tref
+        mg = getattr(t, "main_grad", None)
+        if mg is not None:
+            cuda_ops.embed_bwd(dout, ids, mg, ctx.scale, ctx.pad)
+            _notify(t)
+            return None, None, None, None
+        g = torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+        cuda_ops.embed_bwd(dout, ids, g, ctx.scale, ctx.pad)
+        return g.to(t.dtype), None, None, None
+
+
+def embedding(table, ids, scale: float = 1.0, padding_idx=None):
+    return EmbeddingFn.apply(table, ids, scale, padding_idx)

@@ -172,7 +172,7 @@ class PaliGemmaWithExpertModel(nn.Module):
         return self.paligemma.lm_head_weight()
 
     def embed_discrete_actions(self, actions: Tensor) -> Tensor:
-        return self.discrete_action_embedding(actions)
+        return ops.embedding(self.discrete_action_embedding.weight, actions, padding_idx=0)
 
     def forward(self, inputs_embeds, position_ids, q_blk, q_valid, **kw):
         if len(self.decoder.towers) == 1:                   # expert disabled: callers still pass / unpack a pair

@@ -278,7 +278,7 @@ def _cp_policy_worker(rank, world, port, ret):
         noise, time = torch.randn(2, 10, 32, generator=g).to(dev), torch.full((2,), 0.4, device=dev)
         results = []
         for use_cp in (False, True):
-            pol = tiny_pi05(device="cuda", seed=7).to(torch.bfloat16).train()
+            pol = tiny_pi05(device="cuda", seed=7).to(dev).to(torch.bfloat16).train()
             if use_cp:
                 pol.model.context_parallel = ContextParallel(dev, backend="p2p", wait_budget=4_000_000_000)
             for _ in range(2):                      # twice: both parities of the staging buffers
