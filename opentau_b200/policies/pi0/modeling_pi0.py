@@ -134,6 +134,7 @@ class PI0Policy(PI05Policy):
     config_class = PI0Config
     name = "pi0"
     model_class = PI0FlowMatching
+    _TILE_LINEAR_INPUTS = True       # older checkpoints have narrower state / action inputs (reference pi0/modeling_pi0.py:354)
 
     def prepare_language(self, batch):
         cfg = self.config

@@ -142,6 +142,7 @@ class PI07LowLevelPolicy(PI05Policy):
     config_class = PI07LowLevelConfig
     name = "pi07_low_level"
     model_class = PI07LowLevelFlowMatching
+    _PER_GROUP_PROJECTION_PREFIXES = ("model.state_proj.", "model.action_in_proj.", "model.action_out_proj.")
 
     @staticmethod
     def _vocab_size(config) -> int:

@@ -32,6 +32,11 @@ def strip_normalization_buffers(state: dict[str, Tensor]) -> dict[str, Tensor]:
 class PreTrainedPolicy(nn.Module, abc.ABC):
     config_class: type[PreTrainedConfig] | None = None
     name: str | None = None
+    #: state-dict prefixes of learned per-group projections (``PerGroupLinear``) that are duplicated / re-ordered by
+    #: group name when a checkpoint with another group set is loaded; empty = the policy has none
+    _PER_GROUP_PROJECTION_PREFIXES: tuple[str, ...] = ()
+    #: policies whose input layers may be wider than an older checkpoint's set this (pi0: the state / action width)
+    _TILE_LINEAR_INPUTS = False
 
     def __init__(self, config: PreTrainedConfig, *inputs, **kwargs):
         super().__init__()
@@ -143,16 +148,27 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
     @classmethod
     def from_pretrained(cls, pretrained_name_or_path: str | Path, *, config: PreTrainedConfig | None = None,
                         strict: bool = False, map_location: str = "cpu", **kwargs):
-        from ..utils.hub import resolve_local_or_hub
+        """``pretrained_name_or_path``: a checkpoint directory or ``repo[@revision]`` in the local cache.  The
+        normalisation convention is taken from the checkpoint (``loading.resolve_checkpoint_provenance``) BEFORE
+        the policy is built; a local directory without ``model.safetensors`` (a sharded training checkpoint whose
+        weights arrive with the optimizer state) yields the constructed policy with a warning, every other missing
+        source raises."""
+        from . import loading
         if config is None:
             config = PreTrainedConfig.from_pretrained(pretrained_name_or_path)
-            config.validate_input_resolution(strict=False)       # a stored config: warn, keep loading
-        model_dir = resolve_local_or_hub(str(pretrained_name_or_path))
+        loading.resolve_checkpoint_provenance(config, pretrained_name_or_path)
         policy = cls(config, **kwargs)
-        weights = Path(model_dir) / SAFETENSORS_SINGLE_FILE
-        if not weights.is_file():
-            raise FileNotFoundError(f"{SAFETENSORS_SINGLE_FILE} not found in {model_dir}")
-        policy = cls._load_as_safetensor(policy, str(weights), map_location, strict)
+        try:
+            weights = loading.resolve_pretrained_weights_file(pretrained_name_or_path)
+        except loading.CheckpointWeightsNotFoundError as exc:
+            logging.warning("%s  The policy keeps its initial weights until the training state is loaded.", exc)
+            return policy
+        old_names = None
+        try:
+            old_names = PreTrainedConfig.from_pretrained(pretrained_name_or_path).dataset_names
+        except Exception:                                          # a checkpoint without a readable config
+            pass
+        policy = cls._load_as_safetensor(policy, str(weights), map_location, strict, old_dataset_names=old_names)
         policy.eval()
         return policy
 
@@ -161,12 +177,18 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
         return state
 
     @classmethod
-    def _load_as_safetensor(cls, model: "PreTrainedPolicy", model_file: str, map_location: str, strict: bool):
+    def _load_as_safetensor(cls, model: "PreTrainedPolicy", model_file: str, map_location: str, strict: bool,
+                            old_dataset_names: list[str] | None = None):
         from safetensors.torch import load_file
+        from . import loading
         state = load_file(model_file, device=map_location if map_location != "cpu" else "cpu")
         state = cls._fix_state_dict_keys(state, model.config)
         if model.config.skip_normalization_weights:
             state = strip_normalization_buffers(state)
+            model.config.skip_normalization_weights = False       # one shot: a later save / resume keeps the new stats
+        loading.remap_per_group_projection_weights(model, state, cls._PER_GROUP_PROJECTION_PREFIXES, old_dataset_names)
+        if cls._TILE_LINEAR_INPUTS:
+            loading.tile_linear_input_weights(model, state)
         own = model.state_dict()
         for k, v in list(state.items()):  # linear input tiling / shape guards are policy specific
             if k in own and tuple(own[k].shape) != tuple(v.shape) and k.startswith(_NORM_PREFIXES):

@@ -120,3 +120,60 @@ def test_rollouts_become_a_dataset(tmp_path):
     assert meta.episodes[2]["length"] == 12 and meta.episodes[0]["length"] < 12          # success ends the episode early
     only = record_rollouts(data, tmp_path / "ok", fps=10, prompts=["reach the goal"] * 4, only_successful=True)
     assert only["episodes"] == 2 and only["successes"] == 2
+
+
+def test_videos_grid_summary_goal_frames_and_accel_streams(tmp_path):
+    """Everything the evaluator builds from frame arrays: per-episode clips tiled into a grid video whose held last
+    frame carries a green / red border per tile, the final camera frames of successful episodes keyed by seed, and
+    the accel values a policy publishes per chunk."""
+    import cv2
+    from opentau_b200.scripts.eval import create_grid_summary_video, write_video
+    cfg = FakeEnvConfig(tasks=["reach"], episode_length=12, resolution=(64, 64))
+    env = make_envs(cfg, n_envs=2)["reach"][0]
+
+    class WithAccel(Scripted):
+        def __init__(self, gain):
+            super().__init__(gain)
+            self.last_accel, self.last_accel_provenance, self.n = None, {"prefix": 5}, 0
+
+        def select_action(self, batch):
+            self.n += 1
+            if self.n % 3 == 1:                                   # a new chunk every third step
+                self.last_accel = torch.full((2,), float(self.n))
+            return super().select_action(batch)
+
+    res = eval_policy(env, WithAccel(1.0), n_episodes=3, start_seed=5, device="cpu", max_episodes_rendered=3,
+                      videos_dir=tmp_path / "videos", goal_frames_dir=tmp_path / "goals", task_name="reach_0")
+    assert res["aggregated"]["pc_success"] == 100.0
+    grid = tmp_path / "videos" / "grid_summary.mp4"
+    assert grid.exists() and res["video_paths"] == [str(grid)] and not list((tmp_path / "videos").glob("eval_episode_*"))
+    cap = cv2.VideoCapture(str(grid))
+    n, last = 0, None
+    while True:
+        ok, f = cap.read()
+        if not ok:
+            break
+        n, last = n + 1, f
+    assert n > 10 and last.shape[:2] == (128, 128)                # 3 clips -> 2 x 2 tiles of 64 x 64
+    assert last[2, 30, 1] > 120 and last[2, 30, 2] < 90           # green border on a successful tile (BGR)
+    assert len(res["goal_frames"]) == 3 and {r["seed"] for r in res["goal_frames"]} == {5, 6, 7}
+    png = cv2.imread(str(tmp_path / "goals" / res["goal_frames"][0]["camera0"]))
+    assert png is not None and png.shape[:2] == (64, 64)
+    assert (tmp_path / "goals" / "manifest_rank0.jsonl").read_text().count("\n") == 3
+    streams = res["accel"]["streams"]
+    assert len(streams) == 3 and all(len(s) >= 1 for s in streams) and res["accel"]["provenance"] == {"prefix": 5}
+    # a failed tile gets a red border; a clip that ends early keeps its last frame
+    a, b = tmp_path / "a.mp4", tmp_path / "b.mp4"
+    write_video(a, np.full((4, 32, 32, 3), 200, np.uint8), 10)
+    write_video(b, np.full((9, 32, 32, 3), 50, np.uint8), 10)
+    create_grid_summary_video([str(a), str(b)], [False, True], tmp_path / "g.mp4", 10, highlight_duration=0.5,
+                              grid_size=(1, 2), frame_stride=2)
+    cap = cv2.VideoCapture(str(tmp_path / "g.mp4"))
+    frames = []
+    while True:
+        ok, f = cap.read()
+        if not ok:
+            break
+        frames.append(f)
+    assert len(frames) == 5 + 5 and frames[-1][1, 10, 2] > 150 and frames[-1][1, 10, 1] < 90     # red on tile 0
+    assert frames[3][16, 16].mean() > 150                         # tile 0 still shows its last frame after it ended
