@@ -116,10 +116,7 @@ class TrainPipelineConfig:
                 raise ValueError("loss weights must be non-negative")
         if all(float(self.loss_weighting.get(k, 1.0)) == 0.0 for k in ("MSE", "CE")):
             raise ValueError("every loss term has zero weight")
-        if self.running_best_count < 0:
-            raise ValueError("running_best_count must be >= 0")
-        if self.running_best_count > 0 and self.val_freq <= 0 and self.eval_freq <= 0:
-            raise ValueError("running_best_count > 0 needs validation (val_freq) or evaluation (eval_freq)")
+        self._validate_running_best()
         if self.use_policy_training_preset or self.optimizer is None:
             self.optimizer = self.optimizer if (self.optimizer and not self.use_policy_training_preset) \
                 else self.policy.get_optimizer_preset()
@@ -135,6 +132,33 @@ class TrainPipelineConfig:
                 raise FileExistsError(f"output directory {self.output_dir} already holds checkpoints and "
                                       "`resume` is False")
         self.policy.validate_action_horizon()
+
+    def _validate_running_best(self) -> None:
+        """``running_best_metric``: ``eval_success`` (keep the highest simulation success rates), ``val_loss`` (keep
+        the lowest validation losses) or ``auto`` (success when an environment is evaluated during training, else
+        validation loss).  The resolved choice is a runtime attribute, never saved: a resumed ``auto`` run stays
+        ``auto`` (reference ``configs/train.py:438-516``)."""
+        allowed = ("auto", "eval_success", "val_loss", "success")        # "success": accepted alias of eval_success
+        if self.running_best_metric not in allowed:
+            raise ValueError(f"running_best_metric must be one of {sorted(allowed[:3])}, got "
+                             f"{self.running_best_metric!r}")
+        if self.running_best_count < 0:
+            raise ValueError(f"running_best_count must be >= 0, got {self.running_best_count}")
+        self.running_best_metric_resolved = None
+        if self.running_best_count == 0:
+            return
+        has_eval = self.env is not None and self.eval_freq > 0
+        has_val = self.val_freq > 0
+        metric = "eval_success" if self.running_best_metric == "success" else self.running_best_metric
+        if metric == "eval_success" and not has_eval:
+            raise ValueError("running_best_metric='eval_success' needs a simulation evaluation source: set env and "
+                             "eval_freq > 0")
+        if metric == "val_loss" and not has_val:
+            raise ValueError("running_best_metric='val_loss' needs val_freq > 0")
+        if metric == "auto" and not (has_eval or has_val):
+            raise ValueError("running_best_count >= 1 but no metric source is configured: set eval_freq > 0 with an "
+                             "env (success rate) or val_freq > 0 (validation loss)")
+        self.running_best_metric_resolved = ("eval_success" if has_eval else "val_loss") if metric == "auto" else metric
 
     # -- persistence -------------------------------------------------------------------------------
     def to_dict(self) -> dict[str, Any]:
@@ -152,18 +176,45 @@ class TrainPipelineConfig:
         _import_policy_configs()
         return decode(cls, raw)
 
+    @staticmethod
+    def _locate_config_file(config_path: str | Path) -> Path:
+        """A JSON file; a directory holding ``train_config.json`` or, failing that, ``hf_config.json`` (the name
+        the publishing tools give the pipeline config of an uploaded checkpoint); or ``repo[@revision]`` in the local
+        cache with the same two names (reference ``configs/train.py:596-640``).  A revision that is not cached is
+        reported with the revisions that are."""
+        from ..utils.hub import HF_OPENTAU_HOME, split_repo_revision
+        names = (TRAIN_CONFIG_NAME, "hf_config.json")
+        p = Path(str(config_path))
+        if p.is_file():
+            return p
+        if p.is_dir():
+            for n in names:
+                if (p / n).is_file():
+                    return p / n
+            raise FileNotFoundError(f"neither {names[0]} nor {names[1]} found in {p.resolve()}")
+        repo, rev = split_repo_revision(str(config_path))
+        repo_dir = HF_OPENTAU_HOME / repo
+        if not repo_dir.is_dir():
+            raise FileNotFoundError(f"{config_path!r} is not a file, not a directory and not in the local cache "
+                                    f"({repo_dir}); this installation does not download")
+        root = repo_dir / rev if rev else repo_dir
+        if rev and not root.is_dir():
+            tags = sorted(d.name for d in repo_dir.iterdir() if d.is_dir())
+            raise FileNotFoundError(f"revision {rev!r} does not exist in cached repository {repo!r}; training steps "
+                                    f"are published as tags named by step number (cached: {tags or 'none'}).  Omit "
+                                    "the '@<step>' suffix to load the latest step.")
+        for n in names:
+            if (root / n).is_file():
+                return root / n
+        raise FileNotFoundError(f"neither {names[0]} nor {names[1]} was found in {root}")
+
     @classmethod
     def from_pretrained(cls, config_path: str | Path, cli_overrides: list[str] | None = None) -> "TrainPipelineConfig":
         """Loads a JSON config (a file, a checkpoint directory holding ``train_config.json``, or a cached
         ``repo@rev``); ``$ref`` includes are resolved, then dotted CLI overrides applied.  With
         ``--resume=true`` the checkpoint's own ``train_config.json`` wins over the CLI for everything but
         ``steps``/``resume`` (reference ``configs/train.py:352-366``)."""
-        from ..utils.hub import resolve_local_or_hub
-        p = Path(str(config_path))
-        if p.is_dir():
-            p = p / TRAIN_CONFIG_NAME
-        if not p.is_file():
-            p = resolve_local_or_hub(str(config_path), TRAIN_CONFIG_NAME)
+        p = cls._locate_config_file(config_path)
         raw = load_json_with_refs(p)
         overrides = list(cli_overrides or [])
         policy_path = None

@@ -55,13 +55,19 @@ class PatchEmbedding(nn.Module):
         return super()._apply(keep_fp32, recurse)
 
     def interpolated_positions(self, gh: int, gw: int) -> Tensor:
-        """Bilinear resample of the square position grid to ``gh x gw`` (native-resolution inputs)."""
+        """The square position grid resampled to ``gh x gw`` for native-resolution inputs: bicubic, half-pixel
+        centres (what the reference gets from ``interpolate_pos_encoding=True`` of the stock SigLIP embeddings,
+        ``utils/transformers_patch.py:293-300``).  A frozen table on the GPU goes through the resample kernel; a
+        trainable one through the differentiable library op."""
         tab = self.position_embedding.weight
         g = int(math.sqrt(tab.shape[0]))
         if (gh, gw) == (g, g):
             return tab
+        if tab.is_cuda and not ops.oracle_mode() and not (torch.is_grad_enabled() and tab.requires_grad):
+            from ..ops import cuda_ops
+            return cuda_ops.pos_resample(tab, gh, gw)
         t = tab.view(1, g, g, -1).permute(0, 3, 1, 2)
-        t = F.interpolate(t, size=(gh, gw), mode="bilinear", align_corners=False)
+        t = F.interpolate(t, size=(gh, gw), mode="bicubic", align_corners=False)
         return t.permute(0, 2, 3, 1).reshape(gh * gw, -1)
 
     def forward(self, pixels: Tensor, out_dtype: torch.dtype) -> Tensor:

@@ -6,6 +6,8 @@
 //                                 generator (Philox4x32-10 keyed by the call's seed, one call per 8 elements).
 //   masked_mse_fwd / _bwd         flow-matching loss: sum and count of (u - v)^2 over the unmasked elements, per
 //                                 sample, in one pass; the backward writes dv directly.
+//   ce_tile_fwd                   one vocabulary tile of logits folded into the rows' running softmax statistics
+//   pos_resample                  bicubic resample of the SigLIP position table to a native-resolution patch grid
 //   embed_fwd / embed_bwd         token embedding gather (with the sqrt(d) scale) and its scatter-add backward into
 //                                 an fp32 or bf16 gradient table without a dense one-hot product: rows are processed
 //                                 by token ORDER (sorted ids), so each table row is written by one warp, in a fixed
@@ -187,6 +189,85 @@ __global__ void masked_mse_bwd_kernel(const float* __restrict__ u, const float* 
   }
 }
 
+// ------------------------------------------------------------------------------------------ vocabulary-tiled CE
+// One tile of logits (rows x Vc, fp32, columns [c0, c0 + Vc) of the vocabulary) is folded into the running softmax
+// statistics of every row: m = running max, s = running sum of exp(logit - m); the target logit is picked up by the
+// tile that holds the row's label.  After the last tile lse = m + log(s) and loss = lse - target: the full
+// rows x vocabulary logits never exist.
+__global__ void ce_tile_fwd_kernel(const float* __restrict__ logits, const long long* __restrict__ labels,
+                                   long long c0, int Vc, float* __restrict__ m_run, float* __restrict__ s_run,
+                                   float* __restrict__ tgt) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const float* lr = logits + row * (long long)Vc;
+  float m = -INFINITY;
+  for (int c = threadIdx.x; c < Vc; c += blockDim.x) m = fmaxf(m, lr[c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) red[w] = m;
+  __syncthreads();
+  m = red[0];
+  for (int i = 1; i < nw; ++i) m = fmaxf(m, red[i]);
+  __syncthreads();
+  float s = 0.f;
+  for (int c = threadIdx.x; c < Vc; c += blockDim.x) s += __expf(lr[c] - m);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (l == 0) red[w] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ts = 0.f;
+    for (int i = 0; i < nw; ++i) ts += red[i];
+    const float m_old = m_run[row], s_old = s_run[row];
+    const float m_new = fmaxf(m_old, m);
+    s_run[row] = s_old * __expf(m_old - m_new) + ts * __expf(m - m_new);     // exp(-inf) = 0 on the first tile
+    m_run[row] = m_new;
+    const long long lab = labels[row] - c0;
+    if (lab >= 0 && lab < Vc) tgt[row] = lr[lab];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ position table resample
+// Bicubic (A = -0.75, half-pixel centres, border indices clamped: the convention of F.interpolate(mode="bicubic",
+// align_corners=False)) resample of a (g x g, d) fp32 table to (gh x gw, d).
+__device__ __forceinline__ void cubic_weights(float t, float* w) {
+  constexpr float A = -0.75f;
+  const float x0 = t + 1.f, x1 = t, x2 = 1.f - t, x3 = 2.f - t;
+  w[0] = ((A * x0 - 5.f * A) * x0 + 8.f * A) * x0 - 4.f * A;
+  w[1] = ((A + 2.f) * x1 - (A + 3.f)) * x1 * x1 + 1.f;
+  w[2] = ((A + 2.f) * x2 - (A + 3.f)) * x2 * x2 + 1.f;
+  w[3] = ((A * x3 - 5.f * A) * x3 + 8.f * A) * x3 - 4.f * A;
+}
+__global__ void pos_resample_kernel(const float* __restrict__ tab, int g, int d, float* __restrict__ out, int gh,
+                                    int gw) {
+  const long long n = (long long)gh * gw * d;
+  const float sy = (float)g / gh, sx = (float)g / gw;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % d);
+    const int pos = (int)(i / d);
+    const int oy = pos / gw, ox = pos - oy * gw;
+    const float fy = (oy + 0.5f) * sy - 0.5f, fx = (ox + 0.5f) * sx - 0.5f;
+    const int iy = (int)floorf(fy), ix = (int)floorf(fx);
+    float wy[4], wx[4];
+    cubic_weights(fy - iy, wy);
+    cubic_weights(fx - ix, wx);
+    float acc = 0.f;
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int yy = min(max(iy - 1 + a, 0), g - 1);
+      float row = 0.f;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int xx = min(max(ix - 1 + b, 0), g - 1);
+        row += wx[b] * tab[((long long)yy * g + xx) * d + c];
+      }
+      acc += wy[a] * row;
+    }
+    out[i] = acc;
+  }
+}
+
 // ------------------------------------------------------------------------------------------ embedding
 // out[i, :] = table[ids[i], :] * scale
 __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ ids,
@@ -307,6 +388,19 @@ extern "C" int otb_masked_mse_bwd(const float* u, const float* v, const unsigned
   if (B < 1 || T < 1 || D < 1) return -1;
   masked_mse_bwd_kernel<<<grid_for((long long)B * T * D, 256), 256, 0, stream>>>(u, v, frozen, pad, real_dim, B, T, D,
                                                                                  coef, dv);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_ce_tile_fwd(const float* logits, const long long* labels, long long c0, long long rows, int Vc,
+                               float* m_run, float* s_run, float* tgt, cudaStream_t stream) {
+  if (rows < 1 || Vc < 1) return -1;
+  ce_tile_fwd_kernel<<<(unsigned)rows, 256, 0, stream>>>(logits, labels, c0, Vc, m_run, s_run, tgt);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_pos_resample(const float* tab, int g, int d, float* out, int gh, int gw, cudaStream_t stream) {
+  if (g < 1 || d < 1 || gh < 1 || gw < 1) return -1;
+  pos_resample_kernel<<<grid_for((long long)gh * gw * d, 256), 256, 0, stream>>>(tab, g, d, out, gh, gw);
   return (int)cudaGetLastError();
 }
 

@@ -357,32 +357,78 @@ def rope_fwd(x: Tensor, cos: Tensor, sin: Tensor, inverse: bool = False) -> Tens
 
 
 # --------------------------------------------------------------------------------------------- CE
+CE_VOCAB_TILE = 16384      # vocabulary columns per pass of the tiled cross-entropy head
+
+
+def _ce_tiles(V: int):
+    return [(c0, min(V, c0 + CE_VOCAB_TILE)) for c0 in range(0, V, CE_VOCAB_TILE)]
+
+
 def linear_ce_fwd(h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor):
+    """Per-row cross entropy of ``h @ w.T + b`` and the fp32 log-sum-exp, one vocabulary tile at a time: the logits
+    of a tile (rows x <= 16384, fp32) live only until the tile has been folded into the rows' running max / sum,
+    so the 257 152-wide language-model head never needs its 8 GB of logits."""
     global launch_count
     R, V = h.shape[0], w.shape[0]
-    logits = gemm(h, w, "nt", bias=bias, out_dtype=torch.float32)
-    loss = torch.empty(R, dtype=torch.float32, device=h.device)
-    lse = torch.empty(R, dtype=torch.float32, device=h.device)
     labels = labels.contiguous()
-    _check(_lib.load("elementwise").otb_ce_fwd(_p(logits), _p(labels), _p(loss), _p(lse), c_longlong(R), c_int(V),
-                                               _stream()), "ce_fwd")
-    launch_count += 1
-    return loss, lse
+    lib = _lib.load("elementwise")
+    if V <= CE_VOCAB_TILE:
+        logits = gemm(h, w, "nt", bias=bias, out_dtype=torch.float32)
+        loss = torch.empty(R, dtype=torch.float32, device=h.device)
+        lse = torch.empty(R, dtype=torch.float32, device=h.device)
+        _check(lib.otb_ce_fwd(_p(logits), _p(labels), _p(loss), _p(lse), c_longlong(R), c_int(V), _stream()), "ce_fwd")
+        launch_count += 1
+        return loss, lse
+    m = torch.full((R,), float("-inf"), dtype=torch.float32, device=h.device)
+    s = torch.zeros(R, dtype=torch.float32, device=h.device)
+    tgt = torch.zeros(R, dtype=torch.float32, device=h.device)
+    tile_lib = _lib.load("train_elementwise")
+    for c0, c1 in _ce_tiles(V):
+        logits = gemm(h, w[c0:c1], "nt", bias=bias[c0:c1] if bias is not None else None, out_dtype=torch.float32)
+        _check(tile_lib.otb_ce_tile_fwd(_p(logits), _p(labels), c_longlong(c0), c_longlong(R), c_int(c1 - c0), _p(m),
+                                        _p(s), _p(tgt), _stream()), "ce_tile_fwd")
+        launch_count += 1
+        del logits
+    lse = m + torch.log(s)
+    return lse - tgt, lse
 
 
-def linear_ce_bwd(dloss: Tensor, h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor, lse: Tensor):
+def linear_ce_bwd(dloss: Tensor, h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor, lse: Tensor,
+                  dw_into: Tensor | None = None):
+    """``(dh, dw, dbias)`` of :func:`linear_ce_fwd`, tile by tile: each tile's logits are recomputed, turned into
+    ``(softmax - onehot) * dloss`` (bf16) and consumed by the two gradient products before the next tile starts.
+    ``dw_into``: a ``(V, H)`` gradient buffer the weight gradient is ACCUMULATED into (then ``dw`` is None)."""
     global launch_count
     R, V = h.shape[0], w.shape[0]
-    logits = gemm(h, w, "nt", bias=bias, out_dtype=torch.float32)  # recomputed: logits are never kept
-    dlogits = torch.empty(R, V, dtype=torch.bfloat16, device=h.device)
-    _check(_lib.load("elementwise").otb_ce_bwd(_p(logits), _p(labels.contiguous()), _p(lse),
-                                               _p(dloss.float().contiguous()), _p(dlogits), c_longlong(R), c_int(V),
-                                               _stream()), "ce_bwd")
-    launch_count += 1
-    del logits
-    dh = gemm(dlogits, w, "nn")
-    dw = gemm(dlogits, h, "tn")
-    db = col_sum(dlogits).to(bias.dtype) if bias is not None else None
+    lib = _lib.load("elementwise")
+    labels = labels.contiguous()
+    dl32 = dloss.float().contiguous()
+    tiles = _ce_tiles(V)
+    dh32 = None
+    dw = None if dw_into is not None else torch.empty_like(w)
+    db = torch.empty(V, dtype=bias.dtype, device=h.device) if bias is not None else None
+    for c0, c1 in tiles:
+        wc = w[c0:c1]
+        logits = gemm(h, wc, "nt", bias=bias[c0:c1] if bias is not None else None, out_dtype=torch.float32)
+        dlogits = torch.empty(R, c1 - c0, dtype=torch.bfloat16, device=h.device)
+        lab = labels if c0 == 0 else labels - c0          # a label outside the tile matches no column
+        _check(lib.otb_ce_bwd(_p(logits), _p(lab), _p(lse), _p(dl32), _p(dlogits), c_longlong(R), c_int(c1 - c0),
+                              _stream()), "ce_bwd")
+        launch_count += 1
+        del logits
+        if len(tiles) == 1:
+            dh = gemm(dlogits, wc, "nn")
+        else:
+            part = gemm(dlogits, wc, "nn", out_dtype=torch.float32)
+            dh32 = part if dh32 is None else dh32.add_(part)
+        if dw_into is not None:
+            gemm(dlogits, h, "tn", out=dw_into[c0:c1], accumulate=True)
+        else:
+            gemm(dlogits, h, "tn", out=dw[c0:c1])
+        if db is not None:
+            db[c0:c1] = col_sum(dlogits).to(bias.dtype)
+    if len(tiles) > 1:
+        dh = dh32.to(h.dtype)
     return dh, dw, db
 
 
@@ -663,3 +709,16 @@ def embed_bwd(dout: Tensor, ids: Tensor, grad: Tensor, scale: float, padding_idx
         c_longlong(grad.shape[0]), c_longlong(-1 if padding_idx is None else padding_idx), c_float(scale), _stream()),
         "embed_bwd")
     launch_count += 1
+
+
+def pos_resample(table: Tensor, gh: int, gw: int) -> Tensor:
+    """Bicubic resample of a square ``(g*g, d)`` fp32 position table to ``(gh*gw, d)``."""
+    global launch_count
+    import math
+    g = int(math.isqrt(table.shape[0]))
+    tab = table.detach().float().contiguous()
+    out = torch.empty(gh * gw, tab.shape[1], dtype=torch.float32, device=tab.device)
+    _check(_lib.load("train_elementwise").otb_pos_resample(_p(tab), c_int(g), c_int(tab.shape[1]), _p(out), c_int(gh),
+                                                           c_int(gw), _stream()), "pos_resample")
+    launch_count += 1
+    return out

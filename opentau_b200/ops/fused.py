@@ -245,10 +245,9 @@ class LinearCEFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         h, w, labels, lse = ctx.saved_tensors
-        dh, dw, db = prims.linear_ce_bwd(dloss.contiguous(), h, w, ctx.bref, labels, lse)
         mg = getattr(ctx.wref, "main_grad", None)
+        dh, dw, db = prims.linear_ce_bwd(dloss.contiguous(), h, w, ctx.bref, labels, lse, dw_into=mg)
         if mg is not None:
-            mg.add_(dw.to(mg.dtype))
             _notify(ctx.wref)
             dw = None
         if db is not None:

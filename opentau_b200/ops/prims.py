@@ -306,11 +306,17 @@ def linear_ce_fwd(h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor) -> 
     return lse - tgt, lse
 
 
-def linear_ce_bwd(dloss: Tensor, h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor, lse: Tensor):
-    """Returns ``(dh, dw, dbias)`` for per-row upstream gradients ``dloss (N,)``."""
+def linear_ce_bwd(dloss: Tensor, h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor, lse: Tensor,
+                  dw_into: Tensor | None = None):
+    """Returns ``(dh, dw, dbias)`` for per-row upstream gradients ``dloss (N,)``; with ``dw_into`` the weight
+    gradient is accumulated into that buffer and ``dw`` is None."""
     if _cuda(h):
         from . import cuda_ops
-        return cuda_ops.linear_ce_bwd(dloss, h, w, bias, labels, lse)
+        if dw_into is not None and (dw_into.dtype != torch.bfloat16 or dw_into.stride(1) != 1):
+            dh, dw, db = cuda_ops.linear_ce_bwd(dloss, h, w, bias, labels, lse)
+            dw_into.add_(dw.to(dw_into.dtype))
+            return dh, None, db
+        return cuda_ops.linear_ce_bwd(dloss, h, w, bias, labels, lse, dw_into)
     logits = F.linear(h, w, bias).float()
     p = torch.exp(logits - lse[:, None])
     p[torch.arange(p.shape[0], device=p.device), labels] -= 1.0
@@ -318,4 +324,7 @@ def linear_ce_bwd(dloss: Tensor, h: Tensor, w: Tensor, bias: Tensor | None, labe
     dh = dlogits @ w
     dw = dlogits.t() @ h
     db = dlogits.float().sum(0).to(bias.dtype) if bias is not None else None
+    if dw_into is not None:
+        dw_into.add_(dw.to(dw_into.dtype))
+        dw = None
     return dh, dw, db

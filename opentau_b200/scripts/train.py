@@ -259,8 +259,10 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
 
     # success rates are kept highest-first, losses lowest-first (reference scripts/train.py: higher_is_better is
     # true only for the eval-success metric); "auto" means success when an environment is evaluated in training
-    best_on_success = cfg.running_best_metric in ("success", "eval_success") or (
-        cfg.running_best_metric == "auto" and cfg.env is not None and cfg.eval_freq > 0)
+    resolved = getattr(cfg, "running_best_metric_resolved", None)
+    best_on_success = resolved == "eval_success" if resolved is not None else (
+        cfg.running_best_metric in ("success", "eval_success") or (
+            cfg.running_best_metric == "auto" and cfg.env is not None and cfg.eval_freq > 0))
     best = RunningBestTracker(out_dir, cfg.running_best_count, cfg.running_best_metric,
                               higher_is_better=best_on_success) if cfg.running_best_count else None
     names = list(train_mix.meta.dataset_names)

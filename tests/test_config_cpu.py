@@ -164,3 +164,39 @@ def test_input_resolution_validation(caplog):
         cfg((224, 224), [(180, 320)]).validate_input_resolution(strict=False)              # eval load: warn only
         cfg((224, 224), [(180, 320)], skip_input_resolution_check=True).validate_input_resolution(strict=True)
     assert sum("differs from the bound image features" in r.getMessage() for r in caplog.records) == 2
+
+
+def test_pipeline_config_location_fallbacks_and_running_best_resolution(tmp_path, monkeypatch):
+    """``from_pretrained`` finds ``train_config.json``, falls back to ``hf_config.json``, resolves ``repo@step`` in
+    the local cache and names the cached revisions when one is missing; the running-best metric resolves like the
+    reference's and is never serialised."""
+    import json
+    import pytest
+    from opentau_b200.configs.train import TrainPipelineConfig
+    from opentau_b200.utils import hub
+    raw = {"dataset_mixture": {"datasets": [{"synthetic": {"length": 8, "name": "a"}}], "action_freq": 10.0},
+           "policy": {"type": "pi05"}, "steps": 7, "batch_size": 2}
+    d = tmp_path / "published"
+    d.mkdir()
+    (d / "hf_config.json").write_text(json.dumps(raw))
+    assert TrainPipelineConfig.from_pretrained(d).steps == 7
+    (d / "train_config.json").write_text(json.dumps({**raw, "steps": 9}))
+    assert TrainPipelineConfig.from_pretrained(d).steps == 9              # the training name wins
+    with pytest.raises(FileNotFoundError, match="neither train_config.json nor hf_config.json"):
+        (tmp_path / "empty").mkdir()
+        TrainPipelineConfig.from_pretrained(tmp_path / "empty")
+    monkeypatch.setattr(hub, "HF_OPENTAU_HOME", tmp_path / "cache")
+    rev = tmp_path / "cache" / "org" / "run" / "step-000500"
+    rev.mkdir(parents=True)
+    (rev / "hf_config.json").write_text(json.dumps({**raw, "steps": 500}))
+    assert TrainPipelineConfig.from_pretrained("org/run@500").steps == 500
+    with pytest.raises(FileNotFoundError, match="step-000500"):
+        TrainPipelineConfig.from_pretrained("org/run@123")
+    cfg = TrainPipelineConfig.from_dict({**raw, "running_best_count": 1, "val_freq": 5})
+    cfg.validate()
+    assert cfg.running_best_metric_resolved == "val_loss" and "running_best_metric_resolved" not in cfg.to_dict()
+    bad = TrainPipelineConfig.from_dict({**raw, "running_best_count": 1, "running_best_metric": "eval_success"})
+    with pytest.raises(ValueError, match="simulation evaluation source"):
+        bad.validate()
+    with pytest.raises(ValueError, match="must be one of"):
+        TrainPipelineConfig.from_dict({**raw, "running_best_metric": "accuracy"}).validate()

@@ -43,7 +43,7 @@ def test_fused_step_two_emulated_ranks_matches_reference():
     for r in range(world):
         rc = lib.otb_comm_reduce_scatter(_table(g), c_int(world), c_longlong(r * shard), c_longlong(shard),
                                          c_void_p(g32[r].data_ptr()), c_void_p(partial[r].data_ptr()), c_int(256),
-                                         _stream())
+                                         c_int(2), status, _stream())
         assert rc == 0
     gsum = g[0].float() + g[1].float()
     for r in range(world):
@@ -65,7 +65,7 @@ def test_fused_step_two_emulated_ranks_matches_reference():
                                           c_int(world), c_longlong(r * shard), c_longlong(shard), c_float(hp["lr"]),
                                           c_float(hp["beta1"]), c_float(hp["beta2"]), c_float(hp["eps"]),
                                           c_float(hp["wd"]), c_float(1 - hp["beta1"]), c_float(1 - hp["beta2"]),
-                                          c_void_p(scale[r].data_ptr()), c_int(64), _stream())
+                                          c_void_p(scale[r].data_ptr()), c_int(64), c_int(2), status, _stream())
         assert rc == 0
     torch.cuda.synchronize()
     cuda_ops.check_status()
@@ -88,6 +88,25 @@ def test_barrier_wait_times_out_and_reports_status():
     rc = lib.otb_comm_barrier(_table(flags), c_int(0), c_int(2), c_int(0), c_int(5), c_longlong(2_000_000), status,
                               _stream())
     assert rc == 0
+    # while the record stands, the data kernels behind the wait write NOTHING: a late or dead peer can stall a step
+    # but cannot get half-written gradients averaged into the weights
+    n = 1 << 12
+    g = [torch.ones(n, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    g32 = torch.full((n,), 7.0, device=dev)
+    partial = torch.full((64,), 7.0, device=dev)
+    assert lib.otb_comm_reduce_scatter(_table(g), c_int(2), c_longlong(0), c_longlong(n), c_void_p(g32.data_ptr()),
+                                       c_void_p(partial.data_ptr()), c_int(64), c_int(2), status, _stream()) == 0
+    p16 = [torch.full((n,), 3.0, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    master, m, v = torch.full((n,), 3.0, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    scale = torch.ones(2, device=dev)
+    assert lib.otb_comm_adamw_allgather(
+        c_void_p(master.data_ptr()), c_void_p(g32.data_ptr()), c_void_p(m.data_ptr()), c_void_p(v.data_ptr()),
+        _table(p16), c_int(2), c_longlong(0), c_longlong(n), c_float(0.1), c_float(0.9), c_float(0.95), c_float(1e-8),
+        c_float(0.0), c_float(0.1), c_float(0.05), c_void_p(scale.data_ptr()), c_int(16), c_int(2), status,
+        _stream()) == 0
+    torch.cuda.synchronize()
+    assert float(g32.min()) == 7.0 and float(partial.min()) == 7.0 and float(master.min()) == 3.0
+    assert float(p16[1].float().min()) == 3.0 and float(m.abs().max()) == 0.0
     with pytest.raises(RuntimeError, match="timed out"):
         cuda_ops.check_status()
     cuda_ops.check_status()                       # status word was reset

@@ -104,3 +104,73 @@ def test_embedding_gather_and_scatter_add(grad_dtype, dev):
     cuda_ops.embed_bwd(dout, ids, a, scale, 0)
     cuda_ops.embed_bwd(dout, ids, b, scale, 0)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("with_bias,into_main_grad", [(True, False), (False, True)])
+def test_vocabulary_tiled_cross_entropy_head(with_bias, into_main_grad, dev, monkeypatch):
+    """The CE head over several vocabulary tiles (no rows x vocabulary tensor in either direction) equals the fp32
+    statement; also with the weight gradient accumulated straight into a flat gradient buffer."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import cuda_ops
+    monkeypatch.setattr(cuda_ops, "CE_VOCAB_TILE", 256)
+    torch.manual_seed(4)
+    R, H, V = 300, 128, 1000                           # tiles of 256, 256, 256 and 232 columns
+    h = (torch.randn(R, H, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = torch.nn.Parameter((torch.randn(V, H, device=dev) * 0.2).to(torch.bfloat16))
+    b = torch.nn.Parameter((torch.randn(V, device=dev) * 0.1).to(torch.bfloat16)) if with_bias else None
+    labels = torch.randint(0, V, (R,), device=dev)
+    labels[:4] = torch.tensor([0, 255, 256, V - 1], device=dev)      # tile borders
+    if into_main_grad:
+        w.main_grad = torch.full((V, H), 0.5, device=dev, dtype=torch.bfloat16)
+    loss = ops.linear_cross_entropy(h, w, b, labels)
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    br = b.detach().float().requires_grad_(True) if with_bias else None
+    want = torch.nn.functional.cross_entropy(torch.nn.functional.linear(hr, wr, br), labels, reduction="none")
+    torch.testing.assert_close(loss, want, rtol=2e-2, atol=2e-2)
+    wts = torch.rand(R, device=dev)
+    (loss * wts).sum().backward()
+    (want * wts).sum().backward()
+    torch.testing.assert_close(h.grad.float(), hr.grad, rtol=5e-2, atol=2e-2)
+    if into_main_grad:
+        assert w.grad is None
+        torch.testing.assert_close(w.main_grad.float() - 0.5, wr.grad, rtol=5e-2, atol=3e-2)
+    else:
+        torch.testing.assert_close(w.grad.float(), wr.grad, rtol=5e-2, atol=3e-2)
+    if with_bias:
+        torch.testing.assert_close(b.grad.float(), br.grad, rtol=5e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("grid", [(16, 16), (13, 23), (32, 20), (7, 7)])
+def test_position_table_resample_matches_bicubic_interpolate(grid, dev):
+    """Native-resolution inputs: the 16 x 16 SigLIP position table resampled to the image's patch grid equals
+    ``F.interpolate(mode="bicubic", align_corners=False)``."""
+    from opentau_b200.ops import cuda_ops
+    torch.manual_seed(5)
+    g, d = 16, 96
+    tab = torch.randn(g * g, d, device=dev)
+    gh, gw = grid
+    got = cuda_ops.pos_resample(tab, gh, gw)
+    want = torch.nn.functional.interpolate(tab.view(1, g, g, d).permute(0, 3, 1, 2), size=(gh, gw), mode="bicubic",
+                                           align_corners=False).permute(0, 2, 3, 1).reshape(gh * gw, d)
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+
+
+def test_native_resolution_image_through_the_vision_tower(dev):
+    """A 180 x 320 image (not a patch multiple, not the config grid) is padded to patches and embedded with the
+    resampled position table; the tower's output matches the CPU fp32 tower."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from opentau_b200.models.siglip import SiglipConfig, SiglipVisionModel
+    torch.manual_seed(6)
+    cfg = SiglipConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                       patch_size=14, image_size=224)
+    cpu = SiglipVisionModel(cfg).eval()
+    gpu = SiglipVisionModel(cfg).eval()
+    gpu.load_state_dict(cpu.state_dict())
+    gpu = gpu.to(dev).to(torch.bfloat16)
+    x = torch.rand(2, 3, 180, 320) * 2 - 1
+    with torch.no_grad():
+        want = cpu(x)
+        got = gpu(x.to(dev).to(torch.bfloat16))
+    assert got.shape == want.shape == (2, 13 * 23, 128)
+    torch.testing.assert_close(got.float().cpu(), want, rtol=5e-2, atol=5e-2)
