@@ -31,6 +31,11 @@ enum EpiFlags {
   EPI_BIAS_F32 = 64,   // bias is fp32
   EPI_NO_OUT = 128,    // skip the plain store of D (GLU inference: only out2 is wanted)
   EPI_ACT_GELU = 256,  // out = gelu_tanh(result + bias)
+  // 512 (EPI_GATE) belongs to the few-row kernel
+  EPI_GLU_BWD_GELU = 1024,  // the result is dH of a gated MLP: out2 holds the saved gate/up (block-interleaved, 2N
+                            // columns) and is overwritten IN PLACE with (dgate, dup) = (dH * up * act'(gate),
+                            // dH * act(gate)); dH itself is never written (combine with EPI_NO_OUT)
+  EPI_GLU_BWD_SILU = 2048,
 };
 
 struct GemmParams {
@@ -275,6 +280,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
         }
+        if (active && (flags & (EPI_GLU_BWD_GELU | EPI_GLU_BWD_SILU))) {
+          // r = dH[row, col0 .. col0+31]; its gate block sits at out2[row, 2*col0 .. +31], its up block right behind
+          __nv_bfloat16* gp = p.out2 + (long long)row * p.ldo2 + 2LL * col0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 gq = *reinterpret_cast<const uint4*>(gp + j * 8);
+            const uint4 uq = *reinterpret_cast<const uint4*>(gp + 32 + j * 8);
+            const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
+            float dg[8], du[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float2 g2 = unpack_bf16(gw[e >> 1]), u2 = unpack_bf16(uw[e >> 1]);
+              const float x = (e & 1) ? g2.y : g2.x, u = (e & 1) ? u2.y : u2.x;
+              const float d = __uint_as_float(r[j * 8 + e]);
+              float a, da;
+              if (flags & EPI_GLU_BWD_GELU) {
+                // s = sigmoid(2t) = 0.5 (1 + tanh t); 1 - tanh^2 t = 4 s (1 - s)
+                const float k = 0.7978845608028654f;
+                const float inner = k * (x + 0.044715f * x * x * x);
+                const float sg = __fdividef(1.f, 1.f + __expf(-2.f * inner));
+                a = x * sg;
+                da = sg + 2.f * x * sg * (1.f - sg) * k * (1.f + 3.f * 0.044715f * x * x);
+              } else {
+                const float sg = __fdividef(1.f, 1.f + __expf(-x));
+                a = x * sg;
+                da = sg * (1.f + x * (1.f - sg));
+              }
+              dg[e] = d * u * da;
+              du[e] = d * a;
+            }
+            uint4 o;
+            o.x = pack_bf16(dg[0], dg[1]); o.y = pack_bf16(dg[2], dg[3]);
+            o.z = pack_bf16(dg[4], dg[5]); o.w = pack_bf16(dg[6], dg[7]);
+            *reinterpret_cast<uint4*>(gp + j * 8) = o;
+            o.x = pack_bf16(du[0], du[1]); o.y = pack_bf16(du[2], du[3]);
+            o.z = pack_bf16(du[4], du[5]); o.w = pack_bf16(du[6], du[7]);
+            *reinterpret_cast<uint4*>(gp + 32 + j * 8) = o;
+          }
+        }
         if (active && glu) {
           // gate = r (columns col0..col0+31), up = r2; output column = col0/2 .. +31
           const int ocol0 = col0 >> 1;
@@ -355,6 +399,10 @@ extern "C" int otb_gemm_bf16(const void* A, const void* B, void* out, int M, int
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15) return -4;
   if ((flags & EPI_RESIDUAL) && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -5;
   if ((flags & (EPI_GLU_GELU | EPI_GLU_SILU)) && ((N % 64) || (ldo2 % 8) || out2 == nullptr)) return -6;
+  if ((flags & (EPI_GLU_BWD_GELU | EPI_GLU_BWD_SILU)) &&
+      ((N % 32) || (ldo2 % 8) || out2 == nullptr || (reinterpret_cast<uintptr_t>(out2) & 15) ||
+       (flags & (EPI_GLU_GELU | EPI_GLU_SILU))))
+    return -9;
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);

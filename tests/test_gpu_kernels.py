@@ -144,6 +144,29 @@ def test_gemm_glu_epilogue(act, dev):
     cuda_ops.check_status()
 
 
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("shape", [(260, 256, 384), (1000, 512, 2048), (128, 64, 64)])
+def test_gemm_glu_backward_epilogue(act, shape, dev):
+    """dH = dy @ w_down is turned into (dgate, dup) in the GEMM's epilogue, in place over the saved gate / up: equals
+    the product followed by the gated-MLP backward in fp32."""
+    from opentau_b200.ops import cuda_ops, prims
+    M, H, I = shape
+    torch.manual_seed(M + I)
+    dy = (torch.randn(M, H) * 0.5).to(torch.bfloat16).to(dev)
+    w_down = (torch.randn(H, I) * 0.1).to(torch.bfloat16).to(dev)
+    gu = torch.randn(M, 2 * I).to(torch.bfloat16).to(dev)
+    want = prims.glu_bwd(gu.cpu().float(), dy.cpu().float() @ w_down.cpu().float(), act)
+    keep = gu.clone()
+    got = prims.mm_nn_glu_bwd(dy, w_down, gu, act)
+    assert got.data_ptr() == gu.data_ptr()                          # in place
+    torch.testing.assert_close(got.cpu().float(), want, rtol=3e-2, atol=3e-2)
+    # the unfused pair gives the same result (dH rounded to bf16 in between)
+    dh = cuda_ops.gemm(dy, w_down, "nn")
+    ref2 = cuda_ops.glu_bwd(keep, dh, act)
+    torch.testing.assert_close(got.float(), ref2.float(), rtol=3e-2, atol=3e-2)
+    cuda_ops.check_status()
+
+
 @pytest.mark.parametrize("H", [64, 256, 1024, 1152, 2048, 5120])
 @pytest.mark.parametrize("mode", ["plain1", "plain0", "noweight"])
 def test_rms_norm_kernels(H, mode, dev):
