@@ -21,7 +21,6 @@ launch_count = 0  # number of native kernel launches issued through this module 
 
 EPI_BIAS, EPI_RESIDUAL, EPI_ACCUM, EPI_OUT_F32 = 1, 2, 4, 8
 EPI_GLU_GELU, EPI_GLU_SILU, EPI_BIAS_F32, EPI_NO_OUT, EPI_ACT_GELU, EPI_GATE = 16, 32, 64, 128, 256, 512
-EPI_GLU_BWD_GELU, EPI_GLU_BWD_SILU = 1024, 2048
 
 _status_ptr: dict[int, int] = {}
 
@@ -77,7 +76,7 @@ def use_skinny(layout: str, M: int, N: int, accumulate: bool, bn: int) -> bool:
 def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual: Tensor | None = None,
          out: Tensor | None = None, accumulate: bool = False, out_dtype: torch.dtype | None = None,
          glu: str | None = None, glu_out: Tensor | None = None, store_out: bool = True, act: str | None = None,
-         bn: int = 0, splits: int = 0, gate: Tensor | None = None, glu_bwd: str | None = None) -> Tensor:
+         bn: int = 0, splits: int = 0, gate: Tensor | None = None) -> Tensor:
     """tcgen05 GEMM.  layout 'nt': a(M,K) b(N,K); 'nn': a(M,K) b(K,N); 'tn': a(K,M) b(K,N).  ``bn`` forces the column
     tile of the persistent kernel, ``splits`` (1, 2, 4, 8) forces the weight-streaming split-K kernel."""
     global launch_count
@@ -144,17 +143,9 @@ def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual
         if glu_out is None:
             glu_out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=a.device)
         ldo2 = glu_out.stride(0)
-    if glu_bwd is not None:
-        # the product is dH of a gated MLP: `glu_out` holds the saved gate / up (M, 2N, block-interleaved) and is
-        # overwritten in place with their gradients; dH itself is not stored
-        if glu is not None or glu_out is None or glu_out.shape != (M, 2 * N) or glu_out.dtype != torch.bfloat16 \
-                or glu_out.stride(1) != 1 or N % 32 or store_out:
-            raise ValueError("bad arguments for the gated-MLP backward epilogue")
-        flags |= EPI_GLU_BWD_GELU if glu_bwd == "gelu_tanh" else EPI_GLU_BWD_SILU
-        ldo2 = glu_out.stride(0)
     if splits and (layout != "nt" or accumulate):
         raise ValueError("the split-K kernel computes a @ b^T without accumulation")
-    skinny = (bool(splits) or use_skinny(layout, M, N, accumulate, bn)) and glu_bwd is None
+    skinny = bool(splits) or use_skinny(layout, M, N, accumulate, bn)
     g_stride, g_rows = 0, 1
     if gate is not None:
         # out = residual + gate * (a @ b^T): rows of N gates, one per `M / gate rows` consecutive output rows
@@ -181,8 +172,6 @@ def gemm(a: Tensor, b: Tensor, layout: str, bias: Tensor | None = None, residual
         _stream())
     _check(rc, f"gemm[{layout} {M}x{N}x{K}]")
     launch_count += 1
-    if glu_bwd is not None:
-        return glu_out
     if glu is not None:
         return glu_out if not store_out else (out, glu_out)
     return out

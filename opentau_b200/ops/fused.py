@@ -118,8 +118,9 @@ class GatedMLPFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dwd = _sink_wgrad(ctx.wdown, dy2, h) if ctx.needs_input_grad[2] else None
-        del h
-        dgu = prims.mm_nn_glu_bwd(dy2, w_down, gu, ctx.act)   # dH lives only in the GEMM's accumulator
+        dh = prims.mm_nn(dy2, w_down, out=h)  # h is dead after the weight gradient
+        dgu = prims.glu_bwd(gu, dh, ctx.act, inplace=True)
+        del dh, h
         dwgu = _sink_wgrad(ctx.wgu, dgu, x2) if ctx.needs_input_grad[1] else None
         dx = prims.mm_nn(dgu, w_gu).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         return dx, dwgu, dwd, (dy if ctx.has_res else None), None

@@ -202,16 +202,6 @@ def glu_fwd(gu: Tensor, act: str) -> Tensor:
     return (a * u.float()).flatten(-2).to(gu.dtype)
 
 
-def mm_nn_glu_bwd(dy: Tensor, w_down: Tensor, gu: Tensor, act: str) -> Tensor:
-    """``dgu`` of a gated MLP from the gradient of its output: ``dH = dy @ w_down`` is formed tile by tile in
-    tensor memory and turned into ``(dgate, dup)`` in the GEMM's epilogue, which OVERWRITES ``gu`` in place; dH is
-    never written to memory (it is the widest tensor of the layer's backward pass)."""
-    if _cuda(dy) and gu.is_contiguous() and gu.shape[-1] % 64 == 0:
-        from . import cuda_ops
-        return cuda_ops.gemm(dy, w_down, "nn", store_out=False, glu_bwd=act, glu_out=gu)
-    return glu_bwd(gu, mm_nn(dy, w_down), act, inplace=True)
-
-
 def glu_bwd(gu: Tensor, dh: Tensor, act: str, inplace: bool = False) -> Tensor:
     """Gradient w.r.t. the interleaved ``gu``; may overwrite ``gu`` when ``inplace``."""
     if _cuda(gu):

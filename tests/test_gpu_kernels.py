@@ -33,7 +33,7 @@ def _operands(layout, M, N, K, dev):
 @pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 264, 136), (1000, 2048, 1024),
                                    (50, 1024, 2048), (384, 64, 512), (130, 128, 72)])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512])        # 512: the CTA-pair kernel (256 x 256 tiles on two SMs)
 def test_gemm_layouts(layout, shape, bn, dev):
     from opentau_b200.ops import cuda_ops
     M, N, K = shape
@@ -141,29 +141,6 @@ def test_gemm_glu_epilogue(act, dev):
     dgu = cuda_ops.glu_bwd(gu, dh, act)
     dgu_ref = prims.glu_bwd(gu.cpu().float(), dh.cpu().float(), act)
     torch.testing.assert_close(dgu.cpu().float(), dgu_ref, rtol=3e-2, atol=3e-2)
-    cuda_ops.check_status()
-
-
-@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
-@pytest.mark.parametrize("shape", [(260, 256, 384), (1000, 512, 2048), (128, 64, 64)])
-def test_gemm_glu_backward_epilogue(act, shape, dev):
-    """dH = dy @ w_down is turned into (dgate, dup) in the GEMM's epilogue, in place over the saved gate / up: equals
-    the product followed by the gated-MLP backward in fp32."""
-    from opentau_b200.ops import cuda_ops, prims
-    M, H, I = shape
-    torch.manual_seed(M + I)
-    dy = (torch.randn(M, H) * 0.5).to(torch.bfloat16).to(dev)
-    w_down = (torch.randn(H, I) * 0.1).to(torch.bfloat16).to(dev)
-    gu = torch.randn(M, 2 * I).to(torch.bfloat16).to(dev)
-    want = prims.glu_bwd(gu.cpu().float(), dy.cpu().float() @ w_down.cpu().float(), act)
-    keep = gu.clone()
-    got = prims.mm_nn_glu_bwd(dy, w_down, gu, act)
-    assert got.data_ptr() == gu.data_ptr()                          # in place
-    torch.testing.assert_close(got.cpu().float(), want, rtol=3e-2, atol=3e-2)
-    # the unfused pair gives the same result (dH rounded to bf16 in between)
-    dh = cuda_ops.gemm(dy, w_down, "nn")
-    ref2 = cuda_ops.glu_bwd(keep, dh, act)
-    torch.testing.assert_close(got.float(), ref2.float(), rtol=3e-2, atol=3e-2)
     cuda_ops.check_status()
 
 
@@ -470,3 +447,39 @@ def test_patch_embed_kernel(pix_dtype, out_dtype, dev):
     torch.testing.assert_close(w.grad, w2.grad, atol=1e-3, rtol=1e-3)
     torch.testing.assert_close(b.grad, b2.grad, atol=1e-3, rtol=1e-3)
     torch.testing.assert_close(pos.grad, pos2.grad, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("shape", [(2048, 2048, 512), (1500, 1288, 328), (4096, 1024, 2048), (520, 264, 72)])
+def test_cta_pair_gemm_epilogues(layout, shape, dev):
+    """The CTA-pair kernel (tcgen05 cta_group::2, each CTA loads half of the B tile) on full, ragged and tiny
+    problems, with the residual / bias / accumulate epilogues; run twice: bitwise identical."""
+    from opentau_b200.ops import cuda_ops
+    M, N, K = shape
+    a, b = _operands(layout, M, N, K, dev)
+    want = _ref_gemm(a, b, layout)
+    got = cuda_ops.gemm(a, b, layout, bn=512)
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+    assert torch.equal(got, cuda_ops.gemm(a, b, layout, bn=512))
+    bias = torch.randn(N, device=dev).to(torch.bfloat16)
+    res = torch.randn(M, N, device=dev).to(torch.bfloat16)
+    got2 = cuda_ops.gemm(a, b, layout, bias=bias, residual=res, bn=512)
+    torch.testing.assert_close(got2.float(), want + bias.float() + res.float(), rtol=2e-2,
+                               atol=2e-2 * float(want.abs().max()))
+    acc = torch.ones(M, N, device=dev, dtype=torch.bfloat16)
+    cuda_ops.gemm(a, b, layout, out=acc, accumulate=True, bn=512)
+    torch.testing.assert_close(acc.float(), want + 1.0, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_cta_pair_gemm_glu_epilogues(act, dev):
+    from opentau_b200.ops import cuda_ops, prims
+    M, K, I = 1100, 256, 1024
+    x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(dev)
+    w = (torch.randn(2 * I, K) * 0.1).to(torch.bfloat16).to(dev)
+    gu, h = cuda_ops.gemm(x, w, "nt", glu=act, bn=512)
+    gu1, h1 = cuda_ops.gemm(x, w, "nt", glu=act, bn=256)
+    torch.testing.assert_close(gu.float(), gu1.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(h.float(), h1.float(), rtol=1e-2, atol=1e-2)
+    cuda_ops.check_status()
