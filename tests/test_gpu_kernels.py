@@ -450,7 +450,7 @@ def test_patch_embed_kernel(pix_dtype, out_dtype, dev):
 
 
 @pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
-@pytest.mark.parametrize("shape", [(2048, 2048, 512), (1500, 1288, 328), (4096, 1024, 2048), (520, 264, 72)])
+@pytest.mark.parametrize("shape", [(2048, 2048, 512), (1504, 1288, 328), (4096, 1024, 2048), (520, 264, 72)])
 def test_cta_pair_gemm_epilogues(layout, shape, dev):
     """The CTA-pair kernel (tcgen05 cta_group::2, each CTA loads half of the B tile) on full, ragged and tiny
     problems, with the residual / bias / accumulate epilogues; run twice: bitwise identical."""
