@@ -104,3 +104,51 @@ def test_success_role_resolution_chain_and_mistake_polarity():
     assert attach(Fake({}), item, {}, 0) is None and "mistake_raw" not in item
     item = {"oops": torch.tensor([0])}
     assert attach(Fake({"mistake": "oops"}), item, {}, 0) is None and item["mistake_raw"] is False
+
+
+def test_video_backend_selection_tolerance_and_resample(tmp_path, caplog):
+    """Backend probing falls back in order and warns once; every query must lie within the tolerance of a decoded
+    frame; a clip is re-timed and trimmed to an exact frame count."""
+    import logging
+    import numpy as np
+    import pytest
+    import torch
+    from opentau_b200.datasets import video_utils as vu
+    from opentau_b200.scripts.eval import write_video
+    assert vu.get_safe_default_codec() in vu.BACKENDS
+    assert vu.resolve_backend(None) == vu.get_safe_default_codec()
+    with pytest.raises(ValueError, match="Unsupported video backend"):
+        vu.resolve_backend("gstreamer")
+    if vu._probe_backend("torchcodec") is not None:
+        vu._warn_downgrade.cache_clear()
+        with caplog.at_level(logging.WARNING):
+            a = vu.resolve_backend("torchcodec")
+            b = vu.resolve_backend("torchcodec")
+        assert a == b == vu.get_safe_default_codec()
+        assert sum("was requested but cannot load" in r.message for r in caplog.records) == 1     # once per process
+    frames = np.stack([np.full((32, 48, 3), 10 * i, np.uint8) for i in range(20)])
+    src = tmp_path / "src.mp4"
+    write_video(src, frames, 10)
+    got = vu.decode_video_frames(src, [0.0, 0.5, 1.9], tolerance_s=0.04, backend="opencv")
+    assert got.shape == (3, 3, 32, 48) and abs(float(got[1].mean()) * 255 - 50) < 6
+    with pytest.raises(vu.FrameTimestampError):
+        vu.decode_video_frames(src, [0.55], tolerance_s=0.01, backend="opencv")
+    idx = vu._check_tolerance(torch.tensor([0.1, 0.31]), torch.tensor([0.0, 0.1, 0.2, 0.3]), 0.02, "x")
+    assert idx.tolist() == [1, 3]
+    with pytest.raises(vu.FrameTimestampError, match="farther than tolerance_s"):
+        vu._check_tolerance(torch.tensor([0.16]), torch.tensor([0.0, 0.1, 0.2]), 0.02, "x")
+    assert vu.get_video_pixel_channels("yuv420p") == 3 and vu.get_video_pixel_channels("gray16le") == 1
+    assert vu.get_video_pixel_channels("yuva420p") == 4
+    with pytest.raises(ValueError):
+        vu.get_video_pixel_channels("bayer")
+    from PIL import Image
+    assert vu.get_image_pixel_channels(Image.new("RGBA", (2, 2))) == 4
+    out = tmp_path / "out.mp4"
+    vu.resample_and_trim_video(src, out, target_fps=5, num_frames=6, start_time=0.4)
+    info = vu.get_video_info(out)
+    assert info["video.num_frames"] == 6 and abs(info["video.fps"] - 5) < 0.01
+    first = vu.decode_video_frames(out, [0.0], 0.05, backend="opencv")
+    assert abs(float(first.mean()) * 255 - 40) < 6                        # source frame 4 (0.4 s at 10 fps)
+    with pytest.raises(ValueError, match="too short"):
+        vu.resample_and_trim_video(src, tmp_path / "o2.mp4", target_fps=10, num_frames=40)
+    vu.close_all()
