@@ -375,6 +375,179 @@ def run_train(args) -> int:
     return 0
 
 
+def run_infer(args) -> int:
+    """Prints the benchmark line for the reference's pi0.5 action-chunk latency (scripts/benchmark_inference.py:
+    policy in bf16 with the SigLIP embeddings kept fp32, ``policy.model.sample_actions`` compiled unless
+    ``--ref-compile off``, batch 1, ``policy.sample_actions`` in a timed loop), or its ``unavailable`` line."""
+    if args.model != "pi05":
+        return _unavailable(f"the reference arm builds pi0.5 only; the {args.model} policy of the reference needs its "
+                            "backbone's hub processor files, which this machine cannot fetch (cosmos3 has a "
+                            "published 1 x B200 figure instead, carried in vs_baseline)")
+    if not os.path.isdir(os.path.join(REF_ROOT, "opentau")):
+        return _unavailable("baseline/_ref holds no installed reference (pip install --target baseline/_ref "
+                            "/root/reference was not run on this machine)")
+    try:
+        shims = _prepare_imports()
+        import torch
+        import torch.distributed as dist
+        import opentau  # noqa: F401
+        from opentau.configs.types import FeatureType, PolicyFeature
+        from opentau.policies.pi05 import modeling_pi05 as ref_modeling
+        from opentau.policies.pi05.configuration_pi05 import PI05Config
+        from opentau.policies.utils import to_dtype_preserving_siglip_float32
+    except Exception as exc:
+        import traceback
+        return _unavailable(f"reference import failed: {type(exc).__name__}: {exc} | "
+                            f"{traceback.format_exc().strip().splitlines()[-3:]}")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    use_cuda = torch.cuda.is_available()
+    device = torch.device(f"cuda:{local_rank}" if use_cuda else "cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl" if use_cuda else "gloo", device_id=device if use_cuda else None)
+
+    cams, prompt_len, num_steps = 3, 200, 10
+    if args.tiny:
+        prompt_len = 16
+        _tiny_geometry(ref_modeling)
+        SyntheticTokenizer.vocab_size = 1024
+    tok = SyntheticTokenizer(seed=rank, id_high=1000 if args.tiny else 256000)
+    fast = SyntheticFastProcessor(256 if args.tiny else 2048, 16 if args.tiny else 256, seed=100 + rank)
+    ref_modeling.AutoTokenizer = type("_Tok", (), {"from_pretrained": staticmethod(lambda *a, **k: tok)})
+    ref_modeling.AutoProcessor = type("_Proc", (), {"from_pretrained": staticmethod(lambda *a, **k: fast)})
+
+    feats = {f"camera{i}": PolicyFeature(type=FeatureType.VISUAL, shape=(3, 224, 224)) for i in range(cams)}
+    feats["state"] = PolicyFeature(type=FeatureType.STATE, shape=(32,))
+    compile_on = args.ref_compile == "on"
+    try:
+        cfg = PI05Config(chunk_size=50, n_action_steps=50, prompt_max_length=prompt_len, num_steps=num_steps,
+                         discrete_action_max_length=16 if args.tiny else 256,
+                         attention_implementation=args.ref_attn,
+                         **({"proj_width": 128} if args.tiny else {}),
+                         input_features=feats,
+                         output_features={"actions": PolicyFeature(type=FeatureType.ACTION, shape=(32,))})
+        torch.manual_seed(1234)
+        with torch.device(device):
+            policy = ref_modeling.PI05Policy(cfg, per_dataset_stats=[_identity_stats(torch, cams)])
+        to_dtype_preserving_siglip_float32(policy, device=device, dtype=torch.bfloat16)
+        policy.eval()
+        policy.reset()
+    except Exception as exc:
+        import traceback
+        traceback.print_exc(file=sys.stderr)
+        return _unavailable(f"reference policy construction failed on this image (transformers "
+                            f"{_tf_version()}): {type(exc).__name__}: {exc}")
+
+    g = torch.Generator().manual_seed(7 + rank)
+    host = {f"camera{i}": torch.rand(1, 3, 224, 224, generator=g).to(torch.bfloat16) for i in range(cams)}
+    host["state"] = torch.randn(1, 32, generator=g).clamp_(-1, 1).to(torch.bfloat16)
+    if use_cuda:
+        host = {k: v.pin_memory() for k, v in host.items()}
+    h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
+    prompt = ["pick up the object and place it in the bin"]
+
+    def observation(non_blocking):
+        b = {k: v.to(device, non_blocking=non_blocking) for k, v in host.items()}
+        b["prompt"] = list(prompt)
+        return b
+
+    resident = observation(False)
+    eager = policy.model.sample_actions
+    compile_error = None
+
+    def one(e2e: bool):
+        if use_cuda:
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        t0 = time.perf_counter()
+        with torch.inference_mode():
+            out = policy.sample_actions(observation(True) if e2e else dict(resident))
+            if e2e:
+                out = out.float().cpu()
+        if use_cuda:
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1), out
+        return (time.perf_counter() - t0) * 1e3, out
+
+    n_warm = max(args.warmup, 3)
+    if compile_on:
+        torch._dynamo.reset()
+        policy.model.sample_actions = torch.compile(eager, mode="reduce-overhead", fullgraph=False)
+    try:
+        first_ms = one(False)[0]
+        for _ in range(n_warm - 1):
+            one(False)
+    except Exception as exc:
+        if not compile_on:
+            import traceback
+            traceback.print_exc(file=sys.stderr)
+            return _unavailable(f"reference sample_actions failed on this image: {type(exc).__name__}: "
+                                f"{str(exc)[:160]}")
+        compile_error = f"{type(exc).__name__}: {str(exc)[:160]}"
+    if compile_error is not None:
+        # the compiled sampler does not build here: the reference's own --no-compile path
+        torch._dynamo.reset()
+        policy.model.sample_actions = eager
+        compile_on = False
+        first_ms = one(False)[0]
+        for _ in range(n_warm - 1):
+            one(False)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        if use_cuda:
+            torch.cuda.synchronize()
+
+    sampler = args.clock_sampler(local_rank) if (rank == 0 and use_cuda) else None
+    if sampler:
+        sampler.start()
+    sync()
+    dev_ms = sorted(one(False)[0] for _ in range(args.steps))
+    sync()
+    one(True)
+    res = [one(True) for _ in range(args.steps)]
+    sync()
+    clocks = sampler.stop() if sampler else {}
+    e2e_ms, out = sorted(r[0] for r in res), res[-1][1]
+    stats = torch.tensor([dev_ms[len(dev_ms) // 2], e2e_ms[len(e2e_ms) // 2], sum(dev_ms) / len(dev_ms)],
+                         dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({
+            "metric": f"pi05 p50 {num_steps}-step action-chunk latency", "value": round(float(stats[0]), 3),
+            "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
+            "ms_per_step": round(float(stats[2]), 3), "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"model": "pi0.5 full (reference PI05Policy, default geometry)" if not args.tiny
+                       else "pi0.5 tiny (plumbing)", "global_batch": world, "parallelism": f"replica x{world}",
+                       "denoise_steps": num_steps, "action_chunk": "50x32", "prompt_tokens": prompt_len,
+                       "attention_implementation": args.ref_attn,
+                       "torch_compile": "reduce-overhead" if compile_on else "off",
+                       **({"torch_compile_failed": compile_error} if compile_error else {}),
+                       "first_call_ms": round(first_ms, 1),
+                       "l2": "each call streams every bf16 weight once (GBs, far more than the 126 MB L2); no "
+                             "explicit flush"},
+            "reference_shims": shims,
+            "env": {k: os.environ.get(k) for k in ("PYTORCH_CUDA_ALLOC_CONF", "CXX", "CC")},
+            "tokenizer_assets": "synthetic (hub tokenizers unavailable offline): uniform-random ids",
+            "clocks": clocks,
+            "e2e": {"value": round(float(stats[1]), 3), "unit": "ms", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": out.numel() * out.element_size()},
+            "gpu_launches": 0,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def _tf_version() -> str:
     try:
         import transformers
