@@ -381,9 +381,12 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
                                  if args.model == "pi05" else
                                  "pi0.6 (Gemma-3-4B backbone, SigLIP @448 x3 cams pooled to 256 tokens each, "
                                  "1280-wide 34-layer expert)" if args.model == "pi06" else
+                                 "cosmos3 (Qwen3-VL-32B-shaped backbone sharded over the ranks, 24-layer expert on "
+                                 "backbone layer 63, 2 cams @448, 128 prompt tokens)" if args.tp > 1 else
                                  "cosmos3 (Qwen3-VL-32B-shaped backbone, 64-layer 0.9B expert, 3 cams @224, "
                                  "prompt <= 64 tokens)"),
-                       "global_batch": world, "parallelism": f"replica x{world}",
+                       "global_batch": world,
+                       "parallelism": f"tp{args.tp}, one observation per rank" if args.tp > 1 else f"replica x{world}",
                        "params": n_params, "denoise_steps": num_steps, "action_chunk": "50x32",
                        "cuda_graph": bool(use_graphs), "tensor_parallel": args.tp,
                        "l2": "each call streams every bf16 weight once (GBs, far more than the 126 MB L2); no "
@@ -550,7 +553,8 @@ def main():
         engine.check()
     if args.kernel_table:
         if rank == 0:
-            write_kernel_table(args.kernel_table, lambda: run_device_only(1), sync)
+            # local synchronisation only: the other ranks run the same step without the tracer around it
+            write_kernel_table(args.kernel_table, lambda: run_device_only(1), torch.cuda.synchronize)
         else:
             run_device_only(1)
         if world > 1:

@@ -19,6 +19,12 @@
 //   * All calls on a device share the one array and it keeps the previous call's contents.  Nothing in it has
 //     to start at zero: each launch overwrites every element it later reads.  Two calls whose kernels overlap
 //     in time on the same GPU (different streams) race on the scratch; serialise them.
+//   * `a`, `out` and `stream` must belong to the device that is current in the calling thread: the scratch
+//     address is looked up for the current device and nothing checks the pointers against it.  A pointer of
+//     another GPU would be combined with this GPU's scratch.
+//   * The per-device address cache is filled without a lock.  Two host threads that make the very first call
+//     on a device at the same moment both store the same value, which is harmless, but the cache is not
+//     otherwise thread-safe: make the first call per device from one thread before sharing the entry point.
 //   * No cudaMalloc, cudaFree or other allocating routine is called, on any path.
 #pragma once
 #include <cuda_runtime.h>

@@ -213,6 +213,15 @@ class Cosmos3FlowMatching(nn.Module):
             out["MSE_per_sample"], out["CE_per_sample"] = per, (z, z.clone())
         return out
 
+    def executed_rows(self, batch: int, device, frozen: Tensor | None = None) -> Tensor:
+        """``(B, chunk)`` bool rows that are executed: not frozen and inside the first ``n_action_steps`` live rows."""
+        from ..accel import executed_row_mask
+        cfg = self.config
+        if frozen is None:
+            frozen = torch.zeros(batch, cfg.chunk_size, dtype=torch.bool, device=device)
+        return executed_row_mask(prefix_mask=frozen, delay=frozen.sum(dim=1), chunk_size=cfg.chunk_size,
+                                 n_action_steps=cfg.n_action_steps, device=device)
+
     @torch.no_grad()
     def sample_actions(self, images, img_masks, lang_tokens, lang_masks, state, noise=None, action_prefix=None,
                        frozen=None, n_candidates: int = 1, accel=None) -> Tensor:
@@ -230,6 +239,8 @@ class Cosmos3FlowMatching(nn.Module):
         if frozen is None:
             frozen = torch.zeros(Bn, cfg.chunk_size, dtype=torch.bool, device=device)
         live = (~frozen).float()
+        if accel is not None:
+            accel.set_row_mask(self.executed_rows(Bn, device, frozen))
         dt = -1.0 / cfg.num_steps
         if action_prefix is not None:
             x_t = torch.where(frozen[:, :, None], action_prefix.float(), x_t)
@@ -261,6 +272,10 @@ class Cosmos3Policy(PreTrainedPolicy):
         self.model = Cosmos3FlowMatching(config)
         from ..utils import apply_policy_level_freezes
         apply_policy_level_freezes(self.model, self.model.qwen3vl_with_expert, config)
+        self.accel_prefix: int | None = None       # armed by accel.configure_accel
+        self.last_accel_provenance = None
+        self.last_candidate_scores = None
+        self._n_candidates, self._critic = 1, None  # armed by candidates.configure_candidates
         self.reset()
 
     def enable_tensor_parallel(self, tp, free_replicated_weights: bool = False) -> None:
@@ -268,6 +283,8 @@ class Cosmos3Policy(PreTrainedPolicy):
 
     def reset(self) -> None:
         self._action_queue: deque = deque([], maxlen=self.config.n_action_steps)
+        self.last_accel = None
+        self.last_accel_candidates = None
 
     def get_optim_params(self):
         return [p for p in self.parameters() if p.requires_grad]
@@ -318,15 +335,43 @@ class Cosmos3Policy(PreTrainedPolicy):
 
     @torch.no_grad()
     def sample_actions(self, batch, noise=None, n_candidates: int | None = None, **_) -> Tensor:
+        """Un-normalised action chunk ``(B, chunk, real_dim)``; best-of-N and the accel score as in the pi0.5 wrapper
+        (reference ``src/opentau/policies/cosmos3/modeling_cosmos3.py`` ``sample_actions``)."""
+        from ..accel import make_meter, publish
+        from ..candidates import (MEDOID, MedoidCritic, expand_candidates, pick, select_candidate,
+                                  warn_if_no_candidate_scored)
         self.eval()
+        cfg = self.config
         idx, images, masks, lt, lm, state = self._common(batch)
-        if getattr(self, "_use_graphs", False) and state.device.type == "cuda":
+        B, device = lt.shape[0], lt.device
+        n = int(n_candidates or getattr(self, "_n_candidates", None) or 1)
+        critic = getattr(self, "_critic", None)
+        if n > 1 and critic is None:
+            if getattr(cfg, "action_chunk_critic_path", None) not in (None, MEDOID):
+                raise ValueError(f"n_candidates={n} but no action-chunk critic is attached; arm best-of-N through "
+                                 "candidates.configure_candidates")
+            critic = MedoidCritic(max_action_dim=cfg.max_action_dim)
+        sampler_idx = expand_candidates(idx, n)
+        meter = make_meter(self, batch_size=B * n, device=device, dataset_index=sampler_idx)
+        if getattr(self, "_use_graphs", False) and device.type == "cuda" and meter is None and n == 1:
             actions = self._graphed_sample(images, masks, lt, lm, state, noise)
         else:
-            actions = self.model.sample_actions(images, masks, lt, lm, state, noise=noise)
-        feat = self.config.action_feature
+            actions = self.model.sample_actions(images, masks, lt, lm, state, noise=noise, n_candidates=n, accel=meter)
+        if n == 1:
+            publish(self, meter, dataset_index=idx)
+        feat = cfg.action_feature
         real = feat.shape[0] if feat is not None else actions.shape[-1]
-        return self.unnormalize_outputs({"actions": actions[:, :, :real]}, idx)["actions"]
+        actions = self.unnormalize_outputs({"actions": actions[:, :, :real]}, sampler_idx)["actions"]
+        if n == 1:
+            return actions
+        candidates = actions.view(B, n, *actions.shape[1:])
+        scores = critic.score_chunks(batch, candidates, row_mask=self.model.executed_rows(B, device),
+                                     dataset_index=idx)
+        selected = select_candidate(scores)
+        self.last_candidate_scores = scores.detach().to(torch.float32).cpu().tolist()
+        warn_if_no_candidate_scored(self.last_candidate_scores)
+        publish(self, meter, dataset_index=sampler_idx, n_candidates=n, selected=selected)
+        return pick(candidates, selected)
 
     def enable_cuda_graphs(self, flag: bool = True) -> None:
         """Replay the sampler (backbone prefix pass + Euler loop over the expert) from one CUDA graph per input

@@ -513,6 +513,17 @@ class PI05FlowMatching(nn.Module):
         d = delay.to(device).reshape(-1, 1)
         return (torch.arange(c, device=device)[None, :] < d).expand(batch, -1)
 
+    def executed_rows(self, delay: Tensor | int, batch: int, device, frozen: Tensor | None = None) -> Tensor:
+        """``(B, chunk)`` bool: rows that reach the robot (not frozen, inside ``[delay, delay + n_action_steps)``);
+        shared by the accel meter and the candidate critic so that the two score the same rows."""
+        from ..accel import executed_row_mask
+        if frozen is None:
+            frozen = self.frozen_mask(delay, batch, device)
+        if isinstance(delay, Tensor) and delay.ndim and 1 < delay.numel() < batch:
+            delay = delay.repeat_interleave(batch // delay.numel())     # candidates: rows i*n .. i*n+n-1 share a delay
+        return executed_row_mask(prefix_mask=frozen, delay=delay, chunk_size=self.config.chunk_size,
+                                 n_action_steps=self.config.n_action_steps, device=device)
+
     @torch.no_grad()
     def denoise_loop(self, cache: KVCache, prefix_len: Tensor, noise: Tensor, action_prefix: Tensor | None = None,
                      delay: Tensor | int = 0, accel=None, frozen: Tensor | None = None) -> Tensor:
@@ -527,6 +538,8 @@ class PI05FlowMatching(nn.Module):
         if frozen is None:
             frozen = self.frozen_mask(delay, B, device)
         live = (~frozen).to(torch.float32)
+        if accel is not None:
+            accel.set_row_mask(self.executed_rows(delay, B, device, frozen))
         has_prefix = action_prefix is not None
         if has_prefix:               # committed actions enter every step unchanged ...
             x_t = torch.where(frozen[:, :, None], action_prefix.to(x_t.dtype), x_t)
@@ -596,10 +609,18 @@ class PI05Policy(PreTrainedPolicy):
         self.model = self.model_class(config, tokenizer=self.language_tokenizer)
         from ..utils import apply_policy_level_freezes
         apply_policy_level_freezes(self.model, self.model.wrapper, config)
+        # uncertainty proxy and best-of-N are off until accel.configure_accel / candidates.configure_candidates
+        # arm them; the attributes exist so that those switches can tell a wired sampler from an unwired one
+        self.accel_prefix: int | None = None
+        self.last_accel_provenance = None
+        self.last_candidate_scores = None
+        self._n_candidates, self._critic = 1, None
         self.reset()
 
     def reset(self) -> None:
         self._action_queue: deque = deque([], maxlen=self.config.n_action_steps)
+        self.last_accel = None
+        self.last_accel_candidates = None
 
     def get_optim_params(self):
         return [p for p in self.parameters() if p.requires_grad]
@@ -726,7 +747,14 @@ class PI05Policy(PreTrainedPolicy):
     @torch.no_grad()
     def sample_actions(self, batch: dict[str, Any], noise: Tensor | None = None, action_prefix: Tensor | None = None,
                        delay: int | Tensor = 0, n_candidates: int | None = None) -> Tensor:
-        """Returns an un-normalised action chunk ``(B, chunk, real_dim)``."""
+        """Returns an un-normalised action chunk ``(B, chunk, real_dim)``.
+
+        With ``n_candidates > 1`` (armed by ``candidates.configure_candidates`` or passed here) the expert denoises
+        that many noise draws per observation over one prefix pass and the attached critic keeps one, scored in raw
+        units on the executed rows (reference ``src/opentau/policies/pi05/modeling_pi05.py:780-867``).  With
+        ``accel_prefix`` set, ``last_accel`` / ``last_accel_provenance`` are published for the emitted chunk."""
+        from ..accel import make_meter, publish
+        from ..candidates import expand_candidates, pick, select_candidate, warn_if_no_candidate_scored
         self.eval()
         cfg = self.config
         B = batch["state"].shape[0]
@@ -738,22 +766,43 @@ class PI05Policy(PreTrainedPolicy):
         state = nb["state"]
         if state.dim() == 3:
             state = state[:, -1]
-        n = n_candidates or cfg.n_candidates or 1
+        n = int(n_candidates or getattr(self, "_n_candidates", None) or 1)
+        critic = getattr(self, "_critic", None)
+        if n > 1 and critic is None:
+            from ..candidates import MEDOID, MedoidCritic
+            if getattr(cfg, "action_chunk_critic_path", None) in (None, MEDOID):
+                critic = MedoidCritic(max_action_dim=cfg.max_action_dim)   # the parameter-free selector
+            else:
+                raise ValueError(f"n_candidates={n} but no action-chunk critic is attached; arm best-of-N through "
+                                 "candidates.configure_candidates")
+        sampler_idx = expand_candidates(idx, n)
+        meter = make_meter(self, batch_size=B * n, device=device, dataset_index=sampler_idx)
         st = state if cfg.state_type == "continuous" else None
-        if getattr(self, "_use_graphs", False) and device.type == "cuda":
+        # the meter keeps host-side step counts, which a replayed graph would not advance: metered calls run eagerly
+        if getattr(self, "_use_graphs", False) and device.type == "cuda" and meter is None:
             actions = self._graphed_sample(images, img_masks, lang_tokens, lang_masks, action_prefix, delay, noise,
                                            st, n)
         else:
             actions = self.model.sample_actions(images, img_masks, lang_tokens, lang_masks,
                                                 action_prefix=action_prefix, delay=delay, noise=noise, state=st,
-                                                n_candidates=n, prefix_kwargs=self._prefix_kwargs(batch, nb))
-        if n > 1:
-            from ..candidates import select_candidate
-            actions = select_candidate(actions.view(B, n, *actions.shape[1:]))
+                                                n_candidates=n, accel=meter,
+                                                prefix_kwargs=self._prefix_kwargs(batch, nb))
+        if n == 1:
+            # before the un-normalisation: if that raises (non-finite buffers) the score is still there
+            publish(self, meter, dataset_index=idx)
         feat = cfg.action_feature
         real = feat.shape[0] if feat is not None else actions.shape[-1]
-        actions = actions[:, :, :real]
-        return self.unnormalize_outputs({"actions": actions}, idx)["actions"]
+        actions = self.unnormalize_outputs({"actions": actions[:, :, :real]}, sampler_idx)["actions"]
+        if n == 1:
+            return actions
+        candidates = actions.view(B, n, *actions.shape[1:])
+        rows = self.model.executed_rows(delay, B, device)
+        scores = critic.score_chunks(batch, candidates, row_mask=rows, dataset_index=idx)
+        selected = select_candidate(scores)
+        self.last_candidate_scores = scores.detach().to(torch.float32).cpu().tolist()
+        warn_if_no_candidate_scored(self.last_candidate_scores)
+        publish(self, meter, dataset_index=sampler_idx, n_candidates=n, selected=selected)
+        return pick(candidates, selected)
 
     def enable_cuda_graphs(self, flag: bool = True) -> None:
         """Replay the sampler (prefix pass + Euler loop) from a CUDA graph: one launch per action chunk."""

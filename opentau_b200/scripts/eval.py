@@ -114,7 +114,8 @@ def rollout(env, policy, seeds: list[int] | None = None, cfg=None, device=None, 
         out["last_frames"] = last_frames
     if seen_accel is not None:
         out["accel"] = accel
-        out["accel_provenance"] = getattr(policy, "last_accel_provenance", None)
+        prov = getattr(policy, "last_accel_provenance", None)
+        out["accel_provenance"] = prov.to_dict() if hasattr(prov, "to_dict") else prov     # JSON-ready
     return out
 
 
@@ -368,9 +369,14 @@ def consolidate_eval_info(per_rank: list[dict[str, Any]]) -> dict[str, Any]:
                 "pc_success": float(np.mean([e["success"] for e in eps]) * 100), "n": len(eps)}
 
     every = [e for eps in per_group.values() for e in eps]
-    return {"per_task": {k: v["aggregated"] for k, v in merged.items()},
+    info = {"per_task": {k: v["aggregated"] for k, v in merged.items()},
             "per_group": {g: agg(eps) for g, eps in per_group.items()}, "aggregated": agg(every),
             "per_episode": {k: v["per_episode"] for k, v in merged.items()}}
+    # per-task accel streams (index-aligned with per_episode) and their provenance: what the calibration tool reads
+    accel = {k: v["accel"] for k, v in merged.items() if v.get("accel")}
+    if accel:
+        info["accel"] = accel
+    return info
 
 
 def eval_policy_on_config(policy, cfg: TrainPipelineConfig, device, rank: int = 0, world: int = 1,
@@ -419,6 +425,13 @@ def eval_main(cfg: TrainPipelineConfig):
     if device.type == "cuda":
         policy.to(torch.bfloat16)
     policy.eval()
+    from ..policies.accel import configure_accel
+    from ..policies.candidates import configure_candidates
+    if configure_accel(policy, cfg) is not None:               # cfg.policy.accel_prefix or $OPENTAU_ACCEL_PREFIX
+        logging.info("accel streams are recorded per episode (prefix %d)", policy.accel_prefix)
+    if getattr(cfg.policy, "n_candidates", 1) > 1 and hasattr(policy, "_n_candidates"):
+        configure_candidates(policy, cfg.policy.n_candidates, getattr(cfg.policy, "action_chunk_critic_path", None)
+                             or "medoid")
     out = Path(cfg.output_dir or "outputs/eval")
     info = eval_policy_on_config(policy, cfg, device, rank, world, videos_dir=out / "videos")
     if rank == 0:

@@ -86,6 +86,12 @@ class RobotPolicyServicer(pb_grpc.RobotPolicyServiceServicer):
         self.infer = InferenceThread()
         self.planner = planner
         self.policy = policy if policy is not None else self.infer.submit(self._load_policy).result()
+        # before the warm-up requests, so that a checkpoint that cannot support the score fails at start-up
+        from ...policies.accel import configure_accel
+        from ...policies.candidates import configure_candidates
+        self.accel_prefix = configure_accel(self.policy, cfg)
+        if getattr(cfg.policy, "n_candidates", 1) > 1 and hasattr(self.policy, "_n_candidates"):
+            configure_candidates(self.policy, cfg.policy.n_candidates)
         self.requests = 0
         self._lock = threading.Lock()
         for _ in range(cfg.server.warmup_requests if policy is None else 0):

@@ -23,6 +23,8 @@ def inference_main(cfg: TrainPipelineConfig, n: int = 10):
     if device.type == "cuda":
         policy.to(torch.bfloat16)
     policy.eval()
+    from ..policies.accel import configure_accel
+    accel_prefix = configure_accel(policy, cfg)          # cfg.policy.accel_prefix or $OPENTAU_ACCEL_PREFIX
     obs = create_dummy_observation(cfg, device)
     times = []
     with torch.inference_mode():
@@ -34,7 +36,8 @@ def inference_main(cfg: TrainPipelineConfig, n: int = 10):
             if device.type == "cuda":
                 torch.cuda.synchronize()
             times.append((time.perf_counter() - t0) * 1e3)
-            logging.info("call %d: %.2f ms, actions %s", i, times[-1], tuple(actions.shape))
+            logging.info("call %d: %.2f ms, actions %s%s", i, times[-1], tuple(actions.shape),
+                         f", accel {policy.last_accel}" if accel_prefix else "")
     logging.info("first %.2f ms; mean of the rest %.2f ms", times[0], sum(times[1:]) / max(1, len(times) - 1))
     return times
 

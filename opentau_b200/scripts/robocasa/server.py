@@ -114,7 +114,8 @@ class OpenTauRoboCasaPolicy:
         if self.device.type == "cuda":
             self.policy.to(torch.bfloat16)
         self.policy.eval()
-        self.accel_prefix = configure_accel(self.policy, accel_prefix) if accel_prefix else None
+        # precedence: this entry point's flag, then cfg.policy.accel_prefix, then $OPENTAU_ACCEL_PREFIX
+        self.accel_prefix = configure_accel(self.policy, cfg, override=accel_prefix)
         self.last_accel: list[float] | None = None
 
     def infer_batch(self, items, action_dim: int) -> list[np.ndarray]:

@@ -74,7 +74,7 @@ class CusumCalibration:
     def from_dict(cls, payload: dict) -> "CusumCalibration":
         p = dict(payload)
         prov = p.pop("provenance", None)
-        return cls(**p, provenance=AccelProvenance(**prov) if prov else None)
+        return cls(**p, provenance=AccelProvenance.from_dict(prov) if prov else None)
 
     def save(self, path: str | Path) -> Path:
         path = Path(path)

@@ -40,3 +40,40 @@ def test_detector_flags_drifting_episodes_and_keeps_false_alarms_near_alpha(tmp_
     (tmp_path / "eps.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
     out = calibrate_main(["--episodes", str(tmp_path / "eps.jsonl"), "--out", str(tmp_path), "--alpha", "0.1"])
     assert out["report"]["true_positive_rate"] == 1.0
+
+
+def test_calibration_from_eval_info_pooled_and_per_task(tmp_path):
+    """The evaluator's own output feeds the tool: per-task streams index-aligned with per-episode outcomes, one
+    provenance for the pool (per-sample fields cleared), per-task files on request, and a clear refusal when no
+    group has enough successful episodes for the requested rate."""
+    rng = np.random.default_rng(1)
+    prov = {"policy_type": "pi05", "num_steps": 10, "prefix": 9, "chunk_size": 50, "n_action_steps": 50, "max_delay": 0,
+            "action_norm_mode": "MEAN_STD", "has_delta_action_map": False, "velocity_dtype": "bfloat16",
+            "num_scored_dims": [7], "dataset_index": [0], "n_candidates": 1}
+
+    def task(n_ok, n_bad):
+        streams = [list(rng.normal(1.0, 0.1, size=30)) for _ in range(n_ok)]
+        streams += [list(rng.normal(1.0, 0.1, size=15)) + list(rng.normal(1.6, 0.1, size=15)) for _ in range(n_bad)]
+        eps = [{"episode_ix": i, "success": i < n_ok} for i in range(n_ok + n_bad)]
+        return streams, eps
+    s_a, e_a = task(30, 6)
+    s_b, e_b = task(12, 3)
+    info = {"per_episode": {"g/0": e_a, "g/1": e_b, "g/2": [{"success": True}]},
+            "accel": {"g/0": {"streams": s_a, "provenance": prov},
+                      "g/1": {"streams": s_b, "provenance": {**prov, "dataset_index": [1], "num_scored_dims": [6]}}}}
+    (tmp_path / "eval_info.json").write_text(json.dumps(info))
+    out = calibrate_main([str(tmp_path), "--out", str(tmp_path / "cal"), "--alpha", "0.1"])
+    cal = out["calibration"]
+    assert set(out["summary"]) == {"pooled"} and out["summary"]["pooled"]["num_successful"] == 42
+    assert out["report"]["true_positive_rate"] == 1.0 and cal.provenance.prefix == 9
+    assert cal.provenance.dataset_index == () and cal.provenance.num_scored_dims == ()
+    assert CusumCalibration.load(tmp_path / "cal" / "accel_calibration__pooled.json") == cal
+    per = calibrate_main([str(tmp_path / "eval_info.json"), "--out", str(tmp_path / "per"), "--per-task", "--holdout", "0.2"])
+    assert set(per["summary"]) == {"g__0", "g__1"} and per["summary"]["g__0"]["held_out"] is True
+    assert (tmp_path / "per" / "accel_calibration_summary.json").exists()
+    with pytest.raises(SystemExit, match="No calibration could be fitted"):
+        calibrate_main([str(tmp_path), "--out", str(tmp_path / "x"), "--alpha", "0.01"])
+    info["accel"]["g/1"]["provenance"] = {**prov, "prefix": 4}
+    (tmp_path / "eval_info.json").write_text(json.dumps(info))
+    mixed = calibrate_main([str(tmp_path), "--out", str(tmp_path / "m")])
+    assert mixed["calibration"].provenance is None            # disagreeing tasks leave the pool unlabelled
