@@ -315,8 +315,9 @@ def run_infer(args, device, rank, world, local_rank, use_cuda) -> int:
         enable_tp(args, policy, device, world)
     else:
         policy, batch = BUILDERS[args.model](3, prompt_len, device, tiny=args.tiny, num_steps=num_steps)
-    # graph replay would repeat the flag epochs of the tensor-parallel kernels: those passes run eagerly
-    use_graphs = use_cuda and args.impl == "ours" and not (args.model == "cosmos3" and args.tp > 1)
+    # with a tensor-parallel backbone the prefix pass runs eagerly (its kernels carry a per-call epoch and it contains
+    # collectives) and the expert's Euler loop behind it is replayed from a graph
+    use_graphs = use_cuda and args.impl == "ours"
     if use_graphs:
         policy.enable_cuda_graphs(True)
     host = {k: (v.cpu().pin_memory() if use_cuda else v.cpu()) for k, v in batch.items() if hasattr(v, "cpu")}

@@ -13,13 +13,105 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, ClassVar
 
-from ..constants import CONFIG_NAME
+from ..constants import CONFIG_NAME, TRAIN_CONFIG_NAME
 from .codec import ChoiceRegistry, decode, encode
 from .types import FeatureType, NormalizationMode, PolicyFeature
 
+# Version of the behavioural conventions a checkpoint's weights were trained under (not the package version):
+#   0  legacy: a zero-range MIN_MAX / QUANTILE band maps to -1.0, normalisation epsilon 1e-8
+#   1  a zero-range band maps to 0.0 and the epsilon is 1e-6
+# A config without the field runs as CURRENT in a fresh run and is resolved to 0 when weights that predate the field
+# are loaded (policies/loading.py: resolve_checkpoint_provenance).
 CURRENT_CONFIG_VERSION = 1
 OPENPI_EPS = 1e-6   # normalization epsilon for config_version >= 1
 LEGACY_EPS = 1e-8   # epsilon for checkpoints without a version
+
+#: whole-pipeline configs that a checkpoint folder may hold instead of (or beside) ``config.json``; their ``policy``
+#: object is a valid policy config, so both config loaders fall back to them
+HF_CONFIG_NAME = "hf_config.json"
+
+DEPRECATED_LATENCY_FIELDS = ("cloud_vlm_latency_mean", "cloud_vlm_latency_std", "cloud_vlm_latency_lower",
+                             "cloud_vlm_latency_upper", "action_decoder_latency_mean", "action_decoder_latency_std",
+                             "action_decoder_latency_lower", "action_decoder_latency_upper")
+#: removed from the dataclass: dropped from incoming JSON (old configs still load) and from outgoing JSON
+REMOVED_POLICY_FIELDS = ("init_strategy",)
+STRIPPED_FIELDS = DEPRECATED_LATENCY_FIELDS + REMOVED_POLICY_FIELDS
+
+
+def strip_keys(data: dict, keys: tuple[str, ...]) -> bool:
+    """Drops ``keys`` at the top level and under a ``"policy"`` object; True if anything changed."""
+    changed = False
+    for scope in (data, data.get("policy") if isinstance(data.get("policy"), dict) else None):
+        if scope is None:
+            continue
+        for k in keys:
+            if k in scope:
+                del scope[k]
+                changed = True
+    return changed
+
+
+def find_present_keys(data: dict, keys: tuple[str, ...]) -> list[str]:
+    found = [k for k in keys if k in data]
+    if isinstance(data.get("policy"), dict):
+        found += [f"policy.{k}" for k in keys if k in data["policy"]]
+    return found
+
+
+def strip_deprecated_fields_from_json(path: str | Path) -> None:
+    """Rewrites a config file WE own (one just written into a save directory) without the stripped fields.  Never
+    for incoming files: a hub cache path is a link into a content-addressed store and a rewrite would corrupt it;
+    incoming configs are stripped in memory (:func:`stripped_copy`)."""
+    data = json.loads(Path(path).read_text())
+    if strip_keys(data, STRIPPED_FIELDS):
+        Path(path).write_text(json.dumps(data, indent=4))
+
+
+def load_resolved_config_dict(source_path: str | Path) -> dict:
+    """The config as one dict with ``$ref`` includes resolved; a non-object root is an error for every loader."""
+    from .refs import load_json_with_refs
+    data = load_json_with_refs(source_path)
+    if not isinstance(data, dict):
+        raise TypeError(f"Top-level config at {source_path} must be a JSON object after $ref resolution, "
+                        f"got {type(data).__name__}")
+    return data
+
+
+def stripped_copy(data: dict) -> dict:
+    """``data`` without the stripped fields; the caller's dict is left as it was (two-level copy: the keys only
+    ever live at the top level or under ``policy``)."""
+    out = dict(data)
+    if isinstance(out.get("policy"), dict):
+        out["policy"] = dict(out["policy"])
+    strip_keys(out, STRIPPED_FIELDS)
+    return out
+
+
+def warn_deprecated_latency_fields_from_dict(data: dict, config_path: str | Path) -> None:
+    import warnings
+    found = find_present_keys(data, DEPRECATED_LATENCY_FIELDS)
+    if found:
+        warnings.warn(f"Config '{config_path}' contains deprecated latency fields that are no longer used and will "
+                      f"be ignored: {', '.join(found)}. Consider re-saving the config to remove them.",
+                      DeprecationWarning, stacklevel=4)
+
+
+def warn_removed_policy_fields_from_dict(data: dict, config_path: str | Path) -> None:
+    import warnings
+    found = find_present_keys(data, REMOVED_POLICY_FIELDS)
+    if found:
+        warnings.warn(f"Config '{config_path}' contains fields that have been removed and will be ignored: "
+                      f"{', '.join(found)}. Re-save the config to drop them.", DeprecationWarning, stacklevel=4)
+
+
+def warn_deprecated_latency_fields(config_path: str | Path) -> None:
+    """Warns when a config file (``$ref`` includes followed) still carries latency fields."""
+    warn_deprecated_latency_fields_from_dict(load_resolved_config_dict(config_path), config_path)
+
+
+def warn_removed_policy_fields(config_path: str | Path) -> None:
+    """Warns when a config file carries a removed field: the user's explicit choice is being dropped."""
+    warn_removed_policy_fields_from_dict(load_resolved_config_dict(config_path), config_path)
 
 
 @dataclass
@@ -71,14 +163,19 @@ class PreTrainedConfig(ChoiceRegistry, abc.ABC):
     def type(self) -> str:
         return self.get_choice_name()
 
+    def resolved_config_version(self) -> int:
+        """The version behaviour reads through: an unresolved ``None`` is a fresh run and runs as CURRENT.  The
+        stored field stays ``None`` until a save or the checkpoint-provenance resolution makes it concrete."""
+        return self.config_version if self.config_version is not None else CURRENT_CONFIG_VERSION
+
     @property
     def zero_range_centers_on_zero(self) -> bool:
         """New-format checkpoints map a zero-range dim to 0; legacy ones to -1."""
-        return (self.config_version or 0) >= 1
+        return self.resolved_config_version() >= 1
 
     @property
     def normalization_epsilon(self) -> float:
-        return OPENPI_EPS if (self.config_version or 0) >= 1 else LEGACY_EPS
+        return OPENPI_EPS if self.resolved_config_version() >= 1 else LEGACY_EPS
 
     @property
     def robot_state_feature(self) -> PolicyFeature | None:
@@ -188,11 +285,15 @@ class PreTrainedConfig(ChoiceRegistry, abc.ABC):
         return encode(self)
 
     def _save_pretrained(self, save_directory: str | Path) -> None:
+        """Writes ``config.json`` with the ``type`` discriminator, a concrete ``config_version`` (a saved ``null``
+        would later be read as "no tag" = legacy) and the writing package's version; stripped fields are left out."""
         from .. import __version__
         d = self.to_dict()
-        if d.get("config_version") is None:
-            d["config_version"] = CURRENT_CONFIG_VERSION
-        d["opentau_version"] = __version__
+        d["config_version"] = self.resolved_config_version()
+        d["opentau_version"] = __version__ if __version__ != "unknown" else (self.opentau_version or __version__)
+        strip_keys(d, REMOVED_POLICY_FIELDS)
+        for k in DEPRECATED_LATENCY_FIELDS:          # still dataclass fields (old configs set them); never written
+            d.pop(k, None)
         Path(save_directory).mkdir(parents=True, exist_ok=True)
         with open(Path(save_directory) / CONFIG_NAME, "w") as f:
             json.dump(d, f, indent=4)
@@ -205,15 +306,43 @@ class PreTrainedConfig(ChoiceRegistry, abc.ABC):
 
     @classmethod
     def from_pretrained(cls, pretrained_name_or_path: str | Path, *, cli_overrides: list[str] | None = None,
-                        **_unused) -> "PreTrainedConfig":
-        """Loads ``config.json`` from a local directory (``repo@rev`` hub ids need network and raise)."""
+                        revision: str | None = None, **_unused) -> "PreTrainedConfig":
+        """Loads a policy config from a directory, a file, or a ``repo@rev`` id in the local hub cache.
+
+        Candidates in order: ``config.json``, then the whole-pipeline ``hf_config.json`` / ``train_config.json``, whose
+        ``policy`` object is the policy config (published checkpoints historically carried ``hf_config.json`` alone).
+        ``$ref`` includes are resolved once; deprecated and removed fields are reported with a ``DeprecationWarning``
+        and dropped in memory -- the source file is never rewritten.  Reference:
+        ``src/opentau/configs/policies.py:849-985``."""
+        from ..utils.hub import resolve_local_or_hub, split_repo_revision
         from .codec import apply_overrides
-        from ..utils.hub import resolve_local_or_hub
-        path = resolve_local_or_hub(str(pretrained_name_or_path), CONFIG_NAME)
-        with open(path) as f:
-            raw = json.load(f)
+        name = str(pretrained_name_or_path)
+        if revision is not None and not os.path.exists(name) and "@" not in name:
+            name = f"{name}@{revision}"
+        root = resolve_local_or_hub(name)
+        if root.is_file():
+            config_file, nested = root, root.name != CONFIG_NAME and root.name in (HF_CONFIG_NAME, TRAIN_CONFIG_NAME)
+        else:
+            for filename in (CONFIG_NAME, HF_CONFIG_NAME, TRAIN_CONFIG_NAME):
+                if (root / filename).is_file():
+                    config_file, nested = root / filename, filename != CONFIG_NAME
+                    break
+            else:
+                repo, rev = split_repo_revision(name)
+                raise FileNotFoundError(f"None of {CONFIG_NAME}, {HF_CONFIG_NAME}, {TRAIN_CONFIG_NAME} found in "
+                                        f"{root.resolve()}" + (f" (revision {rev!r} of {repo!r})" if rev else ""))
+        raw = load_resolved_config_dict(config_file)
+        if nested:
+            raw = raw.get("policy")
+            if not isinstance(raw, dict):
+                raise FileNotFoundError(f"{config_file} carries no 'policy' object, so it cannot be read as a policy "
+                                        f"config for {name}.")
+        warn_deprecated_latency_fields_from_dict(raw, config_file)
+        warn_removed_policy_fields_from_dict(raw, config_file)
+        raw = dict(raw)
+        strip_keys(raw, REMOVED_POLICY_FIELDS)
         if "config_version" not in raw:
-            raw["config_version"] = None  # legacy provenance: keep eps 1e-8 / centre -1 behaviour
+            raw["config_version"] = None   # no tag: resolved against the weights when they are loaded
         if cli_overrides:
             raw = apply_overrides(raw, list(cli_overrides))
         return decode(PreTrainedConfig, raw)

@@ -234,6 +234,15 @@ class Cosmos3FlowMatching(nn.Module):
             cache = cache.expand_batch(n_candidates)
             ppos = ppos.repeat_interleave(n_candidates, 1)
             state = state.repeat_interleave(n_candidates, 0)
+        return self.denoise_loop(cache, ppos, state, noise, action_prefix, frozen, accel)
+
+    @torch.no_grad()
+    def denoise_loop(self, cache, ppos, state, noise, action_prefix=None, frozen=None, accel=None) -> Tensor:
+        """``num_steps`` Euler steps of the expert over a finished prefix cache: fixed trip count, device-only
+        operations and no collective, so the loop can be replayed from a CUDA graph also when the backbone that
+        produced the cache runs tensor parallel."""
+        cfg = self.config
+        device = noise.device
         x_t = noise.float().clone()
         Bn = x_t.shape[0]
         if frozen is None:
@@ -379,12 +388,28 @@ class Cosmos3Policy(PreTrainedPolicy):
         (``src/opentau/scripts/benchmark_inference.py:249-259``)."""
         self._use_graphs = bool(flag)
         self._graph_runner = None
+        self._loop_runner = None
 
     def _graphed_sample(self, images, masks, lt, lm, state, noise):
+        from ...models.dual_stream import KVCache
         from ...runtime.graphs import CudaGraphRunner
         cfg = self.config
         if noise is None:
             noise = self.model.sample_noise((lt.shape[0], cfg.chunk_size, cfg.max_action_dim), lt.device)
+        if getattr(self.model.qwen3vl_with_expert, "tp_backbone", None) is not None:
+            # tensor-parallel backbone: its kernels carry a per-call epoch in their arguments and its pass contains
+            # library collectives, so the prefix pass runs eagerly; the expert loop behind it touches no peer and
+            # is replayed from a graph whose inputs are the cache tensors
+            cache, ppos = self.model.qwen3vl_with_expert.run_prefix(images, masks, lt, lm)
+            length = cache.length
+            if getattr(self, "_loop_runner", None) is None:
+                def loop(k, v, valid, ppos, state, noise):
+                    return self.model.denoise_loop(KVCache(k, v, valid, length), ppos, state, noise)
+                self._loop_runner, self._loop_length = CudaGraphRunner(loop), length
+            if length != self._loop_length:
+                raise RuntimeError(f"prefix length changed from {self._loop_length} to {length}: the captured expert "
+                                   "loop is for one prompt / camera geometry; call enable_cuda_graphs(True) again")
+            return self._loop_runner(cache.k, cache.v, cache.valid, ppos, state, noise.float()).clone()
         if getattr(self, "_graph_runner", None) is None:
             def fn(images, masks, lt, lm, state, noise):
                 return self.model.sample_actions(list(images), list(masks), lt, lm, state, noise=noise)

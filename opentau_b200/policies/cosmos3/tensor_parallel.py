@@ -72,10 +72,17 @@ class TPBackbone:
         k_all, v_all = torch.stack(ks), torch.stack(vs)                            # (L', B, S, hk_local, D)
         k_own, v_own = self._heads_for_own_samples(k_all, Bl), self._heads_for_own_samples(v_all, Bl)
         L_total = len(self.layers)
-        if col is not None:                                                        # cache indexed by backbone layer id
-            k_full = k_own.new_zeros(L_total, *k_own.shape[1:])
-            v_full = v_own.new_zeros(L_total, *v_own.shape[1:])
-            k_full[col], v_full[col] = k_own[0], v_own[0]
+        # spare token slots behind the prefix, as the unsharded pass leaves them: the expert appends its keys / values
+        # in place instead of concatenating in every layer of every denoise step
+        room = 0 if torch.is_grad_enabled() else m.config.chunk_size + 8
+        if col is not None or room:                                                # cache indexed by backbone layer id
+            _, Bo, So, Ho, Do = k_own.shape
+            k_full = k_own.new_zeros(L_total, Bo, So + room, Ho, Do)
+            v_full = v_own.new_zeros(L_total, Bo, So + room, Ho, Do)
+            if col is not None:
+                k_full[col, :, :So], v_full[col, :, :So] = k_own[0], v_own[0]
+            else:
+                k_full[:, :, :So], v_full[:, :, :So] = k_own, v_own
             k_own, v_own = k_full, v_full
         return KVCache(k_own, v_own, pad, S), pos
 

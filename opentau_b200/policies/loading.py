@@ -34,7 +34,7 @@ from torch import Tensor, nn
 
 from ..constants import CONFIG_NAME, SAFETENSORS_SINGLE_FILE, TRAIN_CONFIG_NAME
 
-HF_CONFIG_NAME = "hf_config.json"
+from ..configs.policies import HF_CONFIG_NAME  # noqa: E402
 
 
 class CheckpointWeightsNotFoundError(FileNotFoundError):

@@ -121,7 +121,9 @@ def test_accelerate_yaml_mapping(tmp_path):
 
 def test_policy_config_save_load_and_version_semantics(tmp_path):
     cfg = TrainPipelineConfig.from_dict(_base_cfg()).policy
-    assert cfg.normalization_epsilon == 1e-8 and not cfg.zero_range_centers_on_zero   # no version = legacy
+    # no version on a fresh config = the current conventions (what a save then stamps, so a reload behaves the same);
+    # legacy behaviour needs the explicit 0 that loading pre-version weights resolves to
+    assert cfg.config_version is None and cfg.normalization_epsilon == 1e-6 and cfg.zero_range_centers_on_zero
     cfg._save_pretrained(tmp_path)
     saved = json.loads((tmp_path / "config.json").read_text())
     assert saved["config_version"] == 1 and saved["type"] == "pi05"
@@ -200,3 +202,55 @@ def test_pipeline_config_location_fallbacks_and_running_best_resolution(tmp_path
         bad.validate()
     with pytest.raises(ValueError, match="must be one of"):
         TrainPipelineConfig.from_dict({**raw, "running_best_metric": "accuracy"}).validate()
+
+
+def test_policy_config_loads_from_pipeline_files_strips_retired_fields_and_warns(tmp_path):
+    """``PreTrainedConfig.from_pretrained``: falls back from config.json to the ``policy`` object of hf_config.json /
+    train_config.json, follows ``$ref`` includes, reports deprecated / removed fields and drops them without
+    rewriting the source, and a save never writes them back.  A fresh config behaves as the current version."""
+    import json
+    import warnings
+
+    import pytest
+
+    from helpers import tiny_pi05_config
+    from opentau_b200.configs import policies as P
+    cfg = tiny_pi05_config()
+    assert cfg.config_version is None and cfg.resolved_config_version() == P.CURRENT_CONFIG_VERSION
+    assert cfg.zero_range_centers_on_zero and cfg.normalization_epsilon == P.OPENPI_EPS
+    cfg.config_version = 0
+    assert not cfg.zero_range_centers_on_zero and cfg.normalization_epsilon == P.LEGACY_EPS
+    cfg.config_version = None
+    cfg._save_pretrained(tmp_path / "a")
+    saved = json.loads((tmp_path / "a" / "config.json").read_text())
+    assert saved["config_version"] == 1 and not set(saved) & set(P.STRIPPED_FIELDS)
+    # the pipeline files: policy nested under "policy", one part of it behind a $ref
+    b = tmp_path / "b"
+    b.mkdir()
+    feats = {"input_features": saved.pop("input_features")}
+    (b / "features.json").write_text(json.dumps(feats))
+    policy = {**saved, "$ref": "features.json", "init_strategy": "expert_only", "cloud_vlm_latency_mean": 0.2}
+    (b / "hf_config.json").write_text(json.dumps({"policy": policy, "steps": 10}))
+    before = (b / "hf_config.json").read_text()
+    with pytest.warns(DeprecationWarning) as rec:
+        loaded = P.PreTrainedConfig.from_pretrained(b)
+    text = " | ".join(str(w.message) for w in rec)
+    assert "cloud_vlm_latency_mean" in text and "init_strategy" in text
+    assert loaded.type == "pi05" and set(loaded.input_features) == set(cfg.input_features)
+    assert (b / "hf_config.json").read_text() == before                  # the source is never rewritten
+    (b / "config.json").write_text(json.dumps({**saved, **feats, "chunk_size": 7, "n_action_steps": 7}))
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        assert P.PreTrainedConfig.from_pretrained(b).chunk_size == 7     # config.json wins over the pipeline files
+    c = tmp_path / "c"
+    c.mkdir()
+    (c / "train_config.json").write_text(json.dumps({"steps": 10}))
+    with pytest.raises(FileNotFoundError, match="no 'policy' object"):
+        P.PreTrainedConfig.from_pretrained(c)
+    (tmp_path / "d").mkdir()
+    with pytest.raises(FileNotFoundError, match="None of config.json, hf_config.json, train_config.json"):
+        P.PreTrainedConfig.from_pretrained(tmp_path / "d")
+    # files we own are cleaned in place
+    (tmp_path / "own.json").write_text(json.dumps({"policy": {"init_strategy": "x", "a": 1}, "action_decoder_latency_std": 1}))
+    P.strip_deprecated_fields_from_json(tmp_path / "own.json")
+    assert json.loads((tmp_path / "own.json").read_text()) == {"policy": {"a": 1}}

@@ -48,7 +48,7 @@ def test_attach_segment_and_visualize(tmp_path):
 
 
 def test_convert_v20_to_v21_and_token_scan(tmp_path):
-    from opentau_b200.datasets.v2.convert_dataset_v20_to_v21 import convert
+    from opentau_b200.datasets.v21.convert_dataset_v20_to_v21 import convert
     from opentau_b200.scripts.compute_max_token_length import scan
     from opentau_b200.utils.tokenizer import DctActionTokenizer, load_text_tokenizer
     _record(tmp_path / "toy", episodes=(6, 6))
@@ -123,7 +123,7 @@ def test_convert_v16_to_v20_then_v21(tmp_path):
 
     from opentau_b200.datasets.utils import load_jsonlines
     from opentau_b200.datasets.v2.convert_dataset_v1_to_v2 import batch_convert, convert_dataset
-    from opentau_b200.datasets.v2.convert_dataset_v20_to_v21 import convert
+    from opentau_b200.datasets.v21.convert_dataset_v20_to_v21 import convert
 
     st = _write_v16(tmp_path / "v1")
     info = convert_dataset(tmp_path / "v1", tmp_path / "v2", single_task="stack the cubes", robot_type="so101",
@@ -161,7 +161,7 @@ def test_convert_v16_to_v20_then_v21(tmp_path):
 def test_convert_v20_to_v21_workers_check_metadata_fix_and_batch(tmp_path):
     from opentau_b200.datasets.compute_stats import aggregate_stats
     from opentau_b200.datasets.utils import load_episodes_stats, serialize_stats
-    from opentau_b200.datasets.v2.convert_dataset_v20_to_v21 import batch_convert, convert, fix_language_instruction
+    from opentau_b200.datasets.v21.convert_dataset_v20_to_v21 import batch_convert, convert, fix_language_instruction
     import pytest
 
     def back_to_v20(root, wrong_stats=False):

@@ -369,10 +369,20 @@ def _tp_backbone_worker(rank, world, port, ret):
                 errs.append(float((cache.v[li][:, :n].float() - full.v[li, sl, :n].float()).abs().max()))
                 scale = max(scale, float(full.k[li].float().abs().max()), float(full.v[li].float().abs().max()))
             assert torch.equal(pos, pos_full[:, sl])
+        # sampling through the sharded backbone: eager, then with the expert loop replayed from a graph (captured on
+        # the first call, replayed on the second); same noise, so the three chunks agree
+        w.tp_backbone = tpb
+        mine = {k: (v[sl] if isinstance(v, (torch.Tensor, list)) else v) for k, v in b.items()}
+        noise = torch.randn(2, 10, 32, device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+        eager = pol.sample_actions(mine, noise=noise).float()
+        pol.enable_cuda_graphs(True)
+        first = pol.sample_actions(mine, noise=noise).float()
+        again = pol.sample_actions(mine, noise=noise).float()
+        graph_err = max(float((first - eager).abs().max()), float((again - eager).abs().max()))
         torch.cuda.synchronize()
         cuda_ops.check_status()
         gathered = [None] * world
-        dist.all_gather_object(gathered, (max(errs), scale))
+        dist.all_gather_object(gathered, (max(errs), scale, graph_err))
         if rank == 0:
             ret["tpb"] = gathered
         dist.barrier()
@@ -388,5 +398,6 @@ def test_cosmos3_tensor_parallel_backbone_matches_the_replicated_backbone_on_gpu
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_tp_backbone_worker, args=(2, free_port(), ret), nprocs=2, join=True)
-    for err, scale in ret["tpb"]:
+    for err, scale, graph_err in ret["tpb"]:
         assert err < 0.04 * scale, ret["tpb"]
+        assert graph_err < 0.05, ret["tpb"]
