@@ -8,9 +8,9 @@ two pointwise convolutions (with a per-sample GroupNorm) mix similarities and th
 zero-initialised projection turns the result into a residual on the vision features:
 ``v'(t) = v(t) + S(STSS(v(t)))``.
 
-The local window is gathered directly (``unfold`` of the zero-padded target frame) instead of forming the global
-``(HW x HW)`` correlation and slicing diagonals out of it: ``O(HW k^2 C)`` work and memory instead of
-``O((HW)^2 C)``.  All convolutions of the default ``lite`` integration are 1x1x1, i.e. per-token linear maps, and run
+The local window is read directly instead of forming the global ``(HW x HW)`` correlation and slicing diagonals out of
+it: ``O(HW k^2 C)`` work instead of ``O((HW)^2 C)``; on the GPU one kernel each way computes the similarities from
+the token-major features without materialising the window (``ops/csrc/stss_corr.cu``).  All convolutions of the default ``lite`` integration are 1x1x1, i.e. per-token linear maps, and run
 as GEMMs; parameter names and shapes match the reference (``stss_encoders.N.stss_extraction.conv0.0.weight``
 ``(C, k*k, 1, 1, 1)`` ...) so checkpoints interchange.
 """
@@ -60,23 +60,25 @@ class STSSTransformation(nn.Module):
         self.window, self.corr_func = tuple(window), corr_func
 
     def forward(self, x: Tensor, t: int, h: int, w: int) -> Tensor:
-        """``x (B*t*h*w, C)`` -> ``(B, t, h, w, L, k, k)`` similarities."""
+        """``x (B*t*h*w, C)`` -> ``(B, t, h, w, L, k, k)`` similarities.  The features stay token-major: the window
+        kernel (``ops/stss.py``) reads neighbour vectors in place instead of unfolding ``L * k * k`` copies."""
+        from ..ops.stss import local_window_correlation
         L, k, _ = self.window
         C = x.shape[-1]
-        v = x.view(-1, t, h, w, C).permute(0, 1, 4, 2, 3)                      # (B, t, C, h, w)
+        v = x.view(-1, t, h * w, C)
         B = v.shape[0]
-        if L > 1:
-            pad = L // 2
-            idx = (torch.arange(t, device=x.device)[:, None] + torch.arange(-pad, pad + 1, device=x.device)[None, :]
-                   ).clamp(0, t - 1)                                          # (t, L): clamped neighbour frames
-            tgt = v[:, idx]                                                   # (B, t, L, C, h, w)
-            src = v[:, :, None].expand(B, t, L, C, h, w)
-        else:
-            idx = (torch.arange(t, device=x.device) - 1).clamp(min=0)[:, None]
-            tgt = v[:, idx]
-            src = v[:, :, None]
-        corr = local_correlation(src.reshape(-1, C, h, w), tgt.reshape(-1, C, h, w), k, self.corr_func)
-        return corr.view(B, t, max(L, 1), h, w, k, k).permute(0, 1, 3, 4, 2, 5, 6)
+        if self.corr_func == "cosine":
+            v = F.normalize(v, p=2, dim=-1)
+        elif self.corr_func not in ("dotproduct", "dotproduct_softmax"):
+            raise ValueError(f"unknown corr_func {self.corr_func!r}")
+        corr = local_window_correlation(v, t, h, w, L, k)                          # (B, t, hw, L, k*k)
+        if self.corr_func != "cosine":
+            corr = corr * C ** -0.5
+        if self.corr_func == "dotproduct_softmax":
+            ones = F.unfold(torch.ones(1, 1, h, w, device=x.device, dtype=corr.dtype), kernel_size=k, padding=k // 2)
+            inside = ones.view(k * k, h * w).t() > 0                              # (hw, k*k)
+            corr = corr.masked_fill(~inside[None, None, :, None, :], float("-inf")).softmax(dim=-1)
+        return corr.view(B, t, h, w, max(L, 1), k, k)
 
 
 class _Pointwise(nn.Sequential):

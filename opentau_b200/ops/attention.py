@@ -1,8 +1,8 @@
 """Block-causal attention launchers for CUDA tensors.
 
-The tcgen05 kernel (``csrc/attention_tcgen05.cu``) serves the forward pass when the geometry fits
-(head_dim a multiple of 16 up to 256); the backward and the remaining shapes use a dense
-PyTorch body evaluated in batch chunks.
+bf16 tensors go to the tcgen05 kernels (``csrc/attention_tcgen05.cu``, ``csrc/attention_bwd_tcgen05.cu``), fp32
+tensors to the exact CUDA-core kernels (``csrc/attention_f32.cu``); geometries neither takes (and
+``OPENTAU_B200_DENSE_ATTN=1``) use a dense PyTorch body evaluated in batch chunks.
 """
 
 from __future__ import annotations
@@ -69,6 +69,8 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk, k_blk, q_valid, k_valid, sc
     from . import attention_native
     if attention_native.supported(q, k, v):
         return attention_native.attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
+    if attention_native.supported_f32(q, k, v):
+        return attention_native.attn_f32_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
     return dense_attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
 
 
@@ -76,4 +78,6 @@ def attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale):
     from . import attention_native
     if attention_native.supported_bwd(q, k, v):
         return attention_native.attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)
+    if attention_native.supported_f32(q, k, v):
+        return attention_native.attn_f32_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)
     return dense_attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)

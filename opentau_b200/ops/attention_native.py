@@ -1,4 +1,4 @@
-"""ctypes launcher of the tcgen05 block-causal attention kernels."""
+"""ctypes launchers of the block-causal attention kernels: tcgen05 (bf16) and the exact fp32 CUDA-core kernels."""
 
 from __future__ import annotations
 
@@ -124,4 +124,72 @@ def attn_bwd(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor
     if rc != 0:
         raise RuntimeError(f"native attn_bwd failed with code {rc} (B={B} Sq={Sq} Sk={Sk} H={H} Hkv={Hkv} D={D})")
     cuda_ops.launch_count += 4
+    return dq, dk, dv
+
+
+# ------------------------------------------------------------------------------------------- exact fp32 (CUDA cores)
+def supported_f32(q: Tensor, k: Tensor, v: Tensor) -> bool:
+    """fp32 CUDA tensors with a head width that is a multiple of 4 up to 256 go to ``csrc/attention_f32.cu``: exact
+    fp32 arithmetic without the (B, H, Sq, Sk) score tensor of the dense body."""
+    if not _enabled() or q.dtype != torch.float32 or not q.is_cuda:
+        return False
+    D, H, Hkv = q.shape[3], q.shape[2], k.shape[2]
+    return k.dtype == v.dtype == torch.float32 and D % 4 == 0 and 4 <= D <= 256 and H % Hkv == 0
+
+
+def _prep_f32(t: Tensor) -> Tensor:
+    if t.stride(3) != 1 or any(s % 4 for s in t.stride()[:3]) or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def _f32_common(q, k, v, q_blk, k_blk, q_valid, k_valid):
+    B, Sq, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    q, k, v = _prep_f32(q), _prep_f32(k), _prep_f32(v)
+    keep = (q, k, v, q_blk.to(torch.int32).contiguous(), k_blk.to(torch.int32).contiguous(), _u8(q_valid), _u8(k_valid))
+    dims = [c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(Hkv), c_int(D),
+            c_longlong(q.stride(0)), c_longlong(q.stride(1)), c_longlong(q.stride(2)),
+            c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
+            c_longlong(v.stride(0)), c_longlong(v.stride(1)), c_longlong(v.stride(2))]
+    return keep, dims
+
+
+def attn_f32_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk, k_blk, q_valid, k_valid, scale: float):
+    from . import cuda_ops
+    B, Sq, H, D = q.shape
+    (q, k, v, qb, kb, qv, kv), dims = _f32_common(q, k, v, q_blk, k_blk, q_valid, k_valid)
+    o = torch.empty(B, Sq, H * D, dtype=torch.float32, device=q.device)
+    lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device)
+    rc = _lib.load("attention_f32").otb_attn_f32_fwd(
+        c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
+        c_void_p(lse.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()), c_void_p(qv.data_ptr()),
+        c_void_p(kv.data_ptr()), *dims, c_float(scale), cuda_ops._stream())
+    if rc != 0:
+        raise RuntimeError(f"fp32 attn_fwd failed with code {rc} (B={B} Sq={Sq} Sk={k.shape[1]} H={H} D={D})")
+    cuda_ops.launch_count += 1
+    return o, lse
+
+
+def attn_f32_bwd(do: Tensor, q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse: Tensor, q_blk, k_blk, q_valid, k_valid,
+                 scale: float):
+    from . import cuda_ops
+    B, Sq, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    (q, k, v, qb, kb, qv, kv), dims = _f32_common(q, k, v, q_blk, k_blk, q_valid, k_valid)
+    o = o.contiguous().float()
+    do = do.contiguous().float()
+    lse = lse.contiguous()
+    dq = torch.empty(B, Sq, H, D, dtype=torch.float32, device=q.device)
+    dk = torch.empty(B, Sk, Hkv, D, dtype=torch.float32, device=q.device)
+    dv = torch.empty(B, Sk, Hkv, D, dtype=torch.float32, device=q.device)
+    delta = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device)
+    rc = _lib.load("attention_f32").otb_attn_f32_bwd(
+        c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()), c_void_p(o.data_ptr()),
+        c_void_p(do.data_ptr()), c_void_p(lse.data_ptr()), c_void_p(delta.data_ptr()), c_void_p(dq.data_ptr()),
+        c_void_p(dk.data_ptr()), c_void_p(dv.data_ptr()), c_void_p(qb.data_ptr()), c_void_p(kb.data_ptr()),
+        c_void_p(qv.data_ptr()), c_void_p(kv.data_ptr()), *dims, c_float(scale), cuda_ops._stream())
+    if rc != 0:
+        raise RuntimeError(f"fp32 attn_bwd failed with code {rc} (B={B} Sq={Sq} Sk={Sk} H={H} Hkv={Hkv} D={D})")
+    cuda_ops.launch_count += 3
     return dq, dk, dv

@@ -19,7 +19,7 @@ CSRC = Path(__file__).parent / "csrc"
 OUT = Path(__file__).parent / "_native"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC"]
-SOURCES = ["gemm_tcgen05", "elementwise", "train_elementwise", "attention_tcgen05", "attention_bwd_tcgen05", "comm_p2p", "noalloc_colsum",
+SOURCES = ["gemm_tcgen05", "elementwise", "train_elementwise", "attention_tcgen05", "attention_bwd_tcgen05", "attention_f32", "stss_corr", "comm_p2p", "noalloc_colsum",
            "gemm_dist_tcgen05", "attention_cp_tcgen05", "gemm_skinny_tcgen05"]
 
 

@@ -165,3 +165,68 @@ def test_split_kv_matches_single_pass(B, Sq, Sk, H, Hkv, D, nsplit):
     cuda_ops.check_status()
     torch.testing.assert_close(got_o.float(), want_o.float(), atol=1e-2, rtol=1e-2)
     torch.testing.assert_close(got_lse, want_lse, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("D", [32, 72, 128, 160, 256])
+@pytest.mark.parametrize("H,Hkv", [(8, 1), (6, 3), (4, 4)])
+@pytest.mark.parametrize("Sq,cross", [(50, 0), (131, 0), (50, 203), (33, 64)])
+def test_fp32_attention_kernels_match_the_dense_fp32_reference(D, H, Hkv, Sq, cross):
+    """The exact fp32 kernels (forward, dQ, dK / dV over the whole GQA group) against the CPU fp32 dense evaluation,
+    at fp32 tolerances: block-causal mask, pads, a cross-attention prefix with block id INT_MIN, strided inputs."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import attention_native
+    dev = torch.device("cuda:0")
+    B = 2
+    qh, kh, vh, qb, kb, qv, kv = _case(B, Sq, H, Hkv, D, cross, dev, seed=3 * D + Sq)
+    g = torch.Generator().manual_seed(11)
+    Sk = Sq + cross
+    # q as a strided view of a fused (B, Sq, H + 2 Hkv, D) projection, as the models produce it
+    fused = torch.randn(B, Sq, H + 2 * Hkv, D, generator=g).to(dev)
+    q = fused[:, :, :H]
+    k = torch.randn(B, Sk, Hkv, D, generator=g).to(dev)
+    v = torch.randn(B, Sk, Hkv, D, generator=g).to(dev)
+    scale = D ** -0.5
+    assert attention_native.supported_f32(q, k, v) and not attention_native.supported(q, k, v)
+    from opentau_b200.ops import attention as dispatch
+    o, lse = dispatch.attn_fwd(q, k, v, qb, kb, qv, kv, scale)          # the dispatcher picks the fp32 kernels
+    qc, kc, vc = q.cpu().contiguous(), k.cpu(), v.cpu()
+    o_ref, lse_ref = ops.prims.attn_fwd(qc, kc, vc, qb.cpu(), kb.cpu(), qv.cpu(), kv.cpu(), scale)
+    vq, vk = qv.cpu(), kv.cpu()
+    torch.testing.assert_close(o.cpu().view(B, Sq, H, D)[vq], o_ref.view(B, Sq, H, D)[vq], rtol=2e-4, atol=2e-5)
+    torch.testing.assert_close(lse.cpu().permute(0, 2, 1)[vq], lse_ref.permute(0, 2, 1)[vq], rtol=1e-5, atol=2e-5)
+    do = (torch.randn(B, Sq, H * D, generator=g) * vq[:, :, None]).to(dev)
+    dq, dk, dv = attention_native.attn_f32_bwd(do, q, k, v, o, lse, qb, kb, qv, kv, scale)
+    dqr, dkr, dvr = ops.prims.attn_bwd(do.cpu(), qc, kc, vc, o_ref, lse_ref, qb.cpu(), kb.cpu(), vq, vk, scale)
+    torch.testing.assert_close(dq.cpu()[vq], dqr[vq], rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(dk.cpu()[vk], dkr[vk], rtol=5e-4, atol=1e-4)
+    torch.testing.assert_close(dv.cpu()[vk], dvr[vk], rtol=5e-4, atol=1e-4)
+    hidden = ~vq                                               # rows that see nothing: zero output, zero gradient
+    if hidden.any():
+        assert float(o.cpu().view(B, Sq, H, D)[hidden].abs().max()) == 0.0
+        assert float(dq.cpu()[hidden].abs().max()) == 0.0
+
+
+def test_fp32_attention_through_autograd_on_gpu():
+    """fp32 CUDA tensors through ``ops.block_attention`` (the autograd function the models call) take the fp32 kernels
+    and give the CPU gradients."""
+    from opentau_b200 import ops
+    dev = torch.device("cuda:0")
+    B, Sq, H, Hkv, D = 2, 70, 8, 2, 64
+    _, _, _, qb, kb, qv, kv = _case(B, Sq, H, Hkv, D, 0, dev, seed=9)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B, Sq, H, D, generator=g)
+    k = torch.randn(B, Sq, Hkv, D, generator=g)
+    v = torch.randn(B, Sq, Hkv, D, generator=g)
+    w = torch.randn(B, Sq, H * D, generator=g) * qv.cpu()[:, :, None]
+    outs = []
+    for device in ("cpu", dev):
+        a, b_, c = (t.clone().to(device).requires_grad_(True) for t in (q, k, v))
+        o = ops.block_attention(a, b_, c, qb.to(device), kb.to(device), qv.to(device), kv.to(device), D ** -0.5)
+        (o * w.to(device)).sum().backward()
+        outs.append((o.detach().cpu(), a.grad.cpu(), b_.grad.cpu(), c.grad.cpu()))
+    (o_c, dq_c, dk_c, dv_c), (o_g, dq_g, dk_g, dv_g) = outs
+    vq = qv.cpu()
+    torch.testing.assert_close(o_g[vq], o_c[vq], rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(dq_g[vq], dq_c[vq], rtol=5e-4, atol=1e-4)
+    torch.testing.assert_close(dk_g[vq], dk_c[vq], rtol=5e-4, atol=1e-4)
+    torch.testing.assert_close(dv_g[vq], dv_c[vq], rtol=5e-4, atol=1e-4)

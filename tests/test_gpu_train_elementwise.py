@@ -174,3 +174,28 @@ def test_native_resolution_image_through_the_vision_tower(dev):
         got = gpu(x.to(dev).to(torch.bfloat16))
     assert got.shape == want.shape == (2, 13 * 23, 128)
     torch.testing.assert_close(got.float().cpu(), want, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,T,H,W,C,L,k", [(2, 4, 16, 16, 256, 5, 9), (1, 3, 5, 7, 64, 3, 3), (2, 2, 6, 4, 96, 1, 5),
+                                           (1, 6, 4, 4, 40, 5, 3)])
+def test_stss_window_correlation_kernels_match_the_dense_evaluation(dtype, B, T, H, W, C, L, k):
+    """Forward and backward of the space-time window correlation against the unfold + einsum evaluation on the CPU in
+    fp32: clamped frame offsets (a frame is its own neighbour at the ends, so a feature is source and target of the
+    same product), zeros outside the image, a head width that is not a power of two, L = 1."""
+    from opentau_b200.ops import stss
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(B * 100 + C + L)
+    x = torch.nn.functional.normalize(torch.randn(B, T, H * W, C, generator=g), dim=-1)
+    w = torch.randn(B, T, H * W, L, k * k, generator=g)
+    xc = x.to(dtype).float().requires_grad_(True)
+    ref = stss.dense_window_correlation(xc, T, H, W, L, k)
+    (ref * w).sum().backward()
+    xg = x.to(dtype).to(dev).requires_grad_(True)
+    assert stss.native_supported(xg)
+    out = stss.local_window_correlation(xg, T, H, W, L, k)
+    (out.float() * w.to(dev)).sum().backward()
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-2)
+    torch.testing.assert_close(out.float().cpu(), ref.detach(), **tol)
+    gtol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=0.15)
+    torch.testing.assert_close(xg.grad.float().cpu(), xc.grad, **gtol)

@@ -43,6 +43,29 @@ def test_temporal_window_clamps_at_the_ends():
     assert torch.allclose(s[0, 0, :, :, 0], s[0, 0, :, :, 1], atol=1e-6)
 
 
+def test_window_correlation_over_token_major_features_matches_the_two_tensor_form():
+    """The op the motion module calls (token-major features, all frame offsets at once) against ``local_correlation``
+    applied frame pair by frame pair, for every correlation variant, L = 1 included, on a non-square grid."""
+    from opentau_b200.ops.stss import local_window_correlation, target_frames
+    torch.manual_seed(1)
+    B, t, h, w, C = 2, 4, 3, 5, 8
+    x = torch.randn(B * t * h * w, C)
+    for L, k in ((3, 3), (1, 3), (5, 5)):
+        idx = target_frames(t, L, "cpu")
+        assert idx.shape == (t, L) and int(idx.min()) == 0 and int(idx.max()) <= t - 1
+        for func in ("cosine", "dotproduct", "dotproduct_softmax"):
+            got = STSSTransformation((L, k, k), func)(x, t, h, w)
+            v = x.view(B, t, h, w, C).permute(0, 1, 4, 2, 3)
+            for ti in range(t):
+                for li in range(L):
+                    want = local_correlation(v[:, ti], v[:, int(idx[ti, li])], k, func)
+                    assert torch.allclose(got[:, ti, :, :, li], want, atol=1e-5), (L, k, func, ti, li)
+    raw = local_window_correlation(x.view(B, t, h * w, C), t, h, w, 3, 3)
+    assert raw.shape == (B, t, h * w, 3, 9)
+    with pytest.raises(ValueError):
+        local_window_correlation(x.view(B, t, h * w, C), t, h, w, 2, 3)
+
+
 def test_motion_module_is_a_noop_at_init_and_learns():
     torch.manual_seed(0)
     mm = MotionModule(32, 16, 32, window=(3, 3, 3), ext_chnls=(8,), int_chnls=(8, 8, 12))
