@@ -91,7 +91,8 @@ class DatasetConfig:
 class DatasetMixtureConfig:
     datasets: list[DatasetConfig] = field(default_factory=list)
     weights: list[float] | None = None
-    action_freq: float = 30.0
+    #: Hz at which every dataset's actions are resampled; None = each dataset at its own fps
+    action_freq: float | None = None
     image_resample_strategy: str = "nearest"
     vector_resample_strategy: str = "nearest"
     val_split_ratio: float = 0.05
@@ -122,6 +123,8 @@ class DatasetMixtureConfig:
             raise ValueError("vector_resample_strategy must be 'nearest' or 'linear'")
         if not (0.0 <= self.val_split_ratio < 1.0):
             raise ValueError("val_split_ratio must be in [0, 1)")
+        if self.action_freq is not None and not self.action_freq > 0:
+            raise ValueError(f"action_freq must be positive or None, got {self.action_freq}")
         for p in ("history_state_drop_prob", "subgoal_drop_prob", "subgoal_end_of_segment_prob",
                   "response_drop_prob", "metadata_drop_all_prob", "metadata_drop_each_prob"):
             if not (0.0 <= getattr(self, p) <= 1.0):

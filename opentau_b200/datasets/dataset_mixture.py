@@ -177,7 +177,7 @@ class _MixtureStream(IterableDataset):
 
 class WeightedDatasetMixture:
     def __init__(self, datasets: Sequence[Dataset], names: Sequence[str], weights: Sequence[float] | None = None,
-                 norm_keys: Sequence[str] | None = None, seed: int = 1000, action_freq: float = 30.0):
+                 norm_keys: Sequence[str] | None = None, seed: int = 1000, action_freq: float | None = None):
         if not datasets:
             raise ValueError("a mixture needs at least one dataset")
         self.weights = list(weights) if weights is not None else [float(len(d)) for d in datasets]

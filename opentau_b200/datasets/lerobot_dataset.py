@@ -231,6 +231,32 @@ def _jsonable_info(info: dict) -> dict:
     return out
 
 
+def resolve_selected_episodes(all_episodes, episodes: list[int] | None, excluded_episodes: list[int] | None,
+                              repo_id: str = "") -> list[int] | None:
+    """``(episodes if given else all) - excluded``, sorted; the deny list wins over the allow list.  ``None`` means
+    "no selection active: every episode".  A deny list that empties the selection is an error."""
+    if not excluded_episodes:
+        return sorted(episodes) if episodes is not None else None
+    excluded = set(excluded_episodes)
+    base = list(episodes) if episodes is not None else list(all_episodes)
+    kept = sorted(e for e in base if e not in excluded)
+    if not kept:
+        raise ValueError(f"excluded_episodes removed every episode from {repo_id!r} (base={len(base)} episodes, "
+                         f"excluded={sorted(excluded)}).")
+    return kept
+
+
+def aggregate_selected_stats(meta: "LeRobotDatasetMetadata", episodes: list[int] | None = None,
+                             excluded_episodes: list[int] | None = None) -> dict:
+    """Per-feature statistics over the SELECTED episodes (what the policy trains on), for off-line consumers such as
+    the tokenizer fit and the normalisation diagnostic.  Falls back to the dataset-level statistics when no selection
+    is active or the dataset has no per-episode statistics (v2.0)."""
+    selected = resolve_selected_episodes(meta.episodes, episodes, excluded_episodes, meta.repo_id)
+    if selected is None or not meta.episodes_stats:
+        return meta.stats
+    return aggregate_stats([meta.episodes_stats[e] for e in selected])
+
+
 # ------------------------------------------------------------------------------------------------ base
 class BaseDataset(torch.utils.data.Dataset):
     """Shared standard-format conversion (LeRobot and VQA datasets both end here)."""
@@ -242,12 +268,45 @@ class BaseDataset(torch.utils.data.Dataset):
         self.max_state_dim, self.max_action_dim = cfg.max_state_dim, cfg.max_action_dim
         self.action_chunk = cfg.action_chunk
         self.n_obs_history = cfg.dataset_mixture.n_obs_history
-        self.train = train
+        # the two augmentation switches of a dataset instance: optional-key dropout rolls (masking / zero-fill; the
+        # choice of WHICH future frame becomes a subgoal stays random either way) and per-task prompt substitution.
+        # The validation subset is a shallow copy with its own values (shallow_copy_with_dropout).
+        self.enable_optional_key_dropout = bool(train)
+        self.enable_prompt_substitution = bool(train)
         self._name_map = name_map or {}
         self.state_index: list[int] | None = None
         self.action_index: list[int] | None = None
         self.delta_action_state_map: dict | None = None
         self._opt_rng = random.Random(0)
+
+    @property
+    def train(self) -> bool:
+        return self.enable_optional_key_dropout
+
+    @train.setter
+    def train(self, flag: bool) -> None:
+        self.enable_optional_key_dropout = bool(flag)
+
+    def shallow_copy_with_dropout(self, *, enable_dropout: bool, enable_prompt_substitution: bool = False) -> "BaseDataset":
+        """A copy that shares the table, metadata, index and cached segment tables by reference and differs only in the
+        two augmentation switches: how the validation subset gets its own instance."""
+        import copy
+        clone = copy.copy(self)
+        clone.enable_optional_key_dropout = enable_dropout
+        clone.enable_prompt_substitution = enable_prompt_substitution
+        return clone
+
+    def _assert_image_in_unit_range(self, img: Tensor, *, name: str, expect_temporal: bool | None = None) -> None:
+        """Rank (``(3, H, W)``, or ``(T, 3, H, W)`` with an observation history; subgoals pass ``expect_temporal=False``),
+        three channels and values in [0, 1]."""
+        if expect_temporal is None:
+            expect_temporal = self.n_obs_history is not None
+        ndim, cdim, desc = (4, 1, "(T, 3, H, W)") if expect_temporal else (3, 0, "(3, H, W)")
+        ok = img.dim() == ndim and img.shape[cdim] == 3 and float(img.min()) >= -1e-6 and float(img.max()) <= 1.0 + 1e-6
+        if not ok:
+            raise AssertionError(f"Expected image {name} to have shape {desc} with values in [0, 1], got shape "
+                                 f"{tuple(img.shape)}, min={float(img.min())}, max={float(img.max())}, "
+                                 f"self={self._get_feature_mapping_key()}.")
 
     # hooks -------------------------------------------------------------------------------------------
     def _get_name_map(self) -> dict[str, str]:
@@ -301,35 +360,73 @@ class BaseDataset(torch.utils.data.Dataset):
 
     def _roll(self, p: float) -> bool:
         """True = drop.  Dropout rolls are active in training (or when validation opts in)."""
-        if not self.train:
+        if not self.enable_optional_key_dropout:
             return False
         return self._opt_rng.random() < p
 
     def _emit_optional_keys(self, item: dict, out: dict) -> None:
+        """Memory / subgoal / metadata keys with their training-time dropout.  Every key is ALWAYS present: numeric and
+        image keys are zero-filled with a parallel ``<key>_is_pad`` flag when absent or masked, string keys use the
+        empty string as the pad signal.  Order of the rolls (all of them off when ``enable_optional_key_dropout`` is):
+
+        1. ``history_state_drop_prob``: ``obs_history_is_pad`` all True and the historical camera frames zeroed; the
+           state history is left alone here (zeroing a raw state before normalisation would turn 0 into -mean/std; the
+           policy zeroes it after normalising) and the current step is always kept;
+        2. subgoals are all-or-none: ``subgoal_is_pad`` is one flag for every ``subgoal{k}`` (their drop roll was taken
+           before the frames were decoded, in ``_load_subgoal_frames``);
+        3. ``response_drop_prob``: only when the subgoals were kept;
+        4. ``metadata_drop_all_prob`` masks speed, mistake, quality, robot type and control mode together, otherwise
+           ``metadata_drop_each_prob`` rolls per field.  ``fps`` (the mixture's ``action_freq`` when it resamples, else
+           the dataset's own rate) takes part in no roll; a dataset without a frame rate emits ``fps=0`` padded."""
         mix = self.cfg.dataset_mixture
-        drop_all = self._roll(mix.metadata_drop_all_prob)
-        for key, dtype in (("speed", torch.long), ("quality", torch.long), ("mistake", torch.bool)):
-            raw = item.get(f"{key}_raw")
-            if raw is None:
-                continue
-            dropped = drop_all or self._roll(mix.metadata_drop_each_prob)
-            out[key] = torch.tensor(raw if not dropped else 0, dtype=dtype)
-            out[f"{key}_is_pad"] = torch.tensor(dropped, dtype=torch.bool)
-        for key in ("robot_type", "control_mode"):
-            if item.get(key) is not None:
-                out[key] = "" if drop_all else str(item[key])
-        if "memory_raw" in item:
-            out["memory"] = item["memory_raw"]
-            out["next_memory"] = item.get("next_memory_raw") or ""
-        if mix.emit_fps and "fps" in item:
-            out["fps"] = torch.tensor(int(item["fps"]), dtype=torch.long)
-        if out.get("response") and self._roll(mix.response_drop_prob):
+        if self._roll(mix.history_state_drop_prob):
+            if self.n_obs_history is not None:
+                out["obs_history_is_pad"] = torch.ones(self.n_obs_history, dtype=torch.bool)
+                if self.n_obs_history > 1:
+                    for k in range(self.num_cams):
+                        if f"camera{k}" in out:
+                            out[f"camera{k}"][:-1] = 0
+            else:
+                out["obs_history_is_pad"] = torch.tensor([True], dtype=torch.bool)
+
+        H, W = self.resolution
+        pad_subgoals = not all(item.get(f"subgoal{k}_raw") is not None for k in range(self.num_cams))
+        for k in range(self.num_cams):
+            if pad_subgoals:
+                out[f"subgoal{k}"] = torch.zeros(3, H, W)
+            else:
+                im = item[f"subgoal{k}_raw"].float()
+                if tuple(im.shape[-2:]) != (H, W):
+                    im = ops.resize_with_pad(im[None], W, H, pad_value=0.0)[0]
+                out[f"subgoal{k}"] = im
+            self._assert_image_in_unit_range(out[f"subgoal{k}"], name=f"subgoal{k}", expect_temporal=False)
+        out["subgoal_is_pad"] = torch.tensor(pad_subgoals)
+        if not pad_subgoals and self._roll(mix.response_drop_prob):
             out["response"] = ""
-        for k, v in item.items():
-            if k.startswith("subgoal") and isinstance(v, Tensor):
-                dropped = self._roll(mix.subgoal_drop_prob)
-                out[k] = v if not dropped else torch.zeros_like(v)
-                out[f"{k}_is_pad"] = torch.tensor(dropped, dtype=torch.bool)
+
+        out["memory"] = item["memory_raw"] if isinstance(item.get("memory_raw"), str) else ""
+        out["next_memory"] = item["next_memory_raw"] if isinstance(item.get("next_memory_raw"), str) else ""
+
+        drop_all = self._roll(mix.metadata_drop_all_prob)
+        for key, dtype in (("speed", torch.long), ("mistake", torch.bool), ("quality", torch.long)):
+            raw = item.get(f"{key}_raw")
+            dropped = drop_all or self._roll(mix.metadata_drop_each_prob)
+            if raw is None or dropped:
+                out[key] = torch.tensor(False if dtype is torch.bool else 0, dtype=dtype)
+                out[f"{key}_is_pad"] = torch.tensor(True)
+            else:
+                out[key] = torch.tensor(bool(raw) if dtype is torch.bool else int(raw), dtype=dtype)
+                out[f"{key}_is_pad"] = torch.tensor(False)
+        for key in ("robot_type", "control_mode"):
+            dropped = drop_all or self._roll(mix.metadata_drop_each_prob)
+            out[key] = "" if dropped else str(item.get(key) or "")
+        if mix.emit_fps:
+            native = item.get("fps")
+            if native is None:
+                out["fps"], out["fps_is_pad"] = torch.tensor(0, dtype=torch.long), torch.tensor(True)
+            else:
+                eff = int(mix.action_freq) if getattr(mix, "action_freq", None) is not None else int(native)
+                out["fps"], out["fps_is_pad"] = torch.tensor(eff, dtype=torch.long), torch.tensor(False)
 
     @staticmethod
     def _resolve_episode_success(item: dict, episodes_info: dict, name_map: dict[str, str],
@@ -430,14 +527,24 @@ class LeRobotDataset(BaseDataset):
                  tolerance_s: float = 1e-4, revision: str | None = None, video_backend: str | None = None,
                  image_resample_strategy: str = "nearest", vector_resample_strategy: str = "nearest",
                  standardize: bool = True, dataset_cfg=None, train: bool = True, meta: LeRobotDatasetMetadata | None = None,
-                 return_advantage_input: bool = False):
+                 return_advantage_input: bool = False, excluded_episodes: list[int] | None = None):
         self.repo_id = repo_id
         self.meta = meta or LeRobotDatasetMetadata(repo_id, root, revision)
         self.root = self.meta.root
         dcfg = dataset_cfg
         name_map = get_mapping(repo_id, self.meta.features, getattr(dcfg, "data_features_name_mapping", None))
         super().__init__(cfg, name_map=name_map, train=train)
-        self.episodes = sorted(episodes) if episodes is not None else sorted(self.meta.episodes)
+        if excluded_episodes is None and dcfg is not None:
+            excluded_episodes = getattr(dcfg, "excluded_episodes", None)
+        selected = resolve_selected_episodes(self.meta.episodes, episodes, excluded_episodes, repo_id)
+        if selected is not None and self.meta.episodes_stats:
+            # the mixture normaliser pools ``meta.stats``: it must describe the episodes that are trained on, not the
+            # whole dataset on disk (a v2.0 dataset has no per-episode statistics and keeps the dataset-level ones)
+            # (on a shallow copy: a metadata object handed in by the caller may be shared with the other split)
+            import copy
+            self.meta = copy.copy(self.meta)
+            self.meta.stats = aggregate_stats([self.meta.episodes_stats[e] for e in selected])
+        self.episodes = selected if selected is not None else sorted(self.meta.episodes)
         self.image_transforms = image_transforms
         self.delta_timestamps = {k: np.asarray(v, dtype=np.float64) for k, v in (delta_timestamps or {}).items()}
         self.tolerance_s = tolerance_s
@@ -460,7 +567,78 @@ class LeRobotDataset(BaseDataset):
         self._load_table()
         self.episode_data_index = get_episode_data_index(self.meta.episodes, self.episodes)
         self.epi2idx = {ep: i for i, ep in enumerate(self.episodes)}
-        self.speed_raw_by_episode = {ep: int(self.meta.episodes[ep].get("speed", 0) or 0) for ep in self.episodes}
+        self._build_episode_tables()
+
+    def _build_episode_tables(self) -> None:
+        """Per-episode caches of the optional-key path, read once: lengths, segment start frames (a legacy episode is
+        one segment starting at 0), the speed label of every selected episode, one memory string per segment."""
+        from .speed_percentiles import (episode_to_task_index, load_or_compute_speed_percentiles,
+                                        speed_bucket_by_episode)
+        self.episode_lengths = {ep: int(info["length"]) for ep, info in self.meta.episodes.items()}
+        self.segment_starts_by_episode: dict[int, np.ndarray] = {}
+        for ep, info in self.meta.episodes.items():
+            starts = info.get("segments")
+            if starts is None or len(starts) == 0:
+                starts = [0]
+            # a list of start frames; [start, end) pairs are accepted and reduced to their starts
+            starts = [int(s[0]) if isinstance(s, (list, tuple)) else int(s) for s in starts]
+            self.segment_starts_by_episode[ep] = np.asarray(starts, dtype=np.int64)
+        first_rows = {ep: int(self._numeric["task_index"][int(self.episode_data_index["from"][self.epi2idx[ep]])])
+                      for ep in self.episodes} if "task_index" in self._numeric else {}
+        self.episode_to_task_index = episode_to_task_index(first_rows, set(self.meta.task_to_task_index.values()))
+        if any("speed" in self.meta.episodes[ep] for ep in self.episodes):
+            # an explicit per-episode label in the metadata wins over the length ranking
+            self.speed_percentiles_by_task = {}
+            self.speed_raw_by_episode = {ep: int(self.meta.episodes[ep].get("speed", 0) or 0) for ep in self.episodes}
+        else:
+            self.speed_percentiles_by_task = load_or_compute_speed_percentiles(
+                self.root, self.episode_lengths, self.episode_to_task_index, self.meta.task_to_task_index)
+            self.speed_raw_by_episode = speed_bucket_by_episode(self.episodes, self.episode_lengths,
+                                                                self.episode_to_task_index,
+                                                                self.speed_percentiles_by_task)
+        self.segment_memories_by_episode: dict[int, list[str]] = {}
+        has_memory = "memory" in self._string_cols
+        col = self._table.column("memory") if has_memory else None
+        for ep in self.episodes:
+            starts = self.segment_starts_by_episode[ep]
+            if has_memory:
+                ep_start = int(self.episode_data_index["from"][self.epi2idx[ep]])
+                self.segment_memories_by_episode[ep] = [str(col[ep_start + int(s)].as_py() or "") for s in starts]
+            else:
+                self.segment_memories_by_episode[ep] = [""] * len(starts)
+
+    # -- segments, memory, subgoals -----------------------------------------------------------------------
+    def _lookup_segment_index(self, ep_idx: int, frame_in_ep: int) -> int:
+        starts = self.segment_starts_by_episode[ep_idx]
+        return max(int(np.searchsorted(starts, frame_in_ep, side="right")) - 1, 0)
+
+    def _segment_end_in_ep(self, ep_idx: int, seg_idx: int) -> int:
+        """Exclusive end frame of a segment inside its episode."""
+        starts = self.segment_starts_by_episode[ep_idx]
+        return int(starts[seg_idx + 1]) if seg_idx + 1 < len(starts) else self.episode_lengths[ep_idx]
+
+    def _lookup_next_memory(self, ep_idx: int, frame_in_ep: int) -> str:
+        """The memory string that holds at frame ``frame_in_ep + 1`` (clipped at the episode's end)."""
+        nxt = min(frame_in_ep + 1, self.episode_lengths[ep_idx] - 1)
+        memories = self.segment_memories_by_episode.get(ep_idx, [""])
+        if not memories:
+            return ""
+        return memories[min(self._lookup_segment_index(ep_idx, nxt), len(memories) - 1)]
+
+    def _sample_subgoal_frame(self, ep_idx: int, frame_in_ep: int, *, at_end_of_segment: bool) -> int:
+        """A future frame of the episode to serve as the subgoal: the last frame of the current segment, or one drawn
+        uniformly from ``[t, t + 4 s]`` clipped to the segment and the episode.  Episodes without a ``segments``
+        annotation get a fixed 4 s look-ahead (clipped to the episode), so legacy datasets still get supervision."""
+        n = self.episode_lengths[ep_idx]
+        window = int(round(4.0 * self.fps))
+        if "segments" not in self.meta.episodes[ep_idx]:
+            return min(frame_in_ep + window, n - 1)
+        seg = self._lookup_segment_index(ep_idx, frame_in_ep)
+        upper = max(min(self._segment_end_in_ep(ep_idx, seg), n) - 1, frame_in_ep)
+        if at_end_of_segment:
+            return upper
+        top = min(frame_in_ep + window, upper)
+        return frame_in_ep if top <= frame_in_ep else self._opt_rng.randint(frame_in_ep, top)
 
     # -- table ------------------------------------------------------------------------------------------
     def _load_table(self) -> None:
@@ -584,36 +762,29 @@ class LeRobotDataset(BaseDataset):
     def _resolve_task(self, task_index: int) -> str:
         task = self.meta.tasks.get(int(task_index), "")
         subs = self.prompt_substitutions
-        allow = self.train or self.cfg.dataset_mixture.val_enable_prompt_substitution
-        if subs and allow and task in subs:
+        if subs and self.enable_prompt_substitution and task in subs:
             return self._opt_rng.choice(subs[task])
         return task
 
     def _load_subgoal_frames(self, ep_idx: int, frame_in_ep: int) -> dict[str, Tensor]:
-        """Goal frames for datasets that declare subtask segments (``episodes[ep]["segments"] = [[start, end], ..]``):
-        the frame at the end of the current segment, or with probability ``subgoal_end_of_segment_prob`` ... a
-        uniformly drawn later frame of the segment."""
-        segs = self.meta.episodes[ep_idx].get("segments")
-        if not segs:
-            return {}
-        seg = next(((s, e) for s, e in segs if s <= frame_in_ep < e), None)
-        if seg is None:
+        """One goal frame per camera slot, for any dataset that has cameras.  The drop roll comes first, so a dropped
+        subgoal costs no decode (with dropout switched off it is never rolled); the end-of-segment versus uniform roll
+        happens once per sample and is shared by the cameras; video features are decoded at the frame's timestamp,
+        image features come from the parquet row of the same frame."""
+        if self.num_cams <= 0 or not self.meta.camera_keys:
             return {}
         mix = self.cfg.dataset_mixture
-        end = seg[1] - 1
-        if self.train and self._opt_rng.random() >= mix.subgoal_end_of_segment_prob and end > frame_in_ep:
-            end = self._opt_rng.randint(frame_in_ep + 1, end)
-        gidx = int(self.episode_data_index["from"][self.epi2idx[ep_idx]]) + end
-        out = {}
+        if self.enable_optional_key_dropout and self._opt_rng.random() < mix.subgoal_drop_prob:
+            return {}
+        at_end = self._opt_rng.random() < mix.subgoal_end_of_segment_prob
+        goal = self._sample_subgoal_frame(ep_idx, frame_in_ep, at_end_of_segment=at_end)
+        gidx = int(self.episode_data_index["from"][self.epi2idx[ep_idx]]) + goal
         imgs = {**self._query_images(gidx, {}), **(self._query_videos(gidx, ep_idx, {}) if self.meta.video_keys else {})}
-        H, W = self.resolution
+        out = {}
         for i in range(self.num_cams):
             raw = self._name_map.get(f"camera{i}")
             if raw in imgs:
-                im = imgs[raw][None]
-                if tuple(im.shape[-2:]) != (H, W):
-                    im = ops.resize_with_pad(im, W, H, pad_value=0.0)
-                out[f"subgoal{i}"] = im[0]
+                out[f"subgoal{i}_raw"] = imgs[raw]
         return out
 
     @retry_random_on_failure
@@ -649,6 +820,7 @@ class LeRobotDataset(BaseDataset):
         item.setdefault("response", "")
         if "memory" in item:
             item["memory_raw"] = str(item["memory"])
+            item["next_memory_raw"] = self._lookup_next_memory(ep_idx, frame_in_ep)
         success = self._attach_mistake_raw(item, ep_info, ep_idx)
         if ep_info.get("quality") is not None:
             item["quality_raw"] = int(ep_info["quality"])

@@ -239,6 +239,8 @@ class PI07LowLevelPolicy(PI05Policy):
                     im = ops.resize_with_pad(im.float(), cfgsz[1], cfgsz[0], pad_value=0.0)
                 imgs.append(im * 2.0 - 1.0)
                 pad = batch.get(f"{k}_is_pad")
+                if pad is None:                       # datasets emit one flag for all cameras: subgoals are all-or-none
+                    pad = batch.get("subgoal_is_pad")
                 ms.append(~pad.bool().to(device) if pad is not None
                           else torch.ones(im.shape[0], dtype=torch.bool, device=device))
             kw["subgoal_images"], kw["subgoal_masks"] = imgs, ms

@@ -35,7 +35,9 @@ def attach(root: str | Path, labels: dict) -> dict:
                 ep[f] = lab[f]
         segs = lab.get("segments")
         if segs:
-            ep["segments"] = [[int(s), int(e)] for s, e, *_ in segs]
+            # the metadata keeps the START frame of every segment (a segment ends where the next one starts, the
+            # last one at the episode's end): the format the dataset reader's segment tables are built from
+            ep["segments"] = [int(s) for s, *_ in segs]
             path = root / info["data_path"].format(episode_chunk=int(key) // info.get("chunks_size", 1000), episode_index=int(key))
             table = pq.read_table(path)
             resp = [""] * table.num_rows

@@ -1,7 +1,7 @@
 """Cut the episodes of a LeRobot dataset into one episode per subtask segment
 (reference ``src/opentau/scripts/segment_lerobot_dataset.py``).
 
-Reads ``segments`` of every episode (``[[start, end], ...]``, see ``attach_metadata``), and writes a new v2.1 dataset
+Reads ``segments`` of every episode (segment start frames, see ``attach_metadata``; ``[start, end)`` pairs work too), and writes a new v2.1 dataset
 whose episodes are the segments; the task of a new episode is the segment's ``response`` text when present, else the
 original task.  Image features are carried over (videos are re-encoded per new episode).
 """
@@ -27,7 +27,15 @@ def segment(src_ds, out_root: str | Path, repo_id: str) -> dict:
     n_new = 0
     try:
         for ep in src_ds.episodes:
-            segs = src_ds.meta.episodes[ep].get("segments") or [[0, int(src_ds.meta.episodes[ep]["length"])]]
+            length = int(src_ds.meta.episodes[ep]["length"])
+            raw = src_ds.meta.episodes[ep].get("segments") or [0]
+            # start frames (each segment runs to the next start, the last to the episode's end); explicit
+            # [start, end) pairs are accepted as well
+            starts = [int(x[0]) if isinstance(x, (list, tuple)) else int(x) for x in raw]
+            ends = [int(x[1]) if isinstance(x, (list, tuple)) and len(x) > 1 else (starts[i + 1] if i + 1 < len(starts)
+                                                                                    else length)
+                    for i, x in enumerate(raw)]
+            segs = list(zip(starts, ends))
             base = int(src_ds.episode_data_index["from"][src_ds.epi2idx[ep]])
             for s, e in segs:
                 for fi in range(int(s), int(e)):

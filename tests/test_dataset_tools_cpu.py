@@ -29,13 +29,13 @@ def test_attach_segment_and_visualize(tmp_path):
                                                  "1": {"success": False}}})
     assert out == {"episodes": 2, "frames_labelled": 10}
     meta = LeRobotDatasetMetadata("local/toy", root=tmp_path / "toy")
-    assert meta.episodes[0]["segments"] == [[0, 4], [4, 10]] and meta.episodes[1]["success"] is False
+    assert meta.episodes[0]["segments"] == [0, 4] and meta.episodes[1]["success"] is False
     dc, cfg = _cfg(tmp_path / "toy", subgoal_drop_prob=0.0, subgoal_end_of_segment_prob=1.0, response_drop_prob=0.0,
                    metadata_drop_all_prob=0.0, metadata_drop_each_prob=0.0)
     ds = make_dataset(dc, cfg)
     s = ds[1]
     assert s["response"] == "reach" and ds[6]["response"] == "grasp" and ds[12]["response"] == ""
-    assert s["subgoal0"].shape == (3, 56, 56) and not bool(s["subgoal0_is_pad"])
+    assert s["subgoal0"].shape == (3, 56, 56) and not bool(s["subgoal_is_pad"])
     assert abs(float(s["subgoal0"][0, 28, 28]) * 255 - 9) < 2            # frame 3 = end of the first segment
     assert int(s["quality"]) == 4 and int(s["speed"]) == 2
     rep = segment(ds, tmp_path / "seg", "local/toy_seg")

@@ -6,7 +6,7 @@ import torch
 
 from opentau_b200.datasets.delta_action_stats import HistogramQuantiles, RunningStats, cache_key
 from opentau_b200.datasets.online_buffer import OnlineBuffer, compute_sampler_weights
-from opentau_b200.datasets.speed_percentiles import episode_speed, speed_buckets
+from opentau_b200.datasets import speed_percentiles as SP
 
 
 def _episode(n, fps=10):
@@ -55,12 +55,45 @@ def test_streaming_stats_equal_batch_stats():
     assert cache_key("a/b", 50, 30.0, {"0": 1}, None) != cache_key("a/b", 50, 30.0, {"0": 2}, None)
 
 
-def test_speed_buckets_per_task():
-    assert episode_speed(np.array([[0.0, 0.0], [3.0, 4.0], [6.0, 8.0]]), fps=2) == 10.0
-    speeds = {0: 1.0, 1: 2.0, 2: 3.0, 3: 4.0, 4: 0.5, 5: 9.0}
-    tasks = {0: "a", 1: "a", 2: "a", 3: "a", 4: "b", 5: "b"}
-    b = speed_buckets(speeds, tasks, n_buckets=2)
-    assert [b[i] for i in range(6)] == [1, 1, 2, 2, 1, 2]
+def test_speed_labels_from_episode_length_percentiles_per_task(tmp_path, caplog):
+    """Length ranking per task: 11 labels between the p5 .. p95 boundaries (a length on a boundary takes the upper
+    bucket), the neutral label for tasks with fewer than ten distinct lengths, a persisted file that is trusted as it
+    is, rows appended for tasks the file lacks, a staleness warning when episodes were added, unknown task indices
+    skipped with one warning."""
+    import logging
+    lengths = {ep: 100 + 10 * ep for ep in range(20)}
+    lengths.update({20: 50, 21: 50, 22: 60})                       # task 1: three episodes, two distinct lengths
+    ep2task = {**{ep: 0 for ep in range(20)}, 20: 1, 21: 1, 22: 1}
+    pct = SP.compute_task_percentiles({0: [lengths[e] for e in range(20)], 1: [50, 50, 60]})
+    assert pct[1] is None and len(pct[0]) == 10 and pct[0] == sorted(pct[0])
+    assert SP.bucket_episode_length(10, pct[0]) == 0 and SP.bucket_episode_length(10_000, pct[0]) == 100
+    assert SP.bucket_episode_length(pct[0][2], pct[0]) == 30        # == p25 -> upper bucket
+    assert SP.bucket_episode_length(123, None) == SP.SPARSE_TASK_BUCKET == 50
+    (tmp_path / "meta").mkdir()
+    names = {"pick": 0, "place": 1}
+    got = SP.load_or_compute_speed_percentiles(tmp_path, lengths, ep2task, names)
+    rows = SP.load_jsonlines(tmp_path / SP.SPEED_PERCENTILES_PATH)
+    assert got == pct and [r["task_index"] for r in rows] == [0, 1] and rows[0]["n_episodes"] == 20
+    assert rows[1]["percentiles"] is None and rows[0]["task"] == "pick"
+    labels = SP.speed_bucket_by_episode(list(range(23)) + [99], {**lengths, 99: 5}, ep2task, got)
+    assert labels[0] == 0 and labels[19] == 100 and labels[21] == 50 and labels[99] == 50
+    # a subset load trusts the file silently; a load with MORE episodes warns and still trusts it
+    sub = {e: t for e, t in ep2task.items() if e < 10}
+    with caplog.at_level(logging.WARNING):
+        assert SP.load_or_compute_speed_percentiles(tmp_path, lengths, sub, names) == pct
+        assert "stale" not in caplog.text
+        more = {**ep2task, 23: 0}
+        assert SP.load_or_compute_speed_percentiles(tmp_path, {**lengths, 23: 7}, more, names) == pct
+        assert "stale" in caplog.text
+    # a task the file lacks is appended, existing rows stay verbatim
+    ep3 = {**ep2task, **{30 + i: 2 for i in range(12)}}
+    len3 = {**lengths, **{30 + i: 200 + i for i in range(12)}}
+    got3 = SP.load_or_compute_speed_percentiles(tmp_path, len3, ep3, {**names, "push": 2})
+    rows3 = SP.load_jsonlines(tmp_path / SP.SPEED_PERCENTILES_PATH)
+    assert rows3[:2] == rows and rows3[2]["task_index"] == 2 and got3[0] == pct[0] and len(got3[2]) == 10
+    with caplog.at_level(logging.WARNING):
+        assert SP.episode_to_task_index({0: 0, 1: 7, 2: 7}, {0, 1}) == {0: 0}
+        assert caplog.text.count("task_index=7") == 1
 
 
 def test_success_role_resolution_chain_and_mistake_polarity():

@@ -188,10 +188,10 @@ def test_stss_window_correlation_kernels_match_the_dense_evaluation(dtype, B, T,
     g = torch.Generator().manual_seed(B * 100 + C + L)
     x = torch.nn.functional.normalize(torch.randn(B, T, H * W, C, generator=g), dim=-1)
     w = torch.randn(B, T, H * W, L, k * k, generator=g)
-    xc = x.to(dtype).float().requires_grad_(True)
+    xc = x.to(dtype).float().detach().clone().requires_grad_(True)
     ref = stss.dense_window_correlation(xc, T, H, W, L, k)
     (ref * w).sum().backward()
-    xg = x.to(dtype).to(dev).requires_grad_(True)
+    xg = x.to(dtype).to(dev).detach().clone().requires_grad_(True)
     assert stss.native_supported(xg)
     out = stss.local_window_correlation(xg, T, H, W, L, k)
     (out.float() * w.to(dev)).sum().backward()
