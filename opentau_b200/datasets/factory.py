@@ -158,6 +158,8 @@ def make_dataset(dataset_cfg: DatasetConfig, cfg, return_advantage_input: bool =
             return train
         val = LeRobotDataset(cfg, dataset_cfg.repo_id, episodes=va, image_transforms=None,
                              train=mix.val_enable_optional_key_dropout, **kw)
+        # the two switches of the validation subset are independent of each other
+        val.enable_prompt_substitution = mix.val_enable_prompt_substitution
         return train, val
     return LeRobotDataset(cfg, dataset_cfg.repo_id, episodes=episodes, image_transforms=tfs, **kw)
 

@@ -225,6 +225,19 @@ class LeRobotDatasetMetadata:
         return obj
 
 
+def _update_video_info(meta: "LeRobotDatasetMetadata", skip_keys: set[str] | None = None) -> None:
+    """Fills the ``info`` block of every video feature (size, codec, pixel format, fps) from the FIRST episode's file,
+    assuming all videos were encoded alike; keys in ``skip_keys`` and keys whose file does not exist yet are left."""
+    from .video_utils import get_video_info
+    for key in meta.video_keys:
+        if skip_keys and key in skip_keys:
+            continue
+        if not meta.features[key].get("info"):
+            path = meta.root / meta.get_video_file_path(0, key)
+            if path.is_file():
+                meta.info["features"][key]["info"] = get_video_info(path)
+
+
 def _jsonable_info(info: dict) -> dict:
     out = dict(info)
     out["features"] = {k: {**ft, "shape": list(ft["shape"])} for k, ft in info["features"].items()}
@@ -824,7 +837,7 @@ class LeRobotDataset(BaseDataset):
         success = self._attach_mistake_raw(item, ep_info, ep_idx)
         if ep_info.get("quality") is not None:
             item["quality_raw"] = int(ep_info["quality"])
-        item["speed_raw"] = self.speed_raw_by_episode[ep_idx] if "speed" in ep_info else None
+        item["speed_raw"] = self.speed_raw_by_episode.get(ep_idx)
         item["robot_type"], item["control_mode"], item["fps"] = self.robot_type, self.control_mode, self.fps
         item.update(self._load_subgoal_frames(ep_idx, frame_in_ep))
         timestamp = float(item["timestamp"])
@@ -853,18 +866,26 @@ class LeRobotDataset(BaseDataset):
     # -- recording API (v2.1) ---------------------------------------------------------------------------
     @classmethod
     def create(cls, repo_id: str, fps: int, root: str | Path | None = None, robot_type: str | None = None,
-               features: dict | None = None, use_videos: bool = False, image_writer_threads: int = 0) -> "LeRobotRecorder":
+               features: dict | None = None, use_videos: bool = False, image_writer_threads: int = 0,
+               deferred_video_keys: set[str] | list[str] | None = None) -> "LeRobotRecorder":
+        """``deferred_video_keys``: video features whose frames are NOT handed to ``add_frame``; their files are
+        attached after ``save_episode`` from recordings made elsewhere (``LeRobotRecorder.attach_video``)."""
         meta = LeRobotDatasetMetadata.create(repo_id, fps, root, robot_type, features, use_videos)
-        return LeRobotRecorder(meta, image_writer_threads)
+        return LeRobotRecorder(meta, image_writer_threads, deferred_video_keys)
 
 
 class LeRobotRecorder:
     """Frame-by-frame recording into the v2.1 layout: ``add_frame`` buffers, ``save_episode`` writes the parquet file,
     images or encoded videos, per-episode stats and the metadata records."""
 
-    def __init__(self, meta: LeRobotDatasetMetadata, image_writer_threads: int = 0):
+    def __init__(self, meta: LeRobotDatasetMetadata, image_writer_threads: int = 0,
+                 deferred_video_keys: set[str] | list[str] | None = None):
         self.meta, self.root, self.fps = meta, meta.root, meta.fps
         self.features = meta.features
+        self.deferred_video_keys = set(deferred_video_keys or ())
+        unknown = self.deferred_video_keys - set(meta.video_keys)
+        if unknown:
+            raise ValueError(f"deferred_video_keys {sorted(unknown)} are not video features ({meta.video_keys})")
         self.image_writer = None
         if image_writer_threads > 0:
             from .image_writer import AsyncImageWriter
@@ -880,7 +901,10 @@ class LeRobotRecorder:
 
     def add_frame(self, frame: dict) -> None:
         frame = {k: (v.numpy() if isinstance(v, Tensor) else v) for k, v in frame.items()}
-        validate_frame(frame, self.features)
+        given = self.deferred_video_keys & set(frame)
+        if given:
+            raise ValueError(f"{sorted(given)} are deferred video keys: their frames come from attach_video, not add_frame")
+        validate_frame(frame, {k: v for k, v in self.features.items() if k not in self.deferred_video_keys})
         buf = self.episode_buffer
         fi = buf["size"]
         buf["frame_index"].append(fi)
@@ -922,6 +946,8 @@ class LeRobotRecorder:
                 arr = np.full(n, ep)
             elif k == "task_index":
                 arr = np.asarray([self.meta.get_task_index(t) for t in tasks])
+            elif k in self.deferred_video_keys:
+                continue                                   # no frames here: attached later, no statistics yet
             elif ft["dtype"] in ("image", "video"):
                 paths = buf[k]
                 from PIL import Image
@@ -943,15 +969,58 @@ class LeRobotRecorder:
         path = self.root / self.meta.get_data_file_path(ep)
         path.parent.mkdir(parents=True, exist_ok=True)
         pq.write_table(pa.table(cols), path)
-        for k in self.meta.video_keys:
-            encode_video_frames(self._image_path(k, ep, 0).parent, self.root / self.meta.get_video_file_path(ep, k),
-                                self.fps, overwrite=True)
-        stats = compute_episode_stats(stats_in, self.features)
+        self.encode_episode_videos(ep, skip_keys=self.deferred_video_keys)
+        stats = compute_episode_stats(stats_in, {k: v for k, v in self.features.items() if k in stats_in})
         self.meta.save_episode(ep, n, list(dict.fromkeys(tasks)), stats)
         img_dir = self.root / "images"
         if img_dir.exists():
             shutil.rmtree(img_dir)
         self.episode_buffer = self.create_episode_buffer()
+
+    # -- videos -----------------------------------------------------------------------------------------------
+    def encode_episode_videos(self, episode_index: int, skip_keys: set[str] | None = None) -> dict[str, str]:
+        """Frames written as image files -> one mp4 per video feature; a file that already exists is kept (resuming a
+        recording).  Returns ``{video key: path}``."""
+        out = {}
+        for k in self.meta.video_keys:
+            if skip_keys and k in skip_keys:
+                continue
+            path = self.root / self.meta.get_video_file_path(episode_index, k)
+            out[k] = str(path)
+            if not path.is_file():
+                encode_video_frames(self._image_path(k, episode_index, 0).parent, path, self.fps, overwrite=True)
+        return out
+
+    def encode_videos(self) -> None:
+        for ep in range(self.meta.total_episodes):
+            self.encode_episode_videos(ep, skip_keys=self.deferred_video_keys)
+
+    def attach_video(self, episode_index: int, video_key: str, input_video_path: str | Path, overwrite: bool = False,
+                     start_time: float | None = None, **encode_kw) -> Path:
+        """Attaches a recording made elsewhere to a saved episode: the source is resampled to the dataset's fps and
+        trimmed to exactly the episode's number of frames (``start_time`` skips into the source) and lands at the
+        standard video path.  Call ``update_video_info`` once all deferred videos are in place."""
+        from .video_utils import resample_and_trim_video
+        if video_key not in self.meta.video_keys:
+            raise ValueError(f"'{video_key}' is not a video feature. Available video keys: {self.meta.video_keys}")
+        if episode_index not in self.meta.episodes:
+            raise ValueError(f"Episode {episode_index} does not exist. Total episodes: {self.meta.total_episodes}")
+        if not Path(input_video_path).is_file():
+            raise FileNotFoundError(input_video_path)
+        out = self.root / self.meta.get_video_file_path(episode_index, video_key)
+        if out.is_file() and not overwrite:
+            logging.info("video already exists at %s, skipping (use overwrite=True to replace)", out)
+            return out
+        n = int(self.meta.episodes[episode_index]["length"])
+        resample_and_trim_video(input_video_path, out, self.fps, n, overwrite=overwrite, start_time=start_time, **encode_kw)
+        logging.info("attached video for episode %d, key '%s': %s -> %s (%d frames @ %d fps)", episode_index, video_key,
+                     input_video_path, out, n, self.fps)
+        return out
+
+    def update_video_info(self) -> None:
+        """Writes the real video properties (from the first episode's files) into ``meta/info.json``."""
+        _update_video_info(self.meta)
+        write_json(_jsonable_info(self.meta.info), self.root / INFO_PATH)
 
     def clear_episode_buffer(self) -> None:
         img_dir = self.root / "images"

@@ -38,7 +38,8 @@ def _record(root, use_videos=False, episodes=(12, 9, 15), fps=10):
 def _cfg(root, **kw):
     mix = DatasetMixtureConfig(datasets=[DatasetConfig(repo_id="local/toy", root=str(root), **kw.pop("ds", {}))],
                                action_freq=10.0, **kw.pop("mix", {}))
-    return TrainPipelineConfig(dataset_mixture=mix, resolution=(56, 56), num_cams=2, action_chunk=5, batch_size=2,
+    kw.setdefault("num_cams", 2)
+    return TrainPipelineConfig(dataset_mixture=mix, resolution=(56, 56), action_chunk=5, batch_size=2,
                                dataloader_batch_size=2, **kw)
 
 
@@ -160,3 +161,117 @@ def test_push_to_hub_helpers(tmp_path):
         with pytest.raises(ValueError):
             check_repo_id(bad)
     assert isinstance(get_default_encoding(), dict)
+
+
+def test_selection_segments_memory_subgoals_and_optional_keys(tmp_path):
+    """Deny list and selected-episode statistics; segment tables from start frames; the memory of the next frame; subgoal
+    frame choice (end of segment, 4 s window, legacy look-ahead); every optional key always present with the documented
+    pad signals; history dropout; the validation copy shares data and differs only in its switches."""
+    from opentau_b200.datasets.lerobot_dataset import aggregate_selected_stats, resolve_selected_episodes
+    from opentau_b200.datasets.utils import EPISODES_PATH, load_jsonlines, write_jsonlines
+    _record(tmp_path / "toy", episodes=(12, 9, 15))
+    eps = load_jsonlines(tmp_path / "toy" / EPISODES_PATH)
+    eps[0]["segments"] = [0, 5, 9]
+    write_jsonlines(eps, tmp_path / "toy" / EPISODES_PATH)
+
+    assert resolve_selected_episodes(range(3), None, None) is None
+    assert resolve_selected_episodes(range(3), [2, 0], None) == [0, 2]
+    assert resolve_selected_episodes(range(3), [0, 1], [1]) == [0]                # the deny list wins
+    assert resolve_selected_episodes(range(3), None, [1]) == [0, 2]
+    with pytest.raises(ValueError, match="removed every episode"):
+        resolve_selected_episodes(range(3), [1], [1], "local/toy")
+    meta = LeRobotDatasetMetadata("local/toy", root=tmp_path / "toy")
+    full = meta.stats["observation.state"]["mean"].copy()
+    sel = aggregate_selected_stats(meta, None, [1])["observation.state"]["mean"]
+    np.testing.assert_allclose(sel, np.full(6, (np.arange(12).sum() + np.arange(21, 36).sum()) / 27.0), rtol=1e-6)
+    assert not np.allclose(sel, full) and aggregate_selected_stats(meta) is meta.stats
+
+    mixkw = dict(subgoal_drop_prob=0.0, subgoal_end_of_segment_prob=1.0, response_drop_prob=0.0,
+                 metadata_drop_all_prob=0.0, metadata_drop_each_prob=0.0, history_state_drop_prob=0.0, emit_fps=True)
+    cfg = _cfg(tmp_path / "toy", mix=mixkw, ds=dict(excluded_episodes=[1]))
+    ds = make_dataset(cfg.dataset_mixture.datasets[0], cfg)
+    assert ds.episodes == [0, 2] and len(ds) == 27
+    np.testing.assert_allclose(ds.meta.stats["observation.state"]["mean"], sel, rtol=1e-6)   # what the normaliser pools
+    assert ds.segment_starts_by_episode[0].tolist() == [0, 5, 9] and ds.segment_starts_by_episode[2].tolist() == [0]
+    assert [ds._lookup_segment_index(0, f) for f in (0, 4, 5, 8, 9, 11)] == [0, 0, 1, 1, 2, 2]
+    assert ds._segment_end_in_ep(0, 0) == 5 and ds._segment_end_in_ep(0, 2) == 12
+    assert ds._sample_subgoal_frame(0, 2, at_end_of_segment=True) == 4
+    assert all(6 <= ds._sample_subgoal_frame(0, 6, at_end_of_segment=False) <= 8 for _ in range(20))
+    assert ds._sample_subgoal_frame(2, 3, at_end_of_segment=True) == 14         # no annotation: 4 s ahead, clipped
+    ds.segment_memories_by_episode[0] = ["m0", "m1", "m2"]
+    assert ds._lookup_next_memory(0, 3) == "m0" and ds._lookup_next_memory(0, 4) == "m1"
+    assert ds._lookup_next_memory(0, 11) == "m2"
+    assert set(ds.speed_raw_by_episode.values()) == {50}                         # two tasks, too few episodes to rank
+    assert (tmp_path / "toy" / "meta" / "speed_percentiles.jsonl").exists()
+
+    s = ds[2]
+    for k in ("subgoal0", "subgoal1", "subgoal_is_pad", "memory", "next_memory", "speed", "speed_is_pad", "mistake",
+              "mistake_is_pad", "quality", "quality_is_pad", "robot_type", "control_mode", "fps", "fps_is_pad",
+              "obs_history_is_pad"):
+        assert k in s, k
+    # one camera of two is mapped, so the subgoals are padded as a whole (all-or-none) and zero-filled
+    assert bool(s["subgoal_is_pad"]) and float(s["subgoal0"].float().abs().sum()) == 0.0
+    assert int(s["speed"]) == 50 and not bool(s["speed_is_pad"]) and bool(s["quality_is_pad"]) and int(s["quality"]) == 0
+    assert s["robot_type"] == "toybot" and s["memory"] == "" and int(s["fps"]) == 10 and not bool(s["fps_is_pad"])
+
+    cfg1 = _cfg(tmp_path / "toy", mix=mixkw, num_cams=1)
+    ds1 = make_dataset(cfg1.dataset_mixture.datasets[0], cfg1)
+    s1 = ds1[2]
+    assert not bool(s1["subgoal_is_pad"]) and s1["subgoal0"].shape == (3, 56, 56)
+    assert abs(float(s1["subgoal0"].float()[0, 28, 28]) * 255 - 12) < 2          # frame 4 = last frame of segment 0
+    val = ds1.shallow_copy_with_dropout(enable_dropout=False, enable_prompt_substitution=False)
+    assert val._table is ds1._table and val.meta is ds1.meta and not val.enable_optional_key_dropout
+    assert ds1.enable_optional_key_dropout and ds1.enable_prompt_substitution
+    ds1.cfg.dataset_mixture.history_state_drop_prob = 1.0
+    assert bool(ds1[2]["obs_history_is_pad"].all()) and not bool(val[2]["obs_history_is_pad"].any())
+    ds1.cfg.dataset_mixture.subgoal_drop_prob = 1.0
+    assert bool(ds1[2]["subgoal_is_pad"]) and not bool(val[2]["subgoal_is_pad"])
+    with pytest.raises(AssertionError, match=r"\(3, H, W\)"):
+        ds1._assert_image_in_unit_range(torch.full((3, 4, 4), 1.5), name="x", expect_temporal=False)
+
+
+def test_deferred_videos_are_attached_after_recording(tmp_path):
+    """A video feature declared as deferred takes no frames in ``add_frame``; a clip recorded elsewhere is re-timed to
+    the dataset's rate, cut to the episode's length and placed at the standard path; the metadata then gets the real
+    video properties and the dataset reads the frames back."""
+    import cv2
+    feats = {**FEATURES, "observation.images.wrist": {"dtype": "video", "shape": (48, 64, 3), "names": ["h", "w", "c"]}}
+    rec = LeRobotDataset.create("local/toy", fps=10, root=tmp_path / "toy", robot_type="toybot", features=feats,
+                                use_videos=True, image_writer_threads=2, deferred_video_keys={"observation.images.wrist"})
+    with pytest.raises(ValueError, match="not video features"):
+        LeRobotDataset.create("local/x", fps=10, root=tmp_path / "x", features=feats, use_videos=True,
+                              deferred_video_keys={"nope"})
+    for t in range(8):
+        rec.add_frame({"observation.images.top": np.full((48, 64, 3), 10 * t, np.uint8),
+                       "observation.state": np.full(6, t, np.float32), "action": np.full(6, t, np.float32), "task": "go"})
+    with pytest.raises(ValueError, match="deferred video keys"):
+        rec.add_frame({"observation.images.top": np.zeros((48, 64, 3), np.uint8),
+                       "observation.images.wrist": np.zeros((48, 64, 3), np.uint8),
+                       "observation.state": np.zeros(6, np.float32), "action": np.zeros(6, np.float32), "task": "go"})
+    rec.clear_episode_buffer()
+    for t in range(8):
+        rec.add_frame({"observation.images.top": np.full((48, 64, 3), 10 * t, np.uint8),
+                       "observation.state": np.full(6, t, np.float32), "action": np.full(6, t, np.float32), "task": "go"})
+    rec.save_episode()
+    rec.stop_image_writer()
+    wrist = rec.root / rec.meta.get_video_file_path(0, "observation.images.wrist")
+    assert not wrist.exists() and (rec.root / rec.meta.get_video_file_path(0, "observation.images.top")).exists()
+    src = tmp_path / "clip.mp4"                               # 30 fps source, 40 frames, brightness = 5 * frame
+    wr = cv2.VideoWriter(str(src), cv2.VideoWriter_fourcc(*"mp4v"), 30, (64, 48))
+    for i in range(40):
+        wr.write(np.full((48, 64, 3), 5 * i, np.uint8))
+    wr.release()
+    with pytest.raises(ValueError, match="not a video feature"):
+        rec.attach_video(0, "observation.state", src)
+    with pytest.raises(ValueError, match="does not exist"):
+        rec.attach_video(3, "observation.images.wrist", src)
+    out = rec.attach_video(0, "observation.images.wrist", src)
+    assert out == wrist and wrist.exists() and rec.attach_video(0, "observation.images.wrist", src) == wrist
+    rec.update_video_info()
+    meta = LeRobotDatasetMetadata("local/toy", root=tmp_path / "toy")
+    info = meta.features["observation.images.wrist"]["info"]
+    assert info["video.height"] == 48 and info["video.width"] == 64 and round(info["video.fps"]) == 10
+    cap = cv2.VideoCapture(str(wrist))
+    assert int(cap.get(cv2.CAP_PROP_FRAME_COUNT)) == 8
+    cap.release()
+    assert rec.encode_episode_videos(0, skip_keys={"observation.images.wrist"}).keys() == {"observation.images.top"}
