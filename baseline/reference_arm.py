@@ -123,7 +123,7 @@ def run_train(args) -> int:
     """Prints the benchmark line for the reference's pi0.5 training step (or its ``unavailable`` line)."""
     if not os.path.isdir(os.path.join(REF_ROOT, "opentau")):
         return _unavailable("baseline/_ref holds no installed reference (pip install --target baseline/_ref "
-                            "/root/reference was not run on this machine)")
+                            "<reference checkout> was not run on this machine)")
     try:
         shims = _prepare_imports()
         import torch
@@ -385,7 +385,7 @@ def run_infer(args) -> int:
                             "published 1 x B200 figure instead, carried in vs_baseline)")
     if not os.path.isdir(os.path.join(REF_ROOT, "opentau")):
         return _unavailable("baseline/_ref holds no installed reference (pip install --target baseline/_ref "
-                            "/root/reference was not run on this machine)")
+                            "<reference checkout> was not run on this machine)")
     try:
         shims = _prepare_imports()
         import torch

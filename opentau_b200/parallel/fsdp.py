@@ -72,7 +72,7 @@ class _BackwardAcquire(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        ctx.gate.acquire(ctx.unit)
+        ctx.gate.acquire(ctx.unit, backward=True)
         return g, None, None
 
 
@@ -85,8 +85,14 @@ class ParamGate:
         self.e = engine
         self.by_layer: dict[tuple[int, int], list[int]] = {}      # (id(layer list owner) , layer) -> bucket indices
 
-    def acquire(self, bucket_index: int) -> None:
-        self.e._gather_bucket(bucket_index)
+    def acquire(self, bucket_index: int, backward: bool = False) -> None:
+        """Makes a unit resident for the kernels queued next on the current stream, then starts pulling the unit the
+        pass needs after it (the next layer of the same tower going forward, the previous one going backward) on the
+        engine's side stream, into the other slot of the pool, so that the pull runs under this layer's kernels."""
+        e = self.e
+        e._wait_prefetched(bucket_index)
+        e._gather_bucket(bucket_index)
+        e._prefetch_neighbour(bucket_index, -1 if backward else 1)
 
     def enter(self, layers: list[nn.Module]) -> list[int]:
         """Makes the units of the given layer modules resident; returns their bucket indices."""
@@ -134,6 +140,10 @@ class ShardedParamEngine(TrainEngine):
         self._slots: list[list[Tensor]] = []
         self._holds: list[list[int]] = []
         self._gathers = 0
+        self._pool_pos: dict[int, tuple[list[int], int]] = {}     # bucket -> (its pool's members in layer order, index)
+        self._pending: dict[int, "torch.cuda.Event"] = {}           # bucket -> its prefetch has been queued
+        self._prefetch_stream = (torch.cuda.Stream(device=dev) if dev.type == "cuda" and W > 1 and self.p2p is not None
+                                 else None)
         for gi, (g, sh) in enumerate(zip(store.groups, self.shards)):
             # at rest: this rank's slices of every bucket, back to back (same order / offsets as the fp32 shard)
             alloc = self.p2p.alloc_symmetric if self.p2p is not None else (
@@ -157,6 +167,8 @@ class ShardedParamEngine(TrainEngine):
                     holds.append(-1)
                 for j, i in enumerate(members):
                     self._slot_of[i] = (gi, base + (j % n_slots))
+                    if n_slots > 1:
+                        self._pool_pos[i] = (members, j)
             self._slots.append(slots)
             self._holds.append(holds)
             # parameters become views of their unit's slot; the replicated flat buffer goes away
@@ -204,6 +216,9 @@ class ShardedParamEngine(TrainEngine):
         gi, si = self._slot_of[index]
         if self._holds[gi][si] == index and not force:
             return
+        for other in [o for o in self._pending if o != index and self._slot_of[o] == (gi, si)]:
+            # an unconsumed prefetch of another unit into this slot: let it finish before the slot is rewritten
+            torch.cuda.current_stream().wait_event(self._pending.pop(other))
         b = self.store.buckets[index]
         sh, ps = self.shards[gi], self.pshard[gi]
         k = self.store.groups[gi].buckets.index(b)
@@ -234,12 +249,42 @@ class ShardedParamEngine(TrainEngine):
         self._holds[gi][si] = index
         self._gathers += 1
 
+    def _wait_prefetched(self, index: int) -> None:
+        ev = self._pending.pop(index, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def _prefetch_neighbour(self, index: int, step: int) -> None:
+        """Queues the pull of the unit ``step`` layers away in the same pool on the side stream.  Its slot holds the
+        unit on the other side of ``index``, whose last readers are already queued on the current stream: the side
+        stream waits for them first.  The consumer waits for the recorded event (``_wait_prefetched``)."""
+        if self._prefetch_stream is None or index not in self._pool_pos:
+            return
+        members, j = self._pool_pos[index]
+        if not 0 <= j + step < len(members):
+            return
+        nb = members[j + step]
+        gi, si = self._slot_of[nb]
+        if self._holds[gi][si] == nb or nb in self._pending:
+            return
+        side = self._prefetch_stream
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._gather_bucket(nb)
+            ev = torch.cuda.Event()
+            ev.record(side)
+        self._pending[nb] = ev
+
     def _gather_resident(self) -> None:
         for i, key in enumerate(self.store.bucket_keys):
             if key == "root":
                 self._gather_bucket(i, force=True)
 
     def _invalidate(self) -> None:
+        if self._pending:                                  # nothing may still be writing a slot that is re-gathered
+            for ev in self._pending.values():
+                torch.cuda.current_stream().wait_event(ev)
+            self._pending.clear()
         for holds in self._holds:
             for i in range(len(holds)):
                 holds[i] = -1
