@@ -129,6 +129,7 @@ class DualStreamDecoder(nn.Module):
         these ``(B, S_buf, Hkv, D)`` buffers at ``offset`` (behind a cached prefix, or at 0 when a cache is being
         filled) and attends over ``[:offset + T]`` in place: no concatenation, no copy."""
         towers = self.towers
+        xs = list(xs)                       # the forked norms below replace entries; the caller's list stays as it is
         qs, ks, vs, gates1, lens = [], [], [], [], []
         present = [(tower, x) for tower, x in zip(towers, xs) if x is not None]
         cos, sin = cos_sin
@@ -137,10 +138,15 @@ class DualStreamDecoder(nn.Module):
             if x is None:
                 continue
             layer: DecoderLayer = tower.layers[li]
+            # forked norms: the residual connection takes the norm's second output, so that the two gradients of the
+            # residual stream are summed inside the norm's backward kernel
+            fork = torch.is_grad_enabled()
             if mods[ti] is not None:
-                h, g1 = layer.input_layernorm(x, precomputed=mods[ti][2 * li])
+                h, g1, *xr = layer.input_layernorm(x, precomputed=mods[ti][2 * li], fork=fork)
             else:
-                h, g1 = layer.input_layernorm(x)
+                h, g1, *xr = layer.input_layernorm(x, fork=fork)
+            if xr:
+                xs[ti] = xr[0]
             gates1.append(g1), lens.append(x.shape[1])
             if fused_post:
                 # one kernel: split + qk-norm + rotation + K/V store (into the cache when there is room)
@@ -156,7 +162,7 @@ class DualStreamDecoder(nn.Module):
                 if kv_dst is not None:
                     k, v = kv_dst[0][:, :off + T], kv_dst[1][:, :off + T]
                 elif cache_k is not None:
-                    k, v = torch.cat([cache_k, new_k], dim=1), torch.cat([cache_v, new_v], dim=1)
+                    k, v = ops.seq_concat(cache_k, new_k), ops.seq_concat(cache_v, new_v)
                 else:
                     k, v = new_k, new_v
                 continue
@@ -170,8 +176,8 @@ class DualStreamDecoder(nn.Module):
             k = ops.rope(k, cos, sin)
             new_k, new_v = k, v
             if cache_k is not None:
-                k = torch.cat([cache_k, k], dim=1)
-                v = torch.cat([cache_v, v], dim=1)
+                k = ops.seq_concat(cache_k, k)
+                v = ops.seq_concat(cache_v, v)
         first = next(t for t, x in zip(towers, xs) if x is not None)
         if cp is not None:
             # the sequence is sharded over the ranks: q / k / v are this rank's slice, k_blk / k_valid cover all keys
@@ -197,7 +203,10 @@ class DualStreamDecoder(nn.Module):
                 if drop is not None:
                     o = drop(o)
                 y = x + layer.post_attention_layernorm(o)[0]
-                m = layer.mlp(layer.pre_feedforward_layernorm(y)[0])
+                n, _, *yr = layer.pre_feedforward_layernorm(y, fork=torch.is_grad_enabled())
+                if yr:
+                    y = yr[0]
+                m = layer.mlp(n)
                 if drop is not None:
                     m = drop(m)
                 outs.append(y + layer.post_feedforward_layernorm(m)[0])
@@ -209,10 +218,13 @@ class DualStreamDecoder(nn.Module):
                 y = ops.linear_gated_residual(a.to(op.weight.dtype), op.weight, op.bias, x, g1)
             else:
                 y = ops.dropout_gated_residual(x, layer.self_attn.o_proj(a), g1, drop.p, True)
+            fork = torch.is_grad_enabled()
             if mods[ti] is not None:
-                n, g2 = layer.post_attention_layernorm(y, precomputed=mods[ti][2 * li + 1])
+                n, g2, *yr = layer.post_attention_layernorm(y, precomputed=mods[ti][2 * li + 1], fork=fork)
             else:
-                n, g2 = layer.post_attention_layernorm(y)
+                n, g2, *yr = layer.post_attention_layernorm(y, fork=fork)
+            if yr:
+                y = yr[0]
             if g2 is None and drop is None:
                 outs.append(layer.mlp(n, residual=y))
             elif drop is None:

@@ -57,7 +57,12 @@ class RMSNorm(nn.Module):
         self.eps, self.unit_offset = eps, unit_offset
         self.weight = nn.Parameter(torch.zeros(dim) if unit_offset else torch.ones(dim))
 
-    def forward(self, x: Tensor, cond: Tensor | None = None) -> tuple[Tensor, None]:
+    def forward(self, x: Tensor, cond: Tensor | None = None, fork: bool = False):
+        """``(y, None)``; with ``fork`` ``(y, None, x_res)`` where ``x_res`` carries ``x`` to the residual connection
+        around this norm's branch (``ops.rms_norm_fork``)."""
+        if fork:
+            y, xr = ops.rms_norm_fork(x, self.weight, self.eps, self.unit_offset)
+            return y, None, xr
         return ops.rms_norm(x, self.weight, self.eps, self.unit_offset), None
 
 
@@ -73,11 +78,13 @@ class AdaRMSNorm(nn.Module):
         self.eps, self.dim = eps, dim
         self.dense = Linear(cond_dim, 3 * dim, bias=True, zero_init=True)
 
-    def forward(self, x: Tensor, cond: Tensor | None = None, precomputed: Tensor | None = None):
+    def forward(self, x: Tensor, cond: Tensor | None = None, precomputed: Tensor | None = None, fork: bool = False):
         if precomputed is None:
             if cond is None:
                 raise ValueError("AdaRMSNorm needs a condition")
             precomputed = self.dense(cond.to(self.dense.weight.dtype))
+        if fork:
+            return ops.ada_rms_norm_fork(x, precomputed, self.eps)
         return ops.ada_rms_norm(x, precomputed, self.eps)
 
 

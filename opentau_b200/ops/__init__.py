@@ -43,6 +43,24 @@ def ada_rms_norm(x: Tensor, mod: Tensor, eps: float = 1e-6):
     return fused.ada_rms_norm(x, mod, eps)
 
 
+def rms_norm_fork(x: Tensor, weight: Tensor | None, eps: float = 1e-6, unit_offset: bool = True):
+    """``(norm(x), x_res)``: use ``x_res`` (the same values as ``x``) for the residual connection around the normalised
+    branch, so that the backward adds the residual gradient inside the norm's backward kernel."""
+    import torch
+    if oracle_mode() or not (torch.is_grad_enabled() and x.requires_grad):
+        return rms_norm(x, weight, eps, unit_offset), x
+    return fused.rms_norm_fork(x, weight, eps, unit_offset)
+
+
+def ada_rms_norm_fork(x: Tensor, mod: Tensor, eps: float = 1e-6):
+    """Adaptive form of :func:`rms_norm_fork`: ``(y, gate, x_res)``."""
+    import torch
+    if oracle_mode() or not (torch.is_grad_enabled() and x.requires_grad):
+        y, gate = ada_rms_norm(x, mod, eps)
+        return y, gate, x
+    return fused.ada_rms_norm_fork(x, mod, eps)
+
+
 def layer_norm(x: Tensor, weight: Tensor, bias: Tensor, eps: float = 1e-6) -> Tensor:
     if oracle_mode():
         return ref.layer_norm(x, weight, bias, eps)
@@ -259,6 +277,19 @@ def embedding(table: Tensor, ids: Tensor, scale: float = 1.0, padding_idx: int |
     return out * scale if scale != 1.0 else out
 
 
+def seq_concat(a: Tensor, c: Tensor) -> Tensor:
+    """``cat([a, c], dim=1)``: cached keys / values followed by the new ones.  One copy kernel for dense bf16 rows on
+    the GPU, ``torch.cat`` otherwise."""
+    import torch
+    if a.is_cuda and not oracle_mode():
+        from . import cuda_ops
+        if cuda_ops.seq_concat_supported(a, c):
+            if torch.is_grad_enabled() and (a.requires_grad or c.requires_grad):
+                return fused.SeqConcatFn.apply(a, c)
+            return cuda_ops.seq_concat(a, c)
+    return torch.cat([a, c], dim=1)
+
+
 def linear_cross_entropy(h: Tensor, w: Tensor, bias: Tensor | None, labels: Tensor) -> Tensor:
     if oracle_mode():
         return ref.linear_cross_entropy(h, w, bias, labels)
@@ -276,5 +307,5 @@ __all__ = [
     "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "linear_gated_residual", "gated_mlp_gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
     "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
     "resize_with_pad", "dropout_gated_residual", "embedding", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
-    "apply_rope", "sinusoidal_time_embedding", "flow_interpolate", "euler_step", "patch_embed", "oracle_mode", "prims", "fused", "ref",
+    "apply_rope", "rms_norm_fork", "ada_rms_norm_fork", "seq_concat", "sinusoidal_time_embedding", "flow_interpolate", "euler_step", "patch_embed", "oracle_mode", "prims", "fused", "ref",
 ]

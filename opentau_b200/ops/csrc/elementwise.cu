@@ -119,8 +119,8 @@ __global__ void rms_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
                                const __nv_bfloat16* __restrict__ mod, long long mod_stride, int rows_per_mod,
                                const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                                float* __restrict__ dw_partial, __nv_bfloat16* __restrict__ dscale,
-                               __nv_bfloat16* __restrict__ dshift, long long rows, int H, int mode,
-                               int rows_per_block) {
+                               __nv_bfloat16* __restrict__ dshift, const __nv_bfloat16* __restrict__ dres,
+                               long long rows, int H, int mode, int rows_per_block) {
   __shared__ float red[32];
   const int nvec = H >> 3;
   float dwacc[MAXV][8];
@@ -180,6 +180,12 @@ __global__ void rms_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
         float o[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = (g[i][e] - xh[i][e] * dot) * rstd;
+        if (dres) {   // the gradient that reached x through the residual branch: summed here, not by a separate add
+          float rr[8];
+          load8(dres + row * (long long)H + idx * 8, rr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += rr[e];
+        }
         store8(dx + row * (long long)H + idx * 8, o);
       }
     }
@@ -916,13 +922,13 @@ extern "C" int otb_rms_fwd(const void* x, long long x_stride, const void* w, con
 // dw_partial must hold nblocks*H floats where nblocks = ceil(rows / rows_per_block).
 extern "C" int otb_rms_bwd(const void* dy, const void* x, long long x_stride, const void* w, const void* mod,
                            long long mod_stride, int rows_per_mod, const float* rstd, void* dx, float* dw_partial,
-                           void* dscale, void* dshift, long long rows, int H, int mode, int rows_per_block,
-                           cudaStream_t stream) {
+                           void* dscale, void* dshift, const void* dres, long long rows, int H, int mode,
+                           int rows_per_block, cudaStream_t stream) {
   if (H % 8 || rows <= 0 || rows_per_block <= 0) return -1;
   dim3 grid((unsigned)((rows + rows_per_block - 1) / rows_per_block));
   LAUNCH_BY_H(rms_bwd_kernel, H, (const bf16*)dy, (const bf16*)x, x_stride, (const bf16*)w, (const bf16*)mod,
               mod_stride, rows_per_mod < 1 ? 1 : rows_per_mod, rstd, (bf16*)dx, dw_partial, (bf16*)dscale,
-              (bf16*)dshift, rows, H, mode, rows_per_block);
+              (bf16*)dshift, (const bf16*)dres, rows, H, mode, rows_per_block);
   return (int)cudaGetLastError();
 }
 

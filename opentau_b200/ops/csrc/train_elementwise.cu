@@ -332,6 +332,23 @@ __global__ void embed_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const l
   }
 }
 
+// out[b, s, :] = s < S1 ? a[b, s, :] : c[b, s - S1, :] for rows of E two-byte elements (E a multiple of 8, 16-byte
+// aligned rows): the sequence concatenation of cached and new keys / values.  One 16-byte piece per thread.
+__global__ void seq_concat_kernel(const uint4* __restrict__ a, long long a_sb, long long a_ss, const uint4* __restrict__ c,
+                                  long long c_sb, long long c_ss, uint4* __restrict__ out, long long B, int S1, int S2,
+                                  int vec) {
+  const long long total = B * (long long)(S1 + S2) * vec;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total;
+       t += (long long)gridDim.x * blockDim.x) {
+    const int v = int(t % vec);
+    const long long row = t / vec;
+    const int s = int(row % (S1 + S2));
+    const long long b = row / (S1 + S2);
+    out[t] = s < S1 ? a[b * a_sb + (long long)s * a_ss + v] : c[b * c_sb + (long long)(s - S1) * c_ss + v];
+  }
+}
+
+
 }  // namespace otb
 
 using namespace otb;
@@ -426,5 +443,21 @@ extern "C" int otb_embed_bwd(const void* dout, const long long* sorted_ids, cons
     embed_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout), sorted_ids,
                                                               order, n_tok, static_cast<__nv_bfloat16*>(grad), H,
                                                               vocab, pad_id, scale);
+  return (int)cudaGetLastError();
+}
+
+// a: (B, S1, E), c: (B, S2, E) with batch / row strides in ELEMENTS (multiples of 8), innermost contiguous; out: (B, S1 + S2, E)
+// contiguous.  Two-byte elements.
+extern "C" int otb_seq_concat(const void* a, long long a_sb, long long a_ss, const void* c, long long c_sb, long long c_ss,
+                              void* out, long long B, int S1, int S2, int E, cudaStream_t stream) {
+  if (B <= 0 || S1 < 0 || S2 < 0 || S1 + S2 <= 0 || E <= 0 || E % 8) return -2;
+  if ((a_sb | a_ss | c_sb | c_ss) % 8) return -3;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(out)) & 15) return -4;
+  const int vec = E / 8;
+  const long long total = B * (long long)(S1 + S2) * vec;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  seq_concat_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(a), a_sb / 8, a_ss / 8,
+                                                static_cast<const uint4*>(c), c_sb / 8, c_ss / 8,
+                                                static_cast<uint4*>(out), B, S1, S2, vec);
   return (int)cudaGetLastError();
 }

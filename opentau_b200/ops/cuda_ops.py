@@ -205,7 +205,15 @@ def _bwd_blocks(R: int) -> tuple[int, int]:
     return rpb, (R + rpb - 1) // rpb
 
 
-def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: bool):
+def _dres_rows(dres: Tensor | None, R: int, H: int) -> Tensor | None:
+    if dres is None:
+        return None
+    d = dres.reshape(R, H)
+    return d if d.is_contiguous() else d.contiguous()
+
+
+def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: bool, dres: Tensor | None = None):
+    """``dres``: a gradient of the same shape as ``x`` that is added to ``dx`` inside the kernel."""
     global launch_count
     x2, R, H = _rows(x)
     dy2, _, _ = _rows(dy)
@@ -217,8 +225,9 @@ def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: 
     partial = torch.empty(nb, H, dtype=torch.float32, device=x.device) if w is not None else None
     wt = w.to(torch.bfloat16).contiguous() if w is not None else None
     lib = _lib.load("elementwise")
+    dr = _dres_rows(dres, R, H)
     _check(lib.otb_rms_bwd(_p(dy2), _p(x2), c_longlong(x2.stride(0)), _p(wt), c_void_p(0), c_longlong(0), c_int(1),
-                           _p(rstd), _p(dx), _p(partial), c_void_p(0), c_void_p(0), c_longlong(R), c_int(H),
+                           _p(rstd), _p(dx), _p(partial), c_void_p(0), c_void_p(0), _p(dr), c_longlong(R), c_int(H),
                            c_int(mode), c_int(rpb), _stream()), "rms_bwd")
     launch_count += 1
     dw = None
@@ -248,7 +257,7 @@ def ada_rms_fwd(x: Tensor, mod: Tensor, eps: float):
     return y.view(x.shape), rstd
 
 
-def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor):
+def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor, dres: Tensor | None = None):
     global launch_count
     B, S, H = x.shape
     x2, R, _ = _rows(x)
@@ -262,8 +271,8 @@ def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor):
     dshift = torch.empty(R, H, dtype=x.dtype, device=x.device)
     _check(_lib.load("elementwise").otb_rms_bwd(_p(dy2), _p(x2), c_longlong(x2.stride(0)), c_void_p(0), _p(mod2),
                                                 c_longlong(mod2.stride(0)), c_int(rows_per_mod), _p(rstd), _p(dx),
-                                                c_void_p(0), _p(dscale), _p(dshift), c_longlong(R), c_int(H), c_int(0),
-                                                c_int(1), _stream()), "ada_rms_bwd")
+                                                c_void_p(0), _p(dscale), _p(dshift), _p(_dres_rows(dres, R, H)),
+                                                c_longlong(R), c_int(H), c_int(0), c_int(1), _stream()), "ada_rms_bwd")
     launch_count += 1
     dscale, dshift = dscale.view(B, S, H), dshift.view(B, S, H)
     if mod.dim() == 2:
@@ -722,3 +731,34 @@ def pos_resample(table: Tensor, gh: int, gw: int) -> Tensor:
                                                            c_int(gw), _stream()), "pos_resample")
     launch_count += 1
     return out
+
+
+def seq_concat(a: Tensor, c: Tensor) -> Tensor:
+    """``cat([a, c], dim=1)`` for bf16 ``(B, S, ...)`` tensors whose trailing dims are dense: one vectorised copy kernel
+    (the library's batched concatenation moves these shapes at a tenth of the copy bandwidth)."""
+    global launch_count
+    B, S1, S2 = a.shape[0], a.shape[1], c.shape[1]
+    E = a[0, 0].numel() if S1 else c[0, 0].numel()
+    out = torch.empty(B, S1 + S2, *a.shape[2:], dtype=a.dtype, device=a.device)
+    _check(_lib.load("train_elementwise").otb_seq_concat(
+        _p(a), c_longlong(a.stride(0)), c_longlong(a.stride(1)), _p(c), c_longlong(c.stride(0)), c_longlong(c.stride(1)),
+        _p(out), c_longlong(B), c_int(S1), c_int(S2), c_int(E), _stream()), "seq_concat")
+    launch_count += 1
+    return out
+
+
+def seq_concat_supported(a: Tensor, c: Tensor) -> bool:
+    if not (a.is_cuda and a.dtype == c.dtype == torch.bfloat16 and a.dim() == c.dim() >= 3):
+        return False
+    if a.shape[0] != c.shape[0] or a.shape[2:] != c.shape[2:] or a.shape[1] == 0 or c.shape[1] == 0:
+        return False
+    E = a[0, 0].numel()
+
+    def rows_dense(t: Tensor) -> bool:
+        exp = 1
+        for size, stride in zip(reversed(t.shape[2:]), reversed(t.stride()[2:])):
+            if size != 1 and stride != exp:
+                return False
+            exp *= size
+        return t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
+    return E % 8 == 0 and rows_dense(a) and rows_dense(c)

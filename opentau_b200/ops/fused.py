@@ -151,6 +151,34 @@ def rms_norm(x, w, eps=1e-6, unit_offset=True):
     return RMSNormFn.apply(x, w, eps, unit_offset)
 
 
+class RMSNormForkFn(torch.autograd.Function):
+    """``x -> (norm(x), x)``: the second output is ``x`` itself, to be used by the residual connection around the
+    normalised branch.  The two gradients that reach ``x`` (through the norm and through the residual) then arrive at
+    ONE backward, which adds the residual gradient inside the norm's backward kernel instead of leaving the sum to a
+    separate element-wise launch over the whole residual stream."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps, unit_offset):
+        y, rstd = prims.rms_fwd(x, w, eps, unit_offset)
+        ctx.save_for_backward(x, w if w is not None else x.new_empty(0), rstd)
+        ctx.has_w, ctx.unit_offset, ctx.wref = w is not None, unit_offset, w
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, w, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None, None
+        dx, dw = prims.rms_bwd(dy.contiguous(), x, w if ctx.has_w else None, rstd, ctx.unit_offset, dres)
+        if dw is not None:
+            dw = _sink_vec(ctx.wref, dw) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None
+
+
+def rms_norm_fork(x, w, eps=1e-6, unit_offset=True):
+    return RMSNormForkFn.apply(x, w, eps, unit_offset)
+
+
 class AdaRMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, mod, eps):
@@ -176,6 +204,37 @@ class AdaRMSNormFn(torch.autograd.Function):
 
 def ada_rms_norm(x, mod, eps=1e-6):
     return AdaRMSNormFn.apply(x, mod, eps)
+
+
+class AdaRMSNormForkFn(torch.autograd.Function):
+    """Adaptive form of :class:`RMSNormForkFn`: ``x, mod -> (y, gate, x)``."""
+
+    @staticmethod
+    def forward(ctx, x, mod, eps):
+        y, rstd = prims.ada_rms_fwd(x, mod, eps)
+        ctx.save_for_backward(x, mod, rstd)
+        H = x.shape[-1]
+        gate = mod[..., 2 * H:]
+        if gate.dim() == 2:
+            gate = gate[:, None, :]
+        return y, gate, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dgate, dres):
+        x, mod, rstd = ctx.saved_tensors
+        if dy is None:
+            dy = torch.zeros_like(x)
+        dx, dscale, dshift = prims.ada_rms_bwd(dy.contiguous(), x, mod, rstd, dres)
+        if dgate is None:
+            dgate = torch.zeros_like(dscale)
+        elif mod.dim() == 2:
+            dgate = dgate.reshape(mod.shape[0], -1, dscale.shape[-1]).sum(1) if dgate.dim() == 3 else dgate
+        dmod = torch.cat([dscale, dshift, dgate.to(dscale.dtype)], dim=-1)
+        return dx, dmod, None
+
+
+def ada_rms_norm_fork(x, mod, eps=1e-6):
+    return AdaRMSNormForkFn.apply(x, mod, eps)
 
 
 class LayerNormFn(torch.autograd.Function):
@@ -378,3 +437,19 @@ class EmbeddingFn(torch.autograd.Function):
 
 def embedding(table, ids, scale: float = 1.0, padding_idx=None):
     return EmbeddingFn.apply(table, ids, scale, padding_idx)
+
+
+class SeqConcatFn(torch.autograd.Function):
+    """``cat([a, c], dim=1)`` with the copy done by one kernel; the gradients are the two slices of the incoming
+    gradient (views: nothing is copied in the backward)."""
+
+    @staticmethod
+    def forward(ctx, a: Tensor, c: Tensor) -> Tensor:
+        from . import cuda_ops
+        ctx.s1 = a.shape[1]
+        return cuda_ops.seq_concat(a, c)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return (g[:, :ctx.s1] if ctx.needs_input_grad[0] else None,
+                g[:, ctx.s1:] if ctx.needs_input_grad[1] else None)

@@ -111,10 +111,15 @@ def rms_fwd(x: Tensor, w: Tensor | None, eps: float, unit_offset: bool) -> tuple
     return y.to(x.dtype), rstd.reshape(-1)
 
 
-def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: bool) -> tuple[Tensor, Tensor | None]:
+def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: bool,
+            dres: Tensor | None = None) -> tuple[Tensor, Tensor | None]:
+    """``dres``: the gradient that reached ``x`` through a residual branch; it is added to ``dx`` (inside the kernel on
+    the GPU)."""
     if _cuda(x):
         from . import cuda_ops
-        return cuda_ops.rms_bwd(dy, x, w, rstd, unit_offset)
+        if dres is not None and dres.dtype != x.dtype:
+            dres = dres.to(x.dtype)
+        return cuda_ops.rms_bwd(dy, x, w, rstd, unit_offset, dres)
     H = x.shape[-1]
     xf = x.float().reshape(-1, H)
     dyf = dy.float().reshape(-1, H)
@@ -127,6 +132,8 @@ def rms_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor, unit_offset: 
         dw = None
         g = dyf
     dx = (g - xhat * (g * xhat).mean(-1, keepdim=True)) * rstd[:, None]
+    if dres is not None:
+        dx = dx + dres.float().reshape(-1, H)
     return dx.reshape(x.shape).to(x.dtype), dw
 
 
@@ -140,11 +147,15 @@ def ada_rms_fwd(x: Tensor, mod: Tensor, eps: float) -> tuple[Tensor, Tensor]:
     return y, rstd
 
 
-def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor) -> tuple[Tensor, Tensor, Tensor]:
-    """Returns ``(dx, dscale, dshift)`` with dscale/dshift shaped like the matching ``mod`` chunk."""
+def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor,
+                dres: Tensor | None = None) -> tuple[Tensor, Tensor, Tensor]:
+    """Returns ``(dx, dscale, dshift)`` with dscale/dshift shaped like the matching ``mod`` chunk; ``dres`` as in
+    :func:`rms_bwd`."""
     if _cuda(x):
         from . import cuda_ops
-        return cuda_ops.ada_rms_bwd(dy, x, mod, rstd)
+        if dres is not None and dres.dtype != x.dtype:
+            dres = dres.to(x.dtype)
+        return cuda_ops.ada_rms_bwd(dy, x, mod, rstd, dres)
     B, S, H = x.shape
     m = mod if mod.dim() == 3 else mod[:, None, :]
     scale = m[..., :H].float()
@@ -152,6 +163,8 @@ def ada_rms_bwd(dy: Tensor, x: Tensor, mod: Tensor, rstd: Tensor) -> tuple[Tenso
     xhat = xf * rstd.view(B, S, 1)
     g = dyf * (1.0 + scale)
     dx = (g - xhat * (g * xhat).mean(-1, keepdim=True)) * rstd.view(B, S, 1)
+    if dres is not None:
+        dx = dx + dres.float()
     dscale = dyf * xhat
     dshift = dyf
     if mod.dim() == 2:

@@ -483,3 +483,30 @@ def test_cta_pair_gemm_glu_epilogues(act, dev):
     torch.testing.assert_close(gu.float(), gu1.float(), rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(h.float(), h1.float(), rtol=1e-2, atol=1e-2)
     cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("H", [1024, 2048, 2560])
+def test_norm_backward_adds_the_residual_gradient_in_the_kernel(H):
+    """``rms_bwd`` / ``ada_rms_bwd`` with ``dres``: dx equals the kernel's dx without it plus ``dres`` (bf16), for the
+    weighted, the weightless and the adaptive form; the weight / modulation gradients are unchanged."""
+    from opentau_b200.ops import cuda_ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(H)
+    B, S = 3, 37
+    x = torch.randn(B, S, H, device=dev, generator=g).to(torch.bfloat16)
+    dy = torch.randn(B, S, H, device=dev, generator=g).to(torch.bfloat16)
+    dres = torch.randn(B, S, H, device=dev, generator=g).to(torch.bfloat16)
+    w = (0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+    mod = (0.1 * torch.randn(B, 3 * H, device=dev, generator=g)).to(torch.bfloat16)
+    _, rstd = cuda_ops.rms_fwd(x, w, 1e-6, True)
+    for wt in (w, None):
+        dx0, dw0 = cuda_ops.rms_bwd(dy, x, wt, rstd, True)
+        dx1, dw1 = cuda_ops.rms_bwd(dy, x, wt, rstd, True, dres)
+        torch.testing.assert_close(dx1.float(), dx0.float() + dres.float(), rtol=1e-2, atol=2e-2)
+        if wt is not None:
+            assert torch.equal(dw0, dw1)
+    _, rstd_a = cuda_ops.ada_rms_fwd(x, mod, 1e-6)
+    a0 = cuda_ops.ada_rms_bwd(dy, x, mod, rstd_a)
+    a1 = cuda_ops.ada_rms_bwd(dy, x, mod, rstd_a, dres)
+    torch.testing.assert_close(a1[0].float(), a0[0].float() + dres.float(), rtol=1e-2, atol=2e-2)
+    assert torch.equal(a0[1], a1[1]) and torch.equal(a0[2], a1[2])

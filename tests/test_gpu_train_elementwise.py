@@ -199,3 +199,25 @@ def test_stss_window_correlation_kernels_match_the_dense_evaluation(dtype, B, T,
     torch.testing.assert_close(out.float().cpu(), ref.detach(), **tol)
     gtol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=0.15)
     torch.testing.assert_close(xg.grad.float().cpu(), xc.grad, **gtol)
+
+
+def test_seq_concat_kernel_matches_cat_forward_and_backward(dev):
+    """Cached keys followed by new keys: a layer view of a (L, B, S, H, D) cache with spare room (strided batch) and a
+    strided slice of a fused projection, against ``torch.cat``; gradients are the slices of the incoming gradient."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import cuda_ops
+    torch.manual_seed(0)
+    cache = torch.randn(3, 4, 40, 2, 64, device=dev).to(torch.bfloat16)
+    a = cache[1][:, :33]                                         # (4, 33, 2, 64): batch stride 40 * 128
+    fused_qkv = torch.randn(4, 7, 6, 64, device=dev).to(torch.bfloat16)
+    c = fused_qkv[:, :, 4:].detach().requires_grad_(True)        # (4, 7, 2, 64): row stride 6 * 64
+    assert cuda_ops.seq_concat_supported(a, c)
+    out = ops.seq_concat(a, c)
+    ref = torch.cat([a, c.detach()], dim=1)
+    assert out.shape == (4, 40, 2, 64) and torch.equal(out, ref)
+    w = torch.randn_like(out)
+    (out.float() * w.float()).sum().backward()
+    torch.testing.assert_close(c.grad.float(), w[:, 33:].float())
+    odd = torch.randn(4, 7, 2, 60, device=dev).to(torch.bfloat16)   # 120 elements per row: not a multiple of 8 -> cat
+    assert not cuda_ops.seq_concat_supported(odd, odd) and ops.seq_concat(odd, odd).shape == (4, 14, 2, 60)
+    assert torch.equal(ops.seq_concat(a.float().cpu(), c.detach().float().cpu()), ref.float().cpu())

@@ -210,3 +210,42 @@ def test_resize_with_pad_semantics():
     assert out.shape == (1, 3, 224, 224)
     assert torch.all(out[:, :, :112, :] == 0)      # padding is on the top
     assert out[:, :, 112:, :].abs().sum() > 0
+
+
+def test_forked_norms_give_the_gradients_of_norm_plus_residual():
+    """``rms_norm_fork`` / ``ada_rms_norm_fork``: same values as the plain norms, and the gradient of x through
+    (branch on the norm) + (residual on the second output) equals the plain two-path graph, including when only one of
+    the two outputs is used."""
+    import torch
+
+    from opentau_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(2, 5, 16, requires_grad=True)
+    w = torch.randn(16, requires_grad=True)
+    mod = torch.randn(2, 48, requires_grad=True)
+    lin = torch.randn(16, 16)
+
+    def plain():
+        h = ops.rms_norm(x, w, 1e-6, True)
+        y = x + h @ lin
+        h2, gate = ops.ada_rms_norm(y, mod, 1e-6)
+        return (y + gate * (h2 @ lin)).square().sum()
+
+    def forked():
+        h, xr = ops.rms_norm_fork(x, w, 1e-6, True)
+        y = xr + h @ lin
+        h2, gate, yr = ops.ada_rms_norm_fork(y, mod, 1e-6)
+        return (yr + gate * (h2 @ lin)).square().sum()
+
+    ga = torch.autograd.grad(plain(), (x, w, mod))
+    gb = torch.autograd.grad(forked(), (x, w, mod))
+    for a, b in zip(ga, gb):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(plain(), forked())
+    h, xr = ops.rms_norm_fork(x, w)
+    torch.testing.assert_close(torch.autograd.grad(xr.sum(), x)[0], torch.ones_like(x))      # residual path alone
+    h, xr = ops.rms_norm_fork(x, w)
+    torch.testing.assert_close(torch.autograd.grad(h.sum(), x)[0], torch.autograd.grad(ops.rms_norm(x, w).sum(), x)[0])
+    with torch.no_grad():
+        h, xr = ops.rms_norm_fork(x, w)
+        assert xr is x                                                                       # nothing to fork
