@@ -388,13 +388,15 @@ def eval_policy_on_config(policy, cfg: TrainPipelineConfig, device, rank: int = 
     ev = cfg.eval
     render: dict[str, Any] = {}
     if videos_dir is not None and ev.max_episodes_rendered > 0:
-        render.update(max_episodes_rendered=ev.max_episodes_rendered, videos_dir=videos_dir, grid_size=ev.grid_size)
+        render.update(max_episodes_rendered=ev.max_episodes_rendered, videos_dir=videos_dir, grid_size=ev.grid_size,
+                      keep_per_episode_videos=ev.keep_per_episode_videos, video_frame_stride=ev.video_frame_stride)
     if ev.goal_frames_dir:
         render["goal_frames_dir"] = ev.goal_frames_dir
     envs = make_envs(env_cfg, n_envs=ev.batch_size, use_async_envs=ev.use_async_envs)
     was_training = policy.training
     try:
-        seed = None if ev.seed is None else ev.seed + _rank_seed_offset(rank, ev.decorrelate_rank_seeds)
+        base = ev.seed if ev.seed is not None else cfg.seed          # the pipeline seed is the fallback
+        seed = None if base is None else base + _rank_seed_offset(rank, ev.decorrelate_rank_seeds)
         mine = eval_policy_all(envs, policy, ev.n_episodes, seed, cfg, device, rank, world, ev.seed_list,
                                render or None)
     finally:

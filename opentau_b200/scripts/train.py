@@ -74,7 +74,7 @@ def to_device(batch: dict[str, Any], device: torch.device) -> dict[str, Any]:
 class WandBLogger:
     """Thin tracker: wandb when enabled and importable (offline mode works without network), else a JSONL file."""
 
-    def __init__(self, cfg: TrainPipelineConfig, out_dir: Path, is_main: bool):
+    def __init__(self, cfg: TrainPipelineConfig, out_dir: Path, is_main: bool, resume_step: int | None = None):
         self.run = None
         self.file = None
         if not is_main:
@@ -85,10 +85,10 @@ class WandBLogger:
             try:
                 import wandb
                 os.environ.setdefault("WANDB_MODE", getattr(w, "mode", None) or "offline")
-                self.run = wandb.init(project=getattr(w, "project", None) or "opentau", entity=getattr(w, "entity", None),
-                                      name=getattr(w, "name", None) or out_dir.name, dir=str(out_dir),
-                                      config=cfg.to_dict(), resume="allow" if cfg.resume else None,
-                                      id=getattr(w, "run_id", None))
+                # a resumed run forks from (or continues) its parent as `wandb.on_resume` says
+                kw = w.to_wandb_kwargs(step=resume_step if cfg.resume else None)
+                kw["name"] = kw.get("name") or out_dir.name
+                self.run = wandb.init(project=w.project or "opentau", dir=str(out_dir), config=cfg.to_dict(), **kw)
             except Exception as e:  # noqa: BLE001 - logging must never stop a run
                 logging.warning("wandb disabled: %s", e)
 
@@ -195,7 +195,11 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
     control.wait_for_everyone()
     if cfg.seed is not None:
         set_seed(cfg.seed, rank)
-    tracker_wb = WandBLogger(cfg, out_dir, is_main)
+    resume_step = None
+    if cfg.resume and (out_dir / CHECKPOINTS_DIR / LAST_LINK / "training_step.json").exists():
+        from ..utils.train_utils import load_training_step
+        resume_step = load_training_step((out_dir / CHECKPOINTS_DIR / LAST_LINK).resolve())
+    tracker_wb = WandBLogger(cfg, out_dir, is_main, resume_step)
 
     # ---- data
     res = make_dataset_mixture(cfg)

@@ -254,3 +254,55 @@ def test_policy_config_loads_from_pipeline_files_strips_retired_fields_and_warns
     (tmp_path / "own.json").write_text(json.dumps({"policy": {"init_strategy": "x", "a": 1}, "action_decoder_latency_std": 1}))
     P.strip_deprecated_fields_from_json(tmp_path / "own.json")
     assert json.loads((tmp_path / "own.json").read_text()) == {"policy": {"a": 1}}
+
+
+def test_dataset_wandb_and_eval_config_rules():
+    """The per-dataset index / delta-action rules (JSON string keys coerced), the W&B resume policy and its init
+    keywords, and the evaluation video / seed fields."""
+    import pytest
+
+    from opentau_b200.configs.default import DatasetConfig, DatasetMixtureConfig, EvalConfig, WandBConfig
+    d = DatasetConfig(repo_id="a/b", use_delta_joint_actions=True, delta_action_state_map={"0": 0, "2": "1"})
+    assert d.delta_action_state_map == {0: 0, 2: 1}
+    for kw, msg in ((dict(delta_action_state_map={0: 0}), "silently ignored"),
+                    (dict(use_delta_joint_actions=True), "requires a non-empty"),
+                    (dict(use_delta_joint_actions=True, delta_action_state_map={"x": 0}), "must map int"),
+                    (dict(use_delta_joint_actions=True, delta_action_state_map={0: -1}), "non-negative"),
+                    (dict(state_index=[0, 1, 1]), r"duplicate indices \[1\]"),
+                    (dict(action_index=[]), "non-empty list"),
+                    (dict(action_index=[True, 2]), "non-negative ints"),
+                    (dict(prompt_substitutions={"t": []}), "non-empty list"),
+                    (dict(prompt_substitutions={"t": ["ok", ""]}), "empty or non-string"),
+                    (dict(prompt_substitutions={"$ref": ["x"]}), "file include"),
+                    (dict(val_split_ratio=1.5), r"\[0, 1\]"), (dict(tolerance_s=-1.0), ">= 0")):
+        with pytest.raises(ValueError, match=msg):
+            DatasetConfig(repo_id="a/b", **kw)
+    with pytest.raises(ValueError, match="only applies to LeRobot"):
+        DatasetConfig(vqa="dummy", state_index=[0])
+    with pytest.raises(ValueError, match="only applies to LeRobot"):
+        DatasetConfig(vqa="dummy", prompt_substitutions={"t": ["u"]})
+    for kw, msg in ((dict(n_obs_history=0), "positive integer"), (dict(delta_stats_max_rows=True), "positive integer"),
+                    (dict(tolerance_s=-1e-3), ">= 0"), (dict(action_freq=0.0), "positive")):
+        with pytest.raises(ValueError, match=msg):
+            DatasetMixtureConfig(**kw)
+    assert DatasetMixtureConfig().action_freq is None
+
+    w = WandBConfig(run_id="abc", notes="n")
+    assert w.to_wandb_kwargs(step=None).get("fork_from") is None
+    kw = w.to_wandb_kwargs(step=40)
+    assert kw["fork_from"] == "abc?_step=40" and kw["notes"].endswith("Forked from run abc at step 40.") and "id" not in kw
+    kw = WandBConfig(run_id="abc", on_resume="continue").to_wandb_kwargs(step=40)
+    assert kw["id"] == "abc" and kw["resume"] == "allow" and "fork_from" not in kw
+    kw = WandBConfig(run_id="abc", mode="offline").to_wandb_kwargs(step=40)
+    assert "fork_from" not in kw and "would fork from run abc" in kw["notes"]
+    with pytest.warns(FutureWarning, match="deprecated"):
+        assert WandBConfig(allow_resume=True).on_resume == "continue"
+    with pytest.raises(ValueError, match="on_resume"):
+        WandBConfig(on_resume="restart")
+
+    e = EvalConfig(seed_list="3, 5,8", n_episodes=16, batch_size=16)
+    assert e.seed_list == [3, 5, 8] and e.n_episodes == 3 and e.batch_size == 3 and e.decorrelate_rank_seeds is False
+    for kw, msg in ((dict(video_crf=60), "video_crf"), (dict(video_frame_stride=0), "video_frame_stride"),
+                    (dict(video_preset="warp"), "video_preset"), (dict(batch_size=8, n_episodes=4), "batch size")):
+        with pytest.raises(ValueError, match=msg):
+            EvalConfig(**kw)
