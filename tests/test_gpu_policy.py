@@ -160,4 +160,7 @@ def test_loss_curves_of_native_and_oracle_paths_agree(monkeypatch):
     a, o = curves["native"], curves["oracle"]
     assert a[-1] < 0.8 * a[0] and o[-1] < 0.8 * o[0]
     rel = [abs(x - y) / max(abs(y), 1e-6) for x, y in zip(a, o)]
-    assert max(rel[:10]) < 0.03 and max(rel) < 0.12, (max(rel[:10]), max(rel))
+    # early steps agree to bf16 rounding; later, with the loss of this one batch driven towards zero, two bf16
+    # trajectories drift apart in RELATIVE terms, so the whole curve is held to a tolerance in units of the initial loss
+    scaled = [abs(x - y) / o[0] for x, y in zip(a, o)]
+    assert max(rel[:10]) < 0.03 and max(scaled) < 0.03, (max(rel[:10]), max(scaled), max(rel))
