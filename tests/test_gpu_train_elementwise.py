@@ -218,6 +218,6 @@ def test_seq_concat_kernel_matches_cat_forward_and_backward(dev):
     w = torch.randn_like(out)
     (out.float() * w.float()).sum().backward()
     torch.testing.assert_close(c.grad.float(), w[:, 33:].float())
-    odd = torch.randn(4, 7, 2, 60, device=dev).to(torch.bfloat16)   # 120 elements per row: not a multiple of 8 -> cat
-    assert not cuda_ops.seq_concat_supported(odd, odd) and ops.seq_concat(odd, odd).shape == (4, 14, 2, 60)
+    odd = torch.randn(4, 7, 1, 60, device=dev).to(torch.bfloat16)   # 60 elements per row: not a multiple of 8 -> cat
+    assert not cuda_ops.seq_concat_supported(odd, odd) and ops.seq_concat(odd, odd).shape == (4, 14, 1, 60)
     assert torch.equal(ops.seq_concat(a.float().cpu(), c.detach().float().cpu()), ref.float().cpu())
