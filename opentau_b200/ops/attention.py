@@ -69,7 +69,7 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, q_blk, k_blk, q_valid, k_valid, sc
     from . import attention_native
     if attention_native.supported(q, k, v):
         return attention_native.attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
-    if attention_native.supported_f32(q, k, v):
+    if attention_native.supported_f32(q, k, v) and attention_native.prefer_f32_kernels(q, k):
         return attention_native.attn_f32_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
     return dense_attn_fwd(q, k, v, q_blk, k_blk, q_valid, k_valid, scale)
 
@@ -78,6 +78,6 @@ def attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale):
     from . import attention_native
     if attention_native.supported_bwd(q, k, v):
         return attention_native.attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)
-    if attention_native.supported_f32(q, k, v):
+    if attention_native.supported_f32(q, k, v) and attention_native.prefer_f32_kernels(q, k):
         return attention_native.attn_f32_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)
     return dense_attn_bwd(do, q, k, v, o, lse, q_blk, k_blk, q_valid, k_valid, scale)

@@ -137,6 +137,24 @@ def supported_f32(q: Tensor, k: Tensor, v: Tensor) -> bool:
     return k.dtype == v.dtype == torch.float32 and D % 4 == 0 and 4 <= D <= 256 and H % Hkv == 0
 
 
+#: score bytes of one 8-sample chunk of the dense evaluation above which the kernels are used whatever the head width
+F32_DENSE_SCORE_LIMIT = 1 << 30
+
+
+def prefer_f32_kernels(q: Tensor, k: Tensor) -> bool:
+    """Which fp32 path the dispatcher takes when both can run (``OPENTAU_B200_F32_ATTN=kernel|dense`` forces one).
+    Measured on a B200: the kernels need O(S) extra memory instead of the (B, H, Sq, Sk) score tensor and are 2.5 x
+    (forward) / 1.1 x (backward) the dense evaluation at head width 64, but at head width 256 the library's fp32 GEMMs
+    win (forward 0.9 x, backward 0.3 x) as long as the scores fit.  So: kernels for head widths up to 128, and at any
+    width once the scores of a chunk would pass :data:`F32_DENSE_SCORE_LIMIT`."""
+    mode = os.environ.get("OPENTAU_B200_F32_ATTN", "auto")
+    if mode in ("kernel", "dense"):
+        return mode == "kernel"
+    B, Sq, H, D = q.shape
+    scores = min(B, 8) * H * Sq * k.shape[1] * 4
+    return D <= 128 or scores > F32_DENSE_SCORE_LIMIT
+
+
 def _prep_f32(t: Tensor) -> Tensor:
     if t.stride(3) != 1 or any(s % 4 for s in t.stride()[:3]) or t.data_ptr() % 16:
         t = t.contiguous()

@@ -91,13 +91,20 @@ __global__ void reduce_scatter_kernel(PeerTable grads, int world, long long lo, 
   const long long nvec = n >> 3;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
        t += (long long)gridDim.x * blockDim.x) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < world; ++r) {
-      float f[8];
-      load8<T>(static_cast<const T*>(grads.ptr[r]) + lo + t * 8, f);
+    // all ranks' pieces are requested before any is consumed: up to eight independent 16-byte (bf16) or 32-byte
+    // (fp32) loads in flight per thread, which is what hides the latency of the peer reads; the sum itself runs in
+    // rank order
+    float f[MAX_RANKS][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += f[e];
-    }
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) load8<T>(static_cast<const T*>(grads.ptr[r]) + lo + t * 8, f[r]);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[r][e];
+      }
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += acc[e] * acc[e];
     float4* o = reinterpret_cast<float4*>(out32 + t * 8);
@@ -123,12 +130,21 @@ __global__ void reduce_scatter_kernel(PeerTable grads, int world, long long lo, 
 __global__ void allgather_pull_kernel(PeerTable src, int world, long long n_vec16, uint4* __restrict__ out,
                                       const KernelStatus* status) {
   if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
+  const long long stride = (long long)gridDim.x * blockDim.x;
   for (int r = 0; r < world; ++r) {
     const uint4* s = static_cast<const uint4*>(src.ptr[r]);
     uint4* o = out + (long long)r * n_vec16;
-    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < n_vec16;
-         t += (long long)gridDim.x * blockDim.x)
-      o[t] = s[t];
+    long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    // four independent 16-byte peer loads in flight per thread: with one, a grid of 64 K threads keeps 1 MB on the
+    // link, about half of what its bandwidth-delay product needs
+    for (; t + 3 * stride < n_vec16; t += 4 * stride) {
+      const uint4 a = s[t], b = s[t + stride], c = s[t + 2 * stride], d = s[t + 3 * stride];
+      o[t] = a;
+      o[t + stride] = b;
+      o[t + 2 * stride] = c;
+      o[t + 3 * stride] = d;
+    }
+    for (; t < n_vec16; t += stride) o[t] = s[t];
   }
 }
 
@@ -140,13 +156,17 @@ __global__ void reduce_scatter_bf16_kernel(PeerTable src, int world, long long l
   const long long nvec = n >> 3;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
        t += (long long)gridDim.x * blockDim.x) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < world; ++r) {
-      float f[8];
-      load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(src.ptr[r]) + lo + t * 8, f);
+    float f[MAX_RANKS][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += f[e];
-    }
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(src.ptr[r]) + lo + t * 8, f[r]);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[r][e];
+      }
     store8<__nv_bfloat16>(out + t * 8, acc);
   }
 }

@@ -231,6 +231,77 @@ def bench_attention(B, Sq, H, Hkv, D, cross=0, causal_tail=0, iters=20, with_sdp
     return rec
 
 
+def bench_attention_f32(B, Sq, H, Hkv, D, causal_tail=0, iters=10) -> dict:
+    """The exact fp32 kernels (``csrc/attention_f32.cu``) against the dense fp32 PyTorch evaluation of the same masked
+    attention (which materialises the ``(B, H, Sq, Sk)`` scores), forward and backward, with the peak memory of each."""
+    from opentau_b200 import ops
+    from opentau_b200.ops import attention as dispatch
+    from opentau_b200.ops import attention_native
+    dev = torch.device("cuda")
+    q = torch.randn(B, Sq, H, D, device=dev)
+    k = torch.randn(B, Sq, Hkv, D, device=dev)
+    v = torch.randn(B, Sq, Hkv, D, device=dev)
+    att = torch.zeros(B, Sq, dtype=torch.bool, device=dev)
+    if causal_tail:
+        att[:, Sq - causal_tail:] = True
+    q_blk, q_valid = ops.make_block_ids(torch.ones(B, Sq, dtype=torch.bool, device=dev), att)
+    scale = D ** -0.5
+    visible = float(ops.dense_mask_from_blocks(q_blk, q_blk, q_valid, q_valid).sum().item()) * H
+    flops = 4.0 * visible * D
+    assert attention_native.supported_f32(q, k, v)
+    o, lse = attention_native.attn_f32_fwd(q, k, v, q_blk, q_blk, q_valid, q_valid, scale)
+    do = torch.randn_like(o)
+    rec = {"kernel": "attn_f32", "B": B, "Sq": Sq, "H": H, "Hkv": Hkv, "D": D}
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        ms = time_ms([fn], iters)
+        return ms, (torch.cuda.max_memory_allocated() - base) / 2**20
+
+    ms, mem = timed(lambda: attention_native.attn_f32_fwd(q, k, v, q_blk, q_blk, q_valid, q_valid, scale))
+    rec.update(fwd_ms=round(ms, 3), fwd_tflops_visible=round(flops / ms / 1e9, 2), fwd_extra_mib=round(mem, 1))
+    ms, mem = timed(lambda: attention_native.attn_f32_bwd(do, q, k, v, o, lse, q_blk, q_blk, q_valid, q_valid, scale))
+    rec.update(bwd_ms=round(ms, 3), bwd_tflops_visible=round(2.5 * flops / ms / 1e9, 2), bwd_extra_mib=round(mem, 1))
+    ms, mem = timed(lambda: dispatch.dense_attn_fwd(q, k, v, q_blk, q_blk, q_valid, q_valid, scale))
+    rec.update(dense_fwd_ms=round(ms, 3), dense_fwd_extra_mib=round(mem, 1))
+    ms, mem = timed(lambda: dispatch.dense_attn_bwd(do, q, k, v, o, lse, q_blk, q_blk, q_valid, q_valid, scale))
+    rec.update(dense_bwd_ms=round(ms, 3), dense_bwd_extra_mib=round(mem, 1))
+    rec["fwd_speedup"] = round(rec["dense_fwd_ms"] / rec["fwd_ms"], 2)
+    rec["bwd_speedup"] = round(rec["dense_bwd_ms"] / rec["bwd_ms"], 2)
+    return rec
+
+
+def bench_stss(B=32, T=4, HW=16, C=256, L=5, k=9, iters=10) -> dict:
+    """Space-time window correlation: the kernels (``csrc/stss_corr.cu``) against the unfold + einsum evaluation, forward
+    and forward + backward, with the extra memory each needs."""
+    from opentau_b200.ops import stss
+    dev = torch.device("cuda")
+    x = torch.nn.functional.normalize(torch.randn(B, T, HW * HW, C, device=dev), dim=-1).to(torch.bfloat16)
+    rec = {"kernel": "stss_corr", "B": B, "T": T, "grid": HW, "C": C, "L": L, "k": k}
+
+    def run(fn, backward):
+        def step():
+            xr = x.detach().requires_grad_(backward)
+            out = fn(xr, T, HW, HW, L, k)
+            if backward:
+                out.backward(torch.ones_like(out))
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        ms = time_ms([step], iters)
+        return round(ms, 3), round((torch.cuda.max_memory_allocated() - base) / 2**20, 1)
+
+    rec["fwd_ms"], rec["fwd_extra_mib"] = run(stss.local_window_correlation, False)
+    rec["fwd_bwd_ms"], rec["fwd_bwd_extra_mib"] = run(stss.local_window_correlation, True)
+    rec["dense_fwd_ms"], rec["dense_fwd_extra_mib"] = run(stss.dense_window_correlation, False)
+    rec["dense_fwd_bwd_ms"], rec["dense_fwd_bwd_extra_mib"] = run(stss.dense_window_correlation, True)
+    rec["fwd_speedup"] = round(rec["dense_fwd_ms"] / rec["fwd_ms"], 2)
+    rec["fwd_bwd_speedup"] = round(rec["dense_fwd_bwd_ms"] / rec["fwd_bwd_ms"], 2)
+    return rec
+
+
 def bench_membound(rows=39264, H=2048, iters=20) -> list[dict]:
     from opentau_b200.ops import cuda_ops
     dev = torch.device("cuda")
@@ -283,7 +354,9 @@ def main(argv=None):
     a.add_argument("--iters", type=int, default=20)
     a.add_argument("--no-sdpa", action="store_true")
     a.add_argument("--backward", action="store_true")
+    a.add_argument("--fp32", action="store_true", help="the exact fp32 kernels against the dense fp32 evaluation")
     sub.add_parser("membound")
+    sub.add_parser("stss")
     sk = sub.add_parser("skinny")
     sk.add_argument("--shape", type=int, nargs=3, action="append", default=None, metavar=("M", "N", "K"))
     sk.add_argument("--iters", type=int, default=20)
@@ -292,9 +365,14 @@ def main(argv=None):
     args = ap.parse_args(argv)
     if args.cmd == "gemm":
         print(json.dumps(bench_gemm(args.m, args.n, args.k, args.layout, args.iters, not args.no_torch, args.glu)))
+    elif args.cmd == "attention" and args.fp32:
+        print(json.dumps(bench_attention_f32(args.batch, args.sq, args.heads, args.kv_heads, args.dim, args.causal_tail,
+                                             args.iters)))
     elif args.cmd == "attention":
         print(json.dumps(bench_attention(args.batch, args.sq, args.heads, args.kv_heads, args.dim, args.cross,
                                          args.causal_tail, args.iters, not args.no_sdpa, args.backward)))
+    elif args.cmd == "stss":
+        print(json.dumps(bench_stss()))
     elif args.cmd == "membound":
         for r in bench_membound():
             print(json.dumps(r))

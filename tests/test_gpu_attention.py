@@ -170,7 +170,7 @@ def test_split_kv_matches_single_pass(B, Sq, Sk, H, Hkv, D, nsplit):
 @pytest.mark.parametrize("D", [32, 72, 128, 160, 256])
 @pytest.mark.parametrize("H,Hkv", [(8, 1), (6, 3), (4, 4)])
 @pytest.mark.parametrize("Sq,cross", [(50, 0), (131, 0), (50, 203), (33, 64)])
-def test_fp32_attention_kernels_match_the_dense_fp32_reference(D, H, Hkv, Sq, cross):
+def test_fp32_attention_kernels_match_the_dense_fp32_reference(D, H, Hkv, Sq, cross, monkeypatch):
     """The exact fp32 kernels (forward, dQ, dK / dV over the whole GQA group) against the CPU fp32 dense evaluation,
     at fp32 tolerances: block-causal mask, pads, a cross-attention prefix with block id INT_MIN, strided inputs."""
     from opentau_b200 import ops
@@ -188,7 +188,11 @@ def test_fp32_attention_kernels_match_the_dense_fp32_reference(D, H, Hkv, Sq, cr
     scale = D ** -0.5
     assert attention_native.supported_f32(q, k, v) and not attention_native.supported(q, k, v)
     from opentau_b200.ops import attention as dispatch
-    o, lse = dispatch.attn_fwd(q, k, v, qb, kb, qv, kv, scale)          # the dispatcher picks the fp32 kernels
+    monkeypatch.setenv("OPENTAU_B200_F32_ATTN", "kernel")               # at small sizes "auto" may take the dense body
+    o, lse = dispatch.attn_fwd(q, k, v, qb, kb, qv, kv, scale)
+    assert attention_native.prefer_f32_kernels(q, k)
+    monkeypatch.setenv("OPENTAU_B200_F32_ATTN", "auto")
+    assert attention_native.prefer_f32_kernels(q, k) == (D <= 128)      # these score tensors are far below the limit
     qc, kc, vc = q.cpu().contiguous(), k.cpu(), v.cpu()
     o_ref, lse_ref = ops.prims.attn_fwd(qc, kc, vc, qb.cpu(), kb.cpu(), qv.cpu(), kv.cpu(), scale)
     vq, vk = qv.cpu(), kv.cpu()
@@ -206,10 +210,11 @@ def test_fp32_attention_kernels_match_the_dense_fp32_reference(D, H, Hkv, Sq, cr
         assert float(dq.cpu()[hidden].abs().max()) == 0.0
 
 
-def test_fp32_attention_through_autograd_on_gpu():
+def test_fp32_attention_through_autograd_on_gpu(monkeypatch):
     """fp32 CUDA tensors through ``ops.block_attention`` (the autograd function the models call) take the fp32 kernels
     and give the CPU gradients."""
     from opentau_b200 import ops
+    monkeypatch.setenv("OPENTAU_B200_F32_ATTN", "kernel")
     dev = torch.device("cuda:0")
     B, Sq, H, Hkv, D = 2, 70, 8, 2, 64
     _, _, _, qb, kb, qv, kv = _case(B, Sq, H, Hkv, D, 0, dev, seed=9)
