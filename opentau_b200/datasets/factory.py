@@ -2,7 +2,7 @@
 
 ``make_dataset`` builds one member (LeRobot on disk, a VQA corpus, or the synthetic generator) and, when a
 validation ratio is set, its deterministic episode-level train/val split; ``make_dataset_mixture`` assembles the
-weighted mixture(s) with one normalisation head per ``(repo, robot_type, control_mode)`` key.
+weighted mixture(s) with one normalisation head per usable ``(robot_type, control_mode)`` pair.
 """
 
 from __future__ import annotations
@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from ..configs.default import DatasetConfig
-from .dataset_mixture import WeightedDatasetMixture, compute_norm_key
+from .dataset_mixture import WeightedDatasetMixture
 from .lerobot_dataset import LeRobotDataset, LeRobotDatasetMetadata
 from .standard_data_format_mapping import get_mapping
 from .transforms import ImageTransforms
@@ -160,15 +160,58 @@ def make_dataset(dataset_cfg: DatasetConfig, cfg, return_advantage_input: bool =
                              train=mix.val_enable_optional_key_dropout, **kw)
         # the two switches of the validation subset are independent of each other
         val.enable_prompt_substitution = mix.val_enable_prompt_substitution
+        attach_delta_action_stats(train, dataset_cfg, cfg)
+        val.delta_action_stats = train.delta_action_stats      # validation is normalised like training
         return train, val
-    return LeRobotDataset(cfg, dataset_cfg.repo_id, episodes=episodes, image_transforms=tfs, **kw)
+    ds = LeRobotDataset(cfg, dataset_cfg.repo_id, episodes=episodes, image_transforms=tfs, **kw)
+    attach_delta_action_stats(ds, dataset_cfg, cfg)
+    return ds
 
 
-def _norm_key(dcfg: DatasetConfig, ds) -> str:
-    meta = getattr(ds, "meta", None)
-    rt = dcfg.robot_type if dcfg.robot_type is not None else getattr(meta, "robot_type", None)
-    cm = dcfg.control_mode if dcfg.control_mode is not None else getattr(meta, "control_mode", None)
-    return compute_norm_key(dcfg.name, rt, cm)
+def attach_delta_action_stats(dataset: LeRobotDataset, dataset_cfg: DatasetConfig, cfg) -> None:
+    """A delta-action dataset's stored statistics describe ABSOLUTE per-frame actions; the training targets are
+    displacements from the chunk-start state, typically several times narrower.  Their statistics are computed from
+    the numeric columns the dataset already holds in memory (cached under the dataset's root, keyed by everything that
+    changes them) and replace ``state`` / ``actions`` in the mixture's pooled statistics
+    (reference ``src/opentau/datasets/factory.py:112-235``)."""
+    dataset.delta_action_stats = None
+    if not dataset.delta_action_state_map:
+        return
+    from .delta_action_stats import compute_delta_stats_from_columns, delta_stats_cache_key, load_or_compute_delta_stats
+    name_map = dataset._get_name_map()
+    a_key, s_key = name_map["actions"], name_map["state"]
+    # the action horizon in frames (mean offsets: with a jittered horizon the statistics describe its centre)
+    offsets = np.asarray(dataset.delta_timestamps.get(a_key, [0.0]), np.float64) * dataset.fps
+    max_rows = cfg.dataset_mixture.delta_stats_max_rows
+    logging.info("%s: delta joint actions on; stored map %s -> post-index map %s (state_index=%s, action_index=%s)",
+                 dataset_cfg.repo_id, dataset_cfg.delta_action_state_map, dataset.delta_action_state_map,
+                 dataset_cfg.state_index, dataset_cfg.action_index)
+    key = delta_stats_cache_key(state_index=dataset_cfg.state_index, action_index=dataset_cfg.action_index,
+                                delta_map=dataset.delta_action_state_map, chunk_offsets=offsets,
+                                vector_resample_strategy=dataset.vector_resample_strategy, episodes=dataset.episodes,
+                                excluded_episodes=dataset_cfg.excluded_episodes, fps=dataset.fps,
+                                revision=dataset_cfg.revision, max_rows=max_rows)
+
+    def compute():
+        num = dataset._numeric
+        return compute_delta_stats_from_columns(
+            num[s_key].numpy(), num[a_key].numpy(), num["episode_index"].numpy(),
+            delta_map=dataset.delta_action_state_map, chunk_offsets=offsets, state_index=dataset_cfg.state_index,
+            action_index=dataset_cfg.action_index, strategy=dataset.vector_resample_strategy, max_rows=max_rows)
+
+    dataset.delta_action_stats = load_or_compute_delta_stats(dataset.root, key, compute)
+
+
+def dedup_names(names: list[str]) -> list[str]:
+    """Mixture-level names: the second and later entries of one repository get ``#1``, ``#2``, ... appended, so the
+    name -> head table and the per-dataset validation buckets keep one row per entry."""
+    seen: dict[str, int] = {}
+    out = []
+    for n in names:
+        k = seen.get(n, 0)
+        seen[n] = k + 1
+        out.append(n if k == 0 else f"{n}#{k}")
+    return out
 
 
 def make_dataset_mixture(cfg, return_advantage_input: bool = False):
@@ -176,20 +219,24 @@ def make_dataset_mixture(cfg, return_advantage_input: bool = False):
     mix = cfg.dataset_mixture
     if not mix.datasets:
         raise ValueError("dataset_mixture.datasets is empty")
-    trains, vals, names, keys, val_names, val_keys, val_w = [], [], [], [], [], [], []
+    trains, vals, names, val_names, val_w = [], [], [], [], []
     weights = list(mix.weights) if mix.weights else None
     for i, dcfg in enumerate(mix.datasets):
         res = make_dataset(dcfg, cfg, return_advantage_input)
         tr, va = res if isinstance(res, tuple) else (res, None)
         if dcfg.stats is not None:
             tr.stats = {k: {s: np.asarray(v, np.float32) for s, v in d.items()} for k, d in dcfg.stats.items()}
-        trains.append(tr), names.append(dcfg.name), keys.append(_norm_key(dcfg, tr))
+        trains.append(tr), names.append(dcfg.name)
         if va is not None:
-            vals.append(va), val_names.append(dcfg.name), val_keys.append(_norm_key(dcfg, tr))
+            vals.append(va), val_names.append(dcfg.name)
             val_w.append(weights[i] if weights else float(len(va)))
     seed = cfg.seed if cfg.seed is not None else 0
-    train_mix = WeightedDatasetMixture(trains, names, weights, keys, seed=seed, action_freq=mix.action_freq)
+    names, val_names = dedup_names(names), dedup_names(val_names)
+    # heads come from each member's (robot_type, control_mode), config overrides included; the validation split takes
+    # the TRAINING split's rows, so a validation batch is normalised exactly like a training batch of that dataset
+    train_mix = WeightedDatasetMixture(trains, names, weights, seed=seed, action_freq=mix.action_freq)
     if vals:
-        return train_mix, WeightedDatasetMixture(vals, val_names, val_w, val_keys, seed=seed + 1,
-                                                 action_freq=mix.action_freq)
+        by_name = dict(zip(names, [train_mix.meta.norm_keys[train_mix.meta.dataset_to_norm_index[n]] for n in names]))
+        return train_mix, WeightedDatasetMixture(vals, val_names, val_w, [by_name.get(n, n) for n in val_names],
+                                                 seed=seed + 1, action_freq=mix.action_freq)
     return train_mix

@@ -30,7 +30,7 @@ import torch
 from torch import Tensor
 
 from .. import ops
-from .action_indexing import apply_column_index, apply_delta_actions
+from .action_indexing import apply_column_index, resolve_delta_map, subtract_chunk_start_state
 from .compute_stats import aggregate_stats, compute_episode_stats, sample_indices
 from .standard_data_format_mapping import get_mapping
 from .utils import (CODEBASE_VERSION, DEFAULT_CHUNK_SIZE, DEFAULT_FEATURES, DEFAULT_IMAGE_PATH, DEFAULT_PARQUET_PATH,
@@ -366,10 +366,11 @@ class BaseDataset(torch.utils.data.Dataset):
         return pads
 
     def _apply_column_index_and_delta(self, out: dict) -> None:
-        out["state"] = apply_column_index(out["state"], self.state_index)
-        out["actions"] = apply_column_index(out["actions"], self.action_index)
-        if self.delta_action_state_map:
-            out["actions"] = apply_delta_actions(out["actions"], out["state"], self.delta_action_state_map)
+        who = getattr(self, "repo_id", None) or type(self).__name__
+        out["state"] = apply_column_index(out["state"], self.state_index, what="state", who=who)
+        out["actions"] = apply_column_index(out["actions"], self.action_index, what="action", who=who)
+        if self.delta_action_state_map:      # post-index positions (resolved once in the constructor)
+            out["actions"] = subtract_chunk_start_state(out["actions"], out["state"], self.delta_action_state_map)
 
     def _roll(self, p: float) -> bool:
         """True = drop.  Dropout rolls are active in training (or when validation opts in)."""
@@ -571,7 +572,12 @@ class LeRobotDataset(BaseDataset):
         if dcfg is not None:
             self.state_index, self.action_index = dcfg.state_index, dcfg.action_index
             if dcfg.use_delta_joint_actions:
-                self.delta_action_state_map = dcfg.delta_action_state_map
+                # the config's map is written against the stored columns; what is applied (and published to the
+                # policy through the mixture metadata) is its image after the column selection
+                shape = (self.meta.features.get(self._name_map.get("actions", "action"), {}) or {}).get("shape")
+                width = len(dcfg.action_index) if dcfg.action_index is not None else (shape[-1] if shape else None)
+                self.delta_action_state_map = resolve_delta_map(dcfg.delta_action_state_map, dcfg.action_index,
+                                                                dcfg.state_index, who=repo_id, action_dim=width)
             self.prompt_substitutions = dcfg.prompt_substitutions
             self.robot_type = dcfg.robot_type if dcfg.robot_type is not None else self.meta.robot_type
             self.control_mode = dcfg.control_mode if dcfg.control_mode is not None else self.meta.control_mode

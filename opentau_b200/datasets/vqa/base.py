@@ -46,6 +46,8 @@ class VQADatasetMetadata:
 
 
 class VQADataset(BaseDataset):
+    is_vqa = True        # emits no action chunk: exempt from the mixture's all-delta / all-absolute rule
+
     def __init__(self, cfg, train: bool = True):
         super().__init__(cfg, name_map={"camera0": "image", "prompt": "prompt", "response": "postfix",
                                         "state": "state", "actions": "actions"}, train=train)

@@ -120,6 +120,25 @@ def resolve_pretrained_weights_file(pretrained_name_or_path: str | Path) -> str:
     return str(f)
 
 
+ACTION_NORM_META_FILE = "opentau_action_norm.json"
+
+
+def read_action_norm_meta(tokenizer_path: str | Path) -> dict | None:
+    """``{"config_version": int, "zero_range_center": bool}`` stored beside a FAST tokenizer fitted by this framework,
+    or ``None`` when the tokenizer is not a local directory / cached snapshot with that file or the file is unreadable:
+    a tokenizer without the sidecar (an upstream one, or one fitted before the convention was versioned) makes no
+    claim (reference ``src/opentau/policies/pretrained.py:294-331``)."""
+    import json
+    try:
+        root = _source_dir(tokenizer_path)
+        if root is None or not (root / ACTION_NORM_META_FILE).is_file():
+            return None
+        data = json.loads((root / ACTION_NORM_META_FILE).read_text())
+    except Exception:  # noqa: BLE001 - best effort by contract
+        return None
+    return data if isinstance(data, dict) else None
+
+
 def reconcile_projection_tensor(key: str, loaded: Tensor, target: Tensor, old_names: list[str] | None,
                                 new_names: list[str] | None) -> Tensor:
     """The tensor to load for one per-group projection key (``loaded`` itself when nothing has to change)."""

@@ -56,7 +56,11 @@ class PI05Config(PreTrainedConfig):
     scheduler_warmup_steps: int = 1000
     scheduler_decay_steps: int = 30000
     scheduler_decay_lr: float = 2.5e-6
-    delta_action_state_map: dict[str, list[int]] | None = None
+    # {emitted action position: emitted state position} of a delta-joint-action mixture (post-index space): filled by
+    # make_policy from the mixture's metadata, stored with the checkpoint, inverted in sample_actions.  JSON turns the
+    # keys into strings; __post_init__ turns them back.
+    delta_action_state_map: dict[int, int] | None = None
+    # an openpi-style norm_stats.json that replaces the dataset-derived statistics of EVERY head (teacher replay)
     norm_stats_override_path: str | None = None
     tokenizer_path: str = "google/paligemma-3b-pt-224"
     # geometry overrides (dict of TowerConfig / SiglipConfig fields); None = the published sizes
@@ -78,6 +82,14 @@ class PI05Config(PreTrainedConfig):
         if self.train_state_action_representation_only and (self.train_expert_only or self.train_vision_encoder_only):
             raise ValueError("train_state_action_representation_only is mutually exclusive with "
                              "train_expert_only and train_vision_encoder_only")
+        if self.delta_action_state_map is not None:
+            try:
+                self.delta_action_state_map = {int(a): int(b) for a, b in self.delta_action_state_map.items()}
+            except (TypeError, ValueError, AttributeError) as exc:
+                raise ValueError("`delta_action_state_map` must map int action positions to int state positions, got "
+                                 f"{self.delta_action_state_map!r}") from exc
+            if any(a < 0 or b < 0 for a, b in self.delta_action_state_map.items()):
+                raise ValueError(f"`delta_action_state_map` positions must be non-negative, got {self.delta_action_state_map!r}")
         self.validate_action_horizon()
 
     def validate_features(self) -> None:

@@ -26,6 +26,7 @@ from torch import Tensor, nn
 from ... import ops
 from ...models.dual_stream import DualStreamDecoder, KVCache
 from ...models.layers import Linear, Tower, TowerConfig
+from ...datasets.action_indexing import add_chunk_start_state, subtract_chunk_start_state
 from ...models.siglip import MultiModalProjector, SiglipConfig, SiglipVisionModel
 from ...utils.tokenizer import load_action_tokenizer, load_text_tokenizer, pad_tokens
 from ..normalize import Normalize, Unnormalize
@@ -757,6 +758,7 @@ class PI05Policy(PreTrainedPolicy):
         from ..candidates import expand_candidates, pick, select_candidate, warn_if_no_candidate_scored
         self.eval()
         cfg = self.config
+        raw_state = self._delta_anchor_state(batch)          # before normalize_inputs: the raw state anchors the chunk
         B = batch["state"].shape[0]
         device = batch["state"].device
         idx = self._resolve_dataset_index(batch, B, device)
@@ -766,6 +768,8 @@ class PI05Policy(PreTrainedPolicy):
         state = nb["state"]
         if state.dim() == 3:
             state = state[:, -1]
+        if action_prefix is not None:
+            action_prefix = self._model_space_prefix(action_prefix, raw_state, idx)
         n = int(n_candidates or getattr(self, "_n_candidates", None) or 1)
         critic = getattr(self, "_critic", None)
         if n > 1 and critic is None:
@@ -793,6 +797,11 @@ class PI05Policy(PreTrainedPolicy):
         feat = cfg.action_feature
         real = feat.shape[0] if feat is not None else actions.shape[-1]
         actions = self.unnormalize_outputs({"actions": actions[:, :, :real]}, sampler_idx)["actions"]
+        if raw_state is not None:
+            # the dataset subtracted the chunk-start state from the mapped dims; without the other half the consumer
+            # would read displacements as absolute joint targets
+            actions = add_chunk_start_state(actions, expand_candidates(raw_state, n).to(actions.dtype),
+                                            cfg.delta_action_state_map)
         if n == 1:
             return actions
         candidates = actions.view(B, n, *actions.shape[1:])
@@ -803,6 +812,34 @@ class PI05Policy(PreTrainedPolicy):
         warn_if_no_candidate_scored(self.last_candidate_scores)
         publish(self, meter, dataset_index=sampler_idx, n_candidates=n, selected=selected)
         return pick(candidates, selected)
+
+    def _delta_anchor_state(self, batch: dict[str, Any]) -> Tensor | None:
+        """The RAW (un-normalised) state the emitted chunk is anchored to, when the policy was trained on delta joint
+        actions; ``None`` for absolute actions.  A configured map without a ``state`` in the batch is an error: the
+        inverse is impossible and returning displacements would silently emit actions in the wrong space
+        (reference ``src/opentau/policies/pi05/modeling_pi05.py:896-927``)."""
+        if not getattr(self.config, "delta_action_state_map", None):
+            return None
+        if "state" not in batch:
+            raise KeyError("delta_action_state_map is configured, so sample_actions must add the conditioning state back "
+                           f"onto its output, but the batch has no 'state' (keys: {sorted(batch)})")
+        st = batch["state"].detach().clone().float()
+        return st[:, -1] if st.dim() == 3 else st
+
+    def _model_space_prefix(self, action_prefix: Tensor, raw_state: Tensor | None, idx: Tensor) -> Tensor:
+        """The frozen rows of real-time chunking arrive as the caller holds them: ABSOLUTE, un-normalised actions off the
+        queue.  The model was trained on (delta-transformed and) normalised targets, so the prefix takes the same route
+        as a training target and is then padded to ``(B, chunk_size, max_action_dim)``."""
+        cfg = self.config
+        feat = cfg.action_feature
+        real = min(feat.shape[0] if feat is not None else action_prefix.shape[-1], action_prefix.shape[-1])
+        p = action_prefix[..., :real].float()
+        if raw_state is not None:
+            p = subtract_chunk_start_state(p, raw_state, cfg.delta_action_state_map)
+        p = self.normalize_targets({"actions": p}, idx)["actions"]
+        out = torch.zeros(p.shape[0], cfg.chunk_size, cfg.max_action_dim, dtype=torch.float32, device=p.device)
+        out[:, :min(p.shape[1], cfg.chunk_size), :real] = p[:, :cfg.chunk_size]
+        return out
 
     def enable_cuda_graphs(self, flag: bool = True) -> None:
         """Replay the sampler (prefix pass + Euler loop) from a CUDA graph: one launch per action chunk."""

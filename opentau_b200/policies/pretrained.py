@@ -71,32 +71,159 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
         """Kept for API compatibility: there is no tracing compiler in this framework."""
 
     # -- normalization heads -----------------------------------------------------------------------
-    def _resolve_dataset_index(self, batch: dict[str, Any], batch_size: int, device) -> Tensor:
-        """Row of the stacked statistics for each sample.
+    #: batch keys that identify a sample but carry no data (skipped when the batch size / device are inferred)
+    _NON_DATA_BATCH_KEYS = frozenset({"dataset_index", "dataset_repo_id", "robot_type", "control_mode"})
 
-        Order of precedence: an explicit ``dataset_index`` tensor; ``dataset_repo_id`` names looked
-        up in ``config.dataset_to_norm_index`` / ``config.dataset_names``; a single head -> zeros.
-        """
+    @property
+    def _norm_key_to_index(self) -> dict[str, int] | None:
+        """``{head key: row}`` from ``config.dataset_names`` (the head keys, one per row); ``None`` = no names."""
+        names = self.config.dataset_names
+        return {n: i for i, n in enumerate(names)} if names else None
+
+    @property
+    def _dataset_to_norm_index(self) -> dict[str, int] | None:
+        """``{training dataset name: row}``; a checkpoint that stored only the head keys gets the identity table."""
+        table = self.config.dataset_to_norm_index
+        return dict(table) if table else self._norm_key_to_index
+
+    def _model_device(self) -> torch.device:
+        try:
+            return next(self.parameters()).device
+        except StopIteration:
+            return torch.device("cpu")
+
+    def _stat_modules(self):
+        from .normalize import _StatsModule
+        return [m for m in self.modules() if isinstance(m, _StatsModule)]
+
+    def _iter_norm_buffer_params(self):
+        for mi, mod in enumerate(self._stat_modules()):
+            for name, p in mod.named_parameters(recurse=True):
+                if name.startswith("buffer_"):
+                    yield f"{type(mod).__name__.lower()}[{mi}].{name}", p
+
+    def _stacked_num_datasets(self) -> int:
+        """Rows of the stacked statistics, read from the buffers themselves: the one source of truth, also for a policy
+        built directly with two statistics dicts and no names.  1 when there is no statistics buffer at all."""
+        for _, p in self._iter_norm_buffer_params():
+            return int(p.shape[0])
+        return 1
+
+    def _norm_buffers_have_inf(self) -> bool:
+        """True while any statistics buffer still holds the ``+inf`` it was created with, i.e. was neither loaded from
+        a checkpoint nor filled from statistics (a checkpoint saved with ``save_normalization_stats=False``)."""
+        return any(bool(torch.isinf(p).any()) for _, p in self._iter_norm_buffer_params())
+
+    def _check_norm_stats_loaded(self) -> None:
+        """Fails at construction time, with the buffer names, instead of at the first forward pass."""
+        bad = [n for n, p in self._iter_norm_buffer_params() if bool(torch.isinf(p).any())]
+        if bad:
+            raise RuntimeError("normalisation buffers were neither loaded from the checkpoint nor given statistics; "
+                               f"still +inf: {bad}.  Save the checkpoint with `save_normalization_stats=True`, or pass "
+                               "`ds_meta=` to `make_policy(...)` so that statistics are injected after the load.")
+
+    def _check_discrete_action_tokenizer_convention(self, tokenizer_path: str | Path) -> None:
+        """A fitted FAST tokenizer bakes the zero-range convention of the normalised actions into its BPE corpus
+        (version 0: a zero-range dim maps to -1; later: to 0), so tokenizer and policy must agree or padded action
+        columns tokenize to values the corpus never saw.  Only tokenizers fitted by this framework carry the sidecar;
+        one without it makes no claim and passes (reference ``src/opentau/policies/pretrained.py:996-1044``)."""
+        from .loading import read_action_norm_meta
+        meta = read_action_norm_meta(tokenizer_path)
+        if meta is None or "zero_range_center" not in meta:
+            return
+        ours = bool(self.config.zero_range_centers_on_zero)
+        if bool(meta["zero_range_center"]) != ours:
+            v = self.config.resolved_config_version()
+            raise ValueError(
+                f"FAST tokenizer / policy normalisation mismatch: the tokenizer at '{tokenizer_path}' was fitted with "
+                f"zero_range_center={bool(meta['zero_range_center'])} (config_version {meta.get('config_version', '?')}), "
+                f"this policy resolves to zero_range_center={ours} (config_version {v}).  Re-fit the tokenizer with "
+                f"`fit_fast_tokenizer --config-version {v}`, or pin the policy with "
+                f"`--policy.config_version={meta.get('config_version', 0)}`.")
+
+    def _infer_batch_size_and_device(self, batch: dict[str, Any]) -> tuple[int, torch.device]:
+        for key, v in batch.items():
+            if key not in self._NON_DATA_BATCH_KEYS and isinstance(v, Tensor):
+                return (v.shape[0] if v.ndim > 0 else 1), v.device
+        return 0, self._model_device()
+
+    def _resolve_dataset_index(self, batch: dict[str, Any], batch_size: int | None = None, device=None) -> Tensor:
+        """Row of the stacked statistics for each sample (reference ``src/opentau/policies/pretrained.py:681-829``).
+
+        First match wins:
+
+        1. ``dataset_index``: the tensor the mixture tags every training sample with.  The only route used in training,
+           because ``robot_type`` / ``control_mode`` are subject to per-sample dropout there.
+        2. ``robot_type`` AND ``control_mode`` (a string or one per sample): looked up as ``"<rt>::<cm>"`` among the
+           head keys; a pair that was dropped or is unknown raises instead of picking a row.
+        3. ``dataset_repo_id`` (a string or one per sample): training dataset name -> row, which also works when
+           several datasets share a head.
+        4. nothing of the above and ONE row: zeros.  With several rows the batch must identify itself.
+
+        A single-head policy without name tables (an old checkpoint) answers routes 2 and 3 with row 0: there is
+        nothing to resolve.  ``KeyError``: unidentifiable batch on a multi-head policy; ``ValueError``: an identifier
+        that matches no row; ``RuntimeError``: names given to a multi-head policy that has no name tables."""
+        inferred_b, inferred_dev = self._infer_batch_size_and_device(batch)
+        B = batch_size if batch_size is not None else (inferred_b or 1)
+        dev = device if device is not None else inferred_dev
         idx = batch.get("dataset_index")
         if idx is not None:
-            return torch.as_tensor(idx, device=device).long().reshape(-1)
+            # onto the device of the statistics, not of whichever batch tensor comes first
+            return torch.as_tensor(idx).to(dtype=torch.long, device=device if device is not None
+                                           else self._model_device()).reshape(-1)
+
+        def single_head():
+            return torch.zeros(B, dtype=torch.long, device=dev) if self._stacked_num_datasets() <= 1 else None
+
+        def spread(v):
+            return [v] * B if isinstance(v, str) else list(v)
+
+        if batch.get("robot_type") is not None and batch.get("control_mode") is not None:
+            table = self._norm_key_to_index
+            if table is None:
+                row0 = single_head()
+                if row0 is not None:
+                    return row0
+                raise RuntimeError("the policy has several normalisation heads but no `dataset_names`: it cannot map "
+                                   "(robot_type, control_mode) to a head; pass `dataset_index`, or build the policy "
+                                   "through `make_policy(cfg, ds_meta=...)`")
+            from ..datasets.dataset_mixture import compute_norm_key
+            rts, cms = spread(batch["robot_type"]), spread(batch["control_mode"])
+            if len(rts) != len(cms):
+                raise ValueError(f"`robot_type` ({len(rts)}) and `control_mode` ({len(cms)}) differ in length")
+            keys = [compute_norm_key(rt, cm, "")[0] for rt, cm in zip(rts, cms)]     # "" matches no row: raises below
+            if not any(k in table for k in keys):
+                row0 = single_head()          # one head under another name (a hand-named or name-keyed head)
+                if row0 is not None:
+                    return row0
+            try:
+                return torch.tensor([table[k] for k in keys], dtype=torch.long, device=dev)
+            except KeyError as e:
+                raise ValueError(f"norm key {e.args[0]!r} (from robot_type / control_mode) is not one of this policy's "
+                                 f"heads {list(table)}") from None
         names = batch.get("dataset_repo_id")
-        cfg = self.config
         if names is not None:
-            table = cfg.dataset_to_norm_index or (
-                {n: i for i, n in enumerate(cfg.dataset_names)} if cfg.dataset_names else None)
-            if table is not None:
-                if isinstance(names, str):
-                    names = [names] * batch_size
-                try:
-                    return torch.tensor([table[n] for n in names], dtype=torch.long, device=device)
-                except KeyError as e:
-                    raise KeyError(f"dataset {e.args[0]!r} has no normalization head; known: {sorted(table)}") from None
-        n_heads = len(cfg.dataset_names) if cfg.dataset_names else 1
-        if n_heads > 1:
-            raise ValueError("the policy has several normalization heads; the batch must carry "
-                             "'dataset_index' or 'dataset_repo_id'")
-        return torch.zeros(batch_size, dtype=torch.long, device=device)
+            table = self._dataset_to_norm_index
+            if table is None:
+                row0 = single_head()
+                if row0 is not None:
+                    return row0
+                raise RuntimeError("the policy has several normalisation heads but no `dataset_names`: it cannot map "
+                                   "`dataset_repo_id` to a head; pass `dataset_index`, or build the policy through "
+                                   "`make_policy(cfg, ds_meta=...)`")
+            try:
+                return torch.tensor([table[n] for n in spread(names)], dtype=torch.long, device=dev)
+            except KeyError as e:
+                row0 = single_head()
+                if row0 is not None:
+                    return row0
+                raise ValueError(f"dataset_repo_id {e.args[0]!r} is not in this policy's training set "
+                                 f"{sorted(table)}") from None
+        rows = self._stacked_num_datasets()
+        if rows <= 1:
+            return torch.zeros(B, dtype=torch.long, device=dev)
+        raise KeyError(f"normalisation with {rows} heads needs one of `dataset_index` (LongTensor (B,)), "
+                       "`dataset_repo_id` (str or one per sample), or both `robot_type` and `control_mode` in the batch")
 
     def _inject_stats(self, per_dataset_stats: list[dict], dataset_names: list[str] | None = None) -> None:
         """Overwrites every statistics buffer from ``per_dataset_stats`` (one dict per head)."""

@@ -26,6 +26,7 @@ import torch
 from torch import Tensor
 
 from ..configs import parser
+from ..configs.deployment import tag_norm_head
 from ..configs.train import TrainPipelineConfig
 from ..envs.configs import EnvConfig
 from ..envs.factory import make_envs
@@ -83,6 +84,7 @@ def rollout(env, policy, seeds: list[int] | None = None, cfg=None, device=None, 
         batch = {k: (v.to(device) if isinstance(v, Tensor) else v) for k, v in batch.items()}
         if extra_batch:
             batch.update(extra_batch)
+        tag_norm_head(batch, getattr(cfg, "eval", None))
         if return_observations:
             all_o.append({k: v.cpu() for k, v in batch.items() if isinstance(v, Tensor)})
         with torch.inference_mode():

@@ -108,8 +108,10 @@ class RobotPolicyServicer(pb_grpc.RobotPolicyServiceServicer):
         return policy.eval()
 
     def _dummy_batch(self) -> dict[str, Any]:
+        from ...configs.deployment import tag_norm_head
         from ...utils.utils import create_dummy_observation
-        return create_dummy_observation(self.cfg, self.device)
+        # warm-up takes the same head as real requests (a multi-head policy refuses an untagged batch)
+        return tag_norm_head(create_dummy_observation(self.cfg, self.device), self.cfg.server)
 
     def _sample(self, batch, action_prefix, delay) -> torch.Tensor:
         with torch.inference_mode():
@@ -157,6 +159,8 @@ class RobotPolicyServicer(pb_grpc.RobotPolicyServiceServicer):
                 raise ValueError("delay exceeds the number of prefix actions")
         elif delay:
             raise ValueError("delay > 0 needs prefix_action")
+        from ...configs.deployment import tag_norm_head
+        tag_norm_head(batch, cfg.server)
         return batch, prefix, delay
 
     def _apply_planner(self, request, batch: dict[str, Any]) -> None:

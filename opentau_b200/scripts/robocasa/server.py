@@ -119,7 +119,8 @@ class OpenTauRoboCasaPolicy:
         self.last_accel: list[float] | None = None
 
     def infer_batch(self, items, action_dim: int) -> list[np.ndarray]:
-        batch = build_batch(self.cfg, items, self.device)
+        from ...configs.deployment import tag_norm_head
+        batch = tag_norm_head(build_batch(self.cfg, items, self.device), getattr(self.cfg, "server", None))
         with torch.inference_mode():
             actions = self.policy.sample_actions(batch).float().cpu().numpy()
         acc = getattr(self.policy, "last_accel", None) if self.accel_prefix else None

@@ -83,10 +83,23 @@ def test_video_backed_dataset_and_history(tmp_path):
 def test_column_index_and_delta_actions(tmp_path):
     _record(tmp_path / "toy")
     cfg = _cfg(tmp_path / "toy", ds=dict(state_index=[0, 1], action_index=[2, 3, 4], use_delta_joint_actions=True,
-                                         delta_action_state_map={"0": 1}))
-    s = make_dataset(cfg.dataset_mixture.datasets[0], cfg)[3]
+                                         delta_action_state_map={"2": 1}))   # stored action column 2 (emitted 0), state column 1
+    ds = make_dataset(cfg.dataset_mixture.datasets[0], cfg)
+    s = ds[3]
     assert int(s["real_action_dim"]) == 3
     assert s["actions"][:3, :3].float().tolist() == [[0.5, 3.5, 3.5], [1.5, 4.5, 4.5], [2.5, 5.5, 5.5]]
+    # the statistics that normalise these targets describe the DELTAS (computed from the columns, cached beside the
+    # dataset) and reach the mixture's head in the emitted layout, padded
+    assert ds.delta_action_state_map == {0: 1}
+    every = torch.stack([ds[i]["actions"][:, :3].float() for i in range(len(ds))])
+    got = ds.delta_action_stats["actions"]
+    assert np.allclose(got["mean"], every.reshape(-1, 3).mean(0).numpy(), atol=1e-4)
+    assert np.allclose(got["min"], every.reshape(-1, 3).amin(0).numpy(), atol=1e-5)
+    assert len(list((tmp_path / "toy" / "meta" / "delta_action_stats").glob("*.json"))) == 1
+    mix = make_dataset_mixture(cfg)
+    head = mix.meta.per_norm_key_stats[0]["actions"]
+    assert head["mean"].shape == (32,) and np.allclose(head["mean"][:3], got["mean"]) and np.all(head["mean"][3:] == 0)
+    assert mix.meta.delta_action_state_map == {0: 1} and mix.meta.per_norm_key_stats[0]["state"]["mean"].shape == (32,)
     a, st = torch.randn(2, 5, 4), torch.randn(2, 3)
     d = torch.stack([apply_delta_actions(a[i], st[i], {1: 2}) for i in range(2)])
     assert torch.allclose(undo_delta_actions(d, st, {1: 2}), a, atol=1e-6)
