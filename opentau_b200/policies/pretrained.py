@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import abc
 import logging
+import re
 import os
 from pathlib import Path
 from typing import Any
@@ -24,9 +25,17 @@ _NORM_PREFIXES = ("normalize_inputs.", "normalize_targets.", "normalize_actions.
                   "normalize_discrete_actions.", "unnormalize_outputs.")
 
 
+_NORM_BUFFER_KEY = re.compile(r"(^|\.)(un)?normalize_[a-z_]+\.buffer_")
+
+
+def is_norm_buffer_key(key: str) -> bool:
+    """``normalize_*.buffer_*`` / ``unnormalize_*.buffer_*`` at the top level or under a wrapper prefix."""
+    return bool(_NORM_BUFFER_KEY.search(key))
+
+
 def strip_normalization_buffers(state: dict[str, Tensor]) -> dict[str, Tensor]:
     """Drops every ``(un)normalize_*.buffer_*`` entry (used with ``skip_normalization_weights``)."""
-    return {k: v for k, v in state.items() if not k.startswith(_NORM_PREFIXES)}
+    return {k: v for k, v in state.items() if not is_norm_buffer_key(k)}
 
 
 class PreTrainedPolicy(nn.Module, abc.ABC):
@@ -300,6 +309,60 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
         return policy
 
     @classmethod
+    def _strip_normalization_buffers_from_state_dict(cls, state: dict[str, Tensor], config, *,
+                                                     is_main_process: bool = True) -> tuple[dict[str, Tensor], frozenset]:
+        """With ``config.skip_normalization_weights`` the statistics stored in the checkpoint are ignored, so that the
+        buffers built from the CURRENT mixture survive the load (fine-tuning a checkpoint whose statistics were pooled
+        over other data; the buffers do not train, so nothing else would correct them).  Returns the filtered dict and
+        the dropped keys.  The flag is consumed by this load whether or not anything was dropped (a later save stores
+        ``False``, so a resume does not strip the now-correct buffers); a flag that dropped nothing is reported, since
+        the user expected it to void something (reference ``src/opentau/policies/pretrained.py:1213-1305``)."""
+        if not config.skip_normalization_weights:
+            return state, frozenset()
+        dropped = frozenset(k for k in state if is_norm_buffer_key(k))
+        config.skip_normalization_weights = False
+        if not dropped:
+            if is_main_process:
+                logging.warning("skip_normalization_weights=True, but the checkpoint holds no normalize_ / unnormalize_ "
+                                "keys: the flag had no effect")
+            return state, dropped
+        if is_main_process:
+            logging.info("skip_normalization_weights=True: dropped %d stored statistics buffers", len(dropped))
+        return {k: v for k, v in state.items() if k not in dropped}, dropped
+
+    @classmethod
+    def _promote_legacy_norm_buffers(cls, model: "PreTrainedPolicy", state: dict[str, Tensor]) -> None:
+        """Checkpoints from before the stacked layout store statistics as ``(*feature_shape,)``; the buffers are now
+        ``(heads, *feature_shape)``.  A stored tensor exactly one rank short of its buffer becomes the single row of a
+        one-head policy (such a checkpoint was trained on one mixture); in place, one warning."""
+        own = model.state_dict()
+        promoted = []
+        for k, v in list(state.items()):
+            tgt = own.get(k)
+            if tgt is None or not is_norm_buffer_key(k):
+                continue
+            if v.dim() == tgt.dim() - 1 and tuple(v.shape) == tuple(tgt.shape[1:]):
+                state[k] = v.unsqueeze(0).expand_as(tgt).clone()
+                promoted.append(k)
+        if promoted:
+            logging.warning("promoted %d single-dataset statistics buffers to the stacked (heads, ...) layout, e.g. %s",
+                            len(promoted), promoted[:3])
+
+    @classmethod
+    def _assert_normalize_buffers_initialized(cls, model: "PreTrainedPolicy", *, stripped_keys: frozenset) -> None:
+        """After a load that dropped the stored statistics, fresh ones must have been given to the constructor;
+        otherwise the first forward pass would fail with a message about "a pretrained model", which misleads when a
+        pretrained model WAS used and its statistics were dropped on purpose."""
+        if not stripped_keys:
+            return
+        bad = [n for n, p in model._iter_norm_buffer_params() if bool(torch.isinf(p).any())]
+        if bad:
+            raise ValueError("skip_normalization_weights=True needs `per_dataset_stats` at construction (e.g. "
+                             "`make_policy(..., ds_meta=...)`) to replace the dropped statistics; "
+                             f"{len(bad)} buffer(s) are still +inf: " + ", ".join(bad[:5])
+                             + (f", ... ({len(bad) - 5} more)" if len(bad) > 5 else ""))
+
+    @classmethod
     def _fix_state_dict_keys(cls, state: dict[str, Tensor], config) -> dict[str, Tensor]:
         return state
 
@@ -310,21 +373,15 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
         from . import loading
         state = load_file(model_file, device=map_location if map_location != "cpu" else "cpu")
         state = cls._fix_state_dict_keys(state, model.config)
-        if model.config.skip_normalization_weights:
-            state = strip_normalization_buffers(state)
-            model.config.skip_normalization_weights = False       # one shot: a later save / resume keeps the new stats
+        state, stripped = cls._strip_normalization_buffers_from_state_dict(state, model.config)
         loading.remap_per_group_projection_weights(model, state, cls._PER_GROUP_PROJECTION_PREFIXES, old_dataset_names)
         if cls._TILE_LINEAR_INPUTS:
             loading.tile_linear_input_weights(model, state)
-        own = model.state_dict()
-        for k, v in list(state.items()):  # linear input tiling / shape guards are policy specific
-            if k in own and tuple(own[k].shape) != tuple(v.shape) and k.startswith(_NORM_PREFIXES):
-                # legacy (unstacked) statistics: promote to one head
-                if tuple(own[k].shape[1:]) == tuple(v.shape):
-                    state[k] = v.unsqueeze(0).expand_as(own[k]).clone()
+        cls._promote_legacy_norm_buffers(model, state)
         missing, unexpected = model.load_state_dict(state, strict=False)
         tied = {"model.paligemma_with_expert.paligemma.lm_head.weight"}
-        missing = [m for m in missing if m not in tied]
+        missing = [m for m in missing if m not in tied and m not in stripped]      # dropped on purpose: not "missing"
+        cls._assert_normalize_buffers_initialized(model, stripped_keys=stripped)
         if missing:
             logging.info("Missing keys when loading state dict: %d keys\n%s", len(missing),
                          "\n".join(f"  - {k}" for k in missing))

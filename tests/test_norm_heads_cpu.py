@@ -333,3 +333,33 @@ def test_inference_batches_are_tagged_from_the_config_section():
     assert tag_norm_head({"x": 1}, None) == {"x": 1}
     with pytest.raises(ValueError, match="max_send_message_length_mb"):
         ServerConfig(max_send_message_length_mb=0)
+
+
+def test_stored_statistics_can_be_dropped_or_promoted_on_load(tmp_path, caplog):
+    from safetensors.torch import load_file, save_file
+    from opentau_b200.policies.pretrained import is_norm_buffer_key
+    assert is_norm_buffer_key("normalize_inputs.buffer_state.mean") and is_norm_buffer_key("module.unnormalize_outputs.buffer_actions.std")
+    assert not is_norm_buffer_key("model.normalizer.weight")
+    pol = tiny_pi05()
+    pol.save_pretrained(tmp_path / "ck")
+    # fine-tuning on other data: the checkpoint's statistics are ignored, the fresh ones survive, the flag is consumed
+    fresh = identity_stats()
+    fresh["state"] = {k: (v + 3.0 if k != "count" else v) for k, v in fresh["state"].items()}
+    cfg = tiny_pi05_config(pretrained_path=str(tmp_path / "ck"), skip_normalization_weights=True)
+    with caplog.at_level(logging.INFO):
+        loaded = make_policy(cfg, per_dataset_stats=[fresh])
+    assert "dropped" in caplog.text and cfg.skip_normalization_weights is False
+    name = next(iter(loaded.normalize_inputs.buffer_state.keys()))
+    assert float(loaded.normalize_inputs.buffer_state[name][0, 0]) == float(fresh["state"][name][0])
+    assert float(pol.normalize_inputs.buffer_state[name][0, 0]) == float(fresh["state"][name][0]) - 3.0
+    with pytest.raises(ValueError, match="needs `per_dataset_stats`"):
+        make_policy(tiny_pi05_config(pretrained_path=str(tmp_path / "ck"), skip_normalization_weights=True))
+    # a checkpoint from before the stacked layout: (*feature_shape,) becomes the one row
+    f = tmp_path / "ck" / "model.safetensors"
+    state = load_file(str(f))
+    legacy = {k: (v[0].contiguous() if is_norm_buffer_key(k) else v) for k, v in state.items()}
+    save_file(legacy, str(f))
+    caplog.clear()
+    with caplog.at_level(logging.WARNING):
+        old = make_policy(tiny_pi05_config(pretrained_path=str(tmp_path / "ck")))
+    assert "promoted" in caplog.text and not old._norm_buffers_have_inf()
