@@ -1,8 +1,8 @@
-"""Builds the native libraries in-tree with nvcc for sm_100a.
+"""Builds the native libraries in-tree: CUDA sources with nvcc for sm_100a, host-only C++ with g++.
 
-Each ``csrc/<name>.cu`` becomes ``_native/libotb_<name>.so`` (plain ``extern "C"`` entry points, loaded
-with ctypes — no torch headers, so a full rebuild takes seconds).  Cross-compiles without a GPU.
-Run ``python -m opentau_b200.ops.build`` or call :func:`build_all`.
+Each ``csrc/<name>.cu`` (and each host source of :data:`HOST_SOURCES`) becomes ``_native/libotb_<name>.so`` (plain
+``extern "C"`` entry points, loaded with ctypes — no torch headers, so a full rebuild takes seconds).  Cross-compiles
+without a GPU.  Run ``python -m opentau_b200.ops.build`` or call :func:`build_all`.
 """
 
 from __future__ import annotations
@@ -21,6 +21,32 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC"]
 SOURCES = ["gemm_tcgen05", "elementwise", "train_elementwise", "attention_tcgen05", "attention_bwd_tcgen05", "attention_f32", "stss_corr", "comm_p2p", "noalloc_colsum",
            "gemm_dist_tcgen05", "attention_cp_tcgen05", "gemm_skinny_tcgen05"]
+
+
+#: host-only runtime pieces (no device code): name -> source
+HOST_SOURCES = {"bpe": Path(__file__).parent.parent / "runtime" / "csrc" / "bpe.cpp"}
+CXX_FLAGS = ["-O3", "-std=c++17", "-shared", "-fPIC", "-pthread"]
+
+
+def _cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++"):
+        if cand and (Path(cand).exists() or shutil.which(cand)):
+            return cand
+    raise RuntimeError("no C++ compiler found")
+
+
+def build_host(name: str, force: bool = False) -> Path:
+    src = HOST_SOURCES[name]
+    OUT.mkdir(exist_ok=True)
+    lib, stamp = lib_path(name), OUT / f"{name}.sha256"
+    dig = hashlib.sha256(src.read_bytes() + " ".join(CXX_FLAGS).encode()).hexdigest()
+    if not force and lib.exists() and stamp.exists() and stamp.read_text() == dig:
+        return lib
+    res = subprocess.run([_cxx(), *CXX_FLAGS, "-o", str(lib), str(src)], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"{_cxx()} failed for {src.name}:\n{res.stdout}\n{res.stderr}")
+    stamp.write_text(dig)
+    return lib
 
 
 def _nvcc() -> str:
@@ -68,7 +94,8 @@ def build_one(name: str, force: bool = False, verbose: bool = False) -> Path:
 def build_all(force: bool = False, verbose: bool = False) -> list[Path]:
     names = [n for n in SOURCES if (CSRC / f"{n}.cu").exists()]
     with ThreadPoolExecutor(max_workers=min(8, len(names))) as ex:
-        return list(ex.map(lambda n: build_one(n, force, verbose), names))
+        built = list(ex.map(lambda n: build_one(n, force, verbose), names))
+    return built + [build_host(n, force) for n in HOST_SOURCES]
 
 
 def main() -> None:

@@ -607,6 +607,8 @@ class PI05Policy(PreTrainedPolicy):
         self.language_tokenizer = load_text_tokenizer(config.tokenizer_path, self._vocab_size(config))
         self.discrete_action_processor = load_action_tokenizer(config.discrete_action_tokenizer_path,
                                                                config.discrete_action_vocab_size)
+        # a tokenizer fitted under the other zero-range convention would tokenize padded columns off its corpus
+        self._check_discrete_action_tokenizer_convention(config.discrete_action_tokenizer_path)
         self.model = self.model_class(config, tokenizer=self.language_tokenizer)
         from ..utils import apply_policy_level_freezes
         apply_policy_level_freezes(self.model, self.model.wrapper, config)

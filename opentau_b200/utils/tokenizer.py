@@ -159,7 +159,23 @@ class DctActionTokenizer:
         return out
 
 
+FITTED_TOKENIZER_FILE = "action_tokenizer.json"
+
+
 def load_action_tokenizer(name_or_path: str, vocab_size: int = 2048):
+    """A tokenizer fitted by ``scripts/fit_fast_tokenizer`` (a directory, or the file itself, holding
+    ``action_tokenizer.json``), else a FAST processor from the local transformers cache, else the offline DCT
+    tokenizer.  A fitted table larger than the policy's ``discrete_action_vocab_size`` cannot be embedded and is an
+    error; a smaller one simply leaves ids unused."""
+    from pathlib import Path
+    p = Path(str(name_or_path))
+    fitted = p / FITTED_TOKENIZER_FILE if p.is_dir() else (p if p.is_file() and p.suffix == ".json" else None)
+    if fitted is not None and fitted.is_file():
+        tok = BpeDctActionTokenizer.load(fitted)
+        if tok.vocab_size > vocab_size:
+            raise ValueError(f"the tokenizer at {fitted} has {tok.vocab_size} ids, the policy embeds {vocab_size} "
+                             "(discrete_action_vocab_size): refit with a smaller --vocab-size or widen the policy")
+        return tok
     try:
         from transformers import AutoProcessor
         return AutoProcessor.from_pretrained(name_or_path, trust_remote_code=True, local_files_only=True)
@@ -180,6 +196,73 @@ def pad_tokens(rows: list[list[int]], max_length: int, pad_id: int = 0) -> tuple
             ids[i, :len(r)] = torch.tensor(r, dtype=torch.long)
             mask[i, :len(r)] = True
     return ids, mask
+
+
+_BPE_LIB: list = []          # [handle or None], filled on first use
+
+
+def _bpe_lib():
+    """The native byte-pair library (``runtime/csrc/bpe.cpp``), or ``None`` when it has not been built."""
+    if not _BPE_LIB:
+        import ctypes
+        from ..ops.build import lib_path
+        handle = None
+        f = lib_path("bpe")
+        if f.exists():
+            try:
+                handle = ctypes.CDLL(str(f))
+                i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+                handle.otb_bpe_train.argtypes = [i32p, i64p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
+                                                 ctypes.c_int32, i32p]
+                handle.otb_bpe_train.restype = ctypes.c_int32
+                handle.otb_bpe_encode.argtypes = [i32p, i64p, ctypes.c_int64, i32p, ctypes.c_int32, ctypes.c_int32,
+                                                  i32p, i64p, ctypes.c_int32]
+                handle.otb_bpe_encode.restype = ctypes.c_int32
+            except OSError:
+                handle = None
+        _BPE_LIB.append(handle)
+    return _BPE_LIB[0]
+
+
+def _flatten(seqs: list[list[int]]):
+    import ctypes
+    lens = np.fromiter((len(s) for s in seqs), np.int64, len(seqs))
+    offsets = np.zeros(len(seqs) + 1, np.int64)
+    np.cumsum(lens, out=offsets[1:])
+    flat = np.fromiter((x for s in seqs for x in s), np.int32, int(offsets[-1])) if offsets[-1] else np.zeros(1, np.int32)
+    ptr = lambda a, t: a.ctypes.data_as(ctypes.POINTER(t))  # noqa: E731
+    return flat, offsets, ptr
+
+
+def _native_train(lib, seqs: list[list[int]], base: int, vocab_size: int, min_count: int) -> list[tuple[int, int]]:
+    import ctypes
+    room = max(vocab_size - base, 0)
+    if room == 0 or not seqs:
+        return []
+    flat, offsets, ptr = _flatten(seqs)
+    out = np.zeros(2 * room, np.int32)
+    n = lib.otb_bpe_train(ptr(flat, ctypes.c_int32), ptr(offsets, ctypes.c_int64), len(seqs), base, vocab_size,
+                          min_count, ptr(out, ctypes.c_int32))
+    if n < 0:
+        raise RuntimeError(f"otb_bpe_train refused its arguments ({n})")
+    return [(int(out[2 * i]), int(out[2 * i + 1])) for i in range(n)]
+
+
+def _native_encode(lib, seqs: list[list[int]], merges: list[tuple[int, int]], base: int) -> list[list[int]]:
+    import ctypes
+    import os
+    if not seqs:
+        return []
+    flat, offsets, ptr = _flatten(seqs)
+    table = np.asarray(merges, np.int32).reshape(-1) if merges else np.zeros(2, np.int32)
+    out, out_len = np.zeros_like(flat), np.zeros(len(seqs), np.int64)
+    threads = min(len(seqs), max(1, (os.cpu_count() or 1) // 2), 16)
+    rc = lib.otb_bpe_encode(ptr(flat, ctypes.c_int32), ptr(offsets, ctypes.c_int64), len(seqs),
+                            ptr(table, ctypes.c_int32), len(merges), base, ptr(out, ctypes.c_int32),
+                            ptr(out_len, ctypes.c_int64), threads)
+    if rc != 0:
+        raise RuntimeError(f"otb_bpe_encode refused its arguments ({rc})")
+    return [out[offsets[i]:offsets[i] + out_len[i]].tolist() for i in range(len(seqs))]
 
 
 class BpeDctActionTokenizer:
@@ -230,13 +313,27 @@ class BpeDctActionTokenizer:
                 i += 1
         return out
 
-    def fit(self, chunks, vocab_size: int = 2048, min_count: int = 2) -> "BpeDctActionTokenizer":
-        """``chunks (N, T, D)`` normalised action chunks."""
+    def fit(self, chunks, vocab_size: int = 2048, min_count: int = 2, native: bool | None = None) -> "BpeDctActionTokenizer":
+        """``chunks (N, T, D)`` normalised action chunks.  The most frequent adjacent pair becomes a new symbol, ties go
+        to the smaller left then the smaller right symbol, occurrences merge left to right without overlap; until the
+        vocabulary is full or the best pair occurs fewer than ``min_count`` times.  ``native``: the C++ trainer
+        (``None`` = when its library is built); both give the same table."""
         arr = np.asarray(chunks)
         self.time_horizon, self.action_dim = int(arr.shape[1]), int(arr.shape[2])
         seqs = self._symbols(arr)
-        self.merges = []
-        while self.base + len(self.merges) < vocab_size:
+        lib = _bpe_lib() if native in (None, True) else None
+        if native and lib is None:
+            raise RuntimeError("the native byte-pair library is not built (python -m opentau_b200.ops.build)")
+        if lib is not None:
+            self.merges = _native_train(lib, seqs, self.base, vocab_size, min_count)
+        else:
+            self.merges = self._fit_python(seqs, vocab_size, min_count)
+        self._rank = {m: i for i, m in enumerate(self.merges)}
+        return self
+
+    def _fit_python(self, seqs: list[list[int]], vocab_size: int, min_count: int) -> list[tuple[int, int]]:
+        merges: list[tuple[int, int]] = []
+        while self.base + len(merges) < vocab_size:
             counts: dict[tuple[int, int], int] = {}
             for s in seqs:
                 for a, b in zip(s[:-1], s[1:]):
@@ -246,15 +343,18 @@ class BpeDctActionTokenizer:
             pair, c = max(counts.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))
             if c < min_count:
                 break
-            new_id = self.base + len(self.merges)
-            self.merges.append(pair)
+            new_id = self.base + len(merges)
+            merges.append(pair)
             seqs = [self._merge(s, pair, new_id) for s in seqs]
-        self._rank = {m: i for i, m in enumerate(self.merges)}
-        return self
+        return merges
 
-    def __call__(self, actions) -> list[list[int]]:
+    def __call__(self, actions, native: bool | None = None) -> list[list[int]]:
+        seqs = self._symbols(actions)
+        lib = _bpe_lib() if native in (None, True) else None
+        if lib is not None:
+            return _native_encode(lib, seqs, self.merges, self.base)
         out = []
-        for s in self._symbols(actions):
+        for s in seqs:
             while len(s) > 1:
                 best = min(((self._rank.get((a, b), 1 << 30), i) for i, (a, b) in enumerate(zip(s[:-1], s[1:]))))
                 if best[0] == 1 << 30:
