@@ -17,6 +17,7 @@ table; numeric columns are materialised as torch tensors once), not HF ``dataset
 
 from __future__ import annotations
 
+import contextlib
 import functools
 import io
 import logging
@@ -32,6 +33,7 @@ from torch import Tensor
 from .. import ops
 from .action_indexing import apply_column_index, resolve_delta_map, subtract_chunk_start_state
 from .compute_stats import aggregate_stats, compute_episode_stats, sample_indices
+from .hub_transfer import HubTransferMixin
 from .standard_data_format_mapping import get_mapping
 from .utils import (CODEBASE_VERSION, DEFAULT_CHUNK_SIZE, DEFAULT_FEATURES, DEFAULT_IMAGE_PATH, DEFAULT_PARQUET_PATH,
                     DEFAULT_VIDEO_PATH, EPISODES_PATH, EPISODES_STATS_PATH, INFO_PATH, TASKS_PATH, append_jsonlines,
@@ -65,15 +67,24 @@ def retry_random_on_failure(fn: Callable) -> Callable:
     return wrapped
 
 
-class LeRobotDatasetMetadata:
+class LeRobotDatasetMetadata(HubTransferMixin):
     def __init__(self, repo_id: str, root: str | Path | None = None, revision: str | None = None):
         self.repo_id = repo_id
         self.root = Path(root) if root is not None else HF_HOME / repo_id
         self.revision = revision
         if not (self.root / INFO_PATH).exists():
-            raise FileNotFoundError(
-                f"dataset {repo_id!r} not found under {self.root} (no network here: place the dataset on disk and "
-                "pass `root`)")
+            # not on disk: the metadata folder alone is small, fetch it (the data follows per selected episode)
+            try:
+                self.root.mkdir(parents=True, exist_ok=True)
+                self.pull_from_repo(allow_patterns="meta/")
+            except Exception as exc:  # noqa: BLE001 - offline, unknown repository, no credentials: one message
+                with contextlib.suppress(OSError):
+                    self.root.rmdir()                   # leave no empty folder behind
+                raise FileNotFoundError(
+                    f"dataset {repo_id!r} not found under {self.root} and it could not be fetched from the hub "
+                    f"({type(exc).__name__}: {exc}); place the dataset on disk and pass `root`") from exc
+            if not (self.root / INFO_PATH).exists():
+                raise FileNotFoundError(f"dataset {repo_id!r}: the hub repository has no {INFO_PATH}")
         self.load_metadata()
 
     def load_metadata(self) -> None:
@@ -535,7 +546,7 @@ class BaseDataset(torch.utils.data.Dataset):
 
 
 # ------------------------------------------------------------------------------------------------ reader
-class LeRobotDataset(BaseDataset):
+class LeRobotDataset(BaseDataset, HubTransferMixin):
     def __init__(self, cfg, repo_id: str, root: str | Path | None = None, episodes: list[int] | None = None,
                  image_transforms: Callable | None = None, delta_timestamps: dict[str, list[float]] | None = None,
                  tolerance_s: float = 1e-4, revision: str | None = None, video_backend: str | None = None,
@@ -559,6 +570,9 @@ class LeRobotDataset(BaseDataset):
             self.meta = copy.copy(self.meta)
             self.meta.stats = aggregate_stats([self.meta.episodes_stats[e] for e in selected])
         self.episodes = selected if selected is not None else sorted(self.meta.episodes)
+        self.revision = revision if revision is not None else self.meta.revision
+        self._episodes_were_specified = selected is not None
+        self._fetch_missing_files()
         self.image_transforms = image_transforms
         self.delta_timestamps = {k: np.asarray(v, dtype=np.float64) for k, v in (delta_timestamps or {}).items()}
         self.tolerance_s = tolerance_s
@@ -658,6 +672,20 @@ class LeRobotDataset(BaseDataset):
             return upper
         top = min(frame_in_ep + window, upper)
         return frame_in_ep if top <= frame_in_ep else self._opt_rng.randint(frame_in_ep, top)
+
+    def _fetch_missing_files(self) -> None:
+        """Data (and video) files of the selected episodes that are not under the root are fetched from the hub; a
+        complete root makes no request at all."""
+        files = self.get_episodes_file_paths()
+        missing = [f for f in dict.fromkeys(files) if not (self.root / f).is_file()]
+        if not missing:
+            return
+        try:
+            self.download_episodes(download_videos=True)
+        except Exception as exc:  # noqa: BLE001
+            raise FileNotFoundError(f"dataset {self.repo_id!r}: {len(missing)} file(s) of the selected episodes are not "
+                                    f"under {self.root} (first: {missing[0]}) and could not be fetched from the hub "
+                                    f"({type(exc).__name__}: {exc})") from exc
 
     # -- table ------------------------------------------------------------------------------------------
     def _load_table(self) -> None:

@@ -31,6 +31,12 @@ def is_main_process() -> bool:
     return rank() == 0
 
 
+def is_local_main_process() -> bool:
+    """Rank 0 of THIS node (``LOCAL_RANK``): the one that writes to node-local disks."""
+    import os
+    return int(os.environ.get("LOCAL_RANK", "0") or 0) == 0 if is_dist() else True
+
+
 def wait_for_everyone() -> None:
     if is_dist():
         dist.barrier()

@@ -149,8 +149,81 @@ def test_mixture_with_vqa_and_validation_split(tmp_path):
 
 
 def test_missing_dataset_raises_clear_error(tmp_path):
-    with pytest.raises(FileNotFoundError, match="no network"):
+    with pytest.raises(FileNotFoundError, match="could not be fetched"):
         LeRobotDatasetMetadata("nobody/nothing", root=tmp_path / "absent")
+    assert not (tmp_path / "absent").exists()
+
+
+class _FakeHub:
+    """Serves files out of a source folder and records every call."""
+
+    def __init__(self, source):
+        self.source, self.calls = source, []
+
+    def snapshot_download(self, repo_id, *, revision, local_dir, allow_patterns=None, ignore_patterns=None):
+        import shutil
+        self.calls.append(("snapshot", allow_patterns, ignore_patterns))
+        for f in self.source.rglob("*"):
+            rel = f.relative_to(self.source).as_posix()
+            if not f.is_file() or (allow_patterns and not rel.startswith(allow_patterns)) \
+                    or (ignore_patterns and rel.startswith(ignore_patterns)):
+                continue
+            (local_dir / rel).parent.mkdir(parents=True, exist_ok=True)
+            shutil.copy(f, local_dir / rel)
+
+    def download_file(self, repo_id, filename, *, revision, local_dir):
+        import shutil
+        self.calls.append(("file", filename))
+        (local_dir / filename).parent.mkdir(parents=True, exist_ok=True)
+        shutil.copy(self.source / filename, local_dir / filename)
+
+    def create_repo(self, repo_id, *, private):
+        self.calls.append(("create_repo", repo_id, private))
+
+    def create_branch(self, repo_id, branch, *, revision):
+        self.calls.append(("create_branch", branch))
+
+    def upload_folder(self, repo_id, folder, *, revision, allow_patterns=None, ignore_patterns=None, large=False):
+        self.calls.append(("upload_folder", str(folder), revision, tuple(ignore_patterns), large))
+
+    def file_exists(self, repo_id, filename, *, revision):
+        return False
+
+    def upload_text(self, repo_id, filename, text, *, revision):
+        self.calls.append(("upload_text", filename, text))
+
+    def retag(self, repo_id, tag, *, revision):
+        self.calls.append(("retag", tag, revision))
+
+
+def test_hub_transfer_fetches_only_what_is_missing(tmp_path):
+    from opentau_b200.datasets.hub_transfer import set_hub_client
+    _record(tmp_path / "origin", use_videos=True)
+    hub = _FakeHub(tmp_path / "origin")
+    set_hub_client(hub)
+    try:
+        # nothing on disk: the metadata folder comes first, then exactly the selected episodes' files
+        meta = LeRobotDatasetMetadata("local/toy", root=tmp_path / "copy")
+        assert hub.calls == [("snapshot", "meta/", None)] and meta.total_episodes == 3
+        cfg = _cfg(tmp_path / "copy")
+        ds = LeRobotDataset(cfg, "local/toy", root=tmp_path / "copy", episodes=[1])
+        fetched = sorted(c[1] for c in hub.calls if c[0] == "file")
+        assert fetched == ["data/chunk-000/episode_000001.parquet", "videos/chunk-000/observation.images.top/episode_000001.mp4"]
+        assert len(ds) == 9
+        hub.calls.clear()
+        LeRobotDataset(cfg, "local/toy", root=tmp_path / "copy", episodes=[1])           # complete: no request at all
+        assert hub.calls == []
+        LeRobotDataset(cfg, "local/toy", root=tmp_path / "copy")                         # all episodes: one snapshot
+        assert hub.calls == [("snapshot", None, None)]
+        hub.calls.clear()
+        ds.push_to_hub(branch="v2", tags=["toy"], push_videos=False, private=True)
+        kinds = [c[0] for c in hub.calls]
+        assert kinds == ["create_repo", "create_branch", "upload_folder", "upload_text", "retag"]
+        assert hub.calls[2][3] == ("images/", "videos/") and hub.calls[2][2] == "v2"
+        card = hub.calls[3][2]
+        assert card.startswith("---") and "- toy" in card and "| total_episodes | 3 |" in card and "| robot_type | toybot |" in card
+    finally:
+        set_hub_client(None)
 
 
 def test_push_to_hub_helpers(tmp_path):
