@@ -62,6 +62,8 @@ class TrainPipelineConfig:
     eval: EvalConfig = field(default_factory=EvalConfig)
     eval_freq: int = 0
     val_freq: int = 0
+    # None: a validation pass scores the WHOLE validation split (every sample once); a number caps the batches per rank
+    val_max_batches: int | None = None
     last_checkpoint_only: bool = True
     running_best_count: int = 0
     running_best_metric: str = "auto"

@@ -223,6 +223,20 @@ class DatasetMixtureMetadata:
         self.policy_features = self._features(datasets[0])
         self.stats = self.per_norm_key_stats[0] if self.per_norm_key_stats else {}
 
+    def aggregated_action_stats(self, weights: Sequence[float] | None = None) -> dict[str, np.ndarray]:
+        """ONE set of action statistics for the whole mixture (the few consumers that need a single range, such as a
+        tokenizer fitted under global normalisation).  Heads without ``actions`` are left out together with their
+        weight, so the parallel lists cannot slip against each other."""
+        w = list(weights) if weights is not None else [1.0] * len(self.per_norm_key_stats)
+        rows = [({"actions": s["actions"]}, wi, k) for s, wi, k in zip(self.per_norm_key_stats, w, self.norm_keys)
+                if s and "actions" in s]
+        if not rows:
+            raise ValueError("no head of the mixture has 'actions' statistics")
+        if len(rows) == 1:
+            return dict(rows[0][0]["actions"])
+        return _aggregate_stats([r[0] for r in rows], weights=[r[1] for r in rows],
+                                contributor_names=[r[2] for r in rows], context="mixture-wide action statistics")["actions"]
+
     @staticmethod
     def _total_frames(ds) -> int:
         info = getattr(getattr(ds, "meta", None), "info", None) or {}
@@ -311,6 +325,20 @@ class _MixtureStream(IterableDataset):
             yield self.m.get_global(gi)
 
 
+class _SequentialShard(Dataset):
+    """Every ``world``-th sample of the concatenated mixture, starting at ``rank``: each sample is visited once."""
+
+    def __init__(self, mixture: "WeightedDatasetMixture", rank: int, world: int):
+        self.m, self.rank, self.world = mixture, rank, world
+
+    def __len__(self) -> int:
+        n = len(self.m)
+        return (n - self.rank + self.world - 1) // self.world if n > self.rank else 0
+
+    def __getitem__(self, i: int) -> dict[str, Any]:
+        return self.m.get_global(self.rank + i * self.world)
+
+
 class WeightedDatasetMixture:
     def __init__(self, datasets: Sequence[Dataset], names: Sequence[str], weights: Sequence[float] | None = None,
                  norm_keys: Sequence[str] | None = None, seed: int = 1000, action_freq: float | None = None):
@@ -343,3 +371,37 @@ class WeightedDatasetMixture:
             kw.update(prefetch_factor=prefetch_factor or 2, persistent_workers=True)
         return DataLoader(_MixtureStream(self, rank, world), batch_size=batch_size, num_workers=num_workers,
                           collate_fn=collate_standard, pin_memory=pin, drop_last=True, **kw)
+
+    def get_combined_val_dataloader(self, batch_size: int, num_workers: int = 0, rank: int = 0, world: int = 1,
+                                    prefetch_factor: int | None = None) -> DataLoader | None:
+        """ONE deterministic sequential loader over the whole mixture (validation): no shuffling, no dropped tail,
+        every sample scored exactly once, and every rank's shard is full even when a member has fewer frames than
+        there are ranks (one loader per dataset would leave most ranks idle on small members, member after member).
+        Each sample carries ``dataset_index`` / ``dataset_repo_id``, so the caller can split the metrics per head and
+        per dataset afterwards.  ``None`` for an empty mixture
+        (reference ``src/opentau/datasets/dataset_mixture.py:1229-1270``)."""
+        if len(self) == 0:
+            logging.info("combined validation loader skipped: the mixture is empty")
+            return None
+        kw: dict[str, Any] = {}
+        if num_workers > 0:
+            kw.update(prefetch_factor=prefetch_factor or 2)
+        return DataLoader(_SequentialShard(self, rank, world), batch_size=batch_size, shuffle=False,
+                          num_workers=num_workers, collate_fn=collate_standard, pin_memory=torch.cuda.is_available(),
+                          drop_last=False, **kw)
+
+    def get_per_dataset_dataloaders(self, batch_size: int, num_workers: int = 0,
+                                    prefetch_factor: int | None = None) -> dict[str, DataLoader]:
+        """One sequential loader per member (per-dataset evaluation: each member once, in order); empty members are
+        skipped (reference ``dataset_mixture.py:1194-1227``)."""
+        kw: dict[str, Any] = {}
+        if num_workers > 0:
+            kw.update(prefetch_factor=prefetch_factor or 2)
+        out: dict[str, DataLoader] = {}
+        for name, ds in zip(self.names, self.datasets):
+            if len(ds) == 0:
+                logging.info("no per-dataset loader for the empty dataset %r", name)
+                continue
+            out[name] = DataLoader(ds, batch_size=batch_size, shuffle=False, num_workers=num_workers,
+                                   collate_fn=collate_standard, pin_memory=torch.cuda.is_available(), drop_last=False, **kw)
+        return out

@@ -67,6 +67,31 @@ def gather_tensors(t: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
     return out
 
 
+def gather_ragged(t: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """Like :func:`gather_tensors` when the ranks hold DIFFERENT numbers of rows (the last shard of a sequential pass):
+    the lengths are exchanged first, every rank pads to the longest, and the padding is cut out after the gather, so
+    all keys stay row-aligned.  Every key of one rank must have the same number of rows."""
+    if not is_dist():
+        return dict(t)
+    keys = sorted(t)
+    n = int(t[keys[0]].shape[0]) if keys else 0
+    dev = t[keys[0]].device if keys else torch.device("cpu")
+    mine = torch.tensor([n], dtype=torch.long, device=dev)
+    lens = [torch.zeros_like(mine) for _ in range(world_size())]
+    dist.all_gather(lens, mine)
+    lens = [int(x) for x in lens]
+    longest = max(lens)
+    out = {}
+    for k in keys:
+        v = t[k].contiguous()
+        if v.shape[0] < longest:
+            v = torch.cat([v, v.new_zeros((longest - v.shape[0], *v.shape[1:]))])
+        parts = [torch.empty_like(v) for _ in range(world_size())]
+        dist.all_gather(parts, v)
+        out[k] = torch.cat([p_[:m] for p_, m in zip(parts, lens)], 0)
+    return out
+
+
 def reduce_sum(t: torch.Tensor) -> torch.Tensor:
     if is_dist():
         t = t.clone()

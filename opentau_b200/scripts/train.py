@@ -131,33 +131,78 @@ def mixture_weighted_aggregate(buckets: dict[str, dict[str, float]], weights: di
 
 
 @torch.no_grad()
-def run_validation(policy, loader, n_batches: int, device, names: list[str], weights: dict[str, float],
-                   loss_weights: dict[str, float]) -> dict[str, float]:
+def run_validation(policy, loader, n_batches: int | None, device, names: list[str], weights: dict[str, float],
+                   loss_weights: dict[str, float], dataset_names: list[str] | None = None) -> dict[str, float]:
+    """One pass over ``loader`` (all of it, or ``n_batches`` per rank) without gradients.
+
+    Policies whose ``forward`` takes ``return_per_sample`` report per-sample ``(sum, count)`` losses; those are
+    gathered from all ranks (the ranks' last shards may differ in length) and split per normalisation head
+    (``Validation/<head>/...``, the headline) and per source dataset (``Validation/by_dataset/<name>/...``: nothing is
+    lost where datasets share a head).  The overall ``Validation/Loss`` weights the heads like the TRAINING mixture, so
+    it is not dominated by whichever head has the most validation frames.  Other policies (planners, value heads) get
+    the batch-mean aggregate only; their optional ``L1`` / ``Accuracy`` outputs are averaged
+    (reference ``src/opentau/scripts/train.py:1225-1436``)."""
+    import inspect
+    was_training = policy.training
     policy.eval()
-    acc: dict[str, list[Tensor]] = {k: [] for k in ("MSE_sum", "MSE_count", "CE_sum", "CE_count", "idx")}
-    it = iter(loader)
-    for _ in range(n_batches):
-        try:
-            batch = to_device(next(it), device)
-        except StopIteration:
+    per_sample_ok = "return_per_sample" in inspect.signature(policy.forward).parameters
+    keys = ("MSE_sum", "MSE_count", "CE_sum", "CE_count", "idx", "src")
+    acc: dict[str, list[Tensor]] = {k: [] for k in keys}
+    plain: dict[str, list[Tensor]] = {"MSE": [], "CE": [], "L1": [], "Accuracy": []}
+    src_of = {n: i for i, n in enumerate(dataset_names or [])}
+    threshold = getattr(getattr(policy, "config", None), "warn_outlier_threshold", None)
+    for bi, raw in enumerate(loader):
+        if n_batches is not None and bi >= n_batches:
             break
-        out = policy(batch, return_per_sample=True)
-        for key in ("MSE", "CE"):
-            ps = out.get(f"{key}_per_sample")
-            B = batch["state"].shape[0]
-            s, c = ps if ps is not None else (torch.zeros(B, device=device), torch.zeros(B, device=device))
-            acc[f"{key}_sum"].append(s.float()), acc[f"{key}_count"].append(c.float())
-        acc["idx"].append(batch.get("dataset_index", torch.zeros(batch["state"].shape[0], dtype=torch.long, device=device)))
-    policy.train()
-    if not acc["idx"]:
-        return {}
-    flat = control.gather_tensors({k: torch.cat(v) for k, v in acc.items()})
-    buckets = bucket_per_sample(flat, flat["idx"], names)
+        batch = to_device(raw, device)
+        out = policy(batch, return_per_sample=True) if per_sample_ok else policy(batch)
+        records = out.pop("outlier_records", []) if isinstance(out, dict) else []
+        if threshold is not None and threshold > 0:
+            from ..policies.outlier_utils import log_outlier_records_distributed
+            log_outlier_records_distributed(records, threshold)
+        B = next(v.shape[0] for v in batch.values() if isinstance(v, Tensor) and v.dim() > 0)
+        for key in ("L1", "Accuracy"):
+            if key in out:
+                plain[key].append(out[key].detach().float().reshape(1))
+        if per_sample_ok and out.get("MSE_per_sample") is not None:
+            for key in ("MSE", "CE"):
+                ps = out.get(f"{key}_per_sample")
+                s_, c_ = ps if ps is not None else (torch.zeros(B, device=device), torch.zeros(B, device=device))
+                acc[f"{key}_sum"].append(s_.float()), acc[f"{key}_count"].append(c_.float())
+            acc["idx"].append(torch.as_tensor(batch.get("dataset_index", torch.zeros(B, dtype=torch.long)),
+                                              device=device).long().reshape(-1))
+            repo = batch.get("dataset_repo_id")
+            acc["src"].append(torch.tensor([src_of.get(r, -1) for r in repo], dtype=torch.long, device=device)
+                              if repo is not None and src_of else torch.full((B,), -1, dtype=torch.long, device=device))
+        else:
+            for key in ("MSE", "CE"):
+                if key in out:
+                    plain[key].append(out[key].detach().float().reshape(1))
+    policy.train(was_training)
     metrics: dict[str, float] = {}
-    for name, row in buckets.items():
-        metrics[f"Validation/{name}/MSE Loss"] = row["MSE"]
-        metrics[f"Validation/{name}/CE Loss"] = row["CE"]
-    agg = mixture_weighted_aggregate(buckets, weights)
+    for key, label in (("L1", "Validation/L1 Loss"), ("Accuracy", "Validation/Accuracy")):
+        if plain[key]:
+            metrics[label] = float(control.gather_ragged({"v": torch.cat(plain[key])})["v"].mean())
+    if acc["idx"]:
+        flat = control.gather_ragged({k: torch.cat(v) for k, v in acc.items()})
+        buckets = bucket_per_sample(flat, flat["idx"], names)
+        for name, row in buckets.items():
+            metrics[f"Validation/{name}/MSE Loss"] = row["MSE"]
+            metrics[f"Validation/{name}/CE Loss"] = row["CE"]
+            metrics[f"Validation/{name}/Loss"] = loss_weights.get("MSE", 1.0) * row["MSE"] + loss_weights.get("CE", 1.0) * row["CE"]
+        if dataset_names and bool((flat["src"] >= 0).any()):
+            for name, row in bucket_per_sample(flat, flat["src"], dataset_names).items():
+                metrics[f"Validation/by_dataset/{name}/MSE Loss"] = row["MSE"]
+                metrics[f"Validation/by_dataset/{name}/CE Loss"] = row["CE"]
+                metrics[f"Validation/by_dataset/{name}/Loss"] = (loss_weights.get("MSE", 1.0) * row["MSE"]
+                                                                 + loss_weights.get("CE", 1.0) * row["CE"])
+        agg = mixture_weighted_aggregate(buckets, weights)
+        metrics["Validation/Num Samples"] = float(flat["idx"].shape[0])
+    elif plain["MSE"] or plain["CE"]:
+        agg = {k: (float(control.gather_ragged({"v": torch.cat(plain[k])})["v"].mean()) if plain[k] else 0.0)
+               for k in ("MSE", "CE")}
+    else:
+        return metrics
     metrics["Validation/MSE Loss"], metrics["Validation/CE Loss"] = agg["MSE"], agg["CE"]
     metrics["Validation/Loss"] = loss_weights.get("MSE", 1.0) * agg["MSE"] + loss_weights.get("CE", 1.0) * agg["CE"]
     return metrics
@@ -331,9 +376,10 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
             tracker.reset_averages()
 
         if is_val:
-            vloader = val_mix.get_dataloader(micro_bs, 0, rank, world)
-            n_val = max(1, min(8, len(val_mix) // max(1, micro_bs * world)))
-            vm = run_validation(policy, vloader, n_val, device, names, head_w, cfg.loss_weighting)
+            # deterministic and complete: every validation sample once, strided over the ranks
+            vloader = val_mix.get_combined_val_dataloader(micro_bs, cfg.num_workers, rank, world, cfg.prefetch_factor)
+            vm = run_validation(policy, vloader, cfg.val_max_batches, device, names, head_w, cfg.loss_weighting,
+                                dataset_names=list(val_mix.names)) if vloader is not None else {}
             metrics.update(vm)
             if is_main and vm:
                 logging.info("validation @%d: loss %.4f (MSE %.4f, CE %.4f)", step, vm["Validation/Loss"],

@@ -111,3 +111,64 @@ def test_train_and_resume_with_sharded_parameters(tmp_path):
     resumed = train(_cfg(out, 6, resume=True, distributed={"strategy": "fsdp"}, val_freq=0))
     rows = [json.loads(line) for line in (out / "metrics.jsonl").read_text().splitlines()]
     assert rows[-1]["step"] == 6 and resumed["loss"] < rows[0]["Training/Loss"] * 1.5
+
+
+def test_validation_pass_is_complete_and_split_by_head_and_dataset(tmp_path):
+    """Two synthetic members under different heads: every validation sample is scored once, per head and per
+    dataset, and the headline is weighted like the training mixture."""
+    from opentau_b200.datasets.factory import make_dataset_mixture
+    from opentau_b200.policies.factory import make_policy
+    from opentau_b200.scripts.train import run_validation
+    cfg = _cfg(tmp_path / "o", 1)
+    cfg.dataset_mixture.datasets.append(type(cfg.dataset_mixture.datasets[0])(
+        synthetic={"length": 40, "state_dim": 6, "action_dim": 6, "name": "b"}))
+    cfg.dataset_mixture.weights = [3.0, 1.0]
+    train_mix, val_mix = make_dataset_mixture(cfg)
+    assert len(val_mix) == 16 + 10
+    shards = [val_mix.get_combined_val_dataloader(4, rank=r, world=3).dataset for r in range(3)]
+    seen = sorted((s[i]["source"], int(s[i]["frame_index"]) + 100 * int(s[i]["episode_index"]))
+                  for s in shards for i in range(len(s)))
+    assert len(seen) == 26 and len(set(seen)) == 26                       # a partition: nothing twice, nothing lost
+    assert sorted(val_mix.get_per_dataset_dataloaders(4)) == sorted(val_mix.names)
+    policy = make_policy(cfg.policy, ds_meta=train_mix.meta)
+    names = list(train_mix.meta.dataset_names)
+    weights = {names[train_mix.meta.dataset_to_norm_index[n]]: w / 4.0 for n, w in zip(train_mix.names, train_mix.weights)}
+    loader = val_mix.get_combined_val_dataloader(4)
+    m = run_validation(policy, loader, None, torch.device("cpu"), names, weights, {"MSE": 1.0, "CE": 1.0},
+                       dataset_names=list(val_mix.names))
+    assert m["Validation/Num Samples"] == 26.0
+    for n in names:
+        assert f"Validation/{n}/Loss" in m
+    for n in val_mix.names:
+        assert f"Validation/by_dataset/{n}/MSE Loss" in m
+    expect = sum(weights[n] * m[f"Validation/{n}/MSE Loss"] for n in names)
+    assert abs(m["Validation/MSE Loss"] - expect) < 1e-6
+    capped = run_validation(policy, loader, 2, torch.device("cpu"), names, weights, {"MSE": 1.0, "CE": 1.0})
+    assert capped["Validation/Num Samples"] == 8.0 and not any("by_dataset" in k for k in capped)
+    assert policy.training                                                  # the mode it came in with is restored
+    agg = train_mix.meta.aggregated_action_stats([3.0, 1.0])
+    assert agg["mean"].shape == (32,)
+
+
+def _ragged_rank(rank, world, port, ret):
+    import os
+
+    import torch.distributed as dist
+
+    from opentau_b200.parallel import control
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n = 3 if rank == 0 else 1
+    out = control.gather_ragged({"a": torch.arange(n, dtype=torch.float32) + 10 * rank,
+                                 "b": torch.full((n, 2), rank, dtype=torch.long)})
+    ret[rank] = (out["a"].tolist(), out["b"][:, 0].tolist())
+    dist.destroy_process_group()
+
+
+def test_ragged_gather_keeps_rows_aligned_across_ranks():
+    import torch.multiprocessing as mp
+
+    from helpers import free_port
+    ret = mp.Manager().dict()
+    mp.spawn(_ragged_rank, args=(2, free_port(), ret), nprocs=2, join=True)
+    assert ret[0] == ret[1] == ([0.0, 1.0, 2.0, 10.0], [0, 0, 0, 1])
