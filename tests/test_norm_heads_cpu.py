@@ -363,3 +363,41 @@ def test_stored_statistics_can_be_dropped_or_promoted_on_load(tmp_path, caplog):
     with caplog.at_level(logging.WARNING):
         old = make_policy(tiny_pi05_config(pretrained_path=str(tmp_path / "ck")))
     assert "promoted" in caplog.text and not old._norm_buffers_have_inf()
+
+
+def test_zero_variance_guard_reports_real_deviations_once(caplog):
+    from opentau_b200.configs.types import FeatureType, NormalizationMode, PolicyFeature
+    from opentau_b200.policies import normalize as nz
+    nz._WARNED_SNAPS.clear()
+    stats = {"state": {"mean": np.array([1.0, 5.0, 0.0], np.float32), "std": np.array([2.0, 0.0, 0.0], np.float32),
+                       "min": np.array([0.0, 5.0, 0.0], np.float32), "max": np.array([2.0, 5.0, 0.0], np.float32)}}
+    feats = {"state": PolicyFeature(FeatureType.STATE, (3,))}
+    for mode in (NormalizationMode.MEAN_STD, NormalizationMode.MIN_MAX):
+        nz._WARNED_SNAPS.clear()
+        caplog.clear()
+        norm = nz.Normalize(feats, {"STATE": mode}, per_dataset_stats=[stats], dataset_names=["arm::joint"])
+        with caplog.at_level(logging.WARNING):
+            ok = norm({"state": torch.tensor([[1.0, 5.0, 0.0]])})["state"]            # constant dims hold their constant
+            assert "zero-variance" not in caplog.text and torch.isfinite(ok).all()
+            bad = norm({"state": torch.tensor([[1.0, 5.5, 0.0]])})["state"]           # dim 1 deviates by 0.5
+        assert "dim(s) [1]" in caplog.text and "arm::joint" in caplog.text
+        assert float(bad.abs().max()) < 10.0                                           # no division by ~eps
+        caplog.clear()
+        with caplog.at_level(logging.WARNING):
+            norm({"state": torch.tensor([[1.0, 5.3, 0.0]])})                          # smaller than already reported
+            assert "zero-variance" not in caplog.text
+            norm({"state": torch.tensor([[1.0, 7.0, 0.0]])})                          # larger: reported again
+            assert "zero-variance" in caplog.text
+    healthy = nz.Normalize(feats, {"STATE": NormalizationMode.MEAN_STD}, per_dataset_stats=[
+        {"state": {k: np.ones(3, np.float32) for k in ("mean", "std", "min", "max")}}])
+    healthy({"state": torch.zeros(1, 3)})
+    assert healthy._snap_active is False
+    # QUANTILE never degrades to min / max
+    with pytest.raises(KeyError, match="QUANTILE normalisation needs"):
+        nz.Normalize(feats, {"STATE": NormalizationMode.QUANTILE}, per_dataset_stats=[stats])
+    caplog.clear()
+    nz._WARNED_MISSING.clear()
+    with caplog.at_level(logging.WARNING):
+        healthy({"other": torch.zeros(1)})
+        healthy({"other": torch.zeros(1)})
+    assert caplog.text.count("'state' was missing from the batch during normalization") == 1
