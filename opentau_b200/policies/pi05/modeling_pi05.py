@@ -475,8 +475,66 @@ class PI05FlowMatching(nn.Module):
         self._mrope = pos.dim() == 3
         _, cache = self.wrapper(inputs_embeds=[prefix_embs, None], position_ids=pos, q_blk=blk,
                                               q_valid=valid, fill_cache_len=prefix_embs.shape[1], mrope=self._mrope,
-                                              cache_room=self.config.chunk_size + 8)   # the suffix appends in place
-        return cache, self.suffix_offset(pos, prefix_pad, prefix_embs.shape[1])
+                                              cache_room=self.config.chunk_size + 8 + self._response_room())
+        return cache, self.suffix_offset(pos, prefix_pad, prefix_embs.shape[1])   # (the suffix appends in place)
+
+    def _response_room(self) -> int:
+        return int(self.config.response_max_length) if self.config.predict_response else 0
+
+    @torch.no_grad()
+    def generate_response(self, cache: KVCache, prefix_len: Tensor) -> tuple[KVCache, Tensor, Tensor, Tensor]:
+        """Greedy decoding of the response (the subtask / reasoning text) behind the cached prefix, one token per pass
+        of the backbone alone, each token's keys / values appended to the cache so that the action expert then attends
+        to the generated text (reference ``src/opentau/policies/pi05/modeling_pi05.py:1974-1999, 2122-2236``).
+
+        The first token is ``<bos>``; every later one is the arg-max of the language head on the previous token's
+        output.  Once a sample has produced ``<eos>`` (or a pad) its further tokens are pads, marked invalid in the
+        cache and given no position.  Always ``response_max_length`` passes, no host synchronisation, so the loop can
+        be captured in a CUDA graph.  Returns the longer cache, the per-sample first position of the action suffix,
+        the tokens ``(B, L)`` and their validity mask."""
+        cfg, pwe, tok = self.config, self.wrapper, self.language_tokenizer
+        B, device = prefix_len.shape[0], prefix_len.device
+        bos, eos, pad = tok.bos_token_id, tok.eos_token_id, tok.pad_token_id
+        if bos is None or eos is None or pad is None:
+            raise ValueError("response generation needs a tokenizer with bos, eos and pad ids")
+        mrope = getattr(self, "_mrope", False)
+        tokens = torch.empty(B, 0, dtype=torch.long, device=device)
+        masks = torch.empty(B, 0, dtype=torch.bool, device=device)
+        offset = prefix_len.clone()
+        out = None
+        for step in range(cfg.response_max_length):
+            if step == 0:
+                nxt = torch.full((B, 1), bos, dtype=torch.long, device=device)
+            else:
+                nxt = ops.linear(out[:, -1:], pwe.lm_head_weight()).float().argmax(dim=-1)
+            if tokens.shape[1] > 1:
+                done = ((tokens == eos) | (tokens == pad)).any(dim=1, keepdim=True)
+                live = ~done
+                nxt = torch.where(live, nxt, torch.full_like(nxt, pad))
+            else:
+                live = torch.ones(B, 1, dtype=torch.bool, device=device)
+            tokens, masks = torch.cat([tokens, nxt], 1), torch.cat([masks, live], 1)
+            emb = pwe.embed_language_tokens(nxt)
+            pos = offset                                            # a finished sample's pad takes no new position
+            offset = offset + live.long()
+            blk, valid = ops.make_block_ids(live, torch.ones(B, 1, dtype=torch.long, device=device))
+            (out, _), new = self.wrapper(inputs_embeds=[emb, None], position_ids=pos[None].expand(3, -1, -1) if mrope else pos,
+                                         q_blk=blk, q_valid=valid, past=cache, fill_cache_len=1, mrope=mrope)
+            cache = self._append_cache(cache, new, live)
+        return cache, offset, tokens, masks
+
+    @staticmethod
+    def _append_cache(cache: KVCache, new: KVCache, valid: Tensor) -> KVCache:
+        """``cache`` with the ``new.length`` tokens of ``new`` behind it: in place while the buffers have room."""
+        n, at = new.length, cache.length
+        if cache.writable_room() >= n:
+            k, v = cache.k, cache.v
+            k[:, :, at:at + n].copy_(new.k[:, :, :n])
+            v[:, :, at:at + n].copy_(new.v[:, :, :n])
+        else:
+            k = torch.cat([cache.k[:, :, :at], new.k[:, :, :n]], dim=2)
+            v = torch.cat([cache.v[:, :, :at], new.v[:, :, :n]], dim=2)
+        return KVCache(k, v, torch.cat([cache.valid[:, :at], valid], dim=1), at + n)
 
     @staticmethod
     def suffix_offset(pos: Tensor, prefix_pad: Tensor, n_cross: int) -> Tensor:
@@ -568,6 +626,11 @@ class PI05FlowMatching(nn.Module):
                              f"(got {tuple(noise.shape)})")
         cache, prefix_len = self.prefill(images, img_masks, lang_tokens, lang_masks, state=state,
                                          prefix_kwargs=prefix_kwargs)
+        self.last_response_tokens = self.last_response_masks = None
+        if cfg.predict_response:
+            # before the candidates fan out: the decode is greedy and independent of the noise, so all candidates
+            # share one response, and it extends the very cache that is widened below
+            cache, prefix_len, self.last_response_tokens, self.last_response_masks = self.generate_response(cache, prefix_len)
         if n_candidates > 1:
             cache = cache.expand_batch(n_candidates)
             prefix_len = prefix_len.repeat_interleave(n_candidates, 0)
@@ -785,7 +848,7 @@ class PI05Policy(PreTrainedPolicy):
         meter = make_meter(self, batch_size=B * n, device=device, dataset_index=sampler_idx)
         st = state if cfg.state_type == "continuous" else None
         # the meter keeps host-side step counts, which a replayed graph would not advance: metered calls run eagerly
-        if getattr(self, "_use_graphs", False) and device.type == "cuda" and meter is None:
+        if getattr(self, "_use_graphs", False) and device.type == "cuda" and meter is None and not cfg.predict_response:
             actions = self._graphed_sample(images, img_masks, lang_tokens, lang_masks, action_prefix, delay, noise,
                                            st, n)
         else:
@@ -793,6 +856,7 @@ class PI05Policy(PreTrainedPolicy):
                                                 action_prefix=action_prefix, delay=delay, noise=noise, state=st,
                                                 n_candidates=n, accel=meter,
                                                 prefix_kwargs=self._prefix_kwargs(batch, nb))
+        self.last_response = self._decode_response()
         if n == 1:
             # before the un-normalisation: if that raises (non-finite buffers) the score is still there
             publish(self, meter, dataset_index=idx)
@@ -814,6 +878,16 @@ class PI05Policy(PreTrainedPolicy):
         warn_if_no_candidate_scored(self.last_candidate_scores)
         publish(self, meter, dataset_index=sampler_idx, n_candidates=n, selected=selected)
         return pick(candidates, selected)
+
+    def _decode_response(self) -> list[str] | None:
+        """The text the backbone generated for the last chunk (one string per observation), ``None`` when the policy
+        does not predict responses; servers and planners read it from ``last_response``."""
+        toks = getattr(self.model, "last_response_tokens", None)
+        if toks is None:
+            return None
+        masks = self.model.last_response_masks
+        rows = [t[m].tolist() for t, m in zip(toks.cpu(), masks.cpu())]
+        return [self.language_tokenizer.decode(r, skip_special_tokens=True) for r in rows]
 
     def _delta_anchor_state(self, batch: dict[str, Any]) -> Tensor | None:
         """The RAW (un-normalised) state the emitted chunk is anchored to, when the policy was trained on delta joint
