@@ -164,3 +164,35 @@ def test_loss_curves_of_native_and_oracle_paths_agree(monkeypatch):
     # trajectories drift apart in RELATIVE terms, so the whole curve is held to a tolerance in units of the initial loss
     scaled = [abs(x - y) / o[0] for x, y in zip(a, o)]
     assert max(rel[:10]) < 0.03 and max(scaled) < 0.03, (max(rel[:10]), max(scaled), max(rel))
+
+
+def test_response_decoding_on_the_gpu_matches_the_teacher_forced_pass():
+    """The token-by-token decode appends keys / values in place behind the prefix through the fused kernels; one full
+    pass over the same text must predict the same tokens."""
+    from helpers import tiny_pi05
+    from opentau_b200 import ops
+    pol = tiny_pi05(predict_response=True, response_max_length=6).to(DEV).to(torch.bfloat16).eval()
+    model, cfg = pol.model, pol.config
+    b = _to_dev(tiny_batch())
+    B = b["state"].shape[0]
+    actions = pol.sample_actions(b)
+    toks, masks = model.last_response_tokens, model.last_response_masks
+    assert toks.shape == (B, 6) and torch.isfinite(actions.float()).all() and len(pol.last_response) == B
+    idx = pol._resolve_dataset_index(b, B, b["state"].device)
+    nb = pol.normalize_inputs(b, idx)
+    images, img_masks = pol.prepare_images(nb)
+    lang_tokens, lang_masks = pol.prepare_language(nb)
+    embs, pad, att, pos = model.embed_prefix(images, img_masks, lang_tokens, lang_masks, response_tokens=toks,
+                                             response_masks=masks)
+    blk, valid = ops.make_block_ids(pad, att)
+    pos = torch.cumsum(pad, dim=1) - 1 if pos is None else pos
+    with torch.no_grad():
+        (out, _), _ = model.wrapper(inputs_embeds=[embs, None], position_ids=pos, q_blk=blk, q_valid=valid)
+    logits = ops.linear(out[:, -6:], model.wrapper.lm_head_weight()).float()
+    top2 = logits.topk(2, dim=-1)
+    for i in range(5):
+        live = masks[:, i + 1]
+        same = top2.indices[:, i, 0] == toks[:, i + 1]
+        # bf16: a near-tie between the two best logits may flip between the incremental and the full pass
+        near_tie = (top2.values[:, i, 0] - top2.values[:, i, 1]) < 0.05 * top2.values[:, i, 0].abs().clamp(min=1.0)
+        assert bool((same | near_tie | ~live).all()), i
