@@ -247,6 +247,16 @@ class PreTrainedConfig(ChoiceRegistry, abc.ABC):
                 out[key] = (int(shape[1]), int(shape[2]))
         return out
 
+    @property
+    def input_image_size(self) -> tuple[int, int] | None:
+        """``(H, W)`` at which frames reach the vision tower: the resize target, or (native pass-through) the one
+        resolution the image features were bound at; ``None`` when that is unknown or mixed."""
+        target = getattr(self, "resize_imgs_with_padding", None)
+        if target is not None:
+            return tuple(int(x) for x in target)
+        bound = set(self._bound_image_resolutions().values())
+        return next(iter(bound)) if len(bound) == 1 else None
+
     def validate_input_resolution(self, *, strict: bool) -> None:
         """``resize_imgs_with_padding`` must equal the resolution of the bound image features, else every frame is
         letterboxed a second time inside the policy; with ``None`` (native pass-through) all cameras must agree with

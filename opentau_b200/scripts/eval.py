@@ -43,9 +43,47 @@ def resolve_env_config(env: Any) -> EnvConfig:
     raise TypeError(f"cannot build an environment from {type(env).__name__}")
 
 
-def _rank_seed_offset(rank: int, decorrelate: bool) -> int:
-    """Ranks evaluate different seeds unless asked to repeat the same ones."""
-    return rank * 100_003 if decorrelate else 0
+def _rank_seed_offset(rank: int, decorrelate: bool, per_rank_span: int = 100_003) -> int:
+    """Added to every episode seed of a rank.  Off (the default): 0, every rank seeds alike, so the scene that a
+    ``(task, episode)`` maps to does not depend on the number of GPUs or nodes.  On: rank ``r`` owns the block
+    ``[r * span, (r + 1) * span)`` of the seed line, where ``span`` is exactly the number of seeds one rank consumes
+    (batches x environments): the blocks tile the line, no gap, no overlap, however many episodes a rank runs.  ``rank``
+    is the GLOBAL rank (a node-local one would alias across nodes).  Adjacent seeds are fine: each goes through a
+    seed-sequence hash (reference ``src/opentau/scripts/eval.py:375-411``)."""
+    return rank * per_rank_span if decorrelate else 0
+
+
+def validate_eval_input_resolution(cfg) -> None:
+    """Environment frames arrive at exactly ``cfg.resolution``.  With a resize target on the policy a mismatch only
+    repeats the checkpoint's own double letterbox (a warning at construction); with NO resize target
+    (``resize_imgs_with_padding`` null) nothing would correct the frames and the tower would silently run at another
+    geometry than it was trained at: an error, unless ``policy.skip_input_resolution_check`` is set
+    (reference ``src/opentau/scripts/eval.py:1049-1092``)."""
+    pol = cfg.policy
+    expected = getattr(pol, "input_image_size", None)
+    if expected is None or tuple(cfg.resolution) == tuple(expected) \
+            or getattr(pol, "resize_imgs_with_padding", None) is not None:
+        return
+    if pol.skip_input_resolution_check:
+        logging.warning("resolution=%s differs from the policy's bound input resolution %s with "
+                        "resize_imgs_with_padding=null; proceeding because skip_input_resolution_check=true",
+                        tuple(cfg.resolution), tuple(expected))
+        return
+    raise ValueError(f"resolution={tuple(cfg.resolution)} but the policy was trained at {tuple(expected)} with "
+                     "resize_imgs_with_padding=null (native pass-through): environment frames would reach the vision "
+                     "tower at the wrong geometry with nothing to correct them.  Set resolution to match the checkpoint, "
+                     "or policy.skip_input_resolution_check=true to proceed anyway.")
+
+
+def collect_grid_summary_videos(videos_dir: Path) -> list[tuple[str, str]]:
+    """Sorted ``(task name, path)`` of every ``grid_summary.mp4`` below ``videos_dir`` (for the experiment tracker); the
+    task name is the folder name without a trailing ``_rank<N>``, so the keys stay the same when the number of GPUs
+    changes (each task is evaluated on exactly one rank).  Per-episode clips are not listed."""
+    import re
+    videos_dir = Path(videos_dir)
+    if not videos_dir.exists():
+        return []
+    return sorted((re.sub(r"_rank\d+$", "", g.parent.name), str(g)) for g in videos_dir.rglob("grid_summary.mp4"))
 
 
 def rollout(env, policy, seeds: list[int] | None = None, cfg=None, device=None, return_observations: bool = False,
@@ -398,7 +436,10 @@ def eval_policy_on_config(policy, cfg: TrainPipelineConfig, device, rank: int = 
     was_training = policy.training
     try:
         base = ev.seed if ev.seed is not None else cfg.seed          # the pipeline seed is the fallback
-        seed = None if base is None else base + _rank_seed_offset(rank, ev.decorrelate_rank_seeds)
+        n_tasks = sum(len(by_id) for by_id in envs.values())
+        n_batches = -(-ev.n_episodes // max(1, ev.batch_size))
+        span = max(1, n_batches * ev.batch_size * max(1, n_tasks))          # seeds one rank can consume
+        seed = None if base is None else base + _rank_seed_offset(rank, ev.decorrelate_rank_seeds, span)
         mine = eval_policy_all(envs, policy, ev.n_episodes, seed, cfg, device, rank, world, ev.seed_list,
                                render or None)
     finally:
@@ -425,6 +466,8 @@ def eval_main(cfg: TrainPipelineConfig):
         logging.info("best-of-N without a critic: the medoid candidate is used")
     if cfg.seed is not None:
         set_seed(cfg.seed, rank)
+    if cfg.policy is not None:
+        validate_eval_input_resolution(cfg)
     policy = make_policy(cfg.policy).to(device)
     if device.type == "cuda":
         policy.to(torch.bfloat16)

@@ -177,3 +177,34 @@ def test_videos_grid_summary_goal_frames_and_accel_streams(tmp_path):
         frames.append(f)
     assert len(frames) == 5 + 5 and frames[-1][1, 10, 2] > 150 and frames[-1][1, 10, 1] < 90     # red on tile 0
     assert frames[3][16, 16].mean() > 150                         # tile 0 still shows its last frame after it ended
+
+
+def test_seed_blocks_resolution_check_and_grid_collection(tmp_path):
+    import pytest
+
+    from helpers import tiny_pi05_config
+    from opentau_b200.configs.train import TrainPipelineConfig
+    from opentau_b200.scripts.eval import _rank_seed_offset, collect_grid_summary_videos, validate_eval_input_resolution
+    # off: every rank seeds alike; on: blocks of exactly one rank's span tile the seed line
+    assert [_rank_seed_offset(r, False, 40) for r in range(3)] == [0, 0, 0]
+    blocks = [range(_rank_seed_offset(r, True, 40), _rank_seed_offset(r, True, 40) + 40) for r in range(4)]
+    assert all(blocks[i].stop == blocks[i + 1].start for i in range(3))
+    # frames reach the tower at cfg.resolution: only a policy WITHOUT a resize target can be silently wrong
+    pol = tiny_pi05_config(resize_imgs_with_padding=None)
+    cfg = TrainPipelineConfig(policy=pol, resolution=(224, 224))
+    validate_eval_input_resolution(cfg)
+    cfg.resolution = (128, 128)
+    with pytest.raises(ValueError, match="wrong geometry"):
+        validate_eval_input_resolution(cfg)
+    pol.skip_input_resolution_check = True
+    validate_eval_input_resolution(cfg)
+    cfg.policy = tiny_pi05_config(resize_imgs_with_padding=(224, 224))
+    validate_eval_input_resolution(cfg)                               # a resize target corrects the frames
+    assert cfg.policy.input_image_size == (224, 224)
+    for name in ("libero_3_rank0", "libero_1_rank12", "robocasa_7"):
+        (tmp_path / name).mkdir()
+        (tmp_path / name / "grid_summary.mp4").write_bytes(b"x")
+        (tmp_path / name / "eval_episode_0.mp4").write_bytes(b"x")
+    got = collect_grid_summary_videos(tmp_path)
+    assert [g[0] for g in got] == ["libero_1", "libero_3", "robocasa_7"] and all(g[1].endswith("grid_summary.mp4") for g in got)
+    assert collect_grid_summary_videos(tmp_path / "absent") == []
