@@ -78,33 +78,72 @@ template <> __device__ __forceinline__ void store8<float>(float* p, const float*
   reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
 }
 
+// One rank's 8 elements as they come off the wire: 16 bytes (bf16) stay packed in 4 registers until they are summed,
+// so that a thread can keep eight ranks' loads in flight with 32 registers; fp32 pieces (8 registers) go 4 at a time.
+template <typename T> struct Piece8;
+template <> struct Piece8<__nv_bfloat16> {
+  static constexpr int BATCH = 8;
+  uint4 v;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void add_to(float* acc) const {
+    float2 t;
+    t = unpack_bf16(v.x); acc[0] += t.x; acc[1] += t.y;
+    t = unpack_bf16(v.y); acc[2] += t.x; acc[3] += t.y;
+    t = unpack_bf16(v.z); acc[4] += t.x; acc[5] += t.y;
+    t = unpack_bf16(v.w); acc[6] += t.x; acc[7] += t.y;
+  }
+};
+template <> struct Piece8<float> {
+  static constexpr int BATCH = 4;
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = reinterpret_cast<const float4*>(p)[0];
+    b = reinterpret_cast<const float4*>(p)[1];
+  }
+  __device__ __forceinline__ void add_to(float* acc) const {
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+};
+
+// acc[0..8) = sum over ranks (in rank order) of the 8 elements at `offset` of every rank's buffer.  The loads of a
+// batch of ranks are all issued before the first is consumed.
+template <typename T>
+__device__ __forceinline__ void sum_ranks8(const PeerTable& bufs, int world, long long offset, float* acc) {
+  constexpr int G = Piece8<T>::BATCH;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+  for (int r0 = 0; r0 < MAX_RANKS; r0 += G) {
+    if (r0 < world) {                                      // uniform over the grid
+      Piece8<T> piece[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        if (r0 + g < world) piece[g].load(static_cast<const T*>(bufs.ptr[r0 + g]) + offset);
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        if (r0 + g < world) piece[g].add_to(acc);
+    }
+  }
+}
+
 // out32[i] = sum_r grad_r[lo + i]; partial[blockIdx.x] = sum of squares of this block's outputs.
 // A wait that gave up earlier in this step left a record in `status`: the peers' buffers cannot be trusted then, so
 // the kernel writes nothing (the optimizer kernel behind it does the same and the parameters stay as they were).
+// Two 512-thread blocks per SM (at most 64 registers): the loads in flight per SM are what hides the latency of peer
+// reads, and they are the product of resident threads and loads per thread.
 template <typename T>
-__global__ void reduce_scatter_kernel(PeerTable grads, int world, long long lo, long long n,
-                                      float* __restrict__ out32, float* __restrict__ partial,
-                                      const KernelStatus* status) {
+__global__ void __launch_bounds__(512, 2) reduce_scatter_kernel(PeerTable grads, int world, long long lo, long long n,
+                                                                float* __restrict__ out32, float* __restrict__ partial,
+                                                                const KernelStatus* status) {
   __shared__ float red[32];
   if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
   float ss = 0.f;
   const long long nvec = n >> 3;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
        t += (long long)gridDim.x * blockDim.x) {
-    // all ranks' pieces are requested before any is consumed: up to eight independent 16-byte (bf16) or 32-byte
-    // (fp32) loads in flight per thread, which is what hides the latency of the peer reads; the sum itself runs in
-    // rank order
-    float f[MAX_RANKS][8];
-#pragma unroll
-    for (int r = 0; r < MAX_RANKS; ++r)
-      if (r < world) load8<T>(static_cast<const T*>(grads.ptr[r]) + lo + t * 8, f[r]);
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-    for (int r = 0; r < MAX_RANKS; ++r)
-      if (r < world) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += f[r][e];
-      }
+    float acc[8];
+    sum_ranks8<T>(grads, world, lo + t * 8, acc);
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += acc[e] * acc[e];
     float4* o = reinterpret_cast<float4*>(out32 + t * 8);
@@ -150,23 +189,15 @@ __global__ void allgather_pull_kernel(PeerTable src, int world, long long n_vec1
 
 // out[i] = sum_r src_r[lo + i] for bf16 buffers, summed in fp32 in rank order, stored as bf16: the reduce-scatter of
 // partial results (context-parallel dK / dV) back to the rank that owns the slice.
-__global__ void reduce_scatter_bf16_kernel(PeerTable src, int world, long long lo, long long n,
-                                           __nv_bfloat16* __restrict__ out, const KernelStatus* status) {
+__global__ void __launch_bounds__(512, 2) reduce_scatter_bf16_kernel(PeerTable src, int world, long long lo, long long n,
+                                                                     __nv_bfloat16* __restrict__ out,
+                                                                     const KernelStatus* status) {
   if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
   const long long nvec = n >> 3;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
        t += (long long)gridDim.x * blockDim.x) {
-    float f[MAX_RANKS][8];
-#pragma unroll
-    for (int r = 0; r < MAX_RANKS; ++r)
-      if (r < world) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(src.ptr[r]) + lo + t * 8, f[r]);
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-    for (int r = 0; r < MAX_RANKS; ++r)
-      if (r < world) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += f[r][e];
-      }
+    float acc[8];
+    sum_ranks8<__nv_bfloat16>(src, world, lo + t * 8, acc);
     store8<__nv_bfloat16>(out + t * 8, acc);
   }
 }

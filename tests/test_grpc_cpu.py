@@ -119,3 +119,38 @@ def test_planner_sees_observations_and_sets_the_subtask(tmp_path):
         assert len(calls) == 2 and "water the plant" in calls[1][0]        # a new task plans afresh
     finally:
         svc.infer.stop()
+
+
+def test_robot_control_loop_and_client_retries(running):
+    from opentau_b200.scripts.grpc.client import ClientConfig, RobotControlLoop, RobotLoopConfig
+    port = running()
+    sent = []
+    joints = tuple(f"j{i}" for i in range(4))
+    cfg = RobotLoopConfig(server_address=f"127.0.0.1:{port}", num_cameras=1, joint_names=joints)
+    loop = RobotControlLoop(cfg, publish=lambda names, q: sent.append((names, q)))
+    assert loop.step() == "no_state" and not sent
+    assert loop.on_joint_state([0.1, 0.2], [0.0, 0.0]) is False and loop.last_status == "short_state"
+    assert loop.on_joint_state([0.1, 0.2, 0.3, 0.4, 9.0], [0.0] * 5) and loop.positions == [0.1, 0.2, 0.3, 0.4]
+    assert loop.step() == "no_prompt" and not sent
+    cfg.prompt = "pick up the block"
+    assert loop.step() == "ok" and len(sent) == 1 and sent[0][0] == joints and len(sent[0][1]) == 4
+    assert loop.last_inference_ms > 0
+    # the command is the LAST row of the chunk; malformed chunks publish nothing
+    assert loop.apply(np.arange(12, dtype=np.float32).reshape(3, 4)) == "ok" and sent[-1][1] == [8.0, 9.0, 10.0, 11.0]
+    assert loop.apply(np.zeros((0, 4), np.float32)) == "empty_chunk"
+    assert loop.apply(np.zeros((2, 3), np.float32)) == "short_action"
+    assert loop.apply(np.zeros((1, 2, 3), np.float32)) == "bad_chunk" and len(sent) == 2
+    health = loop.client.health_check()
+    assert health["healthy"] and health["model_name"] == "pi05"
+    loop.stop()                                                       # damping: hold the current positions
+    assert sent[-1][1] == [0.1, 0.2, 0.3, 0.4] and not loop.client.is_connected()
+    assert loop.step() == "not_connected" and loop.client.health_check() == {"healthy": False, "status": "not connected"}
+    # a dead address: bounded retries, then one error
+    from opentau_b200.scripts.grpc.client import PolicyClient as C
+    dead = C(ClientConfig(server_address="127.0.0.1:1", timeout_seconds=0.3, max_retries=2, retry_delay_seconds=0.01))
+    with pytest.raises(RuntimeError, match="after 2 attempts"):
+        dead.request_action_chunk([np.zeros((8, 8, 3), np.uint8)], np.zeros(3), "x")
+    assert dead.health_check()["healthy"] is False
+    assert dead.connect(wait_ready_s=0.2) is False
+    with pytest.raises(ValueError):
+        ClientConfig(max_retries=0)
