@@ -256,41 +256,49 @@ __global__ void norm_exchange_kernel(const float* __restrict__ partial, int n_pa
 // AdamW on the shard, then the new values are stored (in the parameters' own dtype) into every rank's parameter
 // buffer.  Writes nothing when a wait gave up earlier in this step (see reduce_scatter_kernel).
 template <typename T>
-__global__ void adamw_allgather_kernel(float* __restrict__ p32, const float* __restrict__ g32, float* __restrict__ m,
-                                       float* __restrict__ v, PeerTable params, int world, long long lo, long long n,
-                                       float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
-                                       const float* __restrict__ scale_ptr, const KernelStatus* status) {
+__global__ void __launch_bounds__(512, 2) adamw_allgather_kernel(
+    float* __restrict__ p32, const float* __restrict__ g32, float* __restrict__ m, float* __restrict__ v,
+    PeerTable params, int world, long long lo, long long n, float lr, float beta1, float beta2, float eps, float wd,
+    float bc1, float bc2, const float* __restrict__ scale_ptr, const KernelStatus* status) {
   if (status != nullptr && *reinterpret_cast<const volatile unsigned*>(&status->code) != 0u) return;
   const float gs = scale_ptr[0];
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
+  const float decay = 1.f - lr * wd, c1 = 1.f - beta1, c2 = 1.f - beta2;
   const long long nvec = n >> 3;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < nvec;
        t += (long long)gridDim.x * blockDim.x) {
+    const long long i = t * 8;
+    // the eight 16-byte loads of this vector are requested before any is used
+    float4 p4[2], g4[2], m4[2], v4[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      p4[h] = *reinterpret_cast<const float4*>(p32 + i + h * 4);
+      g4[h] = *reinterpret_cast<const float4*>(g32 + i + h * 4);
+      m4[h] = *reinterpret_cast<const float4*>(m + i + h * 4);
+      v4[h] = *reinterpret_cast<const float4*>(v + i + h * 4);
+    }
     float pn[8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const long long i = t * 8 + h * 4;
-      float4 p4 = *reinterpret_cast<float4*>(p32 + i);
-      const float4 g4 = *reinterpret_cast<const float4*>(g32 + i);
-      float4 m4 = *reinterpret_cast<float4*>(m + i);
-      float4 v4 = *reinterpret_cast<float4*>(v + i);
-      float pp[4] = {p4.x, p4.y, p4.z, p4.w}, gg[4] = {g4.x, g4.y, g4.z, g4.w};
-      float mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      float pp[4] = {p4[h].x, p4[h].y, p4[h].z, p4[h].w}, gg[4] = {g4[h].x, g4[h].y, g4[h].z, g4[h].w};
+      float mm[4] = {m4[h].x, m4[h].y, m4[h].z, m4[h].w}, vv[4] = {v4[h].x, v4[h].y, v4[h].z, v4[h].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float gr = gg[e] * gs;
-        float pe = pp[e] * (1.f - lr * wd);
-        mm[e] = beta1 * mm[e] + (1.f - beta1) * gr;
-        vv[e] = beta2 * vv[e] + (1.f - beta2) * gr * gr;
+        float pe = pp[e] * decay;
+        mm[e] = beta1 * mm[e] + c1 * gr;
+        vv[e] = beta2 * vv[e] + c2 * gr * gr;
         pe -= lr * inv_bc1 * mm[e] / (sqrtf(vv[e]) * inv_sqrt_bc2 + eps);
         pp[e] = pe;
         pn[h * 4 + e] = pe;
       }
-      *reinterpret_cast<float4*>(p32 + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
-      *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-      *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      *reinterpret_cast<float4*>(p32 + i + h * 4) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+      *reinterpret_cast<float4*>(m + i + h * 4) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      *reinterpret_cast<float4*>(v + i + h * 4) = make_float4(vv[0], vv[1], vv[2], vv[3]);
     }
-    for (int r = 0; r < world; ++r) store8<T>(static_cast<T*>(params.ptr[r]) + lo + t * 8, pn);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) store8<T>(static_cast<T*>(params.ptr[r]) + lo + i, pn);
   }
 }
 

@@ -99,8 +99,10 @@ class PeerComm:
     """
 
     OVERLAP_BLOCKS = 48      # CTAs of a reduce-scatter that runs under the backward pass (leaves the SMs to the GEMMs)
-    FLUSH_BLOCKS = 512       # CTAs of a reduce-scatter / optimizer kernel that runs alone
-    PARTIALS_PER_BUCKET = 512
+    # CTAs of a reduce-scatter / optimizer kernel that runs alone: two 512-thread CTAs are resident per SM, so 4 x 148
+    # fills the GPU in exactly two waves (measured: 296, 512 and 592 CTAs within 7 % of each other, 592 never worst)
+    FLUSH_BLOCKS = 592
+    PARTIALS_PER_BUCKET = 592
 
     def __init__(self, device: torch.device, group=None, wait_budget: int = DEFAULT_WAIT_BUDGET):
         from ..ops import _lib

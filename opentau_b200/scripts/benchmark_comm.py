@@ -42,7 +42,7 @@ def main(argv: list[str] | None = None) -> list[dict]:
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--mparams", type=int, default=512, help="parameters of the whole bucket set, in Mi elements")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--blocks", type=int, default=512)
+    ap.add_argument("--blocks", type=int, default=592)
     a = ap.parse_args(argv)
     from ..ops import _lib, cuda_ops
     lib = _lib.load("comm_p2p")
@@ -55,7 +55,7 @@ def main(argv: list[str] | None = None) -> list[dict]:
     p16 = [torch.zeros(n, device=dev, dtype=torch.bfloat16) for _ in range(W)]
     master, m, v = (torch.randn(shard, device=dev), torch.zeros(shard, device=dev), torch.zeros(shard, device=dev))
     g32 = torch.empty(shard, device=dev)
-    partial = torch.zeros(512, device=dev)
+    partial = torch.zeros(max(512, a.blocks), device=dev)
     scale = torch.ones(2, device=dev)
     peak, src = _hbm_gbs()
 
