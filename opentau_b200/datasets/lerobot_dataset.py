@@ -37,9 +37,9 @@ from .hub_transfer import HubTransferMixin
 from .standard_data_format_mapping import get_mapping
 from .utils import (CODEBASE_VERSION, DEFAULT_CHUNK_SIZE, DEFAULT_FEATURES, DEFAULT_IMAGE_PATH, DEFAULT_PARQUET_PATH,
                     DEFAULT_VIDEO_PATH, EPISODES_PATH, EPISODES_STATS_PATH, INFO_PATH, TASKS_PATH, append_jsonlines,
-                    check_version_compatibility, get_episode_data_index, get_version, load_episodes,
-                    load_episodes_stats, load_info, load_stats, load_tasks, serialize_stats, validate_frame,
-                    write_json)
+                    check_timestamps_sync, check_version_compatibility, get_episode_data_index, get_version, load_episodes,
+                    load_episodes_stats, load_info, load_stats, load_tasks, serialize_stats, validate_episode_buffer,
+                    validate_frame, write_json)
 from .video_utils import decode_video_frames, encode_video_frames
 
 HF_HOME = Path.home() / ".cache" / "huggingface" / "lerobot"
@@ -599,6 +599,9 @@ class LeRobotDataset(BaseDataset, HubTransferMixin):
             self.prompt_substitutions, self.robot_type, self.control_mode = None, self.meta.robot_type, self.meta.control_mode
         self._load_table()
         self.episode_data_index = get_episode_data_index(self.meta.episodes, self.episodes)
+        if "timestamp" in self._numeric:
+            check_timestamps_sync(self._numeric["timestamp"].numpy(), self._numeric["episode_index"].numpy(),
+                                  {"to": np.asarray(self.episode_data_index["to"])}, self.fps, self.tolerance_s)
         self.epi2idx = {ep: i for i, ep in enumerate(self.episodes)}
         self._build_episode_tables()
 
@@ -913,9 +916,10 @@ class LeRobotRecorder:
     images or encoded videos, per-episode stats and the metadata records."""
 
     def __init__(self, meta: LeRobotDatasetMetadata, image_writer_threads: int = 0,
-                 deferred_video_keys: set[str] | list[str] | None = None):
+                 deferred_video_keys: set[str] | list[str] | None = None, tolerance_s: float = 1e-4):
         self.meta, self.root, self.fps = meta, meta.root, meta.fps
         self.features = meta.features
+        self.tolerance_s = tolerance_s
         self.deferred_video_keys = set(deferred_video_keys or ())
         unknown = self.deferred_video_keys - set(meta.video_keys)
         if unknown:
@@ -961,9 +965,11 @@ class LeRobotRecorder:
         import pyarrow as pa
         import pyarrow.parquet as pq
         buf = self.episode_buffer
+        validate_episode_buffer(buf, self.meta.total_episodes, self.features, self.deferred_video_keys)
         n, ep = buf["size"], buf["episode_index"]
-        if n == 0:
-            raise ValueError("You must add one or several frames with `add_frame` before calling `save_episode`.")
+        # frames 1 / fps apart: a recorder that dropped frames would shift every "k steps ahead" lookup
+        check_timestamps_sync(np.asarray(buf["timestamp"], np.float64), np.full(n, ep), {"to": np.array([n])},
+                              self.fps, self.tolerance_s)
         tasks = buf["task"]
         for t in dict.fromkeys(tasks):
             if self.meta.get_task_index(t) is None:

@@ -234,3 +234,52 @@ def hf_transform_to_torch(value: Any) -> Any:
     if isinstance(value, (int, float, np.integer, np.floating)):
         return torch.tensor(value)
     return value
+
+
+def check_timestamps_sync(timestamps: np.ndarray, episode_indices: np.ndarray, episode_data_index: dict,
+                          fps: float, tolerance_s: float, raise_value_error: bool = True) -> bool:
+    """Consecutive frames of one episode must be ``1 / fps`` apart within ``tolerance_s`` (differences across an
+    episode boundary are not looked at).  A recording with dropped or duplicated frames makes every "``k`` steps ahead"
+    lookup land on the wrong instant, so it is refused at load time with the offending pairs
+    (reference ``src/opentau/datasets/utils.py:1265-1339``)."""
+    timestamps, episode_indices = np.asarray(timestamps, np.float64), np.asarray(episode_indices)
+    if timestamps.shape != episode_indices.shape:
+        raise ValueError(f"timestamps and episode_indices must have the same shape, got {timestamps.shape} and "
+                         f"{episode_indices.shape}")
+    if len(timestamps) < 2:
+        return True
+    diffs = np.diff(timestamps)
+    ok = np.abs(diffs - 1.0 / fps) <= tolerance_s
+    inside = np.ones(len(diffs), bool)
+    ends = np.asarray(episode_data_index["to"], np.int64)[:-1] - 1          # last frame of every episode but the last
+    inside[ends[(ends >= 0) & (ends < len(diffs))]] = False
+    bad = np.flatnonzero(~ok & inside)
+    if bad.size == 0:
+        return True
+    if raise_value_error:
+        shown = [{"timestamps": [float(timestamps[i]), float(timestamps[i + 1])], "diff": float(diffs[i]),
+                  "episode_index": int(episode_indices[i])} for i in bad[:10]]
+        raise ValueError(f"{bad.size} pair(s) of consecutive frames are not 1/fps = {1.0 / fps:.6f} s apart within "
+                         f"tolerance_s={tolerance_s}: the recording dropped or duplicated frames, or the tolerance is "
+                         f"too tight for its clock.  First offenders: {shown}")
+    return False
+
+
+def validate_episode_buffer(episode_buffer: dict, total_episodes: int, features: dict,
+                            deferred_features: set[str] | None = None) -> None:
+    """An episode buffer about to be saved: it has ``size`` and ``task``, is not empty, continues the episode numbering,
+    and holds exactly the dataset's features (those whose data arrives later, e.g. deferred videos, may be absent)."""
+    for key in ("size", "task"):
+        if key not in episode_buffer:
+            raise ValueError(f"{key} key not found in episode_buffer")
+    if episode_buffer["episode_index"] != total_episodes:
+        raise NotImplementedError(f"episode_index {episode_buffer['episode_index']} does not continue the dataset "
+                                  f"({total_episodes} episodes so far): out-of-order episodes are not supported")
+    if episode_buffer["size"] == 0:
+        raise ValueError("You must add one or several frames with `add_frame` before calling `save_episode`.")
+    have = set(episode_buffer) - {"task", "size"}
+    want = set(features) - set(deferred_features or ())
+    extra, missing = have - set(features), want - have
+    if extra or missing:
+        raise ValueError(f"features of the episode buffer and of the dataset differ: missing {sorted(missing)}, "
+                         f"unexpected {sorted(extra)}")

@@ -185,3 +185,42 @@ def test_video_backend_selection_tolerance_and_resample(tmp_path, caplog):
     with pytest.raises(ValueError, match="too short"):
         vu.resample_and_trim_video(src, tmp_path / "o2.mp4", target_fps=10, num_frames=40)
     vu.close_all()
+
+
+def test_timestamp_sync_and_episode_buffer_validation(tmp_path):
+    import pytest
+
+    from opentau_b200.datasets.utils import check_timestamps_sync, validate_episode_buffer
+    ts = np.concatenate([np.arange(5) / 10.0, np.arange(4) / 10.0])          # two episodes, clocks restart
+    ep = np.array([0] * 5 + [1] * 4)
+    index = {"to": np.array([5, 9])}
+    assert check_timestamps_sync(ts, ep, index, fps=10, tolerance_s=1e-4)
+    dropped = ts.copy()
+    dropped[7:] += 0.1                                                        # a frame missing inside episode 1
+    assert check_timestamps_sync(dropped, ep, index, 10, 1e-4, raise_value_error=False) is False
+    with pytest.raises(ValueError, match="episode_index': 1"):
+        check_timestamps_sync(dropped, ep, index, 10, 1e-4)
+    assert check_timestamps_sync(dropped, ep, index, 10, 0.2)                 # a looser tolerance accepts it
+    with pytest.raises(ValueError, match="same shape"):
+        check_timestamps_sync(ts, ep[:-1], index, 10, 1e-4)
+    feats = {"action": {}, "observation.images.top": {}, "timestamp": {}, "episode_index": {}}
+    good = {"size": 2, "task": ["a", "a"], "episode_index": 3, "action": [], "observation.images.top": [], "timestamp": []}
+    validate_episode_buffer(good, 3, feats)
+    with pytest.raises(NotImplementedError):
+        validate_episode_buffer(good, 4, feats)
+    with pytest.raises(ValueError, match="add one or several frames"):
+        validate_episode_buffer({**good, "size": 0}, 3, feats)
+    late = {k: v for k, v in good.items() if k != "observation.images.top"}
+    with pytest.raises(ValueError, match="missing"):
+        validate_episode_buffer(late, 3, feats)
+    validate_episode_buffer(late, 3, feats, deferred_features={"observation.images.top"})
+    with pytest.raises(ValueError, match="task key"):
+        validate_episode_buffer({k: v for k, v in good.items() if k != "task"}, 3, feats)
+    # the recorder refuses an episode whose clock skipped
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDataset
+    rec = LeRobotDataset.create("local/skip", fps=10, root=tmp_path / "skip", features={
+        "action": {"dtype": "float32", "shape": (2,), "names": None}}, use_videos=False)
+    for t in (0.0, 0.1, 0.3):
+        rec.add_frame({"action": np.zeros(2, np.float32), "task": "x", "timestamp": t})
+    with pytest.raises(ValueError, match="dropped or duplicated"):
+        rec.save_episode()
