@@ -194,3 +194,61 @@ def test_convert_v20_to_v21_workers_check_metadata_fix_and_batch(tmp_path):
         convert(b, check=True)
     status = batch_convert([b, tmp_path / "nope"], log_path=tmp_path / "log.txt")
     assert status[str(b)] == "converted 2 episodes" and status[str(tmp_path / "nope")].startswith("failed")
+
+
+def test_strict_copy_only_annotation_pipeline(tmp_path):
+    import pyarrow.parquet as pq
+    import pytest
+
+    from opentau_b200.planner.high_level_planner import CallableClient
+    from opentau_b200.scripts.attach_metadata import attach_annotations, load_and_validate_annotations
+    _record(tmp_path / "toy", episodes=(10, 8))
+    ann = [{"episode_id": 0, "quality": 4, "segments": [{"start": 0, "subtask": "reach", "success": True},
+                                                        {"start": 4, "subtask": "grasp", "success": False}]},
+           {"episode_id": 1, "quality": 2, "segments": [{"start": 0, "subtask": "place", "success": True}]}]
+    before = (tmp_path / "toy" / "meta" / "episodes.jsonl").read_text()
+    out = attach_annotations(tmp_path / "toy", ann, tmp_path / "copy", skip_memory=True)
+    assert out["episodes"] == 2 and out["frames"] == 18 and out["memory_calls"] == 0
+    assert (tmp_path / "toy" / "meta" / "episodes.jsonl").read_text() == before            # the source is never touched
+    t = pq.read_table(tmp_path / "copy" / "data/chunk-000/episode_000000.parquet").to_pydict()
+    assert t["response"] == ["reach"] * 4 + ["grasp"] * 6 and t["mistake"] == [0] * 4 + [1] * 6
+    assert t["memory"][5] == "memory5"
+    meta = LeRobotDatasetMetadata("local/toy", root=tmp_path / "copy")
+    assert meta.episodes[0]["segments"] == [0, 4] and meta.episodes[0]["quality"] == 4 and meta.episodes[1]["quality"] == 2
+    assert meta.features["mistake"]["dtype"] == "int64" and meta.features["memory"]["dtype"] == "string"
+    with pytest.raises(FileExistsError):
+        attach_annotations(tmp_path / "toy", ann, tmp_path / "copy", skip_memory=True)
+    # memories: one model call per segment, asked before anything is written
+    seen = []
+    client = CallableClient(lambda messages, images: seen.append(messages[-1]["content"]) or f"did {len(seen)} things")
+    out = attach_annotations(tmp_path / "toy", ann, tmp_path / "copy", overwrite=True, client=client)
+    assert out["memory_calls"] == 3 and "[FAILED]" in seen[1] and "task 0" in seen[0]
+    t = pq.read_table(tmp_path / "copy" / "data/chunk-000/episode_000000.parquet").to_pydict()
+    assert t["memory"][0] == "did 1 things" and t["memory"][9] == "did 2 things"
+    with pytest.raises(ValueError, match="chat client"):
+        attach_annotations(tmp_path / "toy", ann, tmp_path / "other")
+    assert not (tmp_path / "other").exists()
+    # every structural fault is named before any file is written
+    lengths = {0: 10, 1: 8}
+    good = json.loads(json.dumps(ann))
+    cases = [
+        (lambda a: a.pop(), "Missing annotations for episodes: \\[1\\]"),
+        (lambda a: a.append({**a[0], "episode_id": 7}), "Unknown episodes"),
+        (lambda a: a.append(dict(a[0])), "Duplicate episode_id 0"),
+        (lambda a: a[0].update(quality=6), "quality must be in 1..5"),
+        (lambda a: a[0].update(quality=True), "quality must be int"),
+        (lambda a: a[0]["segments"][0].update(start=1), "first segment must start at 0"),
+        (lambda a: a[0]["segments"][1].update(start=0), "strictly increase"),
+        (lambda a: a[0]["segments"][1].update(start=4.0), "frame index, not a time"),
+        (lambda a: a[0]["segments"][1].update(start=10), ">= episode length 10"),
+        (lambda a: a[0]["segments"][1].update(success="no"), "success must be bool"),
+        (lambda a: a[1].update(segments=[]), "non-empty 'segments'"),
+        (lambda a: a[0].pop("quality"), "missing required key 'quality'"),
+    ]
+    for mutate, message in cases:
+        bad = json.loads(json.dumps(good))
+        mutate(bad)
+        with pytest.raises(ValueError, match=message):
+            load_and_validate_annotations(bad, lengths)
+    with pytest.raises(ValueError, match="must be a list"):
+        load_and_validate_annotations({"episodes": {}}, lengths)
