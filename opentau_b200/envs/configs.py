@@ -14,6 +14,53 @@ from ..configs.codec import ChoiceRegistry
 from ..configs.types import FeatureType, PolicyFeature
 
 
+SPEED_BUCKET_STEP = 10
+CONTROL_MODE_CHOICES = ("joint", "ee")
+
+
+@dataclass
+class EnvMetadataConfig:
+    """Metadata the pi0.7 family tokenizes as a ``"Metadata: ..."`` segment of its prefix, broadcast over the rollout
+    batch at inference (reference ``src/opentau/envs/configs.py:46-126``).  It belongs to the environment config (WHAT is
+    being run), not the eval config (how much of it).  ``None`` leaves a field out: no batch key, no segment.  Allowed
+    values are those the dataset emits in training: ``speed`` a multiple of 10 in [0, 100] (0 = fastest decile of the
+    task), ``quality`` in [1, 5], ``mistake`` a bool (``False`` emits "Mistake: False", which differs from leaving it
+    out), ``robot_type`` a non-empty string, ``control_mode`` ``"joint"`` or ``"ee"``.  ``emit_fps`` broadcasts the
+    environment's stepping frequency as ``fps``; off by default so that checkpoints trained without that conditioning
+    see no surprise segment.  Other policy families ignore all of it."""
+
+    speed: int | None = None
+    quality: int | None = None
+    mistake: bool | None = None
+    robot_type: str | None = None
+    control_mode: str | None = None
+    emit_fps: bool = False
+
+    def __post_init__(self) -> None:
+        def is_int(x):            # bool is a subclass of int: speed=True must not pass as 1
+            return isinstance(x, int) and not isinstance(x, bool)
+        if self.speed is not None:
+            if not is_int(self.speed):
+                raise TypeError(f"env.metadata.speed must be int, got {type(self.speed).__name__}")
+            if not 0 <= self.speed <= 100 or self.speed % SPEED_BUCKET_STEP:
+                raise ValueError(f"env.metadata.speed must be a multiple of {SPEED_BUCKET_STEP} in [0, 100], got {self.speed}")
+        if self.quality is not None:
+            if not is_int(self.quality):
+                raise TypeError(f"env.metadata.quality must be int, got {type(self.quality).__name__}")
+            if not 1 <= self.quality <= 5:
+                raise ValueError(f"env.metadata.quality must be in [1, 5], got {self.quality}")
+        if self.mistake is not None and not isinstance(self.mistake, bool):
+            raise TypeError(f"env.metadata.mistake must be bool, got {type(self.mistake).__name__}")
+        if self.robot_type is not None:
+            if not isinstance(self.robot_type, str):
+                raise TypeError(f"env.metadata.robot_type must be str, got {type(self.robot_type).__name__}")
+            if not self.robot_type:
+                raise ValueError("env.metadata.robot_type must be a non-empty string; use None to leave it out")
+        if self.control_mode is not None and self.control_mode not in CONTROL_MODE_CHOICES:
+            raise ValueError(f"env.metadata.control_mode must be one of {CONTROL_MODE_CHOICES} or None, got "
+                             f"{self.control_mode!r}")
+
+
 @dataclass
 class EnvConfig(ChoiceRegistry):
     task: str | None = None
@@ -22,6 +69,7 @@ class EnvConfig(ChoiceRegistry):
     max_parallel_tasks: int = 1
     features: dict[str, PolicyFeature] = field(default_factory=dict)
     features_map: dict[str, str] = field(default_factory=dict)
+    metadata: EnvMetadataConfig = field(default_factory=EnvMetadataConfig)
 
     @property
     def type(self) -> str:

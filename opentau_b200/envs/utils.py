@@ -48,6 +48,54 @@ def add_envs_task(env, observation: dict[str, Any]) -> dict[str, Any]:
     return observation
 
 
+def add_eval_metadata(observation: dict[str, Any], env_cfg) -> dict[str, Any]:
+    """Writes ``env_cfg.metadata`` into an inference batch with the dtypes the dataset emits in training: ``speed`` /
+    ``quality`` long and ``mistake`` bool tensors of the batch size, each with ``<key>_is_pad`` all False;
+    ``robot_type`` / ``control_mode`` as one string per environment; ``fps`` (the environment's stepping frequency)
+    when ``emit_fps`` is set.  Fields that are ``None`` add nothing, so the policy's pad path leaves that segment out
+    (reference ``src/opentau/envs/utils.py:234-290``)."""
+    meta = getattr(env_cfg, "metadata", None)
+    if meta is None:
+        return observation
+    state = observation["state"]
+    n, dev = state.shape[0], state.device
+    for key, dtype in (("speed", torch.long), ("quality", torch.long), ("mistake", torch.bool)):
+        val = getattr(meta, key)
+        if val is not None:
+            observation[key] = torch.full((n,), val, dtype=dtype, device=dev)
+            observation[f"{key}_is_pad"] = torch.zeros(n, dtype=torch.bool, device=dev)
+    for key in ("robot_type", "control_mode"):
+        val = getattr(meta, key)
+        if val is not None:
+            observation[key] = [val] * n
+    if meta.emit_fps:
+        observation["fps"] = torch.full((n,), int(env_cfg.fps), dtype=torch.long, device=dev)
+        observation["fps_is_pad"] = torch.zeros(n, dtype=torch.bool, device=dev)
+    return observation
+
+
+def close_envs(obj) -> None:
+    """Closes one environment, or every environment of a (nested) list / dict of them; an environment that fails to
+    close is reported and the others are still closed."""
+    from collections.abc import Mapping, Sequence
+    if obj is None or isinstance(obj, (str, bytes)):
+        return
+    if isinstance(obj, Mapping):
+        for v in obj.values():
+            close_envs(v)
+    elif isinstance(obj, Sequence):
+        for v in obj:
+            close_envs(v)
+    elif hasattr(obj, "close"):
+        try:
+            obj.close()
+        except Exception as exc:  # noqa: BLE001
+            import logging
+            logging.warning("exception while closing environment %r: %s", obj, exc)
+    else:
+        raise NotImplementedError(f"close_envs cannot close a {type(obj).__name__}")
+
+
 def add_subgoal_images(observation: dict[str, Any], generator) -> dict[str, Any]:
     """Merges ``subgoal{k}`` / ``subgoal_is_pad`` from a subgoal generator into the observation (no-op for None; the
     policy then falls back to zero subgoals marked as padding).  ``generator.start_episode`` must have run."""

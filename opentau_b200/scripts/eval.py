@@ -30,7 +30,8 @@ from ..configs.deployment import tag_norm_head
 from ..configs.train import TrainPipelineConfig
 from ..envs.configs import EnvConfig
 from ..envs.factory import make_envs
-from ..envs.utils import add_envs_task, add_subgoal_images, check_env_attributes_and_types, preprocess_observation
+from ..envs.utils import (add_envs_task, add_eval_metadata, add_subgoal_images, check_env_attributes_and_types, close_envs,
+                          preprocess_observation)
 from ..parallel import control
 
 
@@ -38,8 +39,9 @@ def resolve_env_config(env: Any) -> EnvConfig:
     if isinstance(env, EnvConfig):
         return env
     if isinstance(env, dict):
+        from ..configs.codec import decode
         d = dict(env)
-        return EnvConfig.get_choice_class(d.pop("type"))(**d)
+        return decode(EnvConfig.get_choice_class(d.pop("type")), d, "env")      # nested blocks (metadata) included
     raise TypeError(f"cannot build an environment from {type(env).__name__}")
 
 
@@ -118,6 +120,8 @@ def rollout(env, policy, seeds: list[int] | None = None, cfg=None, device=None, 
                     last_frames[b] = {k: v[b] for k, v in cams.items()}
         batch = preprocess_observation(obs, cfg)
         batch = add_envs_task(env, batch)
+        if cfg is not None and getattr(cfg, "env", None) is not None:
+            batch = add_eval_metadata(batch, resolve_env_config(cfg.env))
         batch = add_subgoal_images(batch, subgoal_generator)
         batch = {k: (v.to(device) if isinstance(v, Tensor) else v) for k, v in batch.items()}
         if extra_batch:
@@ -443,9 +447,7 @@ def eval_policy_on_config(policy, cfg: TrainPipelineConfig, device, rank: int = 
         mine = eval_policy_all(envs, policy, ev.n_episodes, seed, cfg, device, rank, world, ev.seed_list,
                                render or None)
     finally:
-        for by_id in envs.values():
-            for e in by_id.values():
-                e.close()
+        close_envs(envs)
         policy.train(was_training)
     return consolidate_eval_info(control.gather_object(mine))
 

@@ -208,3 +208,38 @@ def test_seed_blocks_resolution_check_and_grid_collection(tmp_path):
     got = collect_grid_summary_videos(tmp_path)
     assert [g[0] for g in got] == ["libero_1", "libero_3", "robocasa_7"] and all(g[1].endswith("grid_summary.mp4") for g in got)
     assert collect_grid_summary_videos(tmp_path / "absent") == []
+
+
+def test_environment_metadata_reaches_the_batch():
+    import pytest
+    import torch
+
+    from opentau_b200.envs.configs import EnvMetadataConfig, FakeEnvConfig
+    from opentau_b200.envs.utils import add_eval_metadata, close_envs
+    from opentau_b200.scripts.eval import resolve_env_config
+    env = resolve_env_config({"type": "fake", "fps": 20, "metadata": {"speed": 30, "mistake": False, "control_mode": "ee",
+                                                                      "emit_fps": True}})
+    assert isinstance(env, FakeEnvConfig) and env.metadata.speed == 30
+    obs = add_eval_metadata({"state": torch.zeros(3, 8)}, env)
+    assert obs["speed"].tolist() == [30] * 3 and obs["speed"].dtype == torch.long and not obs["speed_is_pad"].any()
+    assert obs["mistake"].tolist() == [False] * 3 and obs["mistake"].dtype == torch.bool        # False is a value
+    assert obs["control_mode"] == ["ee"] * 3 and "quality" not in obs and "robot_type" not in obs
+    assert obs["fps"].tolist() == [20] * 3 and not obs["fps_is_pad"].any()
+    assert set(add_eval_metadata({"state": torch.zeros(2, 8)}, FakeEnvConfig())) == {"state"}     # all None: nothing added
+    for bad, err in ((dict(speed=35), ValueError), (dict(speed=True), TypeError), (dict(quality=0), ValueError),
+                     (dict(quality=2.0), TypeError), (dict(mistake=1), TypeError), (dict(robot_type=""), ValueError),
+                     (dict(control_mode="torque"), ValueError)):
+        with pytest.raises(err):
+            EnvMetadataConfig(**bad)
+
+    class E:
+        def __init__(self, fail=False):
+            self.closed, self.fail = False, fail
+
+        def close(self):
+            self.closed = True
+            if self.fail:
+                raise RuntimeError("boom")
+    envs = {"suite": {0: E(), 1: E(fail=True)}, "other": [E(), None]}
+    close_envs(envs)                                                   # one failure does not keep the others open
+    assert all(e.closed for e in (*envs["suite"].values(), envs["other"][0]))
