@@ -224,3 +224,35 @@ def test_timestamp_sync_and_episode_buffer_validation(tmp_path):
         rec.add_frame({"action": np.zeros(2, np.float32), "task": "x", "timestamp": t})
     with pytest.raises(ValueError, match="dropped or duplicated"):
         rec.save_episode()
+
+
+def test_image_writer_threads_and_processes(tmp_path):
+    import pytest
+    from PIL import Image
+
+    from opentau_b200.datasets.image_writer import AsyncImageWriter, safe_stop_image_writer
+    rng = np.random.default_rng(0)
+    for label, kw in (("threads", dict(num_processes=0, num_threads=3)), ("procs", dict(num_processes=2, num_threads=2))):
+        w = AsyncImageWriter(**kw)
+        frames = [rng.integers(0, 255, (24, 32, 3), dtype=np.uint8) for _ in range(12)]
+        for i, f in enumerate(frames):
+            w.save_image(f if i % 2 else torch.from_numpy(f).permute(2, 0, 1), tmp_path / label / f"frame_{i:03d}.png")
+        w.wait_until_done()
+        got = sorted((tmp_path / label).glob("*.png"))
+        assert len(got) == 12 and np.array_equal(np.asarray(Image.open(got[5])), frames[5])
+        w.stop()
+        w.stop()                                                            # idempotent
+        assert all(not p.is_alive() for p in w.processes)
+
+    class Session:
+        def __init__(self):
+            self.image_writer = AsyncImageWriter(num_threads=1)
+
+    @safe_stop_image_writer
+    def record(dataset):
+        raise KeyboardInterrupt
+
+    s = Session()
+    with pytest.raises(KeyboardInterrupt):
+        record(s)
+    assert s.image_writer._stopped
