@@ -904,11 +904,12 @@ class LeRobotDataset(BaseDataset, HubTransferMixin):
     @classmethod
     def create(cls, repo_id: str, fps: int, root: str | Path | None = None, robot_type: str | None = None,
                features: dict | None = None, use_videos: bool = False, image_writer_threads: int = 0,
-               deferred_video_keys: set[str] | list[str] | None = None) -> "LeRobotRecorder":
+               deferred_video_keys: set[str] | list[str] | None = None, image_writer_processes: int = 0,
+               tolerance_s: float = 1e-4) -> "LeRobotRecorder":
         """``deferred_video_keys``: video features whose frames are NOT handed to ``add_frame``; their files are
         attached after ``save_episode`` from recordings made elsewhere (``LeRobotRecorder.attach_video``)."""
         meta = LeRobotDatasetMetadata.create(repo_id, fps, root, robot_type, features, use_videos)
-        return LeRobotRecorder(meta, image_writer_threads, deferred_video_keys)
+        return LeRobotRecorder(meta, image_writer_threads, deferred_video_keys, tolerance_s, image_writer_processes)
 
 
 class LeRobotRecorder:
@@ -916,7 +917,8 @@ class LeRobotRecorder:
     images or encoded videos, per-episode stats and the metadata records."""
 
     def __init__(self, meta: LeRobotDatasetMetadata, image_writer_threads: int = 0,
-                 deferred_video_keys: set[str] | list[str] | None = None, tolerance_s: float = 1e-4):
+                 deferred_video_keys: set[str] | list[str] | None = None, tolerance_s: float = 1e-4,
+                 image_writer_processes: int = 0):
         self.meta, self.root, self.fps = meta, meta.root, meta.fps
         self.features = meta.features
         self.tolerance_s = tolerance_s
@@ -925,9 +927,10 @@ class LeRobotRecorder:
         if unknown:
             raise ValueError(f"deferred_video_keys {sorted(unknown)} are not video features ({meta.video_keys})")
         self.image_writer = None
-        if image_writer_threads > 0:
+        if image_writer_threads > 0 or image_writer_processes > 0:
             from .image_writer import AsyncImageWriter
-            self.image_writer = AsyncImageWriter(num_threads=image_writer_threads)
+            self.image_writer = AsyncImageWriter(num_processes=image_writer_processes,
+                                                 num_threads=max(1, image_writer_threads))
         self.episode_buffer = self.create_episode_buffer()
 
     def create_episode_buffer(self, episode_index: int | None = None) -> dict:
