@@ -184,7 +184,7 @@ class HubTransferMixin:
         client.upload_folder(self.repo_id, Path(self.root), revision=branch, allow_patterns=allow_patterns,
                              ignore_patterns=ignore, large=upload_large_folder)
         if not client.file_exists(self.repo_id, REPOCARD_NAME, revision=branch):
-            client.upload_text(self.repo_id, REPOCARD_NAME, dataset_card(self.meta.info, tags, license, **card_kwargs),
+            client.upload_text(self.repo_id, REPOCARD_NAME, dataset_card(getattr(self, "meta", self).info, tags, license, **card_kwargs),
                                revision=branch)
         if tag_version:
             client.retag(self.repo_id, CODEBASE_VERSION, revision=branch)

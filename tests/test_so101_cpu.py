@@ -122,3 +122,47 @@ def test_stable_device_aliases(tmp_path):
     assert len(stable_link_map(by_path)) == 1
     assert stable_video_path(0, by_path) is None and stable_serial_path(str(dev / "ttyACM9"), by_id) is None
     assert stable_link_map(tmp_path / "missing") == {}
+
+
+def test_record_session_rerecord_stop_and_resume(tmp_path):
+    from opentau_b200.datasets.lerobot_dataset import LeRobotDataset, LeRobotDatasetMetadata
+    from opentau_b200.scripts.so101.record import (features, new_events, open_dataset_for_append, record_episode,
+                                                   record_session)
+    leader = SOLeader(SOArmConfig(port=FakeFeetechPort(IDS), id="l", calibration_dir=str(tmp_path / "c")))
+    follower = SOFollower(SOArmConfig(port=FakeFeetechPort(IDS), id="f", calibration_dir=str(tmp_path / "c")))
+    for arm in (leader, follower):
+        arm.bus.connect()
+        arm.calibrate({n: (0, 4095) for n in arm.bus.motors})
+        arm.configure()
+    rec = LeRobotDataset.create("local/so101", 50, root=tmp_path / "ds", robot_type="so101", features=features({}))
+    events, said = new_events(), []
+
+    class Script(dict):
+        """Plays the operator: throws the first take away, ends the second early, asks to stop during the third."""
+        takes = 0
+
+    def say(msg):
+        said.append(msg)
+        if msg.startswith("recording episode"):
+            Script.takes += 1
+            if Script.takes == 1:
+                events["rerecord_episode"] = True
+            if Script.takes == 3:
+                events["stop_recording"] = True
+    saved = record_session(rec, leader, follower, "wave", num_episodes=5, episode_time_s=0.06, reset_time_s=0.02, fps=50,
+                           events=events, say=say)
+    assert saved == 2 and Script.takes == 3 and "re-recording the episode" in said and "reset the environment" in said
+    meta = LeRobotDatasetMetadata("local/so101", root=tmp_path / "ds")
+    assert meta.total_episodes == 2 and meta.total_frames == 6
+    # an early exit keeps what was recorded so far
+    ev = new_events()
+    ev["exit_early"] = True
+    assert record_episode(rec, leader, follower, "wave", 1.0, 50, ev, save=False) == 0 and ev["exit_early"] is False
+    rec.clear_episode_buffer()
+    # a resumed session only adds what is missing, and continues the numbering
+    again = open_dataset_for_append("local/so101", tmp_path / "ds")
+    assert record_session(again, leader, follower, "wave", 3, 0.04, 0.0, 50, new_events(), say=lambda m: None) == 1
+    assert record_session(again, leader, follower, "wave", 3, 0.04, 0.0, 50, new_events(), say=said.append) == 0
+    assert "nothing to record" in said[-1]
+    meta = LeRobotDatasetMetadata("local/so101", root=tmp_path / "ds")
+    assert meta.total_episodes == 3 and sorted(meta.episodes) == [0, 1, 2]
