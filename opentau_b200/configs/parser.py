@@ -63,8 +63,60 @@ def load_plugin(path: str) -> None:
         raise ModuleNotFoundError(f"plugin {path!r} could not be imported: {e}") from e
 
 
-def parse_config(config_cls, argv: list[str] | None = None):
+def describe_fields(config_cls, prefix: str = "", depth: int = 0, max_depth: int = 2) -> list[str]:
+    """``--a.b=<type> (default)`` lines for the help text: the dataclass's fields, nested dataclasses two levels deep."""
+    import dataclasses
+    import typing
+    lines: list[str] = []
+    if not dataclasses.is_dataclass(config_cls):
+        return lines
+    try:
+        hints = typing.get_type_hints(config_cls)
+    except Exception:  # noqa: BLE001 - forward references that cannot be resolved here
+        hints = {}
+    for f in dataclasses.fields(config_cls):
+        tp = hints.get(f.name, f.type)
+        inner = next((a for a in typing.get_args(tp) if dataclasses.is_dataclass(a)), None)
+        nested = tp if dataclasses.is_dataclass(tp) else inner
+        name = f"{prefix}{f.name}"
+        if nested is not None and depth < max_depth:
+            lines.append(f"  --{name}.*")
+            lines += describe_fields(nested, f"{name}.", depth + 1, max_depth)
+            continue
+        if f.default is not dataclasses.MISSING:
+            default = repr(f.default)
+        elif f.default_factory is not dataclasses.MISSING:      # type: ignore[misc]
+            default = "<factory>"
+        else:
+            default = "<required>"
+        tname = getattr(tp, "__name__", None) or str(tp).replace("typing.", "")
+        lines.append(f"  --{name}=<{tname}>  (default {default})")
+    return lines
+
+
+def print_help(config_cls, doc: str | None = None) -> None:
+    prog = sys.argv[0].rsplit("/", 1)[-1]
+    print(f"usage: {prog} [--config_path=<json | dir | repo@rev>] [--<field>=<value> ...]\n")
+    if doc:
+        print(doc.strip() + "\n")
+    print(f"fields of {config_cls.__name__} (dotted overrides; nested blocks as --a.b=value):")
+    print("\n".join(describe_fields(config_cls)))
+    print("\nalso accepted: --plugin=<package>, --accelerate-config=<yaml>; launcher arguments (--local_rank ...) are ignored")
+
+
+def _build(config_cls, raw: dict[str, Any]):
+    """``config_cls.from_dict`` where the class has one (pipeline configs), the generic decoder otherwise."""
+    if hasattr(config_cls, "from_dict"):
+        return config_cls.from_dict(raw)
+    from .codec import decode
+    return decode(config_cls, raw, config_cls.__name__)
+
+
+def parse_config(config_cls, argv: list[str] | None = None, doc: str | None = None):
     argv = filter_distributed_args(list(sys.argv[1:] if argv is None else argv))
+    if any(a in ("-h", "--help") for a in argv):
+        print_help(config_cls, doc)
+        raise SystemExit(0)
     plugin = get_cli_value(argv, "plugin")
     if plugin:
         load_plugin(plugin)
@@ -74,11 +126,16 @@ def parse_config(config_cls, argv: list[str] | None = None):
     config_path = get_cli_value(argv, "config_path")
     argv = strip_arg(argv, "config_path")
     if config_path is not None:
-        cfg = config_cls.from_pretrained(config_path, cli_overrides=argv)
+        if hasattr(config_cls, "from_pretrained"):
+            cfg = config_cls.from_pretrained(config_path, cli_overrides=argv)
+        else:
+            from .codec import apply_overrides
+            from .refs import load_json_with_refs
+            cfg = _build(config_cls, apply_overrides(load_json_with_refs(config_path), argv))
     else:
         from .codec import apply_overrides
         raw: dict[str, Any] = apply_overrides({}, [a for a in argv if not a.startswith("--policy.path=")])
-        cfg = config_cls.from_dict(raw)
+        cfg = _build(config_cls, raw)
     if accel is not None and hasattr(cfg, "distributed"):
         from .default import DistributedConfig
         d = DistributedConfig.from_accelerate_yaml(accel)
@@ -97,7 +154,7 @@ def wrap(config_path: str | None = None) -> Callable:
                 return fn(*args, **kwargs)
             hints = inspect.get_annotations(fn, eval_str=True)
             first = next(iter(inspect.signature(fn).parameters))
-            cfg = parse_config(hints[first])
+            cfg = parse_config(hints[first], doc=sys.modules[fn.__module__].__doc__ or fn.__doc__)
             return fn(cfg)
         return inner
     return deco

@@ -11,6 +11,8 @@ def list_ports() -> set[str]:
 
 
 def main(argv=None):
+    import argparse
+    argparse.ArgumentParser(description=__doc__).parse_args(argv)        # no options: --help explains the procedure
     before = list_ports()
     input("Unplug the USB cable of the arm and press Enter...")
     time.sleep(0.5)

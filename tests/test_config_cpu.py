@@ -306,3 +306,39 @@ def test_dataset_wandb_and_eval_config_rules():
                     (dict(video_preset="warp"), "video_preset"), (dict(batch_size=8, n_episodes=4), "batch size")):
         with pytest.raises(ValueError, match=msg):
             EvalConfig(**kw)
+
+
+def test_cli_help_and_plain_dataclass_configs(tmp_path, capsys):
+    """``--help`` lists the dotted fields and exits 0; a config class without ``from_dict`` / ``from_pretrained`` (the
+    tools' own small dataclasses) is built by the generic decoder, from overrides alone or from a JSON file."""
+    import json
+    from dataclasses import dataclass, field
+
+    import pytest
+
+    from opentau_b200.configs import parser
+    from opentau_b200.configs.train import TrainPipelineConfig
+
+    @dataclass
+    class Inner:
+        rate: float = 0.5
+
+    @dataclass
+    class ToolConfig:
+        root: str = ""
+        count: int = 3
+        inner: Inner = field(default_factory=Inner)
+
+    with pytest.raises(SystemExit) as e:
+        parser.parse_config(ToolConfig, ["--help"], doc="A tool.")
+    out = capsys.readouterr().out
+    assert e.value.code == 0 and "A tool." in out and "--count=<int>  (default 3)" in out and "--inner.rate=<float>" in out
+    with pytest.raises(SystemExit):
+        parser.parse_config(TrainPipelineConfig, ["-h"])
+    out = capsys.readouterr().out
+    assert "--dataset_mixture.*" in out and "--batch_size=" in out and "--eval.n_episodes=" in out
+    cfg = parser.parse_config(ToolConfig, ["--root=/data", "--inner.rate=0.25", "--local_rank=1"])
+    assert (cfg.root, cfg.count, cfg.inner.rate) == ("/data", 3, 0.25)
+    (tmp_path / "tool.json").write_text(json.dumps({"count": 7, "inner": {"rate": 0.1}}))
+    cfg = parser.parse_config(ToolConfig, [f"--config_path={tmp_path / 'tool.json'}", "--count=9"])
+    assert (cfg.count, cfg.inner.rate) == (9, 0.1)
