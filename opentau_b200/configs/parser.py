@@ -133,8 +133,18 @@ def parse_config(config_cls, argv: list[str] | None = None, doc: str | None = No
             from .refs import load_json_with_refs
             cfg = _build(config_cls, apply_overrides(load_json_with_refs(config_path), argv))
     else:
-        from .codec import apply_overrides
-        raw: dict[str, Any] = apply_overrides({}, [a for a in argv if not a.startswith("--policy.path=")])
+        from .codec import apply_overrides, encode
+        policy_path = get_cli_value(argv, "policy.path")
+        raw: dict[str, Any] = apply_overrides({}, strip_arg(argv, "policy.path"))
+        if policy_path is not None:
+            # the policy block starts from the checkpoint's own configuration; dotted --policy.* overrides win
+            from ..policies.factory import _import_all_configs
+            from .policies import PreTrainedConfig
+            _import_all_configs()                       # the registry of policy types fills on import
+            merged = encode(PreTrainedConfig.from_pretrained(policy_path))
+            merged.update({k: v for k, v in (raw.get("policy") or {}).items() if k != "type"})
+            merged["pretrained_path"] = policy_path
+            raw["policy"] = merged
         cfg = _build(config_cls, raw)
     if accel is not None and hasattr(cfg, "distributed"):
         from .default import DistributedConfig

@@ -142,6 +142,19 @@ def make_policy(cfg: PreTrainedConfig, ds_meta: Any | None = None, per_dataset_s
                 head_stats, norm_keys, dataset_to_norm_index = [ds_meta.stats], norm_keys or [key], {repo_id: 0}
         if features is None:
             features = getattr(ds_meta, "policy_features", None)
+    if not features and not cfg.input_features and not cfg.output_features and cfg.pretrained_path:
+        # a pipeline config whose policy block names a checkpoint but binds no features (an eval / diagnosis run
+        # started from the TRAINING config): the checkpoint knows what it was built with
+        try:
+            saved = PreTrainedConfig.from_pretrained(cfg.pretrained_path)
+            features = {**(saved.input_features or {}), **(saved.output_features or {})} or None
+            if features:
+                import logging
+                logging.info("policy features taken from the checkpoint's configuration (%s)", cfg.pretrained_path)
+                if not cfg.dataset_names and saved.dataset_names and norm_keys is None:
+                    cfg.dataset_names, cfg.dataset_to_norm_index = saved.dataset_names, saved.dataset_to_norm_index
+        except Exception:  # noqa: BLE001 - no readable configuration beside the weights: construction reports it
+            features = None
     if features and not cfg.input_features and not cfg.output_features:
         cfg.output_features = {k: f for k, f in features.items() if f.type is FeatureType.ACTION}
         cfg.input_features = {k: f for k, f in features.items() if f.type is not FeatureType.ACTION}

@@ -342,3 +342,26 @@ def test_cli_help_and_plain_dataclass_configs(tmp_path, capsys):
     (tmp_path / "tool.json").write_text(json.dumps({"count": 7, "inner": {"rate": 0.1}}))
     cfg = parser.parse_config(ToolConfig, [f"--config_path={tmp_path / 'tool.json'}", "--count=9"])
     assert (cfg.count, cfg.inner.rate) == (9, 0.1)
+
+
+def test_policy_path_without_a_config_file_and_features_from_the_checkpoint(tmp_path):
+    """``--policy.path=<checkpoint>`` alone builds the policy block from the checkpoint's own configuration; a pipeline
+    config that only names ``policy.pretrained_path`` (an eval started from the training config, whose policy block
+    binds no features) gets its features from the checkpoint too."""
+    from helpers import TINY, tiny_pi05
+    from opentau_b200.configs import parser
+    from opentau_b200.configs.train import TrainPipelineConfig
+    from opentau_b200.policies.factory import make_policy
+    tiny_pi05().save_pretrained(tmp_path / "ck")
+    cfg = parser.parse_config(TrainPipelineConfig, [f"--policy.path={tmp_path / 'ck'}", "--policy.num_steps=3",
+                                                    "--resolution=[224,224]", "--num_cams=1"])
+    assert cfg.policy.type == "pi05" and cfg.policy.num_steps == 3 and cfg.policy.pretrained_path == str(tmp_path / "ck")
+    assert "actions" in cfg.policy.output_features and "state" in cfg.policy.input_features
+    bare = TrainPipelineConfig.from_dict({"policy": {"type": "pi05", "pretrained_path": str(tmp_path / "ck"),
+                                                     "chunk_size": 10, "n_action_steps": 10, "prompt_max_length": 16,
+                                                     "discrete_action_max_length": 8, "discrete_action_vocab_size": 256,
+                                                     "device": "cpu", **TINY},
+                                          "resolution": [224, 224], "num_cams": 1})
+    assert not bare.policy.output_features
+    pol = make_policy(bare.policy)
+    assert "actions" in pol.unnormalize_outputs.features and "state" in pol.normalize_inputs.features
