@@ -461,3 +461,9 @@ extern "C" int otb_seq_concat(const void* a, long long a_sb, long long a_ss, con
                                                 static_cast<uint4*>(out), B, S1, S2, vec);
   return (int)cudaGetLastError();
 }
+
+// Zero-fill of a dense buffer through the driver's memset path (the flat gradient buffer: several GB per step).
+extern "C" int otb_zero_bytes(void* p, unsigned long long bytes, cudaStream_t stream) {
+  if (!p || bytes == 0) return p ? 0 : -1;
+  return (int)cudaMemsetAsync(p, 0, (size_t)bytes, stream);
+}

@@ -747,6 +747,19 @@ def seq_concat(a: Tensor, c: Tensor) -> Tensor:
     return out
 
 
+def zero_(t: Tensor) -> Tensor:
+    """``t.zero_()`` for a dense CUDA tensor through the driver's memset (about twice the rate of the element-wise fill
+    on multi-GB buffers); anything else falls back to ``t.zero_()``."""
+    global launch_count
+    if not (t.is_cuda and t.is_contiguous() and t.numel() > 0):
+        return t.zero_()
+    from ctypes import c_ulonglong
+    _check(_lib.load("train_elementwise").otb_zero_bytes(_p(t), c_ulonglong(t.numel() * t.element_size()), _stream()),
+           "zero_bytes")
+    launch_count += 1
+    return t
+
+
 def seq_concat_supported(a: Tensor, c: Tensor) -> bool:
     if not (a.is_cuda and a.dtype == c.dtype == torch.bfloat16 and a.dim() == c.dim() >= 3):
         return False

@@ -135,7 +135,11 @@ class FlatParamStore:
 
     def zero_grad(self) -> None:
         for g in self.groups:
-            g.grad.zero_()
+            if g.grad.is_cuda:
+                from ..ops import cuda_ops
+                cuda_ops.zero_(g.grad)
+            else:
+                g.grad.zero_()
             for p in g.params:
                 p.grad = None
 

@@ -221,3 +221,17 @@ def test_seq_concat_kernel_matches_cat_forward_and_backward(dev):
     odd = torch.randn(4, 7, 1, 60, device=dev).to(torch.bfloat16)   # 60 elements per row: not a multiple of 8 -> cat
     assert not cuda_ops.seq_concat_supported(odd, odd) and ops.seq_concat(odd, odd).shape == (4, 14, 1, 60)
     assert torch.equal(ops.seq_concat(a.float().cpu(), c.detach().float().cpu()), ref.float().cpu())
+
+
+def test_zero_fill_through_memset(dev):
+    from opentau_b200.ops import cuda_ops
+    t = torch.randn(3, 1000, 7, device=dev, dtype=torch.bfloat16)
+    view = t[1]
+    cuda_ops.zero_(view)                                  # a dense slice: only its bytes are cleared
+    assert float(view.abs().sum()) == 0.0 and float(t[0].abs().sum()) > 0 and float(t[2].abs().sum()) > 0
+    strided = t[:, ::2]
+    cuda_ops.zero_(strided)                               # not dense: the element-wise fallback
+    assert float(strided.abs().sum()) == 0.0 and float(t[0, 1::2].abs().sum()) > 0
+    big = torch.ones(64 << 20, device=dev, dtype=torch.bfloat16)
+    cuda_ops.zero_(big)
+    assert float(big.float().sum()) == 0.0
