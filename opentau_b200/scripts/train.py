@@ -18,6 +18,7 @@ Run one process per GPU::
 
 from __future__ import annotations
 
+import json
 import logging
 import os
 import time
@@ -99,6 +100,22 @@ class WandBLogger:
             self.file.flush()
         if self.run is not None:
             self.run.log(metrics, step=step, commit=True)
+
+    def log_videos(self, videos: dict[str, str], step: int, enabled: bool = True) -> None:
+        """Grid-summary videos go to the experiment tracker (never the per-episode clips); without a tracker the paths
+        are noted in the metrics file so that they can be found later."""
+        if not videos or not enabled:
+            return
+        if self.file is not None:
+            import json
+            self.file.write(json.dumps({"step": step, "videos": videos}) + "\n")
+            self.file.flush()
+        if self.run is not None:
+            try:
+                import wandb
+                self.run.log({k: wandb.Video(v, format="mp4") for k, v in videos.items()}, step=step)
+            except Exception as e:  # noqa: BLE001 - logging must never stop a run
+                logging.warning("video logging skipped: %s", e)
 
     def finish(self) -> None:
         if self.file is not None:
@@ -386,11 +403,27 @@ def train(cfg: TrainPipelineConfig) -> dict[str, float]:
                              vm["Validation/MSE Loss"], vm["Validation/CE Loss"])
 
         if is_eval:
-            from .eval import eval_policy_on_config
-            info = eval_policy_on_config(policy, cfg, device, rank=rank, world=world)
+            from .eval import collect_grid_summary_videos, eval_policy_on_config
+            # fresh environments per evaluation, closed before training resumes (a simulator's render contexts hold
+            # device memory that the caching allocator cannot give back); grid videos and the consolidated
+            # eval_info.json land under <output_dir>/eval/videos_step_<id>
+            step_id = get_step_checkpoint_dir(out_dir, cfg.steps, step).name
+            videos_dir = out_dir / "eval" / f"videos_step_{step_id}"
+            t_eval = time.perf_counter()
+            try:
+                info = eval_policy_on_config(policy, cfg, device, rank=rank, world=world, videos_dir=videos_dir)
+            finally:
+                policy.reset()                  # per-evaluation observation / action queues must not reach training
             metrics["Success Rate"] = info["aggregated"]["pc_success"]
+            metrics["Evaluation Time"] = time.perf_counter() - t_eval
             for g, v in info.get("per_group", {}).items():
                 metrics[f"Success/{g}"] = v["pc_success"]
+            if is_main:
+                videos_dir.mkdir(parents=True, exist_ok=True)
+                (videos_dir / "eval_info.json").write_text(json.dumps(info, indent=2, default=str))
+                tracker_wb.log_videos({f"Eval Videos/{task}": path for task, path in collect_grid_summary_videos(videos_dir)},
+                                  step, enabled=not cfg.wandb.disable_video and cfg.eval.max_episodes_rendered > 0)
+            control.wait_for_everyone()
 
         if is_save:
             control.wait_for_everyone()

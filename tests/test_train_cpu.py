@@ -172,3 +172,23 @@ def test_ragged_gather_keeps_rows_aligned_across_ranks():
     ret = mp.Manager().dict()
     mp.spawn(_ragged_rank, args=(2, free_port(), ret), nprocs=2, join=True)
     assert ret[0] == ret[1] == ([0.0, 1.0, 2.0, 10.0], [0, 0, 0, 1])
+
+
+def test_in_training_evaluation_writes_videos_and_info(tmp_path):
+    """``eval_freq`` with an environment: fresh environments per evaluation, success metrics in the log, the grid video
+    and the consolidated eval_info.json under <output_dir>/eval/videos_step_<id>."""
+    out = tmp_path / "run"
+    cfg = _cfg(out, 2, val_freq=0, eval_freq=2, save_freq=100,
+               env={"type": "fake", "state_dim": 12, "action_dim": 6, "resolution": [224, 224], "episode_length": 6},
+               eval={"n_episodes": 2, "batch_size": 2, "max_episodes_rendered": 2, "use_async_envs": False})
+    train(cfg)
+    rows = [json.loads(line) for line in (out / "metrics.jsonl").read_text().splitlines()]
+    last = next(r for r in reversed(rows) if "Success Rate" in r)
+    assert last["step"] == 2 and "Evaluation Time" in last and any(k.startswith("Success/") for k in last)
+    vdir = out / "eval" / "videos_step_000002"
+    info = json.loads((vdir / "eval_info.json").read_text())
+    assert info["aggregated"]["n"] == 2
+    grids = list(vdir.rglob("grid_summary.mp4"))
+    assert len(grids) == 1
+    noted = [r for r in rows if "videos" in r]
+    assert noted and list(noted[-1]["videos"].values())[0].endswith("grid_summary.mp4")
