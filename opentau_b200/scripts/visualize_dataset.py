@@ -81,16 +81,25 @@ def main(argv=None) -> None:
     from ..configs.default import DatasetConfig, DatasetMixtureConfig
     from ..configs.train import TrainPipelineConfig
     from ..datasets.factory import make_dataset
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--repo-id", required=True)
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--repo-id", default=None, help="dataset name; optional when --root points at a local dataset")
     ap.add_argument("--root", default=None)
-    ap.add_argument("--episode", type=int, default=0)
-    ap.add_argument("--output", default="outputs/dataset_viz")
+    ap.add_argument("--episode", "--episode-index", dest="episode", type=int, nargs="+", default=[0],
+                    help="one or several episode indices")
+    ap.add_argument("--output", "--output-dir", dest="output", default="outputs/dataset_viz")
     a = ap.parse_args(argv)
+    if a.repo_id is None:
+        if a.root is None:
+            ap.error("give --repo-id, or --root of a local dataset")
+        a.repo_id = f"local/{Path(a.root).name}"
     dc = DatasetConfig(repo_id=a.repo_id, root=a.root)
     cfg = TrainPipelineConfig(dataset_mixture=DatasetMixtureConfig(datasets=[dc]))
     ds = make_dataset(dc, cfg)
-    print(json.dumps(visualize_episode(ds, a.episode, a.output), indent=2))
+    known = set(ds.episodes)
+    for ep in a.episode:
+        if ep not in known:
+            ap.error(f"episode {ep} is not in the dataset (it has {len(known)} episodes)")
+        print(json.dumps(visualize_episode(ds, ep, a.output), indent=2))
 
 
 if __name__ == "__main__":
