@@ -171,7 +171,7 @@ class Attention(nn.Module):
         cfg = self.cfg
         h, hk, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         out = self.qkv_proj(x)
-        q, k, v = ops.split_last(out, self._splits)
+        q, k, v = out.split(self._splits, dim=-1)
         q = q.unflatten(-1, (h, hd))
         k = k.unflatten(-1, (hk, hd))
         v = v.unflatten(-1, (hk, hd))

@@ -277,13 +277,6 @@ def embedding(table: Tensor, ids: Tensor, scale: float = 1.0, padding_idx: int |
     return out * scale if scale != 1.0 else out
 
 
-def split_last(x: Tensor, sizes) -> tuple[Tensor, ...]:
-    """``x.split(sizes, dim=-1)`` (views); on the GPU its backward assembles the gradient with one copy kernel."""
-    if oracle_mode():
-        return tuple(x.split(list(sizes), dim=-1))
-    return fused.split_last(x, sizes)
-
-
 def seq_concat(a: Tensor, c: Tensor) -> Tensor:
     """``cat([a, c], dim=1)``: cached keys / values followed by the new ones.  One copy kernel for dense bf16 rows on
     the GPU, ``torch.cat`` otherwise."""
@@ -314,5 +307,5 @@ __all__ = [
     "BIG_NEG", "INT_MIN", "linear", "rms_norm", "ada_rms_norm", "layer_norm", "gated_residual", "linear_gated_residual", "gated_mlp_gated_residual", "qkv_post", "can_fuse_qkv_post", "rope",
     "gated_mlp", "act_fn", "linear_act", "block_attention", "mha", "flow_matching_masked_mse", "linear_cross_entropy",
     "resize_with_pad", "dropout_gated_residual", "embedding", "make_block_ids", "dense_mask_from_blocks", "rope_angles", "mrope_angles",
-    "apply_rope", "rms_norm_fork", "ada_rms_norm_fork", "seq_concat", "split_last", "sinusoidal_time_embedding", "flow_interpolate", "euler_step", "patch_embed", "oracle_mode", "prims", "fused", "ref",
+    "apply_rope", "rms_norm_fork", "ada_rms_norm_fork", "seq_concat", "sinusoidal_time_embedding", "flow_interpolate", "euler_step", "patch_embed", "oracle_mode", "prims", "fused", "ref",
 ]

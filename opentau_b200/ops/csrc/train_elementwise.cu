@@ -462,58 +462,6 @@ extern "C" int otb_seq_concat(const void* a, long long a_sb, long long a_ss, con
   return (int)cudaGetLastError();
 }
 
-// out[r, :] = [p0[r, :], p1[r, :], ...]: concatenation along the innermost dimension in 16-byte pieces (the gradient of
-// a fused projection assembled from the gradients of its slices).  Each part's rows are dense, `stride` 16-byte units
-// apart; one thread moves one piece.
-struct CatLastParts {
-  const uint4* ptr[4];
-  long long stride[4];   // row stride of the part, in 16-byte units
-  int vec[4];            // 16-byte pieces per row of the part
-  int n;
-};
-
-__global__ void concat_last_kernel(CatLastParts parts, uint4* __restrict__ out, long long rows, int out_vec) {
-  const long long total = rows * out_vec;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const long long r = idx / out_vec;
-    int j = (int)(idx - r * out_vec);
-    int k = 0;
-#pragma unroll
-    for (int t = 0; t < 3; ++t)
-      if (k < parts.n - 1 && j >= parts.vec[k]) {
-        j -= parts.vec[k];
-        ++k;
-      }
-    out[idx] = parts.ptr[k][r * parts.stride[k] + j];
-  }
-}
-
-// ptrs / strides / vecs: n (1..4) parts; every pointer 16-byte aligned; out: (rows, sum(vecs)) dense.
-extern "C" int otb_concat_last(const void* const* ptrs, const long long* strides, const int* vecs, int n, void* out,
-                               long long rows, cudaStream_t stream) {
-  if (n < 1 || n > 4 || rows <= 0 || !out) return -1;
-  CatLastParts parts;
-  int out_vec = 0;
-  for (int i = 0; i < 4; ++i) {
-    parts.ptr[i] = i < n ? static_cast<const uint4*>(ptrs[i]) : nullptr;
-    parts.stride[i] = i < n ? strides[i] : 0;
-    parts.vec[i] = i < n ? vecs[i] : 0;
-    if (i < n) {
-      if (!ptrs[i] || vecs[i] <= 0 || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15)) return -2;
-      out_vec += vecs[i];
-    }
-  }
-  parts.n = n;
-  if (reinterpret_cast<uintptr_t>(out) & 15) return -2;
-  const long long total = rows * out_vec;
-  const int threads = 256;
-  const long long want = (total + threads - 1) / threads;
-  const unsigned blocks = (unsigned)(want < 148LL * 32 ? want : 148LL * 32);
-  concat_last_kernel<<<blocks, threads, 0, stream>>>(parts, static_cast<uint4*>(out), rows, out_vec);
-  return (int)cudaGetLastError();
-}
-
 // Zero-fill of a dense buffer through the driver's memset path (the flat gradient buffer: several GB per step).
 extern "C" int otb_zero_bytes(void* p, unsigned long long bytes, cudaStream_t stream) {
   if (!p || bytes == 0) return p ? 0 : -1;

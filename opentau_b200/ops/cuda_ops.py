@@ -747,49 +747,6 @@ def seq_concat(a: Tensor, c: Tensor) -> Tensor:
     return out
 
 
-def _as_rows(t: Tensor) -> Tensor | None:
-    """``t`` as ``(rows, E)`` without a copy, or ``None`` when its leading dims do not collapse onto one row stride."""
-    try:
-        return t.view(-1, t.shape[-1])
-    except RuntimeError:
-        return None
-
-
-def concat_last_supported(parts: list[Tensor]) -> bool:
-    """1 to 4 bf16 CUDA tensors of equal leading shape whose rows are dense, reachable with one row stride, a multiple
-    of 8 elements wide and apart, and 16-byte aligned."""
-    if not 1 <= len(parts) <= 4:
-        return False
-    lead = parts[0].shape[:-1]
-    for t in parts:
-        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() >= 2 and t.shape[:-1] == lead and t.numel() > 0):
-            return False
-        if t.shape[-1] % 8 or t.stride(-1) != 1 or t.data_ptr() % 16:
-            return False
-        rows = _as_rows(t)
-        if rows is None or (rows.shape[0] > 1 and rows.stride(0) % 8):
-            return False
-    return True
-
-
-def concat_last(parts: list[Tensor]) -> Tensor:
-    """``torch.cat(parts, dim=-1)`` in one vectorised copy kernel (see :func:`concat_last_supported`)."""
-    global launch_count
-    import ctypes
-    n = len(parts)
-    views = [_as_rows(t) for t in parts]
-    rows = int(views[0].shape[0])
-    width = sum(int(t.shape[-1]) for t in parts)
-    out = torch.empty(*parts[0].shape[:-1], width, dtype=parts[0].dtype, device=parts[0].device)
-    ptrs = (ctypes.c_void_p * n)(*[ctypes.c_void_p(v.data_ptr()) for v in views])
-    strides = (ctypes.c_longlong * n)(*[(v.stride(0) if rows > 1 else v.shape[1]) // 8 for v in views])
-    vecs = (ctypes.c_int * n)(*[v.shape[1] // 8 for v in views])
-    _check(_lib.load("train_elementwise").otb_concat_last(ptrs, strides, vecs, c_int(n), _p(out), c_longlong(rows),
-                                                          _stream()), "concat_last")
-    launch_count += 1
-    return out
-
-
 def zero_(t: Tensor) -> Tensor:
     """``t.zero_()`` for a dense CUDA tensor through the driver's memset (about twice the rate of the element-wise fill
     on multi-GB buffers); anything else falls back to ``t.zero_()``."""

@@ -198,7 +198,7 @@ class AdaRMSNormFn(torch.autograd.Function):
             dgate = torch.zeros_like(dscale)
         elif mod.dim() == 2:
             dgate = dgate.reshape(mod.shape[0], -1, dscale.shape[-1]).sum(1) if dgate.dim() == 3 else dgate
-        dmod = cat_last([dscale, dshift, dgate.to(dscale.dtype)])
+        dmod = torch.cat([dscale, dshift, dgate.to(dscale.dtype)], dim=-1)
         return dx, dmod, None
 
 
@@ -229,7 +229,7 @@ class AdaRMSNormForkFn(torch.autograd.Function):
             dgate = torch.zeros_like(dscale)
         elif mod.dim() == 2:
             dgate = dgate.reshape(mod.shape[0], -1, dscale.shape[-1]).sum(1) if dgate.dim() == 3 else dgate
-        dmod = cat_last([dscale, dshift, dgate.to(dscale.dtype)])
+        dmod = torch.cat([dscale, dshift, dgate.to(dscale.dtype)], dim=-1)
         return dx, dmod, None
 
 
@@ -453,35 +453,3 @@ class SeqConcatFn(torch.autograd.Function):
     def backward(ctx, g: Tensor):
         return (g[:, :ctx.s1] if ctx.needs_input_grad[0] else None,
                 g[:, ctx.s1:] if ctx.needs_input_grad[1] else None)
-
-
-def cat_last(parts: list[Tensor]) -> Tensor:
-    """``torch.cat(parts, dim=-1)`` through the one-kernel copy where its layout rules hold (bf16, 16-byte rows)."""
-    if parts[0].is_cuda:
-        from . import cuda_ops
-        if cuda_ops.concat_last_supported(parts):
-            return cuda_ops.concat_last(parts)
-    return torch.cat(parts, dim=-1)
-
-
-class SplitLastFn(torch.autograd.Function):
-    """``x.split(sizes, dim=-1)`` whose backward assembles the gradient with one copy kernel instead of the library's
-    batched concatenation (a fused q / k / v projection: three gradient slices of 2048 + 256 + 256 columns per layer)."""
-
-    @staticmethod
-    def forward(ctx, x: Tensor, sizes: tuple[int, ...]):
-        ctx.sizes, ctx.meta = tuple(sizes), (x.shape, x.dtype, x.device)
-        return tuple(x.split(list(sizes), dim=-1))
-
-    @staticmethod
-    def backward(ctx, *grads):
-        shape, dtype, device = ctx.meta
-        parts = [g if g is not None else torch.zeros(*shape[:-1], n, dtype=dtype, device=device)
-                 for g, n in zip(grads, ctx.sizes)]
-        return cat_last(parts), None
-
-
-def split_last(x: Tensor, sizes) -> tuple[Tensor, ...]:
-    if x.is_cuda and x.requires_grad and torch.is_grad_enabled() and x.dtype == torch.bfloat16:
-        return SplitLastFn.apply(x, tuple(int(n) for n in sizes))
-    return tuple(x.split(list(sizes), dim=-1))

@@ -235,33 +235,3 @@ def test_zero_fill_through_memset(dev):
     big = torch.ones(64 << 20, device=dev, dtype=torch.bfloat16)
     cuda_ops.zero_(big)
     assert float(big.float().sum()) == 0.0
-
-
-def test_split_last_backward_assembles_the_gradient_in_one_kernel(dev):
-    from opentau_b200 import ops
-    from opentau_b200.ops import cuda_ops
-    torch.manual_seed(0)
-    x = torch.randn(3, 37, 2560, device=dev, dtype=torch.bfloat16, requires_grad=True)
-    ref = x.detach().clone().requires_grad_()
-    sizes = (2048, 256, 256)
-    q, k, v = ops.split_last(x, sizes)
-    rq, rk, rv = ref.split(list(sizes), dim=-1)
-    assert torch.equal(q, rq) and torch.equal(v, rv)
-    gq, gk, gv = (torch.randn_like(t) for t in (q, k, v))
-    before = cuda_ops.launch_count
-    ((q.unflatten(-1, (8, 256)) * gq.unflatten(-1, (8, 256))).sum() + (k * gk).sum() + (v * gv).sum()).backward()
-    ((rq * gq).sum() + (rk * gk).sum() + (rv * gv).sum()).backward()
-    assert cuda_ops.launch_count > before and torch.equal(x.grad, ref.grad)
-    # a slice that is never used contributes zeros
-    y = torch.randn(5, 64, device=dev, dtype=torch.bfloat16, requires_grad=True)
-    a, _, c = ops.split_last(y, (16, 24, 24))
-    (a.sum() + 2 * c.sum()).backward()
-    assert torch.equal(y.grad[:, 16:40], torch.zeros(5, 24, device=dev, dtype=torch.bfloat16)) and float(y.grad[:, 40:].min()) == 2.0
-    # direct: strided parts (slices of wider tensors), two to four of them, against torch.cat
-    wide = torch.randn(4, 9, 96, device=dev, dtype=torch.bfloat16)
-    parts = [wide[..., :32], wide[..., 32:40], wide[..., 40:96], torch.randn(4, 9, 8, device=dev, dtype=torch.bfloat16)]
-    for n in (1, 2, 3, 4):
-        assert cuda_ops.concat_last_supported(parts[:n])
-        assert torch.equal(cuda_ops.concat_last(parts[:n]), torch.cat(parts[:n], dim=-1))
-    assert not cuda_ops.concat_last_supported([wide[..., 1:9]])              # not 16-byte aligned
-    assert not cuda_ops.concat_last_supported([wide[..., :12]])              # width not a multiple of 8
