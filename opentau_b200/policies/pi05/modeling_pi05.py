@@ -735,7 +735,8 @@ class PI05Policy(PreTrainedPolicy):
         return [" ".join(map(str, row)) for row in ids.cpu().tolist()]
 
     def prepare_language(self, batch) -> tuple[Tensor, Tensor]:
-        """Tokenises ``"Task: {task}, State: {bins};\\n"`` (discrete) or the bare task (continuous);
+        """Tokenises ``"Task: {task}, State: {bins};\\n"`` (discrete) or ``"Task: {task}, "`` (continuous state)
+        (reference ``src/opentau/policies/pi05/modeling_pi05.py:1142-1180``);
         a batch that already carries ``lang_tokens``/``lang_masks`` is passed through."""
         cfg = self.config
         device = batch["state"].device
@@ -748,7 +749,7 @@ class PI05Policy(PreTrainedPolicy):
             states = self.prepare_discrete_state(batch)
             prompts = [f"Task: {t}, State: {s};\n" for t, s in zip(tasks, states)]
         else:
-            prompts = [t if t.endswith("\n") else f"{t}\n" for t in tasks]
+            prompts = [f"Task: {t}, " for t in tasks]      # the state follows as its own "State: " block of the prefix
         enc = self.language_tokenizer(prompts, padding="max_length", padding_side="right",
                                       max_length=cfg.prompt_max_length, return_tensors="pt", truncation=True)
         return enc["input_ids"].to(device), enc["attention_mask"].to(device).bool()

@@ -166,7 +166,8 @@ class PI05MemPolicy(PI05Policy):
             return batch["lang_tokens"].to(device), batch["lang_masks"].to(device).bool()
         tasks = batch["prompt"]
         tasks = [tasks] if isinstance(tasks, str) else list(tasks)
-        enc = self.language_tokenizer([t if t.endswith("\n") else f"{t}\n" for t in tasks], padding="max_length",
+        # "<eos>" is spelled out: the tokenizer maps it to the separator id (reference pi05_mem/modeling_pi05.py:1051-1068)
+        enc = self.language_tokenizer([f"Task: {t}<eos>Actions:" for t in tasks], padding="max_length",
                                       padding_side="right", max_length=self.config.prompt_max_length,
                                       return_tensors="pt", truncation=True)
         return enc["input_ids"].to(device), enc["attention_mask"].to(device).bool()

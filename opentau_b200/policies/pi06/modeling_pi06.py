@@ -82,3 +82,33 @@ class PI06Policy(PI05Policy):
     def _vocab_size(config) -> int:
         vc = dict(getattr(config, "vlm_config", None) or {})
         return gemma3_4b_config(**{**vc.get("text", {}), **(config.vlm or {})}).vocab_size
+
+    def prepare_language(self, batch):
+        """``"Task: {task}<eos>State: {bins}<eos>Response:"`` when the backbone predicts a response, else
+        ``"...<eos>Actions:"``: the prefix has no separate indicator blocks, the prompt spells the separators out
+        (reference ``src/opentau/policies/pi06/modeling_pi06.py:908-943``)."""
+        device = batch["state"].device
+        if "lang_tokens" in batch:
+            return batch["lang_tokens"].to(device), batch["lang_masks"].to(device).bool()
+        tasks = batch["prompt"]
+        tasks = [tasks] if isinstance(tasks, str) else list(tasks)
+        tail = "Response:" if self.config.predict_response else "Actions:"
+        prompts = [f"Task: {t}<eos>State: {s}<eos>{tail}" for t, s in zip(tasks, self.prepare_discrete_state(batch))]
+        enc = self.language_tokenizer(prompts, padding="max_length", padding_side="right",
+                                      max_length=self.config.prompt_max_length, return_tensors="pt", truncation=True)
+        return enc["input_ids"].to(device), enc["attention_mask"].to(device).bool()
+
+    def prepare_response(self, batch):
+        """``"{response}<eos>Actions:"``: the response closes with the separator and hands over to the action block."""
+        cfg = self.config
+        if not cfg.predict_response:
+            return None, None
+        device = batch["state"].device
+        if "response_tokens" in batch:
+            return batch["response_tokens"].to(device), batch["response_masks"].to(device).bool()
+        resp = batch.get("response")
+        if resp is None:
+            return None, None
+        enc = self.language_tokenizer([f"{r}<eos>Actions:" for r in resp], padding="max_length", padding_side="right",
+                                      max_length=cfg.response_max_length, return_tensors="pt", truncation=True)
+        return enc["input_ids"].to(device), enc["attention_mask"].to(device).bool()

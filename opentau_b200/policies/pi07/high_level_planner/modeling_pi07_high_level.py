@@ -228,8 +228,18 @@ class PI07HighLevelPlannerPolicy(PreTrainedPolicy):
             return batch["lang_tokens"].to(device), batch["lang_masks"].to(device).bool()
         tasks = batch["prompt"]
         tasks = [tasks] if isinstance(tasks, str) else list(tasks)
-        mems = batch.get("memory", [""] * len(tasks))
-        texts = [f"Task: {t}, Memory: {m}\n" for t, m in zip(tasks, mems)]
+        # "Task: ..., Past Memory: ..., State: <bins>, " (reference pi07/high_level_planner/modeling_pi07_high_level.py:
+        # 749-760); the memory comes as ``past_memory`` (``memory`` is accepted too), the state part only with a state
+        mems = batch.get("past_memory", batch.get("memory", [""] * len(tasks)))
+        if "state" in batch:
+            from ...pi05.modeling_pi05 import PI05Policy
+            st = batch["state"].to(device)
+            idx = self._resolve_dataset_index(batch, st.shape[0], device)
+            normed = self.normalize_inputs({"state": st}, idx)            # the bins are cut on the NORMALISED state
+            states = PI05Policy.prepare_discrete_state(self, normed)
+            texts = [f"Task: {t}, Past Memory: {m}, State: {s}, " for t, m, s in zip(tasks, mems, states)]
+        else:
+            texts = [f"Task: {t}, Past Memory: {m}, " for t, m in zip(tasks, mems)]
         enc = self.language_tokenizer(texts, padding="max_length", padding_side="right",
                                       max_length=self.config.prompt_max_length, return_tensors="pt", truncation=True)
         return enc["input_ids"].to(device), enc["attention_mask"].to(device).bool()
@@ -240,8 +250,11 @@ class PI07HighLevelPlannerPolicy(PreTrainedPolicy):
         lt, lm = self._lang(batch, device)
         B = lt.shape[0]
         cfg = self.config
-        mem_t, mem_m = self._tok(batch.get("next_memory", [""] * B), cfg.memory_max_length, device, "memory", batch)
-        res_t, res_m = self._tok(batch.get("response", [""] * B), cfg.response_max_length, device, "response", batch)
+        # targets close with the separator, so that decoding knows where a text ends
+        mem_t, mem_m = self._tok([f"{m}<eos>" for m in batch.get("next_memory", [""] * B)], cfg.memory_max_length,
+                                 device, "memory", batch)
+        res_t, res_m = self._tok([f"{r}<eos>" for r in batch.get("response", [""] * B)], cfg.response_max_length,
+                                 device, "response", batch)
         return self.model(images, masks, lt, lm, mem_t, mem_m, res_t, res_m, return_per_sample=return_per_sample)
 
     @torch.no_grad()

@@ -178,7 +178,7 @@ class PI07LowLevelPolicy(PI05Policy):
             return batch["lang_tokens"].to(device), batch["lang_masks"].to(device).bool()
         tasks = batch["prompt"]
         tasks = [tasks] if isinstance(tasks, str) else list(tasks)
-        enc = self.language_tokenizer([f"Task: {t}\n" for t in tasks], padding="max_length", padding_side="right",
+        enc = self.language_tokenizer([f"Task: {t}, " for t in tasks], padding="max_length", padding_side="right",
                                       max_length=self.config.prompt_max_length, return_tensors="pt", truncation=True)
         return enc["input_ids"].to(device), enc["attention_mask"].to(device).bool()
 
@@ -190,36 +190,59 @@ class PI07LowLevelPolicy(PI05Policy):
         resp = batch.get("response")
         if resp is None:
             return None, None
-        enc = self.language_tokenizer(list(resp), padding="max_length", padding_side="right",
-                                      max_length=self.config.response_max_length, return_tensors="pt",
-                                      truncation=True, add_special_tokens=False)
+        # "Subtask: {text}, " without special tokens; an empty subtask is an empty, fully masked segment
+        # (reference pi07/low_level/modeling_pi07_low_level.py:1226-1258)
+        enc = self.language_tokenizer([f"Subtask: {r}, " if r != "" else "" for r in resp], padding="max_length",
+                                      padding_side="right", max_length=self.config.response_max_length,
+                                      return_tensors="pt", truncation=True, add_special_tokens=False)
         mask = enc["attention_mask"].bool() & torch.tensor([bool(r) for r in resp])[:, None]
         return enc["input_ids"].to(device), mask.to(device)
 
     def prepare_metadata(self, batch) -> tuple[Tensor | None, Tensor | None]:
-        """``"Speed: s, Quality: q, Mistake: m, Robot: r, Control: c"`` from whichever keys are present."""
+        """Episode metadata as one text segment per sample, tokenized to ``metadata_max_length``:
+        ``"Metadata: Speed: 30,  Quality: 4,  Mistake: False,  Robot: so101,  FPS: 20,  Control: ee, "`` with only the
+        fields that are present, in exactly this order and spelling (each field is ``"<Label>: <value>, "`` and the
+        fields are joined by one more space: the string a checkpoint was trained on must be reproduced token for token;
+        reference ``src/opentau/policies/pi07/low_level/modeling_pi07_low_level.py:1348-1430``).  ``speed`` / ``quality``
+        / ``mistake`` / ``fps`` are tensors with a ``<key>_is_pad`` flag per sample (a padded entry is dropped; a tensor
+        without its flag counts as present); ``robot_type`` / ``control_mode`` are strings, empty = absent.  A sample
+        with no field gets an empty, fully masked segment; ``(None, None)`` when no sample has any."""
         device = batch["state"].device
         if "metadata_tokens" in batch:
             return batch["metadata_tokens"].to(device), batch["metadata_masks"].to(device).bool()
         B = batch["state"].shape[0]
-        parts: list[list[str]] = [[] for _ in range(B)]
-        for key, label in (("speed", "Speed"), ("quality", "Quality"), ("mistake", "Mistake")):
-            if key in batch:
-                pad = batch.get(f"{key}_is_pad")
-                for i in range(B):
-                    if pad is None or not bool(pad[i]):
-                        parts[i].append(f"{label}: {batch[key][i].item() if isinstance(batch[key], Tensor) else batch[key][i]}")
-        for key, label in (("robot_type", "Robot"), ("control_mode", "Control")):
-            if key in batch:
-                for i in range(B):
-                    if batch[key][i]:
-                        parts[i].append(f"{label}: {batch[key][i]}")
-        if not any(parts):
+
+        def numeric(key: str, i: int):
+            if key not in batch:
+                return None
+            pad = batch.get(f"{key}_is_pad")
+            if pad is not None and bool(pad[i]):
+                return None
+            v = batch[key][i]
+            return v.item() if isinstance(v, Tensor) else v
+
+        def text(key: str, i: int):
+            v = batch.get(key)
+            if v is None:
+                return None
+            v = v if isinstance(v, str) else v[i]
+            return v or None
+
+        rows: list[str] = []
+        for i in range(B):
+            segs = []
+            for label, value in (("Speed", numeric("speed", i)), ("Quality", numeric("quality", i)),
+                                 ("Mistake", numeric("mistake", i)), ("Robot", text("robot_type", i)),
+                                 ("FPS", numeric("fps", i)), ("Control", text("control_mode", i))):
+                if value is not None:
+                    segs.append(f"{label}: {value}, ")
+            rows.append(f"Metadata: {' '.join(segs)}" if segs else "")
+        if not any(rows):
             return None, None
-        enc = self.language_tokenizer([", ".join(p) for p in parts], padding="max_length", padding_side="right",
+        enc = self.language_tokenizer(rows, padding="max_length", padding_side="right",
                                       max_length=self.config.metadata_max_length, return_tensors="pt",
                                       truncation=True, add_special_tokens=False)
-        mask = enc["attention_mask"].bool() & torch.tensor([bool(p) for p in parts])[:, None]
+        mask = enc["attention_mask"].bool() & torch.tensor([bool(r) for r in rows])[:, None]
         return enc["input_ids"].to(device), mask.to(device)
 
     def _prefix_kwargs(self, batch, nb) -> dict[str, Any]:

@@ -29,6 +29,7 @@ class HashTokenizer:
     """Deterministic offline tokenizer: ids 0=pad, 1=eos, 2=bos, pieces hashed into [3, vocab)."""
 
     pad_token_id, eos_token_id, bos_token_id = 0, 1, 2
+    pad_token, eos_token, bos_token = "<pad>", "<eos>", "<bos>"
 
     PALIGEMMA_VOCAB, PALIGEMMA_LOC_BASE = 257152, 256000     # <loc0000>.. live at 256000..257023 in that vocabulary
 
@@ -36,8 +37,12 @@ class HashTokenizer:
         self.vocab_size = vocab_size
         # pieces hash below the range a PaliGemma-sized vocabulary reserves for location / segmentation tokens
         self._hash_range = (self.PALIGEMMA_LOC_BASE if vocab_size == self.PALIGEMMA_VOCAB else vocab_size) - 3
-        self.added_tokens: dict[str, int] = {}
+        # the literal special strings map to their ids, as in the Gemma / PaliGemma tokenizers: prompts spell
+        # separators out ("Task: ...<eos>State: ...")
+        self.added_tokens: dict[str, int] = {self.pad_token: self.pad_token_id, self.eos_token: self.eos_token_id,
+                                             self.bos_token: self.bos_token_id}
         self._added_re: re.Pattern | None = None
+        self._compile_added()
 
     def __len__(self) -> int:
         return self.vocab_size
@@ -58,9 +63,17 @@ class HashTokenizer:
                 self.added_tokens[t] = self.vocab_size
                 self.vocab_size += 1
                 grown += 1
+        self._compile_added()
+        return grown
+
+    def _compile_added(self) -> None:
         self._added_re = re.compile("(" + "|".join(re.escape(t) for t in sorted(self.added_tokens, key=len,
                                                                                 reverse=True)) + ")")
-        return grown
+
+    def convert_tokens_to_ids(self, tokens):
+        one = isinstance(tokens, str)
+        ids = [self.added_tokens[t] if t in self.added_tokens else self._piece_id(t) for t in ([tokens] if one else tokens)]
+        return ids[0] if one else ids
 
     @lru_cache(maxsize=65536)
     def _piece_id(self, piece: str) -> int:

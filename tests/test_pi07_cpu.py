@@ -218,3 +218,98 @@ def test_keep_history_tokens_puts_every_frame_in_the_decoder():
     with torch.no_grad():
         a = long.sample_actions({k: v for k, v in b.items() if k != "actions"})
     assert a.shape[-2:] == (10, 32) and torch.isfinite(a).all()
+
+
+def test_metadata_segment_text_is_reproduced_token_for_token():
+    """The prefix's metadata segment is a fixed spelling: fields in one order, ``"<Label>: <value>, "`` joined by a space,
+    behind ``"Metadata: "``; padded or absent fields are left out, a sample with none gets a masked empty segment."""
+    pol = _ll()
+    pol.config.metadata_max_length = 48
+    seen = []
+    real = pol.language_tokenizer
+
+    class Spy:
+        def __call__(self, texts, **kw):
+            seen.append(list(texts))
+            return real(texts, **kw)
+
+        def __getattr__(self, name):
+            return getattr(real, name)
+    pol.language_tokenizer = Spy()
+    state = torch.zeros(3, 32)
+    batch = {"state": state, "speed": torch.tensor([30, 50, 70]), "speed_is_pad": torch.tensor([False, True, True]),
+             "quality": torch.tensor([4, 4, 4]), "quality_is_pad": torch.tensor([False, False, True]),
+             "mistake": torch.tensor([False, True, False]), "mistake_is_pad": torch.tensor([False, True, True]),
+             "robot_type": ["so101", "", ""], "control_mode": ["ee", "joint", ""],
+             "fps": torch.tensor([20, 20, 20]), "fps_is_pad": torch.tensor([False, False, True])}
+    tokens, masks = pol.prepare_metadata(batch)
+    assert seen[-1] == ["Metadata: Speed: 30,  Quality: 4,  Mistake: False,  Robot: so101,  FPS: 20,  Control: ee, ",
+                        "Metadata: Quality: 4,  FPS: 20,  Control: joint, ", ""]
+    assert tokens.shape == (3, 48) and masks[0].any() and masks[1].any() and not masks[2].any()
+    assert pol.prepare_metadata({"state": state}) == (None, None)
+    # what the evaluator injects from env.metadata goes through unchanged
+    from opentau_b200.envs.configs import FakeEnvConfig, EnvMetadataConfig
+    from opentau_b200.envs.utils import add_eval_metadata
+    obs = add_eval_metadata({"state": state}, FakeEnvConfig(fps=15, metadata=EnvMetadataConfig(
+        quality=5, mistake=False, control_mode="joint", emit_fps=True)))
+    pol.prepare_metadata(obs)
+    assert seen[-1] == ["Metadata: Quality: 5,  Mistake: False,  FPS: 15,  Control: joint, "] * 3
+
+
+class _SpyTok:
+    """Records the strings a policy hands to its tokenizer."""
+
+    def __init__(self, real):
+        self.real, self.seen = real, []
+
+    def __call__(self, texts, **kw):
+        self.seen.append(list(texts))
+        return self.real(texts, **kw)
+
+    def __getattr__(self, name):
+        return getattr(self.real, name)
+
+
+def test_prompt_spellings_follow_the_reference_checkpoints():
+    """A checkpoint only understands the text layout it was trained on: every family's prompt / response strings are
+    pinned here (separators spelled ``<eos>`` map to the separator id)."""
+    import test_pi05_mem_cpu as mem
+    import test_policies_cpu as fam
+    from helpers import tiny_pi05
+    b = {"state": torch.zeros(2, 32), "prompt": ["pick", "place"], "response": ["reach", ""]}
+    pol = tiny_pi05(state_type="continuous")
+    pol.language_tokenizer = spy = _SpyTok(pol.language_tokenizer)
+    pol.prepare_language(b)
+    assert spy.seen[-1] == ["Task: pick, ", "Task: place, "]
+    pol = tiny_pi05()
+    pol.language_tokenizer = spy = _SpyTok(pol.language_tokenizer)
+    pol.prepare_language(b)
+    assert spy.seen[-1][0].startswith("Task: pick, State: 128 128") and spy.seen[-1][0].endswith(";\n")
+    pol = make_policy(mem._cfg(), per_dataset_stats=[identity_stats()])
+    pol.language_tokenizer = spy = _SpyTok(pol.language_tokenizer)
+    pol.prepare_language(b)
+    assert spy.seen[-1] == ["Task: pick<eos>Actions:", "Task: place<eos>Actions:"]
+    assert pol.language_tokenizer.real.encode("a<eos>b", add_special_tokens=False)[1] == pol.language_tokenizer.real.eos_token_id
+    pol = make_policy(fam._pi06(), per_dataset_stats=[identity_stats()])
+    pol.language_tokenizer = spy = _SpyTok(pol.language_tokenizer)
+    pol.prepare_language(b)
+    assert spy.seen[-1][1].startswith("Task: place<eos>State: 128") and spy.seen[-1][1].endswith("<eos>Actions:")
+    pol.config.predict_response = True
+    pol.prepare_language(b)
+    assert spy.seen[-1][0].endswith("<eos>Response:")
+    pol.prepare_response(b)
+    assert spy.seen[-1] == ["reach<eos>Actions:", "<eos>Actions:"]
+    ll = _ll()
+    ll.language_tokenizer = spy = _SpyTok(ll.language_tokenizer)
+    ll.prepare_language(b)
+    assert spy.seen[-1] == ["Task: pick, ", "Task: place, "]
+    _, masks = ll.prepare_response(b)
+    assert spy.seen[-1] == ["Subtask: reach, ", ""] and masks[0].any() and not masks[1].any()
+    hl = make_policy(make_policy_config(
+        "pi07_high_level", prompt_max_length=48, memory_max_length=8, response_max_length=8, dropout=0.0, device="cpu",
+        resize_imgs_with_padding=(224, 224), input_features=dict(FEATS), output_features=dict(OUT), **G3),
+        per_dataset_stats=[identity_stats()])
+    hl.language_tokenizer = spy = _SpyTok(hl.language_tokenizer)
+    hl._lang({**b, "past_memory": ["opened the drawer", ""]}, torch.device("cpu"))
+    assert spy.seen[-1][0].startswith("Task: pick, Past Memory: opened the drawer, State: 12")
+    assert spy.seen[-1][0].endswith(", ")
