@@ -99,25 +99,72 @@ class TrainPipelineConfig:
     def _propagate_shape_fields(self) -> None:
         if self.policy is None:
             return
+        import dataclasses
+        import logging
+        declared = {f.name for f in dataclasses.fields(type(self.policy))} if dataclasses.is_dataclass(self.policy) else set()
         for src, dst in PIPELINE_TO_POLICY_SHAPE_FIELDS.items():
-            if hasattr(self.policy, dst):
-                setattr(self.policy, dst, getattr(self, src))
+            if not hasattr(self.policy, dst):
+                continue
+            new, old = getattr(self, src), getattr(self.policy, dst, None)
+            if dst in declared and old != new and old != type(self.policy).__dataclass_fields__[dst].default:
+                # the data loader shapes every sample from the pipeline-level value, so it wins; say so when it
+                # replaces a value that somebody set (a checkpoint's, say) rather than the class default
+                logging.warning("overriding policy.%s=%s with %s=%s from the training config; to keep the policy's "
+                                "value set %s=%s at the top level instead", dst, old, src, new, src, old)
+            setattr(self.policy, dst, new)
         if hasattr(self.policy, "n_action_steps") and hasattr(self.policy, "chunk_size"):
             if self.policy.n_action_steps > self.policy.chunk_size:
                 self.policy.n_action_steps = self.policy.chunk_size
+
+    def _validate_loss_weighting(self) -> None:
+        """Both terms must be named (a weight of exactly 0 drops that term from the backward pass, which is a supported
+        way to train one head only), none may be negative, and at least one must be active
+        (reference ``src/opentau/configs/train.py:435-465``)."""
+        unknown = set(self.loss_weighting) - {"MSE", "CE"}
+        if unknown:
+            raise ValueError(f"unknown loss term(s) {sorted(unknown)} in loss_weighting (expected MSE / CE)")
+        missing = {"MSE", "CE"} - set(self.loss_weighting)
+        if missing:
+            raise ValueError(f"loss_weighting must define weights for ['CE', 'MSE']; missing {sorted(missing)}. "
+                             f"Got {self.loss_weighting}.")
+        negative = {k: v for k, v in self.loss_weighting.items() if v < 0}
+        if negative:
+            raise ValueError(f"loss_weighting values must be >= 0; got negative entries {negative}.")
+        if all(float(v) == 0.0 for v in self.loss_weighting.values()):
+            raise ValueError("loss_weighting has all-zero weights; there is nothing to optimize")
+
+    def _validate_data_matches_policy(self) -> None:
+        """The loader delivers frames at ``resolution`` and ``n_obs_history`` steps of history: a policy that resizes to
+        another size would letterbox every frame a second time, and one that expects another number of observation
+        steps would meet the wrong time axis.  Training only (evaluation never calls ``validate``), so checkpoints
+        trained with a mismatch stay evaluable; ``policy.skip_input_resolution_check`` downgrades the first to a warning
+        (reference ``src/opentau/configs/train.py:395-433``)."""
+        import logging
+        resize = getattr(self.policy, "resize_imgs_with_padding", None)
+        if resize is not None and tuple(resize) != tuple(self.resolution):
+            msg = (f"policy.resize_imgs_with_padding={tuple(resize)} != resolution={tuple(self.resolution)} (both (H, W)): "
+                   "the policy would resample and pad every frame a second time before the vision tower.  Set both to "
+                   "the same value (Gemma-3 policies: the tower's image size), or policy.resize_imgs_with_padding=null "
+                   "to pass frames through (PaliGemma-family policies only).")
+            if getattr(self.policy, "skip_input_resolution_check", False):
+                logging.warning("%s Proceeding because skip_input_resolution_check=true.", msg)
+            else:
+                raise ValueError(msg + " To resume a run trained with this mismatch set "
+                                       "policy.skip_input_resolution_check=true.")
+        if self.dataset_mixture is not None and self.dataset_mixture.datasets and hasattr(self.policy, "n_obs_steps"):
+            want = self.dataset_mixture.n_obs_history if self.dataset_mixture.n_obs_history else 1
+            if int(self.policy.n_obs_steps) != int(want):
+                raise ValueError(f"policy.n_obs_steps ({self.policy.n_obs_steps}) != dataset_mixture.n_obs_history "
+                                 f"({self.dataset_mixture.n_obs_history}; treated as 1 when unset): set "
+                                 "dataset_mixture.n_obs_history to match")
 
     def validate(self) -> None:
         if self.policy is None:
             raise ValueError("a policy configuration is required (`policy.type=...` or `--policy.path=...`)")
         if not self.dataset_mixture.datasets and self.env is None:
             raise ValueError("at least one dataset (or an env for pure evaluation) is required")
-        for k, w in self.loss_weighting.items():
-            if k not in ("MSE", "CE"):
-                raise ValueError(f"unknown loss term {k!r} in loss_weighting (expected MSE / CE)")
-            if w < 0:
-                raise ValueError("loss weights must be non-negative")
-        if all(float(self.loss_weighting.get(k, 1.0)) == 0.0 for k in ("MSE", "CE")):
-            raise ValueError("every loss term has zero weight")
+        self._validate_loss_weighting()
+        self._validate_data_matches_policy()
         self._validate_running_best()
         if self.use_policy_training_preset or self.optimizer is None:
             self.optimizer = self.optimizer if (self.optimizer and not self.use_policy_training_preset) \

@@ -365,3 +365,37 @@ def test_policy_path_without_a_config_file_and_features_from_the_checkpoint(tmp_
     assert not bare.policy.output_features
     pol = make_policy(bare.policy)
     assert "actions" in pol.unnormalize_outputs.features and "state" in pol.normalize_inputs.features
+
+
+def test_training_config_checks_data_against_policy(caplog):
+    import logging
+
+    import pytest
+
+    from helpers import TINY
+    from opentau_b200.configs.train import TrainPipelineConfig
+
+    def build(**kw):
+        pol = {"type": "pi05", "chunk_size": 10, "n_action_steps": 10, "prompt_max_length": 16, "device": "cpu",
+               "discrete_action_max_length": 8, "discrete_action_vocab_size": 256, **TINY, **kw.pop("policy", {})}
+        raw = {"dataset_mixture": {"datasets": [{"synthetic": {"length": 8}}], "action_freq": 10.0, **kw.pop("mix", {})},
+               "policy": pol, "resolution": [224, 224], "num_cams": 1, "action_chunk": 10, "batch_size": 2,
+               "output_dir": "/tmp/never-created-by-this-test", **kw}
+        return TrainPipelineConfig.from_dict(raw)
+    build().validate()
+    with pytest.raises(ValueError, match="a second time"):
+        build(policy={"resize_imgs_with_padding": [448, 448]}).validate()
+    with caplog.at_level(logging.WARNING):
+        build(policy={"resize_imgs_with_padding": [448, 448], "skip_input_resolution_check": True}).validate()
+    assert "Proceeding because skip_input_resolution_check=true" in caplog.text
+    with pytest.raises(ValueError, match="missing \\['CE'\\]"):
+        build(loss_weighting={"MSE": 1.0}).validate()
+    with pytest.raises(ValueError, match="negative entries"):
+        build(loss_weighting={"MSE": 1.0, "CE": -0.1}).validate()
+    with pytest.raises(ValueError, match="all-zero"):
+        build(loss_weighting={"MSE": 0.0, "CE": 0.0}).validate()
+    build(loss_weighting={"MSE": 1.0, "CE": 0.0}).validate()                   # one term dropped on purpose
+    caplog.clear()
+    with caplog.at_level(logging.WARNING):
+        cfg = build(policy={"chunk_size": 20, "n_action_steps": 10})
+    assert cfg.policy.chunk_size == 10 and "overriding policy.chunk_size=20 with action_chunk=10" in caplog.text
