@@ -109,3 +109,23 @@ def test_diagnose_host_script_writes_a_report(tmp_path):
     assert len(reports) == 1
     text = reports[0].read_text()
     assert "## GPUs" in text and "## python stack" in text and "torch" in text
+
+
+def test_action_generation_script_sweeps_step_counts(tmp_path):
+    import json
+
+    import numpy as np
+    from PIL import Image
+
+    from opentau_b200.scripts import run_action_generation as rag
+    Image.fromarray(np.random.default_rng(0).integers(0, 255, (96, 160, 3)).astype(np.uint8)).save(tmp_path / "frame.png")
+    out = rag.main(["--image", str(tmp_path / "frame.png"), "--prompt", "pick up the cup", "--domain", "droid",
+                    "--chunk-size", "10", "--steps", "3,1", "--warmup", "1", "--tiny", "--device", "cpu",
+                    "--output", str(tmp_path / "o" / "action.json")])
+    saved = json.loads((tmp_path / "o" / "action.json").read_text())
+    assert saved["shape"] == [10, 10] and [r["steps"] for r in saved["sweep"]] == [3, 1]
+    assert all(r["finite"] and r["latency_s"] > 0 for r in saved["sweep"]) and saved["weights"] == "random initialisation"
+    assert np.asarray(out["data"]).shape == (10, 10)
+    import pytest
+    with pytest.raises(SystemExit, match="unknown --domain"):
+        rag.main(["--image", str(tmp_path / "frame.png"), "--domain", "submarine", "--tiny"])
