@@ -557,7 +557,8 @@ class LeRobotDataset(BaseDataset, HubTransferMixin):
         self.meta = meta or LeRobotDatasetMetadata(repo_id, root, revision)
         self.root = self.meta.root
         dcfg = dataset_cfg
-        name_map = get_mapping(repo_id, self.meta.features, getattr(dcfg, "data_features_name_mapping", None))
+        name_map = get_mapping(repo_id, self.meta.features, getattr(dcfg, "data_features_name_mapping", None),
+                               control_mode=(getattr(dcfg, "control_mode", None) or self.meta.control_mode))
         super().__init__(cfg, name_map=name_map, train=train)
         if excluded_episodes is None and dcfg is not None:
             excluded_episodes = getattr(dcfg, "excluded_episodes", None)

@@ -256,3 +256,29 @@ def test_image_writer_threads_and_processes(tmp_path):
     with pytest.raises(KeyboardInterrupt):
         record(s)
     assert s.image_writer._stopped
+
+
+def test_feature_name_registry_is_control_mode_aware():
+    import pytest
+
+    from opentau_b200.datasets import standard_data_format_mapping as m
+    assert m.feature_mapping_key("org/arm", "ee") == "org/arm::ee"
+    for cm in (None, "", "  ", "Unknown"):
+        assert m.feature_mapping_key("org/arm", cm) == "org/arm"
+    try:
+        m.register_mapping("org/arm", {"actions": "action_joint", "state": "s"}, "joint")
+        m.register_mapping("org/arm", {"actions": "action_ee", "state": "s"}, "ee")
+        m.register_mapping("org/arm", {"actions": "action", "state": "s"})
+        assert m.resolve_feature_mapping("org/arm", "joint")["actions"] == "action_joint"
+        assert m.resolve_feature_mapping("org/arm", "ee")["actions"] == "action_ee"
+        assert m.resolve_feature_mapping("org/arm", "torque")["actions"] == "action"       # falls back to the plain entry
+        feats = {"observation.state": {"dtype": "float32"}, "action": {"dtype": "float32"}}
+        assert m.get_mapping("org/arm", feats, control_mode="ee")["actions"] == "action_ee"
+        assert m.get_mapping("org/arm", feats, {"actions": "mine"})["actions"] == "mine"     # the entry's own map wins
+        assert m.get_mapping("nobody/unlisted", feats)["actions"] == "action"                 # inferred
+        with pytest.raises(KeyError, match="No feature mapping"):
+            m.resolve_feature_mapping("nobody/unlisted", "ee")
+    finally:
+        for k in ("org/arm", "org/arm::ee", "org/arm::joint"):
+            m.DATA_FEATURES_NAME_MAPPING.pop(k, None)
+    assert m.DATA_FEATURES_NAME_MAPPING["lerobot/droid_100"]["camera0"].startswith("observation.images.")
