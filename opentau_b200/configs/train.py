@@ -246,7 +246,8 @@ class TrainPipelineConfig:
         if not repo_dir.is_dir():
             raise FileNotFoundError(f"{config_path!r} is not a file, not a directory and not in the local cache "
                                     f"({repo_dir}); this installation does not download")
-        root = repo_dir / rev if rev else repo_dir
+        from ..utils.hub import cached_revision_dir
+        root = cached_revision_dir(repo_dir, rev)
         if rev and not root.is_dir():
             tags = sorted(d.name for d in repo_dir.iterdir() if d.is_dir())
             raise FileNotFoundError(f"revision {rev!r} does not exist in cached repository {repo!r}; training steps "

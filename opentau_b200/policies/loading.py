@@ -108,7 +108,8 @@ def resolve_pretrained_weights_file(pretrained_name_or_path: str | Path) -> str:
     if not repo_dir.is_dir():
         raise FileNotFoundError(f"repository {repo!r} (from {name!r}) is neither a local path nor in the local cache "
                                 f"{HF_OPENTAU_HOME}; this installation does not download")
-    root = repo_dir / rev if rev else repo_dir
+    from ..utils.hub import cached_revision_dir
+    root = cached_revision_dir(repo_dir, rev)
     if rev and not root.is_dir():
         tags = sorted(d.name for d in repo_dir.iterdir() if d.is_dir())
         raise FileNotFoundError(f"revision {rev!r} does not exist in cached repository {repo!r}; training steps are "

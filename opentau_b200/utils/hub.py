@@ -9,21 +9,61 @@ runs without network access, so hub ids resolve only through the local cache dir
 from __future__ import annotations
 
 import os
+import re
 from pathlib import Path
 
 from ..constants import HF_OPENTAU_HOME
 
 
-def split_repo_revision(name: str) -> tuple[str, str | None]:
-    """``"org/repo@rev"`` -> ``("org/repo", "rev")``; paths that exist on disk are never split."""
-    if os.path.exists(name) or "@" not in name:
-        return name, None
-    repo, rev = name.rsplit("@", 1)
-    if not repo or not rev:
-        raise ValueError(f"malformed repo tag {name!r}: expected 'repo_id@revision'")
-    if rev.isdigit():
-        rev = f"step-{int(rev):06d}"
-    return repo, rev
+_HUB_REPO_ID = re.compile(r"^[A-Za-z0-9_][A-Za-z0-9._\-]*(?:/[A-Za-z0-9._\-]+)?$")
+
+
+def split_repo_revision(name, revision: str | None = None) -> tuple[str | None, str | None]:
+    """``"org/repo@rev"`` -> ``("org/repo", "rev")`` (reference ``src/opentau/utils/hub.py:45-107``).
+
+    Training runs are published as one repository per run with every saved step as a tag, so ``org/run@6000`` names
+    step 6000 and a bare ``org/run`` the latest one.  A file-system path is never split (checkpoint directories may
+    contain "@"): an existing path, or a string whose part before the "@" is not a well-formed repository id, comes
+    back unchanged, so that a moved checkpoint fails on its real path and not as a repository lookup.  Idempotent
+    (``split(*split(x)) == split(x)``): an outer loader may split and hand ``(repo, revision)`` to an inner one.
+    A spec that pins ``@rev`` together with a DIFFERENT explicit ``revision`` is an error."""
+    if name is None:
+        return None, revision
+    spec = str(name)
+    if not spec or os.path.exists(spec):
+        return spec, revision
+    head, sep, tail = spec.partition("@")
+    if not sep or not tail or not _HUB_REPO_ID.match(head) or os.path.exists(head):
+        if sep and not tail and _HUB_REPO_ID.match(head):
+            raise ValueError(f"malformed repo tag {spec!r}: expected 'repo_id@revision'")
+        return spec, revision
+    if revision is not None and revision != tail:
+        raise ValueError(f"conflicting revisions for {spec!r}: the path pins '@{tail}' but revision={revision!r} was "
+                         "also passed; give only one")
+    return head, tail
+
+
+def format_repo_revision(repo_id, revision: str | None) -> str:
+    """Inverse of :func:`split_repo_revision` for messages and logs."""
+    return f"{repo_id}@{revision}" if revision else str(repo_id)
+
+
+def revision_dir_names(revision: str) -> list[str]:
+    """Directory names under which a revision may sit in the local cache: the tag as given, and for a bare step
+    number also ``step-<six digits>`` (how this framework's own exporter lays steps out)."""
+    names = [revision]
+    if revision.isdigit():
+        names.append(f"step-{int(revision):06d}")
+    return names
+
+
+def cached_revision_dir(repo_dir: Path, revision: str | None) -> Path:
+    """``repo_dir`` itself without a revision; else the first existing candidate of :func:`revision_dir_names`, or
+    (none existing) the LAST candidate, so that error messages name the canonical directory."""
+    if not revision:
+        return repo_dir
+    cands = [repo_dir / n for n in revision_dir_names(revision)]
+    return next((c for c in cands if c.is_dir()), cands[-1])
 
 
 def resolve_local_or_hub(name: str, filename: str | None = None) -> Path:
@@ -34,9 +74,7 @@ def resolve_local_or_hub(name: str, filename: str | None = None) -> Path:
     if p.is_dir():
         return p / filename if filename else p
     repo, rev = split_repo_revision(name)
-    cached = HF_OPENTAU_HOME / repo
-    if rev:
-        cached = cached / rev
+    cached = cached_revision_dir(HF_OPENTAU_HOME / repo, rev)
     if cached.is_dir():
         return cached / filename if filename else cached
     raise FileNotFoundError(

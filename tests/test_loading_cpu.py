@@ -111,3 +111,32 @@ def test_linear_inputs_are_tiled_cyclically():
     pol.load_state_dict(state, strict=False)
     with pytest.raises(ValueError, match="output width"):
         loading.tile_linear_input_weights(pol, {"inp.weight": torch.zeros(5, 3)})
+
+
+def test_repo_revision_specs(tmp_path, monkeypatch):
+    import pytest
+
+    from opentau_b200.utils import hub
+    assert hub.split_repo_revision("org/run@6000") == ("org/run", "6000")            # the tag as given
+    assert hub.split_repo_revision(*hub.split_repo_revision("org/run@6000")) == ("org/run", "6000")   # idempotent
+    assert hub.split_repo_revision("org/run") == ("org/run", None)
+    assert hub.split_repo_revision("org/run", "main") == ("org/run", "main")
+    assert hub.split_repo_revision(None, "x") == (None, "x")
+    local = tmp_path / "ck@v2"
+    local.mkdir()
+    assert hub.split_repo_revision(str(local)) == (str(local), None)                 # existing paths are never split
+    moved = "/data/moved/ck@v2/sub"
+    assert hub.split_repo_revision(moved) == (moved, None)                           # path-shaped: fails as a path
+    with pytest.raises(ValueError, match="conflicting revisions"):
+        hub.split_repo_revision("org/run@6000", "7000")
+    assert hub.split_repo_revision("org/run@6000", "6000") == ("org/run", "6000")
+    with pytest.raises(ValueError, match="malformed"):
+        hub.split_repo_revision("org/run@")
+    assert hub.format_repo_revision("org/run", "6000") == "org/run@6000" and hub.format_repo_revision("org/run", None) == "org/run"
+    # a step may sit in the cache under its tag or under step-<six digits>
+    repo = tmp_path / "cache" / "org" / "run"
+    (repo / "6000").mkdir(parents=True)
+    (repo / "step-000700").mkdir()
+    assert hub.cached_revision_dir(repo, "6000").name == "6000"
+    assert hub.cached_revision_dir(repo, "700").name == "step-000700"
+    assert hub.cached_revision_dir(repo, "9").name == "step-000009" and hub.cached_revision_dir(repo, None) == repo
