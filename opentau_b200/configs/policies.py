@@ -13,6 +13,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, ClassVar
 
+from ..utils.hub import HubMixin
 from ..constants import CONFIG_NAME, TRAIN_CONFIG_NAME
 from .codec import ChoiceRegistry, decode, encode
 from .types import FeatureType, NormalizationMode, PolicyFeature
@@ -115,7 +116,7 @@ def warn_removed_policy_fields(config_path: str | Path) -> None:
 
 
 @dataclass
-class PreTrainedConfig(ChoiceRegistry, abc.ABC):
+class PreTrainedConfig(ChoiceRegistry, HubMixin, abc.ABC):
     n_obs_steps: int = 1
     normalization_mapping: dict[str, NormalizationMode] = field(default_factory=dict)
     input_features: dict[str, PolicyFeature] = field(default_factory=dict)
@@ -308,7 +309,6 @@ class PreTrainedConfig(ChoiceRegistry, abc.ABC):
         with open(Path(save_directory) / CONFIG_NAME, "w") as f:
             json.dump(d, f, indent=4)
 
-    save_pretrained = _save_pretrained
 
     @classmethod
     def from_dict(cls, d: dict[str, Any]) -> "PreTrainedConfig":

@@ -20,6 +20,7 @@ from torch import Tensor, nn
 
 from ..configs.policies import PreTrainedConfig
 from ..constants import CONFIG_NAME, SAFETENSORS_SINGLE_FILE
+from ..utils.hub import HubMixin
 
 _NORM_PREFIXES = ("normalize_inputs.", "normalize_targets.", "normalize_actions.",
                   "normalize_discrete_actions.", "unnormalize_outputs.")
@@ -38,7 +39,7 @@ def strip_normalization_buffers(state: dict[str, Tensor]) -> dict[str, Tensor]:
     return {k: v for k, v in state.items() if not is_norm_buffer_key(k)}
 
 
-class PreTrainedPolicy(nn.Module, abc.ABC):
+class PreTrainedPolicy(nn.Module, HubMixin, abc.ABC):
     config_class: type[PreTrainedConfig] | None = None
     name: str | None = None
     #: state-dict prefixes of learned per-group projections (``PerGroupLinear``) that are duplicated / re-ordered by
@@ -278,8 +279,6 @@ class PreTrainedPolicy(nn.Module, abc.ABC):
             out[k] = v.detach().contiguous().cpu()
         save_file(out, str(save_directory / SAFETENSORS_SINGLE_FILE), metadata={"format": "pt"})
 
-    def save_pretrained(self, save_directory: str | Path) -> None:
-        self._save_pretrained(save_directory)
 
     @classmethod
     def from_pretrained(cls, pretrained_name_or_path: str | Path, *, config: PreTrainedConfig | None = None,

@@ -80,3 +80,50 @@ def resolve_local_or_hub(name: str, filename: str | None = None) -> Path:
     raise FileNotFoundError(
         f"{name!r} is not a local path and is not in the local cache ({cached}); "
         "downloading from the hub needs network access, which this installation does not assume")
+
+
+class HubMixin:
+    """``save_pretrained(dir, push_to_hub=...)`` / ``push_to_hub(repo_id, ...)`` for anything that implements
+    ``_save_pretrained(dir)`` (policies, configs): lighter than ``huggingface_hub.ModelHubMixin`` and with fewer
+    assumptions about the subclass (reference ``src/opentau/utils/hub.py:119-296``).  Uploading needs network access and
+    the ``huggingface_hub`` package; the upload call is looked up at call time so tests can substitute it."""
+
+    def save_pretrained(self, save_directory: str | Path, *, repo_id: str | None = None, push_to_hub: bool = False,
+                        card_kwargs: dict | None = None, **push_to_hub_kwargs) -> str | None:
+        """Writes the object into ``save_directory``; with ``push_to_hub`` also uploads it (``repo_id`` defaults to the
+        directory's name) and returns the commit URL."""
+        save_directory = Path(save_directory)
+        save_directory.mkdir(parents=True, exist_ok=True)
+        self._save_pretrained(save_directory)
+        if push_to_hub:
+            return self.push_to_hub(repo_id=repo_id or save_directory.name, card_kwargs=card_kwargs, **push_to_hub_kwargs)
+        return None
+
+    def _save_pretrained(self, save_directory: Path) -> None:
+        raise NotImplementedError
+
+    def default_commit_message(self) -> str:
+        name = type(self).__name__
+        return "Upload policy" if "Policy" in name else "Upload config" if "Config" in name else f"Upload {name}"
+
+    def push_to_hub(self, repo_id: str, *, commit_message: str | None = None, private: bool | None = None,
+                    token: str | None = None, branch: str | None = None, create_pr: bool | None = None,
+                    allow_patterns=None, ignore_patterns=None, delete_patterns=None, card_kwargs: dict | None = None,
+                    api=None) -> str:
+        """Saves into a temporary directory and uploads that folder as ONE commit; returns the commit's URL.
+        ``allow_patterns`` / ``ignore_patterns`` filter the files, ``delete_patterns`` removes remote files in the same
+        commit, ``branch`` / ``create_pr`` choose where it lands.  ``api``: an ``HfApi``-like object (default: a new
+        ``huggingface_hub.HfApi(token=token)``)."""
+        from tempfile import TemporaryDirectory
+        if api is None:
+            from huggingface_hub import HfApi
+            api = HfApi(token=token)
+        created = api.create_repo(repo_id=repo_id, private=private, exist_ok=True)
+        repo_id = getattr(created, "repo_id", repo_id)
+        with TemporaryDirectory(ignore_cleanup_errors=True) as tmp:
+            saved = Path(tmp) / repo_id
+            self.save_pretrained(saved, card_kwargs=card_kwargs)
+            return api.upload_folder(repo_id=repo_id, repo_type="model", folder_path=saved,
+                                     commit_message=commit_message or self.default_commit_message(), revision=branch,
+                                     create_pr=create_pr, allow_patterns=allow_patterns, ignore_patterns=ignore_patterns,
+                                     delete_patterns=delete_patterns)

@@ -140,3 +140,34 @@ def test_repo_revision_specs(tmp_path, monkeypatch):
     assert hub.cached_revision_dir(repo, "6000").name == "6000"
     assert hub.cached_revision_dir(repo, "700").name == "step-000700"
     assert hub.cached_revision_dir(repo, "9").name == "step-000009" and hub.cached_revision_dir(repo, None) == repo
+
+
+def test_policies_and_configs_push_one_commit(tmp_path):
+    from helpers import tiny_pi05
+
+    class Api:
+        def __init__(self):
+            self.calls = []
+
+        def create_repo(self, repo_id, private=None, exist_ok=False):
+            self.calls.append(("create_repo", repo_id, private, exist_ok))
+            return type("R", (), {"repo_id": repo_id})()
+
+        def upload_folder(self, **kw):
+            kw["files"] = sorted(p.name for p in kw["folder_path"].iterdir())
+            self.calls.append(("upload_folder", kw))
+            return f"https://hub/{kw['repo_id']}/commit/abc"
+    pol, api = tiny_pi05(), Api()
+    url = pol.push_to_hub("org/tiny", private=True, branch="dev", ignore_patterns=["*.tmp"], api=api)
+    assert url.endswith("org/tiny/commit/abc") and api.calls[0] == ("create_repo", "org/tiny", True, True)
+    up = api.calls[1][1]
+    assert up["commit_message"] == "Upload policy" and up["revision"] == "dev" and up["repo_type"] == "model"
+    assert "model.safetensors" in up["files"] and "config.json" in up["files"] and up["ignore_patterns"] == ["*.tmp"]
+    api2 = Api()
+    pol.config.push_to_hub("org/tiny-config", api=api2)
+    assert api2.calls[1][1]["commit_message"] == "Upload config" and api2.calls[1][1]["files"] == ["config.json"]
+    # save_pretrained alone stays local; with push_to_hub the repository defaults to the folder's name
+    assert pol.save_pretrained(tmp_path / "my-run") is None and (tmp_path / "my-run" / "model.safetensors").is_file()
+    api3 = Api()
+    pol.save_pretrained(tmp_path / "my-run", push_to_hub=True, api=api3)
+    assert api3.calls[0][1] == "my-run"
