@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import contextlib
 import json
 import warnings
 from pathlib import Path
@@ -53,3 +54,45 @@ def warn_once(msg: str, _seen: set = set()) -> None:  # noqa: B006
     if msg not in _seen:
         _seen.add(msg)
         warnings.warn(msg, stacklevel=2)
+
+
+@contextlib.contextmanager
+def silence_output_unless_error(label: str = ""):
+    """Mutes this process's stdout and stderr for the block and replays what was written only if the block raises.
+
+    The redirection is on the FILE DESCRIPTORS 1 and 2 (``os.dup2``), not on ``sys.stdout`` / ``sys.stderr``: that also
+    catches what C extensions print and what logging handlers write that took a reference to the original stream at
+    import time.  Meant for the banner that every simulator worker prints on import and construction (environments x
+    ranks copies per evaluation).  On failure the captured bytes go to the real stderr first, prefixed with ``label``
+    (e.g. ``"task=CloseFridge idx=3"``), then the exception travels on unchanged
+    (reference ``src/opentau/utils/io_utils.py:41-110``)."""
+    import os
+    import sys
+    import tempfile
+    sys.stdout.flush()
+    sys.stderr.flush()
+    saved_out, saved_err = os.dup(1), os.dup(2)
+    failed = False
+    try:
+        with tempfile.TemporaryFile(mode="w+b") as buf:
+            try:
+                os.dup2(buf.fileno(), 1)
+                os.dup2(buf.fileno(), 2)
+                yield
+            except BaseException:
+                failed = True
+                raise
+            finally:
+                sys.stdout.flush()
+                sys.stderr.flush()
+                os.dup2(saved_out, 1)
+                os.dup2(saved_err, 2)
+                if failed:
+                    buf.seek(0)
+                    data = buf.read()
+                    if data:
+                        head = f"--- captured output ({label}) ---\n" if label else "--- captured output ---\n"
+                        os.write(2, head.encode() + data + (b"" if data.endswith(b"\n") else b"\n"))
+    finally:
+        os.close(saved_out)
+        os.close(saved_err)

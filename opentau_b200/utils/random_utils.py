@@ -68,6 +68,27 @@ def deserialize_torch_rng_state(d: dict[str, torch.Tensor]) -> None:
         torch.cuda.set_rng_state(d["torch_cuda_rng_state"].to(torch.uint8).cpu())
 
 
+def get_rng_state() -> dict:
+    """The live states of ``random``, ``numpy.random`` and ``torch`` (and the current CUDA device's generator) as
+    plain Python objects: for bracketing a block in memory (:func:`seeded_context`), not for files
+    (reference ``src/opentau/utils/random_utils.py:176-203``)."""
+    import random
+    state = {"random_state": random.getstate(), "numpy_random_state": np.random.get_state(),
+             "torch_random_state": torch.random.get_rng_state()}
+    if torch.cuda.is_available():
+        state["torch_cuda_random_state"] = torch.cuda.random.get_rng_state()
+    return state
+
+
+def set_rng_state(state: dict) -> None:
+    import random
+    random.setstate(state["random_state"])
+    np.random.set_state(state["numpy_random_state"])
+    torch.random.set_rng_state(state["torch_random_state"])
+    if torch.cuda.is_available() and "torch_cuda_random_state" in state:
+        torch.cuda.random.set_rng_state(state["torch_cuda_random_state"])
+
+
 def serialize_rng_state() -> dict[str, torch.Tensor]:
     return {**serialize_python_rng_state(), **serialize_numpy_rng_state(), **serialize_torch_rng_state()}
 
