@@ -17,6 +17,8 @@ from typing import Any, Iterable, Sequence
 
 import numpy as np
 
+from ..utils.io_utils import silence_output_unless_error
+
 OBS_STATE_DIM, ACTION_DIM = 8, 7
 TASK_SUITE_MAX_STEPS = {"libero_spatial": 280, "libero_object": 280, "libero_goal": 300, "libero_10": 520,
                         "libero_90": 400}
@@ -158,10 +160,12 @@ def real_backend():  # pragma: no cover - needs the simulator and a graphics con
 
         def make(self, name, task_id, height, width, control_freq):
             task = self._suite(name).get_task(task_id)
-            env = OffScreenRenderEnv(bddl_file_name=os.path.join(get_libero_path("bddl_files"), task.problem_folder,
-                                                                 task.bddl_file),
-                                     camera_heights=height, camera_widths=width, control_freq=control_freq)
-            env.reset()
+            # the simulator prints a banner per worker; it is shown only when construction fails
+            with silence_output_unless_error(label=f"libero suite={name} task={task_id}"):
+                env = OffScreenRenderEnv(bddl_file_name=os.path.join(get_libero_path("bddl_files"),
+                                                                     task.problem_folder, task.bddl_file),
+                                         camera_heights=height, camera_widths=width, control_freq=control_freq)
+                env.reset()
             return env
 
     return Backend()

@@ -15,6 +15,8 @@ from typing import Any, Sequence
 
 import numpy as np
 
+from ..utils.io_utils import silence_output_unless_error
+
 ACTION_DIM, STATE_DIM = 12, 16
 DEFAULT_HORIZON = 500
 OFFICIAL_HORIZONS = {"NavigateKitchen": 500, "CloseSingleDoor": 500, "OpenSingleDoor": 500, "CloseDrawer": 500,
@@ -101,9 +103,10 @@ def real_backend():  # pragma: no cover - needs the simulator, its assets and a 
 
     class Backend:
         def make(self, task, split, seed, cameras, height, width):
-            env = robosuite.make(env_name=task, robots="PandaOmron", has_renderer=False, has_offscreen_renderer=True,
-                                 use_camera_obs=True, camera_names=list(cameras), camera_heights=height,
-                                 camera_widths=width, seed=seed, obj_instance_split=split)
+            with silence_output_unless_error(label=f"robocasa task={task} split={split}"):
+                env = robosuite.make(env_name=task, robots="PandaOmron", has_renderer=False,
+                                     has_offscreen_renderer=True, use_camera_obs=True, camera_names=list(cameras),
+                                     camera_heights=height, camera_widths=width, seed=seed, obj_instance_split=split)
             env.language = env.get_ep_meta().get("lang", task)
             inner_step = env.step
 
