@@ -359,7 +359,7 @@ class Cosmos3Policy(PreTrainedPolicy):
             if getattr(cfg, "action_chunk_critic_path", None) not in (None, MEDOID):
                 raise ValueError(f"n_candidates={n} but no action-chunk critic is attached; arm best-of-N through "
                                  "candidates.configure_candidates")
-            critic = MedoidCritic(max_action_dim=cfg.max_action_dim)
+            critic = MedoidCritic(self.unnormalize_outputs, max_action_dim=cfg.max_action_dim)
         sampler_idx = expand_candidates(idx, n)
         meter = make_meter(self, batch_size=B * n, device=device, dataset_index=sampler_idx)
         if getattr(self, "_use_graphs", False) and device.type == "cuda" and meter is None and n == 1:

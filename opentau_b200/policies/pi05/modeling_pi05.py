@@ -841,7 +841,7 @@ class PI05Policy(PreTrainedPolicy):
         if n > 1 and critic is None:
             from ..candidates import MEDOID, MedoidCritic
             if getattr(cfg, "action_chunk_critic_path", None) in (None, MEDOID):
-                critic = MedoidCritic(max_action_dim=cfg.max_action_dim)   # the parameter-free selector
+                critic = MedoidCritic(self.unnormalize_outputs, max_action_dim=cfg.max_action_dim)
             else:
                 raise ValueError(f"n_candidates={n} but no action-chunk critic is attached; arm best-of-N through "
                                  "candidates.configure_candidates")

@@ -37,7 +37,10 @@ def main(cfg: TrainPipelineConfig):
     from ..policies.factory import make_policy
     from ..utils.logging_utils import init_logging
     from ..utils.utils import auto_torch_device
+    from ..policies.candidates import refuse_candidates
     init_logging()
+    refuse_candidates(cfg, reason="the open-loop error compares ONE sampled chunk per observation with the recorded "
+                      "one; a critic's selection would change what is measured. Run it with policy.n_candidates=1.")
     device = auto_torch_device()
     res = make_dataset_mixture(cfg)
     mix = res[0] if isinstance(res, tuple) else res

@@ -204,6 +204,10 @@ def main(argv=None):
     if args.prompt_len is None:
         args.prompt_len = 64 if args.policy == "cosmos3" else 200
     policy, batch = BUILDERS[args.policy](args.cams, args.prompt_len, device, args.tiny, args.num_steps, args.depth)
+    if n_cand > 1:
+        # the parameter-free consensus selector; it cannot rank two candidates, so BENCH_N_CANDIDATES=2 fails here
+        from ..policies.candidates import MEDOID, configure_candidates
+        configure_candidates(policy, n_cand, MEDOID, device=device)
     rec = {"policy": args.policy, "device": torch.cuda.get_device_name(0) if device.type == "cuda" else "cpu",
            "dtype": "bf16", "num_steps": args.num_steps, "n_candidates": n_cand, "cams": args.cams,
            "prompt_len": args.prompt_len}

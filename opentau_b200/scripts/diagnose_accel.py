@@ -458,9 +458,9 @@ def synthetic_observations(cfg: TrainPipelineConfig, device, count: int) -> list
 @parser.wrap()
 def diagnose_main(cfg: TrainPipelineConfig):
     init_logging()
-    if int(getattr(cfg.policy, "n_candidates", 1) or 1) > 1:
-        raise ValueError(f"n_candidates={cfg.policy.n_candidates} is not supported here: this diagnostic controls the "
-                         "noise draw and reads one score per observation. Run it with policy.n_candidates=1.")
+    from ..policies.candidates import refuse_candidates
+    refuse_candidates(cfg, reason="this diagnostic controls the noise draw and reads one score per observation. Run "
+                      "it with policy.n_candidates=1.")
     policy = make_policy(cfg.policy)
     policy.eval()
     device = torch.device(getattr(cfg.policy, "device", None) or "cpu")

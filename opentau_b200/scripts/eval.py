@@ -464,8 +464,6 @@ def eval_main(cfg: TrainPipelineConfig):
         raise ValueError("an `env` block is required for evaluation")
     if cfg.policy is None or not cfg.policy.pretrained_path:
         logging.warning("no pretrained policy path given: evaluating randomly initialised weights")
-    if getattr(cfg.policy, "n_candidates", 1) > 1 and not getattr(cfg.policy, "action_chunk_critic_path", None):
-        logging.info("best-of-N without a critic: the medoid candidate is used")
     if cfg.seed is not None:
         set_seed(cfg.seed, rank)
     if cfg.policy is not None:
@@ -478,9 +476,9 @@ def eval_main(cfg: TrainPipelineConfig):
     from ..policies.candidates import configure_candidates
     if configure_accel(policy, cfg) is not None:               # cfg.policy.accel_prefix or $OPENTAU_ACCEL_PREFIX
         logging.info("accel streams are recorded per episode (prefix %d)", policy.accel_prefix)
-    if getattr(cfg.policy, "n_candidates", 1) > 1 and hasattr(policy, "_n_candidates"):
-        configure_candidates(policy, cfg.policy.n_candidates, getattr(cfg.policy, "action_chunk_critic_path", None)
-                             or "medoid")
+    # best-of-N widens the expert batch by n_candidates per environment; a config that asks for it without naming a
+    # critic is refused there rather than silently evaluated on a single sample
+    configure_candidates(policy, cfg, device=device)
     out = Path(cfg.output_dir or "outputs/eval")
     info = eval_policy_on_config(policy, cfg, device, rank, world, videos_dir=out / "videos")
     if rank == 0:

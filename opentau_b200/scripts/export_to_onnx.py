@@ -95,6 +95,9 @@ def main() -> None:
     ap.add_argument("--format", default="onnx", choices=["onnx", "torchscript"])
     a, rest = ap.parse_known_args()
     cfg: TrainPipelineConfig = parser.parse_config(TrainPipelineConfig, rest)
+    from ..policies.candidates import refuse_candidates
+    refuse_candidates(cfg, reason="the exported graph is one sampler call at a static batch; candidates are expanded "
+                      "and scored in the policy wrapper, outside of what is traced. Export with policy.n_candidates=1.")
     policy = make_policy(cfg.policy)
     out = export(policy, a.output, cfg.num_cams, a.format)
     logging.info("exported %s (%.1f MB)", out, out.stat().st_size / 1e6)

@@ -90,8 +90,8 @@ class RobotPolicyServicer(pb_grpc.RobotPolicyServiceServicer):
         from ...policies.accel import configure_accel
         from ...policies.candidates import configure_candidates
         self.accel_prefix = configure_accel(self.policy, cfg)
-        if getattr(cfg.policy, "n_candidates", 1) > 1 and hasattr(self.policy, "_n_candidates"):
-            configure_candidates(self.policy, cfg.policy.n_candidates)
+        # likewise: the critic is loaded, placed and smoke-called here, and the warm-up runs at the widened batch
+        configure_candidates(self.policy, cfg)
         self.requests = 0
         self._lock = threading.Lock()
         for _ in range(cfg.server.warmup_requests if policy is None else 0):

@@ -116,6 +116,8 @@ class OpenTauRoboCasaPolicy:
         self.policy.eval()
         # precedence: this entry point's flag, then cfg.policy.accel_prefix, then $OPENTAU_ACCEL_PREFIX
         self.accel_prefix = configure_accel(self.policy, cfg, override=accel_prefix)
+        from ...policies.candidates import configure_candidates
+        self.n_candidates = configure_candidates(self.policy, cfg, device=self.device)
         self.last_accel: list[float] | None = None
 
     def infer_batch(self, items, action_dim: int) -> list[np.ndarray]:

@@ -168,3 +168,73 @@ def test_diagnostic_report_on_a_tiny_policy():
     assert "NOT MEASURED" in D.format_report(rep)
     with pytest.raises(ValueError, match="at least two"):
         D.diagnose_accel(pol, obs[:1])
+
+
+def test_candidate_configuration_rules():
+    """Precedence, refusals and the critic's own requirements (reference ``src/opentau/policies/candidates.py``)."""
+    from types import SimpleNamespace
+
+    from opentau_b200.policies import candidates as C
+    pol = tiny_pi05(num_steps=5)
+    cfg = SimpleNamespace(policy=SimpleNamespace(n_candidates=3, action_chunk_critic_path="medoid", type="pi05"))
+    assert C.configure_candidates(pol, cfg) == 3 and isinstance(pol._critic, C.MedoidCritic)
+    # the critic is bound, not registered: nothing of it reaches the policy's state dict or parameters
+    assert "_critic" not in dict(pol.named_children()) and not pol._critic.state_dict()
+    # an entry point's override of 1 disables a config-enabled N and clears the critic
+    assert C.configure_candidates(pol, cfg, override=1) == 1 and pol._critic is None and pol._n_candidates == 1
+    # N > 1 without a critic path, a learned-critic path, a critic without score_chunks, a bad count
+    cfg.policy.action_chunk_critic_path = None
+    with pytest.raises(ValueError, match="action_chunk_critic_path"):
+        C.configure_candidates(pol, cfg)
+    cfg.policy.action_chunk_critic_path = "critics/v1"
+    with pytest.raises(NotImplementedError, match="learned critic"):
+        C.configure_candidates(pol, cfg)
+    with pytest.raises(TypeError, match="score_chunks"):
+        C.configure_candidates(pol, cfg, critic=object())
+    with pytest.raises(ValueError, match=">= 1"):
+        C.configure_candidates(pol, cfg, override=0)
+    # the consensus selector cannot rank two candidates: the start-up probe says so
+    with pytest.raises(ValueError, match=">= 3"):
+        C.configure_candidates(pol, 2, "medoid")
+
+    class WrongShape:
+        def score_chunks(self, batch, candidates, *, row_mask, dataset_index):
+            return candidates.new_zeros(candidates.shape[0])
+    with pytest.raises(TypeError, match=r"\(B, N\)"):
+        C.configure_candidates(pol, 3, WrongShape())
+    # a family without a best-of-N sampler: silent at N == 1, refused above
+    bare = SimpleNamespace(config=SimpleNamespace(max_action_dim=8))
+    assert C.configure_candidates(bare, SimpleNamespace(n_candidates=1)) == 1 and not hasattr(bare, "_n_candidates")
+    with pytest.raises(ValueError, match="no best-of-N sampler"):
+        C.configure_candidates(bare, SimpleNamespace(n_candidates=4, type="value"))
+    # entry points that cannot honour the setting
+    C.refuse_candidates(SimpleNamespace(policy=SimpleNamespace(n_candidates=1)), reason="x")
+    with pytest.raises(ValueError, match="not supported here: static graph"):
+        C.refuse_candidates(SimpleNamespace(policy=SimpleNamespace(n_candidates=4)), reason="static graph")
+    t = torch.arange(12.).view(6, 2)
+    assert torch.equal(C.collapse_candidates(C.expand_candidates(t[:2], 3), 3)[1, 2], t[1])
+
+
+def test_medoid_scores_in_the_policy_normalised_space():
+    """A dim with a large raw scale must not dominate: the distance is taken after the policy's per-dim scale, over
+    dims with a spread and executed rows only."""
+    from opentau_b200.policies import candidates as C
+    pol = tiny_pi05(num_steps=5)
+    critic = C.load_critic("medoid", policy=pol)
+    real = pol.config.action_feature.shape[0]
+    scale = A.action_dim_scale(pol.unnormalize_outputs, max_action_dim=real, dataset_index=torch.zeros(1).long())[0]
+    keep = A.resolve_action_dim_mask(pol.unnormalize_outputs, max_action_dim=real,
+                                     dataset_index=torch.zeros(1).long())[0]
+    cand = torch.randn(1, 4, pol.config.chunk_size, real)
+    rows = torch.ones(1, pol.config.chunk_size, dtype=torch.bool)
+    rows[:, 3:] = False
+    got = critic.score_chunks({}, cand, row_mask=rows, dataset_index=torch.zeros(1).long())
+    x = (cand[0, :, :3] / scale)[..., keep].flatten(1)
+    want = -(torch.cdist(x, x).sum(-1) / 3)
+    torch.testing.assert_close(got[0], want)
+    # rows that are not executed do not matter
+    cand2 = cand.clone()
+    cand2[:, :, 3:] += 100.0
+    torch.testing.assert_close(critic.score_chunks({}, cand2, row_mask=rows, dataset_index=torch.zeros(1).long()), got)
+    with pytest.raises(ValueError, match="row_mask"):
+        critic.score_chunks({}, cand, row_mask=rows[0], dataset_index=torch.zeros(1).long())
