@@ -49,6 +49,10 @@ class HubClient(Protocol):
 
     def retag(self, repo_id: str, tag: str, *, revision: str | None) -> Any: ...
 
+    def list_refs(self, repo_id: str) -> tuple[list[str], list[str]]:
+        """``(branch names, tag names)`` of the repository."""
+        ...
+
 
 class HuggingFaceHubClient:
     """The real thing (dataset repositories)."""
@@ -89,6 +93,10 @@ class HuggingFaceHubClient:
             self._api.delete_tag(repo_id, tag=tag, repo_type="dataset")
         return self._api.create_tag(repo_id, tag=tag, revision=revision, repo_type="dataset")
 
+    def list_refs(self, repo_id):
+        refs = self._api.list_repo_refs(repo_id, repo_type="dataset")
+        return [b.name for b in refs.branches], [t.name for t in refs.tags]
+
 
 _CLIENT: list[HubClient] = []
 
@@ -104,6 +112,83 @@ def set_hub_client(client: HubClient | None) -> None:
     _CLIENT.clear()
     if client is not None:
         _CLIENT.append(client)
+
+
+class ForwardCompatibilityError(Exception):
+    """The repository only carries formats newer than this loader reads."""
+
+
+class RevisionNotFoundError(Exception):
+    """The repository carries no codebase-version ref (and no default branch to fall back to)."""
+
+
+DEFAULT_BRANCHES = ("main", "master")
+
+
+def _parse_version(ref) -> tuple[int, ...] | None:
+    """``"v2.1"`` / ``"2.1"`` -> ``(2, 1)``; anything that is not a dotted number (a branch name) -> ``None``."""
+    parts = str(ref).lstrip("v").split(".")
+    if not parts or not all(p.isdigit() for p in parts):
+        return None
+    return tuple(int(p) for p in parts)
+
+
+def _fmt_version(v: tuple[int, ...]) -> str:
+    return "v" + ".".join(str(x) for x in v)
+
+
+def get_repo_versions(repo_id: str) -> list[tuple[int, ...]]:
+    """Branches and tags of the repository that parse as versions."""
+    branches, tags = hub_client().list_refs(repo_id)
+    return [v for v in (_parse_version(r) for r in [*branches, *tags]) if v is not None]
+
+
+def get_safe_version(repo_id: str, version: str, read_ceiling: str | None = None,
+                     allow_branch_fallback: bool = False) -> str:
+    """The revision to download when ``version`` was asked for (reference ``src/opentau/datasets/utils.py:1004-1110``):
+
+    1. the version itself when the repository carries it;
+    2. else the newest ref of the same major with a minor not above it (with a warning when it is older);
+    3. else the newest ref above it that the loader still reads (up to ``read_ceiling``, default: the newest
+       supported format), e.g. a repository published only as v3.0 while v2.1 is the default target;
+    4. else :class:`BackwardCompatibilityError` (only older majors) or :class:`ForwardCompatibilityError`.
+
+    A repository without any version ref raises :class:`RevisionNotFoundError`, unless ``allow_branch_fallback`` (the
+    caller pinned no revision) and a ``main`` / ``master`` branch exists, which is then used with a warning."""
+    from .utils import SUPPORTED_VERSIONS, BackwardCompatibilityError
+    target = _parse_version(version)
+    if target is None:
+        raise ValueError(f"{version!r} is not a codebase version")
+    ceiling = _parse_version(read_ceiling) if read_ceiling else max(_parse_version(v) for v in SUPPORTED_VERSIONS)
+    branches, tags = hub_client().list_refs(repo_id)
+    versions = [v for v in (_parse_version(r) for r in [*branches, *tags]) if v is not None]
+    if not versions:
+        if allow_branch_fallback:
+            for name in DEFAULT_BRANCHES:
+                if name in branches:
+                    logging.warning("%s has no codebase-version tag; defaulting to the %r branch", repo_id, name)
+                    return name
+        raise RevisionNotFoundError(
+            f"{repo_id} must be tagged with its codebase version (the `codebase_version` of meta/info.json): "
+            f"create that tag on the dataset repository, or pass an explicit `revision`")
+    if target in versions:
+        return _fmt_version(target)
+    same_major = [v for v in versions if v[0] == target[0] and v[1:] <= target[1:]]
+    if same_major:
+        best = max(same_major)
+        logging.warning("revision %s of %s not found, using %s", version, repo_id, _fmt_version(best))
+        return _fmt_version(best)
+    readable_newer = [v for v in versions if target < v <= ceiling]
+    if readable_newer:
+        return _fmt_version(max(readable_newer))
+    older = [v for v in versions if v[0] < target[0]]
+    if older:
+        raise BackwardCompatibilityError(
+            f"dataset {repo_id!r} is only published as {_fmt_version(max(older))}, which this loader does not read; "
+            f"convert it first (datasets/v2/convert_dataset_v1_to_v2.py)")
+    raise ForwardCompatibilityError(
+        f"dataset {repo_id!r} is only available as {_fmt_version(min(v for v in versions if v > target))}; this "
+        f"loader reads up to {_fmt_version(ceiling)}: update the framework")
 
 
 def dataset_card(info: dict, tags: list[str] | None = None, license: str | None = "apache-2.0", **extra) -> str:
@@ -136,9 +221,26 @@ def _on_main_process_then_barrier(fn):
 class HubTransferMixin:
     """Needs ``repo_id``, ``root``, ``revision`` and, for the episode-wise calls, ``meta`` / ``episodes``."""
 
+    def resolved_revision(self) -> str | None:
+        """What is asked of the hub.  A pinned revision is used as it is, if it parses as a version after the same
+        compatibility resolution; an unpinned one resolves from the current format, with the default branch as the
+        last resort.  A client that cannot list refs (a plain mirror) leaves the revision as it is."""
+        from .utils import CODEBASE_VERSION
+        pinned = getattr(self, "revision", None)
+        if pinned is not None and _parse_version(pinned) is None:
+            return pinned                                   # a branch name or a commit hash
+        cached = getattr(self, "_resolved_revision", None)
+        if cached is not None:
+            return cached
+        if not hasattr(hub_client(), "list_refs"):
+            return pinned
+        rev = get_safe_version(self.repo_id, pinned or CODEBASE_VERSION, allow_branch_fallback=pinned is None)
+        self._resolved_revision = rev
+        return rev
+
     @_on_main_process_then_barrier
     def pull_from_repo(self, allow_patterns=None, ignore_patterns=None) -> None:
-        hub_client().snapshot_download(self.repo_id, revision=getattr(self, "revision", None), local_dir=Path(self.root),
+        hub_client().snapshot_download(self.repo_id, revision=self.resolved_revision(), local_dir=Path(self.root),
                                        allow_patterns=allow_patterns, ignore_patterns=ignore_patterns)
 
     @_on_main_process_then_barrier
@@ -148,7 +250,7 @@ class HubTransferMixin:
         if not missing:
             return
         logging.info("%s: %d of %d file(s) are not on disk; fetching them", self.repo_id, len(missing), len(files))
-        client, rev, root = hub_client(), getattr(self, "revision", None), Path(self.root)
+        client, rev, root = hub_client(), self.resolved_revision(), Path(self.root)
         with ThreadPoolExecutor(max_workers=DOWNLOAD_MAX_WORKERS) as pool:
             list(pool.map(lambda f: client.download_file(self.repo_id, f, revision=rev, local_dir=root), missing))
 

@@ -226,6 +226,55 @@ def test_hub_transfer_fetches_only_what_is_missing(tmp_path):
         set_hub_client(None)
 
 
+def test_hub_revision_resolution(tmp_path, caplog):
+    """Which ref is downloaded for a wanted version (reference ``src/opentau/datasets/utils.py:1004-1110``)."""
+    from opentau_b200.datasets import hub_transfer as H
+    from opentau_b200.datasets.utils import BackwardCompatibilityError
+
+    class Refs(_FakeHub):
+        def __init__(self, source, branches, tags):
+            super().__init__(source)
+            self.branches, self.tags, self.revisions = branches, tags, []
+
+        def list_refs(self, repo_id):
+            return list(self.branches), list(self.tags)
+
+        def snapshot_download(self, repo_id, *, revision, **kw):
+            self.revisions.append(revision)
+            return super().snapshot_download(repo_id, revision=revision, **kw)
+
+    def resolve(branches, tags, want="v2.1", **kw):
+        H.set_hub_client(Refs(tmp_path, branches, tags))
+        return H.get_safe_version("a/b", want, **kw)
+
+    try:
+        assert resolve(["main"], ["v2.0", "v2.1", "v3.0"]) == "v2.1"                 # carried as asked
+        with caplog.at_level("WARNING"):
+            assert resolve(["main"], ["v2.0", "v1.6"]) == "v2.0"                     # same major, older minor
+        assert "not found, using v2.0" in caplog.text
+        assert resolve(["main"], ["v3.0"]) == "v3.0"                                 # newer but still readable
+        assert resolve(["main", "v2.1"], []) == "v2.1"                               # a version BRANCH counts
+        with pytest.raises(H.ForwardCompatibilityError, match="v4.0"):
+            resolve(["main"], ["v4.0"])
+        with pytest.raises(BackwardCompatibilityError, match="v1.6"):
+            resolve(["main"], ["v1.6"])
+        with pytest.raises(H.RevisionNotFoundError, match="tagged"):
+            resolve(["main"], [])
+        assert resolve(["master", "dev"], [], allow_branch_fallback=True) == "master"
+        with pytest.raises(H.RevisionNotFoundError):
+            resolve(["dev"], [], allow_branch_fallback=True)
+        assert H.get_repo_versions("a/b") == []
+        # through the dataset: an unpinned revision resolves once, a pinned branch name is used as it is
+        _record(tmp_path / "origin", use_videos=False)
+        hub = Refs(tmp_path / "origin", ["main"], ["v2.0", "v2.1"])
+        H.set_hub_client(hub)
+        LeRobotDatasetMetadata("local/toy", root=tmp_path / "copy")
+        LeRobotDatasetMetadata("local/toy", root=tmp_path / "copy2", revision="experiment")
+        assert hub.revisions == ["v2.1", "experiment"]
+    finally:
+        H.set_hub_client(None)
+
+
 def test_push_to_hub_helpers(tmp_path):
     import pytest
 
