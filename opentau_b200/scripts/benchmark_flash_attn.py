@@ -148,10 +148,10 @@ def stacked_memory_comparison(batch: int = 2, s: int = 1024, heads: int = 8, kv_
     x0 = torch.randn(batch, s, heads, dim, device=dev).to(torch.bfloat16)
 
     def fused(q):
-        return ops.block_attention(q, k, v, blk, blk, valid, valid, scale)
+        return ops.block_attention(q, k, v, blk, blk, valid, valid, scale).reshape(q.shape)   # (B, S, H*D) -> q's
 
     def dense(q):
-        return _sdpa_dense(q, k, v, mask, scale)
+        return _sdpa_dense(q, k, v, mask, scale).reshape(q.shape)
 
     def run(layer, ckpt):
         q = x0.clone().requires_grad_(True)
@@ -186,6 +186,7 @@ def main(argv=None):
     ap.add_argument("--stacked", action="store_true", help="a stack of layers, forward + backward, with / without "
                     "activation checkpointing")
     ap.add_argument("--layers", type=int, default=18)
+    ap.add_argument("--stacked-seqs", type=int, nargs="*", default=[1024])
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("this benchmark needs a CUDA device")
@@ -193,7 +194,8 @@ def main(argv=None):
     if a.long_context:
         rows += long_context_sweep(1, a.heads, a.kv_heads, a.dim, tuple(a.long_seqs))
     if a.stacked:
-        rows += stacked_memory_comparison(min(a.batch, 2), 1024, a.heads, a.kv_heads, a.dim, a.layers)
+        for s in a.stacked_seqs:
+            rows += stacked_memory_comparison(min(a.batch, 2), s, a.heads, a.kv_heads, a.dim, a.layers)
     if a.oom_demo:
         print(json.dumps(oom_demo(a.batch, a.heads, a.kv_heads, a.dim)))
     return rows
